@@ -1,0 +1,180 @@
+// Memory-bound kernels of the step: embedding gather, RMSNorm, rotation + paged
+// key/value store, SwiGLU.  The residual stream is float32 in both precisions;
+// "activation dtype" below is what matrix products read and write (bfloat16 in
+// the serving path, float32 in the true 32-bit path).
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------
+// Embedding: x[t] = E[id_t], ids outside [0, vocab) read row 0
+// (the reference does the same on the host, src/model.c:6148-6162).
+// ---------------------------------------------------------------------------
+template <typename TW>
+__global__ void k_embed(const TW* __restrict__ table, const int* __restrict__ ids, float* __restrict__ x,
+                        int d, int vocab) {
+    int t = blockIdx.x;
+    int id = ids[t];
+    if (id < 0 || id >= vocab) id = 0;
+    const TW* row = table + (size_t)id * d;
+    float* out = x + (size_t)t * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) out[i] = xr_to_f32<TW>(row[i]);
+}
+
+XR_EXPORT int xr_embed(const void* table, int table_dtype, const int* ids, float* x, int n, int d, int vocab,
+                       cudaStream_t stream) {
+    if (n < 1 || d < 1 || vocab < 1) return XR_ERR_ARG;
+    if (table_dtype == XR_F32) k_embed<float><<<n, 256, 0, stream>>>((const float*)table, ids, x, d, vocab);
+    else if (table_dtype == XR_BF16) k_embed<__nv_bfloat16><<<n, 256, 0, stream>>>((const __nv_bfloat16*)table, ids, x, d, vocab);
+    else return XR_ERR_ARG;
+    return xr_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// RMSNorm of float32 rows: y = x * rsqrt(mean(x^2) + eps) * w
+// (src/model.c:3386-3392; the reference's kernel is src/kernels.cu:32-48).
+// `rows` (optional) picks the rows to normalise: out[i] = norm(x[rows[i]]).
+// One block per row; the reduction order depends on the width only.
+// ---------------------------------------------------------------------------
+template <typename TO>
+__global__ void k_rmsnorm(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ w,
+                          TO* __restrict__ out, int d, float eps) {
+    __shared__ float scratch[33];
+    int r = rows ? rows[blockIdx.x] : blockIdx.x;
+    const float* xr = x + (size_t)r * d;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) { float v = xr[i]; ss += v * v; }
+    ss = xr_block_sum(ss, scratch);
+    float scale = 1.0f / sqrtf(ss / (float)d + eps);
+    TO* o = out + (size_t)blockIdx.x * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = xr_from_f32<TO>(xr[i] * scale * w[i]);
+}
+
+XR_EXPORT int xr_rmsnorm(const float* x, const int* rows, const float* w, void* out, int out_dtype, int n, int d,
+                         float eps, cudaStream_t stream) {
+    if (n < 1 || d < 1) return XR_ERR_ARG;
+    int threads = d >= 2048 ? 512 : 256;
+    if (out_dtype == XR_F32) k_rmsnorm<float><<<n, threads, 0, stream>>>(x, rows, w, (float*)out, d, eps);
+    else if (out_dtype == XR_BF16) k_rmsnorm<__nv_bfloat16><<<n, threads, 0, stream>>>(x, rows, w, (__nv_bfloat16*)out, d, eps);
+    else return XR_ERR_ARG;
+    return xr_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// Rotation of Q and K and the store of K, V into their pages.
+//
+// qkv: [n, (H + 2K) * hd] rows as the fused projection wrote them (Q heads,
+// then K heads, then V heads).  For the token at position p and pair index
+// j < rotary_dim/2: a = p * inv_freq[j] in float32, then
+// (x0, x1) -> (x0 c - x1 s, x0 s + x1 c) on elements (j, j + rotary_dim/2)
+// (src/model.c:3514-3532, the half-split pairing).  Q is rotated in place; K
+// is rotated and written to the cache, V copied (src/model.c:6276-6310).
+// The cache of a layer group is [page][layer][K|V][kv head][token in page][hd];
+// `cache_k` points at this layer's K block of page 0.
+// ---------------------------------------------------------------------------
+struct RopeStoreArgs {
+    void* qkv;
+    const int* positions;
+    const int* tok_seg;
+    const int* block_tables;     // [n_seg][max_pages]
+    const float* inv_freq;       // [rotary_dim / 2] or null when rotary_dim == 0
+    void* cache_k;               // null: this layer stores nothing (it reads another layer's cache)
+    long long page_stride;       // elements between pages
+    long long v_offset;          // elements from a layer's K block to its V block
+    int n, H, K, hd, rotary_dim, max_pages, page_size;
+};
+
+template <typename T>
+__global__ void k_rope_store(RopeStoreArgs a) {
+    int t = blockIdx.x, head = blockIdx.y;
+    int qkv_dim = (a.H + 2 * a.K) * a.hd;
+    T* row = (T*)a.qkv + (size_t)t * qkv_dim + (size_t)head * a.hd;
+    int pos = a.positions[t];
+    int half = a.rotary_dim >> 1;
+    bool is_q = head < a.H, is_k = !is_q && head < a.H + a.K;
+    T* dst = nullptr;
+    if (!is_q) {
+        if (a.cache_k == nullptr) return;
+        int kvh = is_k ? head - a.H : head - a.H - a.K;
+        int page = a.block_tables[(size_t)a.tok_seg[t] * a.max_pages + pos / a.page_size];
+        dst = (T*)a.cache_k + (size_t)page * a.page_stride + (is_k ? 0 : a.v_offset) +
+              ((size_t)kvh * a.page_size + (pos % a.page_size)) * a.hd;
+    }
+    if (is_q || is_k) {
+        for (int j = threadIdx.x; j < a.hd; j += blockDim.x) {
+            if (j < half) {
+                float ang = (float)pos * a.inv_freq[j];
+                float c = cosf(ang), s = sinf(ang);
+                float x0 = xr_to_f32<T>(row[j]), x1 = xr_to_f32<T>(row[j + half]);
+                T y0 = xr_from_f32<T>(x0 * c - x1 * s), y1 = xr_from_f32<T>(x0 * s + x1 * c);
+                if (is_q) { row[j] = y0; row[j + half] = y1; }
+                else { dst[j] = y0; dst[j + half] = y1; }
+            } else if (j >= 2 * half && is_k) {
+                dst[j] = row[j];
+            }
+        }
+    } else {
+        for (int j = threadIdx.x; j < a.hd; j += blockDim.x) dst[j] = row[j];
+    }
+}
+
+XR_EXPORT int xr_rope_store(void* qkv, int dtype, const int* positions, const int* tok_seg, const int* block_tables,
+                            const float* inv_freq, void* cache_k, long long page_stride, long long v_offset,
+                            int n, int H, int K, int hd, int rotary_dim, int max_pages, int page_size,
+                            cudaStream_t stream) {
+    if (n < 1 || H < 1 || K < 1 || hd < 1 || rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1) ||
+        page_size < 1 || H + 2 * K > 65535)
+        return XR_ERR_ARG;
+    RopeStoreArgs a{qkv, positions, tok_seg, block_tables, inv_freq, cache_k, page_stride, v_offset,
+                    n, H, K, hd, rotary_dim, max_pages, page_size};
+    dim3 grid(n, H + 2 * K);
+    int threads = hd >= 128 ? 128 : (hd >= 64 ? 64 : 32);
+    if (dtype == XR_F32) k_rope_store<float><<<grid, threads, 0, stream>>>(a);
+    else if (dtype == XR_BF16) k_rope_store<__nv_bfloat16><<<grid, threads, 0, stream>>>(a);
+    else return XR_ERR_ARG;
+    return xr_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// SwiGLU: h = silu(g) * u with g, u the two halves of each row of gu [n, 2F];
+// silu(g) = g / (1 + exp(-g)), and 0 for g < -80 (src/model.c:4451-4452; the
+// reference's kernel is src/kernels.cu:2868-2874).
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void k_silu_mul(const T* __restrict__ gu, T* __restrict__ h, int n, int F) {
+    size_t total = (size_t)n * F;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        size_t t = i / F, f = i % F;
+        float g = xr_to_f32<T>(gu[t * 2 * F + f]), u = xr_to_f32<T>(gu[t * 2 * F + F + f]);
+        float v = g < -80.0f ? 0.0f : (g / (1.0f + expf(-g))) * u;
+        h[i] = xr_from_f32<T>(v);
+    }
+}
+
+XR_EXPORT int xr_silu_mul(const void* gu, void* h, int dtype, int n, int F, cudaStream_t stream) {
+    if (n < 1 || F < 1) return XR_ERR_ARG;
+    size_t total = (size_t)n * F;
+    int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    if (dtype == XR_F32) k_silu_mul<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)h, n, F);
+    else if (dtype == XR_BF16) k_silu_mul<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)h, n, F);
+    else return XR_ERR_ARG;
+    return xr_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// y[t][i] += d[t][i] on the float32 residual stream (src/kernels.cu:2903-2906),
+// for parts whose last product cannot add into the stream itself.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void k_residual_add(float* __restrict__ x, const T* __restrict__ dlt, size_t total) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+        x[i] += xr_to_f32<T>(dlt[i]);
+}
+
+XR_EXPORT int xr_residual_add(float* x, const void* dlt, int dtype, int n, int d, cudaStream_t stream) {
+    if (n < 1 || d < 1) return XR_ERR_ARG;
+    size_t total = (size_t)n * d;
+    int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    if (dtype == XR_F32) k_residual_add<float><<<blocks, 256, 0, stream>>>(x, (const float*)dlt, total);
+    else if (dtype == XR_BF16) k_residual_add<__nv_bfloat16><<<blocks, 256, 0, stream>>>(x, (const __nv_bfloat16*)dlt, total);
+    else return XR_ERR_ARG;
+    return xr_launch_status();
+}

@@ -1,0 +1,294 @@
+"""The engine: a loaded model, its cache, and ONE step function.
+
+``Engine.step`` takes a batch of (request, its next tokens, the places whose
+logits are wanted): portions of prompts beside single decoded tokens, cut
+anywhere.  It runs exactly the tokens it is given, as one flat batch, against
+the keys and values that earlier steps left in the pages, and returns float32
+logits at the wanted places.  The reference has two disjoint primitives for
+this -- ``model_forward_batch`` (n consecutive tokens of one sequence, logits
+of the last, src/model.h:667-670) and ``model_batch_decode`` (one token of each
+of n sequences, src/model.h:796-807) -- and carries the rule that a token's
+result must not depend on what else is in the batch (src/gpu.h:127-131); that
+rule holds here for any mixture.
+
+All token-parallel work (norms, products, rotation, SwiGLU) runs on the flat
+token axis; attention runs per token over its request's block table with the
+causal limit of its own position; the head runs on the gathered wanted rows
+only (the reference's `want_logits`, src/model.c:6478-6481, generalised).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import architectures  # noqa: F401  (registers the built-in architectures)
+from .. import kernels
+from ..cache.pages import CacheManager, OutOfPages
+from ..config import registry
+from ..parts.base import Runtime
+from ..weights.loader import FolderSource, RandomSource, TensorSource
+from .model import LayerRuntime, LoadedModel, ModelPlan
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+
+
+@dataclass
+class EngineParams:
+    dtype: str = "bfloat16"            # "bfloat16": serving kernels; "float32": everything in true 32 bit
+    max_tokens: int = 4096             # tokens the page pool holds (rounded up to whole pages)
+    page_size: int = 64                # tokens per page
+    max_requests: int = 4              # live requests (state slots)
+    max_request_tokens: Optional[int] = None   # longest request; default min(model limit, max_tokens)
+    max_step_tokens: int = 8192        # sizing hint for the step's buffers (they grow if a step brings more)
+    device: str = "cuda:0"
+
+
+@dataclass
+class StepEntry:
+    request: object
+    tokens: Sequence[int]
+    want: Sequence[int] = ()           # indices into `tokens` whose logits are wanted
+
+
+class StepContext:
+    """What the parts see of one step.  Tensors are on the device; `host` holds the same as numpy."""
+
+    def __init__(self, eng: "Engine"):
+        self._eng = eng
+        self.act_dtype = eng.act_dtype
+        self.page_size = eng.params.page_size
+        self.max_pages = eng.cache.max_pages_per_request
+        self.n = 0
+        self.n_seg = 0
+        self.token_ids = self.positions = self.tok_seg = self.logit_rows = None
+        self.seg_start = self.seg_len = self.seg_pos0 = self.seg_slot = None
+        self.block_tables: List[torch.Tensor] = []
+        self.host: Dict[str, np.ndarray] = {}
+        self.max_kv_len = 0            # longest key range any token of the step reads
+        self.decode_only = False       # every segment is a single token
+
+    def buf(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+        return self._eng._buf(name, shape, dtype)
+
+    def cache_layer(self, lay: LayerRuntime):
+        """(pointer to this layer's K block of page 0, elements between pages, elements from K to V)."""
+        return self._eng._cache_layer[lay.entry]
+
+
+class Engine:
+    def __init__(self, model_dir: Optional[str] = None, params: Optional[EngineParams] = None, *,
+                 config=None, architecture: Optional[str] = None, source: Optional[TensorSource] = None):
+        """Load from `model_dir` (config.json + model.safetensors), or from a typed `config` plus a tensor
+        `source` (e.g. ``RandomSource``) for an architecture name."""
+        self.params = params or EngineParams()
+        p = self.params
+        if p.dtype not in _DTYPES:
+            raise ValueError(f"dtype '{p.dtype}': choose bfloat16 or float32")
+        self.act_dtype = _DTYPES[p.dtype]
+        if not torch.cuda.is_available():
+            raise RuntimeError("the engine runs on a CUDA device only; none is visible")
+        self.device = torch.device(p.device)
+        torch.cuda.set_device(self.device)
+        kernels.lib()                      # fail now, and loudly, if the kernels cannot be built or loaded
+        if model_dir is not None:
+            arch, self.config = registry.load_config(model_dir)
+            source = FolderSource(model_dir)
+        else:
+            if config is None or source is None:
+                raise ValueError("give model_dir, or config and source")
+            arch = registry.resolve(architecture or config.architecture)
+            self.config = config
+        plan: ModelPlan = arch.build_plan(self.config)
+        rt = Runtime(self.device, self.act_dtype, p.page_size, p.max_step_tokens, p.max_requests)
+        self.model = LoadedModel(plan, source, rt)
+        self.plan = plan
+        n_pages = max(1, -(-p.max_tokens // p.page_size))
+        max_req = p.max_request_tokens or min(plan.max_positions, n_pages * p.page_size)
+        self.cache = CacheManager([g.spec for g in self.model.groups] or [], n_pages, p.page_size,
+                                  p.max_requests, max_req)
+        # device arrays of keys and values: [page][layer in group][K|V][kv head][token in page][head_dim]
+        self.kv: List[torch.Tensor] = []
+        for g in self.model.groups:
+            self.kv.append(torch.zeros((n_pages, g.n_layers, 2, g.kv_heads, p.page_size, g.head_dim),
+                                       dtype=self.act_dtype, device=self.device))
+        self._cache_layer: Dict[int, tuple] = {}
+        for lay in self.model.layers:
+            if lay.group >= 0:
+                t = self.kv[lay.group]
+                es = t.element_size()
+                self._cache_layer[lay.entry] = (t.data_ptr() + lay.layer_in_group * t.stride(1) * es,
+                                                t.stride(0), t.stride(2))
+        for entry, need in self.model.state_needs:
+            self.model.layers[entry].state = torch.zeros((p.max_requests,) + tuple(need.shape), dtype=need.dtype,
+                                                         device=self.device)
+        self._bufs: Dict[tuple, torch.Tensor] = {}
+        # step descriptions go through a small ring of pinned buffers; an event per buffer says when the
+        # copy that read it has run, so the host never rewrites memory that a copy in flight still reads
+        self._pinned: List[Optional[torch.Tensor]] = [None] * 3
+        self._pinned_done: List[Optional[torch.cuda.Event]] = [None] * 3
+        self._pinned_next = 0
+        self._slot_generation = np.zeros(p.max_requests, dtype=np.int64)
+        self.steps_run = 0
+
+    # ---- buffers ---------------------------------------------------------------
+    def _buf(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        key = (name, dtype)
+        t = self._bufs.get(key)
+        if t is None or t.numel() < n:
+            cap = n
+            if t is None and len(shape) == 2 and shape[0] < self.params.max_step_tokens and name != "logits":
+                cap = self.params.max_step_tokens * int(shape[1])
+            t = torch.empty(max(cap, 1), dtype=dtype, device=self.device)
+            self._bufs[key] = t
+        return t[:n].view(*shape)
+
+    # ---- requests ----------------------------------------------------------------
+    def is_live(self, request) -> bool:
+        return self.cache.is_open(request)
+
+    def length(self, request) -> int:
+        return self.cache.length(request)
+
+    def end(self, request) -> None:
+        """The request is finished: its pages and its state slot are given back."""
+        self.cache.close(request)
+
+    def _open(self, request) -> int:
+        slot = self.cache.open(request)
+        for lay in self.model.layers:
+            if lay.state is not None:
+                lay.state[slot].zero_()
+        return slot
+
+    # ---- the step ----------------------------------------------------------------
+    def step(self, entries: Sequence[StepEntry], reserved: bool = False) -> torch.Tensor:
+        """Run one batch.  Returns float32 logits [number of wanted places, vocab] on the device, in the
+        order of the entries and of each entry's `want`; the tensor is reused by the next step.
+
+        Unless `reserved`, pages for every entry's tokens are taken here (all or nothing: on
+        ``OutOfPages`` the cache is as before the call).  A request not seen before is opened."""
+        entries = [e for e in entries if len(e.tokens) > 0]
+        if not entries:
+            return torch.empty((0, self.plan.vocab_size), dtype=torch.float32, device=self.device)
+        seen = set()
+        for e in entries:
+            if e.request in seen:
+                raise ValueError(f"request {e.request!r} appears twice in one step")
+            seen.add(e.request)
+            for w in e.want:
+                if not (0 <= w < len(e.tokens)):
+                    raise ValueError(f"request {e.request!r}: wanted place {w} is outside its {len(e.tokens)} tokens")
+        opened, taken = [], []
+        if not reserved:
+            try:
+                for e in entries:
+                    if not self.cache.is_open(e.request):
+                        self._open(e.request)
+                        opened.append(e.request)
+                    self.cache.reserve(e.request, len(e.tokens))
+                    taken.append(e.request)
+            except OutOfPages:
+                for r in taken:
+                    self.cache.cancel(r)
+                for r in opened:
+                    self.cache.close(r)
+                raise
+        ctx = self._describe(entries)
+        logits = self._forward(ctx)
+        for e in entries:
+            self.cache.commit(e.request)
+        self.steps_run += 1
+        return logits
+
+    def _describe(self, entries: Sequence[StepEntry]) -> StepContext:
+        """Flatten the batch and bring its description to the device in one copy."""
+        cache = self.cache
+        S = len(entries)
+        n = sum(len(e.tokens) for e in entries)
+        R = sum(len(e.want) for e in entries)
+        G = len(cache.groups)
+        mp = cache.max_pages_per_request
+        sizes = [n, n, n, max(R, 1), S, S, S, S] + [S * mp] * G
+        offs = np.concatenate([[0], np.cumsum([(s + 3) // 4 * 4 for s in sizes])]).astype(np.int64)
+        total = int(offs[-1])
+        slot_i = self._pinned_next
+        self._pinned_next = (slot_i + 1) % len(self._pinned)
+        if self._pinned_done[slot_i] is not None:
+            self._pinned_done[slot_i].synchronize()
+        if self._pinned[slot_i] is None or self._pinned[slot_i].numel() < total:
+            self._pinned[slot_i] = torch.empty(max(total, 1 << 16), dtype=torch.int32).pin_memory()
+        pinned = self._pinned[slot_i]
+        host = pinned.numpy()
+        tok, pos, seg, rows, s_start, s_len, s_pos0, s_slot = (host[offs[i]:offs[i] + sizes[i]] for i in range(8))
+        at, ri, max_kv = 0, 0, 0
+        decode_only = True
+        for si, e in enumerate(entries):
+            m = len(e.tokens)
+            p0 = cache.length(e.request)
+            tok[at:at + m] = np.asarray(e.tokens, dtype=np.int64).astype(np.int32)
+            pos[at:at + m] = np.arange(p0, p0 + m, dtype=np.int32)
+            seg[at:at + m] = si
+            for w in e.want:
+                rows[ri] = at + w
+                ri += 1
+            s_start[si], s_len[si], s_pos0[si], s_slot[si] = at, m, p0, cache.slot_of(e.request)
+            max_kv = max(max_kv, p0 + m)
+            decode_only &= (m == 1)
+            at += m
+        for g in range(G):
+            bt = host[offs[8 + g]:offs[8 + g] + S * mp].reshape(S, mp)
+            for si, e in enumerate(entries):
+                bt[si] = cache.block_table(g, e.request)
+        dev = self._buf("step_description", (total,), torch.int32)
+        dev.copy_(pinned[:total], non_blocking=True)
+        if self._pinned_done[slot_i] is None:
+            self._pinned_done[slot_i] = torch.cuda.Event()
+        self._pinned_done[slot_i].record()
+        ctx = StepContext(self)
+        ctx.n, ctx.n_seg, ctx.n_rows = n, S, R
+        view = lambda i: dev[int(offs[i]):int(offs[i]) + sizes[i]]
+        ctx.token_ids, ctx.positions, ctx.tok_seg, ctx.logit_rows = view(0), view(1), view(2), view(3)
+        ctx.seg_start, ctx.seg_len, ctx.seg_pos0, ctx.seg_slot = view(4), view(5), view(6), view(7)
+        ctx.block_tables = [view(8 + g).view(S, mp) for g in range(G)]
+        ctx.host = {"token_ids": tok.copy(), "positions": pos.copy(), "tok_seg": seg.copy(), "logit_rows": rows[:R].copy(),
+                    "seg_start": s_start.copy(), "seg_len": s_len.copy(), "seg_pos0": s_pos0.copy(),
+                    "seg_slot": s_slot.copy()}
+        ctx.max_kv_len, ctx.decode_only = max_kv, decode_only
+        return ctx
+
+    def _forward(self, ctx: StepContext) -> torch.Tensor:
+        plan = self.plan
+        x = ctx.buf("residual", (ctx.n, plan.width), torch.float32)
+        plan.embedding.forward(ctx, ctx.token_ids, x)
+        for lay in self.model.layers:
+            plan.blocks[plan.schedule[lay.entry].layer].forward(ctx, x, lay)
+        if ctx.n_rows == 0:
+            return torch.empty((0, plan.vocab_size), dtype=torch.float32, device=self.device)
+        hn = ctx.buf("head_normed", (ctx.n_rows, plan.width), ctx.act_dtype)
+        plan.final_norm.forward(ctx, x, hn, rows=ctx.logit_rows)
+        logits = ctx.buf("logits", (ctx.n_rows, plan.vocab_size), torch.float32)
+        plan.head.forward(ctx, hn, logits)
+        return logits
+
+    # ---- accounting (bench) ---------------------------------------------------------
+    def weight_bytes_per_step(self) -> int:
+        return self.model.weight_bytes_per_step()
+
+    def kv_bytes_per_token(self) -> int:
+        return self.model.kv_bytes_per_token(2 if self.act_dtype == torch.bfloat16 else 4)
+
+
+def random_engine(config, seed: int, params: EngineParams, std: float = 0.02, norm_jitter: float = 0.01,
+                  weight_dtype: Optional[torch.dtype] = None) -> Engine:
+    """An engine with seeded random weights generated on the device (nothing is written to disk)."""
+    arch = registry.resolve(config.architecture)
+    plan = arch.build_plan(config)
+    wd = weight_dtype or _DTYPES.get(getattr(config, "torch_dtype", "bfloat16"), torch.bfloat16)
+    src = RandomSource(plan.tensor_specs(), seed, wd, std=std, norm_jitter=norm_jitter, gen_device=params.device)
+    return Engine(params=params, config=config, source=src)

@@ -1,0 +1,193 @@
+"""Python face of the CUDA library: one function per launcher, torch tensors in.
+
+Every function checks what the kernel cannot (device, dtype, contiguity),
+launches on torch's current stream and raises on a refusal.  Nothing here has
+another way to compute its result: if the library cannot be built or loaded,
+the first call raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .csrc import build as _build
+
+F32, BF16 = 0, 1
+_ERR = {-1: "the kernel refuses these sizes or dtypes", -2: "CUDA refused the launch", -3: "tensor map encoding failed",
+        -4: "size beyond the entry point's fixed limit", -5: "set-up of the entry point failed"}
+
+_lib = None
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        path = _build.library_path()
+        try:
+            _lib = ctypes.CDLL(path)
+        except OSError as e:
+            raise KernelError(f"cannot load {path}: {e}") from None
+        _declare(_lib)
+    return _lib
+
+
+def library_file() -> str:
+    lib()
+    return _build.library_path(build=False)
+
+
+_vp, _i, _ll, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+
+
+def _declare(L: ctypes.CDLL) -> None:
+    sig = {
+        "xr_embed": [_vp, _i, _vp, _vp, _i, _i, _i, _vp],
+        "xr_rmsnorm": [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
+        "xr_rope_store": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _vp],
+        "xr_silu_mul": [_vp, _vp, _i, _i, _i, _vp],
+        "xr_residual_add": [_vp, _vp, _i, _i, _i, _vp],
+        "xr_gemm_simt": [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _ll, _ll, _vp],
+        "xr_attention_simt": [_vp, _vp, _i, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
+        "xr_sample": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
+    }
+    for name, args in sig.items():
+        fn = getattr(L, name)
+        fn.argtypes = args
+        fn.restype = ctypes.c_int
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise KernelError(f"{what}: {_ERR.get(code, f'error {code}')}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return F32
+    if dt == torch.bfloat16:
+        return BF16
+    raise KernelError(f"dtype {dt} is not float32 or bfloat16")
+
+
+def _dev(*ts) -> None:
+    for t in ts:
+        if t is not None and (not t.is_cuda or not t.is_contiguous()):
+            raise KernelError("kernel arguments must be contiguous CUDA tensors")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+launch_count = 0   # kernels launched through this module since import (bench reports it)
+
+
+def _count(n: int = 1) -> None:
+    global launch_count
+    launch_count += n
+
+
+# ---------------------------------------------------------------------------
+def embed(table: torch.Tensor, ids: torch.Tensor, x: torch.Tensor) -> None:
+    """x[t] = table[ids[t]] widened to float32; ids outside the table read row 0."""
+    _dev(table, ids, x)
+    n, d = x.shape
+    assert ids.dtype == torch.int32 and ids.numel() >= n and x.dtype == torch.float32 and table.shape[1] == d
+    _check(lib().xr_embed(table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(), x.data_ptr(), n, d,
+                          table.shape[0], _stream()), "embed")
+    _count()
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, eps: float, rows: Optional[torch.Tensor] = None) -> None:
+    """out[i] = x[rows[i] or i] * rsqrt(mean(x^2) + eps) * w; x float32, w float32."""
+    _dev(x, w, out, rows)
+    n, d = out.shape
+    assert x.dtype == torch.float32 and w.dtype == torch.float32 and x.shape[1] == d and w.numel() == d
+    assert rows is None or (rows.dtype == torch.int32 and rows.numel() >= n)
+    _check(lib().xr_rmsnorm(x.data_ptr(), _ptr(rows), w.data_ptr(), out.data_ptr(), dtype_code(out.dtype), n, d,
+                            float(eps), _stream()), "rmsnorm")
+    _count()
+
+
+def rope_store(qkv: torch.Tensor, positions, tok_seg, block_tables, inv_freq: Optional[torch.Tensor],
+               cache_k_ptr: Optional[int], page_stride: int, v_offset: int, H: int, K: int, hd: int,
+               rotary_dim: int, max_pages: int, page_size: int) -> None:
+    """Rotate Q in place, rotate K and store K, V into their pages (cache_k_ptr None: store nothing)."""
+    _dev(qkv, positions, tok_seg, block_tables, inv_freq)
+    n = qkv.shape[0]
+    assert qkv.shape[1] == (H + 2 * K) * hd
+    assert rotary_dim == 0 or (inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() >= rotary_dim // 2)
+    _check(lib().xr_rope_store(qkv.data_ptr(), dtype_code(qkv.dtype), positions.data_ptr(), tok_seg.data_ptr(),
+                               block_tables.data_ptr(), _ptr(inv_freq), cache_k_ptr, page_stride, v_offset,
+                               n, H, K, hd, rotary_dim, max_pages, page_size, _stream()), "rope_store")
+    _count()
+
+
+def silu_mul(gu: torch.Tensor, h: torch.Tensor) -> None:
+    _dev(gu, h)
+    n, F = h.shape
+    assert gu.shape == (n, 2 * F) and gu.dtype == h.dtype
+    _check(lib().xr_silu_mul(gu.data_ptr(), h.data_ptr(), dtype_code(h.dtype), n, F, _stream()), "silu_mul")
+    _count()
+
+
+def residual_add(x: torch.Tensor, delta: torch.Tensor) -> None:
+    _dev(x, delta)
+    n, d = x.shape
+    assert x.dtype == torch.float32 and delta.shape == x.shape
+    _check(lib().xr_residual_add(x.data_ptr(), delta.data_ptr(), dtype_code(delta.dtype), n, d, _stream()), "residual_add")
+    _count()
+
+
+def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+              accumulate: bool = False) -> None:
+    """out[t][r] (+)= sum_k x[t][k] w[r][k] (+ bias[r]) in float32 FMA.  Rows of x and out may be strided."""
+    for t in (x, w, out, bias):
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernel arguments must be CUDA tensors")
+    n, k = x.shape
+    n_out = w.shape[0]
+    assert w.shape[1] == k and out.shape == (n, n_out) and w.is_contiguous()
+    assert x.stride(1) == 1 and out.stride(1) == 1
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == n_out)
+    _check(lib().xr_gemm_simt(x.data_ptr(), dtype_code(x.dtype), w.data_ptr(), dtype_code(w.dtype), _ptr(bias),
+                              out.data_ptr(), dtype_code(out.dtype), int(accumulate), n, n_out, k,
+                              x.stride(0), out.stride(0), _stream()), "gemm_simt")
+    _count()
+
+
+def attention_simt(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, cache_k_ptr: int, positions, tok_seg,
+                   block_tables, page_stride: int, v_offset: int, H: int, K: int, hd: int, max_pages: int,
+                   page_size: int, window: int, scale: float) -> None:
+    """Causal attention of every token of the step over its request's pages, float32 arithmetic."""
+    _dev(out, positions, tok_seg, block_tables)
+    n = out.shape[0]
+    assert out.shape[1] == H * hd and q.dtype == out.dtype
+    _check(lib().xr_attention_simt(q.data_ptr(), out.data_ptr(), dtype_code(out.dtype), cache_k_ptr,
+                                   positions.data_ptr(), tok_seg.data_ptr(), block_tables.data_ptr(), page_stride,
+                                   v_offset, q_row_stride, n, H, K, hd, max_pages, page_size, window, float(scale),
+                                   _stream()), "attention_simt")
+    _count()
+
+
+def sample(logits: torch.Tensor, temp, top_k, top_p, min_p, penalty, draw, recent: Optional[torch.Tensor],
+           scratch: torch.Tensor, out: torch.Tensor) -> None:
+    """One token per row of float32 logits by the reference's sampling chain (see csrc/sampling.cu)."""
+    _dev(temp, top_k, top_p, min_p, penalty, draw, recent, scratch, out)
+    rows, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and scratch.numel() >= rows * V
+    assert out.dtype == torch.int32 and top_k.dtype == torch.int32
+    _check(lib().xr_sample(logits.data_ptr(), logits.stride(0), rows, V, temp.data_ptr(), top_k.data_ptr(),
+                           top_p.data_ptr(), min_p.data_ptr(), penalty.data_ptr(), draw.data_ptr(), _ptr(recent),
+                           scratch.data_ptr(), out.data_ptr(), _stream()), "sample")
+    _count()

@@ -1,0 +1,85 @@
+"""Grouped-query causal attention over the paged cache.
+
+q = Wq h (+bq), k = Wk h (+bk), v = Wv h (+bv) as one fused product; Q and K are
+rotated by the position encoding after the projection and before the cache
+write, V is stored as it is (src/model.c:6243-6310).  Query head h reads kv
+head h / (H/K); scores are (q . k) * scale over the keys t0..p, softmax in
+float32, weighted sum of V (src/model.c:3548-3589); then x += Wo o (+bo)
+(src/model.c:6338, 6350-6352).  Heads, kv heads, head size, scale, window and
+position encoding are all arguments.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from .. import kernels
+from ..weights.loader import TensorSpec
+from .base import KVNeed, Mixer, PositionEncoding, register_mixer
+from .linear import Linear
+
+
+class GQAAttention(Mixer):
+    def __init__(self, width: int, heads: int, kv_heads: int, head_dim: int, position: PositionEncoding,
+                 prefix: str, bias: bool = False, window: Optional[int] = None, scale: Optional[float] = None,
+                 q: str = "q_proj", k: str = "k_proj", v: str = "v_proj", o: str = "o_proj"):
+        if heads % kv_heads:
+            raise ValueError("heads must be a multiple of kv_heads")
+        if head_dim % 16 or head_dim > 256:
+            raise ValueError(f"head_dim {head_dim}: the attention kernels take multiples of 16 up to 256")
+        self.width, self.H, self.K, self.hd = width, heads, kv_heads, head_dim
+        self.position, self.prefix, self.bias, self.window = position, prefix, bias, window
+        self.scale = 1.0 / math.sqrt(head_dim) if scale is None else float(scale)   # src/model.h:464-467
+        self.proj = (q, k, v, o)
+        self.qkv = self.out = None
+
+    def kv_need(self):
+        return KVNeed(self.K, self.hd, self.window)
+
+    def tensors(self):
+        q, k, v, o = (self.prefix + n for n in self.proj)
+        qd, kd = self.H * self.hd, self.K * self.hd
+        t = {q + ".weight": TensorSpec((qd, self.width)), k + ".weight": TensorSpec((kd, self.width)),
+             v + ".weight": TensorSpec((kd, self.width)), o + ".weight": TensorSpec((self.width, qd))}
+        if self.bias:
+            t.update({q + ".bias": TensorSpec((qd,), "vector", "zeros"), k + ".bias": TensorSpec((kd,), "vector", "zeros"),
+                      v + ".bias": TensorSpec((kd,), "vector", "zeros"), o + ".bias": TensorSpec((self.width,), "vector", "zeros")})
+        return t
+
+    def bind(self, tensors, rt):
+        q, k, v, o = (self.prefix + n for n in self.proj)
+        ws = [tensors.pop(n + ".weight") for n in (q, k, v)]
+        if len({w.dtype for w in ws}) > 1:
+            ws = [w.to(torch.float32) for w in ws]
+        bias = obias = None
+        if self.bias:
+            bias = torch.cat([tensors[n + ".bias"].to(torch.float32) for n in (q, k, v)])
+            obias = tensors[o + ".bias"]
+        self.qkv = Linear(torch.cat(ws, dim=0), bias)
+        del ws
+        self.out = Linear(tensors[o + ".weight"], obias)
+        self.position.prepare(rt)
+
+    def weight_bytes(self):
+        return self.qkv.nbytes() + self.out.nbytes()
+
+    def forward(self, ctx, h, x, lay):
+        n = h.shape[0]
+        qkv_dim = (self.H + 2 * self.K) * self.hd
+        qkv = ctx.buf("attn_qkv", (n, qkv_dim), ctx.act_dtype)
+        self.qkv.forward(h, qkv)
+        k_ptr, page_stride, v_offset = ctx.cache_layer(lay)
+        bt = ctx.block_tables[lay.group]
+        kernels.rope_store(qkv, ctx.positions, ctx.tok_seg, bt, self.position.inv_freq,
+                           k_ptr if lay.writes_cache else None, page_stride, v_offset,
+                           self.H, self.K, self.hd, self.position.rotary_dim, ctx.max_pages, ctx.page_size)
+        o = ctx.buf("attn_out", (n, self.H * self.hd), ctx.act_dtype)
+        # Q is read in place from the fused rows (row stride = qkv_dim)
+        kernels.attention_simt(qkv, qkv_dim, o, k_ptr, ctx.positions, ctx.tok_seg, bt, page_stride, v_offset,
+                               self.H, self.K, self.hd, ctx.max_pages, ctx.page_size, self.window or 0, self.scale)
+        self.out.forward(o, x, accumulate=True)
+
+
+register_mixer("gqa_attention", GQAAttention)

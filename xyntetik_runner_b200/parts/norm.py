@@ -1,0 +1,30 @@
+"""RMSNorm: y = x * rsqrt(mean(x^2) + eps) * w, computed in float32 (src/model.c:3386-3392)."""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..weights.loader import TensorSpec
+from .base import Norm, register_norm
+
+
+class RMSNorm(Norm):
+    def __init__(self, width: int, eps: float, name: str):
+        self.width, self.eps, self.name = width, float(eps), name
+        self.weight = None
+
+    def tensors(self):
+        return {self.name: TensorSpec((self.width,), kind="vector", init="ones_jitter")}
+
+    def bind(self, tensors, rt):
+        # norm weights are used in float32 whatever they were stored in (src/model.c:2830-2831)
+        self.weight = tensors[self.name].to(torch.float32).contiguous()
+
+    def weight_bytes(self):
+        return self.width * 4
+
+    def forward(self, ctx, x, out, rows=None):
+        kernels.rmsnorm(x, self.weight, out, self.eps, rows)
+
+
+register_norm("rmsnorm", RMSNorm)
