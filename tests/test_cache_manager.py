@@ -1,0 +1,124 @@
+"""The cache manager's bookkeeping: no page lost, held twice or freed twice, under random request orders."""
+import numpy as np
+import pytest
+
+from xyntetik_runner_b200.cache.pages import CacheError, CacheManager, GroupSpec, OutOfPages, PagePool
+
+
+def test_pool_rules():
+    p = PagePool(3)
+    a, b, c = p.take(), p.take(), p.take()
+    assert sorted([a, b, c]) == [0, 1, 2] and p.n_free == 0
+    with pytest.raises(OutOfPages):
+        p.take()
+    p.give(b)
+    with pytest.raises(CacheError):
+        p.give(b)                      # freed twice
+    with pytest.raises(CacheError):
+        p.give(7)
+    assert p.take() == b               # used again
+
+
+def test_reserve_commit_cancel_close():
+    m = CacheManager([GroupSpec("full")], n_pages=6, page_size=4, max_requests=2, max_request_tokens=24)
+    s = m.open("a")
+    assert s in (0, 1) and m.length("a") == 0
+    m.reserve("a", 5)                  # 2 pages
+    assert m.free_pages() == [4] and (m.block_table(0, "a")[:2] >= 0).all() and m.block_table(0, "a")[2] == -1
+    m.audit()
+    m.cancel("a")                      # a planned step that never ran gives its pages back
+    assert m.free_pages() == [6] and m.length("a") == 0
+    m.reserve("a", 5); m.commit("a")
+    assert m.length("a") == 5
+    m.reserve("a", 3); m.commit("a")   # 8 tokens: still 2 pages
+    assert m.free_pages() == [4]
+    m.reserve("a", 1)                  # 9th token: a third page
+    assert m.free_pages() == [3]
+    m.cancel("a")
+    assert m.free_pages() == [4] and m.length("a") == 8
+    m.open("b")
+    with pytest.raises(OutOfPages):
+        m.open("c")                    # no slot
+    with pytest.raises(OutOfPages):
+        m.reserve("b", 17)             # 5 pages, 4 free: nothing is taken
+    assert m.free_pages() == [4]
+    m.audit()
+    with pytest.raises(OutOfPages):
+        m.reserve("a", 17)             # beyond the longest request
+    m.close("a"); m.close("b")
+    assert m.free_pages() == [6]
+    with pytest.raises(CacheError):
+        m.close("a")
+    m.audit()
+
+
+def test_window_group_releases_pages_behind_the_window():
+    m = CacheManager([GroupSpec("full"), GroupSpec("w", window=6)], n_pages=8, page_size=4, max_requests=2,
+                     max_request_tokens=32)
+    m.open("a")
+    m.reserve("a", 10); m.commit("a")          # positions 0..9: 3 pages in both groups
+    assert m.free_pages() == [5, 5]
+    m.reserve("a", 1); m.commit("a")           # query at 10 sees keys 5..10: page 0 (0..3) is behind the window
+    assert m.free_pages() == [5, 6]
+    assert m.block_table(1, "a")[0] == -1 and m.block_table(0, "a")[0] >= 0
+    m.audit()
+    for _ in range(13):
+        m.reserve("a", 1); m.commit("a")       # up to 24 tokens
+    assert m.length("a") == 24
+    # window group holds pages for keys 18.. only (pages 4, 5); the full group all six
+    assert m.free_pages() == [2, 6]
+    m.audit()
+    m.close("a")
+    assert m.free_pages() == [8, 8]
+    m.audit()
+
+
+def test_window_lets_a_long_request_live_in_a_small_pool():
+    m = CacheManager([GroupSpec("w", window=5)], n_pages=4, page_size=4, max_requests=1, max_request_tokens=400)
+    m.open("a")
+    for i in range(300):
+        assert m.can_reserve("a", 1)
+        m.reserve("a", 1); m.commit("a")
+        m.audit()
+    assert m.high_water[0] <= 3
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_orders_keep_the_invariants(seed):
+    rng = np.random.RandomState(seed)
+    groups = [GroupSpec("full"), GroupSpec("w", window=int(rng.randint(3, 20)))] if seed % 2 else [GroupSpec("full")]
+    ps = int(rng.choice([1, 4, 8, 16]))
+    m = CacheManager(groups, n_pages=int(rng.randint(8, 30)), page_size=ps, max_requests=4, max_request_tokens=ps * 12)
+    live, next_id, held_pages = {}, 0, None
+    for it in range(600):
+        op = rng.rand()
+        if op < 0.2 and m.has_free_slot():
+            m.open(next_id); live[next_id] = 0; next_id += 1
+        elif op < 0.75 and live:
+            rid = list(live)[rng.randint(len(live))]
+            n = int(rng.randint(1, 3 * ps))
+            before = m.free_pages()
+            if m.can_reserve(rid, n):
+                m.reserve(rid, n)
+                if rng.rand() < 0.15:
+                    m.cancel(rid)
+                    # cancel restores the pool except for pages the window let go
+                    assert all(a >= b for a, b in zip(m.free_pages(), before))
+                else:
+                    m.commit(rid); live[rid] += n
+            else:
+                with pytest.raises(OutOfPages):
+                    m.reserve(rid, n)
+                assert m.free_pages() == before        # a failed reservation takes nothing
+        elif live:
+            rid = list(live)[rng.randint(len(live))]
+            m.close(rid); del live[rid]
+        m.audit()
+        for rid, n in live.items():
+            assert m.length(rid) == n
+            tab = m.block_table(0, rid)
+            assert (tab[:-(-n // ps)] >= 0).all() and (tab[-(-n // ps):] == -1).all()     # full group: ceil(len/ps) pages
+    for rid in list(live):
+        m.close(rid)
+    m.audit()
+    assert m.free_pages() == [p.n_pages for p in m.pools]

@@ -1,0 +1,163 @@
+"""Generation through the Python entry point and the command line, against the plain implementation."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import tiny
+import traces
+from plain_llama import PlainLlama, sample_chain, uniform_from_state, xorshift64
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    return {(n, dt): tiny.make_folder(str(tmp_path_factory.mktemp(f"g{n}{dt}")), n, dt)
+            for n in "AB" for dt in ("float32", "bfloat16")}
+
+
+def check_against_plain(plain, prompt, generated, temp, seed, near_tie, **chain):
+    """Teacher-forced: every generated token must be what the plain implementation picks for the same
+    prefix and the same draw, unless the plain pick itself was within `near_tie` of another outcome."""
+    state = seed
+    excused = 0
+    for i, tok in enumerate(generated):
+        lg = plain.logits(list(prompt) + list(generated[:i]))[-1]
+        r = 0.0
+        if temp > 0:
+            state = xorshift64(state)
+            r = uniform_from_state(state)
+        pick, margin = sample_chain(lg, r, temp, with_margin=True, **chain)
+        if pick != tok:
+            assert margin < near_tie, f"token {i}: engine {tok}, plain {pick} with margin {margin:.3e}"
+            excused += 1
+    return excused
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_workload_a_greedy(folders, dtype):
+    """Three requests, prompts of 5/11/17 tokens, 16 greedy steps each, pages of 16."""
+    from xyntetik_runner_b200.engine.runner import Runner
+    folder = folders["A", dtype]
+    plain = PlainLlama(folder)
+    prompts = [traces.random_tokens(i, n, 256) for i, n in enumerate((5, 11, 17))]
+    r = Runner(folder, dtype=dtype, ctx=128, parallel=3, page_size=16)
+    res = r.generate(prompts, n=16, temp=0.0, ignore_eos=True)
+    for p, g in zip(prompts, res):
+        assert len(g.tokens) == 16 and g.finish_reason == "length"
+        if dtype == "float32":
+            assert g.tokens == plain.generate_greedy(p, 16)
+        else:
+            assert check_against_plain(plain, p, g.tokens, 0.0, 0, near_tie=0.08) <= 2
+    r.engine.cache.audit()
+    assert not r.engine.cache.live_requests()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_workload_b_temperature_chunked(folders, dtype):
+    """Four requests, prompts of 1/9/33/70 tokens, prefill in portions of 24 mixed with decoding, 20 steps at
+    temperature 0.8 with fixed seeds, pages of 8."""
+    from xyntetik_runner_b200.engine.runner import Runner
+    folder = folders["B", dtype]
+    plain = PlainLlama(folder)
+    prompts = [traces.random_tokens(10 + i, n, 387) for i, n in enumerate((1, 9, 33, 70))]
+    r = Runner(folder, dtype=dtype, ctx=128, parallel=4, page_size=8, batch=40, prefill_chunk=24)
+    res = r.generate(prompts, n=20, temp=0.8, seed=77, ignore_eos=True)
+    assert r.scheduler.stats["max_batch"] >= 3
+    tie = 1e-4 if dtype == "float32" else 2e-2
+    for i, (p, g) in enumerate(zip(prompts, res)):
+        assert len(g.tokens) == 20
+        assert check_against_plain(plain, p, g.tokens, 0.8, 77 + i, near_tie=tie) <= (0 if dtype == "float32" else 2)
+    # the same seeds give the same tokens whatever the batching
+    r2 = Runner(folder, dtype=dtype, ctx=128, parallel=1, page_size=64)
+    for i, (p, g) in enumerate(zip(prompts, res)):
+        alone = r2.generate(p, n=20, temp=0.8, seed=77 + i, ignore_eos=True)
+        if dtype == "float32":
+            assert alone.tokens == g.tokens
+
+
+def test_full_chain_options(folders):
+    from xyntetik_runner_b200.engine.runner import Runner
+    folder = folders["B", "float32"]
+    plain = PlainLlama(folder)
+    p = traces.random_tokens(3, 12, 387)
+    r = Runner(folder, dtype="float32", ctx=128, parallel=1, page_size=8)
+    g = r.generate(p, n=24, temp=1.3, top_k=40, top_p=0.9, min_p=0.02, repeat_penalty=1.3, seed=9, ignore_eos=True)
+    # the plain chain needs the penalty window: prompt and generated tokens so far
+    state = 9
+    for i, tok in enumerate(g.tokens):
+        lg = plain.logits(p + g.tokens[:i])[-1]
+        state = xorshift64(state)
+        pick, margin = sample_chain(lg, uniform_from_state(state), 1.3, top_k=40, top_p=0.9, min_p=0.02,
+                                    repeat_penalty=1.3, recent=(p + g.tokens[:i])[-256:], with_margin=True)
+        assert pick == tok or margin < 1e-4, (i, tok, pick, margin)
+
+
+def test_stop_ids_end_a_request(folders):
+    from xyntetik_runner_b200.engine.runner import Runner
+    folder = folders["A", "float32"]
+    plain = PlainLlama(folder)
+    p = traces.random_tokens(8, 9, 256)
+    free = plain.generate_greedy(p, 12)
+    r = Runner(folder, dtype="float32", ctx=128, parallel=1, page_size=16)
+    rid = r.submit(p, n=12, stop_ids=[free[5]])
+    while r.scheduler.has_work():
+        r.scheduler.step()
+    q = r.scheduler.finished[rid]
+    first = free.index(free[5])
+    assert q.finish_reason == "stop" and q.generated == free[:first]
+
+
+def test_starved_pool_preempts_and_gives_the_same_tokens(folders):
+    from xyntetik_runner_b200.engine.runner import Runner
+    folder = folders["A", "float32"]
+    prompts = [traces.random_tokens(40 + i, n, 256) for i, n in enumerate((30, 22, 27, 18))]
+    ample = Runner(folder, dtype="float32", ctx=128, parallel=4, page_size=8)
+    want = [g.tokens for g in ample.generate(prompts, n=40, temp=0.0, ignore_eos=True)]
+    tight = Runner(folder, dtype="float32", ctx=128, parallel=4, page_size=8, max_tokens=20 * 8)
+    got = tight.generate(prompts, n=40, temp=0.0, ignore_eos=True)
+    assert tight.scheduler.stats["preemptions"] >= 1
+    assert [g.tokens for g in got] == want
+    tight.engine.cache.audit()
+    assert tight.engine.cache.free_pages() == [20]
+
+
+def test_command_line(folders, tmp_path):
+    folder = folders["A", "float32"]
+    plain = PlainLlama(folder)
+    ids = [65, 66, 67, 68, 69]
+    want = plain.generate_greedy([1] + ids, 6)          # BOS (id 1) is prepended
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "runner"), "-m", folder, "-p", "ABCDE", "-n", "6",
+                          "--temp", "0", "--ignore-eos", "--dtype", "float32", "-c", "64"],
+                         capture_output=True, text=True, env=env, timeout=300)
+    assert out.returncode == 0, out.stderr
+    assert out.stdout.splitlines()[0] == "ids:" + ",".join(map(str, want))
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "runner"), "-m", folder, "-p", "ids:3,4", "-s", "0",
+                          "--temp", "0.5"], capture_output=True, text=True, env=env, timeout=300)
+    assert out.returncode == 2 and "refused" in out.stderr
+
+
+def test_trace_run_program(folders, tmp_path):
+    """bin/trace_run as a user runs it: steps on standard input, <step>.f32 files and `done` lines out."""
+    folder = folders["B", "bfloat16"]
+    reqs = {"a": traces.random_tokens(1, 45, 387), "b": traces.random_tokens(2, 70, 387)}
+    steps = traces.mixed(reqs, seed=5, max_live=2)
+    out_dir = tmp_path / "out"
+    env = dict(os.environ, PYTHONPATH="")
+    p = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", "bfloat16", "--out",
+                        str(out_dir), "--max-tokens", str(traces.pool_tokens(steps))],
+                       input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, env=env,
+                       timeout=300)
+    assert p.returncode == 0, p.stderr
+    assert p.stdout.split() == [w for s in steps for w in ("done", str(s["step"]))]
+    res = {s["step"]: np.fromfile(out_dir / f"{s['step']}.f32", dtype="<f4") for s in steps}
+    got = traces.collect(steps, res, 387)
+    plain = PlainLlama(folder)
+    for rid, toks in reqs.items():
+        traces.assert_close(got[rid], plain.logits(toks), "bfloat16", f"trace_run/{rid}")

@@ -1,0 +1,148 @@
+"""The command line, in the reference's manner (`runner -m MODEL -p TEXT -n N --temp F`, src/main.c:188-340).
+
+Options keep the reference's names and meanings where it has them: -m (here a model FOLDER with
+config.json and model.safetensors), -p, -f, -n (default 256, -1 = until a stop id), -c, -b, -s (0 is
+refused), --temp (0 = greedy), --top-k, --top-p, --min-p, --repeat-penalty, --ignore-eos, --no-bos,
+--bench-json, -v/--version.  Tokenisation is outside the engine: a prompt is either ``ids:1,2,3`` or
+text taken byte by byte (token id = byte value), and the output is printed as ids (and as bytes where
+every id is one).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+import time
+
+from . import __version__
+
+
+def unescape(s: str) -> str:
+    """\\n \\t \\r \\\\ in a -p argument (src/main.c:168-186)."""
+    out, i = [], 0
+    while i < len(s):
+        if s[i] == "\\" and i + 1 < len(s) and s[i + 1] in "ntr\\":
+            out.append({"n": "\n", "t": "\t", "r": "\r", "\\": "\\"}[s[i + 1]])
+            i += 2
+        else:
+            out.append(s[i])
+            i += 1
+    return "".join(out)
+
+
+def encode_prompt(text: str, vocab: int):
+    if text.startswith("ids:"):
+        try:
+            ids = [int(t) for t in text[4:].replace(" ", "").split(",") if t != ""]
+        except ValueError:
+            raise SystemExit("error: -p ids:... must be a comma-separated list of integers")
+    else:
+        ids = list(text.encode("utf-8"))
+    bad = [t for t in ids if t < 0 or t >= vocab]
+    if bad:
+        raise SystemExit(f"error: token id {bad[0]} is outside the vocabulary of {vocab}")
+    return ids
+
+
+def build_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser(prog="runner", description="generate with a dense Llama model on one B200")
+    ap.add_argument("-m", dest="model", help="model folder (config.json + model.safetensors)")
+    ap.add_argument("-p", dest="prompt", default=None, help="prompt: text (bytes) or ids:1,2,3; \\n etc. are unescaped")
+    ap.add_argument("-f", dest="file", default=None, help="read prompt from file (appended after -p text)")
+    ap.add_argument("-n", dest="n", type=int, default=256, help="max tokens to generate (default 256, -1 = until a stop id)")
+    ap.add_argument("-c", dest="ctx", type=int, default=None, help="context length (default: min(model max, 4096))")
+    ap.add_argument("-b", dest="batch", type=int, default=2048, help="prompt portion / step token budget (default 2048)")
+    ap.add_argument("-s", dest="seed", type=int, default=None, help="RNG seed (default: time; 0 is refused)")
+    ap.add_argument("--temp", type=float, default=0.0, help="temperature (0 = greedy: the argmax, no repeat penalty)")
+    ap.add_argument("--top-k", type=int, default=0, help="top-k (0 = off)")
+    ap.add_argument("--top-p", type=float, default=1.0, help="top-p")
+    ap.add_argument("--min-p", type=float, default=0.0, help="min-p vs the top candidate (0 = off)")
+    ap.add_argument("--repeat-penalty", type=float, default=1.0, help="penalty on recently emitted tokens (1 = off)")
+    ap.add_argument("--ignore-eos", action="store_true", help="keep generating past stop ids")
+    ap.add_argument("--no-bos", action="store_true", help="do not prepend the BOS token")
+    ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16",
+                    help="bfloat16: serving kernels; float32: everything in true 32 bit")
+    ap.add_argument("--page-size", type=int, default=64, help="tokens per cache page")
+    ap.add_argument("--bench-json", action="store_true",
+                    help="prefill a 512-token prompt, decode -n tokens with stop ids ignored, print timings as JSON")
+    ap.add_argument("--random", type=int, default=None, metavar="SEED",
+                    help="with -m: write config.json-described random weights into the folder first (needs config.json)")
+    ap.add_argument("-v", "--version", action="version", version=f"runner-b200 {__version__}")
+    return ap
+
+
+def main(argv=None) -> int:
+    args = build_parser().parse_args(argv)
+    if not args.model:
+        print("error: -m MODEL is required", file=sys.stderr)
+        return 2
+    if args.seed is not None and args.seed == 0:
+        print("error: -s 0 is refused (it is the generator's fixed point); pick another seed", file=sys.stderr)
+        return 2
+    if args.random is not None:
+        import os
+        import torch
+        from .config import registry
+        from .weights.loader import write_model_folder
+        from . import architectures  # noqa: F401
+        arch, cfg = registry.load_config(args.model)
+        specs = arch.build_plan(cfg).tensor_specs()
+        dt = {"bfloat16": torch.bfloat16, "float32": torch.float32, "float16": torch.float32}[cfg.torch_dtype]
+        write_model_folder(args.model, cfg.to_dict(), specs, args.random, dt)
+        print(f"wrote random weights (seed {args.random}) to {os.path.join(args.model, 'model.safetensors')}", file=sys.stderr)
+        if args.prompt is None and args.file is None and not args.bench_json:
+            return 0
+    from .engine.runner import Runner
+    t0 = time.perf_counter()
+    runner = Runner(args.model, dtype=args.dtype, ctx=args.ctx, batch=args.batch, parallel=1, page_size=args.page_size)
+    plan = runner.engine.plan
+    print(f"loaded {args.model} in {time.perf_counter() - t0:.2f} s ({args.dtype})", file=sys.stderr)
+    if args.bench_json:
+        import numpy as np
+        ids = [int(t) for t in np.random.RandomState(0).randint(0, plan.vocab_size, size=512)]
+        n_new = args.n if args.n > 0 else 128
+        stamps = {}
+        def on_token(rid, tok, done):
+            stamps.setdefault("first", time.perf_counter())
+        t0 = time.perf_counter()
+        res = runner.generate(ids, n=n_new, temp=args.temp, seed=args.seed, ignore_eos=True, on_token=on_token)
+        t1 = time.perf_counter()
+        prompt_s = stamps["first"] - t0
+        gen_s = t1 - stamps["first"]
+        print(json.dumps({"prompt_tokens": 512, "gen_tokens": len(res.tokens), "prompt_s": prompt_s, "gen_s": gen_s,
+                          "prompt_tok_s": 512 / prompt_s, "gen_tok_s": (len(res.tokens) - 1) / gen_s if gen_s > 0 else 0.0}))
+        return 0
+    text = unescape(args.prompt) if args.prompt is not None else ""
+    if args.file:
+        with open(args.file, "r", encoding="utf-8") as f:
+            text += f.read()
+    ids = encode_prompt(text, plan.vocab_size)
+    if not args.no_bos and plan.bos_id is not None:
+        ids = [plan.bos_id] + ids
+    if not ids:
+        print("error: empty prompt", file=sys.stderr)
+        return 2
+    t0 = time.perf_counter()
+    first = {}
+    def on_token(rid, tok, done):
+        first.setdefault("t", time.perf_counter())
+    try:
+        res = runner.generate(ids, n=args.n, temp=args.temp, top_k=args.top_k, top_p=args.top_p, min_p=args.min_p,
+                              repeat_penalty=args.repeat_penalty, seed=args.seed, ignore_eos=args.ignore_eos,
+                              on_token=on_token)
+    except ValueError as e:
+        print(f"error: {e}", file=sys.stderr)
+        return 2
+    t1 = time.perf_counter()
+    print("ids:" + ",".join(str(t) for t in res.tokens))
+    if res.tokens and all(0 <= t < 256 for t in res.tokens):
+        sys.stdout.buffer.write(bytes(res.tokens) + b"\n")
+    tp = first.get("t", t1) - t0
+    tg = t1 - first.get("t", t1)
+    print(f"prompt: {len(ids)} tokens, {len(ids) / tp if tp > 0 else 0:.1f} tok/s | gen: {len(res.tokens)} tokens, "
+          f"{(len(res.tokens) - 1) / tg if tg > 0 else 0:.1f} tok/s | finish: {res.finish_reason}", file=sys.stderr)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -159,6 +159,14 @@ class Engine:
         """The request is finished: its pages and its state slot are given back."""
         self.cache.close(request)
 
+    def adopt(self, request, n_tokens: int) -> None:
+        """Open `request` as if `n_tokens` had been run: pages are taken, nothing is computed, and the keys
+        and values in those pages are whatever the pool holds.  For measurements that need a long context
+        without paying for its prefill."""
+        self._open(request)
+        self.cache.reserve(request, n_tokens)
+        self.cache.commit(request)
+
     def _open(self, request) -> int:
         slot = self.cache.open(request)
         for lay in self.model.layers:

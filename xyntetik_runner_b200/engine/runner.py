@@ -1,0 +1,114 @@
+"""The Python entry point: a model folder (or a seeded random model) in, generated token ids out.
+
+It is the same path as the command line: requests go to the scheduler, the scheduler plans steps for the
+engine's step function, the device sampler picks tokens.  Option names follow the reference's command
+line (src/main.c:188-340): ``n`` (-n, max new tokens, default 256), ``temp`` (--temp, 0 = greedy),
+``top_k``, ``top_p``, ``min_p``, ``repeat_penalty``, ``seed`` (-s), ``ignore_eos``; ``ctx`` (-c) and
+``batch`` (-b) size the engine.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Union
+
+import torch
+
+from ..sampling.sampler import DeviceSampler, SamplingParams
+from .engine import Engine, EngineParams, StepEntry, random_engine
+from .scheduler import Request, Scheduler, SchedulerParams, StepPlan
+
+
+@dataclass
+class GenerationResult:
+    tokens: List[int]
+    finish_reason: str
+    prompt_tokens: int
+    preemptions: int = 0
+
+
+class EngineExecutor:
+    """Runs a scheduler's plan on the engine and samples on the device."""
+
+    def __init__(self, engine: Engine):
+        self.engine = engine
+        self.sampler = DeviceSampler(engine.device)
+
+    def run(self, plan: StepPlan) -> Dict[object, int]:
+        entries = [StepEntry(e.request.id, e.tokens, [e.count - 1] if e.wants_token else []) for e in plan.entries]
+        logits = self.engine.step(entries, reserved=True)
+        wanting = [e.request for e in plan.entries if e.wants_token]
+        if not wanting:
+            return {}
+        picked = self.sampler.pick(logits, [r.sampler for r in wanting]).cpu().tolist()   # device -> host
+        return {r.id: t for r, t in zip(wanting, picked)}
+
+
+class Runner:
+    def __init__(self, model: Optional[str] = None, *, config=None, random_seed: Optional[int] = None,
+                 dtype: str = "bfloat16", ctx: Optional[int] = None, batch: int = 2048, parallel: int = 8,
+                 max_tokens: Optional[int] = None, page_size: int = 64, prefill_chunk: Optional[int] = None,
+                 device: str = "cuda:0", engine: Optional[Engine] = None):
+        """model: folder with config.json + model.safetensors.  Or `config` (a typed configuration) with
+        `random_seed` for seeded random weights.  ctx: longest request (default min(model limit, 4096), the
+        reference's -c default, src/model.c:3075).  batch: token budget of a step (-b).  parallel: live
+        requests.  max_tokens: tokens the page pool holds (default parallel * ctx)."""
+        if engine is None:
+            limit = None
+            if model is not None:
+                from ..config import registry
+                _, cfg = registry.load_config(model)
+            else:
+                cfg = config
+            model_limit = getattr(cfg, "max_position_embeddings", 4096)
+            ctx = ctx or min(model_limit, 4096)
+            ep = EngineParams(dtype=dtype, max_tokens=max_tokens or parallel * ctx, page_size=page_size,
+                              max_requests=parallel, max_request_tokens=ctx, max_step_tokens=batch, device=device)
+            engine = Engine(model, ep) if model is not None else random_engine(cfg, random_seed or 0, ep)
+        self.engine = engine
+        self.executor = EngineExecutor(engine)
+        self.scheduler = Scheduler(engine.cache, self.executor,
+                                   SchedulerParams(max_step_tokens=batch, prefill_chunk=prefill_chunk),
+                                   open_request=engine._open)
+        self._next_id = 0
+        self.timing: Dict[str, float] = {}
+
+    def submit(self, prompt: Sequence[int], n: int = 256, temp: float = 0.0, top_k: int = 0, top_p: float = 1.0,
+               min_p: float = 0.0, repeat_penalty: float = 1.0, seed: Optional[int] = None,
+               ignore_eos: bool = False, stop_ids: Optional[Sequence[int]] = None) -> object:
+        rid = self._next_id
+        self._next_id += 1
+        sp = SamplingParams(temperature=temp, top_k=top_k, top_p=top_p, min_p=min_p, repeat_penalty=repeat_penalty,
+                            seed=seed)
+        stops = tuple(stop_ids) if stop_ids is not None else tuple(self.engine.plan.stop_ids)
+        self.scheduler.add(Request(rid, [int(t) for t in prompt], max_new_tokens=n, sampling=sp, stop_ids=stops,
+                                   ignore_eos=ignore_eos))
+        return rid
+
+    def generate(self, prompts: Union[Sequence[int], Sequence[Sequence[int]]], n: int = 256, temp: float = 0.0,
+                 top_k: int = 0, top_p: float = 1.0, min_p: float = 0.0, repeat_penalty: float = 1.0,
+                 seed: Optional[int] = None, ignore_eos: bool = False, on_token=None):
+        """Generate for one prompt (a list of ids) or several (a list of lists), all scheduled together.
+        With several prompts and a seed, request i samples with seed + i.  Returns GenerationResult(s)."""
+        single = len(prompts) > 0 and isinstance(prompts[0], int)
+        plist = [prompts] if single else list(prompts)
+        ids = [self.submit(p, n, temp, top_k, top_p, min_p, repeat_penalty,
+                           None if seed is None else seed + i, ignore_eos) for i, p in enumerate(plist)]
+        t0 = time.perf_counter()
+        sch = self.scheduler
+        while sch.has_work():
+            before = len(sch.finished)
+            res = sch.step()
+            if on_token is not None:
+                for rid, tok, done in res:
+                    on_token(rid, tok, done)
+            if not res and not sch.live and sch.waiting and len(sch.finished) == before:
+                r = sch.waiting.popleft()
+                sch._finish(r, "rejected")
+        torch.cuda.synchronize(self.engine.device)
+        self.timing["generate_s"] = time.perf_counter() - t0
+        out = []
+        for rid in ids:
+            r = sch.finished.pop(rid)
+            out.append(GenerationResult(list(r.generated), r.finish_reason, len(r.prompt), r.preemptions))
+        return out[0] if single else out

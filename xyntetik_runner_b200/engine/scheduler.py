@@ -1,0 +1,284 @@
+"""The scheduler above the step function: admit, cut prompts under a token budget, decode, finish, free.
+
+The reference runs fixed slots and lets prefill chunks (``-b``, src/engine.c:875-883) and batched decode
+steps take turns on the device (src/scheduler.c:101-125, 153-220).  Here one step holds both: every live
+request that is decoding contributes its one token first; what is left of the step's token budget goes to
+requests that are still reading their prompt, in the order they were admitted, as portions; then waiting
+requests are admitted (first come, first served) while a slot and pages are free.  A request finishes on a
+stop id, on its token limit, or at the longest length the engine holds (src/engine.c:1834, 1844-1854), and
+gives its pages and slot back in the same tick.
+
+When pages run out:
+ 1. a prompt portion is shrunk to what fits (possibly to nothing: the request waits);
+ 2. if a decoding request cannot get the page its next token needs, the most recently admitted live
+    request is preempted: its pages are freed and it goes back to the FRONT of the waiting queue with
+    prompt + generated so far as its new prompt (recompute; its sampler state is kept, so it goes on
+    with the same tokens);
+ 3. the same happens when no live request can make progress at all;
+ 4. a request that could never fit the pool alone is refused when it is added; one that outgrows the
+    pool while it is the only live request finishes with reason "length".
+
+This module is host logic only.  It talks to the cache manager for reservations and to an executor
+(``run(plan) -> {request id: sampled token}``) for the step, so its decisions are testable without a GPU.
+"""
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Deque, Dict, List, Optional, Sequence, Tuple
+
+from ..cache.pages import CacheManager, OutOfPages
+from ..sampling.sampler import RequestSampler, SamplingParams
+
+WAITING, LIVE, FINISHED = "waiting", "live", "finished"
+
+
+@dataclass
+class Request:
+    id: object
+    prompt: List[int]
+    max_new_tokens: int = 256
+    sampling: SamplingParams = field(default_factory=SamplingParams)
+    stop_ids: Tuple[int, ...] = ()
+    ignore_eos: bool = False
+    # ---- run-time state ----
+    tokens: List[int] = field(default_factory=list)      # prompt + generated
+    generated: List[int] = field(default_factory=list)
+    computed: int = 0                                     # tokens whose keys are in the cache
+    status: str = WAITING
+    finish_reason: Optional[str] = None
+    admitted_at: int = -1
+    preemptions: int = 0
+    sampler: Optional[RequestSampler] = None
+
+    @property
+    def pending(self) -> int:
+        return len(self.tokens) - self.computed
+
+
+@dataclass
+class PlannedEntry:
+    request: Request
+    start: int
+    count: int
+    wants_token: bool
+
+    @property
+    def tokens(self) -> List[int]:
+        return self.request.tokens[self.start:self.start + self.count]
+
+
+@dataclass
+class StepPlan:
+    entries: List[PlannedEntry] = field(default_factory=list)
+    preempted: List[object] = field(default_factory=list)
+
+    @property
+    def n_tokens(self) -> int:
+        return sum(e.count for e in self.entries)
+
+
+@dataclass
+class SchedulerParams:
+    max_step_tokens: int = 2048      # token budget of one step
+    prefill_chunk: Optional[int] = None   # cap on one request's portion (the reference's -b); None: the budget
+
+
+class Scheduler:
+    def __init__(self, cache: CacheManager, executor, params: Optional[SchedulerParams] = None, open_request=None):
+        self.cache, self.executor = cache, executor
+        # opening a request takes a state slot; an engine also zeroes the slot's per-request state
+        self._open = open_request or cache.open
+        self.params = params or SchedulerParams()
+        self.waiting: Deque[Request] = deque()
+        self.live: List[Request] = []           # in admission order
+        self.finished: Dict[object, Request] = {}
+        self._tick = 0
+        self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "preemptions": 0, "max_batch": 0}
+
+    # ---- adding ---------------------------------------------------------------------
+    def add(self, req: Request) -> None:
+        if not req.prompt:
+            raise ValueError(f"request {req.id!r}: empty prompt")     # src/main.c:1522-1529
+        limit = self.cache.max_pages_per_request * self.cache.page_size
+        if len(req.prompt) >= limit:
+            raise ValueError(f"request {req.id!r}: prompt of {len(req.prompt)} tokens does not fit the "
+                             f"longest request the engine holds ({limit})")
+        if any(g.window is None for g in self.cache.groups) or not self.cache.groups:
+            pool = min((p.n_pages for p in self.cache.pools), default=1 << 30)
+            if -(-(len(req.prompt) + 1) // self.cache.page_size) > pool:
+                raise ValueError(f"request {req.id!r}: prompt of {len(req.prompt)} tokens can never fit a pool of "
+                                 f"{pool} pages of {self.cache.page_size}")
+        if req.max_new_tokens == 0:
+            raise ValueError("max_new_tokens must not be 0")
+        req.tokens = list(req.prompt)
+        req.generated = []
+        req.computed = 0
+        req.status = WAITING
+        req.sampler = RequestSampler(req.sampling, no_penalty=req.stop_ids)
+        for t in req.prompt:
+            req.sampler.accept(t)                # the prompt seeds the penalty window (src/engine.c:881)
+        self.waiting.append(req)
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.live)
+
+    # ---- planning -----------------------------------------------------------------------
+    def _preempt(self, victim: Request, plan: StepPlan) -> None:
+        for e in list(plan.entries):
+            if e.request is victim:
+                plan.entries.remove(e)
+        self.cache.cancel(victim.id)
+        self.cache.close(victim.id)
+        self.live.remove(victim)
+        victim.computed = 0
+        victim.status = WAITING
+        victim.preemptions += 1
+        self.waiting.appendleft(victim)
+        plan.preempted.append(victim.id)
+        self.stats["preemptions"] += 1
+
+    def _fit(self, req: Request, want: int) -> int:
+        """Largest portion <= want whose pages can be reserved now (0: none)."""
+        if want < 1:
+            return 0
+        if self.cache.can_reserve(req.id, want):
+            return want
+        lo, hi = 0, want            # can_reserve is monotone in the count
+        while lo < hi:
+            mid = (lo + hi + 1) // 2
+            if self.cache.can_reserve(req.id, mid):
+                lo = mid
+            else:
+                hi = mid - 1
+        return lo
+
+    def plan(self) -> StepPlan:
+        plan = StepPlan()
+        budget = self.params.max_step_tokens
+        chunk_cap = self.params.prefill_chunk or budget
+        # 1. decoding requests: one token each; pages for them come before anything else
+        i = 0
+        while i < len(self.live):
+            r = self.live[i]
+            if r.pending != 1 or budget < 1:
+                i += 1
+                continue
+            if self.cache.can_reserve(r.id, 1):
+                self.cache.reserve(r.id, 1)
+                plan.entries.append(PlannedEntry(r, r.computed, 1, True))
+                budget -= 1
+                i += 1
+                continue
+            if len(self.live) == 1:
+                self._finish(r, "length")          # alone and still no page: the pool is its limit
+                continue
+            victim = self.live[-1]
+            vi = len(self.live) - 1
+            self._preempt(victim, plan)
+            if vi < i:
+                i -= 1
+            # try the same index again (it is r again unless r itself was the victim)
+        # 2. requests still reading their prompt, in admission order
+        for r in self.live:
+            if r.pending < 1 or budget < 1 or any(e.request is r for e in plan.entries):
+                continue
+            n = self._fit(r, min(r.pending, budget, chunk_cap))
+            if n > 0:
+                self.cache.reserve(r.id, n)
+                plan.entries.append(PlannedEntry(r, r.computed, n, n == r.pending))
+                budget -= n
+        # 3. admissions, first come first served
+        #    (not in a step that had to preempt, and only while a page per live request stays free, so that
+        #    a request that was just pushed out does not take the pages the older ones are about to need)
+        while self.waiting and budget > 0 and self.cache.has_free_slot() and not plan.preempted:
+            r = self.waiting[0]
+            self._open(r.id)
+            n = self._fit(r, min(r.pending, budget, chunk_cap))
+            if n > 0 and self.live:
+                need = self.cache.pages_needed(r.id, n)
+                while n > 0 and any(f - q < len(self.live) for f, q in zip(self.cache.free_pages(), need)):
+                    n = (n - 1) // self.cache.page_size * self.cache.page_size if n > self.cache.page_size else 0
+                    need = self.cache.pages_needed(r.id, n) if n > 0 else need
+            if n < 1:
+                self.cache.close(r.id)
+                break
+            self.waiting.popleft()
+            self.cache.reserve(r.id, n)
+            r.status = LIVE
+            r.admitted_at = self._tick
+            self._tick += 1
+            self.live.append(r)
+            plan.entries.append(PlannedEntry(r, r.computed, n, n == r.pending))
+            budget -= n
+        # 4. nobody can move: free the newest request's pages for the older ones
+        if not plan.entries and self.live:
+            if len(self.live) == 1:
+                self._finish(self.live[0], "length")
+            else:
+                self._preempt(self.live[-1], plan)
+                inner = self.plan()
+                inner.preempted = plan.preempted + inner.preempted
+                return inner
+        return plan
+
+    # ---- stepping -------------------------------------------------------------------------
+    def _finish(self, r: Request, reason: str) -> None:
+        r.status, r.finish_reason = FINISHED, reason
+        if self.cache.is_open(r.id):
+            self.cache.cancel(r.id)
+            self.cache.close(r.id)
+        if r in self.live:
+            self.live.remove(r)
+        self.finished[r.id] = r
+
+    def step(self) -> List[Tuple[object, Optional[int], bool]]:
+        """Plan and run one step.  Returns [(request id, new token or None, finished)] for requests that
+        got a token or finished in this step."""
+        plan = self.plan()
+        if not plan.entries:
+            return []
+        sampled: Dict[object, int] = self.executor.run(plan)
+        self.stats["steps"] += 1
+        self.stats["max_batch"] = max(self.stats["max_batch"], len(plan.entries))
+        out = []
+        limit = self.cache.max_pages_per_request * self.cache.page_size
+        for e in plan.entries:
+            r = e.request
+            r.computed += e.count
+            if e.count == 1 and r.generated:
+                self.stats["decode_tokens"] += 1
+            else:
+                self.stats["prefill_tokens"] += e.count
+            if not e.wants_token:
+                continue
+            tok = int(sampled[r.id])
+            r.sampler.accept(tok)
+            if not r.ignore_eos and tok in r.stop_ids:            # src/engine.c:1849-1854
+                self._finish(r, "stop")
+                out.append((r.id, None, True))
+                continue
+            r.generated.append(tok)
+            r.tokens.append(tok)
+            done = None
+            if 0 < r.max_new_tokens <= len(r.generated):
+                done = "length"
+            elif len(r.tokens) >= limit:                            # src/engine.c:1834
+                done = "length"
+            if done:
+                self._finish(r, done)
+            out.append((r.id, tok, done is not None))
+        return out
+
+    def run_to_completion(self, max_steps: int = 1 << 30) -> None:
+        n = 0
+        while self.has_work() and n < max_steps:
+            before = len(self.finished)
+            res = self.step()
+            n += 1
+            if not res and not self.has_work():
+                break
+            if not res and len(self.finished) == before and not self.live and self.waiting:
+                # nothing live and the head of the queue cannot be admitted: it can never run
+                r = self.waiting.popleft()
+                self._finish(r, "rejected")
