@@ -276,7 +276,8 @@ def uniform_from_state(state: int) -> float:
 
 
 def sample_chain(logits: np.ndarray, r: float, temp: float, top_k: int = 0, top_p: float = 1.0,
-                 min_p: float = 0.0, repeat_penalty: float = 1.0, recent=(), with_margin: bool = False):
+                 min_p: float = 0.0, repeat_penalty: float = 1.0, recent=(), with_margin: bool = False,
+                 distance_of=None):
     """The reference's chain on one row (src/sample.c:141-329, `pick_scaled` :86-127):
     penalty on recent tokens (only when temp > 0), greedy for temp <= 0, scale by 1/temp, keep the
     top_k by (logit descending, id ascending), softmax over the survivors, top-p prefix, min-p floor,
@@ -288,6 +289,8 @@ def sample_chain(logits: np.ndarray, r: float, temp: float, top_k: int = 0, top_
             if 0 <= t < V:
                 lg[t] = lg[t] / F32(repeat_penalty) if lg[t] > 0 else lg[t] * F32(repeat_penalty)
     if temp <= 0:
+        if distance_of is not None:
+            return float(lg.max() - lg[distance_of])       # how far below the best logit the given token lies
         if with_margin:
             top2 = np.sort(lg)[-2:]
             return int(np.argmax(lg)), float(top2[1] - top2[0])
@@ -311,6 +314,14 @@ def sample_chain(logits: np.ndarray, r: float, temp: float, top_k: int = 0, top_
     cum = np.cumsum(p)
     idx = int(np.searchsorted(cum, r, side="right"))
     idx = min(idx, len(order) - 1)
+    if distance_of is not None:
+        # how far the draw lies outside the given token's interval of the cumulative distribution
+        where = np.nonzero(order == distance_of)[0]
+        if len(where) == 0:
+            return float("inf")
+        j = int(where[0])
+        lo, hi = (cum[j - 1] if j > 0 else 0.0), cum[j]
+        return float(max(lo - r, r - hi, 0.0))
     if with_margin:
         # distance of the draw to the nearest edge of the picked candidate's interval: a pick is only
         # comparable between two implementations when the draw is not on an edge

@@ -21,22 +21,26 @@ def folders(tmp_path_factory):
             for n in "AB" for dt in ("float32", "bfloat16")}
 
 
-def check_against_plain(plain, prompt, generated, temp, seed, near_tie, **chain):
+def check_against_plain(plain, prompt, generated, temp, seed, tol, **chain):
     """Teacher-forced: every generated token must be what the plain implementation picks for the same
-    prefix and the same draw, unless the plain pick itself was within `near_tie` of another outcome."""
+    prefix and the same draw.  Where it is not, the draw must lie within `tol` of the token's interval of
+    the plain cumulative distribution (greedy: the token's plain logit within `tol` of the best): the
+    engine's logits differ from the plain ones by rounding, which moves the intervals' edges a little.
+    Returns the number of tokens that differed."""
     state = seed
-    excused = 0
+    differed = 0
     for i, tok in enumerate(generated):
         lg = plain.logits(list(prompt) + list(generated[:i]))[-1]
         r = 0.0
         if temp > 0:
             state = xorshift64(state)
             r = uniform_from_state(state)
-        pick, margin = sample_chain(lg, r, temp, with_margin=True, **chain)
+        pick = sample_chain(lg, r, temp, **chain)
         if pick != tok:
-            assert margin < near_tie, f"token {i}: engine {tok}, plain {pick} with margin {margin:.3e}"
-            excused += 1
-    return excused
+            dist = sample_chain(lg, r, temp, distance_of=tok, **chain)
+            assert dist <= tol, f"token {i}: engine {tok}, plain {pick}; the draw is {dist:.3e} outside the token's interval"
+            differed += 1
+    return differed
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -53,7 +57,7 @@ def test_workload_a_greedy(folders, dtype):
         if dtype == "float32":
             assert g.tokens == plain.generate_greedy(p, 16)
         else:
-            assert check_against_plain(plain, p, g.tokens, 0.0, 0, near_tie=0.08) <= 2
+            assert check_against_plain(plain, p, g.tokens, 0.0, 0, tol=0.05) <= 2
     r.engine.cache.audit()
     assert not r.engine.cache.live_requests()
 
@@ -69,10 +73,13 @@ def test_workload_b_temperature_chunked(folders, dtype):
     r = Runner(folder, dtype=dtype, ctx=128, parallel=4, page_size=8, batch=40, prefill_chunk=24)
     res = r.generate(prompts, n=20, temp=0.8, seed=77, ignore_eos=True)
     assert r.scheduler.stats["max_batch"] >= 3
-    tie = 1e-4 if dtype == "float32" else 2e-2
+    # float32 logits agree to ~1e-5, which moves an edge of the cumulative distribution by less than 1e-4;
+    # bfloat16 logits carry ~1% error, and the edges move by about as much
+    tol = 1e-4 if dtype == "float32" else 2e-2
     for i, (p, g) in enumerate(zip(prompts, res)):
         assert len(g.tokens) == 20
-        assert check_against_plain(plain, p, g.tokens, 0.8, 77 + i, near_tie=tie) <= (0 if dtype == "float32" else 2)
+        differed = check_against_plain(plain, p, g.tokens, 0.8, 77 + i, tol=tol)
+        assert dtype != "float32" or differed == 0
     # the same seeds give the same tokens whatever the batching
     r2 = Runner(folder, dtype=dtype, ctx=128, parallel=1, page_size=64)
     for i, (p, g) in enumerate(zip(prompts, res)):

@@ -1,0 +1,408 @@
+// out[t][r] = sum_k X[t][k] * W[r][k] on the 5th-generation tensor cores (tcgen05), bfloat16 in,
+// float32 accumulation in tensor memory.
+//
+// The weight matrix is the M operand: a CTA owns 128 rows of W (output features) and BN tokens
+// (BN = 16..256, the N of the instruction), so the same kernel serves a decode step of one token
+// (weights stream through once, tokens are padding-free up to 16) and a 2,048-token prefill
+// (128 x 256 tiles).  Both operands are K-major in global memory, which is what TMA with the
+// 128-byte swizzle and the K-major shared-memory descriptor want: no transposes anywhere.
+//
+// Roles inside a CTA of 192 threads:
+//   warp 0, one lane : TMA producer  (cp.async.bulk.tensor.2d -> shared, completes on an mbarrier)
+//   warp 1, one lane : MMA issuer    (tcgen05.mma, commits free the stage / signal the epilogue);
+//                      the warp also allocates and frees tensor memory
+//   warps 2..5       : epilogue      (tcgen05.ld of their 32 lanes, then global stores)
+// A K loop over 64-element blocks runs through a ring of shared-memory stages.
+//
+// Epilogues: store (bfloat16 or float32, optional bias), add into the float32 residual stream,
+// two-accumulator SwiGLU (gate rows and up rows of the same features multiply the same X tile;
+// h = silu(g) * u leaves the CTA, the [n, 2F] intermediate never exists), or a split-K partial to
+// scratch that `k_splitk_finish` sums in a fixed order and finishes with the same epilogues.
+//
+// Every wait on an mbarrier is bounded: after XR_SPIN_LIMIT polls the waiter raises the CTA's abort
+// flag, every role leaves its loop, in-flight copies are waited for (bounded again), tensor memory is
+// freed, and the kernel records the failure in a status word that the launcher's caller reads.
+//
+// The reference multiplies bf16 weights with scalar FMA kernels (`k_mv_bf16`, `k_mv_bf16_b`,
+// src/kernels.cu:534-549; `k_gemvb_bf16_x4/_x8`, src/kernels.cu:2814-2852) and adds the residual and
+// the activation in kernels of their own (`k_add` :2903, `k_silu_mul` :2868).
+#include "common.cuh"
+#include <cuda.h>
+
+#define TC_BM 128          // W rows per CTA (the M of the instruction)
+#define TC_BK 64           // K elements per stage: 128 bytes, one swizzle atom
+#define TC_THREADS 192
+#define XR_SPIN_LIMIT (1u << 24)
+
+#define TC_EPI_STORE 0     // out[t][r] = acc (+ bias), bfloat16 or float32
+#define TC_EPI_ADD 1       // out[t][r] += acc (+ bias), float32 residual stream
+#define TC_EPI_SWIGLU 2    // out[t][f] = silu(acc_gate) * acc_up
+#define TC_EPI_PARTIAL 3   // scratch[split][t][r] = acc (float32); dual: gate rows then up rows
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when it gave up (or another role already had).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < XR_SPIN_LIMIT; i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, float* v) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
+}
+
+// K-major operand tile in shared memory, rows of 128 bytes, 128-byte swizzle, groups of 8 rows 1024 bytes
+// apart: start address and offsets in 16-byte units, descriptor version 1 (bit 46), layout type 2 (bits 61-63).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;                 // leading byte offset (unused with a swizzled K-major tile)
+    d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset: 8 rows
+    d |= (uint64_t)1 << 46;                 // descriptor version
+    d |= (uint64_t)2 << 61;                 // SWIZZLE_128B
+    return d;
+}
+// kind::f16 instruction descriptor: D float32, A and B bfloat16, both K-major, M = 128, N = bn.
+__host__ __device__ constexpr uint32_t instr_desc(int bn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+}
+
+struct TcParams {
+    void* out;                  // see TC_EPI_*
+    const float* bias;          // [n_out] or null
+    float* partial;             // split-K scratch
+    int* status;                // device word: non-zero when a wait gave up
+    long long ldo;              // row stride of out in elements
+    int n, n_out, K;            // tokens, output features (per half in SwiGLU mode), reduction length
+    int kblocks_per_split;      // K blocks (of 64) each z-slice of the grid handles
+    int epilogue, out_dtype;
+    int up_row_offset;          // SwiGLU: rows of the up projection start here in W
+};
+
+// ---------------------------------------------------------------------------------------------
+// The kernel.  grid = (token tiles, row tiles, K splits): the CTAs that share a tile of W are neighbours in
+// launch order, so W comes from HBM once and from L2 for the others.
+// ---------------------------------------------------------------------------------------------
+template <int BN, int STAGES, bool DUAL>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    constexpr int W_BYTES = TC_BM * TC_BK * 2;
+    constexpr int X_BYTES = BN * TC_BK * 2;
+    constexpr int STAGE_BYTES = W_BYTES * (DUAL ? 2 : 1) + X_BYTES;
+    constexpr int ACC_COLS = DUAL ? 2 * BN : BN;
+    constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : (ACC_COLS <= 64 ? 64 : (ACC_COLS <= 128 ? 128 : (ACC_COLS <= 256 ? 256 : 512)));
+    // carve shared memory: stages (1024-byte aligned), then barriers
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)(smem + STAGES * STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_ready = empty + STAGES;
+    uint32_t* tmem_slot = (uint32_t*)(acc_ready + 1);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row0 = blockIdx.y * TC_BM, tok0 = blockIdx.x * BN;
+    const int total_kb = (p.K + TC_BK - 1) / TC_BK;
+    const int kb0 = blockIdx.z * p.kblocks_per_split;
+    const int kb1 = min(total_kb, kb0 + p.kblocks_per_split);
+    const int nkb = kb1 - kb0;                     // >= 1 by construction of the grid
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(acc_ready, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int issued = 0;
+            for (int i = 0; i < nkb; i++) {
+                int s = i % STAGES;
+                if (i >= STAGES && !mbar_wait(&empty[s], ((i / STAGES) - 1) & 1, abort_flag)) break;
+                uint8_t* st = smem + s * STAGE_BYTES;
+                mbar_expect_tx(&full[s], STAGE_BYTES);
+                int kx = (kb0 + i) * TC_BK;
+                tma_load_2d(st, &map_w, kx, row0, &full[s]);
+                if (DUAL) tma_load_2d(st + W_BYTES, &map_w, kx, p.up_row_offset + row0, &full[s]);
+                tma_load_2d(st + W_BYTES * (DUAL ? 2 : 1), &map_x, kx, tok0, &full[s]);
+                issued = i + 1;
+            }
+            if (*abort_flag) {
+                // copies already issued still write shared memory: wait for them (bounded) before the CTA may exit
+                for (int i = max(0, issued - STAGES); i < issued; i++)
+                    for (uint32_t w = 0; w < XR_SPIN_LIMIT && !mbar_try_wait(&full[i % STAGES], (i / STAGES) & 1); w++) {}
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc(BN);
+            bool ok = true;
+            for (int i = 0; i < nkb && ok; i++) {
+                int s = i % STAGES;
+                ok = mbar_wait(&full[s], (i / STAGES) & 1, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+                uint32_t b_addr = a_addr + W_BYTES * (DUAL ? 2 : 1);
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; k++) {
+                    uint64_t bd = smem_desc_sw128(b_addr + k * 32);
+                    uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+                    tc_mma(tmem_base, smem_desc_sw128(a_addr + k * 32), bd, idesc, acc);
+                    if (DUAL) tc_mma(tmem_base + BN, smem_desc_sw128(a_addr + W_BYTES + k * 32), bd, idesc, acc);
+                }
+                tc_commit(&empty[s]);          // the stage is free once these MMAs have read it
+            }
+            if (ok) tc_commit(acc_ready);      // accumulators complete
+        }
+    } else {
+        // ---------------- epilogue: warps 2..5 own tensor-memory lanes 32*(warp%4) .. +31 ----------------
+        const int quad = warp & 3;
+        const int r = row0 + quad * 32 + lane;            // output feature of this thread
+        bool ok = mbar_wait(acc_ready, 0, abort_flag);
+        tc_fence_after();
+        if (ok) {
+            const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
+            const bool row_ok = r < p.n_out;
+            const float b = (p.bias != nullptr && row_ok && (p.epilogue == TC_EPI_STORE || p.epilogue == TC_EPI_ADD) && blockIdx.z == 0)
+                                ? p.bias[r] : 0.f;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                if (tok0 + c0 >= p.n) break;               // warp-uniform
+                float g[16], u[16];
+                tc_ld16(taddr + c0, g);
+                if (DUAL) tc_ld16(taddr + BN + c0, u);
+                if (!row_ok) continue;
+#pragma unroll
+                for (int c = 0; c < 16; c++) {
+                    int t = tok0 + c0 + c;
+                    if (t >= p.n) break;
+                    if (p.epilogue == TC_EPI_PARTIAL) {
+                        size_t width = DUAL ? 2 * (size_t)p.n_out : (size_t)p.n_out;
+                        float* dst = p.partial + ((size_t)blockIdx.z * p.n + t) * width;
+                        dst[r] = g[c];
+                        if (DUAL) dst[p.n_out + r] = u[c];
+                    } else if (DUAL) {
+                        float gv = g[c];
+                        float h = gv < -80.0f ? 0.0f : (gv / (1.0f + expf(-gv))) * u[c];
+                        if (p.out_dtype == XR_BF16) ((__nv_bfloat16*)p.out)[(size_t)t * p.ldo + r] = __float2bfloat16_rn(h);
+                        else ((float*)p.out)[(size_t)t * p.ldo + r] = h;
+                    } else if (p.epilogue == TC_EPI_ADD) {
+                        float* dst = (float*)p.out + (size_t)t * p.ldo + r;
+                        *dst = *dst + (g[c] + b);
+                    } else {
+                        float v = g[c] + b;
+                        if (p.out_dtype == XR_BF16) ((__nv_bfloat16*)p.out)[(size_t)t * p.ldo + r] = __float2bfloat16_rn(v);
+                        else ((float*)p.out)[(size_t)t * p.ldo + r] = v;
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+    if (threadIdx.x == 0 && *abort_flag) atomicExch(p.status, 1);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Finish of a split-K product: sum the partials in split order, then the same epilogues.
+// ---------------------------------------------------------------------------------------------
+struct FinishParams {
+    const float* partial; void* out; const float* bias;
+    long long ldo;
+    int n, n_out, splits, epilogue, out_dtype, dual;
+};
+
+__global__ void k_splitk_finish(FinishParams p) {
+    size_t total = (size_t)p.n * p.n_out;
+    size_t width = p.dual ? 2 * (size_t)p.n_out : (size_t)p.n_out;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        size_t t = i / p.n_out, r = i % p.n_out;
+        float g = 0.f, u = 0.f;
+        for (int s = 0; s < p.splits; s++) {
+            const float* src = p.partial + ((size_t)s * p.n + t) * width;
+            g += src[r];
+            if (p.dual) u += src[p.n_out + r];
+        }
+        float v;
+        if (p.dual) v = g < -80.0f ? 0.0f : (g / (1.0f + expf(-g))) * u;
+        else v = g + (p.bias ? p.bias[r] : 0.f);
+        size_t o = t * p.ldo + r;
+        if (p.epilogue == TC_EPI_ADD) ((float*)p.out)[o] += v;
+        else if (p.out_dtype == XR_BF16) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(v);
+        else ((float*)p.out)[o] = v;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)ptr;
+    }
+    return fn;
+}
+
+// [rows, K] bfloat16, row stride `ld` elements; box = 64 (K) x box_rows; 128-byte swizzle; zero fill outside.
+static bool make_map(CUtensorMap* m, const void* base, long long rows, long long K, long long ld, int box_rows) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, int STAGES, bool DUAL>
+static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, dim3 grid, cudaStream_t stream) {
+    constexpr int STAGE_BYTES = TC_BM * TC_BK * 2 * (DUAL ? 2 : 1) + BN * TC_BK * 2;
+    constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + (2 * STAGES + 1) * 8 + 16;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(k_gemm_tc<BN, STAGES, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+            return XR_ERR_LAUNCH;
+        configured = true;
+    }
+    k_gemm_tc<BN, STAGES, DUAL><<<grid, TC_THREADS, SMEM, stream>>>(mw, mx, p);
+    return xr_launch_status();
+}
+
+// Number of K splits that fills the machine when there are few output tiles.
+static int choose_splits(int tiles, int total_kb, int sms) {
+    if (tiles >= sms) return 1;
+    int s = (2 * sms + tiles - 1) / tiles;            // aim at about two CTAs per SM
+    int max_by_k = total_kb / 4;                       // at least four K blocks per split
+    if (s > max_by_k) s = max_by_k;
+    if (s > 16) s = 16;
+    return s < 1 ? 1 : s;
+}
+
+// X: [n, K] bfloat16 (row stride ldx), W: [n_out (x2 when swiglu), K] bfloat16 dense.
+// epilogue: TC_EPI_STORE / TC_EPI_ADD / TC_EPI_SWIGLU.  In SwiGLU mode W holds n_out gate rows followed by
+// n_out up rows and out is [n, n_out].  scratch: float32 workspace of at least xr_gemm_tc_scratch_floats()
+// elements (used when the product is split along K); status: device int, set non-zero if a wait gave up.
+XR_EXPORT long long xr_gemm_tc_scratch_floats(int n, int n_out, int swiglu) {
+    return 16LL * (long long)n * (long long)n_out * (swiglu ? 2 : 1);
+}
+
+XR_EXPORT int xr_gemm_tc(const void* X, const void* W, const float* bias, void* out, int out_dtype, int epilogue,
+                         int n, int n_out, int K, long long ldx, long long ldo, float* scratch,
+                         long long scratch_floats, int* status, int force_splits, cudaStream_t stream) {
+    if (n < 1 || n_out < 1 || K < 8 || (K % 8) != 0 || (ldx % 8) != 0 || ldx < K || ldo < n_out) return XR_ERR_ARG;
+    if (((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return XR_ERR_ARG;
+    if (epilogue != TC_EPI_STORE && epilogue != TC_EPI_ADD && epilogue != TC_EPI_SWIGLU) return XR_ERR_ARG;
+    if (epilogue == TC_EPI_ADD && out_dtype != XR_F32) return XR_ERR_ARG;
+    if (out_dtype != XR_F32 && out_dtype != XR_BF16) return XR_ERR_ARG;
+    const bool dual = epilogue == TC_EPI_SWIGLU;
+    int bn = n <= 16 ? 16 : (n <= 32 ? 32 : (n <= 64 ? 64 : (n <= 128 ? 128 : 256)));
+    CUtensorMap mw, mx;
+    if (!make_map(&mw, W, dual ? 2LL * n_out : n_out, K, K, TC_BM)) return -3;
+    if (!make_map(&mx, X, n, K, ldx, bn)) return -3;
+    int row_tiles = (n_out + TC_BM - 1) / TC_BM, tok_tiles = (n + bn - 1) / bn;
+    int total_kb = (K + TC_BK - 1) / TC_BK;
+    int splits = force_splits > 0 ? force_splits : choose_splits(row_tiles * tok_tiles, total_kb, 148);
+    if (splits > total_kb) splits = total_kb;
+    int per = (total_kb + splits - 1) / splits;
+    splits = (total_kb + per - 1) / per;                 // no empty split
+    if (splits > 1 && (scratch == nullptr || scratch_floats < (long long)splits * n * n_out * (dual ? 2 : 1))) splits = 1, per = total_kb;
+    if (row_tiles > 65535 || splits > 65535) return XR_ERR_ARG;
+    TcParams p{out, bias, scratch, status, ldo, n, n_out, K, per, splits > 1 ? TC_EPI_PARTIAL : epilogue, out_dtype, n_out};
+    dim3 grid(tok_tiles, row_tiles, splits);
+    int rc;
+    if (!dual) {
+        switch (bn) {
+            case 16: rc = launch_tc<16, 6, false>(mw, mx, p, grid, stream); break;
+            case 32: rc = launch_tc<32, 6, false>(mw, mx, p, grid, stream); break;
+            case 64: rc = launch_tc<64, 6, false>(mw, mx, p, grid, stream); break;
+            case 128: rc = launch_tc<128, 5, false>(mw, mx, p, grid, stream); break;
+            default: rc = launch_tc<256, 4, false>(mw, mx, p, grid, stream); break;
+        }
+    } else {
+        switch (bn) {
+            case 16: rc = launch_tc<16, 5, true>(mw, mx, p, grid, stream); break;
+            case 32: rc = launch_tc<32, 5, true>(mw, mx, p, grid, stream); break;
+            case 64: rc = launch_tc<64, 5, true>(mw, mx, p, grid, stream); break;
+            case 128: rc = launch_tc<128, 4, true>(mw, mx, p, grid, stream); break;
+            default: rc = launch_tc<256, 3, true>(mw, mx, p, grid, stream); break;
+        }
+    }
+    if (rc != XR_OK || splits == 1) return rc;
+    FinishParams f{scratch, out, bias, ldo, n, n_out, splits, epilogue, out_dtype, dual ? 1 : 0};
+    size_t total = (size_t)n * n_out;
+    int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+    k_splitk_finish<<<blocks, 256, 0, stream>>>(f);
+    return xr_launch_status();
+}

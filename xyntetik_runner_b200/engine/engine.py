@@ -284,6 +284,10 @@ class Engine:
         plan.head.forward(ctx, hn, logits)
         return logits
 
+    def check_status(self) -> None:
+        """Raise if a kernel reported a failure since the last check (one small read from the device)."""
+        kernels.tc_check_status(self.device)
+
     # ---- accounting (bench) ---------------------------------------------------------
     def weight_bytes_per_step(self) -> int:
         return self.model.weight_bytes_per_step()

@@ -32,6 +32,7 @@ def replay(engine: Engine, steps: Iterable, out_dir: Optional[str] = None,
         logits = engine.step(entries)
         if logits.shape[0] > 0:
             arr = logits.cpu().numpy().astype("<f4", copy=False)
+            engine.check_status()
             if out_dir is not None:
                 arr.tofile(os.path.join(out_dir, f"{step}.f32"))
             else:

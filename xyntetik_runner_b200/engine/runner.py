@@ -106,6 +106,7 @@ class Runner:
                 r = sch.waiting.popleft()
                 sch._finish(r, "rejected")
         torch.cuda.synchronize(self.engine.device)
+        self.engine.check_status()
         self.timing["generate_s"] = time.perf_counter() - t0
         out = []
         for rid in ids:

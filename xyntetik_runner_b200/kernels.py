@@ -54,6 +54,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "xr_residual_add": [_vp, _vp, _i, _i, _i, _vp],
         "xr_gemm_simt": [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _ll, _ll, _vp],
         "xr_attention_simt": [_vp, _vp, _i, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
+        "xr_gemm_tc": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _ll, _ll, _vp, _ll, _vp, _i, _vp],
         "xr_sample": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     }
     for name, args in sig.items():
@@ -181,13 +182,63 @@ def attention_simt(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, cache_
 
 
 def sample(logits: torch.Tensor, temp, top_k, top_p, min_p, penalty, draw, recent: Optional[torch.Tensor],
-           scratch: torch.Tensor, out: torch.Tensor) -> None:
-    """One token per row of float32 logits by the reference's sampling chain (see csrc/sampling.cu)."""
+           scratch: torch.Tensor, out: torch.Tensor, any_sampled: bool = True) -> None:
+    """One token per row of float32 logits by the reference's sampling chain (see csrc/sampling.cu).
+    `scratch` must hold rows * vocab floats unless every row is greedy (`any_sampled` False)."""
     _dev(temp, top_k, top_p, min_p, penalty, draw, recent, scratch, out)
     rows, V = logits.shape
-    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and scratch.numel() >= rows * V
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    assert not any_sampled or scratch.numel() >= rows * V
     assert out.dtype == torch.int32 and top_k.dtype == torch.int32
     _check(lib().xr_sample(logits.data_ptr(), logits.stride(0), rows, V, temp.data_ptr(), top_k.data_ptr(),
                            top_p.data_ptr(), min_p.data_ptr(), penalty.data_ptr(), draw.data_ptr(), _ptr(recent),
                            scratch.data_ptr(), out.data_ptr(), _stream()), "sample")
+    _count()
+
+
+# ---------------------------------------------------------------------------
+EPI_STORE, EPI_ADD, EPI_SWIGLU = 0, 1, 2
+_TC_SCRATCH_FLOATS = 32 << 20
+_tc_state = {}
+
+
+def tc_workspace(device: torch.device):
+    """(split-K scratch, status word) of the tensor-core product on `device`, made on first use."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    st = _tc_state.get(key)
+    if st is None:
+        st = (torch.empty(_TC_SCRATCH_FLOATS, dtype=torch.float32, device=device),
+              torch.zeros(1, dtype=torch.int32, device=device))
+        _tc_state[key] = st
+    return st
+
+
+def tc_check_status(device: torch.device) -> None:
+    """Raise if a tensor-core kernel gave up a wait since the last check (reads one word from the device)."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    st = _tc_state.get(key)
+    if st is not None and int(st[1].item()) != 0:
+        st[1].zero_()
+        raise KernelError("a tcgen05 product gave up waiting on a barrier; its output is not valid")
+
+
+def gemm_tc_supported(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
+    k = x.shape[1]
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and k >= 8 and k % 8 == 0 and x.stride(1) == 1
+            and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and w.is_contiguous()
+            and out.stride(1) == 1)
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+            epilogue: int = EPI_STORE, force_splits: int = 0) -> None:
+    """bfloat16 product on tcgen05.  EPI_STORE: out[t][r] = x.w (+bias); EPI_ADD: float32 out += ...;
+    EPI_SWIGLU: w is [2F, K] (gate rows, then up rows), out[t][f] = silu(x.w_gate) * (x.w_up)."""
+    n, k = x.shape
+    n_out = w.shape[0] // 2 if epilogue == EPI_SWIGLU else w.shape[0]
+    assert w.shape[1] == k and out.shape == (n, n_out) and gemm_tc_supported(x, w, out)
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == n_out and epilogue != EPI_SWIGLU)
+    scratch, status = tc_workspace(x.device)
+    _check(lib().xr_gemm_tc(x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), dtype_code(out.dtype), epilogue,
+                            n, n_out, k, x.stride(0), out.stride(0), scratch.data_ptr(), scratch.numel(),
+                            status.data_ptr(), force_splits, _stream()), "gemm_tc")
     _count()

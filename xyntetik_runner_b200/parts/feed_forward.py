@@ -7,7 +7,7 @@ import torch
 from .. import kernels
 from ..weights.loader import TensorSpec
 from .base import FeedForward, register_feed_forward
-from .linear import Linear
+from .linear import Linear, counters
 
 
 class SwiGLU(FeedForward):
@@ -36,11 +36,17 @@ class SwiGLU(FeedForward):
         return self.gate_up.nbytes() + self.down.nbytes()
 
     def forward(self, ctx, h, x):
+        from . import linear_tc
         n = h.shape[0]
-        gu = ctx.buf("ffn_gate_up", (n, 2 * self.inner), ctx.act_dtype)
-        self.gate_up.forward(h, gu)
         act = ctx.buf("ffn_act", (n, self.inner), ctx.act_dtype)
-        kernels.silu_mul(gu, act)
+        if linear_tc.usable(self.gate_up, h, act, False):
+            # gate and up share the X tile; silu(g) * u happens in the product's epilogue
+            kernels.gemm_tc(h, self.gate_up.weight, act, None, kernels.EPI_SWIGLU)
+            counters["tcgen05"] += 1
+        else:
+            gu = ctx.buf("ffn_gate_up", (n, 2 * self.inner), ctx.act_dtype)
+            self.gate_up.forward(h, gu)
+            kernels.silu_mul(gu, act)
         self.down.forward(act, x, accumulate=True)
 
 

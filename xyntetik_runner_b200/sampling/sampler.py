@@ -114,5 +114,5 @@ class DeviceSampler:
         if self._scratch is None or self._scratch.numel() < need:
             self._scratch = torch.empty(need, dtype=torch.float32, device=self.device)
         out = torch.empty(rows, dtype=torch.int32, device=self.device)
-        kernels.sample(logits, fd[0], kd, fd[1], fd[2], fd[3], fd[4], recent, self._scratch, out)
+        kernels.sample(logits, fd[0], kd, fd[1], fd[2], fd[3], fd[4], recent, self._scratch, out, any_sampled)
         return out
