@@ -142,9 +142,11 @@ def test_command_line(folders, tmp_path):
     env = dict(os.environ, PYTHONPATH=ROOT)
     out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "runner"), "-m", folder, "-p", "ABCDE", "-n", "6",
                           "--temp", "0", "--ignore-eos", "--dtype", "float32", "-c", "64"],
-                         capture_output=True, text=True, env=env, timeout=300)
-    assert out.returncode == 0, out.stderr
-    assert out.stdout.splitlines()[0] == "ids:" + ",".join(map(str, want))
+                         capture_output=True, env=env, timeout=300)
+    assert out.returncode == 0, out.stderr.decode(errors="replace")
+    lines = out.stdout.split(b"\n")
+    assert lines[0].decode() == "ids:" + ",".join(map(str, want))
+    assert lines[1] == bytes(want)              # every id is a byte here, so the bytes are printed too
     out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "runner"), "-m", folder, "-p", "ids:3,4", "-s", "0",
                           "--temp", "0.5"], capture_output=True, text=True, env=env, timeout=300)
     assert out.returncode == 2 and "refused" in out.stderr

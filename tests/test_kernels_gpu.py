@@ -154,3 +154,131 @@ def test_silu_mul():
     kernels.silu_mul(gu.to(DEV), h)
     assert float((h.cpu().double() - ref).abs().max()) <= 1e-6 * float(ref.abs().max())
     assert float(h[0, 0]) == 0.0 and float(h[0, 1]) != 0.0
+
+
+# ---------------------------------------------------------------------------------------------
+# attention over a paged cache, against a float64 computation
+# ---------------------------------------------------------------------------------------------
+def _paged_case(seed, H, K, hd, page, seg_specs, dtype, window=0, spike=None):
+    """seg_specs: [(pos0, length)].  Builds a cache with shuffled pages holding keys/values for positions
+    [0, pos0 + length) of every request, and queries for the last `length` positions.  Returns everything the
+    kernels need plus the float64 reference output."""
+    rng = np.random.RandomState(seed)
+    n_seg = len(seg_specs)
+    max_len = max(p + l for p, l in seg_specs)
+    max_pages = -(-max_len // page)
+    n_pages = sum(-(-(p + l) // page) for p, l in seg_specs) + 3
+    perm = rng.permutation(n_pages)
+    cache = torch.zeros(n_pages, 1, 2, K, page, hd)
+    cache.normal_()                                        # stale values everywhere: reuse must not matter
+    bt = np.full((n_seg, max_pages), -1, dtype=np.int32)
+    ks, vs, qs = [], [], []
+    nxt = 0
+    for s, (p0, L) in enumerate(seg_specs):
+        T = p0 + L
+        k = torch.from_numpy(rng.randn(T, K, hd).astype(np.float32))
+        v = torch.from_numpy(rng.randn(T, K, hd).astype(np.float32))
+        q = torch.from_numpy(rng.randn(L, H, hd).astype(np.float32))
+        if spike is not None and s == spike[0]:
+            # one far key stands out for the last query of this request: its value must dominate the output
+            _, key_pos, strength = spike
+            k[key_pos] = q[-1].reshape(K, H // K, hd)[:, 0] * strength / hd
+        if dtype == torch.bfloat16:
+            k, v, q = bf16_round(k), bf16_round(v), bf16_round(q)
+        for i in range(-(-T // page)):
+            bt[s, i] = perm[nxt]; nxt += 1
+        for t in range(T):
+            if window and t < p0 - window + 1 - page:
+                continue                                    # pages wholly behind the window may be gone
+            cache[bt[s, t // page], 0, 0, :, t % page] = k[t]
+            cache[bt[s, t // page], 0, 1, :, t % page] = v[t]
+        if window:
+            for i in range(max(0, (p0 - window + 1) // page)):
+                bt[s, i] = -1
+        ks.append(k); vs.append(v); qs.append(q)
+    scale = 1.0 / math.sqrt(hd)
+    refs = []
+    G = H // K
+    for (p0, L), k, v, q in zip(seg_specs, ks, vs, qs):
+        out = torch.zeros(L, H, hd, dtype=torch.float64)
+        for i in range(L):
+            p = p0 + i
+            t0 = max(0, p - window + 1) if window else 0
+            for h in range(H):
+                sc = (k[t0:p + 1, h // G].double() @ q[i, h].double()) * scale
+                out[i, h] = torch.softmax(sc, 0) @ v[t0:p + 1, h // G].double()
+        refs.append(out.reshape(L, H * hd))
+    n = sum(l for _, l in seg_specs)
+    qkv = torch.zeros(n, (H + 2 * K) * hd)
+    qkv[:, :H * hd] = torch.cat([q.reshape(-1, H * hd) for q in qs])
+    starts = np.cumsum([0] + [l for _, l in seg_specs[:-1]]).astype(np.int32)
+    lens = np.array([l for _, l in seg_specs], dtype=np.int32)
+    pos0 = np.array([p for p, _ in seg_specs], dtype=np.int32)
+    positions = np.concatenate([np.arange(p, p + l) for p, l in seg_specs]).astype(np.int32)
+    tok_seg = np.concatenate([np.full(l, s) for s, (_, l) in enumerate(seg_specs)]).astype(np.int32)
+    return dict(cache=cache.to(dtype).to(DEV), bt=torch.from_numpy(bt).to(DEV), qkv=qkv.to(dtype).to(DEV),
+                starts=torch.from_numpy(starts).to(DEV), lens=torch.from_numpy(lens).to(DEV), pos0=torch.from_numpy(pos0).to(DEV),
+                positions=torch.from_numpy(positions).to(DEV), tok_seg=torch.from_numpy(tok_seg).to(DEV),
+                ref=torch.cat(refs), n=n, n_seg=n_seg, max_pages=max_pages, max_len=max_len, lens_host=lens, scale=scale)
+
+
+def _run_attention(case, kind, H, K, hd, page, window, dtype):
+    from xyntetik_runner_b200 import kernels
+    c = case
+    out = torch.zeros(c["n"], H * hd, dtype=dtype, device=DEV)
+    cache = c["cache"]
+    k_ptr, page_stride, v_off = cache.data_ptr(), cache.stride(0), cache.stride(2)
+    qkv_dim = (H + 2 * K) * hd
+    if kind == "simt":
+        kernels.attention_simt(c["qkv"], qkv_dim, out, k_ptr, c["positions"], c["tok_seg"], c["bt"], page_stride, v_off,
+                               H, K, hd, c["max_pages"], page, window, c["scale"])
+    else:
+        G = H // K
+        splits = kernels.attention_mma_splits(c["max_len"], window)
+        pa = torch.full((c["n_seg"] * K * splits * 16 * hd,), float("nan"), device=DEV)
+        pm = torch.full((c["n_seg"] * K * splits * 32,), float("nan"), device=DEV)
+        lens = c["lens_host"]
+        kernels.attention_mma(c["qkv"], qkv_dim, out, k_ptr, c["starts"], c["lens"], c["pos0"], c["bt"], pa, pm, page_stride,
+                              v_off, H, K, hd, c["max_pages"], page, window, c["scale"], c["n_seg"], int(lens.max()),
+                              c["max_len"], splits, bool((lens * G <= 16).any()), bool((lens * G > 16).any()))
+    return out.cpu().double()
+
+
+ATT_CASES = [
+    # H, K, hd, page, window, segments (pos0, length)
+    (4, 2, 16, 16, 0, [(0, 5), (0, 70), (37, 1), (120, 9)]),
+    (3, 1, 32, 8, 0, [(0, 1), (63, 2), (64, 1), (0, 129), (700, 1)]),
+    (8, 2, 64, 64, 0, [(0, 200), (1500, 1), (511, 1), (512, 1), (513, 3)]),
+    (32, 8, 128, 64, 0, [(0, 33), (1030, 1), (300, 70)]),
+    (6, 2, 48, 4, 24, [(0, 50), (100, 1), (23, 1), (24, 1), (60, 7), (600, 2)]),
+    (5, 5, 80, 16, 0, [(10, 20), (0, 3), (515, 1)]),
+    (16, 1, 112, 32, 100, [(0, 10), (1100, 1), (90, 30)]),
+    (12, 4, 96, 16, 0, [(5, 6), (250, 40)]),
+]
+
+
+@pytest.mark.parametrize("case_id", range(len(ATT_CASES)))
+@pytest.mark.parametrize("kind", ["simt_f32", "simt_bf16", "mma"])
+def test_attention_kernels(case_id, kind):
+    H, K, hd, page, window, segs = ATT_CASES[case_id]
+    dtype = torch.float32 if kind == "simt_f32" else torch.bfloat16
+    case = _paged_case(case_id, H, K, hd, page, segs, dtype, window)
+    got = _run_attention(case, "simt" if kind.startswith("simt") else "mma", H, K, hd, page, window, dtype)
+    ref = case["ref"]
+    # inputs are exact in the kernel's own dtype, so the error is that of the arithmetic: float32 sums,
+    # or (tensor-core path) probabilities rounded to bfloat16 before P.V and the bfloat16 output
+    tol = 2e-5 if kind == "simt_f32" else 1.2e-2
+    err = (got - ref).abs().max(dim=1).values / ref.abs().max()
+    assert float(err.max()) <= tol, f"worst rows {torch.topk(err, min(5, len(err))).indices.tolist()} err {float(err.max()):.3e}"
+
+
+@pytest.mark.parametrize("kind", ["simt", "mma"])
+def test_attention_finds_a_far_key(kind):
+    """One key hundreds of positions back carries almost all the weight of the last query: a kernel that
+    skipped or misplaced it (a page edge, a span edge) would be far off."""
+    H, K, hd, page = 8, 2, 64, 16
+    for key_pos in (0, 15, 16, 511, 512, 700):
+        case = _paged_case(50 + key_pos, H, K, hd, page, [(0, 3), (900, 1), (1023, 2)], torch.bfloat16, 0, spike=(1, key_pos, 60.0))
+        got = _run_attention(case, kind, H, K, hd, page, 0, torch.bfloat16)
+        err = (got - case["ref"]).abs().max() / case["ref"].abs().max()
+        assert float(err) <= 1.2e-2, (key_pos, float(err))

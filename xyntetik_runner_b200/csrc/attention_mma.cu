@@ -1,0 +1,440 @@
+// Causal grouped-query attention over the paged cache on tensor cores (bfloat16 in, float32 softmax and
+// accumulation), for prompt portions and for decoded tokens, head sizes 16..128 in steps of 16.
+//
+// For the query at position p, head h, kv head h / (H/K):  s_t = (q . k_t) * scale over the keys
+// t0 <= t <= p (t0 = max(0, p - window + 1), or 0), a = softmax(s), o = sum_t a_t v_t
+// (src/model.c:3548-3589, 3409-3415).  The reference's kernels are `k_attn` (one block per head and
+// token, scores through a global scratch, src/kernels.cu:2043-2141) and the split `k_attn_dec` +
+// `k_attn_merge` for decoding (src/kernels.cu:2171-2270).
+//
+// The G = H/K query heads of one kv head are packed along the M axis of the matrix instruction: packed
+// row i of a request's portion is (token i / G, head i % G), so every K and V element that is loaded
+// serves G heads.  Keys are walked in tiles of 64 aligned to absolute positions, always in ascending
+// order and with masked scores contributing exactly zero, so a query's result depends on its position and
+// the keys only -- not on how the step was cut, on the batch, or on the pages.
+//
+// Two kernels share the inner loops:
+//  * rows: a CTA owns 64 packed rows (4 warps x 16) of one (request, kv head) and walks all its keys.
+//    For portions of prompts.
+//  * keys: a request's portion has at most 16 packed rows (a decoded token, or a few); a CTA owns one
+//    span of ATT_SPLIT keys, its four warps take 16 keys each of every tile and their running
+//    (max, sum, accumulator) are combined in shared memory.  Spans are fixed ranges of absolute
+//    positions; `k_attention_merge` combines them in ascending order.
+// K and V rows are gathered page by page with 16-byte cp.async copies (any page size), double buffered.
+#include "common.cuh"
+#include <math.h>
+
+#define ATT_TILE 64            // keys per tile
+#define ATT_ROWS 64            // packed query rows per CTA in the rows kernel
+#define ATT_SPLIT 512          // keys per CTA in the keys kernel
+#define ATT_THREADS 128
+
+struct AttnMmaArgs {
+    const __nv_bfloat16* q;      // token t, head h at q + t * q_stride + h * hd
+    __nv_bfloat16* out;          // [n, H * hd]
+    const __nv_bfloat16* cache_k;
+    const int* seg_start;        // [n_seg] first flat token of the portion
+    const int* seg_len;          // [n_seg]
+    const int* seg_pos0;         // [n_seg] position of its first token
+    const int* block_tables;     // [n_seg][max_pages]
+    float* part_acc;             // keys kernel: [n_seg][K][splits][16][hd]
+    float* part_ml;              // keys kernel: [n_seg][K][splits][16][2]
+    long long q_stride, page_stride, v_offset;
+    int H, K, G, max_pages, page_size, window, max_splits;
+    float scale;
+};
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldsm_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"((uint32_t)__cvta_generic_to_shared(p)));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Gather one tile of keys (or values) [ATT_TILE][HD] into shared memory rows of HD + 8 elements.
+// Rows at positions outside [lo, hi] or on a page the request no longer holds are zero-filled.
+template <int HD>
+__device__ __forceinline__ void load_kv_tile(__nv_bfloat16* dst, const __nv_bfloat16* base, const int* bt, int page_size,
+                                             long long page_stride, int kvh, int key0, int lo, int hi) {
+    constexpr int CH = HD / 8;                       // 16-byte chunks per row
+    constexpr int LD = HD + 8;
+    for (int i = threadIdx.x; i < ATT_TILE * CH; i += ATT_THREADS) {
+        int r = i / CH, c = i % CH;
+        int kp = key0 + r;
+        __nv_bfloat16* d = dst + r * LD + c * 8;
+        int page = (kp >= lo && kp <= hi) ? bt[kp / page_size] : -1;
+        if (page >= 0) {
+            const __nv_bfloat16* src = base + (long long)page * page_stride + ((long long)kvh * page_size + (kp % page_size)) * HD + c * 8;
+            cp_async16(d, src);
+        } else {
+            *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+        }
+    }
+}
+
+// One tile of the online softmax for a warp's 16 rows against NKT n-tiles (8 keys each) starting at
+// column `col0` of the shared tile:  S = Q K^T, mask, running max/sum, O += P V.
+template <int HD, int NKT>
+__device__ __forceinline__ void tile_step(const uint32_t (*qf)[4], const __nv_bfloat16* ks, const __nv_bfloat16* vs,
+                                          int col0, int key0, int pos_a, int pos_b, int window, float scale,
+                                          float* m, float* l, float (*o)[4]) {
+    constexpr int LD = HD + 8;
+    const int lane = threadIdx.x & 31;
+    float s[NKT][4];
+#pragma unroll
+    for (int j = 0; j < NKT; j++) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; kk++) {
+#pragma unroll
+        for (int j = 0; j < NKT; j += 2) {
+            uint32_t b0, b1, b2, b3;
+            const __nv_bfloat16* p = ks + (col0 + j * 8 + (lane & 7) + ((lane >> 4) << 3)) * LD + kk * 16 + (((lane >> 3) & 1) << 3);
+            ldsm_x4(b0, b1, b2, b3, p);
+            mma_bf16(s[j], qf[kk], b0, b1);
+            mma_bf16(s[j + 1], qf[kk], b2, b3);
+        }
+    }
+    // mask and scale: element (row a: c0,c1 ; row b: c2,c3) of n-tile j is key key0 + col0 + 8j + 2t (+1)
+    const int t2 = (lane & 3) * 2;
+    const int lo_a = window > 0 ? pos_a - window + 1 : 0, lo_b = window > 0 ? pos_b - window + 1 : 0;
+    float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < NKT; j++) {
+#pragma unroll
+        for (int e = 0; e < 2; e++) {
+            int kp = key0 + col0 + j * 8 + t2 + e;
+            float va = (kp <= pos_a && kp >= lo_a) ? s[j][e] * scale : -INFINITY;
+            float vb = (kp <= pos_b && kp >= lo_b) ? s[j][2 + e] * scale : -INFINITY;
+            s[j][e] = va; s[j][2 + e] = vb;
+            mx_a = fmaxf(mx_a, va); mx_b = fmaxf(mx_b, vb);
+        }
+    }
+    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1)); mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1)); mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+    float mn_a = fmaxf(m[0], mx_a), mn_b = fmaxf(m[1], mx_b);
+    // a row that has seen no key yet keeps max = -inf; subtracting 0 instead keeps exp() at exactly 0
+    float off_a = mn_a == -INFINITY ? 0.f : mn_a, off_b = mn_b == -INFINITY ? 0.f : mn_b;
+    float ca = expf(m[0] - off_a), cb = expf(m[1] - off_b);      // m = -inf -> 0
+    m[0] = mn_a; m[1] = mn_b;
+    float sa = 0.f, sb = 0.f;
+#pragma unroll
+    for (int j = 0; j < NKT; j++) {
+        s[j][0] = expf(s[j][0] - off_a); s[j][1] = expf(s[j][1] - off_a);
+        s[j][2] = expf(s[j][2] - off_b); s[j][3] = expf(s[j][3] - off_b);
+        sa += s[j][0] + s[j][1]; sb += s[j][2] + s[j][3];
+    }
+    sa += __shfl_xor_sync(0xffffffffu, sa, 1); sa += __shfl_xor_sync(0xffffffffu, sa, 2);
+    sb += __shfl_xor_sync(0xffffffffu, sb, 1); sb += __shfl_xor_sync(0xffffffffu, sb, 2);
+    l[0] = l[0] * ca + sa; l[1] = l[1] * cb + sb;
+#pragma unroll
+    for (int d = 0; d < HD / 8; d++) { o[d][0] *= ca; o[d][1] *= ca; o[d][2] *= cb; o[d][3] *= cb; }
+    // O += P V, 16 keys per step
+#pragma unroll
+    for (int kk = 0; kk < NKT / 2; kk++) {
+        uint32_t a[4] = {pack_bf16(s[2 * kk][0], s[2 * kk][1]), pack_bf16(s[2 * kk][2], s[2 * kk][3]),
+                         pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]), pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3])};
+#pragma unroll
+        for (int d = 0; d < HD / 8; d += 2) {
+            uint32_t b0, b1, b2, b3;
+            const __nv_bfloat16* p = vs + (col0 + kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3)) * LD + d * 8 + ((lane >> 4) << 3);
+            ldsm_x4_t(b0, b1, b2, b3, p);
+            mma_bf16(o[d], a, b0, b1);
+            mma_bf16(o[d + 1], a, b2, b3);
+        }
+    }
+}
+
+// Q rows of this CTA -> shared [ATT_ROWS or 16][HD + 8]; rows past the portion are zero.
+template <int HD>
+__device__ __forceinline__ void load_q(__nv_bfloat16* qs, const AttnMmaArgs& a, int tok_base, int kvh, int row0, int rows,
+                                       int rows_total) {
+    constexpr int CH = HD / 8, LD = HD + 8;
+    for (int i = threadIdx.x; i < rows * CH; i += ATT_THREADS) {
+        int r = i / CH, c = i % CH;
+        int pr = row0 + r;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (pr < rows_total) {
+            int tok = tok_base + pr / a.G, head = kvh * a.G + pr % a.G;
+            v = *reinterpret_cast<const uint4*>(a.q + (long long)tok * a.q_stride + (long long)head * HD + c * 8);
+        }
+        *reinterpret_cast<uint4*>(qs + r * LD + c * 8) = v;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// rows kernel: grid (q tiles, K, segments)
+// ---------------------------------------------------------------------------------------------
+template <int HD>
+__global__ void __launch_bounds__(ATT_THREADS)
+k_attention_rows(AttnMmaArgs a) {
+    constexpr int LD = HD + 8;
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    __nv_bfloat16* qs = (__nv_bfloat16*)smem_raw;                 // [64][LD]
+    __nv_bfloat16* kbuf = qs + ATT_ROWS * LD;                      // [2][64][LD]
+    __nv_bfloat16* vbuf = kbuf + 2 * ATT_TILE * LD;                // [2][64][LD]
+    const int seg = blockIdx.z, kvh = blockIdx.y;
+    const int L = a.seg_len[seg], rows_total = L * a.G, row0 = blockIdx.x * ATT_ROWS;
+    if (rows_total <= 16 || row0 >= rows_total) return;            // short portions belong to the keys kernel
+    const int pos0 = a.seg_pos0[seg], tok_base = a.seg_start[seg];
+    const int* bt = a.block_tables + (size_t)seg * a.max_pages;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    load_q<HD>(qs, a, tok_base, kvh, row0, ATT_ROWS, rows_total);
+    const int last_row = min(rows_total, row0 + ATT_ROWS) - 1;
+    const int hi = pos0 + last_row / a.G;                                            // last key any row may read
+    const int lo = a.window > 0 ? max(0, pos0 + row0 / a.G - a.window + 1) : 0;       // first key any row may read
+    const int t_lo = lo / ATT_TILE, t_hi = hi / ATT_TILE;
+    load_kv_tile<HD>(kbuf, a.cache_k, bt, a.page_size, a.page_stride, kvh, t_lo * ATT_TILE, lo, hi);
+    load_kv_tile<HD>(vbuf, a.cache_k + a.v_offset, bt, a.page_size, a.page_stride, kvh, t_lo * ATT_TILE, lo, hi);
+    cp_async_commit();
+    __syncthreads();
+    uint32_t qf[HD / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; kk++)
+        ldsm_x4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], qs + (warp * 16 + (lane & 15)) * LD + kk * 16 + ((lane >> 4) << 3));
+    const int ra = row0 + warp * 16 + (lane >> 2), rb = ra + 8;
+    const int pos_a = ra < rows_total ? pos0 + ra / a.G : -1, pos_b = rb < rows_total ? pos0 + rb / a.G : -1;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[HD / 8][4];
+#pragma unroll
+    for (int d = 0; d < HD / 8; d++) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
+    // a warp whose rows all end before a tile starts has nothing to do in it
+    const int warp_hi = pos0 + min(last_row, row0 + warp * 16 + 15) / a.G;
+
+    for (int t = t_lo; t <= t_hi; t++) {
+        int cur = (t - t_lo) & 1;
+        if (t < t_hi) {
+            load_kv_tile<HD>(kbuf + (cur ^ 1) * ATT_TILE * LD, a.cache_k, bt, a.page_size, a.page_stride, kvh, (t + 1) * ATT_TILE, lo, hi);
+            load_kv_tile<HD>(vbuf + (cur ^ 1) * ATT_TILE * LD, a.cache_k + a.v_offset, bt, a.page_size, a.page_stride, kvh, (t + 1) * ATT_TILE, lo, hi);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        if (t * ATT_TILE <= warp_hi)
+            tile_step<HD, 8>(qf, kbuf + cur * ATT_TILE * LD, vbuf + cur * ATT_TILE * LD, 0, t * ATT_TILE, pos_a, pos_b,
+                             a.window, a.scale, m, l, o);
+        __syncthreads();
+    }
+    // rows a (lane/4) and b (+8): columns d*8 + 2*(lane%4) (+1)
+    const int t2 = (lane & 3) * 2;
+#pragma unroll
+    for (int half = 0; half < 2; half++) {
+        int pr = half ? rb : ra;
+        if (pr >= rows_total) continue;
+        float inv = 1.0f / l[half];
+        __nv_bfloat16* dst = a.out + ((long long)(tok_base + pr / a.G) * a.H + (kvh * a.G + pr % a.G)) * HD;
+#pragma unroll
+        for (int d = 0; d < HD / 8; d++)
+            *reinterpret_cast<uint32_t*>(dst + d * 8 + t2) = pack_bf16(o[d][2 * half] * inv, o[d][2 * half + 1] * inv);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// keys kernel: grid (spans, K, segments); portions of at most 16 packed rows
+// ---------------------------------------------------------------------------------------------
+template <int HD>
+__global__ void __launch_bounds__(ATT_THREADS)
+k_attention_keys(AttnMmaArgs a) {
+    constexpr int LD = HD + 8;
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    __nv_bfloat16* qs = (__nv_bfloat16*)smem_raw;                 // [16][LD]
+    __nv_bfloat16* kbuf = qs + 16 * LD;
+    __nv_bfloat16* vbuf = kbuf + 2 * ATT_TILE * LD;
+    const int seg = blockIdx.z, kvh = blockIdx.y, span = blockIdx.x;
+    const int L = a.seg_len[seg], rows_total = L * a.G;
+    if (rows_total > 16) return;
+    const int pos0 = a.seg_pos0[seg], tok_base = a.seg_start[seg];
+    const int hi_all = pos0 + L - 1;
+    const int lo_all = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
+    const int first_span = lo_all / ATT_SPLIT;
+    const int k_begin = (first_span + span) * ATT_SPLIT;           // spans are fixed ranges of absolute positions
+    if (k_begin > hi_all) return;
+    const int lo = max(lo_all, k_begin), hi = min(hi_all, k_begin + ATT_SPLIT - 1);
+    const int* bt = a.block_tables + (size_t)seg * a.max_pages;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    load_q<HD>(qs, a, tok_base, kvh, 0, 16, rows_total);
+    const int t_lo = lo / ATT_TILE, t_hi = hi / ATT_TILE;
+    load_kv_tile<HD>(kbuf, a.cache_k, bt, a.page_size, a.page_stride, kvh, t_lo * ATT_TILE, lo, hi);
+    load_kv_tile<HD>(vbuf, a.cache_k + a.v_offset, bt, a.page_size, a.page_stride, kvh, t_lo * ATT_TILE, lo, hi);
+    cp_async_commit();
+    __syncthreads();
+    uint32_t qf[HD / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; kk++)
+        ldsm_x4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], qs + (lane & 15) * LD + kk * 16 + ((lane >> 4) << 3));
+    const int ra = lane >> 2, rb = ra + 8;
+    const int pos_a = ra < rows_total ? pos0 + ra / a.G : -1, pos_b = rb < rows_total ? pos0 + rb / a.G : -1;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[HD / 8][4];
+#pragma unroll
+    for (int d = 0; d < HD / 8; d++) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
+
+    for (int t = t_lo; t <= t_hi; t++) {
+        int cur = (t - t_lo) & 1;
+        if (t < t_hi) {
+            load_kv_tile<HD>(kbuf + (cur ^ 1) * ATT_TILE * LD, a.cache_k, bt, a.page_size, a.page_stride, kvh, (t + 1) * ATT_TILE, lo, hi);
+            load_kv_tile<HD>(vbuf + (cur ^ 1) * ATT_TILE * LD, a.cache_k + a.v_offset, bt, a.page_size, a.page_stride, kvh, (t + 1) * ATT_TILE, lo, hi);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        // warp w takes keys [16w, 16w + 16) of the tile; every key of these tiles lies inside the span, and
+        // keys outside [lo, hi] are outside every row's own range, so the per-row mask is all that is needed
+        int c0 = warp * 16, kfirst = t * ATT_TILE + c0;
+        if (kfirst <= hi && kfirst + 15 >= lo)
+            tile_step<HD, 2>(qf, kbuf + cur * ATT_TILE * LD, vbuf + cur * ATT_TILE * LD, c0, t * ATT_TILE, pos_a, pos_b,
+                             a.window, a.scale, m, l, o);
+        __syncthreads();
+    }
+    // combine the four warps: shared [4][16][HD] accumulators and [4][16][2] (max, sum); the key tiles are done with
+    float* acc_s = reinterpret_cast<float*>(kbuf);
+    float* ml_s = acc_s + 4 * 16 * HD;
+    const int t2 = (lane & 3) * 2;
+#pragma unroll
+    for (int d = 0; d < HD / 8; d++) {
+        acc_s[(warp * 16 + ra) * HD + d * 8 + t2] = o[d][0]; acc_s[(warp * 16 + ra) * HD + d * 8 + t2 + 1] = o[d][1];
+        acc_s[(warp * 16 + rb) * HD + d * 8 + t2] = o[d][2]; acc_s[(warp * 16 + rb) * HD + d * 8 + t2 + 1] = o[d][3];
+    }
+    if ((lane & 3) == 0) {
+        ml_s[(warp * 16 + ra) * 2] = m[0]; ml_s[(warp * 16 + ra) * 2 + 1] = l[0];
+        ml_s[(warp * 16 + rb) * 2] = m[1]; ml_s[(warp * 16 + rb) * 2 + 1] = l[1];
+    }
+    __syncthreads();
+    size_t item = ((size_t)seg * a.K + kvh) * a.max_splits + span;
+    float* pacc = a.part_acc + item * 16 * HD;
+    float* pml = a.part_ml + item * 16 * 2;
+    for (int i = threadIdx.x; i < rows_total * HD; i += ATT_THREADS) {
+        int r = i / HD, d = i % HD;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; w++) mm = fmaxf(mm, ml_s[(w * 16 + r) * 2]);
+        float off = mm == -INFINITY ? 0.f : mm;
+        float acc = 0.f, ll = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            float f = expf(ml_s[(w * 16 + r) * 2] - off);
+            acc += acc_s[(w * 16 + r) * HD + d] * f;
+            ll += ml_s[(w * 16 + r) * 2 + 1] * f;
+        }
+        pacc[r * HD + d] = acc;
+        if (d == 0) { pml[r * 2] = mm; pml[r * 2 + 1] = ll; }
+    }
+}
+
+// Combine the spans of one (request, kv head) in ascending order and write the output rows.
+// grid (K, segments), one warp per packed row.
+template <int HD>
+__global__ void k_attention_merge(AttnMmaArgs a) {
+    const int seg = blockIdx.y, kvh = blockIdx.x;
+    const int L = a.seg_len[seg], rows_total = L * a.G;
+    if (rows_total > 16) return;
+    const int pos0 = a.seg_pos0[seg], tok_base = a.seg_start[seg];
+    const int hi_all = pos0 + L - 1;
+    const int lo_all = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
+    const int n_spans = hi_all / ATT_SPLIT - lo_all / ATT_SPLIT + 1;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int r = warp; r < rows_total; r += blockDim.x >> 5) {
+        size_t item0 = ((size_t)seg * a.K + kvh) * a.max_splits;
+        float mm = -INFINITY;
+        for (int s = 0; s < n_spans; s++) mm = fmaxf(mm, a.part_ml[((item0 + s) * 16 + r) * 2]);
+        float off = mm == -INFINITY ? 0.f : mm;
+        float ll = 0.f;
+        for (int s = 0; s < n_spans; s++) ll += a.part_ml[((item0 + s) * 16 + r) * 2 + 1] * expf(a.part_ml[((item0 + s) * 16 + r) * 2] - off);
+        float inv = 1.0f / ll;
+        __nv_bfloat16* dst = a.out + ((long long)(tok_base + r / a.G) * a.H + (kvh * a.G + r % a.G)) * HD;
+        for (int d = lane; d < HD; d += 32) {
+            float acc = 0.f;
+            for (int s = 0; s < n_spans; s++)
+                acc += a.part_acc[((item0 + s) * 16 + r) * HD + d] * expf(a.part_ml[((item0 + s) * 16 + r) * 2] - off);
+            dst[d] = __float2bfloat16_rn(acc * inv);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+template <int HD>
+static int launch_attention(const AttnMmaArgs& a, int n_seg, int max_seg_len, int max_kv_len, int any_short, int any_long,
+                            cudaStream_t stream) {
+    constexpr int LD = HD + 8;
+    constexpr int SMEM_ROWS = (ATT_ROWS + 4 * ATT_TILE) * LD * 2;
+    constexpr int KEYS_TILES = (16 + 4 * ATT_TILE) * LD * 2;
+    constexpr int KEYS_MERGE = 16 * LD * 2 + (4 * 16 * HD + 4 * 16 * 2) * 4;
+    constexpr int SMEM_KEYS = KEYS_TILES > KEYS_MERGE ? KEYS_TILES : KEYS_MERGE;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(k_attention_rows<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ROWS) != cudaSuccess ||
+            cudaFuncSetAttribute(k_attention_keys<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_KEYS) != cudaSuccess)
+            return XR_ERR_LAUNCH;
+        configured = true;
+    }
+    if (any_long) {
+        long long tiles = ((long long)max_seg_len * a.G + ATT_ROWS - 1) / ATT_ROWS;
+        if (tiles > 0x7fffffffLL || n_seg > 65535 || a.K > 65535) return XR_ERR_ARG;
+        k_attention_rows<HD><<<dim3((unsigned)tiles, a.K, n_seg), ATT_THREADS, SMEM_ROWS, stream>>>(a);
+        int rc = xr_launch_status();
+        if (rc != XR_OK) return rc;
+    }
+    if (any_short) {
+        if (n_seg > 65535 || a.K > 65535) return XR_ERR_ARG;
+        k_attention_keys<HD><<<dim3(a.max_splits, a.K, n_seg), ATT_THREADS, SMEM_KEYS, stream>>>(a);
+        int rc = xr_launch_status();
+        if (rc != XR_OK) return rc;
+        k_attention_merge<HD><<<dim3(a.K, n_seg), 128, 0, stream>>>(a);
+        return xr_launch_status();
+    }
+    return XR_OK;
+}
+
+// Spans the keys kernel needs for a longest key range of `max_kv_len` (window > 0: at most that many keys).
+XR_EXPORT int xr_attention_mma_splits(int max_kv_len, int window) {
+    int range = window > 0 && window + 16 < max_kv_len ? window + 16 : max_kv_len;
+    return (range + ATT_SPLIT - 1) / ATT_SPLIT + (window > 0 ? 1 : 0);
+}
+
+// part_acc: float32 [n_seg * K * splits * 16 * hd], part_ml: float32 [n_seg * K * splits * 32]
+// (only read and written when any_short).  splits must be xr_attention_mma_splits(max_kv_len, window).
+XR_EXPORT int xr_attention_mma(const void* q, void* out, const void* cache_k, const int* seg_start, const int* seg_len,
+                               const int* seg_pos0, const int* block_tables, float* part_acc, float* part_ml,
+                               long long q_stride, long long page_stride, long long v_offset, int n_seg, int H, int K,
+                               int hd, int max_pages, int page_size, int window, float scale, int max_seg_len,
+                               int max_kv_len, int splits, int any_short, int any_long, cudaStream_t stream) {
+    if (n_seg < 1 || H < 1 || K < 1 || H % K != 0 || hd < 16 || hd > 128 || hd % 16 != 0 || page_size < 1 || window < 0 ||
+        (q_stride % 8) != 0 || ((uintptr_t)q & 15) || ((uintptr_t)cache_k & 15) || (page_stride % 8) != 0 || (v_offset % 8) != 0)
+        return XR_ERR_ARG;
+    if (H / K > 16 && any_short) return XR_ERR_ARG;     // more heads per group than one instruction tile holds
+    AttnMmaArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)cache_k, seg_start, seg_len, seg_pos0,
+                  block_tables, part_acc, part_ml, q_stride, page_stride, v_offset, H, K, H / K, max_pages, page_size, window,
+                  splits, scale};
+    switch (hd) {
+        case 16: return launch_attention<16>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, stream);
+        case 32: return launch_attention<32>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, stream);
+        case 48: return launch_attention<48>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, stream);
+        case 64: return launch_attention<64>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, stream);
+        case 80: return launch_attention<80>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, stream);
+        case 96: return launch_attention<96>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, stream);
+        case 112: return launch_attention<112>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, stream);
+        case 128: return launch_attention<128>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, stream);
+    }
+    return XR_ERR_ARG;
+}

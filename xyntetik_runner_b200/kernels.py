@@ -55,6 +55,9 @@ def _declare(L: ctypes.CDLL) -> None:
         "xr_gemm_simt": [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _ll, _ll, _vp],
         "xr_attention_simt": [_vp, _vp, _i, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
         "xr_gemm_tc": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _ll, _ll, _vp, _ll, _vp, _i, _vp],
+        "xr_attention_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _f,
+                             _i, _i, _i, _i, _i, _vp],
+        "xr_attention_mma_splits": [_i, _i],
         "xr_sample": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     }
     for name, args in sig.items():
@@ -242,3 +245,32 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[
                             n, n_out, k, x.stride(0), out.stride(0), scratch.data_ptr(), scratch.numel(),
                             status.data_ptr(), force_splits, _stream()), "gemm_tc")
     _count()
+
+
+# ---------------------------------------------------------------------------
+def attention_mma_supported(dtype: torch.dtype, H: int, K: int, hd: int) -> bool:
+    return dtype == torch.bfloat16 and hd % 16 == 0 and 16 <= hd <= 128 and H % K == 0 and H // K <= 16
+
+
+def attention_mma_splits(max_kv_len: int, window: int) -> int:
+    return int(lib().xr_attention_mma_splits(max_kv_len, window))
+
+
+def attention_mma(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, cache_k_ptr: int, seg_start, seg_len, seg_pos0,
+                  block_tables, part_acc: Optional[torch.Tensor], part_ml: Optional[torch.Tensor], page_stride: int,
+                  v_offset: int, H: int, K: int, hd: int, max_pages: int, page_size: int, window: int, scale: float,
+                  n_seg: int, max_seg_len: int, max_kv_len: int, splits: int, any_short: bool, any_long: bool) -> None:
+    """Causal attention over the pages on tensor cores (bfloat16).  Portions with at most 16 packed rows
+    (tokens x heads per kv head) go through the key-split kernel and need `part_acc` [n_seg*K*splits*16*hd]
+    and `part_ml` [n_seg*K*splits*32] float32 scratch; longer portions through the row-tiled kernel."""
+    _dev(out, seg_start, seg_len, seg_pos0, block_tables, part_acc, part_ml)
+    assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and out.shape[1] == H * hd
+    if any_short:
+        assert part_acc is not None and part_acc.numel() >= n_seg * K * splits * 16 * hd
+        assert part_ml is not None and part_ml.numel() >= n_seg * K * splits * 32
+    _check(lib().xr_attention_mma(q.data_ptr(), out.data_ptr(), cache_k_ptr, seg_start.data_ptr(), seg_len.data_ptr(),
+                                  seg_pos0.data_ptr(), block_tables.data_ptr(), _ptr(part_acc), _ptr(part_ml),
+                                  q_row_stride, page_stride, v_offset, n_seg, H, K, hd, max_pages, page_size, window,
+                                  float(scale), max_seg_len, max_kv_len, splits, int(any_short), int(any_long),
+                                  _stream()), "attention_mma")
+    _count((1 if any_long else 0) + (2 if any_short else 0))

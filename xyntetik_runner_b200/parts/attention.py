@@ -11,6 +11,7 @@ position encoding are all arguments.
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional
 
 import torch
@@ -19,6 +20,10 @@ from .. import kernels
 from ..weights.loader import TensorSpec
 from .base import KVNeed, Mixer, PositionEncoding, register_mixer
 from .linear import Linear
+
+# XRB200_NO_MMA_ATTENTION=1 sends bfloat16 attention to the float32-arithmetic kernel (for bisecting)
+USE_MMA = os.environ.get("XRB200_NO_MMA_ATTENTION", "0") in ("", "0")
+counters = {"mma": 0, "simt": 0}
 
 
 class GQAAttention(Mixer):
@@ -77,8 +82,25 @@ class GQAAttention(Mixer):
                            self.H, self.K, self.hd, self.position.rotary_dim, ctx.max_pages, ctx.page_size)
         o = ctx.buf("attn_out", (n, self.H * self.hd), ctx.act_dtype)
         # Q is read in place from the fused rows (row stride = qkv_dim)
-        kernels.attention_simt(qkv, qkv_dim, o, k_ptr, ctx.positions, ctx.tok_seg, bt, page_stride, v_offset,
-                               self.H, self.K, self.hd, ctx.max_pages, ctx.page_size, self.window or 0, self.scale)
+        G = self.H // self.K
+        if USE_MMA and kernels.attention_mma_supported(ctx.act_dtype, self.H, self.K, self.hd):
+            seg_len = ctx.host["seg_len"]
+            any_short = bool((seg_len * G <= 16).any())
+            any_long = bool((seg_len * G > 16).any())
+            splits = kernels.attention_mma_splits(ctx.max_kv_len, self.window or 0)
+            pa = pm = None
+            if any_short:
+                pa = ctx.buf("attn_part_acc", (ctx.n_seg * self.K * splits * 16 * self.hd,), torch.float32)
+                pm = ctx.buf("attn_part_ml", (ctx.n_seg * self.K * splits * 32,), torch.float32)
+            kernels.attention_mma(qkv, qkv_dim, o, k_ptr, ctx.seg_start, ctx.seg_len, ctx.seg_pos0, bt, pa, pm,
+                                  page_stride, v_offset, self.H, self.K, self.hd, ctx.max_pages, ctx.page_size,
+                                  self.window or 0, self.scale, ctx.n_seg, int(seg_len.max()), ctx.max_kv_len, splits,
+                                  any_short, any_long)
+            counters["mma"] += 1
+        else:
+            kernels.attention_simt(qkv, qkv_dim, o, k_ptr, ctx.positions, ctx.tok_seg, bt, page_stride, v_offset,
+                                   self.H, self.K, self.hd, ctx.max_pages, ctx.page_size, self.window or 0, self.scale)
+            counters["simt"] += 1
         self.out.forward(o, x, accumulate=True)
 
 
