@@ -406,3 +406,61 @@ XR_EXPORT int xr_gemm_tc(const void* X, const void* W, const float* bias, void* 
     k_splitk_finish<<<blocks, 256, 0, stream>>>(f);
     return xr_launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------
+// An entry point that allocates nothing (declared in xrb200_noalloc.h; it has no counterpart in the
+// reference).  Same product as xr_gemm_tc, but the split-K scratch and the status word live in arrays
+// that are part of this library's image, so the caller passes inputs and outputs only.
+//
+// In host code the names below stand for the arrays but are not device addresses; the address a kernel
+// can use comes from cudaGetSymbolAddress, asked once per device (with that device current) on the
+// entry point's first call there.
+// ---------------------------------------------------------------------------------------------
+#define XR_NOALLOC_SCRATCH_FLOATS (4u << 20)          // 16 MiB of float32, held by every GPU that loads the library
+#define XR_NOALLOC_MAX_DEVICES 64
+static __device__ __align__(256) float g_noalloc_scratch[XR_NOALLOC_SCRATCH_FLOATS];
+static __device__ __align__(256) int g_noalloc_status[64];
+
+static float* g_noalloc_scratch_ptr[XR_NOALLOC_MAX_DEVICES];
+static int* g_noalloc_status_ptr[XR_NOALLOC_MAX_DEVICES];
+
+XR_EXPORT long long xr_gemm_tc_noalloc_max_floats() { return (long long)XR_NOALLOC_SCRATCH_FLOATS; }
+
+XR_EXPORT int xr_gemm_tc_noalloc(const void* X, const void* W, const float* bias, void* out, int out_dtype, int epilogue,
+                                 int n, int n_out, int K, long long ldx, long long ldo, int* status_out_host,
+                                 cudaStream_t stream) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= XR_NOALLOC_MAX_DEVICES) return -5;
+    if (g_noalloc_scratch_ptr[dev] == nullptr) {
+        // set-up, once per device: resolve the arrays' device addresses
+        float* sp = nullptr; int* st = nullptr;
+        if (cudaGetSymbolAddress((void**)&sp, g_noalloc_scratch) != cudaSuccess || sp == nullptr) return -5;
+        if (cudaGetSymbolAddress((void**)&st, g_noalloc_status) != cudaSuccess || st == nullptr) return -5;
+        g_noalloc_status_ptr[dev] = st;
+        g_noalloc_scratch_ptr[dev] = sp;
+    }
+    if (n < 1 || n_out < 1 || K < 8) return XR_ERR_ARG;
+    // the split the product would choose, and what it needs of the fixed array
+    const bool dual = epilogue == TC_EPI_SWIGLU;
+    int bn = n <= 16 ? 16 : (n <= 32 ? 32 : (n <= 64 ? 64 : (n <= 128 ? 128 : 256)));
+    int row_tiles = (n_out + TC_BM - 1) / TC_BM, tok_tiles = (n + bn - 1) / bn, total_kb = (K + TC_BK - 1) / TC_BK;
+    int splits = choose_splits(row_tiles * tok_tiles, total_kb, 148);
+    if (splits > total_kb) splits = total_kb;
+    int per = (total_kb + splits - 1) / splits;
+    splits = (total_kb + per - 1) / per;
+    long long need = splits > 1 ? (long long)splits * n * n_out * (dual ? 2 : 1) : 0;
+    if (need > (long long)XR_NOALLOC_SCRATCH_FLOATS) return -4;
+    // the status word must start at zero; the scratch needs no clearing (every partial that is read was
+    // written by this call first)
+    if (cudaMemsetAsync(g_noalloc_status_ptr[dev], 0, sizeof(int), stream) != cudaSuccess) return XR_ERR_LAUNCH;
+    int rc = xr_gemm_tc(X, W, bias, out, out_dtype, epilogue, n, n_out, K, ldx, ldo, g_noalloc_scratch_ptr[dev],
+                        (long long)XR_NOALLOC_SCRATCH_FLOATS, g_noalloc_status_ptr[dev], splits, stream);
+    if (rc != XR_OK) return rc;
+    if (status_out_host != nullptr) {
+        // optional: wait for the product and report whether a wait inside it gave up
+        if (cudaMemcpyAsync(status_out_host, g_noalloc_status_ptr[dev], sizeof(int), cudaMemcpyDeviceToHost, stream) != cudaSuccess ||
+            cudaStreamSynchronize(stream) != cudaSuccess)
+            return XR_ERR_LAUNCH;
+    }
+    return XR_OK;
+}
