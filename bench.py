@@ -101,6 +101,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=CONTEXT)
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--decode-only", action="store_true", help="time the decode step only (for profiling a small run)")
+    ap.add_argument("--no-graphs", action="store_true", help="launch every kernel of a decode step one by one")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -125,11 +127,14 @@ def main() -> int:
     pk = peaks()
     cfgd = dict(LLAMA3_8B, num_hidden_layers=args.layers)
     cfg = LlamaConfig.from_dict(cfgd)
+    if args.decode_only:
+        args.skip_points = True
     max_b = args.batch if args.skip_points else max(args.batch, 64)
     ctx_len = args.context
     t_load = time.perf_counter()
     eng = random_engine(cfg, 2, EngineParams(dtype="bfloat16", max_tokens=max_b * ctx_len, page_size=64, max_requests=max_b,
-                                             max_request_tokens=ctx_len, max_step_tokens=2048))
+                                             max_request_tokens=ctx_len, max_step_tokens=2048,
+                                             cuda_graphs=not args.no_graphs))
     for kv in eng.kv:                      # keys and values of an imagined earlier context
         kv.normal_(0.0, 1.0)
     torch.cuda.synchronize()
@@ -176,6 +181,11 @@ def main() -> int:
     clocks.start()
     start_len = ctx_len - (W + K) - 1
     main_run = decode_run(args.batch, start_len, K, W)
+    if args.decode_only:
+        clocks.stop()
+        print(json.dumps({"decode_only": True, "batch": args.batch, "context": ctx_len, "ms_per_step": main_run["ms"],
+                          "tok_s": args.batch * 1e3 / main_run["ms"], "launches": main_run["launches"]}))
+        return 0
     e2e_run = decode_run(args.batch, start_len, K, W, e2e=True)
 
     # prefill of 2,048 tokens in one step

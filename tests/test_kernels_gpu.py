@@ -282,3 +282,91 @@ def test_attention_finds_a_far_key(kind):
         got = _run_attention(case, kind, H, K, hd, page, 0, torch.bfloat16)
         err = (got - case["ref"]).abs().max() / case["ref"].abs().max()
         assert float(err) <= 1.2e-2, (key_pos, float(err))
+
+
+def test_fused_finishes_match_the_separate_kernels():
+    """Deferred split-K products finished by the fused kernels give what product + separate kernels give."""
+    from xyntetik_runner_b200 import kernels
+    g = torch.Generator().manual_seed(3)
+    n, d, k = 6, 200, 1024
+    x_in = torch.randn(n, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(d, k, generator=g) / 32).to(torch.bfloat16).to(DEV)
+    bias = torch.randn(d, generator=g).to(DEV)
+    nw = torch.randn(d, generator=g).to(DEV)
+    resid = torch.randn(n, d, generator=g).to(DEV)
+    # separate: product adds into the residual, then RMSNorm
+    a = resid.clone()
+    kernels.gemm_tc(x_in, w, a, bias, kernels.EPI_ADD, force_splits=4)
+    h_a = torch.empty(n, d, dtype=torch.bfloat16, device=DEV)
+    kernels.rmsnorm(a, nw, h_a, 1e-5)
+    # fused
+    b = resid.clone()
+    used = kernels.gemm_tc(x_in, w, b, bias, kernels.EPI_ADD, force_splits=4, defer=True)
+    assert used == 4 and torch.equal(b, resid)                    # nothing written yet
+    h_b = torch.empty(n, d, dtype=torch.bfloat16, device=DEV)
+    kernels.finish_add_rmsnorm(kernels.tc_workspace(torch.device(DEV))[0], used, bias, b, nw, h_b, 1e-5)
+    assert torch.allclose(a, b, rtol=0, atol=1e-5 * float(a.abs().max()))
+    assert float((h_a.float() - h_b.float()).abs().max()) <= 2 ** -7 * float(h_a.float().abs().max())
+    # plain finish
+    c = resid.clone()
+    used = kernels.gemm_tc(x_in, w, c, bias, kernels.EPI_ADD, force_splits=3, defer=True)
+    kernels.finish_plain(kernels.tc_workspace(torch.device(DEV))[0], used, bias, c, True)
+    assert torch.allclose(a, c, rtol=0, atol=1e-5 * float(a.abs().max()))
+
+
+def test_finish_rope_store_matches_rope_store():
+    from xyntetik_runner_b200 import kernels
+    g = torch.Generator().manual_seed(4)
+    H, K, hd, page, n, kdim = 6, 2, 48, 8, 5, 512
+    qkv_dim = (H + 2 * K) * hd
+    x_in = torch.randn(n, kdim, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(qkv_dim, kdim, generator=g) / 20).to(torch.bfloat16).to(DEV)
+    bias = torch.randn(qkv_dim, generator=g).to(DEV)
+    positions = torch.tensor([3, 4, 5, 17, 9], dtype=torch.int32, device=DEV)
+    tok_seg = torch.tensor([0, 0, 0, 1, 2], dtype=torch.int32, device=DEV)
+    bt = torch.tensor([[2, 5, -1], [0, 1, 4], [6, 3, -1]], dtype=torch.int32, device=DEV)
+    inv_freq = torch.rand(hd // 2, generator=g).to(DEV)
+    outs = []
+    for fused in (False, True):
+        cache = torch.zeros(7, 1, 2, K, page, hd, dtype=torch.bfloat16, device=DEV)
+        qkv = torch.zeros(n, qkv_dim, dtype=torch.bfloat16, device=DEV)
+        if fused:
+            used = kernels.gemm_tc(x_in, w, qkv, bias, kernels.EPI_STORE, force_splits=2, defer=True)
+            kernels.finish_rope_store(kernels.tc_workspace(torch.device(DEV))[0], used, bias, qkv, positions, tok_seg, bt, inv_freq,
+                                      cache.data_ptr(), cache.stride(0), cache.stride(2), H, K, hd, hd, 3, page)
+        else:
+            kernels.gemm_tc(x_in, w, qkv, bias, kernels.EPI_STORE, force_splits=1)
+            kernels.rope_store(qkv, positions, tok_seg, bt, inv_freq, cache.data_ptr(), cache.stride(0), cache.stride(2),
+                               H, K, hd, hd, 3, page)
+        outs.append((qkv[:, :H * hd].float().cpu(), cache.float().cpu()))
+    (q0, c0), (q1, c1) = outs
+    assert float(c0.abs().sum()) > 0
+    # the two differ by the order of float32 sums before a bfloat16 rounding: at most one step of bfloat16
+    assert float((q0 - q1).abs().max()) <= 2 ** -7 * float(q0.abs().max())
+    assert float((c0 - c1).abs().max()) <= 2 ** -7 * float(c0.abs().max())
+    assert torch.equal(c0 != 0, c1 != 0)                           # the same cache rows were written
+
+
+@pytest.mark.parametrize("n,n_out,k", [(1, 128, 64), (8, 200, 136), (40, 384, 1024), (300, 130, 264)])
+def test_gemm_tc_packed_layout(n, n_out, k):
+    """The tile-packed weight layout gives bit-identical results to the plain one."""
+    from xyntetik_runner_b200 import kernels
+    g = torch.Generator().manual_seed(n + n_out)
+    x = torch.randn(n, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(n_out, k, generator=g) / math.sqrt(k)).to(torch.bfloat16).to(DEV)
+    packed = kernels.pack_weight(w)
+    for splits in (1, 2):
+        a = torch.empty(n, n_out, dtype=torch.float32, device=DEV)
+        b = torch.empty(n, n_out, dtype=torch.float32, device=DEV)
+        kernels.gemm_tc(x, w, a, None, kernels.EPI_STORE, force_splits=splits)
+        kernels.gemm_tc(x, packed, b, None, kernels.EPI_STORE, force_splits=splits, packed_rows=n_out)
+        assert torch.equal(a, b)
+    # SwiGLU halves
+    F = n_out
+    w2 = (torch.randn(2 * F, k, generator=g) / math.sqrt(k)).to(torch.bfloat16).to(DEV)
+    a = torch.empty(n, F, dtype=torch.bfloat16, device=DEV)
+    b = torch.empty(n, F, dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_tc(x, w2, a, None, kernels.EPI_SWIGLU)
+    kernels.gemm_tc(x, kernels.pack_weight(w2, halves=2), b, None, kernels.EPI_SWIGLU, packed_rows=F)
+    assert torch.equal(a, b)
+    kernels.tc_check_status(torch.device(DEV))

@@ -26,7 +26,9 @@
 
 #define ATT_TILE 64            // keys per tile
 #define ATT_ROWS 64            // packed query rows per CTA in the rows kernel
-#define ATT_SPLIT 512          // keys per CTA in the keys kernel
+#define ATT_SPLIT 512          // keys per CTA in the keys kernel (ATT_SPLIT_SHORT while a request is short)
+#define ATT_SPLIT_SHORT 256
+#define ATT_SHORT_LIMIT 2048   // requests of at most this many keys use the short span
 #define ATT_THREADS 128
 
 struct AttnMmaArgs {
@@ -42,7 +44,12 @@ struct AttnMmaArgs {
     long long q_stride, page_stride, v_offset;
     int H, K, G, max_pages, page_size, window, max_splits;
     float scale;
+    int page_shift;              // log2(page_size) when it is a power of two, else -1
 };
+
+// Span length of a request whose last key is at position hi: a function of the request alone, so that its
+// partition into spans does not depend on what else is in the batch.
+__host__ __device__ __forceinline__ int att_span(int hi) { return hi < ATT_SHORT_LIMIT ? ATT_SPLIT_SHORT : ATT_SPLIT; }
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
@@ -67,30 +74,63 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Gather one tile of keys (or values) [ATT_TILE][HD] into shared memory rows of HD + 8 elements.
+// Gather one tile of keys AND values [ATT_TILE][HD] each into shared memory rows of HD + 8 elements.
 // Rows at positions outside [lo, hi] or on a page the request no longer holds are zero-filled.
+// A thread keeps one 16-byte column and walks rows, so the page of a row is looked up once for K and V.
 template <int HD>
-__device__ __forceinline__ void load_kv_tile(__nv_bfloat16* dst, const __nv_bfloat16* base, const int* bt, int page_size,
-                                             long long page_stride, int kvh, int key0, int lo, int hi) {
+__device__ __forceinline__ void load_kv_tile(__nv_bfloat16* kdst, __nv_bfloat16* vdst, const AttnMmaArgs& a, const int* bt,
+                                             int kvh, int key0, int lo, int hi) {
     constexpr int CH = HD / 8;                       // 16-byte chunks per row
     constexpr int LD = HD + 8;
-    for (int i = threadIdx.x; i < ATT_TILE * CH; i += ATT_THREADS) {
-        int r = i / CH, c = i % CH;
+    constexpr int CT = (CH == 2 || CH == 4 || CH == 8 || CH == 16) ? CH : 1;     // threads across a row
+    constexpr int RPP = ATT_THREADS / CT;            // rows per pass
+    const int c = threadIdx.x % CT, r0 = threadIdx.x / CT;
+    const long long head_off = (long long)kvh * a.page_size * HD;
+#pragma unroll 2
+    for (int r = r0; r < ATT_TILE; r += RPP) {
         int kp = key0 + r;
-        __nv_bfloat16* d = dst + r * LD + c * 8;
-        int page = (kp >= lo && kp <= hi) ? bt[kp / page_size] : -1;
+        int page = -1, off = 0;
+        if (kp >= lo && kp <= hi) {
+            int pi;
+            if (a.page_shift >= 0) { pi = kp >> a.page_shift; off = kp & (a.page_size - 1); }
+            else { pi = kp / a.page_size; off = kp - pi * a.page_size; }
+            page = bt[pi];
+        }
+        __nv_bfloat16* kd = kdst + r * LD;
+        __nv_bfloat16* vd = vdst + r * LD;
         if (page >= 0) {
-            const __nv_bfloat16* src = base + (long long)page * page_stride + ((long long)kvh * page_size + (kp % page_size)) * HD + c * 8;
-            cp_async16(d, src);
+            const __nv_bfloat16* src = a.cache_k + (long long)page * a.page_stride + head_off + (long long)off * HD;
+            if (CT == CH) {
+                cp_async16(kd + c * 8, src + c * 8);
+                cp_async16(vd + c * 8, src + a.v_offset + c * 8);
+            } else {
+#pragma unroll
+                for (int cc = 0; cc < CH; cc++) { cp_async16(kd + cc * 8, src + cc * 8); cp_async16(vd + cc * 8, src + a.v_offset + cc * 8); }
+            }
         } else {
-            *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+            if (CT == CH) {
+                *reinterpret_cast<uint4*>(kd + c * 8) = make_uint4(0, 0, 0, 0);
+                *reinterpret_cast<uint4*>(vd + c * 8) = make_uint4(0, 0, 0, 0);
+            } else {
+#pragma unroll
+                for (int cc = 0; cc < CH; cc++) {
+                    *reinterpret_cast<uint4*>(kd + cc * 8) = make_uint4(0, 0, 0, 0);
+                    *reinterpret_cast<uint4*>(vd + cc * 8) = make_uint4(0, 0, 0, 0);
+                }
+            }
         }
     }
 }
 
 // One tile of the online softmax for a warp's 16 rows against NKT n-tiles (8 keys each) starting at
 // column `col0` of the shared tile:  S = Q K^T, mask, running max/sum, O += P V.
-template <int HD, int NKT>
+// exp() of the softmax: ex2.approx on a pre-scaled argument (relative error ~2^-22, far below the bfloat16
+// rounding of the probabilities that follows)
+__device__ __forceinline__ float att_exp(float x) { return __expf(x); }
+
+// LOWER_ONLY: rows 8..15 of the warp's tile hold no query (a decoded token with at most 8 heads per kv head),
+// so their softmax and rescaling are skipped (the matrix instruction computes them regardless).
+template <int HD, int NKT, bool LOWER_ONLY = false>
 __device__ __forceinline__ void tile_step(const uint32_t (*qf)[4], const __nv_bfloat16* ks, const __nv_bfloat16* vs,
                                           int col0, int key0, int pos_a, int pos_b, int window, float scale,
                                           float* m, float* l, float (*o)[4]) {
@@ -120,30 +160,51 @@ __device__ __forceinline__ void tile_step(const uint32_t (*qf)[4], const __nv_bf
         for (int e = 0; e < 2; e++) {
             int kp = key0 + col0 + j * 8 + t2 + e;
             float va = (kp <= pos_a && kp >= lo_a) ? s[j][e] * scale : -INFINITY;
-            float vb = (kp <= pos_b && kp >= lo_b) ? s[j][2 + e] * scale : -INFINITY;
-            s[j][e] = va; s[j][2 + e] = vb;
-            mx_a = fmaxf(mx_a, va); mx_b = fmaxf(mx_b, vb);
+            s[j][e] = va;
+            mx_a = fmaxf(mx_a, va);
+            if (!LOWER_ONLY) {
+                float vb = (kp <= pos_b && kp >= lo_b) ? s[j][2 + e] * scale : -INFINITY;
+                s[j][2 + e] = vb;
+                mx_b = fmaxf(mx_b, vb);
+            }
         }
     }
     mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1)); mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
-    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1)); mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
-    float mn_a = fmaxf(m[0], mx_a), mn_b = fmaxf(m[1], mx_b);
+    if (!LOWER_ONLY) { mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1)); mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2)); }
+    float mn_a = fmaxf(m[0], mx_a), mn_b = LOWER_ONLY ? -INFINITY : fmaxf(m[1], mx_b);
     // a row that has seen no key yet keeps max = -inf; subtracting 0 instead keeps exp() at exactly 0
     float off_a = mn_a == -INFINITY ? 0.f : mn_a, off_b = mn_b == -INFINITY ? 0.f : mn_b;
-    float ca = expf(m[0] - off_a), cb = expf(m[1] - off_b);      // m = -inf -> 0
-    m[0] = mn_a; m[1] = mn_b;
+    // the running sums and accumulators are rescaled only when some row's maximum moved
+    bool moved = (mn_a != m[0]) || (!LOWER_ONLY && mn_b != m[1]);
+    float ca = 1.f, cb = 1.f;
+    if (__any_sync(0xffffffffu, moved)) {
+        ca = att_exp(m[0] - off_a);                               // m = -inf -> 0
+        if (!LOWER_ONLY) cb = att_exp(m[1] - off_b);
+#pragma unroll
+        for (int d = 0; d < HD / 8; d++) {
+            o[d][0] *= ca; o[d][1] *= ca;
+            if (!LOWER_ONLY) { o[d][2] *= cb; o[d][3] *= cb; }
+        }
+    }
+    m[0] = mn_a; if (!LOWER_ONLY) m[1] = mn_b;
     float sa = 0.f, sb = 0.f;
 #pragma unroll
     for (int j = 0; j < NKT; j++) {
-        s[j][0] = expf(s[j][0] - off_a); s[j][1] = expf(s[j][1] - off_a);
-        s[j][2] = expf(s[j][2] - off_b); s[j][3] = expf(s[j][3] - off_b);
-        sa += s[j][0] + s[j][1]; sb += s[j][2] + s[j][3];
+        s[j][0] = att_exp(s[j][0] - off_a); s[j][1] = att_exp(s[j][1] - off_a);
+        sa += s[j][0] + s[j][1];
+        if (!LOWER_ONLY) {
+            s[j][2] = att_exp(s[j][2] - off_b); s[j][3] = att_exp(s[j][3] - off_b);
+            sb += s[j][2] + s[j][3];
+        } else {
+            s[j][2] = 0.f; s[j][3] = 0.f;
+        }
     }
     sa += __shfl_xor_sync(0xffffffffu, sa, 1); sa += __shfl_xor_sync(0xffffffffu, sa, 2);
-    sb += __shfl_xor_sync(0xffffffffu, sb, 1); sb += __shfl_xor_sync(0xffffffffu, sb, 2);
-    l[0] = l[0] * ca + sa; l[1] = l[1] * cb + sb;
-#pragma unroll
-    for (int d = 0; d < HD / 8; d++) { o[d][0] *= ca; o[d][1] *= ca; o[d][2] *= cb; o[d][3] *= cb; }
+    l[0] = l[0] * ca + sa;
+    if (!LOWER_ONLY) {
+        sb += __shfl_xor_sync(0xffffffffu, sb, 1); sb += __shfl_xor_sync(0xffffffffu, sb, 2);
+        l[1] = l[1] * cb + sb;
+    }
     // O += P V, 16 keys per step
 #pragma unroll
     for (int kk = 0; kk < NKT / 2; kk++) {
@@ -200,8 +261,7 @@ k_attention_rows(AttnMmaArgs a) {
     const int hi = pos0 + last_row / a.G;                                            // last key any row may read
     const int lo = a.window > 0 ? max(0, pos0 + row0 / a.G - a.window + 1) : 0;       // first key any row may read
     const int t_lo = lo / ATT_TILE, t_hi = hi / ATT_TILE;
-    load_kv_tile<HD>(kbuf, a.cache_k, bt, a.page_size, a.page_stride, kvh, t_lo * ATT_TILE, lo, hi);
-    load_kv_tile<HD>(vbuf, a.cache_k + a.v_offset, bt, a.page_size, a.page_stride, kvh, t_lo * ATT_TILE, lo, hi);
+    load_kv_tile<HD>(kbuf, vbuf, a, bt, kvh, t_lo * ATT_TILE, lo, hi);
     cp_async_commit();
     __syncthreads();
     uint32_t qf[HD / 16][4];
@@ -220,8 +280,7 @@ k_attention_rows(AttnMmaArgs a) {
     for (int t = t_lo; t <= t_hi; t++) {
         int cur = (t - t_lo) & 1;
         if (t < t_hi) {
-            load_kv_tile<HD>(kbuf + (cur ^ 1) * ATT_TILE * LD, a.cache_k, bt, a.page_size, a.page_stride, kvh, (t + 1) * ATT_TILE, lo, hi);
-            load_kv_tile<HD>(vbuf + (cur ^ 1) * ATT_TILE * LD, a.cache_k + a.v_offset, bt, a.page_size, a.page_stride, kvh, (t + 1) * ATT_TILE, lo, hi);
+            load_kv_tile<HD>(kbuf + (cur ^ 1) * ATT_TILE * LD, vbuf + (cur ^ 1) * ATT_TILE * LD, a, bt, kvh, (t + 1) * ATT_TILE, lo, hi);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
@@ -250,32 +309,39 @@ k_attention_rows(AttnMmaArgs a) {
 // ---------------------------------------------------------------------------------------------
 // keys kernel: grid (spans, K, segments); portions of at most 16 packed rows
 // ---------------------------------------------------------------------------------------------
-template <int HD>
+// ATT_KSTAGES: shared-memory stages.  Two let three CTAs share an SM (best when the grid fills the machine
+// several times over); four keep one CTA's copies far enough ahead when it has the SM to itself.
+template <int HD, int ATT_KSTAGES>
 __global__ void __launch_bounds__(ATT_THREADS)
 k_attention_keys(AttnMmaArgs a) {
     constexpr int LD = HD + 8;
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __nv_bfloat16* qs = (__nv_bfloat16*)smem_raw;                 // [16][LD]
-    __nv_bfloat16* kbuf = qs + 16 * LD;
-    __nv_bfloat16* vbuf = kbuf + 2 * ATT_TILE * LD;
+    __nv_bfloat16* kbuf = qs + 16 * LD;                            // [ATT_KSTAGES][64][LD]
+    __nv_bfloat16* vbuf = kbuf + ATT_KSTAGES * ATT_TILE * LD;      // [ATT_KSTAGES][64][LD]
     const int seg = blockIdx.z, kvh = blockIdx.y, span = blockIdx.x;
     const int L = a.seg_len[seg], rows_total = L * a.G;
     if (rows_total > 16) return;
     const int pos0 = a.seg_pos0[seg], tok_base = a.seg_start[seg];
     const int hi_all = pos0 + L - 1;
     const int lo_all = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
-    const int first_span = lo_all / ATT_SPLIT;
-    const int k_begin = (first_span + span) * ATT_SPLIT;           // spans are fixed ranges of absolute positions
+    const int SPAN = att_span(hi_all);
+    const int first_span = lo_all / SPAN;
+    const int k_begin = (first_span + span) * SPAN;                // spans are fixed ranges of absolute positions
     if (k_begin > hi_all) return;
-    const int lo = max(lo_all, k_begin), hi = min(hi_all, k_begin + ATT_SPLIT - 1);
+    const int lo = max(lo_all, k_begin), hi = min(hi_all, k_begin + SPAN - 1);
     const int* bt = a.block_tables + (size_t)seg * a.max_pages;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     load_q<HD>(qs, a, tok_base, kvh, 0, 16, rows_total);
     const int t_lo = lo / ATT_TILE, t_hi = hi / ATT_TILE;
-    load_kv_tile<HD>(kbuf, a.cache_k, bt, a.page_size, a.page_stride, kvh, t_lo * ATT_TILE, lo, hi);
-    load_kv_tile<HD>(vbuf, a.cache_k + a.v_offset, bt, a.page_size, a.page_stride, kvh, t_lo * ATT_TILE, lo, hi);
-    cp_async_commit();
+    // ring of ATT_KSTAGES tiles: tiles t+1 .. t+ATT_KSTAGES-1 are in flight while tile t is used
+#pragma unroll
+    for (int i = 0; i < ATT_KSTAGES - 1; i++) {
+        if (t_lo + i <= t_hi)
+            load_kv_tile<HD>(kbuf + i * ATT_TILE * LD, vbuf + i * ATT_TILE * LD, a, bt, kvh, (t_lo + i) * ATT_TILE, lo, hi);
+        cp_async_commit();
+    }
     __syncthreads();
     uint32_t qf[HD / 16][4];
 #pragma unroll
@@ -289,24 +355,27 @@ k_attention_keys(AttnMmaArgs a) {
     for (int d = 0; d < HD / 8; d++) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
 
     for (int t = t_lo; t <= t_hi; t++) {
-        int cur = (t - t_lo) & 1;
-        if (t < t_hi) {
-            load_kv_tile<HD>(kbuf + (cur ^ 1) * ATT_TILE * LD, a.cache_k, bt, a.page_size, a.page_stride, kvh, (t + 1) * ATT_TILE, lo, hi);
-            load_kv_tile<HD>(vbuf + (cur ^ 1) * ATT_TILE * LD, a.cache_k + a.v_offset, bt, a.page_size, a.page_stride, kvh, (t + 1) * ATT_TILE, lo, hi);
-            cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
+        int cur = (t - t_lo) % ATT_KSTAGES;
+        int nxt = (t - t_lo + ATT_KSTAGES - 1) % ATT_KSTAGES;
+        if (t + ATT_KSTAGES - 1 <= t_hi)
+            load_kv_tile<HD>(kbuf + nxt * ATT_TILE * LD, vbuf + nxt * ATT_TILE * LD, a, bt, kvh, (t + ATT_KSTAGES - 1) * ATT_TILE, lo, hi);
+        cp_async_commit();
+        cp_async_wait<ATT_KSTAGES - 1>();
         __syncthreads();
         // warp w takes keys [16w, 16w + 16) of the tile; every key of these tiles lies inside the span, and
         // keys outside [lo, hi] are outside every row's own range, so the per-row mask is all that is needed
         int c0 = warp * 16, kfirst = t * ATT_TILE + c0;
-        if (kfirst <= hi && kfirst + 15 >= lo)
-            tile_step<HD, 2>(qf, kbuf + cur * ATT_TILE * LD, vbuf + cur * ATT_TILE * LD, c0, t * ATT_TILE, pos_a, pos_b,
-                             a.window, a.scale, m, l, o);
+        if (kfirst <= hi && kfirst + 15 >= lo) {
+            if (rows_total <= 8)
+                tile_step<HD, 2, true>(qf, kbuf + cur * ATT_TILE * LD, vbuf + cur * ATT_TILE * LD, c0, t * ATT_TILE, pos_a, pos_b,
+                                       a.window, a.scale, m, l, o);
+            else
+                tile_step<HD, 2, false>(qf, kbuf + cur * ATT_TILE * LD, vbuf + cur * ATT_TILE * LD, c0, t * ATT_TILE, pos_a, pos_b,
+                                        a.window, a.scale, m, l, o);
+        }
         __syncthreads();
     }
+    cp_async_wait<0>();
     // combine the four warps: shared [4][16][HD] accumulators and [4][16][2] (max, sum); the key tiles are done with
     float* acc_s = reinterpret_cast<float*>(kbuf);
     float* ml_s = acc_s + 4 * 16 * HD;
@@ -343,31 +412,61 @@ k_attention_keys(AttnMmaArgs a) {
 }
 
 // Combine the spans of one (request, kv head) in ascending order and write the output rows.
-// grid (K, segments), one warp per packed row.
+// grid (K, segments).  Each row's span weights exp(m_s - M) / L are computed once into shared memory.
 template <int HD>
-__global__ void k_attention_merge(AttnMmaArgs a) {
+__global__ void __launch_bounds__(128)
+k_attention_merge(AttnMmaArgs a) {
+    __shared__ float wgt[16][33];                  // [row][span], up to 32 spans at a time
     const int seg = blockIdx.y, kvh = blockIdx.x;
     const int L = a.seg_len[seg], rows_total = L * a.G;
     if (rows_total > 16) return;
     const int pos0 = a.seg_pos0[seg], tok_base = a.seg_start[seg];
     const int hi_all = pos0 + L - 1;
     const int lo_all = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
-    const int n_spans = hi_all / ATT_SPLIT - lo_all / ATT_SPLIT + 1;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int r = warp; r < rows_total; r += blockDim.x >> 5) {
-        size_t item0 = ((size_t)seg * a.K + kvh) * a.max_splits;
+    const int SPAN = att_span(hi_all);
+    const int n_spans = hi_all / SPAN - lo_all / SPAN + 1;
+    const size_t item0 = ((size_t)seg * a.K + kvh) * a.max_splits;
+    const float* ml = a.part_ml + item0 * 32;
+    const float* pa = a.part_acc + item0 * 16 * HD;
+    __shared__ float row_max[16], row_inv[16];
+    if (threadIdx.x < rows_total) {
+        int r = threadIdx.x;
         float mm = -INFINITY;
-        for (int s = 0; s < n_spans; s++) mm = fmaxf(mm, a.part_ml[((item0 + s) * 16 + r) * 2]);
+        for (int s = 0; s < n_spans; s++) mm = fmaxf(mm, ml[(s * 16 + r) * 2]);
         float off = mm == -INFINITY ? 0.f : mm;
         float ll = 0.f;
-        for (int s = 0; s < n_spans; s++) ll += a.part_ml[((item0 + s) * 16 + r) * 2 + 1] * expf(a.part_ml[((item0 + s) * 16 + r) * 2] - off);
-        float inv = 1.0f / ll;
-        __nv_bfloat16* dst = a.out + ((long long)(tok_base + r / a.G) * a.H + (kvh * a.G + r % a.G)) * HD;
-        for (int d = lane; d < HD; d += 32) {
-            float acc = 0.f;
-            for (int s = 0; s < n_spans; s++)
-                acc += a.part_acc[((item0 + s) * 16 + r) * HD + d] * expf(a.part_ml[((item0 + s) * 16 + r) * 2] - off);
-            dst[d] = __float2bfloat16_rn(acc * inv);
+        for (int s = 0; s < n_spans; s++) ll += ml[(s * 16 + r) * 2 + 1] * expf(ml[(s * 16 + r) * 2] - off);
+        row_max[r] = off; row_inv[r] = 1.0f / ll;
+    }
+    __syncthreads();
+    float acc[(16 * HD + 127) / 128];
+#pragma unroll
+    for (int k = 0; k < (16 * HD + 127) / 128; k++) acc[k] = 0.f;
+    for (int s0 = 0; s0 < n_spans; s0 += 32) {
+        int ns = min(32, n_spans - s0);
+        for (int i = threadIdx.x; i < rows_total * ns; i += 128) {
+            int r = i / ns, s = i % ns;
+            wgt[r][s] = expf(ml[((s0 + s) * 16 + r) * 2] - row_max[r]);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < (16 * HD + 127) / 128; k++) {
+            int i = threadIdx.x + k * 128;
+            if (i < rows_total * HD) {
+                int r = i / HD, d = i % HD;
+                float v = acc[k];
+                for (int s = 0; s < ns; s++) v += pa[((size_t)(s0 + s) * 16 + r) * HD + d] * wgt[r][s];
+                acc[k] = v;
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int k = 0; k < (16 * HD + 127) / 128; k++) {
+        int i = threadIdx.x + k * 128;
+        if (i < rows_total * HD) {
+            int r = i / HD, d = i % HD;
+            a.out[((long long)(tok_base + r / a.G) * a.H + (kvh * a.G + r % a.G)) * HD + d] = __float2bfloat16_rn(acc[k] * row_inv[r]);
         }
     }
 }
@@ -378,13 +477,15 @@ static int launch_attention(const AttnMmaArgs& a, int n_seg, int max_seg_len, in
                             cudaStream_t stream) {
     constexpr int LD = HD + 8;
     constexpr int SMEM_ROWS = (ATT_ROWS + 4 * ATT_TILE) * LD * 2;
-    constexpr int KEYS_TILES = (16 + 4 * ATT_TILE) * LD * 2;
     constexpr int KEYS_MERGE = 16 * LD * 2 + (4 * 16 * HD + 4 * 16 * 2) * 4;
-    constexpr int SMEM_KEYS = KEYS_TILES > KEYS_MERGE ? KEYS_TILES : KEYS_MERGE;
+    constexpr int KEYS_TILES2 = (16 + 2 * 2 * ATT_TILE) * LD * 2, KEYS_TILES4 = (16 + 2 * 4 * ATT_TILE) * LD * 2;
+    constexpr int SMEM_KEYS2 = KEYS_TILES2 > KEYS_MERGE ? KEYS_TILES2 : KEYS_MERGE;
+    constexpr int SMEM_KEYS4 = KEYS_TILES4 > KEYS_MERGE ? KEYS_TILES4 : KEYS_MERGE;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(k_attention_rows<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_ROWS) != cudaSuccess ||
-            cudaFuncSetAttribute(k_attention_keys<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_KEYS) != cudaSuccess)
+            cudaFuncSetAttribute(k_attention_keys<HD, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_KEYS2) != cudaSuccess ||
+            cudaFuncSetAttribute(k_attention_keys<HD, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_KEYS4) != cudaSuccess)
             return XR_ERR_LAUNCH;
         configured = true;
     }
@@ -397,7 +498,11 @@ static int launch_attention(const AttnMmaArgs& a, int n_seg, int max_seg_len, in
     }
     if (any_short) {
         if (n_seg > 65535 || a.K > 65535) return XR_ERR_ARG;
-        k_attention_keys<HD><<<dim3(a.max_splits, a.K, n_seg), ATT_THREADS, SMEM_KEYS, stream>>>(a);
+        // few CTAs (small batch): deeper stages; many: more CTAs per SM.  The arithmetic is the same.
+        if ((long long)a.max_splits * a.K * n_seg <= 2 * 148)
+            k_attention_keys<HD, 4><<<dim3(a.max_splits, a.K, n_seg), ATT_THREADS, SMEM_KEYS4, stream>>>(a);
+        else
+            k_attention_keys<HD, 2><<<dim3(a.max_splits, a.K, n_seg), ATT_THREADS, SMEM_KEYS2, stream>>>(a);
         int rc = xr_launch_status();
         if (rc != XR_OK) return rc;
         k_attention_merge<HD><<<dim3(a.K, n_seg), 128, 0, stream>>>(a);
@@ -409,7 +514,9 @@ static int launch_attention(const AttnMmaArgs& a, int n_seg, int max_seg_len, in
 // Spans the keys kernel needs for a longest key range of `max_kv_len` (window > 0: at most that many keys).
 XR_EXPORT int xr_attention_mma_splits(int max_kv_len, int window) {
     int range = window > 0 && window + 16 < max_kv_len ? window + 16 : max_kv_len;
-    return (range + ATT_SPLIT - 1) / ATT_SPLIT + (window > 0 ? 1 : 0);
+    int by_short = ((range < ATT_SHORT_LIMIT ? range : ATT_SHORT_LIMIT) + ATT_SPLIT_SHORT - 1) / ATT_SPLIT_SHORT;
+    int by_long = max_kv_len > ATT_SHORT_LIMIT ? (range + ATT_SPLIT - 1) / ATT_SPLIT : 0;
+    return (by_short > by_long ? by_short : by_long) + (window > 0 ? 1 : 0);
 }
 
 // part_acc: float32 [n_seg * K * splits * 16 * hd], part_ml: float32 [n_seg * K * splits * 32]
@@ -425,7 +532,8 @@ XR_EXPORT int xr_attention_mma(const void* q, void* out, const void* cache_k, co
     if (H / K > 16 && any_short) return XR_ERR_ARG;     // more heads per group than one instruction tile holds
     AttnMmaArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)cache_k, seg_start, seg_len, seg_pos0,
                   block_tables, part_acc, part_ml, q_stride, page_stride, v_offset, H, K, H / K, max_pages, page_size, window,
-                  splits, scale};
+                  splits, scale, -1};
+    if ((page_size & (page_size - 1)) == 0) { int sh = 0; while ((1 << sh) < page_size) sh++; a.page_shift = sh; }
     switch (hd) {
         case 16: return launch_attention<16>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, stream);
         case 32: return launch_attention<32>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, stream);

@@ -1,0 +1,142 @@
+// Kernels that finish a split-K product and do the next memory-bound op in the same pass, so that a decode
+// step does not pay a launch and a round trip through memory for each:
+//   * sum of partials (+ bias) -> added into the float32 residual stream -> RMSNorm of the new row
+//     (the reference runs `k_add` src/kernels.cu:2903 and `k_rmsnorm` :32 as two kernels after its matvec);
+//   * sum of partials (+ bias) of the fused QKV product -> rotation of Q and K -> Q to the activation
+//     buffer, K and V into their pages (`k_rope`, `k_store_kv`, src/kernels.cu:1918, 2008).
+// Partials are [splits][n][width] float32 and are summed in split order, so the result is deterministic.
+#include "common.cuh"
+
+template <typename TO>
+__global__ void k_finish_add_rmsnorm(const float* __restrict__ partial, int splits, int n, const float* __restrict__ bias,
+                                     float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out, int d, float eps) {
+    __shared__ float scratch[33];
+    extern __shared__ float row[];             // the new residual row, kept for the second pass
+    int t = blockIdx.x;
+    float* xr = x + (size_t)t * d;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float v = 0.f;
+        for (int s = 0; s < splits; s++) v += partial[((size_t)s * n + t) * d + i];
+        if (bias) v += bias[i];
+        v = xr[i] + v;
+        xr[i] = v;
+        row[i] = v;
+        ss += v * v;
+    }
+    ss = xr_block_sum(ss, scratch);
+    float scale = 1.0f / sqrtf(ss / (float)d + eps);
+    TO* o = out + (size_t)t * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = xr_from_f32<TO>(row[i] * scale * w[i]);
+}
+
+XR_EXPORT int xr_finish_add_rmsnorm(const float* partial, int splits, const float* bias, float* x, const float* w, void* out,
+                                    int out_dtype, int n, int d, float eps, cudaStream_t stream) {
+    if (n < 1 || d < 1 || splits < 1 || (size_t)d * 4 > 200 * 1024) return XR_ERR_ARG;
+    int threads = d >= 2048 ? 512 : 256;
+    size_t smem = (size_t)d * 4;
+    if (out_dtype == XR_F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k_finish_add_rmsnorm<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        k_finish_add_rmsnorm<float><<<n, threads, smem, stream>>>(partial, splits, n, bias, x, w, (float*)out, d, eps);
+    } else if (out_dtype == XR_BF16) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k_finish_add_rmsnorm<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        k_finish_add_rmsnorm<__nv_bfloat16><<<n, threads, smem, stream>>>(partial, splits, n, bias, x, w, (__nv_bfloat16*)out, d, eps);
+    } else {
+        return XR_ERR_ARG;
+    }
+    return xr_launch_status();
+}
+
+// Plain finish for callers that need the sum itself: out (+)= sum of partials (+ bias).
+template <typename TO, bool ACCUM>
+__global__ void k_finish_plain(const float* __restrict__ partial, int splits, int n, int width, const float* __restrict__ bias,
+                               TO* __restrict__ out, long long ldo) {
+    size_t total = (size_t)n * width;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        size_t t = i / width, r = i % width;
+        float v = 0.f;
+        for (int s = 0; s < splits; s++) v += partial[((size_t)s * n + t) * width + r];
+        if (bias) v += bias[r];
+        size_t o = t * ldo + r;
+        if (ACCUM) out[o] = xr_from_f32<TO>(xr_to_f32<TO>(out[o]) + v);
+        else out[o] = xr_from_f32<TO>(v);
+    }
+}
+
+XR_EXPORT int xr_finish_plain(const float* partial, int splits, const float* bias, void* out, int out_dtype, int accumulate,
+                              int n, int width, long long ldo, cudaStream_t stream) {
+    if (n < 1 || width < 1 || splits < 1 || ldo < width) return XR_ERR_ARG;
+    size_t total = (size_t)n * width;
+    int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+    if (accumulate) {
+        if (out_dtype != XR_F32) return XR_ERR_ARG;
+        k_finish_plain<float, true><<<blocks, 256, 0, stream>>>(partial, splits, n, width, bias, (float*)out, ldo);
+    } else if (out_dtype == XR_F32) {
+        k_finish_plain<float, false><<<blocks, 256, 0, stream>>>(partial, splits, n, width, bias, (float*)out, ldo);
+    } else if (out_dtype == XR_BF16) {
+        k_finish_plain<__nv_bfloat16, false><<<blocks, 256, 0, stream>>>(partial, splits, n, width, bias, (__nv_bfloat16*)out, ldo);
+    } else {
+        return XR_ERR_ARG;
+    }
+    return xr_launch_status();
+}
+
+// QKV finish + rotation + page store.  One block per (token, head); head < H: query, < H + K: key, else value.
+struct FinishRopeArgs {
+    const float* partial; int splits; const float* bias;
+    __nv_bfloat16* qkv;              // Q heads are written here (row stride (H + 2K) * hd); K and V too when cache_k is null
+    const int* positions; const int* tok_seg; const int* block_tables; const float* inv_freq;
+    __nv_bfloat16* cache_k; long long page_stride, v_offset;
+    int n, H, K, hd, rotary_dim, max_pages, page_size;
+};
+
+__global__ void k_finish_rope_store(FinishRopeArgs a) {
+    int t = blockIdx.x, head = blockIdx.y;
+    int qkv_dim = (a.H + 2 * a.K) * a.hd;
+    int col0 = head * a.hd;
+    int pos = a.positions[t];
+    int half = a.rotary_dim >> 1;
+    bool is_q = head < a.H, is_k = !is_q && head < a.H + a.K;
+    __nv_bfloat16* dst = a.qkv + (size_t)t * qkv_dim + col0;
+    if (!is_q && a.cache_k != nullptr) {
+        int kvh = is_k ? head - a.H : head - a.H - a.K;
+        int page = a.block_tables[(size_t)a.tok_seg[t] * a.max_pages + pos / a.page_size];
+        dst = a.cache_k + (size_t)page * a.page_stride + (is_k ? 0 : a.v_offset) + ((size_t)kvh * a.page_size + (pos % a.page_size)) * a.hd;
+    }
+    for (int j = threadIdx.x; j < a.hd; j += blockDim.x) {
+        bool rot_lo = (is_q || is_k) && j < half;
+        bool rot_hi = (is_q || is_k) && j >= half && j < 2 * half;
+        if (rot_hi) continue;                                 // written by the thread that owns j - half
+        float v0 = 0.f, v1 = 0.f;
+        for (int s = 0; s < a.splits; s++) {
+            const float* p = a.partial + ((size_t)s * a.n + t) * qkv_dim + col0;
+            v0 += p[j];
+            if (rot_lo) v1 += p[j + half];
+        }
+        if (a.bias) { v0 += a.bias[col0 + j]; if (rot_lo) v1 += a.bias[col0 + j + half]; }
+        if (rot_lo) {
+            // the product's output is rounded to the activation dtype before the rotation, as on the unfused path
+            v0 = __bfloat162float(__float2bfloat16_rn(v0)); v1 = __bfloat162float(__float2bfloat16_rn(v1));
+            float ang = (float)pos * a.inv_freq[j];
+            float c = cosf(ang), s = sinf(ang);
+            dst[j] = __float2bfloat16_rn(v0 * c - v1 * s);
+            dst[j + half] = __float2bfloat16_rn(v0 * s + v1 * c);
+        } else {
+            dst[j] = __float2bfloat16_rn(v0);
+        }
+    }
+}
+
+XR_EXPORT int xr_finish_rope_store(const float* partial, int splits, const float* bias, void* qkv, const int* positions,
+                                   const int* tok_seg, const int* block_tables, const float* inv_freq, void* cache_k,
+                                   long long page_stride, long long v_offset, int n, int H, int K, int hd, int rotary_dim,
+                                   int max_pages, int page_size, cudaStream_t stream) {
+    if (n < 1 || H < 1 || K < 1 || hd < 1 || rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1) || page_size < 1 ||
+        splits < 1 || H + 2 * K > 65535)
+        return XR_ERR_ARG;
+    FinishRopeArgs a{partial, splits, bias, (__nv_bfloat16*)qkv, positions, tok_seg, block_tables, inv_freq,
+                     (__nv_bfloat16*)cache_k, page_stride, v_offset, n, H, K, hd, rotary_dim, max_pages, page_size};
+    int threads = hd >= 128 ? 128 : (hd >= 64 ? 64 : 32);
+    k_finish_rope_store<<<dim3(n, H + 2 * K), threads, 0, stream>>>(a);
+    return xr_launch_status();
+}

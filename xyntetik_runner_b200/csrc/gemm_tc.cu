@@ -119,17 +119,19 @@ struct TcParams {
     int* status;                // device word: non-zero when a wait gave up
     long long ldo;              // row stride of out in elements
     int n, n_out, K;            // tokens, output features (per half in SwiGLU mode), reduction length
-    int kblocks_per_split;      // K blocks (of 64) each z-slice of the grid handles
+    int splits;                 // z-slices of the grid; slice z handles K blocks [z*total/splits, (z+1)*total/splits)
     int epilogue, out_dtype;
-    int up_row_offset;          // SwiGLU: rows of the up projection start here in W
+    int up_row_offset;          // SwiGLU: rows of the up projection start here in W (packed: in units of rows too)
+    int packed;                 // W is stored tile by tile: [row tile][K block][128][64], see xr_gemm_tc
+    int w_kblocks;              // packed: K blocks per row tile in the packed array
 };
 
 // ---------------------------------------------------------------------------------------------
 // The kernel.  grid = (token tiles, row tiles, K splits): the CTAs that share a tile of W are neighbours in
 // launch order, so W comes from HBM once and from L2 for the others.
 // ---------------------------------------------------------------------------------------------
-template <int BN, int STAGES, bool DUAL>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+template <int BN, int STAGES, bool DUAL, int MINB>
+__global__ void __launch_bounds__(TC_THREADS, MINB)
 k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     constexpr int W_BYTES = TC_BM * TC_BK * 2;
@@ -148,9 +150,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row0 = blockIdx.y * TC_BM, tok0 = blockIdx.x * BN;
     const int total_kb = (p.K + TC_BK - 1) / TC_BK;
-    const int kb0 = blockIdx.z * p.kblocks_per_split;
-    const int kb1 = min(total_kb, kb0 + p.kblocks_per_split);
-    const int nkb = kb1 - kb0;                     // >= 1 by construction of the grid
+    const int kb0 = (int)(((long long)blockIdx.z * total_kb) / p.splits);
+    const int kb1 = (int)(((long long)(blockIdx.z + 1) * total_kb) / p.splits);
+    const int nkb = kb1 - kb0;                     // >= 1: splits <= total_kb
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -177,8 +179,15 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                 uint8_t* st = smem + s * STAGE_BYTES;
                 mbar_expect_tx(&full[s], STAGE_BYTES);
                 int kx = (kb0 + i) * TC_BK;
-                tma_load_2d(st, &map_w, kx, row0, &full[s]);
-                if (DUAL) tma_load_2d(st + W_BYTES, &map_w, kx, p.up_row_offset + row0, &full[s]);
+                if (p.packed) {
+                    // tile (row tile, K block) is 128 consecutive rows of 64 elements: one contiguous 16 KB read
+                    int y = (blockIdx.y * p.w_kblocks + kb0 + i) * TC_BM;
+                    tma_load_2d(st, &map_w, 0, y, &full[s]);
+                    if (DUAL) tma_load_2d(st + W_BYTES, &map_w, 0, y + (p.up_row_offset / TC_BM) * p.w_kblocks * TC_BM, &full[s]);
+                } else {
+                    tma_load_2d(st, &map_w, kx, row0, &full[s]);
+                    if (DUAL) tma_load_2d(st + W_BYTES, &map_w, kx, p.up_row_offset + row0, &full[s]);
+                }
                 tma_load_2d(st + W_BYTES * (DUAL ? 2 : 1), &map_x, kx, tok0, &full[s]);
                 issued = i + 1;
             }
@@ -229,6 +238,17 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                 tc_ld16(taddr + c0, g);
                 if (DUAL) tc_ld16(taddr + BN + c0, u);
                 if (!row_ok) continue;
+                if (p.epilogue == TC_EPI_ADD) {
+                    // read-modify-write of the float32 residual: all loads first, so that they overlap
+                    float* dst = (float*)p.out + (size_t)(tok0 + c0) * p.ldo + r;
+                    float old[16];
+#pragma unroll
+                    for (int c = 0; c < 16; c++) old[c] = (tok0 + c0 + c < p.n) ? dst[(size_t)c * p.ldo] : 0.f;
+#pragma unroll
+                    for (int c = 0; c < 16; c++)
+                        if (tok0 + c0 + c < p.n) dst[(size_t)c * p.ldo] = old[c] + (g[c] + b);
+                    continue;
+                }
 #pragma unroll
                 for (int c = 0; c < 16; c++) {
                     int t = tok0 + c0 + c;
@@ -243,9 +263,6 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                         float h = gv < -80.0f ? 0.0f : (gv / (1.0f + expf(-gv))) * u[c];
                         if (p.out_dtype == XR_BF16) ((__nv_bfloat16*)p.out)[(size_t)t * p.ldo + r] = __float2bfloat16_rn(h);
                         else ((float*)p.out)[(size_t)t * p.ldo + r] = h;
-                    } else if (p.epilogue == TC_EPI_ADD) {
-                        float* dst = (float*)p.out + (size_t)t * p.ldo + r;
-                        *dst = *dst + (g[c] + b);
                     } else {
                         float v = g[c] + b;
                         if (p.out_dtype == XR_BF16) ((__nv_bfloat16*)p.out)[(size_t)t * p.ldo + r] = __float2bfloat16_rn(v);
@@ -326,28 +343,41 @@ static bool make_map(CUtensorMap* m, const void* base, long long rows, long long
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN, int STAGES, bool DUAL>
+template <int BN, int STAGES, bool DUAL, int MINB>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, dim3 grid, cudaStream_t stream) {
     constexpr int STAGE_BYTES = TC_BM * TC_BK * 2 * (DUAL ? 2 : 1) + BN * TC_BK * 2;
     constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + (2 * STAGES + 1) * 8 + 16;
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(k_gemm_tc<BN, STAGES, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+        if (cudaFuncSetAttribute(k_gemm_tc<BN, STAGES, DUAL, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
             return XR_ERR_LAUNCH;
         configured = true;
     }
-    k_gemm_tc<BN, STAGES, DUAL><<<grid, TC_THREADS, SMEM, stream>>>(mw, mx, p);
+    k_gemm_tc<BN, STAGES, DUAL, MINB><<<grid, TC_THREADS, SMEM, stream>>>(mw, mx, p);
     return xr_launch_status();
 }
 
-// Number of K splits that fills the machine when there are few output tiles.
-static int choose_splits(int tiles, int total_kb, int sms) {
-    if (tiles >= sms) return 1;
-    int s = (2 * sms + tiles - 1) / tiles;            // aim at about two CTAs per SM
-    int max_by_k = total_kb / 4;                       // at least four K blocks per split
-    if (s > max_by_k) s = max_by_k;
-    if (s > 16) s = 16;
-    return s < 1 ? 1 : s;
+// CTAs of one product that fit the machine at once: two per SM for the small token tiles (their shared
+// memory is sized for that), one otherwise.
+static int resident_ctas(int bn, bool dual, int sms) { return (bn <= 32 || (bn == 64 && !dual)) ? 2 * sms : sms; }
+
+// Number of K splits when there are few output tiles.  A product runs in waves of `slots` CTAs; the split is
+// chosen so that the last wave is as full as possible (a 224-tile product split 5 ways fills 3.78 waves of
+// 296, split 4 ways it would leave a fourth wave almost empty), keeping at least four K blocks per split.
+static int choose_splits(int tiles, int tok_tiles, int total_kb, int slots) {
+    if (tok_tiles > 1 || tiles >= 4 * slots) return 1;       // only products with one tile of tokens are split
+    int max_s = total_kb / 4;
+    if (max_s > 16) max_s = 16;
+    if (max_s < 1) max_s = 1;
+    int best = 1;
+    double best_eff = 0.0;
+    for (int s = 1; s <= max_s; s++) {
+        long long ctas = (long long)tiles * s;
+        long long waves = (ctas + slots - 1) / slots;
+        double eff = (double)ctas / (double)(waves * slots);
+        if (eff > best_eff + 0.02) { best_eff = eff; best = s; }      // prefer fewer splits unless clearly better
+    }
+    return best;
 }
 
 // X: [n, K] bfloat16 (row stride ldx), W: [n_out (x2 when swiglu), K] bfloat16 dense.
@@ -360,7 +390,8 @@ XR_EXPORT long long xr_gemm_tc_scratch_floats(int n, int n_out, int swiglu) {
 
 XR_EXPORT int xr_gemm_tc(const void* X, const void* W, const float* bias, void* out, int out_dtype, int epilogue,
                          int n, int n_out, int K, long long ldx, long long ldo, float* scratch,
-                         long long scratch_floats, int* status, int force_splits, cudaStream_t stream) {
+                         long long scratch_floats, int* status, int force_splits, int defer_finish, int* splits_used,
+                         int w_packed, cudaStream_t stream) {
     if (n < 1 || n_out < 1 || K < 8 || (K % 8) != 0 || (ldx % 8) != 0 || ldx < K || ldo < n_out) return XR_ERR_ARG;
     if (((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return XR_ERR_ARG;
     if (epilogue != TC_EPI_STORE && epilogue != TC_EPI_ADD && epilogue != TC_EPI_SWIGLU) return XR_ERR_ARG;
@@ -369,37 +400,44 @@ XR_EXPORT int xr_gemm_tc(const void* X, const void* W, const float* bias, void* 
     const bool dual = epilogue == TC_EPI_SWIGLU;
     int bn = n <= 16 ? 16 : (n <= 32 ? 32 : (n <= 64 ? 64 : (n <= 128 ? 128 : 256)));
     CUtensorMap mw, mx;
-    if (!make_map(&mw, W, dual ? 2LL * n_out : n_out, K, K, TC_BM)) return -3;
+    // Packed W: [row tiles (gate tiles then up tiles for SwiGLU)][K blocks][128][64], rows and K padded with
+    // zeros to whole tiles; n_out must then be the logical row count and, for SwiGLU, the up half starts at
+    // the next multiple of 128 rows.
+    const int w_kblocks = (K + TC_BK - 1) / TC_BK;
+    const int rows_padded = (n_out + TC_BM - 1) / TC_BM * TC_BM;
+    if (w_packed) {
+        if (!make_map(&mw, W, (long long)(dual ? 2 : 1) * rows_padded * w_kblocks, TC_BK, TC_BK, TC_BM)) return -3;
+    } else if (!make_map(&mw, W, dual ? 2LL * n_out : n_out, K, K, TC_BM)) return -3;
     if (!make_map(&mx, X, n, K, ldx, bn)) return -3;
     int row_tiles = (n_out + TC_BM - 1) / TC_BM, tok_tiles = (n + bn - 1) / bn;
     int total_kb = (K + TC_BK - 1) / TC_BK;
-    int splits = force_splits > 0 ? force_splits : choose_splits(row_tiles * tok_tiles, total_kb, 148);
+    int splits = force_splits > 0 ? force_splits : choose_splits(row_tiles * tok_tiles, tok_tiles, total_kb, resident_ctas(bn, dual, 148));
     if (splits > total_kb) splits = total_kb;
-    int per = (total_kb + splits - 1) / splits;
-    splits = (total_kb + per - 1) / per;                 // no empty split
-    if (splits > 1 && (scratch == nullptr || scratch_floats < (long long)splits * n * n_out * (dual ? 2 : 1))) splits = 1, per = total_kb;
+    if (splits > 1 && (scratch == nullptr || scratch_floats < (long long)splits * n * n_out * (dual ? 2 : 1))) splits = 1;
     if (row_tiles > 65535 || splits > 65535) return XR_ERR_ARG;
-    TcParams p{out, bias, scratch, status, ldo, n, n_out, K, per, splits > 1 ? TC_EPI_PARTIAL : epilogue, out_dtype, n_out};
+    if (splits_used) *splits_used = splits;
+    TcParams p{out, bias, scratch, status, ldo, n, n_out, K, splits, splits > 1 ? TC_EPI_PARTIAL : epilogue, out_dtype,
+               w_packed ? rows_padded : n_out, w_packed, w_kblocks};
     dim3 grid(tok_tiles, row_tiles, splits);
     int rc;
     if (!dual) {
         switch (bn) {
-            case 16: rc = launch_tc<16, 6, false>(mw, mx, p, grid, stream); break;
-            case 32: rc = launch_tc<32, 6, false>(mw, mx, p, grid, stream); break;
-            case 64: rc = launch_tc<64, 6, false>(mw, mx, p, grid, stream); break;
-            case 128: rc = launch_tc<128, 5, false>(mw, mx, p, grid, stream); break;
-            default: rc = launch_tc<256, 4, false>(mw, mx, p, grid, stream); break;
+            case 16: rc = launch_tc<16, 6, false, 2>(mw, mx, p, grid, stream); break;
+            case 32: rc = launch_tc<32, 5, false, 2>(mw, mx, p, grid, stream); break;
+            case 64: rc = launch_tc<64, 4, false, 2>(mw, mx, p, grid, stream); break;
+            case 128: rc = launch_tc<128, 5, false, 1>(mw, mx, p, grid, stream); break;
+            default: rc = launch_tc<256, 4, false, 1>(mw, mx, p, grid, stream); break;
         }
     } else {
         switch (bn) {
-            case 16: rc = launch_tc<16, 5, true>(mw, mx, p, grid, stream); break;
-            case 32: rc = launch_tc<32, 5, true>(mw, mx, p, grid, stream); break;
-            case 64: rc = launch_tc<64, 5, true>(mw, mx, p, grid, stream); break;
-            case 128: rc = launch_tc<128, 4, true>(mw, mx, p, grid, stream); break;
-            default: rc = launch_tc<256, 3, true>(mw, mx, p, grid, stream); break;
+            case 16: rc = launch_tc<16, 3, true, 2>(mw, mx, p, grid, stream); break;
+            case 32: rc = launch_tc<32, 3, true, 2>(mw, mx, p, grid, stream); break;
+            case 64: rc = launch_tc<64, 5, true, 1>(mw, mx, p, grid, stream); break;
+            case 128: rc = launch_tc<128, 4, true, 1>(mw, mx, p, grid, stream); break;
+            default: rc = launch_tc<256, 3, true, 1>(mw, mx, p, grid, stream); break;
         }
     }
-    if (rc != XR_OK || splits == 1) return rc;
+    if (rc != XR_OK || splits == 1 || defer_finish) return rc;      // deferred: the caller's next kernel sums the partials
     FinishParams f{scratch, out, bias, ldo, n, n_out, splits, epilogue, out_dtype, dual ? 1 : 0};
     size_t total = (size_t)n * n_out;
     int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
@@ -444,17 +482,15 @@ XR_EXPORT int xr_gemm_tc_noalloc(const void* X, const void* W, const float* bias
     const bool dual = epilogue == TC_EPI_SWIGLU;
     int bn = n <= 16 ? 16 : (n <= 32 ? 32 : (n <= 64 ? 64 : (n <= 128 ? 128 : 256)));
     int row_tiles = (n_out + TC_BM - 1) / TC_BM, tok_tiles = (n + bn - 1) / bn, total_kb = (K + TC_BK - 1) / TC_BK;
-    int splits = choose_splits(row_tiles * tok_tiles, total_kb, 148);
+    int splits = choose_splits(row_tiles * tok_tiles, tok_tiles, total_kb, resident_ctas(bn, dual, 148));
     if (splits > total_kb) splits = total_kb;
-    int per = (total_kb + splits - 1) / splits;
-    splits = (total_kb + per - 1) / per;
     long long need = splits > 1 ? (long long)splits * n * n_out * (dual ? 2 : 1) : 0;
     if (need > (long long)XR_NOALLOC_SCRATCH_FLOATS) return -4;
     // the status word must start at zero; the scratch needs no clearing (every partial that is read was
     // written by this call first)
     if (cudaMemsetAsync(g_noalloc_status_ptr[dev], 0, sizeof(int), stream) != cudaSuccess) return XR_ERR_LAUNCH;
     int rc = xr_gemm_tc(X, W, bias, out, out_dtype, epilogue, n, n_out, K, ldx, ldo, g_noalloc_scratch_ptr[dev],
-                        (long long)XR_NOALLOC_SCRATCH_FLOATS, g_noalloc_status_ptr[dev], splits, stream);
+                        (long long)XR_NOALLOC_SCRATCH_FLOATS, g_noalloc_status_ptr[dev], splits, 0, nullptr, 0, stream);
     if (rc != XR_OK) return rc;
     if (status_out_host != nullptr) {
         // optional: wait for the product and report whether a wait inside it gave up

@@ -43,6 +43,7 @@ class EngineParams:
     max_requests: int = 4              # live requests (state slots)
     max_request_tokens: Optional[int] = None   # longest request; default min(model limit, max_tokens)
     max_step_tokens: int = 8192        # sizing hint for the step's buffers (they grow if a step brings more)
+    cuda_graphs: bool = True           # decode-only steps are captured once per (batch, context bucket) and replayed
     device: str = "cuda:0"
 
 
@@ -68,10 +69,27 @@ class StepContext:
         self.block_tables: List[torch.Tensor] = []
         self.host: Dict[str, np.ndarray] = {}
         self.max_kv_len = 0            # longest key range any token of the step reads
+        self._pending = {}
         self.decode_only = False       # every segment is a single token
 
     def buf(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
         return self._eng._buf(name, shape, dtype)
+
+    # A part whose last product was split along K may leave the sum unfinished ("pending") on the residual
+    # stream; the next norm finishes it in its own pass.  Anything else that reads or writes that tensor
+    # directly calls ``materialize`` first.
+    def set_pending(self, x: torch.Tensor, pending) -> None:
+        if pending is not None:
+            self.materialize(x)
+            self._pending[x.data_ptr()] = pending
+
+    def take_pending(self, x: torch.Tensor):
+        return self._pending.pop(x.data_ptr(), None)
+
+    def materialize(self, x: torch.Tensor) -> None:
+        p = self._pending.pop(x.data_ptr(), None)
+        if p is not None:
+            p.finish()
 
     def cache_layer(self, lay: LayerRuntime):
         """(pointer to this layer's K block of page 0, elements between pages, elements from K to V)."""
@@ -132,6 +150,17 @@ class Engine:
         self._pinned_next = 0
         self._slot_generation = np.zeros(p.max_requests, dtype=np.int64)
         self.steps_run = 0
+        # CUDA graphs of decode-only steps, keyed by (tokens, wanted rows, context bucket).  A graph holds the
+        # addresses of the step's buffers, so any buffer that is made anew invalidates all graphs.
+        self._graphs: Dict[tuple, object] = {}
+        self._graph_seen: Dict[tuple, int] = {}
+        self._buf_generation = 0
+        self.graph_replays = 0
+        self._graph_launches: Dict[tuple, int] = {}
+        # the step description's device buffer is made once for the largest step the parameters name
+        T, S = p.max_step_tokens, p.max_requests
+        self._buf("step_description", (4 * (T + 4) + 4 * (S + 4) + len(self.cache.groups) * (S * self.cache.max_pages_per_request + 4),),
+                  torch.int32)
 
     # ---- buffers ---------------------------------------------------------------
     def _buf(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
@@ -146,6 +175,8 @@ class Engine:
                 cap = self.params.max_step_tokens * int(shape[1])
             t = torch.empty(max(cap, 1), dtype=dtype, device=self.device)
             self._bufs[key] = t
+            self._buf_generation += 1
+            self._graphs.clear()
         return t[:n].view(*shape)
 
     # ---- requests ----------------------------------------------------------------
@@ -208,7 +239,10 @@ class Engine:
                     self.cache.close(r)
                 raise
         ctx = self._describe(entries)
-        logits = self._forward(ctx)
+        if ctx.decode_only and self.params.cuda_graphs:
+            logits = self._forward_graphed(ctx)
+        else:
+            logits = self._forward(ctx)
         for e in entries:
             self.cache.commit(e.request)
         self.steps_run += 1
@@ -267,8 +301,41 @@ class Engine:
         ctx.host = {"token_ids": tok.copy(), "positions": pos.copy(), "tok_seg": seg.copy(), "logit_rows": rows[:R].copy(),
                     "seg_start": s_start.copy(), "seg_len": s_len.copy(), "seg_pos0": s_pos0.copy(),
                     "seg_slot": s_slot.copy()}
+        if decode_only:
+            max_kv = -(-max_kv // 1024) * 1024      # a bucket, so that launch shapes repeat from step to step
         ctx.max_kv_len, ctx.decode_only = max_kv, decode_only
         return ctx
+
+    def _forward_graphed(self, ctx: StepContext) -> torch.Tensor:
+        """Decode-only steps have the same launches whenever batch size and context bucket repeat: the
+        first such step runs plainly (and makes every buffer), the second is captured, later ones replay.
+        Everything that changes from step to step is in the step description, which is copied before."""
+        key = (ctx.n, ctx.n_rows, ctx.max_kv_len)
+        g = self._graphs.get(key)
+        if g is not None:
+            g.replay()
+            self.graph_replays += 1
+            kernels.launch_count += self._graph_launches[key]
+            return self._bufs[("logits", torch.float32)][:ctx.n_rows * self.plan.vocab_size].view(ctx.n_rows, -1)
+        seen = self._graph_seen.get(key, 0)
+        self._graph_seen[key] = seen + 1
+        if seen == 0 or ctx.n_rows == 0:
+            return self._forward(ctx)
+        gen = self._buf_generation
+        graph = torch.cuda.CUDAGraph()
+        torch.cuda.synchronize(self.device)
+        launches0 = kernels.launch_count
+        with torch.cuda.graph(graph):
+            logits = self._forward(ctx)
+        self._graph_launches[key] = kernels.launch_count - launches0
+        if self._buf_generation != gen:
+            # a buffer was made during capture: the graph may hold a stale address; run plainly this time
+            self._graph_seen[key] = 1
+            return self._forward(ctx)
+        self._graphs[key] = graph
+        graph.replay()
+        self.graph_replays += 1
+        return logits
 
     def _forward(self, ctx: StepContext) -> torch.Tensor:
         plan = self.plan
@@ -277,6 +344,7 @@ class Engine:
         for lay in self.model.layers:
             plan.blocks[plan.schedule[lay.entry].layer].forward(ctx, x, lay)
         if ctx.n_rows == 0:
+            ctx.materialize(x)
             return torch.empty((0, plan.vocab_size), dtype=torch.float32, device=self.device)
         hn = ctx.buf("head_normed", (ctx.n_rows, plan.width), ctx.act_dtype)
         plan.final_norm.forward(ctx, x, hn, rows=ctx.logit_rows)

@@ -54,7 +54,10 @@ def _declare(L: ctypes.CDLL) -> None:
         "xr_residual_add": [_vp, _vp, _i, _i, _i, _vp],
         "xr_gemm_simt": [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _ll, _ll, _vp],
         "xr_attention_simt": [_vp, _vp, _i, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
-        "xr_gemm_tc": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _ll, _ll, _vp, _ll, _vp, _i, _vp],
+        "xr_gemm_tc": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _ll, _ll, _vp, _ll, _vp, _i, _i, ctypes.POINTER(ctypes.c_int), _i, _vp],
+        "xr_finish_add_rmsnorm": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
+        "xr_finish_plain": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _ll, _vp],
+        "xr_finish_rope_store": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _vp],
         "xr_attention_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _f,
                              _i, _i, _i, _i, _i, _vp],
         "xr_attention_mma_splits": [_i, _i],
@@ -232,18 +235,92 @@ def gemm_tc_supported(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bo
             and out.stride(1) == 1)
 
 
+TILE_ROWS, TILE_K = 128, 64
+
+
+def pack_weight(w: torch.Tensor, halves: int = 1) -> torch.Tensor:
+    """Re-lay a [rows, K] bfloat16 matrix tile by tile for the tensor-core product:
+    [row tile][K block][128][64], rows and K padded with zeros to whole tiles, so that every tile the
+    kernel fetches is one contiguous 16 KB read.  `halves` = 2 packs the two halves of the rows (gate, up)
+    separately, each padded to whole tiles."""
+    assert w.dtype == torch.bfloat16 and w.dim() == 2 and w.shape[0] % halves == 0
+    rows, k = w.shape[0] // halves, w.shape[1]
+    rp, kp = -(-rows // TILE_ROWS) * TILE_ROWS, -(-k // TILE_K) * TILE_K
+    out = torch.zeros((halves, rp // TILE_ROWS, kp // TILE_K, TILE_ROWS, TILE_K), dtype=w.dtype, device=w.device)
+    for h in range(halves):
+        src = w[h * rows:(h + 1) * rows]
+        if rp != rows or kp != k:
+            pad = torch.zeros((rp, kp), dtype=w.dtype, device=w.device)
+            pad[:rows, :k] = src
+            src = pad
+        out[h] = src.view(rp // TILE_ROWS, TILE_ROWS, kp // TILE_K, TILE_K).permute(0, 2, 1, 3)
+    return out
+
+
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
-            epilogue: int = EPI_STORE, force_splits: int = 0) -> None:
+            epilogue: int = EPI_STORE, force_splits: int = 0, defer: bool = False,
+            packed_rows: Optional[int] = None) -> int:
     """bfloat16 product on tcgen05.  EPI_STORE: out[t][r] = x.w (+bias); EPI_ADD: float32 out += ...;
-    EPI_SWIGLU: w is [2F, K] (gate rows, then up rows), out[t][f] = silu(x.w_gate) * (x.w_up)."""
+    EPI_SWIGLU: w is [2F, K] (gate rows, then up rows), out[t][f] = silu(x.w_gate) * (x.w_up).
+
+    Returns the number of K splits used.  With `defer` and more than one split, `out` is NOT written: the
+    partial sums [splits][n][n_out] float32 stay in the workspace (``tc_workspace``) for the caller's next
+    kernel (``finish_*``) to sum, together with the bias."""
     n, k = x.shape
-    n_out = w.shape[0] // 2 if epilogue == EPI_SWIGLU else w.shape[0]
-    assert w.shape[1] == k and out.shape == (n, n_out) and gemm_tc_supported(x, w, out)
+    if packed_rows is not None:
+        # w comes from pack_weight(); packed_rows is the logical number of output features (per half)
+        n_out = packed_rows
+        assert w.dim() == 5 and w.shape[0] == (2 if epilogue == EPI_SWIGLU else 1) and w.shape[2] == -(-k // TILE_K)
+        assert w.shape[1] == -(-n_out // TILE_ROWS) and out.shape == (n, n_out)
+        assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and k % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
+    else:
+        n_out = w.shape[0] // 2 if epilogue == EPI_SWIGLU else w.shape[0]
+        assert w.shape[1] == k and out.shape == (n, n_out) and gemm_tc_supported(x, w, out)
     assert bias is None or (bias.dtype == torch.float32 and bias.numel() == n_out and epilogue != EPI_SWIGLU)
+    assert not defer or epilogue != EPI_SWIGLU
     scratch, status = tc_workspace(x.device)
+    used = ctypes.c_int(1)
     _check(lib().xr_gemm_tc(x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), dtype_code(out.dtype), epilogue,
                             n, n_out, k, x.stride(0), out.stride(0), scratch.data_ptr(), scratch.numel(),
-                            status.data_ptr(), force_splits, _stream()), "gemm_tc")
+                            status.data_ptr(), force_splits, int(defer), ctypes.byref(used),
+                            int(packed_rows is not None), _stream()), "gemm_tc")
+    _count(1 if (used.value == 1 or defer) else 2)
+    return used.value
+
+
+def finish_add_rmsnorm(partial: torch.Tensor, splits: int, bias: Optional[torch.Tensor], x: torch.Tensor,
+                       w: torch.Tensor, out: torch.Tensor, eps: float) -> None:
+    """x += sum of the split-K partials (+ bias); out = RMSNorm(x) * w.  One pass over each row."""
+    _dev(x, w, out, bias)
+    n, d = x.shape
+    assert x.dtype == torch.float32 and w.dtype == torch.float32 and out.shape == (n, d) and partial.numel() >= splits * n * d
+    _check(lib().xr_finish_add_rmsnorm(partial.data_ptr(), splits, _ptr(bias), x.data_ptr(), w.data_ptr(), out.data_ptr(),
+                                       dtype_code(out.dtype), n, d, float(eps), _stream()), "finish_add_rmsnorm")
+    _count()
+
+
+def finish_plain(partial: torch.Tensor, splits: int, bias: Optional[torch.Tensor], out: torch.Tensor,
+                 accumulate: bool) -> None:
+    """out (+)= sum of the split-K partials (+ bias)."""
+    n, width = out.shape
+    assert out.stride(1) == 1 and partial.numel() >= splits * n * width
+    _check(lib().xr_finish_plain(partial.data_ptr(), splits, _ptr(bias), out.data_ptr(), dtype_code(out.dtype),
+                                 int(accumulate), n, width, out.stride(0), _stream()), "finish_plain")
+    _count()
+
+
+def finish_rope_store(partial: torch.Tensor, splits: int, bias: Optional[torch.Tensor], qkv: torch.Tensor, positions,
+                      tok_seg, block_tables, inv_freq: Optional[torch.Tensor], cache_k_ptr: Optional[int],
+                      page_stride: int, v_offset: int, H: int, K: int, hd: int, rotary_dim: int, max_pages: int,
+                      page_size: int) -> None:
+    """Sum the partials of the fused QKV product (+ bias), rotate Q and K, write Q into `qkv` and K, V into
+    their pages (into `qkv` when cache_k_ptr is None)."""
+    _dev(qkv, positions, tok_seg, block_tables, inv_freq, bias)
+    n = qkv.shape[0]
+    assert qkv.dtype == torch.bfloat16 and qkv.shape[1] == (H + 2 * K) * hd and partial.numel() >= splits * n * qkv.shape[1]
+    _check(lib().xr_finish_rope_store(partial.data_ptr(), splits, _ptr(bias), qkv.data_ptr(), positions.data_ptr(),
+                                      tok_seg.data_ptr(), block_tables.data_ptr(), _ptr(inv_freq), cache_k_ptr, page_stride,
+                                      v_offset, n, H, K, hd, rotary_dim, max_pages, page_size, _stream()), "finish_rope_store")
     _count()
 
 

@@ -62,9 +62,9 @@ class GQAAttention(Mixer):
         if self.bias:
             bias = torch.cat([tensors[n + ".bias"].to(torch.float32) for n in (q, k, v)])
             obias = tensors[o + ".bias"]
-        self.qkv = Linear(torch.cat(ws, dim=0), bias)
+        self.qkv = Linear(torch.cat(ws, dim=0), bias).prepare(rt)
         del ws
-        self.out = Linear(tensors[o + ".weight"], obias)
+        self.out = Linear(tensors[o + ".weight"], obias).prepare(rt)
         self.position.prepare(rt)
 
     def weight_bytes(self):
@@ -74,12 +74,20 @@ class GQAAttention(Mixer):
         n = h.shape[0]
         qkv_dim = (self.H + 2 * self.K) * self.hd
         qkv = ctx.buf("attn_qkv", (n, qkv_dim), ctx.act_dtype)
-        self.qkv.forward(h, qkv)
+        pend = self.qkv.forward(h, qkv, defer=True)
         k_ptr, page_stride, v_offset = ctx.cache_layer(lay)
         bt = ctx.block_tables[lay.group]
-        kernels.rope_store(qkv, ctx.positions, ctx.tok_seg, bt, self.position.inv_freq,
-                           k_ptr if lay.writes_cache else None, page_stride, v_offset,
-                           self.H, self.K, self.hd, self.position.rotary_dim, ctx.max_pages, ctx.page_size)
+        store_ptr = k_ptr if lay.writes_cache else None
+        if pend is not None and lay.writes_cache:
+            # the product was split along K: its finish, the rotation and the page store are one kernel
+            kernels.finish_rope_store(pend.partial, pend.splits, pend.bias, qkv, ctx.positions, ctx.tok_seg, bt,
+                                      self.position.inv_freq, store_ptr, page_stride, v_offset, self.H, self.K, self.hd,
+                                      self.position.rotary_dim, ctx.max_pages, ctx.page_size)
+        else:
+            if pend is not None:
+                pend.finish()
+            kernels.rope_store(qkv, ctx.positions, ctx.tok_seg, bt, self.position.inv_freq, store_ptr, page_stride,
+                               v_offset, self.H, self.K, self.hd, self.position.rotary_dim, ctx.max_pages, ctx.page_size)
         o = ctx.buf("attn_out", (n, self.H * self.hd), ctx.act_dtype)
         # Q is read in place from the fused rows (row stride = qkv_dim)
         G = self.H // self.K
@@ -101,7 +109,7 @@ class GQAAttention(Mixer):
             kernels.attention_simt(qkv, qkv_dim, o, k_ptr, ctx.positions, ctx.tok_seg, bt, page_stride, v_offset,
                                    self.H, self.K, self.hd, ctx.max_pages, ctx.page_size, self.window or 0, self.scale)
             counters["simt"] += 1
-        self.out.forward(o, x, accumulate=True)
+        ctx.set_pending(x, self.out.forward(o, x, accumulate=True, defer=True))
 
 
 register_mixer("gqa_attention", GQAAttention)

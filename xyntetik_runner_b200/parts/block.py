@@ -27,6 +27,8 @@ class PreNormBlock(Block):
         return sum(p.weight_bytes() for p in self.parts())
 
     def forward(self, ctx, x, lay):
+        # A norm finishes whatever sum the part before it left pending on x (see StepContext.set_pending),
+        # so x is complete whenever a mixer or a feed-forward runs.
         h = ctx.buf("block_normed", (x.shape[0], x.shape[1]), ctx.act_dtype)
         self.mixer_norm.forward(ctx, x, h)
         self.mixer.forward(ctx, h, x, lay)

@@ -41,7 +41,9 @@ class Head(Part):
         return {} if self.tied_to is not None else {self.name: TensorSpec((self.vocab, self.width), kind="matrix")}
 
     def bind(self, tensors, rt):
-        self.linear = Linear(self.tied_to.table if self.tied_to is not None else tensors[self.name])
+        # a tied head multiplies by the embedding table; the gather keeps reading the table as stored
+        self.linear = Linear(self.tied_to.table if self.tied_to is not None else tensors[self.name]).prepare(
+            rt, keep_plain=self.tied_to is not None)
 
     def weight_bytes(self):
         return self.linear.nbytes()

@@ -7,7 +7,7 @@ import torch
 from .. import kernels
 from ..weights.loader import TensorSpec
 from .base import FeedForward, register_feed_forward
-from .linear import Linear, counters
+from .linear import Linear
 
 
 class SwiGLU(FeedForward):
@@ -28,26 +28,24 @@ class SwiGLU(FeedForward):
         if wg.dtype != wu.dtype:
             wg, wu = wg.to(torch.float32), wu.to(torch.float32)
         # one product for gate and up: rows [0, F) are the gate, [F, 2F) the up projection
-        self.gate_up = Linear(torch.cat([wg, wu], dim=0))
+        self.gate_up = Linear(torch.cat([wg, wu], dim=0), halves=2).prepare(rt)
         del wg, wu
-        self.down = Linear(tensors[d])
+        self.down = Linear(tensors[d]).prepare(rt)
 
     def weight_bytes(self):
         return self.gate_up.nbytes() + self.down.nbytes()
 
     def forward(self, ctx, h, x):
-        from . import linear_tc
         n = h.shape[0]
         act = ctx.buf("ffn_act", (n, self.inner), ctx.act_dtype)
-        if linear_tc.usable(self.gate_up, h, act, False):
+        if self.gate_up.swiglu_fused():
             # gate and up share the X tile; silu(g) * u happens in the product's epilogue
-            kernels.gemm_tc(h, self.gate_up.weight, act, None, kernels.EPI_SWIGLU)
-            counters["tcgen05"] += 1
+            self.gate_up.forward_swiglu(h, act)
         else:
             gu = ctx.buf("ffn_gate_up", (n, 2 * self.inner), ctx.act_dtype)
             self.gate_up.forward(h, gu)
             kernels.silu_mul(gu, act)
-        self.down.forward(act, x, accumulate=True)
+        ctx.set_pending(x, self.down.forward(act, x, accumulate=True, defer=True))
 
 
 register_feed_forward("swiglu", SwiGLU)

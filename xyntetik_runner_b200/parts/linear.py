@@ -1,10 +1,10 @@
 """A weight matrix and the choice of kernel that multiplies by it.
 
-``out[t][r] (+)= sum_k x[t][k] W[r][k] (+ bias[r])``.  W keeps its stored dtype.
-bfloat16 activations times a bfloat16 matrix go to the tensor-core kernel
-(tcgen05, when the shapes meet its alignment rules); everything else -- the
-true 32-bit path above all -- goes to the float32 FMA kernel.  Which kernel ran
-is counted, so that a test can prove its subject ran.
+``out[t][r] (+)= sum_k x[t][k] W[r][k] (+ bias[r])``.  W keeps its stored dtype.  bfloat16 activations times
+a bfloat16 matrix go to the tensor-core kernel (tcgen05); for that the matrix is re-laid tile by tile when the
+part binds it (``prepare``), so that every tile the kernel streams is one contiguous read.  Everything else
+-- the true 32-bit path above all -- goes to the float32 FMA kernel on the matrix as stored.  Which kernel
+ran is counted, so that a test can prove its subject ran.
 """
 from __future__ import annotations
 
@@ -18,21 +18,49 @@ counters = {"tcgen05": 0, "simt": 0}
 
 
 class Linear:
-    def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor] = None):
-        assert weight.dim() == 2
-        self.weight = weight.contiguous()
+    def __init__(self, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, halves: int = 1):
+        """`halves` = 2: the rows are two matrices of equal height (gate, up) that the tensor-core kernel
+        multiplies side by side (see ``forward_swiglu``)."""
+        assert weight.dim() == 2 and weight.shape[0] % halves == 0
+        self.weight: Optional[torch.Tensor] = weight.contiguous()
         self.bias = None if bias is None else bias.to(torch.float32).contiguous()
         self.n_out, self.k = self.weight.shape
-        self._tc = None          # tensor-core plan (built on first use)
+        self.halves = halves
+        self.packed: Optional[torch.Tensor] = None
+        self._nbytes = self.weight.numel() * self.weight.element_size()
+
+    def prepare(self, rt, keep_plain: bool = False) -> "Linear":
+        """Choose the layout for the engine's precision.  Returns self."""
+        from . import linear_tc
+        if (linear_tc.ENABLED and rt.act_dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16
+                and self.k % 8 == 0 and self.weight.is_cuda):
+            self.packed = kernels.pack_weight(self.weight, self.halves)
+            if not keep_plain:
+                self.weight = None
+        return self
 
     def nbytes(self) -> int:
-        return self.weight.numel() * self.weight.element_size()
+        return self._nbytes
 
-    def forward(self, x: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
+    def forward(self, x: torch.Tensor, out: torch.Tensor, accumulate: bool = False, defer: bool = False):
+        """out (+)= x W^T (+ bias).  With `defer`, a product that was split along K leaves its partial sums in
+        the workspace and returns ``Pending``; the caller's next kernel sums them (and adds the bias).
+        Otherwise returns None and `out` is complete."""
         from . import linear_tc
-        if linear_tc.usable(self, x, out, accumulate):
-            linear_tc.run(self, x, out, accumulate)
+        if self.packed is not None:
             counters["tcgen05"] += 1
-        else:
-            kernels.gemm_simt(x, self.weight, out, self.bias, accumulate)
-            counters["simt"] += 1
+            return linear_tc.run(self, x, out, accumulate, defer)
+        if linear_tc.usable(self, x, out, accumulate):
+            counters["tcgen05"] += 1
+            return linear_tc.run(self, x, out, accumulate, defer)
+        kernels.gemm_simt(x, self.weight, out, self.bias, accumulate)
+        counters["simt"] += 1
+        return None
+
+    def swiglu_fused(self) -> bool:
+        return self.halves == 2 and self.packed is not None
+
+    def forward_swiglu(self, x: torch.Tensor, out: torch.Tensor) -> None:
+        """out[t][f] = silu(x . W_gate[f]) * (x . W_up[f]) in the product's epilogue (packed layout only)."""
+        kernels.gemm_tc(x, self.packed, out, None, kernels.EPI_SWIGLU, packed_rows=self.n_out // 2)
+        counters["tcgen05"] += 1

@@ -24,6 +24,13 @@ class RMSNorm(Norm):
         return self.width * 4
 
     def forward(self, ctx, x, out, rows=None):
+        pend = ctx.take_pending(x)
+        if pend is not None and rows is None:
+            # the product before this norm left partial sums: sum, add into x and normalise in one pass
+            kernels.finish_add_rmsnorm(pend.partial, pend.splits, pend.bias, x, self.weight, out, self.eps)
+            return
+        if pend is not None:
+            pend.finish()
         kernels.rmsnorm(x, self.weight, out, self.eps, rows)
 
 
