@@ -66,3 +66,46 @@ def test_cutting_matches_plain(folders, reference, name, cut, dtype):
         # the pool was sized for the peak, so pages of finished requests were used again
         total = sum(-(-len(t) // PAGE[name]) for t in reqs.values())
         assert total > eng.cache.pools[0].n_pages
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(folders, dtype):
+    """40 tokens at once, then 260 tokens one by one (pages fill and new ones are taken many times)."""
+    name = "A"
+    toks = traces.random_tokens(77, 300, tiny.CONFIGS[name]["vocab_size"])
+    ref = PlainLlama(folders[name, dtype]).logits(toks)
+    steps = traces.tail_decoded({"long": toks}, tail=260)
+    res, eng = run(folders[name, dtype], dtype, steps, page_size=16, max_tokens=320)
+    got = traces.collect(steps, res, tiny.CONFIGS[name]["vocab_size"])["long"]
+    traces.assert_close(got, ref, dtype, f"long decoding/{dtype}")
+    if dtype == "bfloat16":
+        assert eng.graph_replays > 200          # the decode steps ran as replayed graphs
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_first_tokens(folders, name, dtype):
+    """Positions 0, 1, 2 of a sequence: whole, and token by token from the very first."""
+    vocab = tiny.CONFIGS[name]["vocab_size"]
+    plain = PlainLlama(folders[name, dtype])
+    reqs = {f"f{n}": traces.random_tokens(n, n, vocab) for n in (1, 2, 3)}
+    for cut in (traces.whole, lambda r: traces.tail_decoded(r, tail=8)):
+        steps = cut(reqs)
+        res, _ = run(folders[name, dtype], dtype, steps, PAGE[name])
+        got = traces.collect(steps, res, vocab)
+        for rid, t in reqs.items():
+            traces.assert_close(got[rid], plain.logits(t), dtype, f"first tokens/{name}/{rid}")
+
+
+def test_batch_does_not_change_a_request_in_32_bit(folders):
+    """float32 path: a request's logits are bit-identical alone, in portions, and mixed with others."""
+    name = "B"
+    vocab = tiny.CONFIGS[name]["vocab_size"]
+    reqs = {f"r{i}": traces.random_tokens(50 + i, n, vocab) for i, n in enumerate((40, 75, 23, 61))}
+    outs = []
+    for cut in (traces.whole, traces.portions, lambda r: traces.mixed(r, seed=9)):
+        steps = cut(reqs)
+        res, _ = run(folders[name, "float32"], "float32", steps, 8)
+        outs.append(traces.collect(steps, res, vocab))
+    for rid in reqs:
+        assert np.array_equal(outs[0][rid], outs[1][rid]) and np.array_equal(outs[0][rid], outs[2][rid]), rid

@@ -153,6 +153,7 @@ class Engine:
         # CUDA graphs of decode-only steps, keyed by (tokens, wanted rows, context bucket).  A graph holds the
         # addresses of the step's buffers, so any buffer that is made anew invalidates all graphs.
         self._graphs: Dict[tuple, object] = {}
+        self._graph_ok = p.cuda_graphs and all(part.graph_safe for part in plan.parts())
         self._graph_seen: Dict[tuple, int] = {}
         self._buf_generation = 0
         self.graph_replays = 0
@@ -239,7 +240,7 @@ class Engine:
                     self.cache.close(r)
                 raise
         ctx = self._describe(entries)
-        if ctx.decode_only and self.params.cuda_graphs:
+        if ctx.decode_only and self._graph_ok:
             logits = self._forward_graphed(ctx)
         else:
             logits = self._forward(ctx)

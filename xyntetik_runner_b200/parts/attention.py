@@ -27,6 +27,7 @@ counters = {"mma": 0, "simt": 0}
 
 
 class GQAAttention(Mixer):
+    graph_safe = True
     def __init__(self, width: int, heads: int, kv_heads: int, head_dim: int, position: PositionEncoding,
                  prefix: str, bias: bool = False, window: Optional[int] = None, scale: Optional[float] = None,
                  q: str = "q_proj", k: str = "k_proj", v: str = "v_proj", o: str = "o_proj"):

@@ -24,6 +24,10 @@ from ..weights.loader import TensorSpec
 class Part:
     """Something with named tensors."""
     prefix: str = ""
+    # True when `forward` only launches kernels on the current stream with shapes that depend on the step's
+    # sizes alone (no host reads of device data, no allocation): such a part may be captured in a CUDA graph.
+    # The default is False, so a part that does not say so is always run plainly.
+    graph_safe: bool = False
 
     def tensors(self) -> Dict[str, TensorSpec]:
         """Full tensor names (prefix included) this part reads, with shapes."""

@@ -13,6 +13,10 @@ class PreNormBlock(Block):
     def parts(self):
         return (self.mixer_norm, self.mixer, self.ff_norm, self.feed_forward)
 
+    @property
+    def graph_safe(self):
+        return all(p.graph_safe for p in self.parts())
+
     def tensors(self):
         out = {}
         for p in self.parts():

@@ -15,6 +15,7 @@ from .linear import Linear
 
 
 class Embedding(Part):
+    graph_safe = True
     def __init__(self, vocab: int, width: int, name: str):
         self.vocab, self.width, self.name = vocab, width, name
         self.table = None
@@ -30,6 +31,7 @@ class Embedding(Part):
 
 
 class Head(Part):
+    graph_safe = True
     """`tied_to` set: no tensor of its own, multiplies by the embedding table."""
 
     def __init__(self, vocab: int, width: int, name: str = None, tied_to: Embedding = None):

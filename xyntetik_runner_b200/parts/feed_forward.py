@@ -11,6 +11,7 @@ from .linear import Linear
 
 
 class SwiGLU(FeedForward):
+    graph_safe = True
     def __init__(self, width: int, inner: int, prefix: str,
                  gate: str = "gate_proj.weight", up: str = "up_proj.weight", down: str = "down_proj.weight"):
         self.width, self.inner, self.prefix = width, inner, prefix

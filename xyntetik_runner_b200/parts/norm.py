@@ -9,6 +9,7 @@ from .base import Norm, register_norm
 
 
 class RMSNorm(Norm):
+    graph_safe = True
     def __init__(self, width: int, eps: float, name: str):
         self.width, self.eps, self.name = width, float(eps), name
         self.weight = None
