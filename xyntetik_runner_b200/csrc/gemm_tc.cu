@@ -361,21 +361,22 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParam
 // memory is sized for that), one otherwise.
 static int resident_ctas(int bn, bool dual, int sms) { return (bn <= 32 || (bn == 64 && !dual)) ? 2 * sms : sms; }
 
-// Number of K splits when there are few output tiles.  A product runs in waves of `slots` CTAs; the split is
-// chosen so that the last wave is as full as possible (a 224-tile product split 5 ways fills 3.78 waves of
-// 296, split 4 ways it would leave a fourth wave almost empty), keeping at least four K blocks per split.
+// Number of K splits when there are few output tiles.  A product runs in waves of `slots` CTAs, and a CTA costs
+// a fixed part (launch, barrier and tensor-memory set-up, filling the pipeline, the epilogue: about as long
+// as streaming six K blocks) plus its K blocks.  The split that minimises waves x (fixed + blocks) is chosen:
+// it fills the machine without cutting the work into pieces that are mostly overhead.
 static int choose_splits(int tiles, int tok_tiles, int total_kb, int slots) {
-    if (tok_tiles > 1 || tiles >= 4 * slots) return 1;       // only products with one tile of tokens are split
+    if (tok_tiles > 1 || tiles >= 2 * slots) return 1;       // only products with one tile of tokens are split
     int max_s = total_kb / 4;
     if (max_s > 16) max_s = 16;
     if (max_s < 1) max_s = 1;
     int best = 1;
-    double best_eff = 0.0;
+    long long best_cost = -1;
     for (int s = 1; s <= max_s; s++) {
         long long ctas = (long long)tiles * s;
         long long waves = (ctas + slots - 1) / slots;
-        double eff = (double)ctas / (double)(waves * slots);
-        if (eff > best_eff + 0.02) { best_eff = eff; best = s; }      // prefer fewer splits unless clearly better
+        long long cost = waves * (6 + (total_kb + s - 1) / s);
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = s; }
     }
     return best;
 }
