@@ -222,7 +222,7 @@ def _paged_case(seed, H, K, hd, page, seg_specs, dtype, window=0, spike=None):
                 ref=torch.cat(refs), n=n, n_seg=n_seg, max_pages=max_pages, max_len=max_len, lens_host=lens, scale=scale)
 
 
-def _run_attention(case, kind, H, K, hd, page, window, dtype):
+def _run_attention(case, kind, H, K, hd, page, window, dtype, tma=False):
     from xyntetik_runner_b200 import kernels
     c = case
     out = torch.zeros(c["n"], H * hd, dtype=dtype, device=DEV)
@@ -240,7 +240,9 @@ def _run_attention(case, kind, H, K, hd, page, window, dtype):
         lens = c["lens_host"]
         kernels.attention_mma(c["qkv"], qkv_dim, out, k_ptr, c["starts"], c["lens"], c["pos0"], c["bt"], pa, pm, page_stride,
                               v_off, H, K, hd, c["max_pages"], page, window, c["scale"], c["n_seg"], int(lens.max()),
-                              c["max_len"], splits, bool((lens * G <= 16).any()), bool((lens * G > 16).any()))
+                              c["max_len"], splits, bool((lens * G <= 16).any()), bool((lens * G > 16).any()),
+                              group=(cache.data_ptr(), cache.shape[0], cache.shape[1], 0) if tma else None)
+        kernels.tc_check_status(torch.device(DEV))
     return out.cpu().double()
 
 
@@ -254,16 +256,19 @@ ATT_CASES = [
     (5, 5, 80, 16, 0, [(10, 20), (0, 3), (515, 1)]),
     (16, 1, 112, 32, 100, [(0, 10), (1100, 1), (90, 30)]),
     (12, 4, 96, 16, 0, [(5, 6), (250, 40)]),
+    (8, 2, 128, 8, 0, [(0, 1), (7, 1), (8, 2), (300, 1), (1029, 1)]),
+    (4, 1, 64, 16, 70, [(100, 1), (69, 1), (70, 1), (71, 1), (2100, 3)]),
+    (16, 4, 128, 128, 0, [(2500, 1), (127, 1), (128, 1), (3000, 4)]),
 ]
 
 
 @pytest.mark.parametrize("case_id", range(len(ATT_CASES)))
-@pytest.mark.parametrize("kind", ["simt_f32", "simt_bf16", "mma"])
+@pytest.mark.parametrize("kind", ["simt_f32", "simt_bf16", "mma", "mma_tma"])
 def test_attention_kernels(case_id, kind):
     H, K, hd, page, window, segs = ATT_CASES[case_id]
     dtype = torch.float32 if kind == "simt_f32" else torch.bfloat16
     case = _paged_case(case_id, H, K, hd, page, segs, dtype, window)
-    got = _run_attention(case, "simt" if kind.startswith("simt") else "mma", H, K, hd, page, window, dtype)
+    got = _run_attention(case, "simt" if kind.startswith("simt") else "mma", H, K, hd, page, window, dtype, tma=kind == "mma_tma")
     ref = case["ref"]
     # inputs are exact in the kernel's own dtype, so the error is that of the arithmetic: float32 sums,
     # or (tensor-core path) probabilities rounded to bfloat16 before P.V and the bfloat16 output
@@ -272,14 +277,14 @@ def test_attention_kernels(case_id, kind):
     assert float(err.max()) <= tol, f"worst rows {torch.topk(err, min(5, len(err))).indices.tolist()} err {float(err.max()):.3e}"
 
 
-@pytest.mark.parametrize("kind", ["simt", "mma"])
+@pytest.mark.parametrize("kind", ["simt", "mma", "mma_tma"])
 def test_attention_finds_a_far_key(kind):
     """One key hundreds of positions back carries almost all the weight of the last query: a kernel that
     skipped or misplaced it (a page edge, a span edge) would be far off."""
     H, K, hd, page = 8, 2, 64, 16
     for key_pos in (0, 15, 16, 511, 512, 700):
         case = _paged_case(50 + key_pos, H, K, hd, page, [(0, 3), (900, 1), (1023, 2)], torch.bfloat16, 0, spike=(1, key_pos, 60.0))
-        got = _run_attention(case, kind, H, K, hd, page, 0, torch.bfloat16)
+        got = _run_attention(case, kind.split("_")[0], H, K, hd, page, 0, torch.bfloat16, tma=kind.endswith("tma"))
         err = (got - case["ref"]).abs().max() / case["ref"].abs().max()
         assert float(err) <= 1.2e-2, (key_pos, float(err))
 

@@ -55,7 +55,7 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_twice():
         assert float((got.double().cpu() - ref).abs().max()) <= tol * float(ref.abs().max()), call
         assert torch.equal(got, want), call                          # same kernels, same splits: same bits
     # a product that would need more scratch than the array holds is refused, and says so
-    n, n_out, k = 256, 8192, 8192
+    n, n_out, k = 200, 12288, 8192          # 96 tiles of 128 rows: split 3 ways, 7.4 M partial sums > 4 Mi
     x = torch.zeros(n, k, dtype=torch.bfloat16, device=dev)
     w = torch.zeros(n_out, k, dtype=torch.bfloat16, device=dev)
     out = torch.zeros(n, n_out, dtype=torch.bfloat16, device=dev)

@@ -23,6 +23,7 @@
 // K and V rows are gathered page by page with 16-byte cp.async copies (any page size), double buffered.
 #include "common.cuh"
 #include <math.h>
+#include <cuda.h>
 
 #define ATT_TILE 64            // keys per tile
 #define ATT_ROWS 64            // packed query rows per CTA in the rows kernel
@@ -45,6 +46,9 @@ struct AttnMmaArgs {
     int H, K, G, max_pages, page_size, window, max_splits;
     float scale;
     int page_shift;              // log2(page_size) when it is a power of two, else -1
+    // bulk-copy (TMA) variant of the keys kernel: the whole cache group as rows of head_dim elements
+    int n_layers, layer;         // layers in the cache group, this layer's index
+    int* status;                 // set non-zero if a bounded wait gives up
 };
 
 // Span length of a request whose last key is at position hi: a function of the request alone, so that its
@@ -130,11 +134,19 @@ __device__ __forceinline__ float att_exp(float x) { return __expf(x); }
 
 // LOWER_ONLY: rows 8..15 of the warp's tile hold no query (a decoded token with at most 8 heads per kv head),
 // so their softmax and rescaling are skipped (the matrix instruction computes them regardless).
-template <int HD, int NKT, bool LOWER_ONLY = false>
+// Element (row, col) of a [64][HD] tile in shared memory.  Plain: rows of HD + 8 elements (the copy kernels'
+// layout).  SWZ: what TMA writes with the 128-byte swizzle: sub-tiles of 64 columns, rows of 128 bytes, the
+// 16-byte chunk index XORed with the row's low three bits (col must be a multiple of 8).
+template <int HD, bool SWZ>
+__device__ __forceinline__ const __nv_bfloat16* tile_ptr(const __nv_bfloat16* base, int row, int col) {
+    if (SWZ) return base + (col >> 6) * (ATT_TILE * 64) + row * 64 + ((((col & 63) >> 3) ^ (row & 7)) << 3);
+    return base + row * (HD + 8) + col;
+}
+
+template <int HD, int NKT, bool LOWER_ONLY = false, bool SWZ = false>
 __device__ __forceinline__ void tile_step(const uint32_t (*qf)[4], const __nv_bfloat16* ks, const __nv_bfloat16* vs,
                                           int col0, int key0, int pos_a, int pos_b, int window, float scale,
                                           float* m, float* l, float (*o)[4]) {
-    constexpr int LD = HD + 8;
     const int lane = threadIdx.x & 31;
     float s[NKT][4];
 #pragma unroll
@@ -144,7 +156,7 @@ __device__ __forceinline__ void tile_step(const uint32_t (*qf)[4], const __nv_bf
 #pragma unroll
         for (int j = 0; j < NKT; j += 2) {
             uint32_t b0, b1, b2, b3;
-            const __nv_bfloat16* p = ks + (col0 + j * 8 + (lane & 7) + ((lane >> 4) << 3)) * LD + kk * 16 + (((lane >> 3) & 1) << 3);
+            const __nv_bfloat16* p = tile_ptr<HD, SWZ>(ks, col0 + j * 8 + (lane & 7) + ((lane >> 4) << 3), kk * 16 + (((lane >> 3) & 1) << 3));
             ldsm_x4(b0, b1, b2, b3, p);
             mma_bf16(s[j], qf[kk], b0, b1);
             mma_bf16(s[j + 1], qf[kk], b2, b3);
@@ -213,7 +225,7 @@ __device__ __forceinline__ void tile_step(const uint32_t (*qf)[4], const __nv_bf
 #pragma unroll
         for (int d = 0; d < HD / 8; d += 2) {
             uint32_t b0, b1, b2, b3;
-            const __nv_bfloat16* p = vs + (col0 + kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3)) * LD + d * 8 + ((lane >> 4) << 3);
+            const __nv_bfloat16* p = tile_ptr<HD, SWZ>(vs, col0 + kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3), d * 8 + ((lane >> 4) << 3));
             ldsm_x4_t(b0, b1, b2, b3, p);
             mma_bf16(o[d], a, b0, b1);
             mma_bf16(o[d + 1], a, b2, b3);
@@ -411,6 +423,169 @@ k_attention_keys(AttnMmaArgs a) {
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// keys kernel with bulk copies: same work split and arithmetic as k_attention_keys, but one thread fetches
+// each tile with TMA (cp.async.bulk.tensor, 128-byte swizzle) straight from the pages: the cache group is
+// one 2-D tensor [(page, layer, K|V, kv head, token)][head_dim], a page's block of one kv head is
+// min(page_size, 64) consecutive rows.  No thread computes gather addresses.  Needs head_dim 64 or 128 and a
+// power-of-two page size >= 8.  Rows beyond a request's last key are not zero-filled by the copy; scores there
+// are masked, and the value rows are cleared in shared memory so that stale bytes cannot reach the output.
+// ---------------------------------------------------------------------------------------------
+#define ATT_SPIN_LIMIT (1u << 22)
+
+__device__ __forceinline__ uint32_t att_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool att_mbar_wait(uint64_t* bar, uint32_t parity) {
+    for (uint32_t i = 0; i < ATT_SPIN_LIMIT; i++) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(att_smem_u32(bar)), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+template <int HD, int STAGES>
+__global__ void __launch_bounds__(ATT_THREADS)
+k_attention_keys_tma(const __grid_constant__ CUtensorMap cache_map, AttnMmaArgs a) {
+    constexpr int LD = HD + 8;
+    constexpr int TILE_ELEMS = ATT_TILE * HD;                      // one K (or V) tile, swizzled sub-tiles of 64 columns
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);     // TMA with the 128-byte swizzle wants 1 KB
+    __nv_bfloat16* kbuf = (__nv_bfloat16*)smem;                    // [STAGES][TILE_ELEMS]
+    __nv_bfloat16* vbuf = kbuf + STAGES * TILE_ELEMS;              // [STAGES][TILE_ELEMS]
+    __nv_bfloat16* qs = vbuf + STAGES * TILE_ELEMS;                // [16][LD]
+    uint64_t* full = (uint64_t*)(qs + 16 * LD);
+    volatile int* gave_up = (volatile int*)(full + STAGES);
+    const int seg = blockIdx.z, kvh = blockIdx.y, span = blockIdx.x;
+    const int L = a.seg_len[seg], rows_total = L * a.G;
+    if (rows_total > 16) return;
+    const int pos0 = a.seg_pos0[seg], tok_base = a.seg_start[seg];
+    const int hi_all = pos0 + L - 1;
+    const int lo_all = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
+    const int SPAN = att_span(hi_all);
+    const int first_span = lo_all / SPAN;
+    const int k_begin = (first_span + span) * SPAN;
+    if (k_begin > hi_all) return;
+    const int lo = max(lo_all, k_begin), hi = min(hi_all, k_begin + SPAN - 1);
+    const int* bt = a.block_tables + (size_t)seg * a.max_pages;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t_lo = lo / ATT_TILE, t_hi = hi / ATT_TILE;
+    const int box_rows = a.page_size < ATT_TILE ? a.page_size : ATT_TILE;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(att_smem_u32(&full[s])), "r"(1));
+        *gave_up = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    // one thread fetches tile `t` into stage `s`: K and V, per page block and per 64-column half
+    auto fetch = [&](int t, int s) {
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(att_smem_u32(&full[s])), "r"(2 * TILE_ELEMS * 2) : "memory");
+        for (int r0 = 0; r0 < ATT_TILE; r0 += box_rows) {
+            int kp = t * ATT_TILE + r0;
+            int page = bt[kp >> a.page_shift];                     // -1 (no page): the copy reads outside the tensor and fills zeros
+            int tok = kp & (a.page_size - 1);
+            long long rowk = ((((long long)page * a.n_layers + a.layer) * 2 + 0) * a.K + kvh) * a.page_size + tok;
+            long long rowv = rowk + (long long)a.K * a.page_size;
+            if (page < 0) { rowk = -(long long)ATT_TILE; rowv = -(long long)ATT_TILE; }
+#pragma unroll
+            for (int c = 0; c < HD / 64; c++) {
+                __nv_bfloat16* kd = kbuf + s * TILE_ELEMS + c * (ATT_TILE * 64) + r0 * 64;
+                __nv_bfloat16* vd = vbuf + s * TILE_ELEMS + c * (ATT_TILE * 64) + r0 * 64;
+                asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                             ::"r"(att_smem_u32(kd)), "l"(&cache_map), "r"(c * 64), "r"((int)rowk), "r"(att_smem_u32(&full[s])) : "memory");
+                asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                             ::"r"(att_smem_u32(vd)), "l"(&cache_map), "r"(c * 64), "r"((int)rowv), "r"(att_smem_u32(&full[s])) : "memory");
+            }
+        }
+    };
+    if (threadIdx.x == 0)
+        for (int i = 0; i < STAGES - 1 && t_lo + i <= t_hi; i++) fetch(t_lo + i, i);
+    load_q<HD>(qs, a, tok_base, kvh, 0, 16, rows_total);
+    __syncthreads();
+    uint32_t qf[HD / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; kk++)
+        ldsm_x4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], qs + (lane & 15) * LD + kk * 16 + ((lane >> 4) << 3));
+    const int ra = lane >> 2, rb = ra + 8;
+    const int pos_a = ra < rows_total ? pos0 + ra / a.G : -1, pos_b = rb < rows_total ? pos0 + rb / a.G : -1;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[HD / 8][4];
+#pragma unroll
+    for (int d = 0; d < HD / 8; d++) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
+
+    for (int t = t_lo; t <= t_hi; t++) {
+        int i = t - t_lo, cur = i % STAGES;
+        if (threadIdx.x == 0 && t + STAGES - 1 <= t_hi) fetch(t + STAGES - 1, (i + STAGES - 1) % STAGES);
+        // A wait that runs out does not leave the loop (the threads of a CTA must keep meeting at the barriers
+        // below); it is recorded, the result of this CTA is then meaningless, and the status word says so.
+        if (!att_mbar_wait(&full[cur], (i / STAGES) & 1)) *gave_up = 1;
+        __nv_bfloat16* vt = vbuf + cur * TILE_ELEMS;
+        if ((t + 1) * ATT_TILE - 1 > hi) {
+            // the tile runs past the last key: clear those value rows (probabilities there are zero, but 0 x garbage
+            // must stay 0 whatever the bytes are)
+            int first_bad = hi + 1 - t * ATT_TILE;
+            for (int e = threadIdx.x; e < (ATT_TILE - first_bad) * (HD / 8); e += ATT_THREADS) {
+                int r = first_bad + e / (HD / 8), c = (e % (HD / 8)) * 8;
+                *reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(tile_ptr<HD, true>(vt, r, c))) = make_uint4(0, 0, 0, 0);
+            }
+            __syncthreads();
+        }
+        if (t * ATT_TILE < lo) {
+            int n_bad = lo - t * ATT_TILE;
+            for (int e = threadIdx.x; e < n_bad * (HD / 8); e += ATT_THREADS) {
+                int r = e / (HD / 8), c = (e % (HD / 8)) * 8;
+                *reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(tile_ptr<HD, true>(vt, r, c))) = make_uint4(0, 0, 0, 0);
+            }
+            __syncthreads();
+        }
+        int c0 = warp * 16, kfirst = t * ATT_TILE + c0;
+        if (kfirst <= hi && kfirst + 15 >= lo) {
+            if (rows_total <= 8)
+                tile_step<HD, 2, true, true>(qf, kbuf + cur * TILE_ELEMS, vt, c0, t * ATT_TILE, pos_a, pos_b, a.window, a.scale, m, l, o);
+            else
+                tile_step<HD, 2, false, true>(qf, kbuf + cur * TILE_ELEMS, vt, c0, t * ATT_TILE, pos_a, pos_b, a.window, a.scale, m, l, o);
+        }
+        __syncthreads();                 // everyone is done with stage `cur` before it is fetched into again
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && *gave_up) atomicExch(a.status, 2);
+    // combine the four warps (same as the copy kernel); the stage buffers are free now
+    float* acc_s = reinterpret_cast<float*>(kbuf);
+    float* ml_s = acc_s + 4 * 16 * HD;
+    const int t2 = (lane & 3) * 2;
+#pragma unroll
+    for (int d = 0; d < HD / 8; d++) {
+        acc_s[(warp * 16 + ra) * HD + d * 8 + t2] = o[d][0]; acc_s[(warp * 16 + ra) * HD + d * 8 + t2 + 1] = o[d][1];
+        acc_s[(warp * 16 + rb) * HD + d * 8 + t2] = o[d][2]; acc_s[(warp * 16 + rb) * HD + d * 8 + t2 + 1] = o[d][3];
+    }
+    if ((lane & 3) == 0) {
+        ml_s[(warp * 16 + ra) * 2] = m[0]; ml_s[(warp * 16 + ra) * 2 + 1] = l[0];
+        ml_s[(warp * 16 + rb) * 2] = m[1]; ml_s[(warp * 16 + rb) * 2 + 1] = l[1];
+    }
+    __syncthreads();
+    size_t item = ((size_t)seg * a.K + kvh) * a.max_splits + span;
+    float* pacc = a.part_acc + item * 16 * HD;
+    float* pml = a.part_ml + item * 16 * 2;
+    for (int i = threadIdx.x; i < rows_total * HD; i += ATT_THREADS) {
+        int r = i / HD, d = i % HD;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; w++) mm = fmaxf(mm, ml_s[(w * 16 + r) * 2]);
+        float off = mm == -INFINITY ? 0.f : mm;
+        float acc = 0.f, ll = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            float f = expf(ml_s[(w * 16 + r) * 2] - off);
+            acc += acc_s[(w * 16 + r) * HD + d] * f;
+            ll += ml_s[(w * 16 + r) * 2 + 1] * f;
+        }
+        pacc[r * HD + d] = acc;
+        if (d == 0) { pml[r * 2] = mm; pml[r * 2 + 1] = ll; }
+    }
+}
+
 // Combine the spans of one (request, kv head) in ascending order and write the output rows.
 // grid (K, segments).  Each row's span weights exp(m_s - M) / L are computed once into shared memory.
 template <int HD>
@@ -472,9 +647,61 @@ k_attention_merge(AttnMmaArgs a) {
 }
 
 // ---------------------------------------------------------------------------------------------
+typedef CUresult (*AttEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static AttEncodeFn att_encode() {
+    static AttEncodeFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (AttEncodeFn)ptr;
+    }
+    return fn;
+}
+
+// The bulk-copy keys kernel, when the shapes allow it.  Returns 1 if launched, 0 if not applicable, < 0 on error.
+template <int HD>
+static int launch_keys_tma(const AttnMmaArgs& a, const void* cache_base, long long n_pages, int n_seg, cudaStream_t stream) {
+  if constexpr (HD != 64 && HD != 128) {
+    return 0;
+  } else {
+    if (a.page_shift < 3 || cache_base == nullptr || a.status == nullptr) return 0;
+    long long total_rows = n_pages * a.n_layers * 2 * a.K * a.page_size;
+    if (total_rows >= (1LL << 31) || ((uintptr_t)cache_base & 15)) return 0;
+    AttEncodeFn enc = att_encode();
+    if (!enc) return 0;
+    CUtensorMap map;
+    cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)total_rows};
+    cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)(a.page_size < ATT_TILE ? a.page_size : ATT_TILE)};
+    cuuint32_t estr[2] = {1, 1};
+    if (enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache_base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return -3;
+    constexpr int LD = HD + 8;
+    constexpr int S2 = 2 * 2 * ATT_TILE * HD * 2 + 16 * LD * 2 + 64 + 1024, S4 = 4 * 2 * ATT_TILE * HD * 2 + 16 * LD * 2 + 64 + 1024;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(k_attention_keys_tma<HD, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, S2) != cudaSuccess ||
+            cudaFuncSetAttribute(k_attention_keys_tma<HD, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, S4) != cudaSuccess)
+            return XR_ERR_LAUNCH;
+        configured = true;
+    }
+    dim3 grid(a.max_splits, a.K, n_seg);
+    if ((long long)a.max_splits * a.K * n_seg <= 2 * 148)
+        k_attention_keys_tma<HD, 4><<<grid, ATT_THREADS, S4, stream>>>(map, a);
+    else
+        k_attention_keys_tma<HD, 2><<<grid, ATT_THREADS, S2, stream>>>(map, a);
+    return xr_launch_status() == XR_OK ? 1 : XR_ERR_LAUNCH;
+  }
+}
+
 template <int HD>
 static int launch_attention(const AttnMmaArgs& a, int n_seg, int max_seg_len, int max_kv_len, int any_short, int any_long,
-                            cudaStream_t stream) {
+                            const void* cache_base, long long n_pages, cudaStream_t stream) {
     constexpr int LD = HD + 8;
     constexpr int SMEM_ROWS = (ATT_ROWS + 4 * ATT_TILE) * LD * 2;
     constexpr int KEYS_MERGE = 16 * LD * 2 + (4 * 16 * HD + 4 * 16 * 2) * 4;
@@ -498,8 +725,11 @@ static int launch_attention(const AttnMmaArgs& a, int n_seg, int max_seg_len, in
     }
     if (any_short) {
         if (n_seg > 65535 || a.K > 65535) return XR_ERR_ARG;
+        int tma = launch_keys_tma<HD>(a, cache_base, n_pages, n_seg, stream);
+        if (tma < 0) return tma;
         // few CTAs (small batch): deeper stages; many: more CTAs per SM.  The arithmetic is the same.
-        if ((long long)a.max_splits * a.K * n_seg <= 2 * 148)
+        if (tma == 1) {
+        } else if ((long long)a.max_splits * a.K * n_seg <= 2 * 148)
             k_attention_keys<HD, 4><<<dim3(a.max_splits, a.K, n_seg), ATT_THREADS, SMEM_KEYS4, stream>>>(a);
         else
             k_attention_keys<HD, 2><<<dim3(a.max_splits, a.K, n_seg), ATT_THREADS, SMEM_KEYS2, stream>>>(a);
@@ -525,24 +755,25 @@ XR_EXPORT int xr_attention_mma(const void* q, void* out, const void* cache_k, co
                                const int* seg_pos0, const int* block_tables, float* part_acc, float* part_ml,
                                long long q_stride, long long page_stride, long long v_offset, int n_seg, int H, int K,
                                int hd, int max_pages, int page_size, int window, float scale, int max_seg_len,
-                               int max_kv_len, int splits, int any_short, int any_long, cudaStream_t stream) {
+                               int max_kv_len, int splits, int any_short, int any_long, const void* cache_base,
+                               long long n_pages, int n_layers, int layer, int* status, cudaStream_t stream) {
     if (n_seg < 1 || H < 1 || K < 1 || H % K != 0 || hd < 16 || hd > 128 || hd % 16 != 0 || page_size < 1 || window < 0 ||
         (q_stride % 8) != 0 || ((uintptr_t)q & 15) || ((uintptr_t)cache_k & 15) || (page_stride % 8) != 0 || (v_offset % 8) != 0)
         return XR_ERR_ARG;
     if (H / K > 16 && any_short) return XR_ERR_ARG;     // more heads per group than one instruction tile holds
     AttnMmaArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)cache_k, seg_start, seg_len, seg_pos0,
                   block_tables, part_acc, part_ml, q_stride, page_stride, v_offset, H, K, H / K, max_pages, page_size, window,
-                  splits, scale, -1};
+                  splits, scale, -1, n_layers, layer, status};
     if ((page_size & (page_size - 1)) == 0) { int sh = 0; while ((1 << sh) < page_size) sh++; a.page_shift = sh; }
     switch (hd) {
-        case 16: return launch_attention<16>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, stream);
-        case 32: return launch_attention<32>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, stream);
-        case 48: return launch_attention<48>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, stream);
-        case 64: return launch_attention<64>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, stream);
-        case 80: return launch_attention<80>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, stream);
-        case 96: return launch_attention<96>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, stream);
-        case 112: return launch_attention<112>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, stream);
-        case 128: return launch_attention<128>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, stream);
+        case 16: return launch_attention<16>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream);
+        case 32: return launch_attention<32>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream);
+        case 48: return launch_attention<48>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream);
+        case 64: return launch_attention<64>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream);
+        case 80: return launch_attention<80>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream);
+        case 96: return launch_attention<96>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream);
+        case 112: return launch_attention<112>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream);
+        case 128: return launch_attention<128>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream);
     }
     return XR_ERR_ARG;
 }

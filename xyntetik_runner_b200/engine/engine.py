@@ -95,6 +95,11 @@ class StepContext:
         """(pointer to this layer's K block of page 0, elements between pages, elements from K to V)."""
         return self._eng._cache_layer[lay.entry]
 
+    def cache_group(self, lay: LayerRuntime):
+        """(pointer to the whole array of the layer's cache group, its pages, its layers, this layer's index)."""
+        t = self._eng.kv[lay.group]
+        return (t.data_ptr(), t.shape[0], t.shape[1], lay.layer_in_group)
+
 
 class Engine:
     def __init__(self, model_dir: Optional[str] = None, params: Optional[EngineParams] = None, *,

@@ -59,7 +59,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "xr_finish_plain": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _ll, _vp],
         "xr_finish_rope_store": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _vp],
         "xr_attention_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _f,
-                             _i, _i, _i, _i, _i, _vp],
+                             _i, _i, _i, _i, _i, _vp, _ll, _i, _i, _vp, _vp],
         "xr_attention_mma_splits": [_i, _i],
         "xr_sample": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     }
@@ -336,10 +336,13 @@ def attention_mma_splits(max_kv_len: int, window: int) -> int:
 def attention_mma(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, cache_k_ptr: int, seg_start, seg_len, seg_pos0,
                   block_tables, part_acc: Optional[torch.Tensor], part_ml: Optional[torch.Tensor], page_stride: int,
                   v_offset: int, H: int, K: int, hd: int, max_pages: int, page_size: int, window: int, scale: float,
-                  n_seg: int, max_seg_len: int, max_kv_len: int, splits: int, any_short: bool, any_long: bool) -> None:
+                  n_seg: int, max_seg_len: int, max_kv_len: int, splits: int, any_short: bool, any_long: bool,
+                  group: Optional[tuple] = None) -> None:
     """Causal attention over the pages on tensor cores (bfloat16).  Portions with at most 16 packed rows
     (tokens x heads per kv head) go through the key-split kernel and need `part_acc` [n_seg*K*splits*16*hd]
-    and `part_ml` [n_seg*K*splits*32] float32 scratch; longer portions through the row-tiled kernel."""
+    and `part_ml` [n_seg*K*splits*32] float32 scratch; longer portions through the row-tiled kernel.
+    `group` = (pointer to the cache group's array, its pages, its layers, this layer's index) lets the
+    key-split kernel fetch whole page blocks with bulk copies (head sizes 64 and 128, power-of-two pages)."""
     _dev(out, seg_start, seg_len, seg_pos0, block_tables, part_acc, part_ml)
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and out.shape[1] == H * hd
     if any_short:
@@ -349,5 +352,7 @@ def attention_mma(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, cache_k
                                   seg_pos0.data_ptr(), block_tables.data_ptr(), _ptr(part_acc), _ptr(part_ml),
                                   q_row_stride, page_stride, v_offset, n_seg, H, K, hd, max_pages, page_size, window,
                                   float(scale), max_seg_len, max_kv_len, splits, int(any_short), int(any_long),
+                                  group[0] if group else None, group[1] if group else 0, group[2] if group else 1,
+                                  group[3] if group else 0, tc_workspace(out.device)[1].data_ptr() if group else None,
                                   _stream()), "attention_mma")
     _count((1 if any_long else 0) + (2 if any_short else 0))

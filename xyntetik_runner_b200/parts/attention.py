@@ -23,6 +23,8 @@ from .linear import Linear
 
 # XRB200_NO_MMA_ATTENTION=1 sends bfloat16 attention to the float32-arithmetic kernel (for bisecting)
 USE_MMA = os.environ.get("XRB200_NO_MMA_ATTENTION", "0") in ("", "0")
+# XRB200_NO_TMA_ATTENTION=1 keeps the decode kernel on per-thread cp.async gathers
+USE_TMA = os.environ.get("XRB200_NO_TMA_ATTENTION", "0") in ("", "0")
 counters = {"mma": 0, "simt": 0}
 
 
@@ -104,7 +106,7 @@ class GQAAttention(Mixer):
             kernels.attention_mma(qkv, qkv_dim, o, k_ptr, ctx.seg_start, ctx.seg_len, ctx.seg_pos0, bt, pa, pm,
                                   page_stride, v_offset, self.H, self.K, self.hd, ctx.max_pages, ctx.page_size,
                                   self.window or 0, self.scale, ctx.n_seg, int(seg_len.max()), ctx.max_kv_len, splits,
-                                  any_short, any_long)
+                                  any_short, any_long, group=ctx.cache_group(lay) if USE_TMA else None)
             counters["mma"] += 1
         else:
             kernels.attention_simt(qkv, qkv_dim, o, k_ptr, ctx.positions, ctx.tok_seg, bt, page_stride, v_offset,
