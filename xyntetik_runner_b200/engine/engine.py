@@ -155,6 +155,7 @@ class Engine:
         self._pinned_next = 0
         self._slot_generation = np.zeros(p.max_requests, dtype=np.int64)
         self.steps_run = 0
+        self.h2d_bytes = 0               # bytes of step descriptions copied to the device so far
         # CUDA graphs of decode-only steps, keyed by (tokens, wanted rows, context bucket).  A graph holds the
         # addresses of the step's buffers, so any buffer that is made anew invalidates all graphs.
         self._graphs: Dict[tuple, object] = {}
@@ -295,6 +296,7 @@ class Engine:
                 bt[si] = cache.block_table(g, e.request)
         dev = self._buf("step_description", (total,), torch.int32)
         dev.copy_(pinned[:total], non_blocking=True)
+        self.h2d_bytes += total * 4
         if self._pinned_done[slot_i] is None:
             self._pinned_done[slot_i] = torch.cuda.Event()
         self._pinned_done[slot_i].record()

@@ -54,7 +54,6 @@ class Runner:
         reference's -c default, src/model.c:3075).  batch: token budget of a step (-b).  parallel: live
         requests.  max_tokens: tokens the page pool holds (default parallel * ctx)."""
         if engine is None:
-            limit = None
             if model is not None:
                 from ..config import registry
                 _, cfg = registry.load_config(model)
@@ -68,7 +67,8 @@ class Runner:
         self.engine = engine
         self.executor = EngineExecutor(engine)
         self.scheduler = Scheduler(engine.cache, self.executor,
-                                   SchedulerParams(max_step_tokens=batch, prefill_chunk=prefill_chunk),
+                                   SchedulerParams(max_step_tokens=max(batch, engine.params.max_requests),
+                                                   prefill_chunk=prefill_chunk),
                                    open_request=engine._open)
         self._next_id = 0
         self.timing: Dict[str, float] = {}
