@@ -256,6 +256,8 @@ __device__ __forceinline__ void load_q(__nv_bfloat16* qs, const AttnMmaArgs& a, 
 template <int HD>
 __global__ void __launch_bounds__(ATT_THREADS)
 k_attention_rows(AttnMmaArgs a) {
+    xr_pdl_wait();
+    xr_pdl_launch();
     constexpr int LD = HD + 8;
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __nv_bfloat16* qs = (__nv_bfloat16*)smem_raw;                 // [64][LD]
@@ -326,6 +328,8 @@ k_attention_rows(AttnMmaArgs a) {
 template <int HD, int ATT_KSTAGES>
 __global__ void __launch_bounds__(ATT_THREADS)
 k_attention_keys(AttnMmaArgs a) {
+    xr_pdl_wait();
+    xr_pdl_launch();
     constexpr int LD = HD + 8;
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __nv_bfloat16* qs = (__nv_bfloat16*)smem_raw;                 // [16][LD]
@@ -447,6 +451,8 @@ __device__ __forceinline__ bool att_mbar_wait(uint64_t* bar, uint32_t parity) {
 template <int HD, int STAGES>
 __global__ void __launch_bounds__(ATT_THREADS)
 k_attention_keys_tma(const __grid_constant__ CUtensorMap cache_map, AttnMmaArgs a) {
+    xr_pdl_wait();
+    xr_pdl_launch();
     constexpr int LD = HD + 8;
     constexpr int TILE_ELEMS = ATT_TILE * HD;                      // one K (or V) tile, swizzled sub-tiles of 64 columns
     extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -591,6 +597,8 @@ k_attention_keys_tma(const __grid_constant__ CUtensorMap cache_map, AttnMmaArgs 
 template <int HD>
 __global__ void __launch_bounds__(128)
 k_attention_merge(AttnMmaArgs a) {
+    xr_pdl_wait();
+    xr_pdl_launch();
     __shared__ float wgt[16][33];                  // [row][span], up to 32 spans at a time
     const int seg = blockIdx.y, kvh = blockIdx.x;
     const int L = a.seg_len[seg], rows_total = L * a.G;
@@ -692,9 +700,9 @@ static int launch_keys_tma(const AttnMmaArgs& a, const void* cache_base, long lo
     }
     dim3 grid(a.max_splits, a.K, n_seg);
     if ((long long)a.max_splits * a.K * n_seg <= 2 * 148)
-        k_attention_keys_tma<HD, 4><<<grid, ATT_THREADS, S4, stream>>>(map, a);
+        xr_launch((k_attention_keys_tma<HD, 4>), dim3(grid), dim3(ATT_THREADS), S4, stream, map, a);
     else
-        k_attention_keys_tma<HD, 2><<<grid, ATT_THREADS, S2, stream>>>(map, a);
+        xr_launch((k_attention_keys_tma<HD, 2>), dim3(grid), dim3(ATT_THREADS), S2, stream, map, a);
     return xr_launch_status() == XR_OK ? 1 : XR_ERR_LAUNCH;
   }
 }
@@ -719,7 +727,7 @@ static int launch_attention(const AttnMmaArgs& a, int n_seg, int max_seg_len, in
     if (any_long) {
         long long tiles = ((long long)max_seg_len * a.G + ATT_ROWS - 1) / ATT_ROWS;
         if (tiles > 0x7fffffffLL || n_seg > 65535 || a.K > 65535) return XR_ERR_ARG;
-        k_attention_rows<HD><<<dim3((unsigned)tiles, a.K, n_seg), ATT_THREADS, SMEM_ROWS, stream>>>(a);
+        xr_launch((k_attention_rows<HD>), dim3((unsigned)tiles, a.K, n_seg), dim3(ATT_THREADS), SMEM_ROWS, stream, a);
         int rc = xr_launch_status();
         if (rc != XR_OK) return rc;
     }
@@ -730,12 +738,12 @@ static int launch_attention(const AttnMmaArgs& a, int n_seg, int max_seg_len, in
         // few CTAs (small batch): deeper stages; many: more CTAs per SM.  The arithmetic is the same.
         if (tma == 1) {
         } else if ((long long)a.max_splits * a.K * n_seg <= 2 * 148)
-            k_attention_keys<HD, 4><<<dim3(a.max_splits, a.K, n_seg), ATT_THREADS, SMEM_KEYS4, stream>>>(a);
+            xr_launch((k_attention_keys<HD, 4>), dim3(a.max_splits, a.K, n_seg), dim3(ATT_THREADS), SMEM_KEYS4, stream, a);
         else
-            k_attention_keys<HD, 2><<<dim3(a.max_splits, a.K, n_seg), ATT_THREADS, SMEM_KEYS2, stream>>>(a);
+            xr_launch((k_attention_keys<HD, 2>), dim3(a.max_splits, a.K, n_seg), dim3(ATT_THREADS), SMEM_KEYS2, stream, a);
         int rc = xr_launch_status();
         if (rc != XR_OK) return rc;
-        k_attention_merge<HD><<<dim3(a.K, n_seg), 128, 0, stream>>>(a);
+        xr_launch((k_attention_merge<HD>), dim3(a.K, n_seg), dim3(128), 0, stream, a);
         return xr_launch_status();
     }
     return XR_OK;

@@ -18,6 +18,33 @@
 
 #define XR_EXPORT extern "C" __attribute__((visibility("default")))
 
+// Programmatic dependent launch: a kernel launched through xr_launch may be scheduled while the kernel before
+// it in the stream is still in its last wave; it must call xr_pdl_wait() before it touches global memory
+// (the wait returns when the earlier kernel has completed and its writes are visible) and calls
+// xr_pdl_launch() to let the kernel after it start the same way.  Launch latency and block scheduling of
+// back-to-back kernels then overlap instead of adding up.  XRB200_NO_PDL=1 turns the attribute off.
+__device__ __forceinline__ void xr_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void xr_pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#include <stdlib.h>
+static inline bool xr_pdl_enabled() {
+    static int on = -1;
+    if (on < 0) { const char* e = getenv("XRB200_NO_PDL"); on = (e && e[0] && e[0] != '0') ? 0 : 1; }
+    return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline void xr_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = xr_pdl_enabled() ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 static inline int xr_launch_status() {
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? XR_OK : XR_ERR_LAUNCH;

@@ -11,6 +11,8 @@
 template <typename TW>
 __global__ void k_embed(const TW* __restrict__ table, const int* __restrict__ ids, float* __restrict__ x,
                         int d, int vocab) {
+    xr_pdl_wait();
+    xr_pdl_launch();
     int t = blockIdx.x;
     int id = ids[t];
     if (id < 0 || id >= vocab) id = 0;
@@ -22,8 +24,8 @@ __global__ void k_embed(const TW* __restrict__ table, const int* __restrict__ id
 XR_EXPORT int xr_embed(const void* table, int table_dtype, const int* ids, float* x, int n, int d, int vocab,
                        cudaStream_t stream) {
     if (n < 1 || d < 1 || vocab < 1) return XR_ERR_ARG;
-    if (table_dtype == XR_F32) k_embed<float><<<n, 256, 0, stream>>>((const float*)table, ids, x, d, vocab);
-    else if (table_dtype == XR_BF16) k_embed<__nv_bfloat16><<<n, 256, 0, stream>>>((const __nv_bfloat16*)table, ids, x, d, vocab);
+    if (table_dtype == XR_F32) xr_launch((k_embed<float>), dim3(n), dim3(256), 0, stream, (const float*)table, ids, x, d, vocab);
+    else if (table_dtype == XR_BF16) xr_launch((k_embed<__nv_bfloat16>), dim3(n), dim3(256), 0, stream, (const __nv_bfloat16*)table, ids, x, d, vocab);
     else return XR_ERR_ARG;
     return xr_launch_status();
 }
@@ -37,6 +39,8 @@ XR_EXPORT int xr_embed(const void* table, int table_dtype, const int* ids, float
 template <typename TO>
 __global__ void k_rmsnorm(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ w,
                           TO* __restrict__ out, int d, float eps) {
+    xr_pdl_wait();
+    xr_pdl_launch();
     __shared__ float scratch[33];
     int r = rows ? rows[blockIdx.x] : blockIdx.x;
     const float* xr = x + (size_t)r * d;
@@ -52,8 +56,8 @@ XR_EXPORT int xr_rmsnorm(const float* x, const int* rows, const float* w, void* 
                          float eps, cudaStream_t stream) {
     if (n < 1 || d < 1) return XR_ERR_ARG;
     int threads = d >= 2048 ? 512 : 256;
-    if (out_dtype == XR_F32) k_rmsnorm<float><<<n, threads, 0, stream>>>(x, rows, w, (float*)out, d, eps);
-    else if (out_dtype == XR_BF16) k_rmsnorm<__nv_bfloat16><<<n, threads, 0, stream>>>(x, rows, w, (__nv_bfloat16*)out, d, eps);
+    if (out_dtype == XR_F32) xr_launch((k_rmsnorm<float>), dim3(n), dim3(threads), 0, stream, x, rows, w, (float*)out, d, eps);
+    else if (out_dtype == XR_BF16) xr_launch((k_rmsnorm<__nv_bfloat16>), dim3(n), dim3(threads), 0, stream, x, rows, w, (__nv_bfloat16*)out, d, eps);
     else return XR_ERR_ARG;
     return xr_launch_status();
 }
@@ -84,6 +88,8 @@ struct RopeStoreArgs {
 
 template <typename T>
 __global__ void k_rope_store(RopeStoreArgs a) {
+    xr_pdl_wait();
+    xr_pdl_launch();
     int t = blockIdx.x, head = blockIdx.y;
     int qkv_dim = (a.H + 2 * a.K) * a.hd;
     T* row = (T*)a.qkv + (size_t)t * qkv_dim + (size_t)head * a.hd;
@@ -127,8 +133,8 @@ XR_EXPORT int xr_rope_store(void* qkv, int dtype, const int* positions, const in
                     n, H, K, hd, rotary_dim, max_pages, page_size};
     dim3 grid(n, H + 2 * K);
     int threads = hd >= 128 ? 128 : (hd >= 64 ? 64 : 32);
-    if (dtype == XR_F32) k_rope_store<float><<<grid, threads, 0, stream>>>(a);
-    else if (dtype == XR_BF16) k_rope_store<__nv_bfloat16><<<grid, threads, 0, stream>>>(a);
+    if (dtype == XR_F32) xr_launch((k_rope_store<float>), dim3(grid), dim3(threads), 0, stream, a);
+    else if (dtype == XR_BF16) xr_launch((k_rope_store<__nv_bfloat16>), dim3(grid), dim3(threads), 0, stream, a);
     else return XR_ERR_ARG;
     return xr_launch_status();
 }
@@ -140,6 +146,8 @@ XR_EXPORT int xr_rope_store(void* qkv, int dtype, const int* positions, const in
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void k_silu_mul(const T* __restrict__ gu, T* __restrict__ h, int n, int F) {
+    xr_pdl_wait();
+    xr_pdl_launch();
     size_t total = (size_t)n * F;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         size_t t = i / F, f = i % F;
@@ -153,8 +161,8 @@ XR_EXPORT int xr_silu_mul(const void* gu, void* h, int dtype, int n, int F, cuda
     if (n < 1 || F < 1) return XR_ERR_ARG;
     size_t total = (size_t)n * F;
     int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-    if (dtype == XR_F32) k_silu_mul<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)h, n, F);
-    else if (dtype == XR_BF16) k_silu_mul<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)h, n, F);
+    if (dtype == XR_F32) xr_launch((k_silu_mul<float>), dim3(blocks), dim3(256), 0, stream, (const float*)gu, (float*)h, n, F);
+    else if (dtype == XR_BF16) xr_launch((k_silu_mul<__nv_bfloat16>), dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)h, n, F);
     else return XR_ERR_ARG;
     return xr_launch_status();
 }
@@ -165,6 +173,8 @@ XR_EXPORT int xr_silu_mul(const void* gu, void* h, int dtype, int n, int F, cuda
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void k_residual_add(float* __restrict__ x, const T* __restrict__ dlt, size_t total) {
+    xr_pdl_wait();
+    xr_pdl_launch();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
         x[i] += xr_to_f32<T>(dlt[i]);
 }
@@ -173,8 +183,8 @@ XR_EXPORT int xr_residual_add(float* x, const void* dlt, int dtype, int n, int d
     if (n < 1 || d < 1) return XR_ERR_ARG;
     size_t total = (size_t)n * d;
     int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-    if (dtype == XR_F32) k_residual_add<float><<<blocks, 256, 0, stream>>>(x, (const float*)dlt, total);
-    else if (dtype == XR_BF16) k_residual_add<__nv_bfloat16><<<blocks, 256, 0, stream>>>(x, (const __nv_bfloat16*)dlt, total);
+    if (dtype == XR_F32) xr_launch((k_residual_add<float>), dim3(blocks), dim3(256), 0, stream, x, (const float*)dlt, total);
+    else if (dtype == XR_BF16) xr_launch((k_residual_add<__nv_bfloat16>), dim3(blocks), dim3(256), 0, stream, x, (const __nv_bfloat16*)dlt, total);
     else return XR_ERR_ARG;
     return xr_launch_status();
 }

@@ -10,6 +10,8 @@
 template <typename TO>
 __global__ void k_finish_add_rmsnorm(const float* __restrict__ partial, int splits, int n, const float* __restrict__ bias,
                                      float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out, int d, float eps) {
+    xr_pdl_wait();
+    xr_pdl_launch();
     __shared__ float scratch[33];
     extern __shared__ float row[];             // the new residual row, kept for the second pass
     int t = blockIdx.x;
@@ -37,10 +39,10 @@ XR_EXPORT int xr_finish_add_rmsnorm(const float* partial, int splits, const floa
     size_t smem = (size_t)d * 4;
     if (out_dtype == XR_F32) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(k_finish_add_rmsnorm<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        k_finish_add_rmsnorm<float><<<n, threads, smem, stream>>>(partial, splits, n, bias, x, w, (float*)out, d, eps);
+        xr_launch((k_finish_add_rmsnorm<float>), dim3(n), dim3(threads), smem, stream, partial, splits, n, bias, x, w, (float*)out, d, eps);
     } else if (out_dtype == XR_BF16) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(k_finish_add_rmsnorm<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        k_finish_add_rmsnorm<__nv_bfloat16><<<n, threads, smem, stream>>>(partial, splits, n, bias, x, w, (__nv_bfloat16*)out, d, eps);
+        xr_launch((k_finish_add_rmsnorm<__nv_bfloat16>), dim3(n), dim3(threads), smem, stream, partial, splits, n, bias, x, w, (__nv_bfloat16*)out, d, eps);
     } else {
         return XR_ERR_ARG;
     }
@@ -51,6 +53,8 @@ XR_EXPORT int xr_finish_add_rmsnorm(const float* partial, int splits, const floa
 template <typename TO, bool ACCUM>
 __global__ void k_finish_plain(const float* __restrict__ partial, int splits, int n, int width, const float* __restrict__ bias,
                                TO* __restrict__ out, long long ldo) {
+    xr_pdl_wait();
+    xr_pdl_launch();
     size_t total = (size_t)n * width;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         size_t t = i / width, r = i % width;
@@ -70,11 +74,11 @@ XR_EXPORT int xr_finish_plain(const float* partial, int splits, const float* bia
     int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
     if (accumulate) {
         if (out_dtype != XR_F32) return XR_ERR_ARG;
-        k_finish_plain<float, true><<<blocks, 256, 0, stream>>>(partial, splits, n, width, bias, (float*)out, ldo);
+        xr_launch((k_finish_plain<float, true>), dim3(blocks), dim3(256), 0, stream, partial, splits, n, width, bias, (float*)out, ldo);
     } else if (out_dtype == XR_F32) {
-        k_finish_plain<float, false><<<blocks, 256, 0, stream>>>(partial, splits, n, width, bias, (float*)out, ldo);
+        xr_launch((k_finish_plain<float, false>), dim3(blocks), dim3(256), 0, stream, partial, splits, n, width, bias, (float*)out, ldo);
     } else if (out_dtype == XR_BF16) {
-        k_finish_plain<__nv_bfloat16, false><<<blocks, 256, 0, stream>>>(partial, splits, n, width, bias, (__nv_bfloat16*)out, ldo);
+        xr_launch((k_finish_plain<__nv_bfloat16, false>), dim3(blocks), dim3(256), 0, stream, partial, splits, n, width, bias, (__nv_bfloat16*)out, ldo);
     } else {
         return XR_ERR_ARG;
     }
@@ -91,6 +95,8 @@ struct FinishRopeArgs {
 };
 
 __global__ void k_finish_rope_store(FinishRopeArgs a) {
+    xr_pdl_wait();
+    xr_pdl_launch();
     int t = blockIdx.x, head = blockIdx.y;
     int qkv_dim = (a.H + 2 * a.K) * a.hd;
     int col0 = head * a.hd;
@@ -137,6 +143,6 @@ XR_EXPORT int xr_finish_rope_store(const float* partial, int splits, const float
     FinishRopeArgs a{partial, splits, bias, (__nv_bfloat16*)qkv, positions, tok_seg, block_tables, inv_freq,
                      (__nv_bfloat16*)cache_k, page_stride, v_offset, n, H, K, hd, rotary_dim, max_pages, page_size};
     int threads = hd >= 128 ? 128 : (hd >= 64 ? 64 : 32);
-    k_finish_rope_store<<<dim3(n, H + 2 * K), threads, 0, stream>>>(a);
+    xr_launch(k_finish_rope_store, dim3(n, H + 2 * K), dim3(threads), 0, stream, a);
     return xr_launch_status();
 }

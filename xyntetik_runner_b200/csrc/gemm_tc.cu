@@ -168,6 +168,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // everything above touched no global memory; from here on the kernel before this one must be complete
+    xr_pdl_wait();
+    xr_pdl_launch();
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -291,6 +294,8 @@ struct FinishParams {
 };
 
 __global__ void k_splitk_finish(FinishParams p) {
+    xr_pdl_wait();
+    xr_pdl_launch();
     size_t total = (size_t)p.n * p.n_out;
     size_t width = p.dual ? 2 * (size_t)p.n_out : (size_t)p.n_out;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
@@ -353,7 +358,7 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParam
             return XR_ERR_LAUNCH;
         configured = true;
     }
-    k_gemm_tc<BN, STAGES, DUAL, MINB><<<grid, TC_THREADS, SMEM, stream>>>(mw, mx, p);
+    xr_launch((k_gemm_tc<BN, STAGES, DUAL, MINB>), dim3(grid), dim3(TC_THREADS), SMEM, stream, mw, mx, p);
     return xr_launch_status();
 }
 
@@ -442,7 +447,7 @@ XR_EXPORT int xr_gemm_tc(const void* X, const void* W, const float* bias, void* 
     FinishParams f{scratch, out, bias, ldo, n, n_out, splits, epilogue, out_dtype, dual ? 1 : 0};
     size_t total = (size_t)n * n_out;
     int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
-    k_splitk_finish<<<blocks, 256, 0, stream>>>(f);
+    xr_launch(k_splitk_finish, dim3(blocks), dim3(256), 0, stream, f);
     return xr_launch_status();
 }
 

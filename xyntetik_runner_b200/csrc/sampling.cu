@@ -109,6 +109,8 @@ __device__ int nth_equal_id(int V, const float* vals, unsigned thr, long long n,
 
 __global__ void __launch_bounds__(SMP_THREADS)
 k_sample(SampleArgs a, float* scratch /* [rows, V] scaled values, or null when nothing needs them */) {
+    xr_pdl_wait();
+    xr_pdl_launch();
     __shared__ double sh[40 + SMP_THREADS];
     __shared__ float sh_f[33];
     __shared__ int sh_i[33];
@@ -319,6 +321,6 @@ XR_EXPORT int xr_sample(const float* logits, long long ld, int rows, int V, cons
                         const int* recent, float* scratch, int* out, cudaStream_t stream) {
     if (rows < 1 || V < 1 || ld < V) return XR_ERR_ARG;
     SampleArgs a{logits, ld, V, temp, top_k, top_p, min_p, penalty, draw, recent, out};
-    k_sample<<<rows, SMP_THREADS, 0, stream>>>(a, scratch);
+    xr_launch(k_sample, dim3(rows), dim3(SMP_THREADS), 0, stream, a, scratch);
     return xr_launch_status();
 }
