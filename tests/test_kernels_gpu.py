@@ -360,6 +360,7 @@ def test_gemm_tc_packed_layout(n, n_out, k):
     x = torch.randn(n, k, generator=g).to(torch.bfloat16).to(DEV)
     w = (torch.randn(n_out, k, generator=g) / math.sqrt(k)).to(torch.bfloat16).to(DEV)
     packed = kernels.pack_weight(w)
+    torch.cuda.synchronize()        # the product may read W before the kernel ahead of it has ended: W must be at rest
     for splits in (1, 2):
         a = torch.empty(n, n_out, dtype=torch.float32, device=DEV)
         b = torch.empty(n, n_out, dtype=torch.float32, device=DEV)
@@ -372,6 +373,8 @@ def test_gemm_tc_packed_layout(n, n_out, k):
     a = torch.empty(n, F, dtype=torch.bfloat16, device=DEV)
     b = torch.empty(n, F, dtype=torch.bfloat16, device=DEV)
     kernels.gemm_tc(x, w2, a, None, kernels.EPI_SWIGLU)
-    kernels.gemm_tc(x, kernels.pack_weight(w2, halves=2), b, None, kernels.EPI_SWIGLU, packed_rows=F)
+    p2 = kernels.pack_weight(w2, halves=2)
+    torch.cuda.synchronize()
+    kernels.gemm_tc(x, p2, b, None, kernels.EPI_SWIGLU, packed_rows=F)
     assert torch.equal(a, b)
     kernels.tc_check_status(torch.device(DEV))

@@ -166,6 +166,7 @@ class Engine:
         self._graph_launches: Dict[tuple, int] = {}
         # the step description's device buffer is made once for the largest step the parameters name
         T, S = p.max_step_tokens, p.max_requests
+        torch.cuda.synchronize(self.device)       # weights are at rest before the first product reads them
         self._buf("step_description", (4 * (T + 4) + 4 * (S + 4) + len(self.cache.groups) * (S * self.cache.max_pages_per_request + 4),),
                   torch.int32)
 
