@@ -378,3 +378,39 @@ def test_gemm_tc_packed_layout(n, n_out, k):
     kernels.gemm_tc(x, p2, b, None, kernels.EPI_SWIGLU, packed_rows=F)
     assert torch.equal(a, b)
     kernels.tc_check_status(torch.device(DEV))
+
+
+TC_ATT_CASES = [
+    # H, K, page, window, segments (pos0, length)
+    (32, 8, 64, 0, [(0, 200), (0, 33), (300, 70)]),
+    (8, 2, 16, 0, [(0, 129), (500, 40), (127, 5)]),
+    (4, 4, 8, 0, [(0, 300)]),
+    (16, 1, 128, 0, [(1000, 24), (0, 9)]),
+    (8, 4, 32, 100, [(0, 260), (400, 64)]),
+]
+
+
+@pytest.mark.parametrize("case_id", range(len(TC_ATT_CASES)))
+def test_attention_tc(case_id):
+    """Prompt attention on tcgen05 against the float64 computation (head size 128)."""
+    from xyntetik_runner_b200 import kernels
+    H, K, page, window, segs = TC_ATT_CASES[case_id]
+    hd = 128
+    assert kernels.attention_tc_supported(torch.bfloat16, H, K, hd, page)
+    c = _paged_case(100 + case_id, H, K, hd, page, segs, torch.bfloat16, window)
+    out = torch.full((c["n"], H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    cache = c["cache"]
+    kernels.attention_tc(c["qkv"], out, c["starts"], c["lens"], c["pos0"], c["bt"], (cache.data_ptr(), cache.shape[0], cache.shape[1], 0),
+                         H, K, hd, c["max_pages"], page, window, c["scale"], c["n_seg"], int(c["lens_host"].max()))
+    kernels.tc_check_status(torch.device(DEV))
+    got, ref = out.cpu().double(), c["ref"]
+    G = H // K
+    # portions with at most 16 packed rows belong to the decode kernel: this kernel leaves them untouched
+    row = 0
+    for (p0, L) in segs:
+        if L * G <= 16:
+            assert torch.isnan(got[row:row + L]).all()
+        else:
+            err = (got[row:row + L] - ref[row:row + L]).abs().max(dim=1).values / ref.abs().max()
+            assert float(err.max()) <= 1.2e-2, (p0, L, torch.topk(err, min(5, L)).indices.tolist(), float(err.max()))
+        row += L

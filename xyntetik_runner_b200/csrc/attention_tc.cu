@@ -1,0 +1,422 @@
+// Causal grouped-query attention of prompt portions on the 5th-generation tensor cores (tcgen05), over the
+// paged cache: S = Q K^T and O += P V as tcgen05.mma with S and O in tensor memory, Q, K, V brought to shared
+// memory by TMA (128-byte swizzle; K and V straight from the pages), softmax in float32 by the thread that
+// owns the row.  Same arithmetic as the row-tiled mma.sync kernel (attention_mma.cu), which stays as the
+// path for the shapes this one does not take.  Needs bfloat16, head size 128, heads per kv head dividing
+// 128, a power-of-two page size >= 8.
+//
+// A CTA owns 128 packed rows (token i / G, head i % G) of one (request, kv head) and walks its keys in tiles
+// of 128, in ascending order.  Roles (192 threads):
+//   warps 0..3 : softmax.  Thread r owns row r = tensor-memory lane r.  Per tile: read S, running maximum,
+//                rescale O in tensor memory when the maximum moved, write P = exp(S - m) as bfloat16 into
+//                shared memory in the layout the matrix instruction reads (K-major, 128-byte swizzle).
+//   warp 4     : one lane issues the TMA copies (Q once, then K and V tiles through a two-stage ring).
+//   warp 5     : one lane issues the matrix instructions; the warp owns the tensor-memory allocation.
+// S is double buffered (S of tile j+1 is computed while the softmax of tile j runs); O is one accumulator.
+// V is the B operand of P V with N = head size contiguous in memory (an "MN-major" operand): its shared
+// memory descriptor has leading byte offset = distance between the two 64-column halves and stride byte
+// offset = 8 keys.
+//
+// Every wait is bounded; a wait that runs out is recorded in the status word and the CTA runs on (its
+// output is then meaningless) so that all its threads still meet at the barriers and tensor memory is freed.
+//
+// The reference computes prompt attention with one block per (head, token) and a global score scratch
+// (`k_attn`, src/kernels.cu:2043-2141); formulas src/model.c:3548-3589, 3409-3415.
+#include "common.cuh"
+#include <cuda.h>
+#include <math.h>
+
+#define TA_ROWS 128
+#define TA_KEYS 128
+#define TA_HD 128
+#define TA_THREADS 192
+#define TA_SPIN (1u << 24)
+
+struct AttnTcArgs {
+    __nv_bfloat16* out;          // [n, H * hd]
+    const int* seg_start; const int* seg_len; const int* seg_pos0; const int* block_tables;
+    int* status;
+    int H, K, G, max_pages, page_size, page_shift, window, n_layers, layer;
+    float scale_log2;            // scale * log2(e)
+};
+
+__device__ __forceinline__ uint32_t ta_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void ta_bar_init(uint64_t* b, uint32_t n) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(ta_smem(b)), "r"(n)); }
+__device__ __forceinline__ void ta_expect(uint64_t* b, uint32_t bytes) { asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(ta_smem(b)), "r"(bytes) : "memory"); }
+__device__ __forceinline__ void ta_arrive(uint64_t* b) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(ta_smem(b)) : "memory"); }
+__device__ __forceinline__ void ta_wait(uint64_t* b, uint32_t parity, volatile int* gave_up) {
+    for (uint32_t i = 0; i < TA_SPIN; i++) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(ta_smem(b)), "r"(parity) : "memory");
+        if (ok) return;
+        if ((i & 4095u) == 4095u && *gave_up) return;
+    }
+    *gave_up = 1;
+}
+__device__ __forceinline__ void ta_tma_2d(void* dst, const CUtensorMap* m, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(ta_smem(dst)), "l"(m), "r"(x), "r"(y), "r"(ta_smem(bar)) : "memory");
+}
+__device__ __forceinline__ void ta_tma_3d(void* dst, const CUtensorMap* m, int x, int y, int z, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(ta_smem(dst)), "l"(m), "r"(x), "r"(y), "r"(z), "r"(ta_smem(bar)) : "memory");
+}
+__device__ __forceinline__ void ta_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(ta_smem(bar)) : "memory");
+}
+__device__ __forceinline__ void ta_mma(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void ta_ld32(uint32_t taddr, float* v) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void ta_st32(uint32_t taddr, const float* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+          "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+          "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+          "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+          "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+          "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+          "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+          "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+        : "memory");
+}
+__device__ __forceinline__ float ta_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// K-major operand (rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart)
+__device__ __forceinline__ uint64_t ta_desc_k(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// MN-major operand: 64 contiguous N elements per 128-byte row, rows are K (keys), 8-key groups 1024 bytes
+// apart (stride byte offset), the next 64 N elements `lbo` bytes on (leading byte offset)
+__device__ __forceinline__ uint64_t ta_desc_mn(uint32_t saddr, uint32_t lbo) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// instruction descriptor: float32 accumulate, bfloat16 A and B, M = 128, N = 128; b_mn: B is MN-major
+__host__ __device__ constexpr uint32_t ta_idesc(bool b_mn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+
+__global__ void __launch_bounds__(TA_THREADS, 1)
+k_attention_tc(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map, AttnTcArgs a) {
+    extern __shared__ __align__(16) uint8_t ta_smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)ta_smem_raw + 1023) & ~(uintptr_t)1023);
+    constexpr int HALF = TA_ROWS * 128;                   // bytes of one [128 rows][64 columns] half tile
+    uint8_t* q_s = smem;                                  // [2 halves][128 rows][128 B]
+    uint8_t* p_s = q_s + 2 * HALF;                        // [2 halves (keys 0-63, 64-127)][128 rows][128 B]
+    uint8_t* k_s = p_s + 2 * HALF;                        // [2 stages][2 halves (hd)][128 keys][128 B]
+    uint8_t* v_s = k_s + 4 * HALF;                        // [2 stages][2 halves (hd)][128 keys][128 B]
+    uint64_t* bars = (uint64_t*)(v_s + 4 * HALF);
+    uint64_t* q_full = bars;            // 1
+    uint64_t* k_full = bars + 1;        // 2
+    uint64_t* v_full = bars + 3;        // 2
+    uint64_t* kv_empty = bars + 5;      // 2
+    uint64_t* s_full = bars + 7;        // 2
+    uint64_t* p_full = bars + 9;        // 1  (count 128)
+    uint64_t* pv_done = bars + 10;      // 1
+    uint32_t* tmem_slot = (uint32_t*)(bars + 11);
+    volatile int* gave_up = (volatile int*)(tmem_slot + 1);
+
+    const int seg = blockIdx.z, kvh = blockIdx.y;
+    const int L = a.seg_len[seg], rows_total = L * a.G;
+    const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;          // tiles with the most keys start first
+    const int row0 = tile * TA_ROWS;
+    if (rows_total <= 16 || row0 >= rows_total) return;             // short portions belong to the key-split kernel
+    xr_pdl_wait();
+    xr_pdl_launch();
+    const int pos0 = a.seg_pos0[seg], tok_base = a.seg_start[seg];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int last_row = min(rows_total, row0 + TA_ROWS) - 1;
+    const int hi = pos0 + last_row / a.G;
+    const int lo = a.window > 0 ? max(0, pos0 + row0 / a.G - a.window + 1) : 0;
+    const int t_lo = lo / TA_KEYS, t_hi = hi / TA_KEYS, n_tiles = t_hi - t_lo + 1;
+
+    if (threadIdx.x == 0) {
+        ta_bar_init(q_full, 1);
+        for (int i = 0; i < 2; i++) { ta_bar_init(&k_full[i], 1); ta_bar_init(&v_full[i], 1); ta_bar_init(&kv_empty[i], 1); ta_bar_init(&s_full[i], 1); }
+        ta_bar_init(p_full, 128);
+        ta_bar_init(pv_done, 1);
+        *gave_up = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ta_smem(tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tm_s0 = tmem, tm_s1 = tmem + 128, tm_o = tmem + 256;
+
+    if (warp == 4) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            ta_expect(q_full, 2 * HALF);
+            int tok0 = tok_base + row0 / a.G;
+            for (int c = 0; c < 2; c++) ta_tma_3d(q_s + c * HALF, &q_map, c * 64, kvh * a.G, tok0, q_full);
+            const int box_rows = a.page_size < 64 ? a.page_size : 64;
+            for (int j = 0; j < n_tiles; j++) {
+                int s = j & 1;
+                if (j >= 2) ta_wait(&kv_empty[s], ((j >> 1) - 1) & 1, gave_up);
+                ta_expect(&k_full[s], 2 * HALF);
+                ta_expect(&v_full[s], 2 * HALF);
+                int key0 = (t_lo + j) * TA_KEYS;
+                for (int r0 = 0; r0 < TA_KEYS; r0 += box_rows) {
+                    int kp = key0 + r0;
+                    int pi = kp >> a.page_shift;
+                    int page = pi < a.max_pages ? a.block_tables[(size_t)seg * a.max_pages + pi] : -1;
+                    long long rowk = ((((long long)page * a.n_layers + a.layer) * 2) * a.K + kvh) * a.page_size + (kp & (a.page_size - 1));
+                    long long rowv = rowk + (long long)a.K * a.page_size;
+                    if (page < 0) { rowk = -1024; rowv = -1024; }          // outside the tensor: the copy fills zeros
+                    for (int c = 0; c < 2; c++) {
+                        ta_tma_2d(k_s + (s * 2 + c) * HALF + r0 * 128, &kv_map, c * 64, (int)rowk, &k_full[s]);
+                        ta_tma_2d(v_s + (s * 2 + c) * HALF + r0 * 128, &kv_map, c * 64, (int)rowv, &v_full[s]);
+                    }
+                }
+            }
+        }
+    } else if (warp == 5) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            constexpr uint32_t id_qk = ta_idesc(false), id_pv = ta_idesc(true);
+            auto issue_qk = [&](int j) {
+                int s = j & 1;
+                ta_wait(&k_full[s], (j >> 1) & 1, gave_up);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                uint32_t qa = ta_smem(q_s), kb = ta_smem(k_s + s * 2 * HALF);
+#pragma unroll
+                for (int kk = 0; kk < TA_HD / 16; kk++) {
+                    uint32_t off = (kk >> 2) * HALF + (kk & 3) * 32;
+                    ta_mma((j & 1) ? tm_s1 : tm_s0, ta_desc_k(qa + off), ta_desc_k(kb + off), id_qk, kk > 0 ? 1u : 0u);
+                }
+                ta_commit(&s_full[j & 1]);
+            };
+            ta_wait(q_full, 0, gave_up);
+            issue_qk(0);
+            for (int j = 0; j < n_tiles; j++) {
+                int s = j & 1;
+                // S of the next tile while the softmax of this one runs: its buffer was released by p_full(j-1),
+                // which this thread waited for in the previous round
+                if (j + 1 < n_tiles) issue_qk(j + 1);
+                ta_wait(p_full, j & 1, gave_up);                    // P(j) is in shared memory, S(j) has been read
+                ta_wait(&v_full[s], (j >> 1) & 1, gave_up);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                uint32_t pa = ta_smem(p_s), vb = ta_smem(v_s + s * 2 * HALF);
+#pragma unroll
+                for (int kk = 0; kk < TA_KEYS / 16; kk++) {
+                    uint64_t ad = ta_desc_k(pa + (kk >> 2) * HALF + (kk & 3) * 32);
+                    uint64_t bd = ta_desc_mn(vb + kk * 16 * 128, HALF);
+                    ta_mma(tm_o, ad, bd, id_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                }
+                ta_commit(&kv_empty[s]);
+                ta_commit(pv_done);
+            }
+        }
+    } else {
+        // ---------------- softmax: thread = row = tensor-memory lane ----------------
+        const int r = threadIdx.x;                               // 0..127
+        const int pr = row0 + r;
+        const int pos = pr < rows_total ? pos0 + pr / a.G : -1;
+        const int lo_r = a.window > 0 ? pos - a.window + 1 : 0;
+        const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+        float m = -INFINITY, l = 0.f;
+        for (int j = 0; j < n_tiles; j++) {
+            const uint32_t tm_s = ((j & 1) ? tm_s1 : tm_s0) + lane_off;
+            const int key0 = (t_lo + j) * TA_KEYS;
+            ta_wait(&s_full[j & 1], (j >> 1) & 1, gave_up);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            float v[32];
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {
+                ta_ld32(tm_s + c * 32, v);
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    int kp = key0 + c * 32 + i;
+                    if (kp <= pos && kp >= lo_r) mx = fmaxf(mx, v[i]);
+                }
+            }
+            float m_new = fmaxf(m, mx * a.scale_log2);           // maxima are kept in the log2 domain
+            float off = m_new == -INFINITY ? 0.f : m_new;
+            // O and the P buffer are in use by the product of the previous tile until it completes
+            if (j > 0) ta_wait(pv_done, (j - 1) & 1, gave_up);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // the loads and stores of tensor memory are warp-wide: a warp rescales if any of its rows moved
+            float corr = (j > 0 && m_new != m) ? ta_exp2(m - off) : 1.0f;      // m = -inf -> 0
+            if (__any_sync(0xffffffffu, corr != 1.0f)) {
+                l *= corr;
+#pragma unroll 1
+                for (int c = 0; c < 4; c++) {
+                    ta_ld32(tm_o + lane_off + c * 32, v);
+#pragma unroll
+                    for (int i = 0; i < 32; i++) v[i] *= corr;
+                    ta_st32(tm_o + lane_off + c * 32, v);
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            }
+            m = m_new;
+            float sum = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {
+                ta_ld32(tm_s + c * 32, v);
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    int kp = key0 + c * 32 + i;
+                    float p0 = (kp <= pos && kp >= lo_r) ? ta_exp2(v[i] * a.scale_log2 - off) : 0.f;
+                    float p1 = (kp + 1 <= pos && kp + 1 >= lo_r) ? ta_exp2(v[i + 1] * a.scale_log2 - off) : 0.f;
+                    sum += p0 + p1;
+                    __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
+                    pk[i >> 1] = *reinterpret_cast<uint32_t*>(&b);
+                }
+                // keys c*32 .. c*32+31 of row r: four 16-byte chunks of the half tile (c >> 1), swizzled by the row
+                uint8_t* rowp = p_s + (c >> 1) * HALF + r * 128;
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    int chunk = (c & 1) * 4 + q;
+                    *reinterpret_cast<uint4*>(rowp + ((chunk ^ (r & 7)) << 4)) = make_uint4(pk[q * 4], pk[q * 4 + 1], pk[q * 4 + 2], pk[q * 4 + 3]);
+                }
+            }
+            l += sum;
+            if (key0 + TA_KEYS - 1 > hi) {
+                // The tile runs past the last key.  Probabilities there are zero, but the value rows hold whatever the
+                // page held before; clear them so that zero times those bytes is zero whatever they are.
+                int s = j & 1;
+                ta_wait(&v_full[s], (j >> 1) & 1, gave_up);
+                int first_bad = hi + 1 - key0;
+                for (int e = r; e < (TA_KEYS - first_bad) * 16; e += 128) {
+                    int row = first_bad + (e >> 4), ch = e & 15;
+                    *reinterpret_cast<uint4*>(v_s + (s * 2 + (ch >> 3)) * HALF + row * 128 + (((ch & 7) ^ (row & 7)) << 4)) = make_uint4(0, 0, 0, 0);
+                }
+            }
+            // make P (and the cleared rows) visible to the tensor core (async proxy), order the tensor-memory reads, then signal
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            ta_arrive(p_full);
+        }
+        ta_wait(pv_done, (n_tiles - 1) & 1, gave_up);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        {
+            const bool live = pr < rows_total;
+            float inv = live ? 1.0f / l : 0.f;
+            __nv_bfloat16* dst = a.out + ((long long)(tok_base + (live ? pr : 0) / a.G) * a.H + (kvh * a.G + (live ? pr : 0) % a.G)) * TA_HD;
+            float v[32];
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {
+                ta_ld32(tm_o + lane_off + c * 32, v);            // warp-wide: rows past the portion load too
+                if (!live) continue;
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        __nv_bfloat162 b = __floats2bfloat162_rn(v[i + 2 * e] * inv, v[i + 2 * e + 1] * inv);
+                        w[e] = *reinterpret_cast<uint32_t*>(&b);
+                    }
+                    *reinterpret_cast<uint4*>(dst + c * 32 + i) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 5) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+    }
+    if (threadIdx.x == 0 && *gave_up) atomicExch(a.status, 3);
+}
+
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*TaEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static TaEncodeFn ta_encode() {
+    static TaEncodeFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (TaEncodeFn)ptr;
+    }
+    return fn;
+}
+
+// 1 if this kernel takes the shape, 0 if not (the caller then uses the mma.sync kernel).
+XR_EXPORT int xr_attention_tc_supported(int H, int K, int hd, int page_size) {
+    if (hd != TA_HD || K < 1 || H % K != 0) return 0;
+    int G = H / K;
+    if (G > 128 || (128 % G) != 0) return 0;
+    if (page_size < 8 || (page_size & (page_size - 1)) != 0) return 0;
+    return 1;
+}
+
+// q: the step's fused rows [n, (H + 2K) * hd] (Q heads first), out: [n, H * hd].  cache_base: the cache group's
+// whole array [pages][layers][K|V][kv heads][page_size][hd].  Handles the portions with more than 16 packed rows.
+XR_EXPORT int xr_attention_tc(const void* q, void* out, const void* cache_base, const int* seg_start, const int* seg_len,
+                              const int* seg_pos0, const int* block_tables, int* status, long long q_row_stride, int n,
+                              int n_seg, int H, int K, int hd, int max_pages, int page_size, int window, float scale,
+                              int max_seg_len, long long n_pages, int n_layers, int layer, cudaStream_t stream) {
+    if (!xr_attention_tc_supported(H, K, hd, page_size) || n < 1 || n_seg < 1 || window < 0 || status == nullptr) return XR_ERR_ARG;
+    if (((uintptr_t)q & 15) || ((uintptr_t)cache_base & 15) || (q_row_stride % 8) != 0) return XR_ERR_ARG;
+    const int G = H / K;
+    long long total_rows = n_pages * n_layers * 2 * K * page_size;
+    if (total_rows >= (1LL << 31) || n_seg > 65535 || K > 65535) return XR_ERR_ARG;
+    TaEncodeFn enc = ta_encode();
+    if (!enc) return -3;
+    CUtensorMap qm, kvm;
+    {
+        // Q as [token][head][hd]; a box is 64 columns x G heads x (128 / G) tokens = 128 packed rows
+        cuuint64_t dims[3] = {(cuuint64_t)hd, (cuuint64_t)H, (cuuint64_t)n};
+        cuuint64_t strides[2] = {(cuuint64_t)hd * 2, (cuuint64_t)q_row_stride * 2};
+        cuuint32_t box[3] = {64, (cuuint32_t)G, (cuuint32_t)(TA_ROWS / G)};
+        cuuint32_t estr[3] = {1, 1, 1};
+        if (enc(&qm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return -3;
+    }
+    {
+        cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)total_rows};
+        cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
+        cuuint32_t box[2] = {64, (cuuint32_t)(page_size < 64 ? page_size : 64)};
+        cuuint32_t estr[2] = {1, 1};
+        if (enc(&kvm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache_base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return -3;
+    }
+    int shift = 0;
+    while ((1 << shift) < page_size) shift++;
+    AttnTcArgs a{(__nv_bfloat16*)out, seg_start, seg_len, seg_pos0, block_tables, status, H, K, G, max_pages, page_size, shift,
+                 window, n_layers, layer, scale * 1.4426950408889634f};
+    constexpr int SMEM = 12 * TA_ROWS * 128 + 1024 + 128;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(k_attention_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return XR_ERR_LAUNCH;
+        configured = true;
+    }
+    long long tiles = ((long long)max_seg_len * G + TA_ROWS - 1) / TA_ROWS;
+    if (tiles > 0x7fffffffLL) return XR_ERR_ARG;
+    xr_launch(k_attention_tc, dim3((unsigned)tiles, K, n_seg), dim3(TA_THREADS), SMEM, stream, qm, kvm, a);
+    return xr_launch_status();
+}

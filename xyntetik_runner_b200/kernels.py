@@ -61,6 +61,8 @@ def _declare(L: ctypes.CDLL) -> None:
         "xr_attention_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _f,
                              _i, _i, _i, _i, _i, _vp, _ll, _i, _i, _vp, _vp],
         "xr_attention_mma_splits": [_i, _i],
+        "xr_attention_tc_supported": [_i, _i, _i, _i],
+        "xr_attention_tc": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _ll, _i, _i, _vp],
         "xr_sample": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
     }
     for name, args in sig.items():
@@ -223,9 +225,12 @@ def tc_check_status(device: torch.device) -> None:
     """Raise if a tensor-core kernel gave up a wait since the last check (reads one word from the device)."""
     key = device.index if device.index is not None else torch.cuda.current_device()
     st = _tc_state.get(key)
-    if st is not None and int(st[1].item()) != 0:
-        st[1].zero_()
-        raise KernelError("a tcgen05 product gave up waiting on a barrier; its output is not valid")
+    if st is not None:
+        code = int(st[1].item())
+        if code != 0:
+            st[1].zero_()
+            what = {1: "a tcgen05 product", 2: "the bulk-copy decode attention", 3: "the tcgen05 attention"}.get(code, "a kernel")
+            raise KernelError(f"{what} gave up waiting on a barrier; its output is not valid")
 
 
 def gemm_tc_supported(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
@@ -356,3 +361,23 @@ def attention_mma(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, cache_k
                                   group[3] if group else 0, tc_workspace(out.device)[1].data_ptr() if group else None,
                                   _stream()), "attention_mma")
     _count((1 if any_long else 0) + (2 if any_short else 0))
+
+
+def attention_tc_supported(dtype: torch.dtype, H: int, K: int, hd: int, page_size: int) -> bool:
+    return dtype == torch.bfloat16 and bool(lib().xr_attention_tc_supported(H, K, hd, page_size))
+
+
+def attention_tc(qkv: torch.Tensor, out: torch.Tensor, seg_start, seg_len, seg_pos0, block_tables, group: tuple,
+                 H: int, K: int, hd: int, max_pages: int, page_size: int, window: int, scale: float, n_seg: int,
+                 max_seg_len: int) -> None:
+    """Causal attention of the portions with more than 16 packed rows on tcgen05 (S and O in tensor memory).
+    qkv: the step's fused rows (Q heads first); group = (pointer to the cache group's array, pages, layers, layer)."""
+    _dev(qkv, out, seg_start, seg_len, seg_pos0, block_tables)
+    n = qkv.shape[0]
+    assert qkv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and out.shape == (n, H * hd)
+    status = tc_workspace(out.device)[1]
+    _check(lib().xr_attention_tc(qkv.data_ptr(), out.data_ptr(), group[0], seg_start.data_ptr(), seg_len.data_ptr(),
+                                 seg_pos0.data_ptr(), block_tables.data_ptr(), status.data_ptr(), qkv.stride(0), n, n_seg,
+                                 H, K, hd, max_pages, page_size, window, float(scale), max_seg_len, group[1], group[2],
+                                 group[3], _stream()), "attention_tc")
+    _count()

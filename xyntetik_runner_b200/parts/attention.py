@@ -25,7 +25,9 @@ from .linear import Linear
 USE_MMA = os.environ.get("XRB200_NO_MMA_ATTENTION", "0") in ("", "0")
 # XRB200_NO_TMA_ATTENTION=1 keeps the decode kernel on per-thread cp.async gathers
 USE_TMA = os.environ.get("XRB200_NO_TMA_ATTENTION", "0") in ("", "0")
-counters = {"mma": 0, "simt": 0}
+# XRB200_NO_TC_ATTENTION=1 keeps prompt portions on the mma.sync kernel
+USE_TC = os.environ.get("XRB200_NO_TC_ATTENTION", "0") in ("", "0")
+counters = {"mma": 0, "simt": 0, "tcgen05": 0}
 
 
 class GQAAttention(Mixer):
@@ -103,11 +105,19 @@ class GQAAttention(Mixer):
             if any_short:
                 pa = ctx.buf("attn_part_acc", (ctx.n_seg * self.K * splits * 16 * self.hd,), torch.float32)
                 pm = ctx.buf("attn_part_ml", (ctx.n_seg * self.K * splits * 32,), torch.float32)
-            kernels.attention_mma(qkv, qkv_dim, o, k_ptr, ctx.seg_start, ctx.seg_len, ctx.seg_pos0, bt, pa, pm,
-                                  page_stride, v_offset, self.H, self.K, self.hd, ctx.max_pages, ctx.page_size,
-                                  self.window or 0, self.scale, ctx.n_seg, int(seg_len.max()), ctx.max_kv_len, splits,
-                                  any_short, any_long, group=ctx.cache_group(lay) if USE_TMA else None)
-            counters["mma"] += 1
+            if any_long and USE_TC and kernels.attention_tc_supported(ctx.act_dtype, self.H, self.K, self.hd, ctx.page_size):
+                # prompt portions: S = Q K^T and O += P V on tcgen05
+                kernels.attention_tc(qkv, o, ctx.seg_start, ctx.seg_len, ctx.seg_pos0, bt, ctx.cache_group(lay), self.H,
+                                     self.K, self.hd, ctx.max_pages, ctx.page_size, self.window or 0, self.scale, ctx.n_seg,
+                                     int(seg_len.max()))
+                counters["tcgen05"] += 1
+                any_long = False
+            if any_short or any_long:
+                kernels.attention_mma(qkv, qkv_dim, o, k_ptr, ctx.seg_start, ctx.seg_len, ctx.seg_pos0, bt, pa, pm,
+                                      page_stride, v_offset, self.H, self.K, self.hd, ctx.max_pages, ctx.page_size,
+                                      self.window or 0, self.scale, ctx.n_seg, int(seg_len.max()), ctx.max_kv_len, splits,
+                                      any_short, any_long, group=ctx.cache_group(lay) if USE_TMA else None)
+                counters["mma"] += 1
         else:
             kernels.attention_simt(qkv, qkv_dim, o, k_ptr, ctx.positions, ctx.tok_seg, bt, page_stride, v_offset,
                                    self.H, self.K, self.hd, ctx.max_pages, ctx.page_size, self.window or 0, self.scale)

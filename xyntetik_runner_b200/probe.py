@@ -86,10 +86,15 @@ def attention(a) -> None:
 
     def run(i):
         kp = cache.data_ptr() + (i % layers) * cache.stride(1) * 2
+        if not short and not a.no_tc and kernels.attention_tc_supported(torch.bfloat16, H, K, hd, page):
+            kernels.attention_tc(qkv, out, starts, lens, pos0, bt, (cache.data_ptr(), n_pages, layers, i % layers), H, K, hd, mp, page,
+                                 0, 1 / math.sqrt(hd), B, L)
+            return
         kernels.attention_mma(qkv, qkv.shape[1], out, kp, starts, lens, pos0, bt, pa, pm, cache.stride(0), cache.stride(2),
                               H, K, hd, mp, page, 0, 1 / math.sqrt(hd), B, L, ctx, splits, short, not short,
                               group=None if a.no_tma else (cache.data_ptr(), n_pages, layers, i % layers))
     us = _time(run, a.iters, a.plain)
+    kernels.tc_check_status(dev)
     kv_bytes = B * ctx * K * hd * 2 * 2
     flops = 4.0 * B * H * hd * (L * (ctx - L) + L * (L + 1) / 2)
     print(f"attention batch={B} context={ctx} portion={L} heads={H}/{K} head_dim={hd}: {us:.1f} us, "
@@ -113,6 +118,7 @@ def main(argv=None) -> int:
     t.add_argument("--kv-heads", type=int, default=8)
     t.add_argument("--head-dim", type=int, default=128)
     t.add_argument("--page-size", type=int, default=64)
+    t.add_argument("--no-tc", action="store_true", help="prompt portions on the mma.sync kernel instead of tcgen05")
     t.add_argument("--no-tma", action="store_true", help="decode kernel with per-thread cp.async gathers instead of bulk copies")
     for p in (g, t):
         p.add_argument("--iters", type=int, default=20)
