@@ -7,11 +7,13 @@
 // (128 x 256 tiles).  Both operands are K-major in global memory, which is what TMA with the
 // 128-byte swizzle and the K-major shared-memory descriptor want: no transposes anywhere.
 //
-// Roles inside a CTA of 192 threads:
+// Roles inside a CTA of 320 threads:
 //   warp 0, one lane : TMA producer  (cp.async.bulk.tensor.2d -> shared, completes on an mbarrier)
 //   warp 1, one lane : MMA issuer    (tcgen05.mma, commits free the stage / signal the epilogue);
 //                      the warp also allocates and frees tensor memory
-//   warps 2..5       : epilogue      (tcgen05.ld of their 32 lanes, then global stores)
+//   warps 2..9       : epilogue      (tcgen05.ld of their 32 lanes, then global stores); a warp may only
+//                      read the 32 tensor-memory lanes of its index mod 4, so two warps share each quarter
+//                      and take alternate 16-column chunks
 // A K loop over 64-element blocks runs through a ring of shared-memory stages.
 //
 // Epilogues: store (bfloat16 or float32, optional bias), add into the float32 residual stream,
@@ -31,7 +33,7 @@
 
 #define TC_BM 128          // W rows per CTA (the M of the instruction)
 #define TC_BK 64           // K elements per stage: 128 bytes, one swizzle atom
-#define TC_THREADS 192
+#define TC_THREADS 320       // producer warp, MMA warp, eight epilogue warps
 #define XR_SPIN_LIMIT (1u << 24)
 
 #define TC_EPI_STORE 0     // out[t][r] = acc (+ bias), bfloat16 or float32
@@ -94,6 +96,13 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, float* v) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
     for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
+}
+
+// silu(g) = g / (1 + exp(-g)), 0 below -80 (src/model.c:4451-4452), with the hardware's approximate exp2 and
+// reciprocal: their error (about 2^-22) disappears in the bfloat16 rounding of the result, and an epilogue that
+// spends hundreds of instructions per element on exact exp and division holds the tensor core up.
+__device__ __forceinline__ float tc_silu(float g) {
+    return g < -80.0f ? 0.0f : __fdividef(g, 1.0f + __expf(-g));
 }
 
 // K-major operand tile in shared memory, rows of 128 bytes, 128-byte swizzle, groups of 8 rows 1024 bytes
@@ -224,8 +233,8 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             if (ok) tc_commit(acc_ready);      // accumulators complete
         }
     } else {
-        // ---------------- epilogue: warps 2..5 own tensor-memory lanes 32*(warp%4) .. +31 ----------------
-        const int quad = warp & 3;
+        // ---------------- epilogue: warps 2..9, tensor-memory lanes 32*(warp%4) .. +31, alternate chunks ----------------
+        const int quad = warp & 3, chunk_first = (warp - 2) >> 2;
         const int r = row0 + quad * 32 + lane;            // output feature of this thread
         bool ok = mbar_wait(acc_ready, 0, abort_flag);
         tc_fence_after();
@@ -235,7 +244,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             const float b = (p.bias != nullptr && row_ok && (p.epilogue == TC_EPI_STORE || p.epilogue == TC_EPI_ADD) && blockIdx.z == 0)
                                 ? p.bias[r] : 0.f;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
+            for (int c0 = chunk_first * 16; c0 < BN; c0 += 32) {
                 if (tok0 + c0 >= p.n) break;               // warp-uniform
                 float g[16], u[16];
                 tc_ld16(taddr + c0, g);
@@ -262,8 +271,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                         dst[r] = g[c];
                         if (DUAL) dst[p.n_out + r] = u[c];
                     } else if (DUAL) {
-                        float gv = g[c];
-                        float h = gv < -80.0f ? 0.0f : (gv / (1.0f + expf(-gv))) * u[c];
+                        float h = tc_silu(g[c]) * u[c];
                         if (p.out_dtype == XR_BF16) ((__nv_bfloat16*)p.out)[(size_t)t * p.ldo + r] = __float2bfloat16_rn(h);
                         else ((float*)p.out)[(size_t)t * p.ldo + r] = h;
                     } else {
@@ -307,7 +315,7 @@ __global__ void k_splitk_finish(FinishParams p) {
             if (p.dual) u += src[p.n_out + r];
         }
         float v;
-        if (p.dual) v = g < -80.0f ? 0.0f : (g / (1.0f + expf(-g))) * u;
+        if (p.dual) v = tc_silu(g) * u;
         else v = g + (p.bias ? p.bias[r] : 0.f);
         size_t o = t * p.ldo + r;
         if (p.epilogue == TC_EPI_ADD) ((float*)p.out)[o] += v;
