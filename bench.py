@@ -102,6 +102,7 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=CONTEXT)
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--decode-only", action="store_true", help="time the decode step only (for profiling a small run)")
+    ap.add_argument("--prefill-only", action="store_true", help="time the 2,048-token prefill only (for profiling a small run)")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel of a decode step one by one")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -127,7 +128,7 @@ def main() -> int:
     pk = peaks()
     cfgd = dict(LLAMA3_8B, num_hidden_layers=args.layers)
     cfg = LlamaConfig.from_dict(cfgd)
-    if args.decode_only:
+    if args.decode_only or args.prefill_only:
         args.skip_points = True
     max_b = args.batch if args.skip_points else max(args.batch, 64)
     ctx_len = args.context
@@ -216,14 +217,14 @@ def main() -> int:
     clocks = ClockSampler()
     clocks.start()
     start_len = ctx_len - (W + K) - 2
-    main_run = decode_run(args.batch, start_len, K, W)
+    main_run = decode_run(args.batch, start_len, K, W) if not args.prefill_only else None
     if args.decode_only:
         clocks.stop()
         print(json.dumps({"decode_only": True, "batch": args.batch, "context": ctx_len, "ms_per_step": main_run["ms"],
                           "tok_s": args.batch * 1e3 / main_run["ms"], "launches": main_run["launches"]}))
         return 0
-    e2e_run = e2e_run_through_entry_point(args.batch, start_len, K, W)
-    assert e2e_run["tokens"] == args.batch * K
+    e2e_run = e2e_run_through_entry_point(args.batch, start_len, K, W) if not args.prefill_only else None
+    assert args.prefill_only or e2e_run["tokens"] == args.batch * K
 
     # prefill of 2,048 tokens in one step
     T = 2048
@@ -240,6 +241,10 @@ def main() -> int:
         if rep >= W:
             pre_ms.append(ev0.elapsed_time(ev1))
     pre = statistics.median(pre_ms)
+    if args.prefill_only:
+        clocks.stop()
+        print(json.dumps({"prefill_only": True, "tokens": T, "ms": pre, "tok_s": T * 1e3 / pre}))
+        return 0
     L, d, H, Kh, hd, F = cfg.num_hidden_layers, cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.intermediate_size
     gemm_flops = 2.0 * T * L * (d * (H + 2 * Kh) * hd + H * hd * d + 3 * d * F) + 2.0 * d * V
     attn_flops = L * 4.0 * H * hd * (T * (T + 1) / 2)

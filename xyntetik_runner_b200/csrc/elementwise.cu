@@ -44,11 +44,30 @@ __global__ void k_rmsnorm(const float* __restrict__ x, const int* __restrict__ r
     __shared__ float scratch[33];
     int r = rows ? rows[blockIdx.x] : blockIdx.x;
     const float* xr = x + (size_t)r * d;
+    TO* o = out + (size_t)blockIdx.x * d;
+    constexpr int PER = 16;                     // elements a thread can keep: rows up to 16 * blockDim.x stay in registers
+    if (d <= PER * (int)blockDim.x) {
+        float v[PER];
+        float ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < PER; k++) {
+            int i = threadIdx.x + k * blockDim.x;
+            v[k] = i < d ? xr[i] : 0.f;
+            ss += v[k] * v[k];
+        }
+        ss = xr_block_sum(ss, scratch);
+        float scale = 1.0f / sqrtf(ss / (float)d + eps);
+#pragma unroll
+        for (int k = 0; k < PER; k++) {
+            int i = threadIdx.x + k * blockDim.x;
+            if (i < d) o[i] = xr_from_f32<TO>(v[k] * scale * w[i]);
+        }
+        return;
+    }
     float ss = 0.f;
     for (int i = threadIdx.x; i < d; i += blockDim.x) { float v = xr[i]; ss += v * v; }
     ss = xr_block_sum(ss, scratch);
     float scale = 1.0f / sqrtf(ss / (float)d + eps);
-    TO* o = out + (size_t)blockIdx.x * d;
     for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = xr_from_f32<TO>(xr[i] * scale * w[i]);
 }
 
@@ -86,39 +105,50 @@ struct RopeStoreArgs {
     int n, H, K, hd, rotary_dim, max_pages, page_size;
 };
 
+// One block per token.  A thread owns pair index j (and every `blockDim.x / half`-th head): the angle
+// pos * inv_freq[j] and its cosine and sine are computed once and used for all the Q and K heads.
 template <typename T>
 __global__ void k_rope_store(RopeStoreArgs a) {
     xr_pdl_wait();
     xr_pdl_launch();
-    int t = blockIdx.x, head = blockIdx.y;
-    int qkv_dim = (a.H + 2 * a.K) * a.hd;
-    T* row = (T*)a.qkv + (size_t)t * qkv_dim + (size_t)head * a.hd;
-    int pos = a.positions[t];
-    int half = a.rotary_dim >> 1;
-    bool is_q = head < a.H, is_k = !is_q && head < a.H + a.K;
-    T* dst = nullptr;
-    if (!is_q) {
-        if (a.cache_k == nullptr) return;
-        int kvh = is_k ? head - a.H : head - a.H - a.K;
+    const int t = blockIdx.x;
+    const int qkv_dim = (a.H + 2 * a.K) * a.hd;
+    T* row = (T*)a.qkv + (size_t)t * qkv_dim;
+    const int pos = a.positions[t];
+    const int half = a.rotary_dim >> 1;
+    T* kdst = nullptr;
+    if (a.cache_k != nullptr) {
         int page = a.block_tables[(size_t)a.tok_seg[t] * a.max_pages + pos / a.page_size];
-        dst = (T*)a.cache_k + (size_t)page * a.page_stride + (is_k ? 0 : a.v_offset) +
-              ((size_t)kvh * a.page_size + (pos % a.page_size)) * a.hd;
+        kdst = (T*)a.cache_k + (size_t)page * a.page_stride + (size_t)(pos % a.page_size) * a.hd;
     }
-    if (is_q || is_k) {
-        for (int j = threadIdx.x; j < a.hd; j += blockDim.x) {
-            if (j < half) {
-                float ang = (float)pos * a.inv_freq[j];
-                float c = cosf(ang), s = sinf(ang);
-                float x0 = xr_to_f32<T>(row[j]), x1 = xr_to_f32<T>(row[j + half]);
+    const size_t head_step = (size_t)a.page_size * a.hd;          // between kv heads inside a page
+    // rotated pairs of the Q and K heads
+    if (half > 0) {
+        const int lanes = blockDim.x / half > 0 ? blockDim.x / half : 1;      // heads handled side by side
+        const int j = threadIdx.x % half, h0 = threadIdx.x / half;
+        if (threadIdx.x < lanes * half) {
+            float ang = (float)pos * a.inv_freq[j];
+            float c = cosf(ang), s = sinf(ang);
+            for (int head = h0; head < a.H + a.K; head += lanes) {
+                T* src = row + (size_t)head * a.hd;
+                float x0 = xr_to_f32<T>(src[j]), x1 = xr_to_f32<T>(src[j + half]);
                 T y0 = xr_from_f32<T>(x0 * c - x1 * s), y1 = xr_from_f32<T>(x0 * s + x1 * c);
-                if (is_q) { row[j] = y0; row[j + half] = y1; }
-                else { dst[j] = y0; dst[j + half] = y1; }
-            } else if (j >= 2 * half && is_k) {
-                dst[j] = row[j];
+                if (head < a.H) { src[j] = y0; src[j + half] = y1; }
+                else if (kdst) { T* d = kdst + (size_t)(head - a.H) * head_step; d[j] = y0; d[j + half] = y1; }
             }
         }
-    } else {
-        for (int j = threadIdx.x; j < a.hd; j += blockDim.x) dst[j] = row[j];
+    }
+    if (kdst == nullptr) return;
+    // the part of K beyond the rotated dimensions, and V, are copied
+    const int tail = a.hd - 2 * half;
+    for (int i = threadIdx.x; i < a.K * tail; i += blockDim.x) {
+        int kvh = i / tail, e = 2 * half + i % tail;
+        kdst[(size_t)kvh * head_step + e] = row[(size_t)(a.H + kvh) * a.hd + e];
+    }
+    T* vdst = kdst + a.v_offset;
+    for (int i = threadIdx.x; i < a.K * a.hd; i += blockDim.x) {
+        int kvh = i / a.hd, e = i % a.hd;
+        vdst[(size_t)kvh * head_step + e] = row[(size_t)(a.H + a.K + kvh) * a.hd + e];
     }
 }
 
@@ -131,10 +161,9 @@ XR_EXPORT int xr_rope_store(void* qkv, int dtype, const int* positions, const in
         return XR_ERR_ARG;
     RopeStoreArgs a{qkv, positions, tok_seg, block_tables, inv_freq, cache_k, page_stride, v_offset,
                     n, H, K, hd, rotary_dim, max_pages, page_size};
-    dim3 grid(n, H + 2 * K);
-    int threads = hd >= 128 ? 128 : (hd >= 64 ? 64 : 32);
-    if (dtype == XR_F32) xr_launch((k_rope_store<float>), dim3(grid), dim3(threads), 0, stream, a);
-    else if (dtype == XR_BF16) xr_launch((k_rope_store<__nv_bfloat16>), dim3(grid), dim3(threads), 0, stream, a);
+    int threads = 256;
+    if (dtype == XR_F32) xr_launch((k_rope_store<float>), dim3(n), dim3(threads), 0, stream, a);
+    else if (dtype == XR_BF16) xr_launch((k_rope_store<__nv_bfloat16>), dim3(n), dim3(threads), 0, stream, a);
     else return XR_ERR_ARG;
     return xr_launch_status();
 }
