@@ -414,3 +414,67 @@ def test_attention_tc(case_id):
             err = (got[row:row + L] - ref[row:row + L]).abs().max(dim=1).values / ref.abs().max()
             assert float(err.max()) <= 1.2e-2, (p0, L, torch.topk(err, min(5, L)).indices.tolist(), float(err.max()))
         row += L
+
+
+# ---------------------------------------------------------------------------------------------
+# the sampling kernel against the plain chain
+# ---------------------------------------------------------------------------------------------
+def _sample_rows(logits, temp, top_k, top_p, min_p, pen, draws, recent=None):
+    from xyntetik_runner_b200 import kernels
+    rows, V = logits.shape
+    f = lambda a: torch.tensor(a, dtype=torch.float32, device=DEV)
+    out = torch.full((rows,), -7, dtype=torch.int32, device=DEV)
+    scratch = torch.empty(rows * V, dtype=torch.float32, device=DEV)
+    rec = None if recent is None else torch.tensor(recent, dtype=torch.int32, device=DEV)
+    kernels.sample(torch.from_numpy(logits).to(DEV), f(temp), torch.tensor(top_k, dtype=torch.int32, device=DEV), f(top_p), f(min_p),
+                   f(pen), f(draws), rec, scratch, out)
+    return out.cpu().tolist()
+
+
+@pytest.mark.parametrize("V", [17, 387, 5000, 128256])
+def test_sampling_kernel_matches_the_plain_chain(V):
+    from plain_llama import sample_chain
+    rng = np.random.RandomState(V)
+    rows = 24
+    logits = (rng.randn(rows, V) * 3).astype(np.float32)
+    logits[3, :] = logits[3, 0]                         # all equal: every cut is decided by ids
+    logits[4, V // 2:] = logits[4, V // 2]              # a long tie in the tail
+    logits[5, 1] = logits[5].max() + 5; logits[5, 2] = logits[5, 1]      # a tie at the top
+    temp = [0.0, 0.7, 1.0, 1.5] * 6
+    top_k = [0, 0, 5, 40, 0, 3, 0, 1] * 3
+    top_p = [1.0, 0.9, 1.0, 0.5, 0.3, 1.0, 0.95, 1.0] * 3
+    min_p = [0.0, 0.0, 0.0, 0.05, 0.0, 0.0, 0.2, 0.0] * 3
+    pen = [1.0, 1.3, 1.0, 1.0, 1.1, 1.0, 1.0, 2.0] * 3
+    draws = [float(np.float32(x)) for x in rng.rand(rows)]
+    draws[6], draws[7] = 0.0, float(np.float32(1.0 - 2 ** -24))
+    recent = np.full((rows, 256), -1, dtype=np.int32)
+    for r in range(rows):
+        k = rng.randint(0, 60)
+        recent[r, :k] = rng.randint(0, V, size=k)
+        if k > 3:
+            recent[r, 1] = recent[r, 0]                 # a token that occurs twice is penalised twice
+    got = _sample_rows(logits, temp, top_k, top_p, min_p, pen, draws, recent)
+    for r in range(rows):
+        kw = dict(top_k=top_k[r], top_p=top_p[r], min_p=min_p[r], repeat_penalty=pen[r], recent=[t for t in recent[r] if t >= 0])
+        want = sample_chain(logits[r], draws[r], temp[r], **kw)
+        if got[r] != want:
+            # float32 sums in another order may move an edge of the cumulative distribution by ~1e-6
+            dist = sample_chain(logits[r], draws[r], temp[r], distance_of=got[r], **kw)
+            assert dist <= 2e-6, f"row {r}: kernel {got[r]}, plain {want}, draw {dist:.3e} outside the token's interval"
+    # greedy rows are exact: first index among equal maxima
+    assert got[0] == int(np.argmax(logits[0])) and got[4 * 1] == int(np.argmax(logits[4]))
+
+
+def test_sampling_kernel_follows_the_distribution():
+    """Many draws at one row: empirical frequencies of the kept tokens match softmax(logits / temp)."""
+    V, n = 50, 4000
+    rng = np.random.RandomState(1)
+    base = (rng.randn(V) * 2).astype(np.float32)
+    logits = np.tile(base, (n, 1))
+    draws = [float(np.float32(x)) for x in rng.rand(n)]
+    got = np.array(_sample_rows(logits, [0.9] * n, [10] * n, [1.0] * n, [0.0] * n, [1.0] * n, draws))
+    order = np.argsort(-base)[:10]
+    p = np.exp((base[order] - base[order[0]]) / 0.9); p /= p.sum()
+    assert set(got.tolist()) <= set(order.tolist())
+    freq = np.array([(got == t).mean() for t in order])
+    assert np.abs(freq - p).max() < 4 * np.sqrt(0.25 / n)

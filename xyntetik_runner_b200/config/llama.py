@@ -128,8 +128,11 @@ class LlamaConfig:
             if not isinstance(rs, Mapping):
                 raise ConfigError("config.json: rope_scaling must be an object or null")
             kind = rs.get("rope_type", rs.get("type"))
-            if kind != "llama3":
+            if kind == "default":
+                rs = None                     # "default" names the unscaled table
+            elif kind != "llama3":
                 raise ConfigError(f"config.json: rope_scaling type '{kind}' is not supported (only 'llama3')")
+        if rs is not None:
             try:
                 scaling = RopeScaling(
                     rope_type="llama3",

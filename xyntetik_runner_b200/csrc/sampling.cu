@@ -225,20 +225,20 @@ k_sample(SampleArgs a, float* scratch /* [rows, V] scaled values, or null when n
             ms = blk_sum_d(ms, sh);
             if (ms >= target) thr = cand;
         }
-        if (thr > cut.thr || (thr == cut.thr && cut.n_eq < 0)) {
-            // among equal keys at thr, keep only as many (by id) as the prefix needs
+        {
+            // among equal keys at thr, keep only as many (by id) as the prefix needs; if thr is also where top-k cut,
+            // no more than top-k left there
             double gtm = 0.0; long long eqn = 0;
             for (int i = tid; i < V; i += SMP_THREADS) { unsigned k = xr_key(vals[i]); if (k > thr) gtm += (double)expf(vals[i] - mx); eqn += (k == thr); }
             gtm = blk_sum_d(gtm, sh);
             eqn = blk_sum_ll(eqn, sh);
-            long long need = eqn;
-            if (eqn > 1) {
+            long long avail = (thr == cut.thr && cut.n_eq >= 0 && cut.n_eq < eqn) ? cut.n_eq : eqn;
+            long long need = avail;
+            if (avail > 1) {
                 // each equal candidate adds e; the prefix ends at the first whose cumulative sum reaches target
-                float e = 0.f;
-                unsigned ut = thr; float vt = __uint_as_float((ut & 0x80000000u) ? (ut & 0x7fffffffu) : ~ut);
-                e = expf(vt - mx);
-                double rest = target - gtm;
-                long long c = (long long)ceil(rest / (double)e);
+                float vt = __uint_as_float((thr & 0x80000000u) ? (thr & 0x7fffffffu) : ~thr);
+                double e = (double)expf(vt - mx);
+                long long c = (long long)ceil((target - gtm) / e - 1e-9);
                 if (c < 1) c = 1;
                 if (c < need) need = c;
             }
