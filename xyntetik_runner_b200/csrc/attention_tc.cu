@@ -7,12 +7,20 @@
 //
 // A CTA owns 128 packed rows (token i / G, head i % G) of one (request, kv head) and walks its keys in tiles
 // of 128, in ascending order.  Roles (192 threads):
-//   warps 0..3 : softmax.  Thread r owns row r = tensor-memory lane r.  Per tile: read S, running maximum,
-//                rescale O in tensor memory when the maximum moved, write P = exp(S - m) as bfloat16 into
-//                shared memory in the layout the matrix instruction reads (K-major, 128-byte swizzle).
-//   warp 4     : one lane issues the TMA copies (Q once, then K and V tiles through a two-stage ring).
-//   warp 5     : one lane issues the matrix instructions; the warp owns the tensor-memory allocation.
-// S is double buffered (S of tile j+1 is computed while the softmax of tile j runs); O is one accumulator.
+//   warps 0..7 : softmax.  Row r = tensor-memory lane r is shared by two threads (warps w and w + 4 may both
+//                read lanes 32 (w % 4) ..): one takes keys 0..63 of a tile, the other keys 64..127; they
+//                exchange their maxima through shared memory.  Per tile: read S, running maximum, rescale O in
+//                tensor memory when needed, write P = exp(S - m) as bfloat16 into shared memory in the layout
+//                the matrix instruction reads (K-major, 128-byte swizzle).  One softmax warp per scheduler
+//                could not hide its own latencies; two can.
+//   warp 8     : one lane issues the TMA copies of Q (once) and of the K tiles (two-stage ring; a K stage is free
+//                as soon as its Q K^T has run, so the next-but-one tile's keys are fetched two tiles ahead).
+//   warp 9     : one lane issues the matrix instructions; the warp owns the tensor-memory allocation.
+//   warp 10    : one lane issues the TMA copies of the V tiles (two-stage ring, freed by P V).
+// S and P are double buffered (S of tile j+1 is computed, and P of tile j is consumed, while the softmax of
+// the neighbouring tile runs); O is one accumulator.  O and the running sum carry an offset m per row; the offset
+// is moved (and O rescaled, which has to wait for the product in flight) only when a row's maximum has grown by
+// more than 8 (in log2) since it was set, so most tiles never wait: exp2(s - m) then stays below 2^8.
 // V is the B operand of P V with N = head size contiguous in memory (an "MN-major" operand): its shared
 // memory descriptor has leading byte offset = distance between the two 64-column halves and stride byte
 // offset = 8 keys.
@@ -29,7 +37,7 @@
 #define TA_ROWS 128
 #define TA_KEYS 128
 #define TA_HD 128
-#define TA_THREADS 192
+#define TA_THREADS 352
 #define TA_SPIN (1u << 24)
 
 struct AttnTcArgs {
@@ -83,6 +91,18 @@ __device__ __forceinline__ void ta_ld32(uint32_t taddr, float* v) {
 #pragma unroll
     for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
 }
+// the same load without the wait, so that several can be in flight; call ta_ld_wait() before using the values
+__device__ __forceinline__ void ta_ld32_nowait(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void ta_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void ta_st32(uint32_t taddr, const float* v) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
@@ -119,23 +139,30 @@ __host__ __device__ constexpr uint32_t ta_idesc(bool b_mn) {
 
 __global__ void __launch_bounds__(TA_THREADS, 1)
 k_attention_tc(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map, AttnTcArgs a) {
-    extern __shared__ __align__(16) uint8_t ta_smem_raw[];
-    uint8_t* smem = (uint8_t*)(((uintptr_t)ta_smem_raw + 1023) & ~(uintptr_t)1023);
+    // 14 half tiles of 16 KB leave no room for alignment slack: the array is declared 1 KB aligned (what the
+    // swizzled TMA boxes and the matrix descriptors need) and the kernel refuses to run if it is not
+    extern __shared__ __align__(1024) uint8_t ta_smem_raw[];
+    uint8_t* smem = ta_smem_raw;
+    if ((ta_smem(smem) & 1023u) != 0) {
+        if (threadIdx.x == 0) atomicExch(a.status, 4);
+        return;
+    }
     constexpr int HALF = TA_ROWS * 128;                   // bytes of one [128 rows][64 columns] half tile
     uint8_t* q_s = smem;                                  // [2 halves][128 rows][128 B]
-    uint8_t* p_s = q_s + 2 * HALF;                        // [2 halves (keys 0-63, 64-127)][128 rows][128 B]
-    uint8_t* k_s = p_s + 2 * HALF;                        // [2 stages][2 halves (hd)][128 keys][128 B]
+    uint8_t* p_s = q_s + 2 * HALF;                        // [2 buffers][2 halves (keys 0-63, 64-127)][128 rows][128 B]
+    uint8_t* k_s = p_s + 4 * HALF;                        // [2 stages][2 halves (hd)][128 keys][128 B]
     uint8_t* v_s = k_s + 4 * HALF;                        // [2 stages][2 halves (hd)][128 keys][128 B]
     uint64_t* bars = (uint64_t*)(v_s + 4 * HALF);
     uint64_t* q_full = bars;            // 1
     uint64_t* k_full = bars + 1;        // 2
     uint64_t* v_full = bars + 3;        // 2
-    uint64_t* kv_empty = bars + 5;      // 2
+    uint64_t* k_empty = bars + 5;       // 2
     uint64_t* s_full = bars + 7;        // 2
-    uint64_t* p_full = bars + 9;        // 1  (count 128)
-    uint64_t* pv_done = bars + 10;      // 1
-    uint32_t* tmem_slot = (uint32_t*)(bars + 11);
+    uint64_t* p_full = bars + 9;        // 1  (count 8)
+    uint64_t* pv_done = bars + 10;      // 2  (product of tile j arrives on pv_done[j & 1]; it also frees V stage j & 1)
+    uint32_t* tmem_slot = (uint32_t*)(bars + 12);
     volatile int* gave_up = (volatile int*)(tmem_slot + 1);
+    float* xch = (float*)(tmem_slot + 4);                // [2 tile parities][2 key halves][128 rows]
 
     const int seg = blockIdx.z, kvh = blockIdx.y;
     const int L = a.seg_len[seg], rows_total = L * a.G;
@@ -153,13 +180,14 @@ k_attention_tc(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
 
     if (threadIdx.x == 0) {
         ta_bar_init(q_full, 1);
-        for (int i = 0; i < 2; i++) { ta_bar_init(&k_full[i], 1); ta_bar_init(&v_full[i], 1); ta_bar_init(&kv_empty[i], 1); ta_bar_init(&s_full[i], 1); }
-        ta_bar_init(p_full, 128);
-        ta_bar_init(pv_done, 1);
+        for (int i = 0; i < 2; i++) { ta_bar_init(&k_full[i], 1); ta_bar_init(&v_full[i], 1); ta_bar_init(&k_empty[i], 1); ta_bar_init(&s_full[i], 1); }
+        ta_bar_init(p_full, 8);            // one arrival per softmax warp
+        ta_bar_init(&pv_done[0], 1);
+        ta_bar_init(&pv_done[1], 1);
         *gave_up = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 5) {
+    if (warp == 9) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ta_smem(tmem_slot)), "r"(512) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -169,34 +197,35 @@ k_attention_tc(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     const uint32_t tmem = *tmem_slot;
     const uint32_t tm_s0 = tmem, tm_s1 = tmem + 128, tm_o = tmem + 256;
 
-    if (warp == 4) {
-        // ---------------- TMA producer ----------------
+    if (warp == 8 || warp == 10) {
+        // ---------------- TMA producers: warp 8 Q and K, warp 10 V ----------------
         if (lane == 0) {
-            ta_expect(q_full, 2 * HALF);
-            int tok0 = tok_base + row0 / a.G;
-            for (int c = 0; c < 2; c++) ta_tma_3d(q_s + c * HALF, &q_map, c * 64, kvh * a.G, tok0, q_full);
+            const bool keys = warp == 8;
+            if (keys) {
+                ta_expect(q_full, 2 * HALF);
+                int tok0 = tok_base + row0 / a.G;
+                for (int c = 0; c < 2; c++) ta_tma_3d(q_s + c * HALF, &q_map, c * 64, kvh * a.G, tok0, q_full);
+            }
             const int box_rows = a.page_size < 64 ? a.page_size : 64;
+            uint64_t* full = keys ? k_full : v_full;
+            uint64_t* empty = keys ? k_empty : pv_done;
+            uint8_t* base = keys ? k_s : v_s;
             for (int j = 0; j < n_tiles; j++) {
                 int s = j & 1;
-                if (j >= 2) ta_wait(&kv_empty[s], ((j >> 1) - 1) & 1, gave_up);
-                ta_expect(&k_full[s], 2 * HALF);
-                ta_expect(&v_full[s], 2 * HALF);
+                if (j >= 2) ta_wait(&empty[s], ((j >> 1) - 1) & 1, gave_up);
+                ta_expect(&full[s], 2 * HALF);
                 int key0 = (t_lo + j) * TA_KEYS;
                 for (int r0 = 0; r0 < TA_KEYS; r0 += box_rows) {
                     int kp = key0 + r0;
                     int pi = kp >> a.page_shift;
                     int page = pi < a.max_pages ? a.block_tables[(size_t)seg * a.max_pages + pi] : -1;
-                    long long rowk = ((((long long)page * a.n_layers + a.layer) * 2) * a.K + kvh) * a.page_size + (kp & (a.page_size - 1));
-                    long long rowv = rowk + (long long)a.K * a.page_size;
-                    if (page < 0) { rowk = -1024; rowv = -1024; }          // outside the tensor: the copy fills zeros
-                    for (int c = 0; c < 2; c++) {
-                        ta_tma_2d(k_s + (s * 2 + c) * HALF + r0 * 128, &kv_map, c * 64, (int)rowk, &k_full[s]);
-                        ta_tma_2d(v_s + (s * 2 + c) * HALF + r0 * 128, &kv_map, c * 64, (int)rowv, &v_full[s]);
-                    }
+                    long long row = ((((long long)page * a.n_layers + a.layer) * 2 + (keys ? 0 : 1)) * a.K + kvh) * a.page_size + (kp & (a.page_size - 1));
+                    if (page < 0) row = -1024;                          // outside the tensor: the copy fills zeros
+                    for (int c = 0; c < 2; c++) ta_tma_2d(base + (s * 2 + c) * HALF + r0 * 128, &kv_map, c * 64, (int)row, &full[s]);
                 }
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             constexpr uint32_t id_qk = ta_idesc(false), id_pv = ta_idesc(true);
@@ -211,6 +240,7 @@ k_attention_tc(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
                     ta_mma((j & 1) ? tm_s1 : tm_s0, ta_desc_k(qa + off), ta_desc_k(kb + off), id_qk, kk > 0 ? 1u : 0u);
                 }
                 ta_commit(&s_full[j & 1]);
+                ta_commit(&k_empty[s]);          // the keys of this tile are not needed again
             };
             ta_wait(q_full, 0, gave_up);
             issue_qk(0);
@@ -222,90 +252,114 @@ k_attention_tc(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
                 ta_wait(p_full, j & 1, gave_up);                    // P(j) is in shared memory, S(j) has been read
                 ta_wait(&v_full[s], (j >> 1) & 1, gave_up);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                uint32_t pa = ta_smem(p_s), vb = ta_smem(v_s + s * 2 * HALF);
+                uint32_t pa = ta_smem(p_s + (j & 1) * 2 * HALF), vb = ta_smem(v_s + s * 2 * HALF);
 #pragma unroll
                 for (int kk = 0; kk < TA_KEYS / 16; kk++) {
                     uint64_t ad = ta_desc_k(pa + (kk >> 2) * HALF + (kk & 3) * 32);
                     uint64_t bd = ta_desc_mn(vb + kk * 16 * 128, HALF);
                     ta_mma(tm_o, ad, bd, id_pv, (j > 0 || kk > 0) ? 1u : 0u);
                 }
-                ta_commit(&kv_empty[s]);
-                ta_commit(pv_done);
+                ta_commit(&pv_done[j & 1]);
             }
         }
     } else {
-        // ---------------- softmax: thread = row = tensor-memory lane ----------------
-        const int r = threadIdx.x;                               // 0..127
+        // ---------------- softmax: row = tensor-memory lane, two threads per row (key halves) ----------------
+        const int r = (warp & 3) * 32 + lane;                    // 0..127
+        const int half = warp >> 2;                              // keys [64 half, 64 half + 64) of every tile
         const int pr = row0 + r;
         const int pos = pr < rows_total ? pos0 + pr / a.G : -1;
         const int lo_r = a.window > 0 ? pos - a.window + 1 : 0;
-        const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
-        float m = -INFINITY, l = 0.f;
+        const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+        float m = -INFINITY, l = 0.f;          // m: the offset O and l currently carry (log2 domain); l: this thread's half
+        const int pos_first = pos0 + row0 / a.G;                  // smallest position of the CTA's rows
         for (int j = 0; j < n_tiles; j++) {
-            const uint32_t tm_s = ((j & 1) ? tm_s1 : tm_s0) + lane_off;
-            const int key0 = (t_lo + j) * TA_KEYS;
+            const uint32_t tm_s = ((j & 1) ? tm_s1 : tm_s0) + lane_off + half * 64;
+            const int key0 = (t_lo + j) * TA_KEYS + half * 64;
+            // a tile every row sees whole needs no per-score mask
+            const bool masked = a.window > 0 || (t_lo + j) * TA_KEYS + TA_KEYS - 1 > pos_first || row0 + TA_ROWS > rows_total;
             ta_wait(&s_full[j & 1], (j >> 1) & 1, gave_up);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // this thread's 64 scores are read once and stay in registers for both passes
+            uint32_t sraw[64];
+            ta_ld32_nowait(tm_s, sraw);
+            ta_ld32_nowait(tm_s + 32, sraw + 32);
+            ta_ld_wait();
             float v[32];
             float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < 4; c++) {
-                ta_ld32(tm_s + c * 32, v);
+            if (masked) {
 #pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    int kp = key0 + c * 32 + i;
-                    if (kp <= pos && kp >= lo_r) mx = fmaxf(mx, v[i]);
+                for (int i = 0; i < 64; i++) {
+                    int kp = key0 + i;
+                    if (kp <= pos && kp >= lo_r) mx = fmaxf(mx, __uint_as_float(sraw[i]));
                 }
+            } else {
+                float m0 = __uint_as_float(sraw[0]), m1 = __uint_as_float(sraw[1]), m2 = __uint_as_float(sraw[2]), m3 = __uint_as_float(sraw[3]);
+#pragma unroll
+                for (int i = 4; i < 64; i += 4) {
+                    m0 = fmaxf(m0, __uint_as_float(sraw[i])); m1 = fmaxf(m1, __uint_as_float(sraw[i + 1]));
+                    m2 = fmaxf(m2, __uint_as_float(sraw[i + 2])); m3 = fmaxf(m3, __uint_as_float(sraw[i + 3]));
+                }
+                mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
             }
-            float m_new = fmaxf(m, mx * a.scale_log2);           // maxima are kept in the log2 domain
-            float off = m_new == -INFINITY ? 0.f : m_new;
-            // O and the P buffer are in use by the product of the previous tile until it completes
-            if (j > 0) ta_wait(pv_done, (j - 1) & 1, gave_up);
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            // the loads and stores of tensor memory are warp-wide: a warp rescales if any of its rows moved
-            float corr = (j > 0 && m_new != m) ? ta_exp2(m - off) : 1.0f;      // m = -inf -> 0
-            if (__any_sync(0xffffffffu, corr != 1.0f)) {
+            // the row's maximum over both halves
+            float* x = xch + (j & 1) * 256;
+            x[half * 128 + r] = mx;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            mx = fmaxf(x[r], x[128 + r]) * a.scale_log2;
+            // move the offset only when the maximum has grown by more than 8 since it was set
+            float corr = 1.0f;
+            if (m == -INFINITY) { if (mx != -INFINITY) m = mx; }          // O and l of this row are still zero
+            else if (mx > m + 8.0f) { corr = ta_exp2(m - mx); m = mx; }
+            if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
+                // O is in use by the product of the previous tile until it completes; each thread rescales its 64 columns
+                ta_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, gave_up);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 l *= corr;
 #pragma unroll 1
-                for (int c = 0; c < 4; c++) {
-                    ta_ld32(tm_o + lane_off + c * 32, v);
+                for (int c = 0; c < 2; c++) {
+                    ta_ld32(tm_o + lane_off + half * 64 + c * 32, v);
 #pragma unroll
                     for (int i = 0; i < 32; i++) v[i] *= corr;
-                    ta_st32(tm_o + lane_off + c * 32, v);
+                    ta_st32(tm_o + lane_off + half * 64 + c * 32, v);
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
-            m = m_new;
-            float sum = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < 4; c++) {
-                ta_ld32(tm_s + c * 32, v);
+            // the P buffer of this tile was read by the product of tile j - 2
+            if (j >= 2) ta_wait(&pv_done[j & 1], ((j >> 1) - 1) & 1, gave_up);
+            const float off = m == -INFINITY ? 0.f : m;
+            uint8_t* rowp = p_s + (j & 1) * 2 * HALF + half * HALF + r * 128;       // this thread's half row of P
+            float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+            for (int c = 0; c < 2; c++) {
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    int kp = key0 + c * 32 + i;
-                    float p0 = (kp <= pos && kp >= lo_r) ? ta_exp2(v[i] * a.scale_log2 - off) : 0.f;
-                    float p1 = (kp + 1 <= pos && kp + 1 >= lo_r) ? ta_exp2(v[i + 1] * a.scale_log2 - off) : 0.f;
-                    sum += p0 + p1;
-                    __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1);
-                    pk[i >> 1] = *reinterpret_cast<uint32_t*>(&b);
+                    float p0 = ta_exp2(fmaf(__uint_as_float(sraw[c * 32 + i]), a.scale_log2, -off));
+                    float p1 = ta_exp2(fmaf(__uint_as_float(sraw[c * 32 + i + 1]), a.scale_log2, -off));
+                    if (masked) {
+                        int kp = key0 + c * 32 + i;
+                        if (!(kp <= pos && kp >= lo_r)) p0 = 0.f;
+                        if (!(kp + 1 <= pos && kp + 1 >= lo_r)) p1 = 0.f;
+                    }
+                    sum0 += p0; sum1 += p1;
+                    __nv_bfloat162 bb = __floats2bfloat162_rn(p0, p1);
+                    pk[i >> 1] = *reinterpret_cast<uint32_t*>(&bb);
                 }
-                // keys c*32 .. c*32+31 of row r: four 16-byte chunks of the half tile (c >> 1), swizzled by the row
-                uint8_t* rowp = p_s + (c >> 1) * HALF + r * 128;
+                // keys c*32 .. c*32+31 of this half: four 16-byte chunks of the row, swizzled by the row
 #pragma unroll
                 for (int q = 0; q < 4; q++) {
-                    int chunk = (c & 1) * 4 + q;
+                    int chunk = c * 4 + q;
                     *reinterpret_cast<uint4*>(rowp + ((chunk ^ (r & 7)) << 4)) = make_uint4(pk[q * 4], pk[q * 4 + 1], pk[q * 4 + 2], pk[q * 4 + 3]);
                 }
             }
-            l += sum;
-            if (key0 + TA_KEYS - 1 > hi) {
+            l += sum0 + sum1;
+            if ((t_lo + j) * TA_KEYS + TA_KEYS - 1 > hi) {
                 // The tile runs past the last key.  Probabilities there are zero, but the value rows hold whatever the
                 // page held before; clear them so that zero times those bytes is zero whatever they are.
                 int s = j & 1;
                 ta_wait(&v_full[s], (j >> 1) & 1, gave_up);
-                int first_bad = hi + 1 - key0;
-                for (int e = r; e < (TA_KEYS - first_bad) * 16; e += 128) {
+                int first_bad = hi + 1 - (t_lo + j) * TA_KEYS;
+                for (int e = half * 128 + r; e < (TA_KEYS - first_bad) * 16; e += 256) {
                     int row = first_bad + (e >> 4), ch = e & 15;
                     *reinterpret_cast<uint4*>(v_s + (s * 2 + (ch >> 3)) * HALF + row * 128 + (((ch & 7) ^ (row & 7)) << 4)) = make_uint4(0, 0, 0, 0);
                 }
@@ -313,26 +367,32 @@ k_attention_tc(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
             // make P (and the cleared rows) visible to the tensor core (async proxy), order the tensor-memory reads, then signal
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            ta_arrive(p_full);
+            __syncwarp();
+            if (lane == 0) ta_arrive(p_full);
         }
-        ta_wait(pv_done, (n_tiles - 1) & 1, gave_up);
+        ta_wait(&pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, gave_up);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         {
+            // the row's sum over both halves
+            float* x = xch + (n_tiles & 1) * 256;
+            x[half * 128 + r] = l;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            l = x[r] + x[128 + r];
             const bool live = pr < rows_total;
             float inv = live ? 1.0f / l : 0.f;
-            __nv_bfloat16* dst = a.out + ((long long)(tok_base + (live ? pr : 0) / a.G) * a.H + (kvh * a.G + (live ? pr : 0) % a.G)) * TA_HD;
+            __nv_bfloat16* dst = a.out + ((long long)(tok_base + (live ? pr : 0) / a.G) * a.H + (kvh * a.G + (live ? pr : 0) % a.G)) * TA_HD + half * 64;
             float v[32];
 #pragma unroll 1
-            for (int c = 0; c < 4; c++) {
-                ta_ld32(tm_o + lane_off + c * 32, v);            // warp-wide: rows past the portion load too
+            for (int c = 0; c < 2; c++) {
+                ta_ld32(tm_o + lane_off + half * 64 + c * 32, v);            // warp-wide: rows past the portion load too
                 if (!live) continue;
 #pragma unroll
                 for (int i = 0; i < 32; i += 8) {
                     uint32_t w[4];
 #pragma unroll
                     for (int e = 0; e < 4; e++) {
-                        __nv_bfloat162 b = __floats2bfloat162_rn(v[i + 2 * e] * inv, v[i + 2 * e + 1] * inv);
-                        w[e] = *reinterpret_cast<uint32_t*>(&b);
+                        __nv_bfloat162 bb = __floats2bfloat162_rn(v[i + 2 * e] * inv, v[i + 2 * e + 1] * inv);
+                        w[e] = *reinterpret_cast<uint32_t*>(&bb);
                     }
                     *reinterpret_cast<uint4*>(dst + c * 32 + i) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
@@ -341,7 +401,7 @@ k_attention_tc(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 5) {
+    if (warp == 9) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
     }
@@ -409,7 +469,7 @@ XR_EXPORT int xr_attention_tc(const void* q, void* out, const void* cache_base, 
     while ((1 << shift) < page_size) shift++;
     AttnTcArgs a{(__nv_bfloat16*)out, seg_start, seg_len, seg_pos0, block_tables, status, H, K, G, max_pages, page_size, shift,
                  window, n_layers, layer, scale * 1.4426950408889634f};
-    constexpr int SMEM = 12 * TA_ROWS * 128 + 1024 + 128;
+    constexpr int SMEM = 14 * TA_ROWS * 128 + 128 + 2 * 2 * 128 * 4;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(k_attention_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return XR_ERR_LAUNCH;

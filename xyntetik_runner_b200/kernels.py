@@ -229,7 +229,7 @@ def tc_check_status(device: torch.device) -> None:
         code = int(st[1].item())
         if code != 0:
             st[1].zero_()
-            what = {1: "a tcgen05 product", 2: "the bulk-copy decode attention", 3: "the tcgen05 attention"}.get(code, "a kernel")
+            what = {1: "a tcgen05 product", 2: "the bulk-copy decode attention", 3: "the tcgen05 attention", 4: "the tcgen05 attention (shared memory not 1 KB aligned)"}.get(code, "a kernel")
             raise KernelError(f"{what} gave up waiting on a barrier; its output is not valid")
 
 
