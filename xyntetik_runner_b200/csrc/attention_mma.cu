@@ -593,13 +593,16 @@ k_attention_keys_tma(const __grid_constant__ CUtensorMap cache_map, AttnMmaArgs 
 }
 
 // Combine the spans of one (request, kv head) in ascending order and write the output rows.
-// grid (K, segments).  Each row's span weights exp(m_s - M) / L are computed once into shared memory.
+// grid (K, segments), 256 threads.  Each row's span weights exp(m_s - M) / L go to shared memory first; then a
+// thread owns output elements and sums the spans with its loads independent of one another.
+#define MERGE_SPANS 64          // spans whose weights fit shared memory at once (longer requests go round again)
 template <int HD>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 k_attention_merge(AttnMmaArgs a) {
     xr_pdl_wait();
     xr_pdl_launch();
-    __shared__ float wgt[16][33];                  // [row][span], up to 32 spans at a time
+    __shared__ float wgt[16][MERGE_SPANS + 1];
+    __shared__ float row_max[16], row_inv[16];
     const int seg = blockIdx.y, kvh = blockIdx.x;
     const int L = a.seg_len[seg], rows_total = L * a.G;
     if (rows_total > 16) return;
@@ -611,42 +614,49 @@ k_attention_merge(AttnMmaArgs a) {
     const size_t item0 = ((size_t)seg * a.K + kvh) * a.max_splits;
     const float* ml = a.part_ml + item0 * 32;
     const float* pa = a.part_acc + item0 * 16 * HD;
-    __shared__ float row_max[16], row_inv[16];
-    if (threadIdx.x < rows_total) {
-        int r = threadIdx.x;
+    // one warp per row: maximum and denominator over the spans
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int r = warp; r < rows_total; r += 8) {
         float mm = -INFINITY;
-        for (int s = 0; s < n_spans; s++) mm = fmaxf(mm, ml[(s * 16 + r) * 2]);
+        for (int s = lane; s < n_spans; s += 32) mm = fmaxf(mm, __ldcg(ml + (s * 16 + r) * 2));
+        mm = xr_warp_max(mm);
         float off = mm == -INFINITY ? 0.f : mm;
-        float ll = 0.f;
-        for (int s = 0; s < n_spans; s++) ll += ml[(s * 16 + r) * 2 + 1] * expf(ml[(s * 16 + r) * 2] - off);
-        row_max[r] = off; row_inv[r] = 1.0f / ll;
+        float ll = 0.f;                      // summed in a fixed order: lane-strided, then the warp tree
+        for (int s = lane; s < n_spans; s += 32) ll += __ldcg(ml + (s * 16 + r) * 2 + 1) * expf(__ldcg(ml + (s * 16 + r) * 2) - off);
+        ll = xr_warp_sum(ll);
+        if (lane == 0) { row_max[r] = off; row_inv[r] = 1.0f / ll; }
     }
     __syncthreads();
-    float acc[(16 * HD + 127) / 128];
+    constexpr int PER = (16 * HD + 255) / 256;
+    float acc[PER];
 #pragma unroll
-    for (int k = 0; k < (16 * HD + 127) / 128; k++) acc[k] = 0.f;
-    for (int s0 = 0; s0 < n_spans; s0 += 32) {
-        int ns = min(32, n_spans - s0);
-        for (int i = threadIdx.x; i < rows_total * ns; i += 128) {
+    for (int k = 0; k < PER; k++) acc[k] = 0.f;
+    for (int s0 = 0; s0 < n_spans; s0 += MERGE_SPANS) {
+        int ns = min(MERGE_SPANS, n_spans - s0);
+        for (int i = threadIdx.x; i < rows_total * ns; i += 256) {
             int r = i / ns, s = i % ns;
-            wgt[r][s] = expf(ml[((s0 + s) * 16 + r) * 2] - row_max[r]);
+            wgt[r][s] = expf(__ldcg(ml + ((s0 + s) * 16 + r) * 2) - row_max[r]);
         }
         __syncthreads();
+#pragma unroll 4
+        for (int s = 0; s < ns; s++) {
+            float v[PER];
 #pragma unroll
-        for (int k = 0; k < (16 * HD + 127) / 128; k++) {
-            int i = threadIdx.x + k * 128;
-            if (i < rows_total * HD) {
-                int r = i / HD, d = i % HD;
-                float v = acc[k];
-                for (int s = 0; s < ns; s++) v += pa[((size_t)(s0 + s) * 16 + r) * HD + d] * wgt[r][s];
-                acc[k] = v;
+            for (int k = 0; k < PER; k++) {
+                int i = threadIdx.x + k * 256;
+                v[k] = i < rows_total * HD ? __ldcg(pa + ((size_t)(s0 + s) * 16 + i / HD) * HD + i % HD) : 0.f;
+            }
+#pragma unroll
+            for (int k = 0; k < PER; k++) {
+                int i = threadIdx.x + k * 256;
+                if (i < rows_total * HD) acc[k] += v[k] * wgt[i / HD][s];
             }
         }
         __syncthreads();
     }
 #pragma unroll
-    for (int k = 0; k < (16 * HD + 127) / 128; k++) {
-        int i = threadIdx.x + k * 128;
+    for (int k = 0; k < PER; k++) {
+        int i = threadIdx.x + k * 256;
         if (i < rows_total * HD) {
             int r = i / HD, d = i % HD;
             a.out[((long long)(tok_base + r / a.G) * a.H + (kvh * a.G + r % a.G)) * HD + d] = __float2bfloat16_rn(acc[k] * row_inv[r]);
@@ -743,7 +753,7 @@ static int launch_attention(const AttnMmaArgs& a, int n_seg, int max_seg_len, in
             xr_launch((k_attention_keys<HD, 2>), dim3(a.max_splits, a.K, n_seg), dim3(ATT_THREADS), SMEM_KEYS2, stream, a);
         int rc = xr_launch_status();
         if (rc != XR_OK) return rc;
-        xr_launch((k_attention_merge<HD>), dim3(a.K, n_seg), dim3(128), 0, stream, a);
+        xr_launch((k_attention_merge<HD>), dim3(a.K, n_seg), dim3(256), 0, stream, a);
         return xr_launch_status();
     }
     return XR_OK;

@@ -7,45 +7,78 @@
 // Partials are [splits][n][width] float32 and are summed in split order, so the result is deterministic.
 #include "common.cuh"
 
+// One block per token.  A thread owns up to FIN_PER elements of the row (strided by the block size) and keeps
+// them in registers; the partial sums are read with all of a thread's loads of one split in flight together
+// (the splits are summed in order, so the result does not depend on timing).
+#define FIN_PER 8
 template <typename TO>
-__global__ void k_finish_add_rmsnorm(const float* __restrict__ partial, int splits, int n, const float* __restrict__ bias,
-                                     float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out, int d, float eps) {
+__global__ void __launch_bounds__(1024)
+k_finish_add_rmsnorm(const float* __restrict__ partial, int splits, int n, const float* __restrict__ bias,
+                     float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out, int d, float eps) {
     xr_pdl_wait();
     xr_pdl_launch();
     __shared__ float scratch[33];
-    extern __shared__ float row[];             // the new residual row, kept for the second pass
-    int t = blockIdx.x;
+    const int t = blockIdx.x;
     float* xr = x + (size_t)t * d;
+    TO* o = out + (size_t)t * d;
     float ss = 0.f;
+    if (d <= FIN_PER * (int)blockDim.x) {
+        float acc[FIN_PER];
+#pragma unroll
+        for (int k = 0; k < FIN_PER; k++) acc[k] = 0.f;
+        const float* p = partial + (size_t)t * d + threadIdx.x;
+        const size_t split_stride = (size_t)n * d;
+#pragma unroll 4
+        for (int s = 0; s < splits; s++) {
+            float v[FIN_PER];
+#pragma unroll
+            for (int k = 0; k < FIN_PER; k++) v[k] = (int)(threadIdx.x + k * blockDim.x) < d ? __ldcg(p + (size_t)s * split_stride + k * blockDim.x) : 0.f;
+#pragma unroll
+            for (int k = 0; k < FIN_PER; k++) acc[k] += v[k];
+        }
+#pragma unroll
+        for (int k = 0; k < FIN_PER; k++) {
+            int i = threadIdx.x + k * blockDim.x;
+            if (i < d) {
+                float v = acc[k];
+                if (bias) v += bias[i];
+                v = xr[i] + v;
+                xr[i] = v;
+                acc[k] = v;
+                ss += v * v;
+            }
+        }
+        ss = xr_block_sum(ss, scratch);
+        float scale = 1.0f / sqrtf(ss / (float)d + eps);
+#pragma unroll
+        for (int k = 0; k < FIN_PER; k++) {
+            int i = threadIdx.x + k * blockDim.x;
+            if (i < d) o[i] = xr_from_f32<TO>(acc[k] * scale * w[i]);
+        }
+        return;
+    }
+    // rows too wide for the registers: two passes through global memory
     for (int i = threadIdx.x; i < d; i += blockDim.x) {
         float v = 0.f;
         for (int s = 0; s < splits; s++) v += partial[((size_t)s * n + t) * d + i];
         if (bias) v += bias[i];
         v = xr[i] + v;
         xr[i] = v;
-        row[i] = v;
         ss += v * v;
     }
     ss = xr_block_sum(ss, scratch);
     float scale = 1.0f / sqrtf(ss / (float)d + eps);
-    TO* o = out + (size_t)t * d;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = xr_from_f32<TO>(row[i] * scale * w[i]);
+    __syncthreads();
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = xr_from_f32<TO>(xr[i] * scale * w[i]);
 }
 
 XR_EXPORT int xr_finish_add_rmsnorm(const float* partial, int splits, const float* bias, float* x, const float* w, void* out,
                                     int out_dtype, int n, int d, float eps, cudaStream_t stream) {
-    if (n < 1 || d < 1 || splits < 1 || (size_t)d * 4 > 200 * 1024) return XR_ERR_ARG;
-    int threads = d >= 2048 ? 512 : 256;
-    size_t smem = (size_t)d * 4;
-    if (out_dtype == XR_F32) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(k_finish_add_rmsnorm<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        xr_launch((k_finish_add_rmsnorm<float>), dim3(n), dim3(threads), smem, stream, partial, splits, n, bias, x, w, (float*)out, d, eps);
-    } else if (out_dtype == XR_BF16) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(k_finish_add_rmsnorm<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        xr_launch((k_finish_add_rmsnorm<__nv_bfloat16>), dim3(n), dim3(threads), smem, stream, partial, splits, n, bias, x, w, (__nv_bfloat16*)out, d, eps);
-    } else {
-        return XR_ERR_ARG;
-    }
+    if (n < 1 || d < 1 || splits < 1) return XR_ERR_ARG;
+    int threads = d >= 4096 ? 1024 : (d >= 1024 ? 512 : 256);      // few tokens, so many threads per token
+    if (out_dtype == XR_F32) xr_launch((k_finish_add_rmsnorm<float>), dim3(n), dim3(threads), 0, stream, partial, splits, n, bias, x, w, (float*)out, d, eps);
+    else if (out_dtype == XR_BF16) xr_launch((k_finish_add_rmsnorm<__nv_bfloat16>), dim3(n), dim3(threads), 0, stream, partial, splits, n, bias, x, w, (__nv_bfloat16*)out, d, eps);
+    else return XR_ERR_ARG;
     return xr_launch_status();
 }
 
