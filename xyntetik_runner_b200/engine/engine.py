@@ -281,9 +281,14 @@ class Engine:
         for si, e in enumerate(entries):
             m = len(e.tokens)
             p0 = cache.length(e.request)
-            tok[at:at + m] = np.asarray(e.tokens, dtype=np.int64).astype(np.int32)
-            pos[at:at + m] = np.arange(p0, p0 + m, dtype=np.int32)
-            seg[at:at + m] = si
+            if m == 1:
+                tok[at] = e.tokens[0]
+                pos[at] = p0
+                seg[at] = si
+            else:
+                tok[at:at + m] = np.asarray(e.tokens, dtype=np.int64).astype(np.int32)
+                pos[at:at + m] = np.arange(p0, p0 + m, dtype=np.int32)
+                seg[at:at + m] = si
             for w in e.want:
                 rows[ri] = at + w
                 ri += 1
@@ -307,9 +312,9 @@ class Engine:
         ctx.token_ids, ctx.positions, ctx.tok_seg, ctx.logit_rows = view(0), view(1), view(2), view(3)
         ctx.seg_start, ctx.seg_len, ctx.seg_pos0, ctx.seg_slot = view(4), view(5), view(6), view(7)
         ctx.block_tables = [view(8 + g).view(S, mp) for g in range(G)]
-        ctx.host = {"token_ids": tok.copy(), "positions": pos.copy(), "tok_seg": seg.copy(), "logit_rows": rows[:R].copy(),
-                    "seg_start": s_start.copy(), "seg_len": s_len.copy(), "seg_pos0": s_pos0.copy(),
-                    "seg_slot": s_slot.copy()}
+        # (views of the pinned buffer: valid until this buffer's turn in the ring comes again, three steps on)
+        ctx.host = {"token_ids": tok, "positions": pos, "tok_seg": seg, "logit_rows": rows[:R], "seg_start": s_start,
+                    "seg_len": s_len, "seg_pos0": s_pos0, "seg_slot": s_slot}
         if decode_only:
             max_kv = -(-max_kv // 1024) * 1024      # a bucket, so that launch shapes repeat from step to step
         ctx.max_kv_len, ctx.decode_only = max_kv, decode_only

@@ -88,12 +88,25 @@ class DeviceSampler:
     def __init__(self, device: torch.device):
         self.device = device
         self._scratch: Optional[torch.Tensor] = None
+        self._greedy: dict = {}          # rows -> parameter tensors of an all-greedy batch (they never change)
 
     def pick(self, logits: torch.Tensor, samplers: List[RequestSampler]) -> torch.Tensor:
         """logits: float32 [rows, vocab] on the device, one RequestSampler per row (each makes its
         draw here).  Returns int32 [rows] on the device."""
         rows, V = logits.shape
         assert rows == len(samplers)
+        if all(s.params.temperature <= 0 for s in samplers):
+            # greedy rows take no draw and no parameters but temp = 0: nothing to send to the device
+            g = self._greedy.get(rows)
+            if g is None:
+                g = (torch.zeros((5, rows), dtype=torch.float32, device=self.device),
+                     torch.zeros(rows, dtype=torch.int32, device=self.device),
+                     torch.empty(1, dtype=torch.float32, device=self.device))
+                self._greedy[rows] = g
+            fd, kd, scratch = g
+            out = torch.empty(rows, dtype=torch.int32, device=self.device)
+            kernels.sample(logits, fd[0], kd, fd[1], fd[2], fd[3], fd[4], None, scratch, out, False)
+            return out
         f = np.zeros((5, rows), dtype=np.float32)
         k = np.zeros(rows, dtype=np.int32)
         any_sampled = any_window = False
