@@ -1,4 +1,4 @@
-"""Llama-3-8B layer sizes (4 of its 32 layers, so that the test takes seconds) with random bfloat16 weights:
+"""Layer sizes of the models the benchmarks name (a few layers of each, so that the test takes seconds) with random bfloat16 weights:
 the serving path against the engine's own true 32-bit path on the same weights, whole and cut.  The tiny
 configurations anchor the arithmetic on the plain implementation; this anchors the kernels at the sizes
 they are tuned for (head size 128, four heads per kv head, widths 4096/14336, a 128,256-entry vocabulary)."""
@@ -18,12 +18,23 @@ SHAPE = {
 }
 
 
-def test_serving_path_matches_the_32_bit_path_at_8b_layer_sizes():
+# Llama-3.2-1B layer sizes: head size 64, tied head, llama3 rope scaling x32
+SHAPE_1B = dict(SHAPE, hidden_size=2048, num_hidden_layers=3, num_attention_heads=32, num_key_value_heads=8, head_dim=64,
+                intermediate_size=8192, tie_word_embeddings=True,
+                rope_scaling={"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                              "original_max_position_embeddings": 8192})
+# Llama-2-13B layer sizes: as many kv heads as heads, a 32,000-entry vocabulary, theta 10000
+SHAPE_13B = dict(SHAPE, hidden_size=5120, num_hidden_layers=2, num_attention_heads=40, num_key_value_heads=40, head_dim=128,
+                 intermediate_size=13824, vocab_size=32000, rope_theta=10000.0, max_position_embeddings=4096)
+
+
+@pytest.mark.parametrize("shape", [SHAPE, SHAPE_1B, SHAPE_13B], ids=["llama-3-8b", "llama-3.2-1b", "llama-2-13b"])
+def test_serving_path_matches_the_32_bit_path_at_8b_layer_sizes(shape):
     from xyntetik_runner_b200.config.llama import LlamaConfig
     from xyntetik_runner_b200.engine.engine import EngineParams, random_engine
     from xyntetik_runner_b200.engine.replay import replay
     from xyntetik_runner_b200.parts import linear
-    cfg = LlamaConfig.from_dict(SHAPE)
+    cfg = LlamaConfig.from_dict(shape)
     V = cfg.vocab_size
     reqs = {"a": traces.random_tokens(1, 150, V), "b": traces.random_tokens(2, 70, V), "c": traces.random_tokens(3, 260, V)}
 
