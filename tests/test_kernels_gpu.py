@@ -234,7 +234,7 @@ def _run_attention(case, kind, H, K, hd, page, window, dtype, tma=False):
                                H, K, hd, c["max_pages"], page, window, c["scale"])
     else:
         G = H // K
-        splits = kernels.attention_mma_splits(c["max_len"], window)
+        splits = kernels.attention_mma_splits(c["max_len"], window, c["n_seg"] * K)
         pa = torch.full((c["n_seg"] * K * splits * 16 * hd,), float("nan"), device=DEV)
         pm = torch.full((c["n_seg"] * K * splits * 32,), float("nan"), device=DEV)
         lens = c["lens_host"]

@@ -17,9 +17,10 @@
 //  * rows: a CTA owns 64 packed rows (4 warps x 16) of one (request, kv head) and walks all its keys.
 //    For portions of prompts.
 //  * keys: a request's portion has at most 16 packed rows (a decoded token, or a few); a CTA owns one
-//    span of ATT_SPLIT keys, its four warps take 16 keys each of every tile and their running
-//    (max, sum, accumulator) are combined in shared memory.  Spans are fixed ranges of absolute
-//    positions; `k_attention_merge` combines them in ascending order.
+//    span of keys, its four warps take 16 keys each of every tile and their running
+//    (max, sum, accumulator) are combined in shared memory.  Spans are ranges of absolute positions,
+//    whole tiles long; the launcher picks their length so that the CTAs fill the machine in whole
+//    waves (att_choose_span); `k_attention_merge` combines them in ascending order.
 // K and V rows are gathered page by page with 16-byte cp.async copies (any page size), double buffered.
 #include "common.cuh"
 #include <math.h>
@@ -27,9 +28,8 @@
 
 #define ATT_TILE 64            // keys per tile
 #define ATT_ROWS 64            // packed query rows per CTA in the rows kernel
-#define ATT_SPLIT 512          // keys per CTA in the keys kernel (ATT_SPLIT_SHORT while a request is short)
-#define ATT_SPLIT_SHORT 256
-#define ATT_SHORT_LIMIT 2048   // requests of at most this many keys use the short span
+#define ATT_KEYS_SLOTS (3 * 148)   // CTAs of the keys kernel that are resident at once (two stages: three per SM)
+#define ATT_MAX_SPLITS 256     // most spans per request
 #define ATT_THREADS 128
 
 struct AttnMmaArgs {
@@ -44,6 +44,7 @@ struct AttnMmaArgs {
     float* part_ml;              // keys kernel: [n_seg][K][splits][16][2]
     long long q_stride, page_stride, v_offset;
     int H, K, G, max_pages, page_size, window, max_splits;
+    int span;                    // keys kernel: keys per span, a multiple of ATT_TILE
     float scale;
     int page_shift;              // log2(page_size) when it is a power of two, else -1
     // bulk-copy (TMA) variant of the keys kernel: the whole cache group as rows of head_dim elements
@@ -51,9 +52,36 @@ struct AttnMmaArgs {
     int* status;                 // set non-zero if a bounded wait gives up
 };
 
-// Span length of a request whose last key is at position hi: a function of the request alone, so that its
-// partition into spans does not depend on what else is in the batch.
-__host__ __device__ __forceinline__ int att_span(int hi) { return hi < ATT_SHORT_LIMIT ? ATT_SPLIT_SHORT : ATT_SPLIT; }
+// Span length (keys) of the keys kernel for a step whose longest request covers `range` keys and that has
+// `items` (request, kv head) pairs.  The kernel runs in waves of ATT_KEYS_SLOTS CTAs and a CTA costs about two
+// tiles' worth of time before its first keys arrive, so the span that minimises waves x (2 + tiles per span) is
+// taken: few requests are cut finely enough to fill the machine, many are cut so that the last wave is full.
+// The partition into spans changes only the order of the float32 sums, never which keys a query sees.
+static int att_choose_span(int range, long long items) {
+    static int forced = -1;
+    if (forced < 0) { const char* e = getenv("XRB200_ATTENTION_SPAN"); forced = e ? atoi(e) : 0; if (forced < 0) forced = 0; }
+    int tiles = (range + ATT_TILE - 1) / ATT_TILE;
+    if (tiles < 1) tiles = 1;
+    if (forced > 0) { int s = (forced + ATT_TILE - 1) / ATT_TILE; while ((tiles + s - 1) / s + 1 > ATT_MAX_SPLITS) s++; return s * ATT_TILE; }
+    if (items < 1) items = 1;
+    // Times in nanoseconds, fitted to measurements at head size 128: a wave costs about 4 us before its first
+    // keys arrive plus its tiles; a tile streams in 0.7 us when a CTA has an SM to itself (latency bound) and in
+    // 2.1 us when the machine is full (bandwidth bound); the merge costs about 0.1 us per span.
+    int best = tiles;
+    long long best_cost = -1;
+    for (int s = tiles; s >= 1; s--) {
+        int splits = (tiles + s - 1) / s;
+        if (splits + 1 > ATT_MAX_SPLITS) break;
+        long long ctas = items * splits;
+        long long waves = (ctas + ATT_KEYS_SLOTS - 1) / ATT_KEYS_SLOTS;
+        long long tile_ns = 2100 * (ctas < ATT_KEYS_SLOTS ? ctas : ATT_KEYS_SLOTS) / ATT_KEYS_SLOTS;
+        if (tile_ns < 700) tile_ns = 700;
+        long long cost = waves * (4000 + s * tile_ns) + 100LL * splits;
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = s; }
+    }
+    return best * ATT_TILE;
+}
+static int att_range(int max_kv_len, int window) { return window > 0 && window + 16 < max_kv_len ? window + 16 : max_kv_len; }
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
@@ -341,7 +369,7 @@ k_attention_keys(AttnMmaArgs a) {
     const int pos0 = a.seg_pos0[seg], tok_base = a.seg_start[seg];
     const int hi_all = pos0 + L - 1;
     const int lo_all = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
-    const int SPAN = att_span(hi_all);
+    const int SPAN = a.span;
     const int first_span = lo_all / SPAN;
     const int k_begin = (first_span + span) * SPAN;                // spans are fixed ranges of absolute positions
     if (k_begin > hi_all) return;
@@ -468,7 +496,7 @@ k_attention_keys_tma(const __grid_constant__ CUtensorMap cache_map, AttnMmaArgs 
     const int pos0 = a.seg_pos0[seg], tok_base = a.seg_start[seg];
     const int hi_all = pos0 + L - 1;
     const int lo_all = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
-    const int SPAN = att_span(hi_all);
+    const int SPAN = a.span;
     const int first_span = lo_all / SPAN;
     const int k_begin = (first_span + span) * SPAN;
     if (k_begin > hi_all) return;
@@ -592,31 +620,36 @@ k_attention_keys_tma(const __grid_constant__ CUtensorMap cache_map, AttnMmaArgs 
     }
 }
 
-// Combine the spans of one (request, kv head) in ascending order and write the output rows.
-// grid (K, segments), 256 threads.  Each row's span weights exp(m_s - M) / L go to shared memory first; then a
-// thread owns output elements and sums the spans with its loads independent of one another.
+// Combine the spans of one (request, kv head) and write the output rows.  grid (K, segments), MERGE_THREADS
+// threads.  Each row's span weights exp(m_s - M) go to shared memory first.  A thread then owns four
+// neighbouring output elements and every `groups`-th span (groups = threads / owned quadruples, so that all
+// threads have work when there are few rows), with its loads independent of one another; the groups' sums
+// meet in shared memory and are added in ascending group order, so the result is a fixed function of the
+// partials.
 #define MERGE_SPANS 64          // spans whose weights fit shared memory at once (longer requests go round again)
+#define MERGE_THREADS 512
 template <int HD>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(MERGE_THREADS)
 k_attention_merge(AttnMmaArgs a) {
     xr_pdl_wait();
     xr_pdl_launch();
     __shared__ float wgt[16][MERGE_SPANS + 1];
     __shared__ float row_max[16], row_inv[16];
+    __shared__ float4 group_sum[MERGE_THREADS];
     const int seg = blockIdx.y, kvh = blockIdx.x;
     const int L = a.seg_len[seg], rows_total = L * a.G;
     if (rows_total > 16) return;
     const int pos0 = a.seg_pos0[seg], tok_base = a.seg_start[seg];
     const int hi_all = pos0 + L - 1;
     const int lo_all = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
-    const int SPAN = att_span(hi_all);
+    const int SPAN = a.span;
     const int n_spans = hi_all / SPAN - lo_all / SPAN + 1;
     const size_t item0 = ((size_t)seg * a.K + kvh) * a.max_splits;
     const float* ml = a.part_ml + item0 * 32;
     const float* pa = a.part_acc + item0 * 16 * HD;
     // one warp per row: maximum and denominator over the spans
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int r = warp; r < rows_total; r += 8) {
+    for (int r = warp; r < rows_total; r += MERGE_THREADS / 32) {
         float mm = -INFINITY;
         for (int s = lane; s < n_spans; s += 32) mm = fmaxf(mm, __ldcg(ml + (s * 16 + r) * 2));
         mm = xr_warp_max(mm);
@@ -627,40 +660,58 @@ k_attention_merge(AttnMmaArgs a) {
         if (lane == 0) { row_max[r] = off; row_inv[r] = 1.0f / ll; }
     }
     __syncthreads();
-    constexpr int PER = (16 * HD + 255) / 256;
-    float acc[PER];
-#pragma unroll
-    for (int k = 0; k < PER; k++) acc[k] = 0.f;
+    constexpr int QUADS = HD / 4;                       // float4 per row
+    const int owned = rows_total * QUADS;               // <= 16 * 32 = MERGE_THREADS
+    const int groups = MERGE_THREADS / owned;
+    const int g = threadIdx.x / owned, e = threadIdx.x % owned;
+    const bool active = g < groups;
+    const int r = e / QUADS;
+    const float4* src = reinterpret_cast<const float4*>(pa) + e;          // span s: + s * 16 * QUADS
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int s0 = 0; s0 < n_spans; s0 += MERGE_SPANS) {
         int ns = min(MERGE_SPANS, n_spans - s0);
-        for (int i = threadIdx.x; i < rows_total * ns; i += 256) {
-            int r = i / ns, s = i % ns;
-            wgt[r][s] = expf(__ldcg(ml + ((s0 + s) * 16 + r) * 2) - row_max[r]);
+        for (int i = threadIdx.x; i < rows_total * ns; i += MERGE_THREADS) {
+            int rr = i / ns, s = i % ns;
+            wgt[rr][s] = expf(__ldcg(ml + ((s0 + s) * 16 + rr) * 2) - row_max[rr]);
         }
         __syncthreads();
-#pragma unroll 4
-        for (int s = 0; s < ns; s++) {
-            float v[PER];
-#pragma unroll
-            for (int k = 0; k < PER; k++) {
-                int i = threadIdx.x + k * 256;
-                v[k] = i < rows_total * HD ? __ldcg(pa + ((size_t)(s0 + s) * 16 + i / HD) * HD + i % HD) : 0.f;
+        if (active) {
+            int s = g;
+            for (; s + 3 * groups < ns; s += 4 * groups) {
+                float4 v0 = __ldcg(src + (size_t)(s0 + s) * 16 * QUADS);
+                float4 v1 = __ldcg(src + (size_t)(s0 + s + groups) * 16 * QUADS);
+                float4 v2 = __ldcg(src + (size_t)(s0 + s + 2 * groups) * 16 * QUADS);
+                float4 v3 = __ldcg(src + (size_t)(s0 + s + 3 * groups) * 16 * QUADS);
+                float w0 = wgt[r][s], w1 = wgt[r][s + groups], w2 = wgt[r][s + 2 * groups], w3 = wgt[r][s + 3 * groups];
+                acc.x += v0.x * w0; acc.y += v0.y * w0; acc.z += v0.z * w0; acc.w += v0.w * w0;
+                acc.x += v1.x * w1; acc.y += v1.y * w1; acc.z += v1.z * w1; acc.w += v1.w * w1;
+                acc.x += v2.x * w2; acc.y += v2.y * w2; acc.z += v2.z * w2; acc.w += v2.w * w2;
+                acc.x += v3.x * w3; acc.y += v3.y * w3; acc.z += v3.z * w3; acc.w += v3.w * w3;
             }
-#pragma unroll
-            for (int k = 0; k < PER; k++) {
-                int i = threadIdx.x + k * 256;
-                if (i < rows_total * HD) acc[k] += v[k] * wgt[i / HD][s];
+            for (; s < ns; s += groups) {
+                float4 v = __ldcg(src + (size_t)(s0 + s) * 16 * QUADS);
+                float w = wgt[r][s];
+                acc.x += v.x * w; acc.y += v.y * w; acc.z += v.z * w; acc.w += v.w * w;
             }
         }
         __syncthreads();
     }
-#pragma unroll
-    for (int k = 0; k < PER; k++) {
-        int i = threadIdx.x + k * 256;
-        if (i < rows_total * HD) {
-            int r = i / HD, d = i % HD;
-            a.out[((long long)(tok_base + r / a.G) * a.H + (kvh * a.G + r % a.G)) * HD + d] = __float2bfloat16_rn(acc[k] * row_inv[r]);
+    group_sum[threadIdx.x] = acc;
+    __syncthreads();
+    if (threadIdx.x < owned) {
+        float4 t = group_sum[threadIdx.x];
+        for (int k = 1; k < groups; k++) {
+            float4 u = group_sum[k * owned + threadIdx.x];
+            t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w;
         }
+        const float inv = row_inv[r];
+        const int d = (e % QUADS) * 4;
+        __nv_bfloat16* dst = a.out + ((long long)(tok_base + r / a.G) * a.H + (kvh * a.G + r % a.G)) * HD + d;
+        __nv_bfloat162 lo2 = __floats2bfloat162_rn(t.x * inv, t.y * inv), hi2 = __floats2bfloat162_rn(t.z * inv, t.w * inv);
+        uint2 packed;
+        packed.x = *reinterpret_cast<uint32_t*>(&lo2);
+        packed.y = *reinterpret_cast<uint32_t*>(&hi2);
+        *reinterpret_cast<uint2*>(dst) = packed;
     }
 }
 
@@ -700,17 +751,23 @@ static int launch_keys_tma(const AttnMmaArgs& a, const void* cache_base, long lo
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return -3;
     constexpr int LD = HD + 8;
-    constexpr int S2 = 2 * 2 * ATT_TILE * HD * 2 + 16 * LD * 2 + 64 + 1024, S4 = 4 * 2 * ATT_TILE * HD * 2 + 16 * LD * 2 + 64 + 1024;
+    constexpr int STAGE = 2 * ATT_TILE * HD * 2, REST = 16 * LD * 2 + 64 + 1024;
+    constexpr int S2 = 2 * STAGE + REST, S3 = 3 * STAGE + REST, S4 = 4 * STAGE + REST;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(k_attention_keys_tma<HD, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, S2) != cudaSuccess ||
+            cudaFuncSetAttribute(k_attention_keys_tma<HD, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, S3) != cudaSuccess ||
             cudaFuncSetAttribute(k_attention_keys_tma<HD, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, S4) != cudaSuccess)
             return XR_ERR_LAUNCH;
         configured = true;
     }
+    // the fewer CTAs there are, the deeper each one's ring of tiles, so that as many bytes stay in flight per SM
     dim3 grid(a.max_splits, a.K, n_seg);
-    if ((long long)a.max_splits * a.K * n_seg <= 2 * 148)
+    long long ctas = (long long)a.max_splits * a.K * n_seg;
+    if (ctas <= 148)
         xr_launch((k_attention_keys_tma<HD, 4>), dim3(grid), dim3(ATT_THREADS), S4, stream, map, a);
+    else if (ctas <= 2 * 148)
+        xr_launch((k_attention_keys_tma<HD, 3>), dim3(grid), dim3(ATT_THREADS), S3, stream, map, a);
     else
         xr_launch((k_attention_keys_tma<HD, 2>), dim3(grid), dim3(ATT_THREADS), S2, stream, map, a);
     return xr_launch_status() == XR_OK ? 1 : XR_ERR_LAUNCH;
@@ -753,22 +810,22 @@ static int launch_attention(const AttnMmaArgs& a, int n_seg, int max_seg_len, in
             xr_launch((k_attention_keys<HD, 2>), dim3(a.max_splits, a.K, n_seg), dim3(ATT_THREADS), SMEM_KEYS2, stream, a);
         int rc = xr_launch_status();
         if (rc != XR_OK) return rc;
-        xr_launch((k_attention_merge<HD>), dim3(a.K, n_seg), dim3(256), 0, stream, a);
+        xr_launch((k_attention_merge<HD>), dim3(a.K, n_seg), dim3(MERGE_THREADS), 0, stream, a);
         return xr_launch_status();
     }
     return XR_OK;
 }
 
 // Spans the keys kernel needs for a longest key range of `max_kv_len` (window > 0: at most that many keys).
-XR_EXPORT int xr_attention_mma_splits(int max_kv_len, int window) {
-    int range = window > 0 && window + 16 < max_kv_len ? window + 16 : max_kv_len;
-    int by_short = ((range < ATT_SHORT_LIMIT ? range : ATT_SHORT_LIMIT) + ATT_SPLIT_SHORT - 1) / ATT_SPLIT_SHORT;
-    int by_long = max_kv_len > ATT_SHORT_LIMIT ? (range + ATT_SPLIT - 1) / ATT_SPLIT : 0;
-    return (by_short > by_long ? by_short : by_long) + (window > 0 ? 1 : 0);
+// `items`: (request, kv head) pairs of the step, n_seg * K.
+XR_EXPORT int xr_attention_mma_splits(int max_kv_len, int window, long long items) {
+    int range = att_range(max_kv_len, window);
+    int span = att_choose_span(range, items);
+    return (range + span - 1) / span + (window > 0 ? 1 : 0);
 }
 
 // part_acc: float32 [n_seg * K * splits * 16 * hd], part_ml: float32 [n_seg * K * splits * 32]
-// (only read and written when any_short).  splits must be xr_attention_mma_splits(max_kv_len, window).
+// (only read and written when any_short).  splits must be xr_attention_mma_splits(max_kv_len, window, n_seg * K).
 XR_EXPORT int xr_attention_mma(const void* q, void* out, const void* cache_k, const int* seg_start, const int* seg_len,
                                const int* seg_pos0, const int* block_tables, float* part_acc, float* part_ml,
                                long long q_stride, long long page_stride, long long v_offset, int n_seg, int H, int K,
@@ -781,7 +838,9 @@ XR_EXPORT int xr_attention_mma(const void* q, void* out, const void* cache_k, co
     if (H / K > 16 && any_short) return XR_ERR_ARG;     // more heads per group than one instruction tile holds
     AttnMmaArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)cache_k, seg_start, seg_len, seg_pos0,
                   block_tables, part_acc, part_ml, q_stride, page_stride, v_offset, H, K, H / K, max_pages, page_size, window,
-                  splits, scale, -1, n_layers, layer, status};
+                  splits, 0, scale, -1, n_layers, layer, status};
+    a.span = att_choose_span(att_range(max_kv_len, window), (long long)n_seg * K);
+    if (any_short && splits != (att_range(max_kv_len, window) + a.span - 1) / a.span + (window > 0 ? 1 : 0)) return XR_ERR_ARG;
     if ((page_size & (page_size - 1)) == 0) { int sh = 0; while ((1 << sh) < page_size) sh++; a.page_shift = sh; }
     switch (hd) {
         case 16: return launch_attention<16>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream);

@@ -60,7 +60,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "xr_finish_rope_store": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _vp],
         "xr_attention_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _f,
                              _i, _i, _i, _i, _i, _vp, _ll, _i, _i, _vp, _vp],
-        "xr_attention_mma_splits": [_i, _i],
+        "xr_attention_mma_splits": [_i, _i, _ll],
         "xr_attention_tc_supported": [_i, _i, _i, _i],
         "xr_attention_tc": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _ll, _i, _i, _vp],
         "xr_sample": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
@@ -334,8 +334,9 @@ def attention_mma_supported(dtype: torch.dtype, H: int, K: int, hd: int) -> bool
     return dtype == torch.bfloat16 and hd % 16 == 0 and 16 <= hd <= 128 and H % K == 0 and H // K <= 16
 
 
-def attention_mma_splits(max_kv_len: int, window: int) -> int:
-    return int(lib().xr_attention_mma_splits(max_kv_len, window))
+def attention_mma_splits(max_kv_len: int, window: int, items: int) -> int:
+    """Spans per request of the key-split kernel for a step with `items` = segments x kv heads."""
+    return int(lib().xr_attention_mma_splits(max_kv_len, window, items))
 
 
 def attention_mma(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, cache_k_ptr: int, seg_start, seg_len, seg_pos0,

@@ -100,7 +100,7 @@ class GQAAttention(Mixer):
             seg_len = ctx.host["seg_len"]
             any_short = bool((seg_len * G <= 16).any())
             any_long = bool((seg_len * G > 16).any())
-            splits = kernels.attention_mma_splits(ctx.max_kv_len, self.window or 0)
+            splits = kernels.attention_mma_splits(ctx.max_kv_len, self.window or 0, ctx.n_seg * self.K)
             pa = pm = None
             if any_short:
                 pa = ctx.buf("attn_part_acc", (ctx.n_seg * self.K * splits * 16 * self.hd,), torch.float32)

@@ -80,7 +80,7 @@ def attention(a) -> None:
     lens = torch.full((B,), L, dtype=torch.int32, device=dev)
     pos0 = torch.full((B,), ctx - L, dtype=torch.int32, device=dev)
     short = L * (H // K) <= 16
-    splits = kernels.attention_mma_splits(ctx, 0)
+    splits = kernels.attention_mma_splits(ctx, 0, B * K)
     pa = torch.empty(B * K * splits * 16 * hd, device=dev)
     pm = torch.empty(B * K * splits * 32, device=dev)
 
