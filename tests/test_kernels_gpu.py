@@ -289,11 +289,13 @@ def test_attention_finds_a_far_key(kind):
         assert float(err) <= 1.2e-2, (key_pos, float(err))
 
 
-def test_fused_finishes_match_the_separate_kernels():
-    """Deferred split-K products finished by the fused kernels give what product + separate kernels give."""
+@pytest.mark.parametrize("n,d", [(6, 200), (6, 1000), (3, 4096), (13, 5128), (70, 1000)])
+def test_fused_finishes_match_the_separate_kernels(n, d):
+    """Deferred split-K products finished by the fused kernels give what product + separate kernels give
+    (one block per token for narrow rows or many tokens, a cluster of blocks per token otherwise)."""
     from xyntetik_runner_b200 import kernels
     g = torch.Generator().manual_seed(3)
-    n, d, k = 6, 200, 1024
+    k = 1024
     x_in = torch.randn(n, k, generator=g).to(torch.bfloat16).to(DEV)
     w = (torch.randn(d, k, generator=g) / 32).to(torch.bfloat16).to(DEV)
     bias = torch.randn(d, generator=g).to(DEV)

@@ -72,13 +72,106 @@ k_finish_add_rmsnorm(const float* __restrict__ partial, int splits, int n, const
     for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = xr_from_f32<TO>(xr[i] * scale * w[i]);
 }
 
+// The same for few tokens: a cluster of FIN_CLUSTER blocks per token, each block owning a contiguous slice of
+// the row, so that the partial sums are read by eight times as many threads.  The slices' sums of squares
+// meet through distributed shared memory and every block adds them in rank order.
+#define FIN_CLUSTER 8
+#define FIN_CL_PER 4
+__device__ __forceinline__ uint32_t fin_cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void fin_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float fin_cluster_read(const float* mine, uint32_t rank) {
+    uint32_t local = (uint32_t)__cvta_generic_to_shared(mine), remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(256)
+k_finish_add_rmsnorm_cluster(const float* __restrict__ partial, int splits, int n, const float* __restrict__ bias,
+                             float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out, int d, int slice, float eps) {
+    xr_pdl_wait();
+    xr_pdl_launch();
+    __shared__ float scratch[33];
+    __shared__ float slice_ss;
+    const int t = blockIdx.x / FIN_CLUSTER;
+    const int rank = (int)fin_cluster_rank();
+    const int c0 = rank * slice, c1 = min(d, c0 + slice);          // slice <= FIN_CL_PER * blockDim.x
+    float* xr = x + (size_t)t * d;
+    TO* o = out + (size_t)t * d;
+    const float* p = partial + (size_t)t * d + c0 + threadIdx.x;
+    const size_t split_stride = (size_t)n * d;
+    float acc[FIN_CL_PER];
+#pragma unroll
+    for (int k = 0; k < FIN_CL_PER; k++) acc[k] = 0.f;
+#pragma unroll 4
+    for (int s = 0; s < splits; s++) {
+        float v[FIN_CL_PER];
+#pragma unroll
+        for (int k = 0; k < FIN_CL_PER; k++) v[k] = c0 + (int)(threadIdx.x + k * blockDim.x) < c1 ? __ldcg(p + (size_t)s * split_stride + k * blockDim.x) : 0.f;
+#pragma unroll
+        for (int k = 0; k < FIN_CL_PER; k++) acc[k] += v[k];
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < FIN_CL_PER; k++) {
+        int i = c0 + threadIdx.x + k * blockDim.x;
+        if (i < c1) {
+            float v = acc[k];
+            if (bias) v += bias[i];
+            v = xr[i] + v;
+            xr[i] = v;
+            acc[k] = v;
+            ss += v * v;
+        }
+    }
+    ss = xr_block_sum(ss, scratch);
+    if (threadIdx.x == 0) slice_ss = ss;
+    fin_cluster_sync();
+    float total = 0.f;
+#pragma unroll
+    for (int r = 0; r < FIN_CLUSTER; r++) total += fin_cluster_read(&slice_ss, (uint32_t)r);
+    float scale = 1.0f / sqrtf(total / (float)d + eps);
+#pragma unroll
+    for (int k = 0; k < FIN_CL_PER; k++) {
+        int i = c0 + threadIdx.x + k * blockDim.x;
+        if (i < c1) o[i] = xr_from_f32<TO>(acc[k] * scale * w[i]);
+    }
+    fin_cluster_sync();            // no block leaves while another may still read its shared memory
+}
+
+template <typename TO>
+static int launch_finish_cluster(const float* partial, int splits, const float* bias, float* x, const float* w, TO* out,
+                                 int n, int d, int slice, float eps, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n * FIN_CLUSTER); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = 0; cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = FIN_CLUSTER; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = xr_pdl_enabled() ? 2 : 1;
+    cudaLaunchKernelEx(&cfg, k_finish_add_rmsnorm_cluster<TO>, partial, splits, n, bias, x, w, out, d, slice, eps);
+    return xr_launch_status();
+}
+
 XR_EXPORT int xr_finish_add_rmsnorm(const float* partial, int splits, const float* bias, float* x, const float* w, void* out,
                                     int out_dtype, int n, int d, float eps, cudaStream_t stream) {
     if (n < 1 || d < 1 || splits < 1) return XR_ERR_ARG;
+    if (out_dtype != XR_F32 && out_dtype != XR_BF16) return XR_ERR_ARG;
+    const int slice = (d + FIN_CLUSTER - 1) / FIN_CLUSTER;
+    if (n <= 64 && d >= 512 && slice <= FIN_CL_PER * 256) {      // few tokens and a row worth cutting up
+        if (out_dtype == XR_F32) return launch_finish_cluster<float>(partial, splits, bias, x, w, (float*)out, n, d, slice, eps, stream);
+        return launch_finish_cluster<__nv_bfloat16>(partial, splits, bias, x, w, (__nv_bfloat16*)out, n, d, slice, eps, stream);
+    }
     int threads = d >= 4096 ? 1024 : (d >= 1024 ? 512 : 256);      // few tokens, so many threads per token
     if (out_dtype == XR_F32) xr_launch((k_finish_add_rmsnorm<float>), dim3(n), dim3(threads), 0, stream, partial, splits, n, bias, x, w, (float*)out, d, eps);
-    else if (out_dtype == XR_BF16) xr_launch((k_finish_add_rmsnorm<__nv_bfloat16>), dim3(n), dim3(threads), 0, stream, partial, splits, n, bias, x, w, (__nv_bfloat16*)out, d, eps);
-    else return XR_ERR_ARG;
+    else xr_launch((k_finish_add_rmsnorm<__nv_bfloat16>), dim3(n), dim3(threads), 0, stream, partial, splits, n, bias, x, w, (__nv_bfloat16*)out, d, eps);
     return xr_launch_status();
 }
 
