@@ -284,8 +284,8 @@ __device__ __forceinline__ void load_q(__nv_bfloat16* qs, const AttnMmaArgs& a, 
 template <int HD>
 __global__ void __launch_bounds__(ATT_THREADS)
 k_attention_rows(AttnMmaArgs a) {
-    xr_pdl_wait();
     xr_pdl_launch();
+    xr_pdl_wait();
     constexpr int LD = HD + 8;
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __nv_bfloat16* qs = (__nv_bfloat16*)smem_raw;                 // [64][LD]
@@ -356,8 +356,8 @@ k_attention_rows(AttnMmaArgs a) {
 template <int HD, int ATT_KSTAGES>
 __global__ void __launch_bounds__(ATT_THREADS)
 k_attention_keys(AttnMmaArgs a) {
-    xr_pdl_wait();
     xr_pdl_launch();
+    xr_pdl_wait();
     constexpr int LD = HD + 8;
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __nv_bfloat16* qs = (__nv_bfloat16*)smem_raw;                 // [16][LD]
@@ -479,8 +479,8 @@ __device__ __forceinline__ bool att_mbar_wait(uint64_t* bar, uint32_t parity) {
 template <int HD, int STAGES>
 __global__ void __launch_bounds__(ATT_THREADS)
 k_attention_keys_tma(const __grid_constant__ CUtensorMap cache_map, AttnMmaArgs a) {
-    xr_pdl_wait();
     xr_pdl_launch();
+    xr_pdl_wait();
     constexpr int LD = HD + 8;
     constexpr int TILE_ELEMS = ATT_TILE * HD;                      // one K (or V) tile, swizzled sub-tiles of 64 columns
     extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -631,8 +631,8 @@ k_attention_keys_tma(const __grid_constant__ CUtensorMap cache_map, AttnMmaArgs 
 template <int HD>
 __global__ void __launch_bounds__(MERGE_THREADS)
 k_attention_merge(AttnMmaArgs a) {
-    xr_pdl_wait();
     xr_pdl_launch();
+    xr_pdl_wait();
     __shared__ float wgt[16][MERGE_SPANS + 1];
     __shared__ float row_max[16], row_inv[16];
     __shared__ float4 group_sum[MERGE_THREADS];

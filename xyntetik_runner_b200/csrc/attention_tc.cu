@@ -169,8 +169,8 @@ k_attention_tc(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;          // tiles with the most keys start first
     const int row0 = tile * TA_ROWS;
     if (rows_total <= 16 || row0 >= rows_total) return;             // short portions belong to the key-split kernel
-    xr_pdl_wait();
     xr_pdl_launch();
+    xr_pdl_wait();
     const int pos0 = a.seg_pos0[seg], tok_base = a.seg_start[seg];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int last_row = min(rows_total, row0 + TA_ROWS) - 1;

@@ -11,8 +11,8 @@
 template <typename TW>
 __global__ void k_embed(const TW* __restrict__ table, const int* __restrict__ ids, float* __restrict__ x,
                         int d, int vocab) {
-    xr_pdl_wait();
     xr_pdl_launch();
+    xr_pdl_wait();
     int t = blockIdx.x;
     int id = ids[t];
     if (id < 0 || id >= vocab) id = 0;
@@ -39,8 +39,8 @@ XR_EXPORT int xr_embed(const void* table, int table_dtype, const int* ids, float
 template <typename TO>
 __global__ void k_rmsnorm(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ w,
                           TO* __restrict__ out, int d, float eps) {
-    xr_pdl_wait();
     xr_pdl_launch();
+    xr_pdl_wait();
     __shared__ float scratch[33];
     int r = rows ? rows[blockIdx.x] : blockIdx.x;
     const float* xr = x + (size_t)r * d;
@@ -109,8 +109,8 @@ struct RopeStoreArgs {
 // pos * inv_freq[j] and its cosine and sine are computed once and used for all the Q and K heads.
 template <typename T>
 __global__ void k_rope_store(RopeStoreArgs a) {
-    xr_pdl_wait();
     xr_pdl_launch();
+    xr_pdl_wait();
     const int t = blockIdx.x;
     const int qkv_dim = (a.H + 2 * a.K) * a.hd;
     T* row = (T*)a.qkv + (size_t)t * qkv_dim;
@@ -175,8 +175,8 @@ XR_EXPORT int xr_rope_store(void* qkv, int dtype, const int* positions, const in
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void k_silu_mul(const T* __restrict__ gu, T* __restrict__ h, int n, int F) {
-    xr_pdl_wait();
     xr_pdl_launch();
+    xr_pdl_wait();
     size_t total = (size_t)n * F;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         size_t t = i / F, f = i % F;
@@ -202,8 +202,8 @@ XR_EXPORT int xr_silu_mul(const void* gu, void* h, int dtype, int n, int F, cuda
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void k_residual_add(float* __restrict__ x, const T* __restrict__ dlt, size_t total) {
-    xr_pdl_wait();
     xr_pdl_launch();
+    xr_pdl_wait();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
         x[i] += xr_to_f32<T>(dlt[i]);
 }

@@ -15,8 +15,8 @@ template <typename TO>
 __global__ void __launch_bounds__(1024)
 k_finish_add_rmsnorm(const float* __restrict__ partial, int splits, int n, const float* __restrict__ bias,
                      float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out, int d, float eps) {
-    xr_pdl_wait();
     xr_pdl_launch();
+    xr_pdl_wait();
     __shared__ float scratch[33];
     const int t = blockIdx.x;
     float* xr = x + (size_t)t * d;
@@ -94,8 +94,8 @@ template <typename TO>
 __global__ void __launch_bounds__(256)
 k_finish_add_rmsnorm_cluster(const float* __restrict__ partial, int splits, int n, const float* __restrict__ bias,
                              float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out, int d, int slice, float eps) {
-    xr_pdl_wait();
     xr_pdl_launch();
+    xr_pdl_wait();
     __shared__ float scratch[33];
     __shared__ float slice_ss;
     const int t = blockIdx.x / FIN_CLUSTER;
@@ -179,8 +179,8 @@ XR_EXPORT int xr_finish_add_rmsnorm(const float* partial, int splits, const floa
 template <typename TO, bool ACCUM>
 __global__ void k_finish_plain(const float* __restrict__ partial, int splits, int n, int width, const float* __restrict__ bias,
                                TO* __restrict__ out, long long ldo) {
-    xr_pdl_wait();
     xr_pdl_launch();
+    xr_pdl_wait();
     size_t total = (size_t)n * width;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         size_t t = i / width, r = i % width;
@@ -221,8 +221,8 @@ struct FinishRopeArgs {
 };
 
 __global__ void k_finish_rope_store(FinishRopeArgs a) {
-    xr_pdl_wait();
     xr_pdl_launch();
+    xr_pdl_wait();
     int t = blockIdx.x, head = blockIdx.y;
     int qkv_dim = (a.H + 2 * a.K) * a.hd;
     int col0 = head * a.hd;

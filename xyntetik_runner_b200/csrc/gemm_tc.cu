@@ -34,6 +34,8 @@
 #define TC_BM 128          // W rows per CTA (the M of the instruction)
 #define TC_BK 64           // K elements per stage: 128 bytes, one swizzle atom
 #define TC_THREADS 320       // producer warp, MMA warp, eight epilogue warps
+// a tile of 16 tokens is one chunk of accumulator columns: four epilogue warps are all it can use
+__host__ __device__ constexpr int tc_threads(int bn) { return bn <= 16 ? 192 : TC_THREADS; }
 #define XR_SPIN_LIMIT (1u << 24)
 
 #define TC_EPI_STORE 0     // out[t][r] = acc (+ bias), bfloat16 or float32
@@ -140,7 +142,7 @@ struct TcParams {
 // launch order, so W comes from HBM once and from L2 for the others.
 // ---------------------------------------------------------------------------------------------
 template <int BN, int STAGES, bool DUAL, int MINB>
-__global__ void __launch_bounds__(TC_THREADS, MINB)
+__global__ void __launch_bounds__(tc_threads(BN), MINB)
 k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     constexpr int W_BYTES = TC_BM * TC_BK * 2;
@@ -163,6 +165,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     const int kb1 = (int)(((long long)(blockIdx.z + 1) * total_kb) / p.splits);
     const int nkb = kb1 - kb0;                     // >= 1: splits <= total_kb
 
+    xr_pdl_launch();
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         mbar_init(acc_ready, 1);
@@ -177,30 +180,39 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    // everything above touched no global memory; from here on the kernel before this one must be complete
+    // Everything above touched no global memory.  The weights are constants, so the producer fills its ring with
+    // them before the kernel ahead in the stream is known to be complete; the tokens are read only after that.
+    auto load_w = [&](int i) {
+        int s = i % STAGES;
+        uint8_t* st = smem + s * STAGE_BYTES;
+        mbar_expect_tx(&full[s], STAGE_BYTES);
+        if (p.packed) {
+            // tile (row tile, K block) is 128 consecutive rows of 64 elements: one contiguous 16 KB read
+            int y = (blockIdx.y * p.w_kblocks + kb0 + i) * TC_BM;
+            tma_load_2d(st, &map_w, 0, y, &full[s]);
+            if (DUAL) tma_load_2d(st + W_BYTES, &map_w, 0, y + (p.up_row_offset / TC_BM) * p.w_kblocks * TC_BM, &full[s]);
+        } else {
+            int kx = (kb0 + i) * TC_BK;
+            tma_load_2d(st, &map_w, kx, row0, &full[s]);
+            if (DUAL) tma_load_2d(st + W_BYTES, &map_w, kx, p.up_row_offset + row0, &full[s]);
+        }
+    };
+    const int early = nkb < STAGES ? nkb : STAGES;
+    if (warp == 0 && lane == 0)
+        for (int i = 0; i < early; i++) load_w(i);
     xr_pdl_wait();
-    xr_pdl_launch();
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            int issued = 0;
+            int issued = early;
             for (int i = 0; i < nkb; i++) {
                 int s = i % STAGES;
-                if (i >= STAGES && !mbar_wait(&empty[s], ((i / STAGES) - 1) & 1, abort_flag)) break;
-                uint8_t* st = smem + s * STAGE_BYTES;
-                mbar_expect_tx(&full[s], STAGE_BYTES);
-                int kx = (kb0 + i) * TC_BK;
-                if (p.packed) {
-                    // tile (row tile, K block) is 128 consecutive rows of 64 elements: one contiguous 16 KB read
-                    int y = (blockIdx.y * p.w_kblocks + kb0 + i) * TC_BM;
-                    tma_load_2d(st, &map_w, 0, y, &full[s]);
-                    if (DUAL) tma_load_2d(st + W_BYTES, &map_w, 0, y + (p.up_row_offset / TC_BM) * p.w_kblocks * TC_BM, &full[s]);
-                } else {
-                    tma_load_2d(st, &map_w, kx, row0, &full[s]);
-                    if (DUAL) tma_load_2d(st + W_BYTES, &map_w, kx, p.up_row_offset + row0, &full[s]);
+                if (i >= STAGES) {
+                    if (!mbar_wait(&empty[s], ((i / STAGES) - 1) & 1, abort_flag)) break;
+                    load_w(i);
                 }
-                tma_load_2d(st + W_BYTES * (DUAL ? 2 : 1), &map_x, kx, tok0, &full[s]);
+                tma_load_2d(smem + s * STAGE_BYTES + W_BYTES * (DUAL ? 2 : 1), &map_x, (kb0 + i) * TC_BK, tok0, &full[s]);
                 issued = i + 1;
             }
             if (*abort_flag) {
@@ -302,8 +314,8 @@ struct FinishParams {
 };
 
 __global__ void k_splitk_finish(FinishParams p) {
-    xr_pdl_wait();
     xr_pdl_launch();
+    xr_pdl_wait();
     size_t total = (size_t)p.n * p.n_out;
     size_t width = p.dual ? 2 * (size_t)p.n_out : (size_t)p.n_out;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
@@ -366,7 +378,7 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParam
             return XR_ERR_LAUNCH;
         configured = true;
     }
-    xr_launch((k_gemm_tc<BN, STAGES, DUAL, MINB>), dim3(grid), dim3(TC_THREADS), SMEM, stream, mw, mx, p);
+    xr_launch((k_gemm_tc<BN, STAGES, DUAL, MINB>), dim3(grid), dim3(tc_threads(BN)), SMEM, stream, mw, mx, p);
     return xr_launch_status();
 }
 
@@ -436,7 +448,7 @@ XR_EXPORT int xr_gemm_tc(const void* X, const void* W, const float* bias, void* 
     int rc;
     if (!dual) {
         switch (bn) {
-            case 16: rc = launch_tc<16, 6, false, 2>(mw, mx, p, grid, stream); break;
+            case 16: rc = launch_tc<16, 4, false, 3>(mw, mx, p, grid, stream); break;
             case 32: rc = launch_tc<32, 5, false, 2>(mw, mx, p, grid, stream); break;
             case 64: rc = launch_tc<64, 4, false, 2>(mw, mx, p, grid, stream); break;
             case 128: rc = launch_tc<128, 5, false, 1>(mw, mx, p, grid, stream); break;

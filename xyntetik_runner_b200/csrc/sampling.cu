@@ -109,8 +109,8 @@ __device__ int nth_equal_id(int V, const float* vals, unsigned thr, long long n,
 
 __global__ void __launch_bounds__(SMP_THREADS)
 k_sample(SampleArgs a, float* scratch /* [rows, V] scaled values, or null when nothing needs them */) {
-    xr_pdl_wait();
     xr_pdl_launch();
+    xr_pdl_wait();
     __shared__ double sh[40 + SMP_THREADS];
     __shared__ float sh_f[33];
     __shared__ int sh_i[33];
