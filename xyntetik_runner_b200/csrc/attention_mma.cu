@@ -480,7 +480,6 @@ template <int HD, int STAGES>
 __global__ void __launch_bounds__(ATT_THREADS)
 k_attention_keys_tma(const __grid_constant__ CUtensorMap cache_map, AttnMmaArgs a) {
     xr_pdl_launch();
-    xr_pdl_wait();
     constexpr int LD = HD + 8;
     constexpr int TILE_ELEMS = ATT_TILE * HD;                      // one K (or V) tile, swizzled sub-tiles of 64 columns
     extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -534,7 +533,13 @@ k_attention_keys_tma(const __grid_constant__ CUtensorMap cache_map, AttnMmaArgs 
             }
         }
     };
-    if (threadIdx.x == 0)
+    // The step's description and the keys of earlier steps do not change while the step runs: a span that ends
+    // before the step's own tokens starts its copies before the kernel ahead in the stream is complete.
+    const bool old_keys_only = hi < pos0;
+    if (threadIdx.x == 0 && old_keys_only)
+        for (int i = 0; i < STAGES - 1 && t_lo + i <= t_hi; i++) fetch(t_lo + i, i);
+    xr_pdl_wait();
+    if (threadIdx.x == 0 && !old_keys_only)
         for (int i = 0; i < STAGES - 1 && t_lo + i <= t_hi; i++) fetch(t_lo + i, i);
     load_q<HD>(qs, a, tok_base, kvh, 0, 16, rows_total);
     __syncthreads();
