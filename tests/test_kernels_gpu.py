@@ -116,7 +116,7 @@ def test_gemm_simt_is_independent_of_the_batch():
         assert torch.equal(one[0], full[t])
 
 
-@pytest.mark.parametrize("n,d", [(1, 16), (5, 100), (3, 4096), (2, 5000)])
+@pytest.mark.parametrize("n,d", [(1, 16), (5, 100), (3, 4096), (2, 5000), (7, 5128), (3, 4090), (300, 1028), (2, 40000)])
 def test_rmsnorm_and_row_gather(n, d):
     from xyntetik_runner_b200 import kernels
     x = torch.randn(n + 3, d) * 3

@@ -140,32 +140,39 @@ def test_parts_alone(setup, name, dtype):
     eng.end("c")
 
 
-def test_rotation_and_store_kernel_at_other_sizes():
-    """rope_store with a partial rotary dimension and odd page size against the plain rotation."""
+@pytest.mark.parametrize("dtype,hd,rot", [(torch.float32, 80, 48), (torch.bfloat16, 80, 48), (torch.bfloat16, 72, 40),
+                                          (torch.bfloat16, 128, 128), (torch.bfloat16, 64, 0)])
+def test_rotation_and_store_kernel_at_other_sizes(dtype, hd, rot):
+    """rope_store with a partial rotary dimension and odd page size against the plain rotation: float32, and
+    bfloat16 on its 16-byte vector path (head size a multiple of 8, rotated width of 16) and off it."""
     from plain_llama import rope_inv_freq
     from xyntetik_runner_b200 import kernels
-    H, K, hd, rot, page, n = 5, 1, 80, 48, 5, 9
+    H, K, page, n = 5, 1, 5, 9
     rng = np.random.RandomState(0)
     qkv = rng.randn(n, (H + 2 * K) * hd).astype(np.float32)
+    qkv = torch.from_numpy(qkv).to(dtype).float().numpy()            # values the dtype holds exactly
+    tol = 1e-5 if dtype == torch.float32 else 2.0 ** -8 * 6
     positions = np.array([0, 1, 2, 3, 4, 5, 6, 300, 301], dtype=np.int32)
     tok_seg = np.array([0] * 7 + [1, 1], dtype=np.int32)
     bt = np.full((2, 62), -1, dtype=np.int32)
     bt[0, :2] = [3, 1]
     bt[1, 60] = 0
-    inv = rope_inv_freq(1234.5, rot)
-    cache = torch.zeros(4, 1, 2, K, page, hd, device="cuda")
-    t = torch.from_numpy(qkv).cuda()
+    inv = rope_inv_freq(1234.5, rot) if rot else np.zeros(0, dtype=np.float32)
+    cache = torch.zeros(4, 1, 2, K, page, hd, device="cuda", dtype=dtype)
+    t = torch.from_numpy(qkv).cuda().to(dtype)
     kernels.rope_store(t, torch.from_numpy(positions).cuda(), torch.from_numpy(tok_seg).cuda(), torch.from_numpy(bt).cuda(),
-                       torch.from_numpy(inv).cuda(), cache.data_ptr(), cache.stride(0), cache.stride(2), H, K, hd, rot, 62, page)
+                       torch.from_numpy(inv).cuda() if rot else None, cache.data_ptr(), cache.stride(0), cache.stride(2),
+                       H, K, hd, rot, 62, page)
     q_ref = qkv[:, :H * hd].reshape(n, H, hd).copy()
     k_ref = qkv[:, H * hd:(H + K) * hd].reshape(n, K, hd).copy()
-    q_ref[:, :, :rot] = rope_apply(q_ref[:, :, :rot], positions, inv)
-    k_ref[:, :, :rot] = rope_apply(k_ref[:, :, :rot], positions, inv)
-    got = t.cpu().numpy()
-    assert np.abs(got[:, :H * hd].reshape(n, H, hd) - q_ref).max() < 1e-5
-    c = cache.cpu().numpy()
+    if rot:
+        q_ref[:, :, :rot] = rope_apply(q_ref[:, :, :rot], positions, inv)
+        k_ref[:, :, :rot] = rope_apply(k_ref[:, :, :rot], positions, inv)
+    got = t.float().cpu().numpy()
+    assert np.abs(got[:, :H * hd].reshape(n, H, hd) - q_ref).max() < tol
+    c = cache.float().cpu().numpy()
     for i in range(n):
         pg = bt[tok_seg[i], positions[i] // page]
-        assert np.abs(c[pg, 0, 0, :, positions[i] % page] - k_ref[i]).max() < 1e-5
+        assert np.abs(c[pg, 0, 0, :, positions[i] % page] - k_ref[i]).max() < tol
         assert np.array_equal(c[pg, 0, 1, :, positions[i] % page], qkv[i, (H + K) * hd:].reshape(K, hd))
     assert np.count_nonzero(c) == n * 2 * K * hd                      # nothing else was written

@@ -71,9 +71,59 @@ __global__ void k_rmsnorm(const float* __restrict__ x, const int* __restrict__ r
     for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = xr_from_f32<TO>(xr[i] * scale * w[i]);
 }
 
+// Rows whose width is a multiple of four: a thread keeps up to eight float4 of the row, so a row needs few
+// threads (width / 32) and many rows are in flight on an SM at once.  The block size, and with it the order
+// of the sum, is a function of the width alone.
+__device__ __forceinline__ void rms_store4(float* o, float4 v) { *reinterpret_cast<float4*>(o) = v; }
+__device__ __forceinline__ void rms_store4(__nv_bfloat16* o, float4 v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<uint32_t*>(&a); u.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(o) = u;
+}
+template <typename TO>
+__global__ void k_rmsnorm_vec(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ w,
+                              TO* __restrict__ out, int d, float eps) {
+    xr_pdl_launch();
+    xr_pdl_wait();
+    __shared__ float scratch[33];
+    constexpr int PER = 8;
+    const int r = rows ? rows[blockIdx.x] : blockIdx.x;
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)r * d);
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+    TO* o = out + (size_t)blockIdx.x * d;
+    const int quads = d >> 2;
+    float4 v[PER];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < PER; k++) {
+        int i = threadIdx.x + k * blockDim.x;
+        v[k] = i < quads ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int k = 0; k < PER; k++) ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+    ss = xr_block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)d + eps);
+#pragma unroll
+    for (int k = 0; k < PER; k++) {
+        int i = threadIdx.x + k * blockDim.x;
+        if (i < quads) {
+            float4 g = w4[i];
+            rms_store4(o + 4 * (size_t)i, make_float4(v[k].x * scale * g.x, v[k].y * scale * g.y, v[k].z * scale * g.z, v[k].w * scale * g.w));
+        }
+    }
+}
+
 XR_EXPORT int xr_rmsnorm(const float* x, const int* rows, const float* w, void* out, int out_dtype, int n, int d,
                          float eps, cudaStream_t stream) {
     if (n < 1 || d < 1) return XR_ERR_ARG;
+    if (out_dtype != XR_F32 && out_dtype != XR_BF16) return XR_ERR_ARG;
+    if ((d & 3) == 0 && d <= 32 * 1024 && (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) == 0) {
+        int threads = (((d / 4 + 7) / 8 + 31) / 32) * 32;          // eight float4 per thread cover the row
+        if (out_dtype == XR_F32) xr_launch((k_rmsnorm_vec<float>), dim3(n), dim3(threads), 0, stream, x, rows, w, (float*)out, d, eps);
+        else xr_launch((k_rmsnorm_vec<__nv_bfloat16>), dim3(n), dim3(threads), 0, stream, x, rows, w, (__nv_bfloat16*)out, d, eps);
+        return xr_launch_status();
+    }
     int threads = d >= 2048 ? 512 : 256;
     if (out_dtype == XR_F32) xr_launch((k_rmsnorm<float>), dim3(n), dim3(threads), 0, stream, x, rows, w, (float*)out, d, eps);
     else if (out_dtype == XR_BF16) xr_launch((k_rmsnorm<__nv_bfloat16>), dim3(n), dim3(threads), 0, stream, x, rows, w, (__nv_bfloat16*)out, d, eps);
@@ -152,6 +202,63 @@ __global__ void k_rope_store(RopeStoreArgs a) {
     }
 }
 
+// bfloat16 rows whose head size and rotated width are multiples of eight and sixteen: every access is a
+// 16-byte vector of eight elements.  The cosines and sines of the token's angles are computed once, in
+// shared memory; a thread then takes (head, group of eight pairs) units.
+struct __align__(16) Bf16x8 { __nv_bfloat162 p[4]; };
+__global__ void __launch_bounds__(256)
+k_rope_store_vec(RopeStoreArgs a) {
+    xr_pdl_launch();
+    xr_pdl_wait();
+    extern __shared__ float rope_cs[];                 // [half] cosines, [half] sines
+    const int t = blockIdx.x;
+    const int qkv_dim = (a.H + 2 * a.K) * a.hd;
+    __nv_bfloat16* row = (__nv_bfloat16*)a.qkv + (size_t)t * qkv_dim;
+    const int pos = a.positions[t];
+    const int half = a.rotary_dim >> 1;
+    __nv_bfloat16* kdst = nullptr;
+    if (a.cache_k != nullptr) {
+        int page = a.block_tables[(size_t)a.tok_seg[t] * a.max_pages + pos / a.page_size];
+        kdst = (__nv_bfloat16*)a.cache_k + (size_t)page * a.page_stride + (size_t)(pos % a.page_size) * a.hd;
+    }
+    const size_t head_step = (size_t)a.page_size * a.hd;
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+        float ang = (float)pos * a.inv_freq[j];
+        rope_cs[j] = cosf(ang);
+        rope_cs[half + j] = sinf(ang);
+    }
+    __syncthreads();
+    const int groups = half >> 3;                      // groups of eight pairs per head
+    const int rot_heads = kdst ? a.H + a.K : a.H;      // without a cache to write, K is not needed
+    for (int u = threadIdx.x; u < rot_heads * groups; u += blockDim.x) {
+        int head = u / groups, j0 = (u % groups) << 3;
+        __nv_bfloat16* src = row + (size_t)head * a.hd + j0;
+        Bf16x8 lo = *reinterpret_cast<const Bf16x8*>(src), hi = *reinterpret_cast<const Bf16x8*>(src + half);
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            float2 x0 = __bfloat1622float2(lo.p[k]), x1 = __bfloat1622float2(hi.p[k]);
+            float c0 = rope_cs[j0 + 2 * k], c1 = rope_cs[j0 + 2 * k + 1];
+            float s0 = rope_cs[half + j0 + 2 * k], s1 = rope_cs[half + j0 + 2 * k + 1];
+            lo.p[k] = __floats2bfloat162_rn(x0.x * c0 - x1.x * s0, x0.y * c1 - x1.y * s1);
+            hi.p[k] = __floats2bfloat162_rn(x0.x * s0 + x1.x * c0, x0.y * s1 + x1.y * c1);
+        }
+        __nv_bfloat16* dst = head < a.H ? src : kdst + (size_t)(head - a.H) * head_step + j0;
+        *reinterpret_cast<Bf16x8*>(dst) = lo;
+        *reinterpret_cast<Bf16x8*>(dst + half) = hi;
+    }
+    if (kdst == nullptr) return;
+    const int tail8 = (a.hd - 2 * half) >> 3, hd8 = a.hd >> 3;
+    for (int i = threadIdx.x; i < a.K * tail8; i += blockDim.x) {
+        int kvh = i / tail8, e = 2 * half + ((i % tail8) << 3);
+        *reinterpret_cast<Bf16x8*>(kdst + (size_t)kvh * head_step + e) = *reinterpret_cast<const Bf16x8*>(row + (size_t)(a.H + kvh) * a.hd + e);
+    }
+    __nv_bfloat16* vdst = kdst + a.v_offset;
+    for (int i = threadIdx.x; i < a.K * hd8; i += blockDim.x) {
+        int kvh = i / hd8, e = (i % hd8) << 3;
+        *reinterpret_cast<Bf16x8*>(vdst + (size_t)kvh * head_step + e) = *reinterpret_cast<const Bf16x8*>(row + (size_t)(a.H + a.K + kvh) * a.hd + e);
+    }
+}
+
 XR_EXPORT int xr_rope_store(void* qkv, int dtype, const int* positions, const int* tok_seg, const int* block_tables,
                             const float* inv_freq, void* cache_k, long long page_stride, long long v_offset,
                             int n, int H, int K, int hd, int rotary_dim, int max_pages, int page_size,
@@ -162,6 +269,11 @@ XR_EXPORT int xr_rope_store(void* qkv, int dtype, const int* positions, const in
     RopeStoreArgs a{qkv, positions, tok_seg, block_tables, inv_freq, cache_k, page_stride, v_offset,
                     n, H, K, hd, rotary_dim, max_pages, page_size};
     int threads = 256;
+    if (dtype == XR_BF16 && (hd & 7) == 0 && (rotary_dim & 15) == 0 && ((uintptr_t)qkv & 15) == 0 &&
+        (cache_k == nullptr || ((((uintptr_t)cache_k) & 15) == 0 && (page_stride & 7) == 0 && (v_offset & 7) == 0))) {
+        xr_launch(k_rope_store_vec, dim3(n), dim3(threads), (size_t)rotary_dim * sizeof(float), stream, a);
+        return xr_launch_status();
+    }
     if (dtype == XR_F32) xr_launch((k_rope_store<float>), dim3(n), dim3(threads), 0, stream, a);
     else if (dtype == XR_BF16) xr_launch((k_rope_store<__nv_bfloat16>), dim3(n), dim3(threads), 0, stream, a);
     else return XR_ERR_ARG;
