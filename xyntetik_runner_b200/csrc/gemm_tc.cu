@@ -133,6 +133,7 @@ struct TcParams {
     int splits;                 // z-slices of the grid; slice z handles K blocks [z*total/splits, (z+1)*total/splits)
     int epilogue, out_dtype;
     int up_row_offset;          // SwiGLU: rows of the up projection start here in W (packed: in units of rows too)
+    int bn;                     // tokens per tile: a multiple of 16, at most the kernel's BN (which sizes the buffers)
     int packed;                 // W is stored tile by tile: [row tile][K block][128][64], see xr_gemm_tc
     int w_kblocks;              // packed: K blocks per row tile in the packed array
 };
@@ -159,7 +160,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row0 = blockIdx.y * TC_BM, tok0 = blockIdx.x * BN;
+    const int row0 = blockIdx.y * TC_BM, tok0 = blockIdx.x * p.bn;
     const int total_kb = (p.K + TC_BK - 1) / TC_BK;
     const int kb0 = (int)(((long long)blockIdx.z * total_kb) / p.splits);
     const int kb1 = (int)(((long long)(blockIdx.z + 1) * total_kb) / p.splits);
@@ -185,7 +186,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     auto load_w = [&](int i) {
         int s = i % STAGES;
         uint8_t* st = smem + s * STAGE_BYTES;
-        mbar_expect_tx(&full[s], STAGE_BYTES);
+        mbar_expect_tx(&full[s], W_BYTES * (DUAL ? 2 : 1) + p.bn * TC_BK * 2);
         if (p.packed) {
             // tile (row tile, K block) is 128 consecutive rows of 64 elements: one contiguous 16 KB read
             int y = (blockIdx.y * p.w_kblocks + kb0 + i) * TC_BM;
@@ -224,7 +225,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            constexpr uint32_t idesc = instr_desc(BN);
+            const uint32_t idesc = instr_desc(p.bn);
             bool ok = true;
             for (int i = 0; i < nkb && ok; i++) {
                 int s = i % STAGES;
@@ -256,7 +257,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             const float b = (p.bias != nullptr && row_ok && (p.epilogue == TC_EPI_STORE || p.epilogue == TC_EPI_ADD) && blockIdx.z == 0)
                                 ? p.bias[r] : 0.f;
 #pragma unroll 1
-            for (int c0 = chunk_first * 16; c0 < BN; c0 += 32) {
+            for (int c0 = chunk_first * 16; c0 < p.bn; c0 += 32) {
                 if (tok0 + c0 >= p.n) break;               // warp-uniform
                 float g[16], u[16];
                 tc_ld16(taddr + c0, g);
@@ -406,6 +407,19 @@ static int choose_splits(int tiles, int tok_tiles, int total_kb, int slots) {
     return best;
 }
 
+// Tokens per tile for a kernel whose buffers hold `cap` of them: up to `cap` tokens, the tokens rounded up to the
+// instruction's step of 16 (no work on padding); more, `cap` -- narrower tiles that would fill the last wave
+// better were measured (144..240 at 2,048 tokens) and are no faster, the product being bound by the operand
+// traffic of its tiles rather than by the number of waves.  The width changes nothing in the sums: every
+// output element is one accumulator over all of K.  XRB200_TOKEN_TILE=<width> overrides it in tuning runs.
+static int choose_token_tile(int n, int cap) {
+    if (n <= cap) return (n + 15) / 16 * 16;
+    static int forced = -1;
+    if (forced < 0) { const char* e = getenv("XRB200_TOKEN_TILE"); forced = e ? atoi(e) : 0; }
+    if (forced >= 16 && forced <= cap && forced % 16 == 0) return forced;
+    return cap;
+}
+
 // X: [n, K] bfloat16 (row stride ldx), W: [n_out (x2 when swiglu), K] bfloat16 dense.
 // epilogue: TC_EPI_STORE / TC_EPI_ADD / TC_EPI_SWIGLU.  In SwiGLU mode W holds n_out gate rows followed by
 // n_out up rows and out is [n, n_out].  scratch: float32 workspace of at least xr_gemm_tc_scratch_floats()
@@ -434,8 +448,10 @@ XR_EXPORT int xr_gemm_tc(const void* X, const void* W, const float* bias, void* 
     if (w_packed) {
         if (!make_map(&mw, W, (long long)(dual ? 2 : 1) * rows_padded * w_kblocks, TC_BK, TC_BK, TC_BM)) return -3;
     } else if (!make_map(&mw, W, dual ? 2LL * n_out : n_out, K, K, TC_BM)) return -3;
-    if (!make_map(&mx, X, n, K, ldx, bn)) return -3;
-    int row_tiles = (n_out + TC_BM - 1) / TC_BM, tok_tiles = (n + bn - 1) / bn;
+    int row_tiles = (n_out + TC_BM - 1) / TC_BM;
+    const int bn_eff = choose_token_tile(n, bn);
+    if (!make_map(&mx, X, n, K, ldx, bn_eff)) return -3;
+    int tok_tiles = (n + bn_eff - 1) / bn_eff;
     int total_kb = (K + TC_BK - 1) / TC_BK;
     int splits = force_splits > 0 ? force_splits : choose_splits(row_tiles * tok_tiles, tok_tiles, total_kb, resident_ctas(bn, dual, 148));
     if (splits > total_kb) splits = total_kb;
@@ -443,7 +459,7 @@ XR_EXPORT int xr_gemm_tc(const void* X, const void* W, const float* bias, void* 
     if (row_tiles > 65535 || splits > 65535) return XR_ERR_ARG;
     if (splits_used) *splits_used = splits;
     TcParams p{out, bias, scratch, status, ldo, n, n_out, K, splits, splits > 1 ? TC_EPI_PARTIAL : epilogue, out_dtype,
-               w_packed ? rows_padded : n_out, w_packed, w_kblocks};
+               w_packed ? rows_padded : n_out, bn_eff, w_packed, w_kblocks};
     dim3 grid(tok_tiles, row_tiles, splits);
     int rc;
     if (!dual) {
