@@ -27,6 +27,7 @@ __device__ __forceinline__ void xr_pdl_wait() { asm volatile("griddepcontrol.wai
 __device__ __forceinline__ void xr_pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 #include <stdlib.h>
+#include <stdio.h>
 static inline bool xr_pdl_enabled() {
     static int on = -1;
     if (on < 0) { const char* e = getenv("XRB200_NO_PDL"); on = (e && e[0] && e[0] != '0') ? 0 : 1; }
@@ -47,6 +48,7 @@ static inline void xr_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
 
 static inline int xr_launch_status() {
     cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) fprintf(stderr, "[xrb200] the runtime refused a launch: %s\n", cudaGetErrorString(e));
     return e == cudaSuccess ? XR_OK : XR_ERR_LAUNCH;
 }
 

@@ -139,6 +139,59 @@ struct TcParams {
 };
 
 // ---------------------------------------------------------------------------------------------
+// Epilogue of one tile, run by warps 2..9 once the accumulators are complete.  A warp may only read the 32
+// tensor-memory lanes of its index mod 4, so two warps share each quarter and take alternate 16-column
+// chunks.  `up_cols`: column offset of the second (up) accumulator of a SwiGLU product.
+// ---------------------------------------------------------------------------------------------
+template <bool DUAL>
+__device__ __forceinline__ void tc_epilogue(const TcParams& p, uint32_t tmem_base, int up_cols, int row0, int tok0, int warp, int lane) {
+    const int quad = warp & 3, chunk_first = (warp - 2) >> 2;
+    const int r = row0 + quad * 32 + lane;            // output feature of this thread
+    const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const bool row_ok = r < p.n_out;
+    const float b = (p.bias != nullptr && row_ok && (p.epilogue == TC_EPI_STORE || p.epilogue == TC_EPI_ADD) && blockIdx.z == 0)
+                        ? p.bias[r] : 0.f;
+#pragma unroll 1
+    for (int c0 = chunk_first * 16; c0 < p.bn; c0 += 32) {
+        if (tok0 + c0 >= p.n) break;               // warp-uniform
+        float g[16], u[16];
+        tc_ld16(taddr + c0, g);
+        if (DUAL) tc_ld16(taddr + up_cols + c0, u);
+        if (!row_ok) continue;
+        if (p.epilogue == TC_EPI_ADD) {
+            // read-modify-write of the float32 residual: all loads first, so that they overlap
+            float* dst = (float*)p.out + (size_t)(tok0 + c0) * p.ldo + r;
+            float old[16];
+#pragma unroll
+            for (int c = 0; c < 16; c++) old[c] = (tok0 + c0 + c < p.n) ? dst[(size_t)c * p.ldo] : 0.f;
+#pragma unroll
+            for (int c = 0; c < 16; c++)
+                if (tok0 + c0 + c < p.n) dst[(size_t)c * p.ldo] = old[c] + (g[c] + b);
+            continue;
+        }
+#pragma unroll
+        for (int c = 0; c < 16; c++) {
+            int t = tok0 + c0 + c;
+            if (t >= p.n) break;
+            if (p.epilogue == TC_EPI_PARTIAL) {
+                size_t width = DUAL ? 2 * (size_t)p.n_out : (size_t)p.n_out;
+                float* dst = p.partial + ((size_t)blockIdx.z * p.n + t) * width;
+                dst[r] = g[c];
+                if (DUAL) dst[p.n_out + r] = u[c];
+            } else if (DUAL) {
+                float h = tc_silu(g[c]) * u[c];
+                if (p.out_dtype == XR_BF16) ((__nv_bfloat16*)p.out)[(size_t)t * p.ldo + r] = __float2bfloat16_rn(h);
+                else ((float*)p.out)[(size_t)t * p.ldo + r] = h;
+            } else {
+                float v = g[c] + b;
+                if (p.out_dtype == XR_BF16) ((__nv_bfloat16*)p.out)[(size_t)t * p.ldo + r] = __float2bfloat16_rn(v);
+                else ((float*)p.out)[(size_t)t * p.ldo + r] = v;
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // The kernel.  grid = (token tiles, row tiles, K splits): the CTAs that share a tile of W are neighbours in
 // launch order, so W comes from HBM once and from L2 for the others.
 // ---------------------------------------------------------------------------------------------
@@ -246,61 +299,170 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             if (ok) tc_commit(acc_ready);      // accumulators complete
         }
     } else {
-        // ---------------- epilogue: warps 2..9, tensor-memory lanes 32*(warp%4) .. +31, alternate chunks ----------------
-        const int quad = warp & 3, chunk_first = (warp - 2) >> 2;
-        const int r = row0 + quad * 32 + lane;            // output feature of this thread
+        // ---------------- epilogue: warps 2..9 ----------------
         bool ok = mbar_wait(acc_ready, 0, abort_flag);
         tc_fence_after();
-        if (ok) {
-            const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
-            const bool row_ok = r < p.n_out;
-            const float b = (p.bias != nullptr && row_ok && (p.epilogue == TC_EPI_STORE || p.epilogue == TC_EPI_ADD) && blockIdx.z == 0)
-                                ? p.bias[r] : 0.f;
-#pragma unroll 1
-            for (int c0 = chunk_first * 16; c0 < p.bn; c0 += 32) {
-                if (tok0 + c0 >= p.n) break;               // warp-uniform
-                float g[16], u[16];
-                tc_ld16(taddr + c0, g);
-                if (DUAL) tc_ld16(taddr + BN + c0, u);
-                if (!row_ok) continue;
-                if (p.epilogue == TC_EPI_ADD) {
-                    // read-modify-write of the float32 residual: all loads first, so that they overlap
-                    float* dst = (float*)p.out + (size_t)(tok0 + c0) * p.ldo + r;
-                    float old[16];
-#pragma unroll
-                    for (int c = 0; c < 16; c++) old[c] = (tok0 + c0 + c < p.n) ? dst[(size_t)c * p.ldo] : 0.f;
-#pragma unroll
-                    for (int c = 0; c < 16; c++)
-                        if (tok0 + c0 + c < p.n) dst[(size_t)c * p.ldo] = old[c] + (g[c] + b);
-                    continue;
-                }
-#pragma unroll
-                for (int c = 0; c < 16; c++) {
-                    int t = tok0 + c0 + c;
-                    if (t >= p.n) break;
-                    if (p.epilogue == TC_EPI_PARTIAL) {
-                        size_t width = DUAL ? 2 * (size_t)p.n_out : (size_t)p.n_out;
-                        float* dst = p.partial + ((size_t)blockIdx.z * p.n + t) * width;
-                        dst[r] = g[c];
-                        if (DUAL) dst[p.n_out + r] = u[c];
-                    } else if (DUAL) {
-                        float h = tc_silu(g[c]) * u[c];
-                        if (p.out_dtype == XR_BF16) ((__nv_bfloat16*)p.out)[(size_t)t * p.ldo + r] = __float2bfloat16_rn(h);
-                        else ((float*)p.out)[(size_t)t * p.ldo + r] = h;
-                    } else {
-                        float v = g[c] + b;
-                        if (p.out_dtype == XR_BF16) ((__nv_bfloat16*)p.out)[(size_t)t * p.ldo + r] = __float2bfloat16_rn(v);
-                        else ((float*)p.out)[(size_t)t * p.ldo + r] = v;
-                    }
-                }
-            }
-        }
+        if (ok) tc_epilogue<DUAL>(p, tmem_base, BN, row0, tok0, warp, lane);
     }
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+    if (threadIdx.x == 0 && *abort_flag) atomicExch(p.status, 1);
+}
+
+// ---------------------------------------------------------------------------------------------
+// The same product on pairs of CTAs (cta_group::2), for steps of many tokens.  A cluster of two CTAs owns
+// 256 rows of W (128 each) and a tile of up to 256 tokens; each CTA stages its own rows of W and HALF of the
+// tokens, and one instruction issued by the even CTA multiplies across both CTAs' shared memory into both
+// CTAs' tensor memory (each gets its 128 rows x all tokens).  A CTA thus fetches 32 KB per K block instead of
+// 48 KB for the same 128 x 256 outputs: the single-CTA kernel is bound by exactly that operand traffic.
+//
+// Barriers: the copies of both CTAs complete on the even CTA's `full` barrier (its producer announces the bytes
+// of both); the even CTA's MMA warp releases a stage, and at the end the accumulators, with commits that arrive
+// on the barrier of the same name in both CTAs.  Both CTAs allocate and free tensor memory together; a cluster
+// barrier after set-up keeps a copy from completing on a barrier that is not initialised yet, and one before
+// the end keeps a CTA from leaving while its partner may still signal it.  grid = (2 x token tiles, pairs of
+// row tiles, 1), cluster (2, 1, 1): CTA x of row y is token tile x / 2, row tile 2 y + (x & 1).
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t tc_cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void tc_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t tc_map_to_rank(uint32_t saddr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+    return r;
+}
+// copy into this CTA's shared memory, completion counted on a barrier that may be the partner's
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int x, int y, uint32_t bar_cluster_addr) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {       // arrives on `bar` of both CTAs
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// M = 256 across the pair, N = bn
+__host__ __device__ constexpr uint32_t instr_desc_pair(int bn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+}
+
+#define TC2_BN 256         // token capacity of a pair's tile; each CTA stages half
+template <int STAGES, bool DUAL>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+k_gemm_tc_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    constexpr int W_BYTES = TC_BM * TC_BK * 2;
+    constexpr int X_BYTES = (TC2_BN / 2) * TC_BK * 2;
+    constexpr int STAGE_BYTES = W_BYTES * (DUAL ? 2 : 1) + X_BYTES;
+    constexpr int TMEM_COLS = DUAL ? 512 : 256;
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)(smem + STAGES * STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_ready = empty + STAGES;
+    uint32_t* tmem_slot = (uint32_t*)(acc_ready + 1);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    xr_pdl_launch();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = tc_cluster_rank();                 // 0: issues the MMAs
+    const int half = p.bn >> 1;                              // tokens this CTA stages
+    const int row_tile = 2 * blockIdx.y + (int)rank;
+    const int row0 = row_tile * TC_BM, tok0 = (blockIdx.x >> 1) * p.bn;
+    const int nkb = (p.K + TC_BK - 1) / TC_BK;
+    const uint32_t stage_bytes = W_BYTES * (DUAL ? 2 : 1) + half * TC_BK * 2;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(acc_ready, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    tc_cluster_sync();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    xr_pdl_wait();
+
+    if (warp == 0) {
+        // ---------------- TMA producer (both CTAs) ----------------
+        if (lane == 0) {
+            int issued = 0;
+            for (int i = 0; i < nkb; i++) {
+                int s = i % STAGES;
+                if (i >= STAGES && !mbar_wait(&empty[s], ((i / STAGES) - 1) & 1, abort_flag)) break;
+                uint8_t* st = smem + s * STAGE_BYTES;
+                const uint32_t bar = tc_map_to_rank(smem_u32(&full[s]), 0);
+                if (rank == 0) mbar_expect_tx(&full[s], 2 * stage_bytes);
+                int kx = i * TC_BK;
+                if (p.packed) {
+                    int y = (row_tile * p.w_kblocks + i) * TC_BM;
+                    tma_load_2d_pair(st, &map_w, 0, y, bar);
+                    if (DUAL) tma_load_2d_pair(st + W_BYTES, &map_w, 0, y + (p.up_row_offset / TC_BM) * p.w_kblocks * TC_BM, bar);
+                } else {
+                    tma_load_2d_pair(st, &map_w, kx, row0, bar);
+                    if (DUAL) tma_load_2d_pair(st + W_BYTES, &map_w, kx, p.up_row_offset + row0, bar);
+                }
+                tma_load_2d_pair(st + W_BYTES * (DUAL ? 2 : 1), &map_x, kx, tok0 + (int)rank * half, bar);
+                issued = i + 1;
+            }
+            if (*abort_flag) {
+                // copies already issued still write shared memory: the even CTA waits (bounded) for the stages it
+                // announced; its partner, whose copies complete over there, stays for as long before the closing barrier
+                for (int i = max(0, issued - STAGES); i < issued; i++)
+                    for (uint32_t w = 0; w < XR_SPIN_LIMIT && (rank != 0 || !mbar_try_wait(&full[i % STAGES], (i / STAGES) & 1)); w++) {}
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (even CTA only) ----------------
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = instr_desc_pair(p.bn);
+            bool ok = true;
+            for (int i = 0; i < nkb && ok; i++) {
+                int s = i % STAGES;
+                ok = mbar_wait(&full[s], (i / STAGES) & 1, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+                uint32_t b_addr = a_addr + W_BYTES * (DUAL ? 2 : 1);
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; k++) {
+                    uint64_t bd = smem_desc_sw128(b_addr + k * 32);
+                    uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+                    tc_mma_pair(tmem_base, smem_desc_sw128(a_addr + k * 32), bd, idesc, acc);
+                    if (DUAL) tc_mma_pair(tmem_base + TC2_BN, smem_desc_sw128(a_addr + W_BYTES + k * 32), bd, idesc, acc);
+                }
+                tc_commit_pair(&empty[s]);
+            }
+            if (ok) tc_commit_pair(acc_ready);
+        }
+    } else {
+        // ---------------- epilogue: warps 2..9 of both CTAs, each CTA its own 128 rows ----------------
+        bool ok = mbar_wait(acc_ready, 0, abort_flag);
+        tc_fence_after();
+        if (ok) tc_epilogue<DUAL>(p, tmem_base, TC2_BN, row0, tok0, warp, lane);
+    }
+    __syncwarp();
+    tc_fence_before();
+    tc_cluster_sync();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
     if (threadIdx.x == 0 && *abort_flag) atomicExch(p.status, 1);
 }
@@ -383,6 +545,34 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParam
     return xr_launch_status();
 }
 
+template <int STAGES, bool DUAL>
+static int launch_tc_pair(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, dim3 grid, cudaStream_t stream) {
+    constexpr int STAGE_BYTES = TC_BM * TC_BK * 2 * (DUAL ? 2 : 1) + (TC2_BN / 2) * TC_BK * 2;
+    constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + (2 * STAGES + 1) * 8 + 16;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(k_gemm_tc_pair<STAGES, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+            return XR_ERR_LAUNCH;
+        configured = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = dim3(TC_THREADS); cfg.dynamicSmemBytes = SMEM; cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = xr_pdl_enabled() ? 2 : 1;
+    cudaLaunchKernelEx(&cfg, k_gemm_tc_pair<STAGES, DUAL>, mw, mx, p);
+    return xr_launch_status();
+}
+static bool pair_enabled() {
+    static int on = -1;
+    if (on < 0) { const char* e = getenv("XRB200_NO_PAIR"); on = (e && e[0] && e[0] != '0') ? 0 : 1; }
+    return on == 1;
+}
+
 // CTAs of one product that fit the machine at once: two per SM for the small token tiles (their shared
 // memory is sized for that), one otherwise.
 static int resident_ctas(int bn, bool dual, int sms) { return (bn <= 32 || (bn == 64 && !dual)) ? 2 * sms : sms; }
@@ -449,20 +639,27 @@ XR_EXPORT int xr_gemm_tc(const void* X, const void* W, const float* bias, void* 
         if (!make_map(&mw, W, (long long)(dual ? 2 : 1) * rows_padded * w_kblocks, TC_BK, TC_BK, TC_BM)) return -3;
     } else if (!make_map(&mw, W, dual ? 2LL * n_out : n_out, K, K, TC_BM)) return -3;
     int row_tiles = (n_out + TC_BM - 1) / TC_BM;
-    const int bn_eff = choose_token_tile(n, bn);
-    if (!make_map(&mx, X, n, K, ldx, bn_eff)) return -3;
+    int bn_eff = choose_token_tile(n, bn);
     int tok_tiles = (n + bn_eff - 1) / bn_eff;
     int total_kb = (K + TC_BK - 1) / TC_BK;
     int splits = force_splits > 0 ? force_splits : choose_splits(row_tiles * tok_tiles, tok_tiles, total_kb, resident_ctas(bn, dual, 148));
     if (splits > total_kb) splits = total_kb;
     if (splits > 1 && (scratch == nullptr || scratch_floats < (long long)splits * n * n_out * (dual ? 2 : 1))) splits = 1;
+    // many tokens and no split along K: pairs of CTAs, each staging half of the tile's tokens
+    const bool pair = bn == 256 && splits == 1 && pair_enabled();
+    if (pair) { bn_eff = (bn_eff + 31) / 32 * 32; tok_tiles = (n + bn_eff - 1) / bn_eff; }
+    if (!make_map(&mx, X, n, K, ldx, pair ? bn_eff / 2 : bn_eff)) return -3;
     if (row_tiles > 65535 || splits > 65535) return XR_ERR_ARG;
     if (splits_used) *splits_used = splits;
     TcParams p{out, bias, scratch, status, ldo, n, n_out, K, splits, splits > 1 ? TC_EPI_PARTIAL : epilogue, out_dtype,
                w_packed ? rows_padded : n_out, bn_eff, w_packed, w_kblocks};
     dim3 grid(tok_tiles, row_tiles, splits);
     int rc;
-    if (!dual) {
+    if (pair) {
+        grid.x = 2 * tok_tiles;
+        grid.y = (row_tiles + 1) / 2;
+        rc = dual ? launch_tc_pair<4, true>(mw, mx, p, grid, stream) : launch_tc_pair<6, false>(mw, mx, p, grid, stream);
+    } else if (!dual) {
         switch (bn) {
             case 16: rc = launch_tc<16, 4, false, 3>(mw, mx, p, grid, stream); break;
             case 32: rc = launch_tc<32, 5, false, 2>(mw, mx, p, grid, stream); break;
