@@ -278,7 +278,8 @@ def main() -> int:
                 "d2h_bytes_per_step": 4 * args.batch, "ms_per_step": e2e_run["wall_ms"],
                 "path": "Runner -> Scheduler.step -> Engine.step -> DeviceSampler -> host ids"},
         "gpu_launches": main_run["launches"],
-        "prefill": {"value": T * 1e3 / pre, "tokens": T, "ms": pre, "frac": pre_flops / (pre * 1e-3) / (pk["bf16_tflops"] * 1e12)},
+        "prefill": {"value": T * 1e3 / pre, "tokens": T, "ms": pre, "frac": pre_flops / (pre * 1e-3) / (pk["bf16_tflops"] * 1e12),
+                    "frac_of_sustained": pre_flops / (pre * 1e-3) / (pk.get("bf16_tflops_sustained", pk["bf16_tflops"]) * 1e12)},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"]},
         "points": points,
         "clocks": clk,

@@ -136,15 +136,18 @@ struct TcParams {
     int bn;                     // tokens per tile: a multiple of 16, at most the kernel's BN (which sizes the buffers)
     int packed;                 // W is stored tile by tile: [row tile][K block][128][64], see xr_gemm_tc
     int w_kblocks;              // packed: K blocks per row tile in the packed array
+    int tok_tiles, pair_tiles;  // CTA-pair kernel: token tiles, and tiles in all (token tiles x pairs of row tiles)
 };
 
 // ---------------------------------------------------------------------------------------------
 // Epilogue of one tile, run by warps 2..9 once the accumulators are complete.  A warp may only read the 32
 // tensor-memory lanes of its index mod 4, so two warps share each quarter and take alternate 16-column
-// chunks.  `up_cols`: column offset of the second (up) accumulator of a SwiGLU product.
+// chunks (with sixteen epilogue warps, four share a quarter).  `up_cols`: column offset of the second (up)
+// accumulator of a SwiGLU product.
 // ---------------------------------------------------------------------------------------------
 template <bool DUAL>
-__device__ __forceinline__ void tc_epilogue(const TcParams& p, uint32_t tmem_base, int up_cols, int row0, int tok0, int warp, int lane) {
+__device__ __forceinline__ void tc_epilogue(const TcParams& p, uint32_t tmem_base, int up_cols, int row0, int tok0, int warp, int lane,
+                                            int warps_per_quarter = 2) {
     const int quad = warp & 3, chunk_first = (warp - 2) >> 2;
     const int r = row0 + quad * 32 + lane;            // output feature of this thread
     const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
@@ -152,7 +155,7 @@ __device__ __forceinline__ void tc_epilogue(const TcParams& p, uint32_t tmem_bas
     const float b = (p.bias != nullptr && row_ok && (p.epilogue == TC_EPI_STORE || p.epilogue == TC_EPI_ADD) && blockIdx.z == 0)
                         ? p.bias[r] : 0.f;
 #pragma unroll 1
-    for (int c0 = chunk_first * 16; c0 < p.bn; c0 += 32) {
+    for (int c0 = chunk_first * 16; c0 < p.bn; c0 += 16 * warps_per_quarter) {
         if (tok0 + c0 >= p.n) break;               // warp-uniform
         float g[16], u[16];
         tc_ld16(taddr + c0, g);
@@ -324,8 +327,8 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
 // of both); the even CTA's MMA warp releases a stage, and at the end the accumulators, with commits that arrive
 // on the barrier of the same name in both CTAs.  Both CTAs allocate and free tensor memory together; a cluster
 // barrier after set-up keeps a copy from completing on a barrier that is not initialised yet, and one before
-// the end keeps a CTA from leaving while its partner may still signal it.  grid = (2 x token tiles, pairs of
-// row tiles, 1), cluster (2, 1, 1): CTA x of row y is token tile x / 2, row tile 2 y + (x & 1).
+// the end keeps a CTA from leaving while its partner may still signal it.  grid = 2 x clusters, cluster
+// (2, 1, 1); a tile is (token tile, pair of row tiles), CTA `rank` of the pair owns row tile 2 x pair + rank.
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t tc_cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
 __device__ __forceinline__ void tc_cluster_sync() {
@@ -359,33 +362,46 @@ __host__ __device__ constexpr uint32_t instr_desc_pair(int bn) {
 }
 
 #define TC2_BN 256         // token capacity of a pair's tile; each CTA stages half
+#define TC2_THREADS 576    // producer warp, MMA warp, sixteen epilogue warps (the tile is wide: four per quarter)
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t bar_cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+
+// The pairs are persistent: `gridDim.x / 2` clusters (as many as the machine holds at once) walk the tiles
+// round-robin, token tile fastest, so that clusters working at the same time share rows of W in L2.  The ring
+// of stages runs on across tiles (the producer fetches the next tile's operands while the epilogue of this one
+// runs), and the single product keeps two accumulators in tensor memory, so that the MMAs of the next tile
+// overlap the epilogue too; the SwiGLU product fills tensor memory with one pair of accumulators and waits.
 template <int STAGES, bool DUAL>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(TC2_THREADS, 1)
 k_gemm_tc_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     constexpr int W_BYTES = TC_BM * TC_BK * 2;
     constexpr int X_BYTES = (TC2_BN / 2) * TC_BK * 2;
     constexpr int STAGE_BYTES = W_BYTES * (DUAL ? 2 : 1) + X_BYTES;
-    constexpr int TMEM_COLS = DUAL ? 512 : 256;
+    constexpr int TMEM_COLS = 512;
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full = (uint64_t*)(smem + STAGES * STAGE_BYTES);
     uint64_t* empty = full + STAGES;
-    uint64_t* acc_ready = empty + STAGES;
-    uint32_t* tmem_slot = (uint32_t*)(acc_ready + 1);
+    uint64_t* acc_full = empty + STAGES;          // [2]
+    uint64_t* acc_empty = acc_full + 2;           // [2], used in the even CTA only
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     xr_pdl_launch();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = tc_cluster_rank();                 // 0: issues the MMAs
+    const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
     const int half = p.bn >> 1;                              // tokens this CTA stages
-    const int row_tile = 2 * blockIdx.y + (int)rank;
-    const int row0 = row_tile * TC_BM, tok0 = (blockIdx.x >> 1) * p.bn;
     const int nkb = (p.K + TC_BK - 1) / TC_BK;
     const uint32_t stage_bytes = W_BYTES * (DUAL ? 2 : 1) + half * TC_BK * 2;
+    // two accumulators (sets of two for SwiGLU) of TC2_BN columns each when they fit the 512 columns, else one
+    const int ACC_BUFS = (DUAL && p.bn > TC2_BN / 2) ? 1 : 2;
+    const int up_cols = p.bn > TC2_BN / 2 ? TC2_BN : TC2_BN / 2;      // SwiGLU: the up accumulator sits this far after the gate's
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        mbar_init(acc_ready, 1);
+        for (int b = 0; b < 2; b++) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 2 * 16); }   // 16 epilogue warps x 2 CTAs
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -402,29 +418,33 @@ k_gemm_tc_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     if (warp == 0) {
         // ---------------- TMA producer (both CTAs) ----------------
         if (lane == 0) {
-            int issued = 0;
-            for (int i = 0; i < nkb; i++) {
-                int s = i % STAGES;
-                if (i >= STAGES && !mbar_wait(&empty[s], ((i / STAGES) - 1) & 1, abort_flag)) break;
-                uint8_t* st = smem + s * STAGE_BYTES;
-                const uint32_t bar = tc_map_to_rank(smem_u32(&full[s]), 0);
-                if (rank == 0) mbar_expect_tx(&full[s], 2 * stage_bytes);
-                int kx = i * TC_BK;
-                if (p.packed) {
-                    int y = (row_tile * p.w_kblocks + i) * TC_BM;
-                    tma_load_2d_pair(st, &map_w, 0, y, bar);
-                    if (DUAL) tma_load_2d_pair(st + W_BYTES, &map_w, 0, y + (p.up_row_offset / TC_BM) * p.w_kblocks * TC_BM, bar);
-                } else {
-                    tma_load_2d_pair(st, &map_w, kx, row0, bar);
-                    if (DUAL) tma_load_2d_pair(st + W_BYTES, &map_w, kx, p.up_row_offset + row0, bar);
+            int it = 0;                                      // K blocks fetched so far, over all tiles
+            bool ok = true;
+            for (int tile = cluster_id; tile < p.pair_tiles && ok; tile += n_clusters) {
+                const int row_tile = 2 * (tile / p.tok_tiles) + (int)rank;
+                const int tok0 = (tile % p.tok_tiles) * p.bn;
+                for (int i = 0; i < nkb; i++, it++) {
+                    int s = it % STAGES;
+                    if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) - 1) & 1, abort_flag)) { ok = false; break; }
+                    uint8_t* st = smem + s * STAGE_BYTES;
+                    const uint32_t bar = tc_map_to_rank(smem_u32(&full[s]), 0);
+                    if (rank == 0) mbar_expect_tx(&full[s], 2 * stage_bytes);
+                    int kx = i * TC_BK;
+                    if (p.packed) {
+                        int y = (row_tile * p.w_kblocks + i) * TC_BM;
+                        tma_load_2d_pair(st, &map_w, 0, y, bar);
+                        if (DUAL) tma_load_2d_pair(st + W_BYTES, &map_w, 0, y + (p.up_row_offset / TC_BM) * p.w_kblocks * TC_BM, bar);
+                    } else {
+                        tma_load_2d_pair(st, &map_w, kx, row_tile * TC_BM, bar);
+                        if (DUAL) tma_load_2d_pair(st + W_BYTES, &map_w, kx, p.up_row_offset + row_tile * TC_BM, bar);
+                    }
+                    tma_load_2d_pair(st + W_BYTES * (DUAL ? 2 : 1), &map_x, kx, tok0 + (int)rank * half, bar);
                 }
-                tma_load_2d_pair(st + W_BYTES * (DUAL ? 2 : 1), &map_x, kx, tok0 + (int)rank * half, bar);
-                issued = i + 1;
             }
             if (*abort_flag) {
                 // copies already issued still write shared memory: the even CTA waits (bounded) for the stages it
                 // announced; its partner, whose copies complete over there, stays for as long before the closing barrier
-                for (int i = max(0, issued - STAGES); i < issued; i++)
+                for (int i = max(0, it - STAGES); i < it; i++)
                     for (uint32_t w = 0; w < XR_SPIN_LIMIT && (rank != 0 || !mbar_try_wait(&full[i % STAGES], (i / STAGES) & 1)); w++) {}
             }
         }
@@ -433,29 +453,48 @@ k_gemm_tc_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (lane == 0 && rank == 0) {
             const uint32_t idesc = instr_desc_pair(p.bn);
             bool ok = true;
-            for (int i = 0; i < nkb && ok; i++) {
-                int s = i % STAGES;
-                ok = mbar_wait(&full[s], (i / STAGES) & 1, abort_flag);
-                if (!ok) break;
-                tc_fence_after();
-                uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
-                uint32_t b_addr = a_addr + W_BYTES * (DUAL ? 2 : 1);
-#pragma unroll
-                for (int k = 0; k < TC_BK / 16; k++) {
-                    uint64_t bd = smem_desc_sw128(b_addr + k * 32);
-                    uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
-                    tc_mma_pair(tmem_base, smem_desc_sw128(a_addr + k * 32), bd, idesc, acc);
-                    if (DUAL) tc_mma_pair(tmem_base + TC2_BN, smem_desc_sw128(a_addr + W_BYTES + k * 32), bd, idesc, acc);
+            int it = 0, j = 0;                               // K blocks and tiles done so far
+            for (int tile = cluster_id; tile < p.pair_tiles && ok; tile += n_clusters, j++) {
+                const int b = j % ACC_BUFS;
+                if (j >= ACC_BUFS) {                         // the epilogues of both CTAs have emptied this accumulator
+                    ok = mbar_wait(&acc_empty[b], ((j / ACC_BUFS) - 1) & 1, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
                 }
-                tc_commit_pair(&empty[s]);
+                const uint32_t acc_addr = tmem_base + (uint32_t)b * TC2_BN;
+                for (int i = 0; i < nkb; i++, it++) {
+                    int s = it % STAGES;
+                    ok = mbar_wait(&full[s], (it / STAGES) & 1, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
+                    uint32_t b_addr = a_addr + W_BYTES * (DUAL ? 2 : 1);
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; k++) {
+                        uint64_t bd = smem_desc_sw128(b_addr + k * 32);
+                        uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+                        tc_mma_pair(acc_addr, smem_desc_sw128(a_addr + k * 32), bd, idesc, acc);
+                        if (DUAL) tc_mma_pair(acc_addr + up_cols, smem_desc_sw128(a_addr + W_BYTES + k * 32), bd, idesc, acc);
+                    }
+                    tc_commit_pair(&empty[s]);
+                }
+                if (ok) tc_commit_pair(&acc_full[b]);
             }
-            if (ok) tc_commit_pair(acc_ready);
         }
     } else {
-        // ---------------- epilogue: warps 2..9 of both CTAs, each CTA its own 128 rows ----------------
-        bool ok = mbar_wait(acc_ready, 0, abort_flag);
-        tc_fence_after();
-        if (ok) tc_epilogue<DUAL>(p, tmem_base, TC2_BN, row0, tok0, warp, lane);
+        // ---------------- epilogue: warps 2..17 of both CTAs, each CTA its own 128 rows ----------------
+        const uint32_t acc_empty_bar0 = tc_map_to_rank(smem_u32(&acc_empty[0]), 0);
+        int j = 0;
+        for (int tile = cluster_id; tile < p.pair_tiles; tile += n_clusters, j++) {
+            const int b = j % ACC_BUFS;
+            if (!mbar_wait(&acc_full[b], (j / ACC_BUFS) & 1, abort_flag)) break;
+            tc_fence_after();
+            const int row0 = (2 * (tile / p.tok_tiles) + (int)rank) * TC_BM, tok0 = (tile % p.tok_tiles) * p.bn;
+            tc_epilogue<DUAL>(p, tmem_base + (uint32_t)b * TC2_BN, up_cols, row0, tok0, warp, lane, 4);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_remote(acc_empty_bar0 + (uint32_t)b * 8);
+        }
     }
     __syncwarp();
     tc_fence_before();
@@ -548,21 +587,27 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParam
 template <int STAGES, bool DUAL>
 static int launch_tc_pair(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, dim3 grid, cudaStream_t stream) {
     constexpr int STAGE_BYTES = TC_BM * TC_BK * 2 * (DUAL ? 2 : 1) + (TC2_BN / 2) * TC_BK * 2;
-    constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + (2 * STAGES + 1) * 8 + 16;
-    static bool configured = false;
-    if (!configured) {
-        if (cudaFuncSetAttribute(k_gemm_tc_pair<STAGES, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
-            return XR_ERR_LAUNCH;
-        configured = true;
-    }
+    constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + (2 * STAGES + 4) * 8 + 16;
+    static int max_clusters = 0;               // pairs of CTAs the device holds at once (one CTA per SM)
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid; cfg.blockDim = dim3(TC_THREADS); cfg.dynamicSmemBytes = SMEM; cfg.stream = stream;
+    cfg.blockDim = dim3(TC2_THREADS); cfg.dynamicSmemBytes = SMEM; cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
+    if (max_clusters == 0) {
+        if (cudaFuncSetAttribute(k_gemm_tc_pair<STAGES, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+            return XR_ERR_LAUNCH;
+        cfg.gridDim = dim3(2 * 74); cfg.numAttrs = 1;
+        int nc = 0;
+        if (cudaOccupancyMaxActiveClusters(&nc, k_gemm_tc_pair<STAGES, DUAL>, &cfg) != cudaSuccess || nc < 1) return XR_ERR_LAUNCH;
+        max_clusters = nc;
+    }
+    int clusters = p.pair_tiles < max_clusters ? p.pair_tiles : max_clusters;
+    (void)grid;
+    cfg.gridDim = dim3(2 * clusters);
     cfg.numAttrs = xr_pdl_enabled() ? 2 : 1;
     cudaLaunchKernelEx(&cfg, k_gemm_tc_pair<STAGES, DUAL>, mw, mx, p);
     return xr_launch_status();
@@ -652,12 +697,10 @@ XR_EXPORT int xr_gemm_tc(const void* X, const void* W, const float* bias, void* 
     if (row_tiles > 65535 || splits > 65535) return XR_ERR_ARG;
     if (splits_used) *splits_used = splits;
     TcParams p{out, bias, scratch, status, ldo, n, n_out, K, splits, splits > 1 ? TC_EPI_PARTIAL : epilogue, out_dtype,
-               w_packed ? rows_padded : n_out, bn_eff, w_packed, w_kblocks};
+               w_packed ? rows_padded : n_out, bn_eff, w_packed, w_kblocks, tok_tiles, tok_tiles * ((row_tiles + 1) / 2)};
     dim3 grid(tok_tiles, row_tiles, splits);
     int rc;
     if (pair) {
-        grid.x = 2 * tok_tiles;
-        grid.y = (row_tiles + 1) / 2;
         rc = dual ? launch_tc_pair<4, true>(mw, mx, p, grid, stream) : launch_tc_pair<6, false>(mw, mx, p, grid, stream);
     } else if (!dual) {
         switch (bn) {
