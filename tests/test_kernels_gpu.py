@@ -15,7 +15,8 @@ def bf16_round(a: torch.Tensor) -> torch.Tensor:
 
 
 @pytest.mark.parametrize("n,n_out,k", [(1, 128, 64), (5, 200, 136), (16, 384, 4096), (17, 130, 72), (64, 512, 1024),
-                                       (100, 256, 264), (300, 640, 512), (2, 96, 8), (200, 384, 512), (520, 100, 200), (1030, 300, 72)])
+                                       (100, 256, 264), (300, 640, 512), (2, 96, 8), (200, 384, 512), (520, 100, 200), (1030, 300, 72),
+                                       (1100, 4000, 512), (2300, 2560, 136)])   # more tiles than CTA pairs: the last round is cut along K
 @pytest.mark.parametrize("epi", ["store_bf16", "store_f32", "add", "bias"])
 def test_gemm_tc(n, n_out, k, epi):
     from xyntetik_runner_b200 import kernels
@@ -48,7 +49,7 @@ def test_gemm_tc(n, n_out, k, epi):
         assert err <= tol * scale, f"splits={splits}: max err {err:.3e} vs {tol * scale:.3e}"
 
 
-@pytest.mark.parametrize("n,F,k", [(1, 128, 64), (7, 176, 72), (33, 300, 256), (256, 256, 128), (70, 1024, 512), (300, 200, 264), (600, 384, 128)])
+@pytest.mark.parametrize("n,F,k", [(1, 128, 64), (7, 176, 72), (33, 300, 256), (256, 256, 128), (70, 1024, 512), (300, 200, 264), (600, 384, 128), (2500, 2000, 192)])
 def test_gemm_tc_swiglu(n, F, k):
     from xyntetik_runner_b200 import kernels
     g = torch.Generator(device="cpu").manual_seed(n + F + k)
