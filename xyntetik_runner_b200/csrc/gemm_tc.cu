@@ -585,33 +585,45 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParam
 }
 
 template <int STAGES, bool DUAL>
-static int launch_tc_pair(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, dim3 grid, cudaStream_t stream) {
-    constexpr int STAGE_BYTES = TC_BM * TC_BK * 2 * (DUAL ? 2 : 1) + (TC2_BN / 2) * TC_BK * 2;
-    constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + (2 * STAGES + 4) * 8 + 16;
-    static int max_clusters = 0;               // pairs of CTAs the device holds at once (one CTA per SM)
-    cudaLaunchConfig_t cfg = {};
-    cfg.blockDim = dim3(TC2_THREADS); cfg.dynamicSmemBytes = SMEM; cfg.stream = stream;
-    cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    if (max_clusters == 0) {
-        if (cudaFuncSetAttribute(k_gemm_tc_pair<STAGES, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
-            return XR_ERR_LAUNCH;
-        cfg.gridDim = dim3(2 * 74); cfg.numAttrs = 1;
-        int nc = 0;
-        if (cudaOccupancyMaxActiveClusters(&nc, k_gemm_tc_pair<STAGES, DUAL>, &cfg) != cudaSuccess || nc < 1) return XR_ERR_LAUNCH;
-        max_clusters = nc;
+struct PairLaunch {
+    static constexpr int STAGE_BYTES = TC_BM * TC_BK * 2 * (DUAL ? 2 : 1) + (TC2_BN / 2) * TC_BK * 2;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + (2 * STAGES + 4) * 8 + 16;
+    static void config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, int clusters, cudaStream_t stream) {
+        cfg = {};
+        cfg.gridDim = dim3(2 * clusters); cfg.blockDim = dim3(TC2_THREADS); cfg.dynamicSmemBytes = SMEM; cfg.stream = stream;
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = xr_pdl_enabled() ? 2 : 1;
     }
-    int clusters = p.pair_tiles < max_clusters ? p.pair_tiles : max_clusters;
-    (void)grid;
-    cfg.gridDim = dim3(2 * clusters);
-    cfg.numAttrs = xr_pdl_enabled() ? 2 : 1;
-    cudaLaunchKernelEx(&cfg, k_gemm_tc_pair<STAGES, DUAL>, mw, mx, p);
-    return xr_launch_status();
-}
+    // pairs of CTAs the device holds at once (one CTA per SM); 0 if it cannot run the kernel as clusters of two
+    static int clusters() {
+        static int n = -1;
+        if (n < 0) {
+            n = 0;
+            cudaLaunchConfig_t cfg; cudaLaunchAttribute attr[2];
+            config(cfg, attr, 74, nullptr);
+            cfg.numAttrs = 1;
+            int nc = 0;
+            if (cudaFuncSetAttribute(k_gemm_tc_pair<STAGES, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) == cudaSuccess &&
+                cudaOccupancyMaxActiveClusters(&nc, k_gemm_tc_pair<STAGES, DUAL>, &cfg) == cudaSuccess && nc > 0)
+                n = nc;
+            else
+                cudaGetLastError();        // the single-CTA kernel takes over; leave no error behind
+        }
+        return n;
+    }
+    static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, cudaStream_t stream) {
+        const int most = clusters();
+        if (most < 1) return XR_ERR_LAUNCH;
+        cudaLaunchConfig_t cfg; cudaLaunchAttribute attr[2];
+        config(cfg, attr, p.pair_tiles < most ? p.pair_tiles : most, stream);
+        cudaLaunchKernelEx(&cfg, k_gemm_tc_pair<STAGES, DUAL>, mw, mx, p);
+        return xr_launch_status();
+    }
+};
 static bool pair_enabled() {
     static int on = -1;
     if (on < 0) { const char* e = getenv("XRB200_NO_PAIR"); on = (e && e[0] && e[0] != '0') ? 0 : 1; }
@@ -691,7 +703,8 @@ XR_EXPORT int xr_gemm_tc(const void* X, const void* W, const float* bias, void* 
     if (splits > total_kb) splits = total_kb;
     if (splits > 1 && (scratch == nullptr || scratch_floats < (long long)splits * n * n_out * (dual ? 2 : 1))) splits = 1;
     // many tokens and no split along K: pairs of CTAs, each staging half of the tile's tokens
-    const bool pair = bn == 256 && splits == 1 && pair_enabled();
+    const bool pair = bn == 256 && splits == 1 && pair_enabled() &&
+                      (dual ? PairLaunch<4, true>::clusters() : PairLaunch<6, false>::clusters()) > 0;
     if (pair) { bn_eff = (bn_eff + 31) / 32 * 32; tok_tiles = (n + bn_eff - 1) / bn_eff; }
     if (!make_map(&mx, X, n, K, ldx, pair ? bn_eff / 2 : bn_eff)) return -3;
     if (row_tiles > 65535 || splits > 65535) return XR_ERR_ARG;
@@ -701,7 +714,7 @@ XR_EXPORT int xr_gemm_tc(const void* X, const void* W, const float* bias, void* 
     dim3 grid(tok_tiles, row_tiles, splits);
     int rc;
     if (pair) {
-        rc = dual ? launch_tc_pair<4, true>(mw, mx, p, grid, stream) : launch_tc_pair<6, false>(mw, mx, p, grid, stream);
+        rc = dual ? PairLaunch<4, true>::launch(mw, mx, p, stream) : PairLaunch<6, false>::launch(mw, mx, p, stream);
     } else if (!dual) {
         switch (bn) {
             case 16: rc = launch_tc<16, 4, false, 3>(mw, mx, p, grid, stream); break;
