@@ -322,10 +322,11 @@ def test_fused_finishes_match_the_separate_kernels(n, d):
     assert torch.allclose(a, c, rtol=0, atol=1e-5 * float(a.abs().max()))
 
 
-def test_finish_rope_store_matches_rope_store():
+@pytest.mark.parametrize("H,K,hd,rot", [(6, 2, 48, 48), (6, 2, 32, 32), (3, 1, 64, 32), (2, 2, 128, 128), (5, 1, 16, 16)])
+def test_finish_rope_store_matches_rope_store(H, K, hd, rot):
     from xyntetik_runner_b200 import kernels
     g = torch.Generator().manual_seed(4)
-    H, K, hd, page, n, kdim = 6, 2, 48, 8, 5, 512
+    page, n, kdim = 8, 5, 512
     qkv_dim = (H + 2 * K) * hd
     x_in = torch.randn(n, kdim, generator=g).to(torch.bfloat16).to(DEV)
     w = (torch.randn(qkv_dim, kdim, generator=g) / 20).to(torch.bfloat16).to(DEV)
@@ -333,7 +334,7 @@ def test_finish_rope_store_matches_rope_store():
     positions = torch.tensor([3, 4, 5, 17, 9], dtype=torch.int32, device=DEV)
     tok_seg = torch.tensor([0, 0, 0, 1, 2], dtype=torch.int32, device=DEV)
     bt = torch.tensor([[2, 5, -1], [0, 1, 4], [6, 3, -1]], dtype=torch.int32, device=DEV)
-    inv_freq = torch.rand(hd // 2, generator=g).to(DEV)
+    inv_freq = torch.rand(rot // 2, generator=g).to(DEV)
     outs = []
     for fused in (False, True):
         cache = torch.zeros(7, 1, 2, K, page, hd, dtype=torch.bfloat16, device=DEV)
@@ -341,11 +342,11 @@ def test_finish_rope_store_matches_rope_store():
         if fused:
             used = kernels.gemm_tc(x_in, w, qkv, bias, kernels.EPI_STORE, force_splits=2, defer=True)
             kernels.finish_rope_store(kernels.tc_workspace(torch.device(DEV))[0], used, bias, qkv, positions, tok_seg, bt, inv_freq,
-                                      cache.data_ptr(), cache.stride(0), cache.stride(2), H, K, hd, hd, 3, page)
+                                      cache.data_ptr(), cache.stride(0), cache.stride(2), H, K, hd, rot, 3, page)
         else:
             kernels.gemm_tc(x_in, w, qkv, bias, kernels.EPI_STORE, force_splits=1)
             kernels.rope_store(qkv, positions, tok_seg, bt, inv_freq, cache.data_ptr(), cache.stride(0), cache.stride(2),
-                               H, K, hd, hd, 3, page)
+                               H, K, hd, rot, 3, page)
         outs.append((qkv[:, :H * hd].float().cpu(), cache.float().cpu()))
     (q0, c0), (q1, c1) = outs
     assert float(c0.abs().sum()) > 0
