@@ -147,12 +147,12 @@ struct TcParams {
 // ---------------------------------------------------------------------------------------------
 template <bool DUAL>
 __device__ __forceinline__ void tc_epilogue(const TcParams& p, uint32_t tmem_base, int up_cols, int row0, int tok0, int warp, int lane,
-                                            int warps_per_quarter = 2) {
+                                            int warps_per_quarter = 2, int split = (int)blockIdx.z) {
     const int quad = warp & 3, chunk_first = (warp - 2) >> 2;
     const int r = row0 + quad * 32 + lane;            // output feature of this thread
     const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
     const bool row_ok = r < p.n_out;
-    const float b = (p.bias != nullptr && row_ok && (p.epilogue == TC_EPI_STORE || p.epilogue == TC_EPI_ADD) && blockIdx.z == 0)
+    const float b = (p.bias != nullptr && row_ok && (p.epilogue == TC_EPI_STORE || p.epilogue == TC_EPI_ADD) && split == 0)
                         ? p.bias[r] : 0.f;
 #pragma unroll 1
     for (int c0 = chunk_first * 16; c0 < p.bn; c0 += 16 * warps_per_quarter) {
@@ -178,7 +178,7 @@ __device__ __forceinline__ void tc_epilogue(const TcParams& p, uint32_t tmem_bas
             if (t >= p.n) break;
             if (p.epilogue == TC_EPI_PARTIAL) {
                 size_t width = DUAL ? 2 * (size_t)p.n_out : (size_t)p.n_out;
-                float* dst = p.partial + ((size_t)blockIdx.z * p.n + t) * width;
+                float* dst = p.partial + ((size_t)split * p.n + t) * width;
                 dst[r] = g[c];
                 if (DUAL) dst[p.n_out + r] = u[c];
             } else if (DUAL) {
@@ -367,8 +367,10 @@ __device__ __forceinline__ void mbar_arrive_remote(uint32_t bar_cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
 
-// The pairs are persistent: `gridDim.x / 2` clusters (as many as the machine holds at once) walk the tiles
-// round-robin, token tile fastest, so that clusters working at the same time share rows of W in L2.  The ring
+// The pairs are persistent: `gridDim.x / 2` clusters (as many as the machine holds at once) walk the work items
+// round-robin.  An item is a tile, or with `splits` > 1 one slice along K of a tile (steps of a few hundred tokens
+// have fewer tiles than the machine has CTA pairs); items are ordered slice by slice and within a slice token tile
+// fastest, so that clusters working at the same time share rows of W, and K ranges, in L2.  The ring
 // of stages runs on across tiles (the producer fetches the next tile's operands while the epilogue of this one
 // runs), and the single product keeps two accumulators in tensor memory, so that the MMAs of the next tile
 // overlap the epilogue too; the SwiGLU product fills tensor memory with one pair of accumulators and waits.
@@ -420,10 +422,12 @@ k_gemm_tc_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (lane == 0) {
             int it = 0;                                      // K blocks fetched so far, over all tiles
             bool ok = true;
-            for (int tile = cluster_id; tile < p.pair_tiles && ok; tile += n_clusters) {
+            for (int item = cluster_id; item < p.pair_tiles * p.splits && ok; item += n_clusters) {
+                const int tile = item % p.pair_tiles, split = item / p.pair_tiles;
                 const int row_tile = 2 * (tile / p.tok_tiles) + (int)rank;
                 const int tok0 = (tile % p.tok_tiles) * p.bn;
-                for (int i = 0; i < nkb; i++, it++) {
+                const int kb0 = (int)(((long long)split * nkb) / p.splits), kb1 = (int)(((long long)(split + 1) * nkb) / p.splits);
+                for (int i = kb0; i < kb1; i++, it++) {
                     int s = it % STAGES;
                     if (it >= STAGES && !mbar_wait(&empty[s], ((it / STAGES) - 1) & 1, abort_flag)) { ok = false; break; }
                     uint8_t* st = smem + s * STAGE_BYTES;
@@ -454,7 +458,9 @@ k_gemm_tc_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const uint32_t idesc = instr_desc_pair(p.bn);
             bool ok = true;
             int it = 0, j = 0;                               // K blocks and tiles done so far
-            for (int tile = cluster_id; tile < p.pair_tiles && ok; tile += n_clusters, j++) {
+            for (int item = cluster_id; item < p.pair_tiles * p.splits && ok; item += n_clusters, j++) {
+                const int split = item / p.pair_tiles;
+                const int kb0 = (int)(((long long)split * nkb) / p.splits), kb1 = (int)(((long long)(split + 1) * nkb) / p.splits);
                 const int b = j % ACC_BUFS;
                 if (j >= ACC_BUFS) {                         // the epilogues of both CTAs have emptied this accumulator
                     ok = mbar_wait(&acc_empty[b], ((j / ACC_BUFS) - 1) & 1, abort_flag);
@@ -462,7 +468,7 @@ k_gemm_tc_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     tc_fence_after();
                 }
                 const uint32_t acc_addr = tmem_base + (uint32_t)b * TC2_BN;
-                for (int i = 0; i < nkb; i++, it++) {
+                for (int i = kb0; i < kb1; i++, it++) {
                     int s = it % STAGES;
                     ok = mbar_wait(&full[s], (it / STAGES) & 1, abort_flag);
                     if (!ok) break;
@@ -472,7 +478,7 @@ k_gemm_tc_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                     for (int k = 0; k < TC_BK / 16; k++) {
                         uint64_t bd = smem_desc_sw128(b_addr + k * 32);
-                        uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+                        uint32_t acc = (i > kb0 || k > 0) ? 1u : 0u;
                         tc_mma_pair(acc_addr, smem_desc_sw128(a_addr + k * 32), bd, idesc, acc);
                         if (DUAL) tc_mma_pair(acc_addr + up_cols, smem_desc_sw128(a_addr + W_BYTES + k * 32), bd, idesc, acc);
                     }
@@ -485,12 +491,13 @@ k_gemm_tc_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // ---------------- epilogue: warps 2..17 of both CTAs, each CTA its own 128 rows ----------------
         const uint32_t acc_empty_bar0 = tc_map_to_rank(smem_u32(&acc_empty[0]), 0);
         int j = 0;
-        for (int tile = cluster_id; tile < p.pair_tiles; tile += n_clusters, j++) {
+        for (int item = cluster_id; item < p.pair_tiles * p.splits; item += n_clusters, j++) {
+            const int tile = item % p.pair_tiles, split = item / p.pair_tiles;
             const int b = j % ACC_BUFS;
             if (!mbar_wait(&acc_full[b], (j / ACC_BUFS) & 1, abort_flag)) break;
             tc_fence_after();
             const int row0 = (2 * (tile / p.tok_tiles) + (int)rank) * TC_BM, tok0 = (tile % p.tok_tiles) * p.bn;
-            tc_epilogue<DUAL>(p, tmem_base + (uint32_t)b * TC2_BN, up_cols, row0, tok0, warp, lane, 4);
+            tc_epilogue<DUAL>(p, tmem_base + (uint32_t)b * TC2_BN, up_cols, row0, tok0, warp, lane, 4, split);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_remote(acc_empty_bar0 + (uint32_t)b * 8);
@@ -619,7 +626,8 @@ struct PairLaunch {
         const int most = clusters();
         if (most < 1) return XR_ERR_LAUNCH;
         cudaLaunchConfig_t cfg; cudaLaunchAttribute attr[2];
-        config(cfg, attr, p.pair_tiles < most ? p.pair_tiles : most, stream);
+        const int items = p.pair_tiles * p.splits;
+        config(cfg, attr, items < most ? items : most, stream);
         cudaLaunchKernelEx(&cfg, k_gemm_tc_pair<STAGES, DUAL>, mw, mx, p);
         return xr_launch_status();
     }
@@ -702,10 +710,30 @@ XR_EXPORT int xr_gemm_tc(const void* X, const void* W, const float* bias, void* 
     int splits = force_splits > 0 ? force_splits : choose_splits(row_tiles * tok_tiles, tok_tiles, total_kb, resident_ctas(bn, dual, 148));
     if (splits > total_kb) splits = total_kb;
     if (splits > 1 && (scratch == nullptr || scratch_floats < (long long)splits * n * n_out * (dual ? 2 : 1))) splits = 1;
-    // many tokens and no split along K: pairs of CTAs, each staging half of the tile's tokens
-    const bool pair = bn == 256 && splits == 1 && pair_enabled() &&
-                      (dual ? PairLaunch<4, true>::clusters() : PairLaunch<6, false>::clusters()) > 0;
-    if (pair) { bn_eff = (bn_eff + 31) / 32 * 32; tok_tiles = (n + bn_eff - 1) / bn_eff; }
+    // many tokens: pairs of CTAs, each staging half of the tile's tokens; few tiles are cut along K so that the
+    // items fill the CTA pairs.  In units of the time of one K block (about 0.27 us): rounds x (a fixed part of six +
+    // K blocks per item), and for a cut product the finish kernel (fifteen) and the partial sums' way to memory
+    // and back (8 bytes per element and slice at about 5 TB/s); the cheapest number of slices is taken.
+    const int pair_clusters = (bn == 256 && pair_enabled()) ? (dual ? PairLaunch<4, true>::clusters() : PairLaunch<6, false>::clusters()) : 0;
+    const bool pair = pair_clusters > 0;
+    if (pair) {
+        bn_eff = (bn_eff + 31) / 32 * 32;
+        tok_tiles = (n + bn_eff - 1) / bn_eff;
+        const int tiles = tok_tiles * ((row_tiles + 1) / 2);
+        splits = 1;
+        if (force_splits > 0) splits = force_splits;
+        else if (tiles < pair_clusters) {
+            long long best_cost = -1;
+            for (int sp = 1; sp <= 8 && sp * 8 <= total_kb; sp++) {
+                long long rounds = ((long long)tiles * sp + pair_clusters - 1) / pair_clusters;
+                long long cost = rounds * (6 + (total_kb + sp - 1) / sp);
+                if (sp > 1) cost += 15 + (long long)sp * n * n_out * (dual ? 2 : 1) / 170000;
+                if (best_cost < 0 || cost < best_cost) { best_cost = cost; splits = sp; }
+            }
+        }
+        if (splits > total_kb) splits = total_kb;
+        if (splits > 1 && (scratch == nullptr || scratch_floats < (long long)splits * n * n_out * (dual ? 2 : 1))) splits = 1;
+    }
     if (!make_map(&mx, X, n, K, ldx, pair ? bn_eff / 2 : bn_eff)) return -3;
     if (row_tiles > 65535 || splits > 65535) return XR_ERR_ARG;
     if (splits_used) *splits_used = splits;
