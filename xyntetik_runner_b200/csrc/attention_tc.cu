@@ -77,6 +77,11 @@ __device__ __forceinline__ void ta_mma(uint32_t d, uint64_t a, uint64_t b, uint3
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
 }
+// the same with the A operand in tensor memory: row = lane, two bfloat16 per 32-bit column, K along the columns
+__device__ __forceinline__ void ta_mma_ts(uint32_t d, uint32_t a_tmem, uint64_t b, uint32_t idesc, uint32_t acc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(d), "r"(a_tmem), "l"(b), "r"(idesc), "r"(acc) : "memory");
+}
 __device__ __forceinline__ void ta_ld32(uint32_t taddr, float* v) {
     uint32_t r[32];
     asm volatile(
@@ -117,6 +122,16 @@ __device__ __forceinline__ void ta_st32(uint32_t taddr, const float* v) {
           "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
         : "memory");
 }
+__device__ __forceinline__ void ta_st32u(uint32_t taddr, const uint32_t* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+          "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]),
+          "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]),
+          "r"(v[30]), "r"(v[31])
+        : "memory");
+}
 __device__ __forceinline__ float ta_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -137,6 +152,9 @@ __host__ __device__ constexpr uint32_t ta_idesc(bool b_mn) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
 
+// P_TMEM: P is written over the first 64 columns of its tile's S in tensor memory and read from there by the
+// product (half the shared-memory traffic of P V, no P stores to shared memory); else through shared memory.
+template <bool P_TMEM>
 __global__ void __launch_bounds__(TA_THREADS, 1)
 k_attention_tc(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map, AttnTcArgs a) {
     // 14 half tiles of 16 KB leave no room for alignment slack: the array is declared 1 KB aligned (what the
@@ -253,11 +271,12 @@ k_attention_tc(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
                 ta_wait(&v_full[s], (j >> 1) & 1, gave_up);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 uint32_t pa = ta_smem(p_s + (j & 1) * 2 * HALF), vb = ta_smem(v_s + s * 2 * HALF);
+                const uint32_t tm_p = (j & 1) ? tm_s1 : tm_s0;
 #pragma unroll
                 for (int kk = 0; kk < TA_KEYS / 16; kk++) {
-                    uint64_t ad = ta_desc_k(pa + (kk >> 2) * HALF + (kk & 3) * 32);
                     uint64_t bd = ta_desc_mn(vb + kk * 16 * 128, HALF);
-                    ta_mma(tm_o, ad, bd, id_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                    if (P_TMEM) ta_mma_ts(tm_o, tm_p + kk * 8, bd, id_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                    else ta_mma(tm_o, ta_desc_k(pa + (kk >> 2) * HALF + (kk & 3) * 32), bd, id_pv, (j > 0 || kk > 0) ? 1u : 0u);
                 }
                 ta_commit(&pv_done[j & 1]);
             }
@@ -324,35 +343,54 @@ k_attention_tc(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
-            // the P buffer of this tile was read by the product of tile j - 2
-            if (j >= 2) ta_wait(&pv_done[j & 1], ((j >> 1) - 1) & 1, gave_up);
+            // the shared-memory P buffer of this tile was read by the product of tile j - 2 (in tensor memory P lies
+            // over this tile's own S, which the tensor core wrote after that product)
+            if (!P_TMEM && j >= 2) ta_wait(&pv_done[j & 1], ((j >> 1) - 1) & 1, gave_up);
             const float off = m == -INFINITY ? 0.f : m;
             uint8_t* rowp = p_s + (j & 1) * 2 * HALF + half * HALF + r * 128;       // this thread's half row of P
-            float sum0 = 0.f, sum1 = 0.f;
+            // The probabilities of this thread's 64 keys.  The pass without a mask has no branch inside, so that the
+            // compiler can interleave the elements' chains (scale, exp2, sum, round) instead of walking them one by one.
+            float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+            uint32_t pall[32];
+            if (!masked) {
 #pragma unroll
-            for (int c = 0; c < 2; c++) {
-                uint32_t pk[16];
+                for (int i = 0; i < 64; i += 4) {
+                    float p0 = ta_exp2(fmaf(__uint_as_float(sraw[i]), a.scale_log2, -off));
+                    float p1 = ta_exp2(fmaf(__uint_as_float(sraw[i + 1]), a.scale_log2, -off));
+                    float p2 = ta_exp2(fmaf(__uint_as_float(sraw[i + 2]), a.scale_log2, -off));
+                    float p3 = ta_exp2(fmaf(__uint_as_float(sraw[i + 3]), a.scale_log2, -off));
+                    sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
+                    __nv_bfloat162 b01 = __floats2bfloat162_rn(p0, p1), b23 = __floats2bfloat162_rn(p2, p3);
+                    pall[i >> 1] = *reinterpret_cast<uint32_t*>(&b01);
+                    pall[(i >> 1) + 1] = *reinterpret_cast<uint32_t*>(&b23);
+                }
+            } else {
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float p0 = ta_exp2(fmaf(__uint_as_float(sraw[c * 32 + i]), a.scale_log2, -off));
-                    float p1 = ta_exp2(fmaf(__uint_as_float(sraw[c * 32 + i + 1]), a.scale_log2, -off));
-                    if (masked) {
-                        int kp = key0 + c * 32 + i;
-                        if (!(kp <= pos && kp >= lo_r)) p0 = 0.f;
-                        if (!(kp + 1 <= pos && kp + 1 >= lo_r)) p1 = 0.f;
-                    }
+                for (int i = 0; i < 64; i += 2) {
+                    float p0 = ta_exp2(fmaf(__uint_as_float(sraw[i]), a.scale_log2, -off));
+                    float p1 = ta_exp2(fmaf(__uint_as_float(sraw[i + 1]), a.scale_log2, -off));
+                    const int kp = key0 + i;
+                    p0 = (kp <= pos && kp >= lo_r) ? p0 : 0.f;
+                    p1 = (kp + 1 <= pos && kp + 1 >= lo_r) ? p1 : 0.f;
                     sum0 += p0; sum1 += p1;
                     __nv_bfloat162 bb = __floats2bfloat162_rn(p0, p1);
-                    pk[i >> 1] = *reinterpret_cast<uint32_t*>(&bb);
-                }
-                // keys c*32 .. c*32+31 of this half: four 16-byte chunks of the row, swizzled by the row
-#pragma unroll
-                for (int q = 0; q < 4; q++) {
-                    int chunk = c * 4 + q;
-                    *reinterpret_cast<uint4*>(rowp + ((chunk ^ (r & 7)) << 4)) = make_uint4(pk[q * 4], pk[q * 4 + 1], pk[q * 4 + 2], pk[q * 4 + 3]);
+                    pall[i >> 1] = *reinterpret_cast<uint32_t*>(&bb);
                 }
             }
-            l += sum0 + sum1;
+            sum0 = (sum0 + sum1) + (sum2 + sum3);
+            if (!P_TMEM) {
+                // keys c*32 .. c*32+31 of this half: four 16-byte chunks of the row, swizzled by the row
+#pragma unroll
+                for (int chunk = 0; chunk < 8; chunk++)
+                    *reinterpret_cast<uint4*>(rowp + ((chunk ^ (r & 7)) << 4)) =
+                        make_uint4(pall[chunk * 4], pall[chunk * 4 + 1], pall[chunk * 4 + 2], pall[chunk * 4 + 3]);
+            }
+            if (P_TMEM) {
+                // this thread's 64 probabilities, two per column, over columns 32 half .. 32 half + 31 of the tile's S
+                ta_st32u(((j & 1) ? tm_s1 : tm_s0) + lane_off + half * 32, pall);
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            }
+            l += sum0;
             if ((t_lo + j) * TA_KEYS + TA_KEYS - 1 > hi) {
                 // The tile runs past the last key.  Probabilities there are zero, but the value rows hold whatever the
                 // page held before; clear them so that zero times those bytes is zero whatever they are.
@@ -471,12 +509,18 @@ XR_EXPORT int xr_attention_tc(const void* q, void* out, const void* cache_base, 
                  window, n_layers, layer, scale * 1.4426950408889634f};
     constexpr int SMEM = 14 * TA_ROWS * 128 + 128 + 2 * 2 * 128 * 4;
     static bool configured = false;
+    static bool p_tmem = true;                 // XRB200_ATTENTION_P_SMEM=1: P through shared memory (for comparisons)
     if (!configured) {
-        if (cudaFuncSetAttribute(k_attention_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return XR_ERR_LAUNCH;
+        if (cudaFuncSetAttribute(k_attention_tc<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
+            cudaFuncSetAttribute(k_attention_tc<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+            return XR_ERR_LAUNCH;
+        const char* e = getenv("XRB200_ATTENTION_P_SMEM");
+        p_tmem = !(e && e[0] && e[0] != '0');
         configured = true;
     }
     long long tiles = ((long long)max_seg_len * G + TA_ROWS - 1) / TA_ROWS;
     if (tiles > 0x7fffffffLL) return XR_ERR_ARG;
-    xr_launch(k_attention_tc, dim3((unsigned)tiles, K, n_seg), dim3(TA_THREADS), SMEM, stream, qm, kvm, a);
+    if (p_tmem) xr_launch(k_attention_tc<true>, dim3((unsigned)tiles, K, n_seg), dim3(TA_THREADS), SMEM, stream, qm, kvm, a);
+    else xr_launch(k_attention_tc<false>, dim3((unsigned)tiles, K, n_seg), dim3(TA_THREADS), SMEM, stream, qm, kvm, a);
     return xr_launch_status();
 }
