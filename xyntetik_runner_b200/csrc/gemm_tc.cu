@@ -172,24 +172,35 @@ __device__ __forceinline__ void tc_epilogue(const TcParams& p, uint32_t tmem_bas
                 if (tok0 + c0 + c < p.n) dst[(size_t)c * p.ldo] = old[c] + (g[c] + b);
             continue;
         }
+        // The values of the chunk first, in one stretch without a branch (the chains of the sixteen elements then
+        // interleave: SiLU is an exp2, a reciprocal and two products each), then the stores; a chunk that runs past
+        // the last token stores only what exists.
+        const int live = p.n - (tok0 + c0) < 16 ? p.n - (tok0 + c0) : 16;
+        if (p.epilogue == TC_EPI_PARTIAL) {
+            const size_t width = DUAL ? 2 * (size_t)p.n_out : (size_t)p.n_out;
+            float* dst = p.partial + ((size_t)split * p.n + tok0 + c0) * width + r;
 #pragma unroll
-        for (int c = 0; c < 16; c++) {
-            int t = tok0 + c0 + c;
-            if (t >= p.n) break;
-            if (p.epilogue == TC_EPI_PARTIAL) {
-                size_t width = DUAL ? 2 * (size_t)p.n_out : (size_t)p.n_out;
-                float* dst = p.partial + ((size_t)split * p.n + t) * width;
-                dst[r] = g[c];
-                if (DUAL) dst[p.n_out + r] = u[c];
-            } else if (DUAL) {
-                float h = tc_silu(g[c]) * u[c];
-                if (p.out_dtype == XR_BF16) ((__nv_bfloat16*)p.out)[(size_t)t * p.ldo + r] = __float2bfloat16_rn(h);
-                else ((float*)p.out)[(size_t)t * p.ldo + r] = h;
-            } else {
-                float v = g[c] + b;
-                if (p.out_dtype == XR_BF16) ((__nv_bfloat16*)p.out)[(size_t)t * p.ldo + r] = __float2bfloat16_rn(v);
-                else ((float*)p.out)[(size_t)t * p.ldo + r] = v;
+            for (int c = 0; c < 16; c++) {
+                if (c < live) {
+                    dst[(size_t)c * width] = g[c];
+                    if (DUAL) dst[(size_t)c * width + p.n_out] = u[c];
+                }
             }
+            continue;
+        }
+        float v[16];
+#pragma unroll
+        for (int c = 0; c < 16; c++) v[c] = DUAL ? tc_silu(g[c]) * u[c] : g[c] + b;
+        if (p.out_dtype == XR_BF16) {
+            __nv_bfloat16* dst = (__nv_bfloat16*)p.out + (size_t)(tok0 + c0) * p.ldo + r;
+#pragma unroll
+            for (int c = 0; c < 16; c++)
+                if (c < live) dst[(size_t)c * p.ldo] = __float2bfloat16_rn(v[c]);
+        } else {
+            float* dst = (float*)p.out + (size_t)(tok0 + c0) * p.ldo + r;
+#pragma unroll
+            for (int c = 0; c < 16; c++)
+                if (c < live) dst[(size_t)c * p.ldo] = v[c];
         }
     }
 }
