@@ -36,7 +36,7 @@ def test_serving_path_matches_the_32_bit_path_at_8b_layer_sizes(shape):
     from xyntetik_runner_b200.parts import linear
     cfg = LlamaConfig.from_dict(shape)
     V = cfg.vocab_size
-    reqs = {"a": traces.random_tokens(1, 150, V), "b": traces.random_tokens(2, 70, V), "c": traces.random_tokens(3, 260, V)}
+    reqs = {"a": traces.random_tokens(1, 150, V), "b": traces.random_tokens(2, 70, V), "c": traces.random_tokens(3, 600, V)}     # 600: several token tiles of the CTA-pair product
 
     def only_last(steps, keep=3):
         """ask for logits at the last `keep` tokens of every entry only (a row of logits is half a megabyte)"""
