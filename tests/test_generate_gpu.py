@@ -120,6 +120,37 @@ def test_stop_ids_end_a_request(folders):
     assert q.finish_reason == "stop" and q.generated == free[:first]
 
 
+@pytest.mark.parametrize("temp", [0.0, 0.9])
+def test_steps_launched_ahead_give_the_same_tokens(folders, temp):
+    """Decode steps launched before the tokens of the step ahead of them are read (the device feeds the sampled ids
+    on) against the same run one step at a time: requests of different lengths, one that meets a stop token."""
+    from xyntetik_runner_b200.engine.runner import Runner
+    folder = folders["B", "float32"]
+    prompts = [traces.random_tokens(60 + i, n, 387) for i, n in enumerate((7, 19, 3, 12))]
+    lengths = [25, 9, 31, 17]
+
+    def run(ahead, stop):
+        r = Runner(folder, dtype="float32", ctx=128, parallel=4, page_size=8)
+        r.scheduler.params.look_ahead = ahead
+        ids = [r.submit(p, n=n, temp=temp, seed=5 + i, stop_ids=stop if i == 2 else [], ignore_eos=False)
+               for i, (p, n) in enumerate(zip(prompts, lengths))]
+        while r.scheduler.has_work():
+            r.scheduler.step()
+        r.engine.cache.audit()
+        assert not r.engine.cache.live_requests()
+        done = [r.scheduler.finished[i] for i in ids]
+        return [q.generated for q in done], [q.finish_reason for q in done], r.scheduler.stats["steps_launched_ahead"]
+
+    free, _, n_ahead = run(False, [])
+    assert n_ahead == 0 and [len(g) for g in free] == lengths
+    stop = [free[2][10]]
+    want, reasons, _ = run(False, stop)
+    assert reasons[2] == "stop" and want[2] == free[2][:free[2].index(stop[0])]
+    got, reasons_ahead, n_ahead = run(True, stop)
+    assert n_ahead >= 10
+    assert got == want and reasons_ahead == reasons
+
+
 def test_starved_pool_preempts_and_gives_the_same_tokens(folders):
     from xyntetik_runner_b200.engine.runner import Runner
     folder = folders["A", "float32"]

@@ -8,24 +8,27 @@
 // Embedding: x[t] = E[id_t], ids outside [0, vocab) read row 0
 // (the reference does the same on the host, src/model.c:6148-6162).
 // ---------------------------------------------------------------------------
+// `feed` (optional): ids[t] = -(1 + j) stands for feed[j], a token that an earlier step of the same stream left
+// on the device (the one it sampled), so that the host need not have seen it when it describes this step.
 template <typename TW>
-__global__ void k_embed(const TW* __restrict__ table, const int* __restrict__ ids, float* __restrict__ x,
-                        int d, int vocab) {
+__global__ void k_embed(const TW* __restrict__ table, const int* __restrict__ ids, const int* __restrict__ feed,
+                        float* __restrict__ x, int d, int vocab, int n_feed) {
     xr_pdl_launch();
     xr_pdl_wait();
     int t = blockIdx.x;
     int id = ids[t];
+    if (feed != nullptr && id < 0 && -(id + 1) < n_feed) id = feed[-(id + 1)];
     if (id < 0 || id >= vocab) id = 0;
     const TW* row = table + (size_t)id * d;
     float* out = x + (size_t)t * d;
     for (int i = threadIdx.x; i < d; i += blockDim.x) out[i] = xr_to_f32<TW>(row[i]);
 }
 
-XR_EXPORT int xr_embed(const void* table, int table_dtype, const int* ids, float* x, int n, int d, int vocab,
-                       cudaStream_t stream) {
-    if (n < 1 || d < 1 || vocab < 1) return XR_ERR_ARG;
-    if (table_dtype == XR_F32) xr_launch((k_embed<float>), dim3(n), dim3(256), 0, stream, (const float*)table, ids, x, d, vocab);
-    else if (table_dtype == XR_BF16) xr_launch((k_embed<__nv_bfloat16>), dim3(n), dim3(256), 0, stream, (const __nv_bfloat16*)table, ids, x, d, vocab);
+XR_EXPORT int xr_embed(const void* table, int table_dtype, const int* ids, const int* feed, int n_feed, float* x, int n, int d,
+                       int vocab, cudaStream_t stream) {
+    if (n < 1 || d < 1 || vocab < 1 || n_feed < 0) return XR_ERR_ARG;
+    if (table_dtype == XR_F32) xr_launch((k_embed<float>), dim3(n), dim3(256), 0, stream, (const float*)table, ids, feed, x, d, vocab, n_feed);
+    else if (table_dtype == XR_BF16) xr_launch((k_embed<__nv_bfloat16>), dim3(n), dim3(256), 0, stream, (const __nv_bfloat16*)table, ids, feed, x, d, vocab, n_feed);
     else return XR_ERR_ARG;
     return xr_launch_status();
 }

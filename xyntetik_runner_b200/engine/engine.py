@@ -65,6 +65,7 @@ class StepContext:
         self.n = 0
         self.n_seg = 0
         self.token_ids = self.positions = self.tok_seg = self.logit_rows = None
+        self.token_feed = None          # tokens that an earlier step left on the device (Engine.step's `feed`)
         self.seg_start = self.seg_len = self.seg_pos0 = self.seg_slot = None
         self.block_tables: List[torch.Tensor] = []
         self.host: Dict[str, np.ndarray] = {}
@@ -159,6 +160,7 @@ class Engine:
         # CUDA graphs of decode-only steps, keyed by (tokens, wanted rows, context bucket).  A graph holds the
         # addresses of the step's buffers, so any buffer that is made anew invalidates all graphs.
         self._graphs: Dict[tuple, object] = {}
+        self._feed_ptr = None
         self._graph_ok = p.cuda_graphs and all(part.graph_safe for part in plan.parts())
         self._graph_seen: Dict[tuple, int] = {}
         self._buf_generation = 0
@@ -214,9 +216,12 @@ class Engine:
         return slot
 
     # ---- the step ----------------------------------------------------------------
-    def step(self, entries: Sequence[StepEntry], reserved: bool = False) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], reserved: bool = False, feed: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Run one batch.  Returns float32 logits [number of wanted places, vocab] on the device, in the
         order of the entries and of each entry's `want`; the tensor is reused by the next step.
+
+        `feed`: int32 tokens on the device (always the same tensor); a token id -(1 + j) in an entry stands for
+        feed[j] as it is when this step runs, e.g. what the step before sampled, which the host has not read yet.
 
         Unless `reserved`, pages for every entry's tokens are taken here (all or nothing: on
         ``OutOfPages`` the cache is as before the call).  A request not seen before is opened."""
@@ -247,6 +252,11 @@ class Engine:
                     self.cache.close(r)
                 raise
         ctx = self._describe(entries)
+        ctx.token_feed = feed
+        if feed is not None:
+            if self._feed_ptr not in (None, feed.data_ptr()):
+                raise ValueError("the token feed must be the same tensor in every step")
+            self._feed_ptr = feed.data_ptr()
         if ctx.decode_only and self._graph_ok:
             logits = self._forward_graphed(ctx)
         else:
@@ -324,7 +334,7 @@ class Engine:
         """Decode-only steps have the same launches whenever batch size and context bucket repeat: the
         first such step runs plainly (and makes every buffer), the second is captured, later ones replay.
         Everything that changes from step to step is in the step description, which is copied before."""
-        key = (ctx.n, ctx.n_rows, ctx.max_kv_len)
+        key = (ctx.n, ctx.n_rows, ctx.max_kv_len, ctx.token_feed is not None)
         g = self._graphs.get(key)
         if g is not None:
             g.replay()

@@ -27,21 +27,57 @@ class GenerationResult:
     preemptions: int = 0
 
 
+@dataclass
+class InFlight:
+    """A step that has been launched: who gets a token from it, where the tokens will arrive, and when."""
+    wanting: list
+    host: Optional[torch.Tensor]
+    done: Optional[torch.cuda.Event]
+
+
 class EngineExecutor:
-    """Runs a scheduler's plan on the engine and samples on the device."""
+    """Runs a scheduler's plan on the engine and samples on the device.
+
+    `launch` queues a step and returns at once; `wait` blocks until its tokens are on the host.  The sampled ids
+    of every step stay in one device array (`feed`), so that the step after it can be launched before the host
+    has read them: an entry whose token is the scheduler's IN_FLIGHT mark is fed row `feed_rows[request]` of it."""
 
     def __init__(self, engine: Engine):
         self.engine = engine
         self.sampler = DeviceSampler(engine.device)
+        self.feed = torch.zeros(max(engine.params.max_requests, 1), dtype=torch.int32, device=engine.device)
+        self._host = [torch.empty(self.feed.numel(), dtype=torch.int32).pin_memory() for _ in range(3)]
+        self._next = 0
 
-    def run(self, plan: StepPlan) -> Dict[object, int]:
-        entries = [StepEntry(e.request.id, e.tokens, [e.count - 1] if e.wants_token else []) for e in plan.entries]
-        logits = self.engine.step(entries, reserved=True)
+    def launch(self, plan: StepPlan, feed_rows: Optional[Dict[object, int]] = None) -> InFlight:
+        entries = []
+        for e in plan.entries:
+            toks = e.tokens
+            if feed_rows is not None and e.request.id in feed_rows:
+                assert e.count == 1
+                toks = [-(1 + feed_rows[e.request.id])]
+            entries.append(StepEntry(e.request.id, toks, [e.count - 1] if e.wants_token else []))
+        logits = self.engine.step(entries, reserved=True, feed=self.feed)
         wanting = [e.request for e in plan.entries if e.wants_token]
         if not wanting:
+            return InFlight([], None, None)
+        ids = self.sampler.pick(logits, [r.sampler for r in wanting], out=self.feed)
+        host = self._host[self._next]
+        self._next = (self._next + 1) % len(self._host)
+        host[:len(wanting)].copy_(ids, non_blocking=True)                       # device -> host
+        done = torch.cuda.Event()
+        done.record()
+        return InFlight(wanting, host, done)
+
+    def wait(self, step: InFlight) -> Dict[object, int]:
+        if not step.wanting:
             return {}
-        picked = self.sampler.pick(logits, [r.sampler for r in wanting]).cpu().tolist()   # device -> host
-        return {r.id: t for r, t in zip(wanting, picked)}
+        step.done.synchronize()
+        picked = step.host[:len(step.wanting)].tolist()
+        return {r.id: t for r, t in zip(step.wanting, picked)}
+
+    def run(self, plan: StepPlan) -> Dict[object, int]:
+        return self.wait(self.launch(plan))
 
 
 class Runner:

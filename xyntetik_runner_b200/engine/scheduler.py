@@ -56,6 +56,9 @@ class Request:
         return len(self.tokens) - self.computed
 
 
+IN_FLIGHT = -1       # stands in a request's tokens for one that a launched step has not delivered yet
+
+
 @dataclass
 class PlannedEntry:
     request: Request
@@ -82,6 +85,9 @@ class StepPlan:
 class SchedulerParams:
     max_step_tokens: int = 2048      # token budget of one step
     prefill_chunk: Optional[int] = None   # cap on one request's portion (the reference's -b); None: the budget
+    # Launch the next decode step before the tokens of the running one have been read (needs an executor with
+    # `launch` / `wait`): the host's planning then overlaps the device's work.  See Scheduler.step.
+    look_ahead: bool = True
 
 
 class Scheduler:
@@ -94,7 +100,9 @@ class Scheduler:
         self.live: List[Request] = []           # in admission order
         self.finished: Dict[object, Request] = {}
         self._tick = 0
-        self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "preemptions": 0, "max_batch": 0}
+        self._ahead = None                      # (plan, executor's handle) of a step launched ahead of its turn
+        self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "preemptions": 0, "max_batch": 0,
+                      "steps_launched_ahead": 0}
 
     # ---- adding ---------------------------------------------------------------------
     def add(self, req: Request) -> None:
@@ -111,7 +119,7 @@ class Scheduler:
                                  f"{pool} pages of {self.cache.page_size}")
         if req.max_new_tokens == 0:
             raise ValueError("max_new_tokens must not be 0")
-        req.tokens = list(req.prompt)
+        req.tokens = [t if t >= 0 else 0 for t in req.prompt]      # an id below zero reads row 0, as one beyond the table does
         req.generated = []
         req.computed = 0
         req.status = WAITING
@@ -234,18 +242,48 @@ class Scheduler:
 
     def step(self) -> List[Tuple[object, Optional[int], bool]]:
         """Plan and run one step.  Returns [(request id, new token or None, finished)] for requests that
-        got a token or finished in this step."""
-        plan = self.plan()
-        if not plan.entries:
-            return []
-        sampled: Dict[object, int] = self.executor.run(plan)
+        got a token or finished in this step.
+
+        Looking ahead.  When the step at hand only decodes (every live request one token, nobody waiting, no
+        penalty window to send, nobody about to reach its length), the step after it is known but for the token
+        values: the same requests, one position on.  It is then launched BEFORE this step's tokens are read; the
+        device feeds it the sampled ids itself (executor's `feed`), and the host does its planning while the
+        device works.  A request that turns out to have stopped in this step has one more row computed in the next;
+        that row is dropped when its turn comes.  A step launched ahead is the next call's step."""
+        plan = handle = None
+        if self._ahead is not None:
+            plan, handle = self._ahead
+            self._ahead = None
+            if all(e.request.status == FINISHED for e in plan.entries):
+                plan = handle = None         # every request of it ended in the step before: nothing to collect
+        if plan is None:
+            plan = self.plan()
+            if not plan.entries:
+                return []
+            handle = self.executor.launch(plan) if hasattr(self.executor, "launch") else None
+        advanced = False
+        if handle is not None and self.params.look_ahead:
+            nxt = self._plan_ahead(plan)
+            if nxt is not None:
+                # the tokens this step will bring take their places now, as marks, so that the next step can be described
+                advanced = True
+                for e in plan.entries:
+                    e.request.computed += e.count
+                    e.request.tokens.append(IN_FLIGHT)
+                rows = {e.request.id: i for i, e in enumerate(plan.entries)}
+                self._ahead = (nxt, self.executor.launch(nxt, feed_rows=rows))
+                self.stats["steps_launched_ahead"] += 1
+        sampled: Dict[object, int] = self.executor.wait(handle) if handle is not None else self.executor.run(plan)
         self.stats["steps"] += 1
         self.stats["max_batch"] = max(self.stats["max_batch"], len(plan.entries))
         out = []
         limit = self.cache.max_pages_per_request * self.cache.page_size
         for e in plan.entries:
             r = e.request
-            r.computed += e.count
+            if r.status == FINISHED:
+                continue                     # it stopped in the step before; this row was computed for nothing
+            if not advanced:
+                r.computed += e.count
             if e.count == 1 and r.generated:
                 self.stats["decode_tokens"] += 1
             else:
@@ -253,6 +291,8 @@ class Scheduler:
             if not e.wants_token:
                 continue
             tok = int(sampled[r.id])
+            if advanced:
+                r.tokens.pop()               # the mark; the token itself is appended below if the request goes on
             r.sampler.accept(tok)
             if not r.ignore_eos and tok in r.stop_ids:            # src/engine.c:1849-1854
                 self._finish(r, "stop")
@@ -269,6 +309,32 @@ class Scheduler:
                 self._finish(r, done)
             out.append((r.id, tok, done is not None))
         return out
+
+    def _plan_ahead(self, plan: StepPlan) -> Optional[StepPlan]:
+        """The step after `plan`, if it can be told without `plan`'s tokens: `plan` decodes one token for every
+        live request, nobody waits, and every request can take one more token afterwards.  Reserves its pages."""
+        if self.waiting or plan.preempted or len(plan.entries) != len(self.live):
+            return None
+        limit = self.cache.max_pages_per_request * self.cache.page_size
+        for e in plan.entries:
+            r = e.request
+            if e.count != 1 or not e.wants_token or r.status != LIVE or r.pending != 1 or r.sampler.needs_window():
+                return None
+            if 0 < r.max_new_tokens <= len(r.generated) + 1 or len(r.tokens) + 1 >= limit:
+                return None                  # it ends with this step's token
+        # pages: this step's reservations are committed (the executor's launch did that), one more token each
+        taken = []
+        for e in plan.entries:
+            if not self.cache.can_reserve(e.request.id, 1):
+                for rid in taken:
+                    self.cache.cancel(rid)
+                return None
+            self.cache.reserve(e.request.id, 1)
+            taken.append(e.request.id)
+        nxt = StepPlan()
+        for e in plan.entries:
+            nxt.entries.append(PlannedEntry(e.request, e.request.computed + e.count, 1, True))
+        return nxt
 
     def run_to_completion(self, max_steps: int = 1 << 30) -> None:
         n = 0

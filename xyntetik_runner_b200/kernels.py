@@ -47,7 +47,7 @@ _vp, _i, _ll, _f = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_fl
 
 def _declare(L: ctypes.CDLL) -> None:
     sig = {
-        "xr_embed": [_vp, _i, _vp, _vp, _i, _i, _i, _vp],
+        "xr_embed": [_vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _vp],
         "xr_rmsnorm": [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
         "xr_rope_store": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _vp],
         "xr_silu_mul": [_vp, _vp, _i, _i, _i, _vp],
@@ -107,13 +107,15 @@ def _count(n: int = 1) -> None:
 
 
 # ---------------------------------------------------------------------------
-def embed(table: torch.Tensor, ids: torch.Tensor, x: torch.Tensor) -> None:
-    """x[t] = table[ids[t]] widened to float32; ids outside the table read row 0."""
-    _dev(table, ids, x)
+def embed(table: torch.Tensor, ids: torch.Tensor, x: torch.Tensor, feed: Optional[torch.Tensor] = None) -> None:
+    """x[t] = table[ids[t]] widened to float32; ids outside the table read row 0.  With `feed` (int32 on the
+    device), ids[t] = -(1 + j) reads token feed[j]."""
+    _dev(table, ids, x, feed)
     n, d = x.shape
     assert ids.dtype == torch.int32 and ids.numel() >= n and x.dtype == torch.float32 and table.shape[1] == d
-    _check(lib().xr_embed(table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(), x.data_ptr(), n, d,
-                          table.shape[0], _stream()), "embed")
+    assert feed is None or feed.dtype == torch.int32
+    _check(lib().xr_embed(table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(), _ptr(feed),
+                          0 if feed is None else feed.numel(), x.data_ptr(), n, d, table.shape[0], _stream()), "embed")
     _count()
 
 

@@ -27,7 +27,8 @@ class Embedding(Part):
         self.table = tensors[self.name]
 
     def forward(self, ctx, ids: torch.Tensor, x: torch.Tensor) -> None:
-        kernels.embed(self.table, ids, x)
+        # ids below zero stand for tokens an earlier step left on the device (the step context's `token_feed`)
+        kernels.embed(self.table, ids, x, getattr(ctx, "token_feed", None))
 
 
 class Head(Part):

@@ -90,11 +90,14 @@ class DeviceSampler:
         self._scratch: Optional[torch.Tensor] = None
         self._greedy: dict = {}          # rows -> parameter tensors of an all-greedy batch (they never change)
 
-    def pick(self, logits: torch.Tensor, samplers: List[RequestSampler]) -> torch.Tensor:
+    def pick(self, logits: torch.Tensor, samplers: List[RequestSampler], out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """logits: float32 [rows, vocab] on the device, one RequestSampler per row (each makes its
-        draw here).  Returns int32 [rows] on the device."""
+        draw here).  Returns int32 [rows] on the device (`out`, if given: int32, at least `rows` long)."""
         rows, V = logits.shape
         assert rows == len(samplers)
+        if out is not None:
+            assert out.dtype == torch.int32 and out.numel() >= rows and out.is_contiguous()
+            out = out[:rows]
         if all(s.params.temperature <= 0 for s in samplers):
             # greedy rows take no draw and no parameters but temp = 0: nothing to send to the device
             g = self._greedy.get(rows)
@@ -104,7 +107,8 @@ class DeviceSampler:
                      torch.empty(1, dtype=torch.float32, device=self.device))
                 self._greedy[rows] = g
             fd, kd, scratch = g
-            out = torch.empty(rows, dtype=torch.int32, device=self.device)
+            if out is None:
+                out = torch.empty(rows, dtype=torch.int32, device=self.device)
             kernels.sample(logits, fd[0], kd, fd[1], fd[2], fd[3], fd[4], None, scratch, out, False)
             return out
         f = np.zeros((5, rows), dtype=np.float32)
@@ -126,6 +130,7 @@ class DeviceSampler:
         need = rows * V if any_sampled else 1
         if self._scratch is None or self._scratch.numel() < need:
             self._scratch = torch.empty(need, dtype=torch.float32, device=self.device)
-        out = torch.empty(rows, dtype=torch.int32, device=self.device)
+        if out is None:
+            out = torch.empty(rows, dtype=torch.int32, device=self.device)
         kernels.sample(logits, fd[0], kd, fd[1], fd[2], fd[3], fd[4], recent, self._scratch, out, any_sampled)
         return out
