@@ -312,9 +312,11 @@ class Scheduler:
 
     def _plan_ahead(self, plan: StepPlan) -> Optional[StepPlan]:
         """The step after `plan`, if it can be told without `plan`'s tokens: `plan` decodes one token for every
-        live request, nobody waits, and every request can take one more token afterwards.  Reserves its pages."""
-        if self.waiting or plan.preempted or len(plan.entries) != len(self.live):
+        live request, nobody can be admitted, and every request can take one more token afterwards.  Reserves its pages."""
+        if plan.preempted or len(plan.entries) != len(self.live):
             return None
+        if self.waiting and self.cache.has_free_slot():
+            return None                      # the next plan may admit somebody: that is for plan() to decide
         limit = self.cache.max_pages_per_request * self.cache.page_size
         for e in plan.entries:
             r = e.request
