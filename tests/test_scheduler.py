@@ -167,6 +167,56 @@ def test_random_load_with_a_starved_pool_gives_every_request_its_own_tokens(seed
     assert cache.free_pages() == [cache.pools[0].n_pages] and not cache.live_requests()
 
 
+class PipelinedFakeExecutor(FakeExecutor):
+    """The same with `launch` / `wait`, as an executor that leaves sampled ids on the device has them: a step may
+    be launched before the tokens of the step ahead of it were read; an entry fed from that step carries the
+    scheduler's IN_FLIGHT mark, and the token it stands for is looked up here when the step 'runs' (at wait)."""
+
+    def __init__(self, cache, stop_at=None):
+        super().__init__(cache, stop_at)
+        self.launched_ahead = 0
+
+    def launch(self, plan, feed_rows=None):
+        from xyntetik_runner_b200.engine.scheduler import IN_FLIGHT
+        for e in plan.entries:
+            fed = feed_rows is not None and e.request.id in feed_rows
+            assert (IN_FLIGHT in e.tokens) == fed, "a token that is still in flight must come through the feed"
+        self.launched_ahead += feed_rows is not None
+        return self.run(plan)          # commits at launch, as Engine.step does
+
+    def wait(self, handle):
+        return handle
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_steps_launched_ahead_change_nothing(seed):
+    """Random loads (starved pools, stop tokens, short and long requests) with and without looking ahead: the
+    same tokens, the same reasons, every page back."""
+    outcomes = []
+    for ahead in (False, True):
+        rng = np.random.RandomState(100 + seed)
+        n_pages, page = int(rng.randint(14, 40)), 4
+        cache = CacheManager([GroupSpec("full")], n_pages, page, 4, 60)
+        sizes = [(int(rng.randint(1, 20)), int(rng.randint(1, 25))) for _ in range(10)]
+        # every third request meets the stop token (7) somewhere among the tokens it would generate
+        stops = {(i, sizes[i][0] + int(rng.randint(1, sizes[i][1] + 1))): 7 for i in range(0, 10, 3)}
+        ex = PipelinedFakeExecutor(cache, stops)
+        s = Scheduler(cache, ex, SchedulerParams(max_step_tokens=int(rng.randint(8, 30)), prefill_chunk=int(rng.randint(3, 12)),
+                                                 look_ahead=ahead))
+        for i, (n, k) in enumerate(sizes):
+            s.add(Request(i, [int(t) for t in rng.randint(10, 50, size=n)], max_new_tokens=k, stop_ids=(7,)))
+        steps = 0
+        while s.has_work():
+            s.step(); steps += 1
+            cache.audit()
+            assert steps < 5000
+        assert cache.free_pages() == [n_pages] and not cache.live_requests()
+        assert (ex.launched_ahead > 0) == ahead
+        outcomes.append({i: (r.generated, r.finish_reason) for i, r in s.finished.items()})
+    assert outcomes[0] == outcomes[1]
+    assert any(reason == "stop" for _, reason in outcomes[0].values())
+
+
 def test_sampler_state_is_per_request_and_follows_the_reference_generator():
     from plain_llama import uniform_from_state, xorshift64
     s = RequestSampler(SamplingParams(temperature=0.8, seed=12345))
