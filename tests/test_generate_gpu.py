@@ -151,6 +151,43 @@ def test_steps_launched_ahead_give_the_same_tokens(folders, temp):
     assert got == want and reasons_ahead == reasons
 
 
+_DIGEST_SCRIPT = """
+import hashlib, sys
+import numpy as np
+sys.path.insert(0, {root!r})
+from xyntetik_runner_b200.config.llama import LlamaConfig
+from xyntetik_runner_b200.engine.runner import Runner
+cfg = LlamaConfig.from_dict({{"architectures": ["LlamaForCausalLM"], "hidden_size": 4096, "num_hidden_layers": 2,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 14336, "vocab_size": 32000,
+    "rms_norm_eps": 1e-5, "rope_theta": 500000.0, "max_position_embeddings": 2048, "tie_word_embeddings": False,
+    "hidden_act": "silu", "torch_dtype": "bfloat16"}})
+rng = np.random.RandomState(1)
+prompts = [[int(t) for t in rng.randint(0, cfg.vocab_size, size=n)] for n in (700, 333, 64, 17, 450, 1100)]
+r = Runner(config=cfg, random_seed=5, ctx=2048, batch=1024, parallel=6)
+h = hashlib.sha256()
+for g in r.generate(prompts, n=48, ignore_eos=True):
+    h.update(np.asarray(g.tokens, dtype=np.int64).tobytes())
+print("digest", h.hexdigest(), r.engine.graph_replays)
+"""
+
+
+def test_dependent_launch_and_copy_variants_change_no_token(tmp_path):
+    """Kernels start before the kernel ahead of them has ended and read, until they wait, only what a step does not
+    change (weights, the step's description, keys of earlier steps).  If one read anything else early, tokens
+    would depend on timing: the same greedy run at 8B layer sizes must give the same ids with programmatic
+    dependent launch switched off, and with the decode attention's bulk copies replaced by per-thread copies."""
+    script = tmp_path / "digest.py"
+    script.write_text(_DIGEST_SCRIPT.format(root=ROOT))
+    digests = []
+    for extra in ({}, {"XRB200_NO_PDL": "1"}, {"XRB200_NO_TMA_ATTENTION": "1"}):
+        p = subprocess.run([sys.executable, str(script)], capture_output=True, text=True, env=dict(os.environ, **extra), timeout=600)
+        assert p.returncode == 0, p.stderr[-2000:]
+        line = [l for l in p.stdout.splitlines() if l.startswith("digest")][-1].split()
+        assert int(line[2]) > 20                     # decode steps were replayed from CUDA graphs
+        digests.append(line[1])
+    assert digests[0] == digests[1] == digests[2]
+
+
 def test_starved_pool_preempts_and_gives_the_same_tokens(folders):
     from xyntetik_runner_b200.engine.runner import Runner
     folder = folders["A", "float32"]
