@@ -10,15 +10,17 @@
 //   warps 0..7 : softmax.  Row r = tensor-memory lane r is shared by two threads (warps w and w + 4 may both
 //                read lanes 32 (w % 4) ..): one takes keys 0..63 of a tile, the other keys 64..127; they
 //                exchange their maxima through shared memory.  Per tile: read S, running maximum, rescale O in
-//                tensor memory when needed, write P = exp(S - m) as bfloat16 into shared memory in the layout
-//                the matrix instruction reads (K-major, 128-byte swizzle).  One softmax warp per scheduler
-//                could not hide its own latencies; two can.
+//                tensor memory when needed, write P = exp(S - m) as bfloat16 over the first 64 columns of the
+//                tile's own S in tensor memory (row = lane, two values per column), where the product reads it
+//                as its A operand.  One softmax warp per scheduler could not hide its own latencies; two can.
+//                (A variant that passes P through shared memory, K-major with the 128-byte swizzle, is kept for
+//                comparisons: XRB200_ATTENTION_P_SMEM=1.)
 //   warp 8     : one lane issues the TMA copies of Q (once) and of the K tiles (two-stage ring; a K stage is free
 //                as soon as its Q K^T has run, so the next-but-one tile's keys are fetched two tiles ahead).
 //   warp 9     : one lane issues the matrix instructions; the warp owns the tensor-memory allocation.
 //   warp 10    : one lane issues the TMA copies of the V tiles (two-stage ring, freed by P V).
-// S and P are double buffered (S of tile j+1 is computed, and P of tile j is consumed, while the softmax of
-// the neighbouring tile runs); O is one accumulator.  O and the running sum carry an offset m per row; the offset
+// S (and with it P) is double buffered (S of tile j+1 is computed, and P of tile j is consumed, while the softmax
+// of the neighbouring tile runs); O is one accumulator.  O and the running sum carry an offset m per row; the offset
 // is moved (and O rescaled, which has to wait for the product in flight) only when a row's maximum has grown by
 // more than 8 (in log2) since it was set, so most tiles never wait: exp2(s - m) then stays below 2^8.
 // V is the B operand of P V with N = head size contiguous in memory (an "MN-major" operand): its shared

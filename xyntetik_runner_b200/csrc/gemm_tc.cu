@@ -7,14 +7,15 @@
 // (128 x 256 tiles).  Both operands are K-major in global memory, which is what TMA with the
 // 128-byte swizzle and the K-major shared-memory descriptor want: no transposes anywhere.
 //
-// Roles inside a CTA of 320 threads:
+// Roles inside a CTA of 320 threads (192 for the 16-token tile, 576 in the CTA-pair kernel):
 //   warp 0, one lane : TMA producer  (cp.async.bulk.tensor.2d -> shared, completes on an mbarrier)
 //   warp 1, one lane : MMA issuer    (tcgen05.mma, commits free the stage / signal the epilogue);
 //                      the warp also allocates and frees tensor memory
-//   warps 2..9       : epilogue      (tcgen05.ld of their 32 lanes, then global stores); a warp may only
-//                      read the 32 tensor-memory lanes of its index mod 4, so two warps share each quarter
-//                      and take alternate 16-column chunks
-// A K loop over 64-element blocks runs through a ring of shared-memory stages.
+//   warps 2..        : epilogue      (tcgen05.ld of their 32 lanes, then global stores); a warp may only
+//                      read the 32 tensor-memory lanes of its index mod 4, so the warps of a quarter
+//                      take alternate 16-column chunks
+// A K loop over 64-element blocks runs through a ring of shared-memory stages.  Steps of more than 128 tokens
+// run on pairs of CTAs (k_gemm_tc_pair below): persistent clusters of two, one instruction across both.
 //
 // Epilogues: store (bfloat16 or float32, optional bias), add into the float32 residual stream,
 // two-accumulator SwiGLU (gate rows and up rows of the same features multiply the same X tile;
