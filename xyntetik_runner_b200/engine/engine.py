@@ -160,7 +160,6 @@ class Engine:
         # CUDA graphs of decode-only steps, keyed by (tokens, wanted rows, context bucket).  A graph holds the
         # addresses of the step's buffers, so any buffer that is made anew invalidates all graphs.
         self._graphs: Dict[tuple, object] = {}
-        self._feed_ptr = None
         self._graph_ok = p.cuda_graphs and all(part.graph_safe for part in plan.parts())
         self._graph_seen: Dict[tuple, int] = {}
         self._buf_generation = 0
@@ -220,7 +219,7 @@ class Engine:
         """Run one batch.  Returns float32 logits [number of wanted places, vocab] on the device, in the
         order of the entries and of each entry's `want`; the tensor is reused by the next step.
 
-        `feed`: int32 tokens on the device (always the same tensor); a token id -(1 + j) in an entry stands for
+        `feed`: int32 tokens on the device; a token id -(1 + j) in an entry stands for
         feed[j] as it is when this step runs, e.g. what the step before sampled, which the host has not read yet.
 
         Unless `reserved`, pages for every entry's tokens are taken here (all or nothing: on
@@ -253,10 +252,6 @@ class Engine:
                 raise
         ctx = self._describe(entries)
         ctx.token_feed = feed
-        if feed is not None:
-            if self._feed_ptr not in (None, feed.data_ptr()):
-                raise ValueError("the token feed must be the same tensor in every step")
-            self._feed_ptr = feed.data_ptr()
         if ctx.decode_only and self._graph_ok:
             logits = self._forward_graphed(ctx)
         else:
@@ -334,7 +329,7 @@ class Engine:
         """Decode-only steps have the same launches whenever batch size and context bucket repeat: the
         first such step runs plainly (and makes every buffer), the second is captured, later ones replay.
         Everything that changes from step to step is in the step description, which is copied before."""
-        key = (ctx.n, ctx.n_rows, ctx.max_kv_len, ctx.token_feed is not None)
+        key = (ctx.n, ctx.n_rows, ctx.max_kv_len, None if ctx.token_feed is None else ctx.token_feed.data_ptr())
         g = self._graphs.get(key)
         if g is not None:
             g.replay()
