@@ -185,7 +185,13 @@ __global__ void k_finish_plain(const float* __restrict__ partial, int splits, in
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         size_t t = i / width, r = i % width;
         float v = 0.f;
-        for (int s = 0; s < splits; s++) v += partial[((size_t)s * n + t) * width + r];
+        for (int s0 = 0; s0 < splits; s0 += 8) {
+            float a[8];
+#pragma unroll
+            for (int q = 0; q < 8; q++) a[q] = __ldcg(partial + ((size_t)min(s0 + q, splits - 1) * n + t) * width + r);
+#pragma unroll
+            for (int q = 0; q < 8; q++) v += s0 + q < splits ? a[q] : 0.f;
+        }
         if (bias) v += bias[r];
         size_t o = t * ldo + r;
         if (ACCUM) out[o] = xr_from_f32<TO>(xr_to_f32<TO>(out[o]) + v);
@@ -239,11 +245,26 @@ __global__ void k_finish_rope_store(FinishRopeArgs a) {
         bool rot_lo = (is_q || is_k) && j < half;
         bool rot_hi = (is_q || is_k) && j >= half && j < 2 * half;
         if (rot_hi) continue;                                 // written by the thread that owns j - half
+        // the loads of eight splits are in flight together (indices clamped, so that none is conditional); the sums
+        // are taken in split order
         float v0 = 0.f, v1 = 0.f;
-        for (int s = 0; s < a.splits; s++) {
-            const float* p = a.partial + ((size_t)s * a.n + t) * qkv_dim + col0;
-            v0 += p[j];
-            if (rot_lo) v1 += p[j + half];
+        const int j1 = rot_lo ? j + half : j;
+        const size_t split_stride = (size_t)a.n * qkv_dim;
+        const float* p0 = a.partial + (size_t)t * qkv_dim + col0;
+        for (int s0 = 0; s0 < a.splits; s0 += 8) {
+            float x0[8], x1[8];
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+                const float* p = p0 + (size_t)min(s0 + q, a.splits - 1) * split_stride;
+                x0[q] = __ldcg(p + j);
+                x1[q] = __ldcg(p + j1);
+            }
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+                const bool live = s0 + q < a.splits;
+                v0 += live ? x0[q] : 0.f;
+                v1 += (live && rot_lo) ? x1[q] : 0.f;
+            }
         }
         if (a.bias) { v0 += a.bias[col0 + j]; if (rot_lo) v1 += a.bias[col0 + j + half]; }
         if (rot_lo) {

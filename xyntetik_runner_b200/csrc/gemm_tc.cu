@@ -541,11 +541,23 @@ __global__ void k_splitk_finish(FinishParams p) {
     size_t width = p.dual ? 2 * (size_t)p.n_out : (size_t)p.n_out;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         size_t t = i / p.n_out, r = i % p.n_out;
+        // four splits' loads in flight together (indices clamped: no load is conditional), summed in split order
         float g = 0.f, u = 0.f;
-        for (int s = 0; s < p.splits; s++) {
-            const float* src = p.partial + ((size_t)s * p.n + t) * width;
-            g += src[r];
-            if (p.dual) u += src[p.n_out + r];
+        const size_t ru = p.dual ? p.n_out + r : r;
+        for (int s0 = 0; s0 < p.splits; s0 += 4) {
+            float a[4], b[4];
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const float* src = p.partial + ((size_t)min(s0 + q, p.splits - 1) * p.n + t) * width;
+                a[q] = __ldcg(src + r);
+                b[q] = __ldcg(src + ru);
+            }
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const bool live = s0 + q < p.splits;
+                g += live ? a[q] : 0.f;
+                u += (live && p.dual) ? b[q] : 0.f;
+            }
         }
         float v;
         if (p.dual) v = tc_silu(g) * u;
