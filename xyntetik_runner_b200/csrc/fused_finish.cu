@@ -95,7 +95,6 @@ __global__ void __launch_bounds__(256)
 k_finish_add_rmsnorm_cluster(const float* __restrict__ partial, int splits, int n, const float* __restrict__ bias,
                              float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out, int d, int slice, float eps) {
     xr_pdl_launch();
-    xr_pdl_wait();
     __shared__ float scratch[33];
     __shared__ float slice_ss;
     const int t = blockIdx.x / FIN_CLUSTER;
@@ -103,27 +102,45 @@ k_finish_add_rmsnorm_cluster(const float* __restrict__ partial, int splits, int 
     const int c0 = rank * slice, c1 = min(d, c0 + slice);          // slice <= FIN_CL_PER * blockDim.x
     float* xr = x + (size_t)t * d;
     TO* o = out + (size_t)t * d;
-    const float* p = partial + (size_t)t * d + c0 + threadIdx.x;
+    // Every load is unconditional (an index past the slice is clamped into it and its value dropped), so that all of
+    // them are in flight at once.  The norm's weights and the bias are constants: they are read before the kernel
+    // ahead is known to be complete; the residual and the partial sums after.
+    int idx[FIN_CL_PER];
+    float wv[FIN_CL_PER], bv[FIN_CL_PER];
+#pragma unroll
+    for (int k = 0; k < FIN_CL_PER; k++) {
+        int i = c0 + threadIdx.x + k * blockDim.x;
+        idx[k] = i < c1 ? i : c1 - 1;
+        wv[k] = w[idx[k]];
+        bv[k] = bias ? bias[idx[k]] : 0.f;
+    }
+    xr_pdl_wait();
     const size_t split_stride = (size_t)n * d;
-    float acc[FIN_CL_PER];
+    const float* p = partial + (size_t)t * d;
+    float acc[FIN_CL_PER], old[FIN_CL_PER];
 #pragma unroll
-    for (int k = 0; k < FIN_CL_PER; k++) acc[k] = 0.f;
-#pragma unroll 4
-    for (int s = 0; s < splits; s++) {
-        float v[FIN_CL_PER];
+    for (int k = 0; k < FIN_CL_PER; k++) { acc[k] = 0.f; old[k] = xr[idx[k]]; }
+    for (int s0 = 0; s0 < splits; s0 += 8) {
+        float v[8][FIN_CL_PER];
 #pragma unroll
-        for (int k = 0; k < FIN_CL_PER; k++) v[k] = c0 + (int)(threadIdx.x + k * blockDim.x) < c1 ? __ldcg(p + (size_t)s * split_stride + k * blockDim.x) : 0.f;
+        for (int q = 0; q < 8; q++) {
+            const float* ps = p + (size_t)min(s0 + q, splits - 1) * split_stride;
 #pragma unroll
-        for (int k = 0; k < FIN_CL_PER; k++) acc[k] += v[k];
+            for (int k = 0; k < FIN_CL_PER; k++) v[q][k] = __ldcg(ps + idx[k]);
+        }
+#pragma unroll
+        for (int q = 0; q < 8; q++) {
+            const bool live = s0 + q < splits;
+#pragma unroll
+            for (int k = 0; k < FIN_CL_PER; k++) acc[k] += live ? v[q][k] : 0.f;
+        }
     }
     float ss = 0.f;
 #pragma unroll
     for (int k = 0; k < FIN_CL_PER; k++) {
         int i = c0 + threadIdx.x + k * blockDim.x;
         if (i < c1) {
-            float v = acc[k];
-            if (bias) v += bias[i];
-            v = xr[i] + v;
+            float v = old[k] + (acc[k] + bv[k]);
             xr[i] = v;
             acc[k] = v;
             ss += v * v;
@@ -139,7 +156,7 @@ k_finish_add_rmsnorm_cluster(const float* __restrict__ partial, int splits, int 
 #pragma unroll
     for (int k = 0; k < FIN_CL_PER; k++) {
         int i = c0 + threadIdx.x + k * blockDim.x;
-        if (i < c1) o[i] = xr_from_f32<TO>(acc[k] * scale * w[i]);
+        if (i < c1) o[i] = xr_from_f32<TO>(acc[k] * scale * wv[k]);
     }
     fin_cluster_sync();            // no block leaves while another may still read its shared memory
 }
