@@ -665,14 +665,21 @@ k_attention_merge(AttnMmaArgs a) {
         const float4* src = reinterpret_cast<const float4*>(pa) + e;
         float2 mine[2];
         const int i0 = threadIdx.x, i1 = threadIdx.x + MERGE_THREADS, n_ml = rows_total * n_spans;      // <= 16 * 64 = 2 * 512
-        mine[0] = i0 < n_ml ? __ldcg(reinterpret_cast<const float2*>(ml) + ((i0 % n_spans) * 16 + i0 / n_spans)) : make_float2(0.f, 0.f);
-        mine[1] = i1 < n_ml ? __ldcg(reinterpret_cast<const float2*>(ml) + ((i1 % n_spans) * 16 + i1 / n_spans)) : make_float2(0.f, 0.f);
+        // (indices clamped so that no load is conditional; xr_ld_now / xr_ld_fence keep them together)
+        const int c0 = i0 < n_ml ? i0 : 0, c1 = i1 < n_ml ? i1 : 0;
+        mine[0].x = xr_ld_now(ml + ((c0 % n_spans) * 16 + c0 / n_spans) * 2);
+        mine[0].y = xr_ld_now(ml + ((c0 % n_spans) * 16 + c0 / n_spans) * 2 + 1);
+        mine[1].x = xr_ld_now(ml + ((c1 % n_spans) * 16 + c1 / n_spans) * 2);
+        mine[1].y = xr_ld_now(ml + ((c1 % n_spans) * 16 + c1 / n_spans) * 2 + 1);
         float4 v[4];
 #pragma unroll
         for (int k = 0; k < 4; k++) {
             int sp = g + k * groups;
-            v[k] = __ldcg(src + (size_t)(active && sp < n_spans ? sp : 0) * 16 * QUADS);
+            v[k] = xr_ld_now4(src + (size_t)(active && sp < n_spans ? sp : 0) * 16 * QUADS);
         }
+        xr_ld_fence(mine[0].x); xr_ld_fence(mine[0].y); xr_ld_fence(mine[1].x); xr_ld_fence(mine[1].y);
+#pragma unroll
+        for (int k = 0; k < 4; k++) xr_ld_fence(v[k]);
         if (i0 < n_ml) mls[i0 / n_spans][i0 % n_spans] = mine[0];
         if (i1 < n_ml) mls[i1 / n_spans][i1 % n_spans] = mine[1];
         __syncthreads();

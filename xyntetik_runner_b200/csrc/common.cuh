@@ -52,6 +52,23 @@ static inline int xr_launch_status() {
     return e == cudaSuccess ? XR_OK : XR_ERR_LAUNCH;
 }
 
+// Loads that stay where they are written.  Left to itself the compiler interleaves a run of independent loads with
+// the arithmetic that consumes them (it saves registers), and a latency-bound kernel then pays one trip to L2 per
+// load instead of one per run.  A run of xr_ld_now() calls is issued back to back; xr_ld_fence() on each value
+// after the run keeps every later use behind all of the loads.
+__device__ __forceinline__ float xr_ld_now(const float* p) {
+    float v;
+    asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ float4 xr_ld_now4(const float4* p) {
+    float4 v;
+    asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void xr_ld_fence(float& v) { asm volatile("" : "+f"(v)); }
+__device__ __forceinline__ void xr_ld_fence(float4& v) { asm volatile("" : "+f"(v.x), "+f"(v.y), "+f"(v.z), "+f"(v.w)); }
+
 template <typename T> __device__ __forceinline__ float xr_to_f32(T v);
 template <> __device__ __forceinline__ float xr_to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float xr_to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }

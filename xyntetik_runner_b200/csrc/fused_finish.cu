@@ -74,7 +74,8 @@ k_finish_add_rmsnorm(const float* __restrict__ partial, int splits, int n, const
 
 // The same for few tokens: a cluster of FIN_CLUSTER blocks per token, each block owning a contiguous slice of
 // the row, so that the partial sums are read by eight times as many threads.  The slices' sums of squares
-// meet through distributed shared memory and every block adds them in rank order.
+// meet through distributed shared memory (each block writes its own into all eight) and every block adds them
+// in rank order.
 #define FIN_CLUSTER 8
 #define FIN_CL_PER 4
 __device__ __forceinline__ uint32_t fin_cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
@@ -82,33 +83,32 @@ __device__ __forceinline__ void fin_cluster_sync() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-__device__ __forceinline__ float fin_cluster_read(const float* mine, uint32_t rank) {
+// writes `v` to the same variable in the shared memory of block `rank` of the cluster
+__device__ __forceinline__ void fin_cluster_write(float* mine, uint32_t rank, float v) {
     uint32_t local = (uint32_t)__cvta_generic_to_shared(mine), remote;
-    float v;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-    return v;
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
 }
 
-template <typename TO>
+template <typename TO, int PER>
 __global__ void __launch_bounds__(256)
 k_finish_add_rmsnorm_cluster(const float* __restrict__ partial, int splits, int n, const float* __restrict__ bias,
                              float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out, int d, int slice, float eps) {
     xr_pdl_launch();
     __shared__ float scratch[33];
-    __shared__ float slice_ss;
+    __shared__ float slice_ss[FIN_CLUSTER];      // every block's sum of squares, written here by that block
     const int t = blockIdx.x / FIN_CLUSTER;
     const int rank = (int)fin_cluster_rank();
-    const int c0 = rank * slice, c1 = min(d, c0 + slice);          // slice <= FIN_CL_PER * blockDim.x
+    const int c0 = rank * slice, c1 = min(d, c0 + slice);          // slice <= PER * blockDim.x
     float* xr = x + (size_t)t * d;
     TO* o = out + (size_t)t * d;
     // Every load is unconditional (an index past the slice is clamped into it and its value dropped), so that all of
     // them are in flight at once.  The norm's weights and the bias are constants: they are read before the kernel
     // ahead is known to be complete; the residual and the partial sums after.
-    int idx[FIN_CL_PER];
-    float wv[FIN_CL_PER], bv[FIN_CL_PER];
+    int idx[PER];
+    float wv[PER], bv[PER];
 #pragma unroll
-    for (int k = 0; k < FIN_CL_PER; k++) {
+    for (int k = 0; k < PER; k++) {
         int i = c0 + threadIdx.x + k * blockDim.x;
         idx[k] = i < c1 ? i : c1 - 1;
         wv[k] = w[idx[k]];
@@ -117,27 +117,32 @@ k_finish_add_rmsnorm_cluster(const float* __restrict__ partial, int splits, int 
     xr_pdl_wait();
     const size_t split_stride = (size_t)n * d;
     const float* p = partial + (size_t)t * d;
-    float acc[FIN_CL_PER], old[FIN_CL_PER];
+    float acc[PER], old[PER];
 #pragma unroll
-    for (int k = 0; k < FIN_CL_PER; k++) { acc[k] = 0.f; old[k] = xr[idx[k]]; }
-    for (int s0 = 0; s0 < splits; s0 += 8) {
-        float v[8][FIN_CL_PER];
+    for (int k = 0; k < PER; k++) { acc[k] = 0.f; old[k] = xr_ld_now(xr + idx[k]); }
+    for (int s0 = 0; s0 < splits; s0 += 16) {
+        float v[16][PER];
 #pragma unroll
-        for (int q = 0; q < 8; q++) {
+        for (int q = 0; q < 16; q++) {
             const float* ps = p + (size_t)min(s0 + q, splits - 1) * split_stride;
 #pragma unroll
-            for (int k = 0; k < FIN_CL_PER; k++) v[q][k] = __ldcg(ps + idx[k]);
+            for (int k = 0; k < PER; k++) v[q][k] = xr_ld_now(ps + idx[k]);
         }
+        // nothing below may be scheduled among the loads above
 #pragma unroll
-        for (int q = 0; q < 8; q++) {
+        for (int q = 0; q < 16; q++)
+#pragma unroll
+            for (int k = 0; k < PER; k++) xr_ld_fence(v[q][k]);
+#pragma unroll
+        for (int q = 0; q < 16; q++) {
             const bool live = s0 + q < splits;
 #pragma unroll
-            for (int k = 0; k < FIN_CL_PER; k++) acc[k] += live ? v[q][k] : 0.f;
+            for (int k = 0; k < PER; k++) acc[k] += live ? v[q][k] : 0.f;
         }
     }
     float ss = 0.f;
 #pragma unroll
-    for (int k = 0; k < FIN_CL_PER; k++) {
+    for (int k = 0; k < PER; k++) {
         int i = c0 + threadIdx.x + k * blockDim.x;
         if (i < c1) {
             float v = old[k] + (acc[k] + bv[k]);
@@ -147,18 +152,19 @@ k_finish_add_rmsnorm_cluster(const float* __restrict__ partial, int splits, int 
         }
     }
     ss = xr_block_sum(ss, scratch);
-    if (threadIdx.x == 0) slice_ss = ss;
+    // each block hands its sum to all eight (itself included); after the one barrier nobody touches a neighbour's
+    // shared memory again, so blocks may leave as they finish
+    if (threadIdx.x < FIN_CLUSTER) fin_cluster_write(&slice_ss[rank], (uint32_t)threadIdx.x, ss);
     fin_cluster_sync();
     float total = 0.f;
 #pragma unroll
-    for (int r = 0; r < FIN_CLUSTER; r++) total += fin_cluster_read(&slice_ss, (uint32_t)r);
+    for (int r = 0; r < FIN_CLUSTER; r++) total += slice_ss[r];
     float scale = 1.0f / sqrtf(total / (float)d + eps);
 #pragma unroll
-    for (int k = 0; k < FIN_CL_PER; k++) {
+    for (int k = 0; k < PER; k++) {
         int i = c0 + threadIdx.x + k * blockDim.x;
         if (i < c1) o[i] = xr_from_f32<TO>(acc[k] * scale * wv[k]);
     }
-    fin_cluster_sync();            // no block leaves while another may still read its shared memory
 }
 
 template <typename TO>
@@ -173,7 +179,9 @@ static int launch_finish_cluster(const float* partial, int splits, const float* 
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = xr_pdl_enabled() ? 2 : 1;
-    cudaLaunchKernelEx(&cfg, k_finish_add_rmsnorm_cluster<TO>, partial, splits, n, bias, x, w, out, d, slice, eps);
+    if (slice <= 256) cudaLaunchKernelEx(&cfg, k_finish_add_rmsnorm_cluster<TO, 1>, partial, splits, n, bias, x, w, out, d, slice, eps);
+    else if (slice <= 512) cudaLaunchKernelEx(&cfg, k_finish_add_rmsnorm_cluster<TO, 2>, partial, splits, n, bias, x, w, out, d, slice, eps);
+    else cudaLaunchKernelEx(&cfg, k_finish_add_rmsnorm_cluster<TO, 4>, partial, splits, n, bias, x, w, out, d, slice, eps);
     return xr_launch_status();
 }
 
@@ -205,7 +213,9 @@ __global__ void k_finish_plain(const float* __restrict__ partial, int splits, in
         for (int s0 = 0; s0 < splits; s0 += 8) {
             float a[8];
 #pragma unroll
-            for (int q = 0; q < 8; q++) a[q] = __ldcg(partial + ((size_t)min(s0 + q, splits - 1) * n + t) * width + r);
+            for (int q = 0; q < 8; q++) a[q] = xr_ld_now(partial + ((size_t)min(s0 + q, splits - 1) * n + t) * width + r);
+#pragma unroll
+            for (int q = 0; q < 8; q++) xr_ld_fence(a[q]);
 #pragma unroll
             for (int q = 0; q < 8; q++) v += s0 + q < splits ? a[q] : 0.f;
         }
@@ -273,9 +283,11 @@ __global__ void k_finish_rope_store(FinishRopeArgs a) {
 #pragma unroll
             for (int q = 0; q < 8; q++) {
                 const float* p = p0 + (size_t)min(s0 + q, a.splits - 1) * split_stride;
-                x0[q] = __ldcg(p + j);
-                x1[q] = __ldcg(p + j1);
+                x0[q] = xr_ld_now(p + j);
+                x1[q] = xr_ld_now(p + j1);
             }
+#pragma unroll
+            for (int q = 0; q < 8; q++) { xr_ld_fence(x0[q]); xr_ld_fence(x1[q]); }
 #pragma unroll
             for (int q = 0; q < 8; q++) {
                 const bool live = s0 + q < a.splits;

@@ -167,7 +167,9 @@ __device__ __forceinline__ void tc_epilogue(const TcParams& p, uint32_t tmem_bas
             float* dst = (float*)p.out + (size_t)(tok0 + c0) * p.ldo + r;
             float old[16];
 #pragma unroll
-            for (int c = 0; c < 16; c++) old[c] = (tok0 + c0 + c < p.n) ? dst[(size_t)c * p.ldo] : 0.f;
+            for (int c = 0; c < 16; c++) old[c] = xr_ld_now(dst + (size_t)(tok0 + c0 + c < p.n ? c : 0) * p.ldo);
+#pragma unroll
+            for (int c = 0; c < 16; c++) xr_ld_fence(old[c]);
 #pragma unroll
             for (int c = 0; c < 16; c++)
                 if (tok0 + c0 + c < p.n) dst[(size_t)c * p.ldo] = old[c] + (g[c] + b);
@@ -549,9 +551,11 @@ __global__ void k_splitk_finish(FinishParams p) {
 #pragma unroll
             for (int q = 0; q < 4; q++) {
                 const float* src = p.partial + ((size_t)min(s0 + q, p.splits - 1) * p.n + t) * width;
-                a[q] = __ldcg(src + r);
-                b[q] = __ldcg(src + ru);
+                a[q] = xr_ld_now(src + r);
+                b[q] = xr_ld_now(src + ru);
             }
+#pragma unroll
+            for (int q = 0; q < 4; q++) { xr_ld_fence(a[q]); xr_ld_fence(b[q]); }
 #pragma unroll
             for (int q = 0; q < 4; q++) {
                 const bool live = s0 + q < p.splits;
