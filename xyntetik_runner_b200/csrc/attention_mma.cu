@@ -653,84 +653,6 @@ k_attention_merge(AttnMmaArgs a) {
     const float* ml = a.part_ml + item0 * 32;
     const float* pa = a.part_acc + item0 * 16 * HD;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (n_spans <= MERGE_SPANS) {
-        // The usual case, in one round of global loads: every thread fetches the (maximum, sum) pairs it is to put into
-        // shared memory AND the first accumulator quadruples it will weigh, before anything is computed; the rows'
-        // maxima and denominators, and then the weights, come from shared memory.
-        __shared__ float2 mls[16][MERGE_SPANS];
-        constexpr int QUADS = HD / 4;
-        const int owned = rows_total * QUADS, groups = MERGE_THREADS / owned;
-        const int g = threadIdx.x / owned, e = threadIdx.x % owned, r = e / QUADS;
-        const bool active = g < groups;
-        const float4* src = reinterpret_cast<const float4*>(pa) + e;
-        float2 mine[2];
-        const int i0 = threadIdx.x, i1 = threadIdx.x + MERGE_THREADS, n_ml = rows_total * n_spans;      // <= 16 * 64 = 2 * 512
-        // (indices clamped so that no load is conditional; xr_ld_now / xr_ld_fence keep them together)
-        const int c0 = i0 < n_ml ? i0 : 0, c1 = i1 < n_ml ? i1 : 0;
-        mine[0].x = xr_ld_now(ml + ((c0 % n_spans) * 16 + c0 / n_spans) * 2);
-        mine[0].y = xr_ld_now(ml + ((c0 % n_spans) * 16 + c0 / n_spans) * 2 + 1);
-        mine[1].x = xr_ld_now(ml + ((c1 % n_spans) * 16 + c1 / n_spans) * 2);
-        mine[1].y = xr_ld_now(ml + ((c1 % n_spans) * 16 + c1 / n_spans) * 2 + 1);
-        float4 v[4];
-#pragma unroll
-        for (int k = 0; k < 4; k++) {
-            int sp = g + k * groups;
-            v[k] = xr_ld_now4(src + (size_t)(active && sp < n_spans ? sp : 0) * 16 * QUADS);
-        }
-        xr_ld_fence(mine[0].x); xr_ld_fence(mine[0].y); xr_ld_fence(mine[1].x); xr_ld_fence(mine[1].y);
-#pragma unroll
-        for (int k = 0; k < 4; k++) xr_ld_fence(v[k]);
-        if (i0 < n_ml) mls[i0 / n_spans][i0 % n_spans] = mine[0];
-        if (i1 < n_ml) mls[i1 / n_spans][i1 % n_spans] = mine[1];
-        __syncthreads();
-        for (int rr = warp; rr < rows_total; rr += MERGE_THREADS / 32) {
-            float mm = -INFINITY;
-            for (int sp = lane; sp < n_spans; sp += 32) mm = fmaxf(mm, mls[rr][sp].x);
-            mm = xr_warp_max(mm);
-            float off = mm == -INFINITY ? 0.f : mm;
-            float ll = 0.f;                      // summed in a fixed order: lane-strided, then the warp tree
-            for (int sp = lane; sp < n_spans; sp += 32) ll += mls[rr][sp].y * expf(mls[rr][sp].x - off);
-            ll = xr_warp_sum(ll);
-            if (lane == 0) { row_max[rr] = off; row_inv[rr] = 1.0f / ll; }
-        }
-        __syncthreads();
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (active) {
-            const float off = row_max[r];
-#pragma unroll
-            for (int k = 0; k < 4; k++) {
-                int sp = g + k * groups;
-                if (sp < n_spans) {
-                    float wk = expf(mls[r][sp].x - off);
-                    acc.x += v[k].x * wk; acc.y += v[k].y * wk; acc.z += v[k].z * wk; acc.w += v[k].w * wk;
-                }
-            }
-            for (int sp = g + 4 * groups; sp < n_spans; sp += groups) {
-                float4 u = __ldcg(src + (size_t)sp * 16 * QUADS);
-                float wk = expf(mls[r][sp].x - off);
-                acc.x += u.x * wk; acc.y += u.y * wk; acc.z += u.z * wk; acc.w += u.w * wk;
-            }
-        }
-        group_sum[threadIdx.x] = acc;
-        __syncthreads();
-        if (threadIdx.x < owned) {
-            float4 t = group_sum[threadIdx.x];
-            for (int k = 1; k < groups; k++) {
-                float4 u = group_sum[k * owned + threadIdx.x];
-                t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w;
-            }
-            const float inv = row_inv[r];
-            const int d = (e % QUADS) * 4;
-            __nv_bfloat16* dst = a.out + ((long long)(tok_base + r / a.G) * a.H + (kvh * a.G + r % a.G)) * HD + d;
-            __nv_bfloat162 lo2 = __floats2bfloat162_rn(t.x * inv, t.y * inv), hi2 = __floats2bfloat162_rn(t.z * inv, t.w * inv);
-            uint2 packed;
-            packed.x = *reinterpret_cast<uint32_t*>(&lo2);
-            packed.y = *reinterpret_cast<uint32_t*>(&hi2);
-            *reinterpret_cast<uint2*>(dst) = packed;
-        }
-        return;
-    }
-    // more spans than the weights' shared memory holds at once: in rounds
     // one warp per row: maximum and denominator over the spans
     for (int r = warp; r < rows_total; r += MERGE_THREADS / 32) {
         float mm = -INFINITY;
@@ -796,6 +718,98 @@ k_attention_merge(AttnMmaArgs a) {
         packed.y = *reinterpret_cast<uint32_t*>(&hi2);
         *reinterpret_cast<uint2*>(dst) = packed;
     }
+}
+
+// The same for at most MERGE_SPANS spans per request (what the launcher's span choice gives unless a context is very
+// long and alone), in one round of global loads and little code: a kernel this short spends as long fetching its
+// instructions as running them, so the rare general case lives in a kernel of its own (k_attention_merge).
+template <int HD>
+__global__ void __launch_bounds__(MERGE_THREADS)
+k_attention_merge_small(AttnMmaArgs a) {
+    xr_pdl_launch();
+    xr_pdl_wait();
+    __shared__ float4 group_sum[MERGE_THREADS];
+    const int seg = blockIdx.y, kvh = blockIdx.x;
+    const int L = a.seg_len[seg], rows_total = L * a.G;
+    if (rows_total > 16) return;
+    const int pos0 = a.seg_pos0[seg], tok_base = a.seg_start[seg];
+    const int hi_all = pos0 + L - 1;
+    const int lo_all = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
+    const int n_spans = hi_all / a.span - lo_all / a.span + 1;
+    const size_t item0 = ((size_t)seg * a.K + kvh) * a.max_splits;
+    const float* ml = a.part_ml + item0 * 32;
+    const float* pa = a.part_acc + item0 * 16 * HD;
+    // The usual case, in one round of global loads: every thread fetches the (maximum, sum) pairs it is to put into
+    // shared memory AND the first accumulator quadruples it will weigh, before anything is computed; the rows'
+    // maxima and denominators, and then the weights, come from shared memory.
+    __shared__ float2 mls[16][MERGE_SPANS];
+    constexpr int QUADS = HD / 4;
+    const int owned = rows_total * QUADS, groups = MERGE_THREADS / owned;
+    const int g = threadIdx.x / owned, e = threadIdx.x % owned, r = e / QUADS;
+    const bool active = g < groups;
+    const float4* src = reinterpret_cast<const float4*>(pa) + e;
+    float2 mine[2];
+    const int i0 = threadIdx.x, i1 = threadIdx.x + MERGE_THREADS, n_ml = rows_total * n_spans;      // <= 16 * 64 = 2 * 512
+    // (indices clamped so that no load is conditional; xr_ld_now / xr_ld_fence keep them together)
+    const int c0 = i0 < n_ml ? i0 : 0, c1 = i1 < n_ml ? i1 : 0;
+    mine[0].x = xr_ld_now(ml + ((c0 % n_spans) * 16 + c0 / n_spans) * 2);
+    mine[0].y = xr_ld_now(ml + ((c0 % n_spans) * 16 + c0 / n_spans) * 2 + 1);
+    mine[1].x = xr_ld_now(ml + ((c1 % n_spans) * 16 + c1 / n_spans) * 2);
+    mine[1].y = xr_ld_now(ml + ((c1 % n_spans) * 16 + c1 / n_spans) * 2 + 1);
+    float4 v[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        int sp = g + k * groups;
+        v[k] = xr_ld_now4(src + (size_t)(active && sp < n_spans ? sp : 0) * 16 * QUADS);
+    }
+    xr_ld_fence(mine[0].x); xr_ld_fence(mine[0].y); xr_ld_fence(mine[1].x); xr_ld_fence(mine[1].y);
+#pragma unroll
+    for (int k = 0; k < 4; k++) xr_ld_fence(v[k]);
+    if (i0 < n_ml) mls[i0 / n_spans][i0 % n_spans] = mine[0];
+    if (i1 < n_ml) mls[i1 / n_spans][i1 % n_spans] = mine[1];
+    __syncthreads();
+    // every thread works out its own row's maximum and denominator from shared memory, walking the spans in order
+    // (a few dozen at most): cheaper than a phase of its own with a barrier after it, and the same sum in every thread
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float inv = 0.f;
+    if (active) {
+        float mm = -INFINITY;
+        for (int sp = 0; sp < n_spans; sp++) mm = fmaxf(mm, mls[r][sp].x);
+        const float off = mm == -INFINITY ? 0.f : mm;
+        float ll = 0.f;
+        for (int sp = 0; sp < n_spans; sp++) ll += mls[r][sp].y * __expf(mls[r][sp].x - off);
+        inv = 1.0f / ll;
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            int sp = g + k * groups;
+            if (sp < n_spans) {
+                float wk = __expf(mls[r][sp].x - off);
+                acc.x += v[k].x * wk; acc.y += v[k].y * wk; acc.z += v[k].z * wk; acc.w += v[k].w * wk;
+            }
+        }
+        for (int sp = g + 4 * groups; sp < n_spans; sp += groups) {
+            float4 u = __ldcg(src + (size_t)sp * 16 * QUADS);
+            float wk = __expf(mls[r][sp].x - off);
+            acc.x += u.x * wk; acc.y += u.y * wk; acc.z += u.z * wk; acc.w += u.w * wk;
+        }
+    }
+    group_sum[threadIdx.x] = acc;
+    __syncthreads();
+    if (threadIdx.x < owned) {
+        float4 t = group_sum[threadIdx.x];
+        for (int k = 1; k < groups; k++) {
+            float4 u = group_sum[k * owned + threadIdx.x];
+            t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w;
+        }
+        const int d = (e % QUADS) * 4;
+        __nv_bfloat16* dst = a.out + ((long long)(tok_base + r / a.G) * a.H + (kvh * a.G + r % a.G)) * HD + d;
+        __nv_bfloat162 lo2 = __floats2bfloat162_rn(t.x * inv, t.y * inv), hi2 = __floats2bfloat162_rn(t.z * inv, t.w * inv);
+        uint2 packed;
+        packed.x = *reinterpret_cast<uint32_t*>(&lo2);
+        packed.y = *reinterpret_cast<uint32_t*>(&hi2);
+        *reinterpret_cast<uint2*>(dst) = packed;
+    }
+    return;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -893,7 +907,8 @@ static int launch_attention(const AttnMmaArgs& a, int n_seg, int max_seg_len, in
             xr_launch((k_attention_keys<HD, 2>), dim3(a.max_splits, a.K, n_seg), dim3(ATT_THREADS), SMEM_KEYS2, stream, a);
         int rc = xr_launch_status();
         if (rc != XR_OK) return rc;
-        xr_launch((k_attention_merge<HD>), dim3(a.K, n_seg), dim3(MERGE_THREADS), 0, stream, a);
+        if (a.max_splits <= MERGE_SPANS) xr_launch((k_attention_merge_small<HD>), dim3(a.K, n_seg), dim3(MERGE_THREADS), 0, stream, a);
+        else xr_launch((k_attention_merge<HD>), dim3(a.K, n_seg), dim3(MERGE_THREADS), 0, stream, a);
         return xr_launch_status();
     }
     return XR_OK;
