@@ -30,6 +30,15 @@ NVCC_FLAGS = [
 ]
 
 
+# XRB200_TRACE=1: a library of its own (libxrb200_trace.so) in which every kernel's first thread writes down when
+# it became resident and when the kernel ahead of it in the stream was complete (common.cuh: XR_TRACE), for
+# `python -m xyntetik_runner_b200.probe timeline`.  Never the library that serves.
+TRACE = os.environ.get("XRB200_TRACE", "0") not in ("", "0")
+if TRACE:
+    NVCC_FLAGS = NVCC_FLAGS + ["-DXR_TRACE"]
+    LIB_NAME = "libxrb200_trace.so"
+
+
 class BuildError(RuntimeError):
     pass
 
@@ -89,7 +98,7 @@ def library_path(build: bool = True, verbose: bool = True) -> str:
     """Path of an up-to-date library; compiles it if needed (and allowed)."""
     digest = _digest()
     for d in _build_dirs():
-        lib, stamp = os.path.join(d, LIB_NAME), os.path.join(d, "digest.txt")
+        lib, stamp = os.path.join(d, LIB_NAME), os.path.join(d, "digest_trace.txt" if TRACE else "digest.txt")
         if os.path.isfile(lib) and os.path.isfile(stamp):
             with open(stamp) as f:
                 if f.read().strip() == digest:
@@ -134,14 +143,17 @@ def _compile(out_dir: str, digest: str, verbose: bool) -> str:
         r = subprocess.run(cmd, capture_output=True, text=True, env=env)
         if r.returncode != 0:
             raise BuildError(f"link failed:\n{r.stdout}\n{r.stderr}")
-        for o in objs:
-            os.remove(o)
         lib = os.path.join(out_dir, LIB_NAME)
         os.replace(tmp_lib, lib)                      # atomic: a concurrent reader sees old or new
-        with open(os.path.join(out_dir, "digest.txt"), "w") as f:
+        with open(os.path.join(out_dir, "digest_trace.txt" if TRACE else "digest.txt"), "w") as f:
             f.write(digest + "\n")
     finally:
         stop.set()
+        for src in srcs:                              # objects of this run, also of one that failed half way
+            try:
+                os.remove(os.path.join(out_dir, src[:-3] + f".{os.getpid()}.o"))
+            except OSError:
+                pass
     if verbose:
         _say(f"built {LIB_NAME} in {time.time() - t0:.1f} s")
     return lib

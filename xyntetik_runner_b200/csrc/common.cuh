@@ -23,7 +23,40 @@
 // (the wait returns when the earlier kernel has completed and its writes are visible) and calls
 // xr_pdl_launch() to let the kernel after it start the same way.  Launch latency and block scheduling of
 // back-to-back kernels then overlap instead of adding up.  XRB200_NO_PDL=1 turns the attribute off.
+#ifndef XR_TRACE
 __device__ __forceinline__ void xr_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#else
+// Tracing build (see build.py): thread 0 of block 0 of every launch records the time it reached the wait (it
+// was resident then), the time the wait returned (the kernel ahead was complete) and the launch's shape.  Each
+// source file has its own record; xr_trace_dump (elementwise.cu) collects them through the functions registered here.
+static __device__ unsigned long long xr_tr_buf[4096 * 4];
+static __device__ unsigned int xr_tr_n;
+typedef int (*xr_tr_dump_fn)(unsigned long long*, unsigned int*);
+extern "C" int xr_trace_add(xr_tr_dump_fn fn);
+static int xr_tr_dump_local(unsigned long long* host, unsigned int* n) {
+    cudaMemcpyFromSymbol(n, xr_tr_n, sizeof(unsigned int));
+    cudaMemcpyFromSymbol(host, xr_tr_buf, sizeof(xr_tr_buf));
+    unsigned int zero = 0;
+    cudaMemcpyToSymbol(xr_tr_n, &zero, sizeof(unsigned int));
+    return 0;
+}
+static int xr_tr_registered = xr_trace_add(xr_tr_dump_local);
+__device__ __forceinline__ void xr_pdl_wait() {
+    const bool me = (blockIdx.x | blockIdx.y | blockIdx.z) == 0 && threadIdx.x == 0;
+    unsigned long long t0 = 0, t1 = 0;
+    if (me) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (me) {
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+        unsigned int i = atomicAdd(&xr_tr_n, 1u);
+        if (i < 4096) {
+            xr_tr_buf[4 * i] = t0; xr_tr_buf[4 * i + 1] = t1;
+            xr_tr_buf[4 * i + 2] = ((unsigned long long)gridDim.x << 40) | ((unsigned long long)gridDim.y << 20) | gridDim.z;
+            xr_tr_buf[4 * i + 3] = blockDim.x;
+        }
+    }
+}
+#endif
 __device__ __forceinline__ void xr_pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 #include <stdlib.h>

@@ -332,3 +332,18 @@ XR_EXPORT int xr_residual_add(float* x, const void* dlt, int dtype, int n, int d
     else return XR_ERR_ARG;
     return xr_launch_status();
 }
+
+#ifdef XR_TRACE
+// ---------------------------------------------------------------------------
+// Tracing build only: the records of all source files, one after another.
+// host: [files][4096][4] (time resident, time the wait returned, grid packed 20 bits a dimension, block size);
+// counts: [files] records written since the last call.  Returns the number of files.
+// ---------------------------------------------------------------------------
+static xr_tr_dump_fn g_tr_fns[32];
+static int g_tr_nfns = 0;
+extern "C" int xr_trace_add(xr_tr_dump_fn fn) { if (g_tr_nfns < 32) g_tr_fns[g_tr_nfns++] = fn; return g_tr_nfns; }
+XR_EXPORT int xr_trace_dump(unsigned long long* host, unsigned int* counts) {
+    for (int i = 0; i < g_tr_nfns; i++) g_tr_fns[i](host + (size_t)i * 4096 * 4, counts + i);
+    return g_tr_nfns;
+}
+#endif

@@ -2,11 +2,17 @@
 
     python -m xyntetik_runner_b200.probe gemm --tokens 8 --rows 14336 --k 4096 --epilogue swiglu
     python -m xyntetik_runner_b200.probe attention --batch 8 --context 8192 [--portion 1]
+    XRB200_TRACE=1 python -m xyntetik_runner_b200.probe timeline --batch 8 --context 8192 --layers 8
 
 Times are CUDA-event times of `--iters` launches replayed from one CUDA graph (so that launch gaps do not
 count), each launch on a different copy of the weights / a different layer of the cache, with more than an
 L2's worth of data between two uses of the same bytes.  `--plain` launches without a graph (what a profiler
 should be given).
+
+`timeline` runs decode steps of a random Llama-3-8B-shaped model (a few layers of it) on a library built with
+XRB200_TRACE=1, in which the first thread of every launch writes down when it was resident and when the kernel
+ahead of it was complete, and prints one layer of one step: for each kernel, how long it took from the moment
+it could begin to the moment the next one could.
 """
 from __future__ import annotations
 
@@ -101,6 +107,64 @@ def attention(a) -> None:
           f"{kv_bytes / us / 1e3:.0f} GB/s of keys+values, {flops / us / 1e6:.1f} TFLOP/s")
 
 
+def timeline(a) -> None:
+    import ctypes
+    import numpy as np
+    from .csrc import build
+    if not build.TRACE:
+        raise SystemExit("the timeline needs the tracing library: run with XRB200_TRACE=1")
+    from .config.llama import LlamaConfig
+    from .engine.engine import EngineParams, StepEntry, random_engine
+    from .sampling.sampler import DeviceSampler, RequestSampler, SamplingParams
+    cfg = LlamaConfig.from_dict({
+        "architectures": ["LlamaForCausalLM"], "hidden_size": 4096, "num_hidden_layers": a.layers, "num_attention_heads": 32,
+        "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 14336, "vocab_size": 128256, "rms_norm_eps": 1e-5,
+        "rope_theta": 500000.0, "max_position_embeddings": a.context, "tie_word_embeddings": False, "hidden_act": "silu",
+        "torch_dtype": "bfloat16"})
+    B = a.batch
+    eng = random_engine(cfg, 2, EngineParams(dtype="bfloat16", max_tokens=B * a.context, page_size=64, max_requests=B,
+                                             max_request_tokens=a.context, max_step_tokens=2048))
+    for kv in eng.kv:
+        kv.normal_(0.0, 1.0)
+    sampler = DeviceSampler(eng.device)
+    ids = [f"r{i}" for i in range(B)]
+    for r in ids:
+        eng.adopt(r, a.context - 40)
+    samplers = [RequestSampler(SamplingParams()) for _ in ids]
+    rng = np.random.RandomState(0)
+    lib = kernels.lib()
+    lib.xr_trace_dump.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+    host = (ctypes.c_ulonglong * (32 * 4096 * 4))()
+    counts = (ctypes.c_uint * 32)()
+    for s in range(12):
+        logits = eng.step([StepEntry(r, [int(rng.randint(0, 1000))], [0]) for r in ids])
+        sampler.pick(logits, samplers)
+        if s == 10:
+            torch.cuda.synchronize()
+            lib.xr_trace_dump(host, counts)            # drop what came before the step that is read
+    torch.cuda.synchronize()
+    n_files = lib.xr_trace_dump(host, counts)
+    rec = np.array(host, dtype=np.uint64).reshape(32, 4096, 4)
+    ev = []
+    for f in range(n_files):
+        for k in range(min(int(counts[f]), 4096)):
+            t0, t1, g, b = (int(x) for x in rec[f, k])
+            ev.append((t1, t0, (g >> 40, (g >> 20) & 0xfffff, g & 0xfffff), b))
+    ev.sort()
+    # the step: embed, norm, then ten kernels a layer; print the second layer and the start of the third
+    per_layer = 10
+    first = 2 + per_layer
+    rows = ev[first:first + per_layer + 1]
+    if len(rows) < per_layer + 1:
+        raise SystemExit(f"only {len(ev)} launches were recorded")
+    print(f"one layer of a decode step, batch {B}, context {a.context} (times in us)")
+    print(f"{'could begin':>12} {'resident before':>16} {'took':>7}  grid / block")
+    base = rows[0][0]
+    for (t1, t0, g, b), nxt in zip(rows[:-1], rows[1:]):
+        print(f"{(t1 - base) / 1e3:12.2f} {(t1 - t0) / 1e3:16.2f} {(nxt[0] - t1) / 1e3:7.2f}  {g} / {b}")
+    print(f"layer: {(rows[-1][0] - base) / 1e3:.2f} us")
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m xyntetik_runner_b200.probe")
     sub = ap.add_subparsers(dest="what", required=True)
@@ -120,11 +184,15 @@ def main(argv=None) -> int:
     t.add_argument("--page-size", type=int, default=64)
     t.add_argument("--no-tc", action="store_true", help="prompt portions on the mma.sync kernel instead of tcgen05")
     t.add_argument("--no-tma", action="store_true", help="decode kernel with per-thread cp.async gathers instead of bulk copies")
+    tl = sub.add_parser("timeline")
+    tl.add_argument("--batch", type=int, default=8)
+    tl.add_argument("--context", type=int, default=8192)
+    tl.add_argument("--layers", type=int, default=8)
     for p in (g, t):
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--plain", action="store_true", help="no CUDA graph")
     a = ap.parse_args(argv)
-    (gemm if a.what == "gemm" else attention)(a)
+    {"gemm": gemm, "attention": attention, "timeline": timeline}[a.what](a)
     return 0
 
 
