@@ -727,12 +727,13 @@ template <int HD>
 __global__ void __launch_bounds__(MERGE_THREADS)
 k_attention_merge_small(AttnMmaArgs a) {
     xr_pdl_launch();
-    xr_pdl_wait();
     __shared__ float4 group_sum[MERGE_THREADS];
+    // (the step's description does not change while the step runs: it is read before the kernel ahead is complete)
     const int seg = blockIdx.y, kvh = blockIdx.x;
     const int L = a.seg_len[seg], rows_total = L * a.G;
     if (rows_total > 16) return;
     const int pos0 = a.seg_pos0[seg], tok_base = a.seg_start[seg];
+    xr_pdl_wait();
     const int hi_all = pos0 + L - 1;
     const int lo_all = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
     const int n_spans = hi_all / a.span - lo_all / a.span + 1;

@@ -14,14 +14,33 @@ template <typename TW>
 __global__ void k_embed(const TW* __restrict__ table, const int* __restrict__ ids, const int* __restrict__ feed,
                         float* __restrict__ x, int d, int vocab, int n_feed) {
     xr_pdl_launch();
-    xr_pdl_wait();
+    // The token ids are part of the step's description and the table is a weight: the row is read before the kernel
+    // ahead is complete, sixteen values a thread in one run of loads; only the stores wait.  (A fed token is another
+    // matter: it is what the step before sampled, so it is read after the wait.)
     int t = blockIdx.x;
     int id = ids[t];
-    if (feed != nullptr && id < 0 && -(id + 1) < n_feed) id = feed[-(id + 1)];
+    const bool fed = feed != nullptr && id < 0 && -(id + 1) < n_feed;
+    if (fed) {
+        xr_pdl_wait();
+        id = feed[-(id + 1)];
+    }
     if (id < 0 || id >= vocab) id = 0;
     const TW* row = table + (size_t)id * d;
     float* out = x + (size_t)t * d;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) out[i] = xr_to_f32<TW>(row[i]);
+    for (int i0 = threadIdx.x; i0 < d; i0 += 16 * blockDim.x) {
+        TW v[16];
+#pragma unroll
+        for (int k = 0; k < 16; k++) {
+            int i = i0 + k * blockDim.x;
+            v[k] = row[i < d ? i : d - 1];
+        }
+        if (i0 == (int)threadIdx.x && !fed) xr_pdl_wait();
+#pragma unroll
+        for (int k = 0; k < 16; k++) {
+            int i = i0 + k * blockDim.x;
+            if (i < d) out[i] = xr_to_f32<TW>(v[k]);
+        }
+    }
 }
 
 XR_EXPORT int xr_embed(const void* table, int table_dtype, const int* ids, const int* feed, int n_feed, float* x, int n, int d,

@@ -255,7 +255,8 @@ struct FinishRopeArgs {
 
 __global__ void k_finish_rope_store(FinishRopeArgs a) {
     xr_pdl_launch();
-    xr_pdl_wait();
+    // The step's description (positions, block tables) and the rotation's frequencies do not change while the step
+    // runs: where this token's rows go, and its angles, are worked out before the kernel ahead is complete.
     int t = blockIdx.x, head = blockIdx.y;
     int qkv_dim = (a.H + 2 * a.K) * a.hd;
     int col0 = head * a.hd;
@@ -268,6 +269,17 @@ __global__ void k_finish_rope_store(FinishRopeArgs a) {
         int page = a.block_tables[(size_t)a.tok_seg[t] * a.max_pages + pos / a.page_size];
         dst = a.cache_k + (size_t)page * a.page_stride + (is_k ? 0 : a.v_offset) + ((size_t)kvh * a.page_size + (pos % a.page_size)) * a.hd;
     }
+    const int j_mine = threadIdx.x;                            // the block is as wide as the head for the usual head sizes
+    float cos_mine = 1.f, sin_mine = 0.f, bias0 = 0.f, bias1 = 0.f;
+    if (j_mine < half && (is_q || is_k)) {
+        float ang = (float)pos * a.inv_freq[j_mine];
+        cos_mine = cosf(ang); sin_mine = sinf(ang);
+    }
+    if (a.bias != nullptr && j_mine < a.hd) {
+        bias0 = a.bias[col0 + j_mine];
+        if (j_mine < half && (is_q || is_k)) bias1 = a.bias[col0 + j_mine + half];
+    }
+    xr_pdl_wait();
     for (int j = threadIdx.x; j < a.hd; j += blockDim.x) {
         bool rot_lo = (is_q || is_k) && j < half;
         bool rot_hi = (is_q || is_k) && j >= half && j < 2 * half;
@@ -295,12 +307,16 @@ __global__ void k_finish_rope_store(FinishRopeArgs a) {
                 v1 += (live && rot_lo) ? x1[q] : 0.f;
             }
         }
-        if (a.bias) { v0 += a.bias[col0 + j]; if (rot_lo) v1 += a.bias[col0 + j + half]; }
+        if (j == j_mine) { v0 += bias0; v1 += bias1; }
+        else if (a.bias) { v0 += a.bias[col0 + j]; if (rot_lo) v1 += a.bias[col0 + j + half]; }
         if (rot_lo) {
             // the product's output is rounded to the activation dtype before the rotation, as on the unfused path
             v0 = __bfloat162float(__float2bfloat16_rn(v0)); v1 = __bfloat162float(__float2bfloat16_rn(v1));
-            float ang = (float)pos * a.inv_freq[j];
-            float c = cosf(ang), s = sinf(ang);
+            float c = cos_mine, s = sin_mine;
+            if (j != j_mine) {                                // a head wider than the block: later rounds
+                float ang = (float)pos * a.inv_freq[j];
+                c = cosf(ang); s = sinf(ang);
+            }
             dst[j] = __float2bfloat16_rn(v0 * c - v1 * s);
             dst[j + half] = __float2bfloat16_rn(v0 * s + v1 * c);
         } else {

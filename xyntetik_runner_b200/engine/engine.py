@@ -366,7 +366,9 @@ class Engine:
             ctx.materialize(x)
             return torch.empty((0, plan.vocab_size), dtype=torch.float32, device=self.device)
         hn = ctx.buf("head_normed", (ctx.n_rows, plan.width), ctx.act_dtype)
-        plan.final_norm.forward(ctx, x, hn, rows=ctx.logit_rows)
+        # a step of single tokens that all want their logits: the wanted rows are all rows, in order
+        every_row = ctx.decode_only and ctx.n_rows == ctx.n
+        plan.final_norm.forward(ctx, x, hn, rows=None if every_row else ctx.logit_rows)
         logits = ctx.buf("logits", (ctx.n_rows, plan.vocab_size), torch.float32)
         plan.head.forward(ctx, hn, logits)
         return logits
