@@ -163,6 +163,13 @@ def timeline(a) -> None:
     for (t1, t0, g, b), nxt in zip(rows[:-1], rows[1:]):
         print(f"{(t1 - base) / 1e3:12.2f} {(t1 - t0) / 1e3:16.2f} {(nxt[0] - t1) / 1e3:7.2f}  {g} / {b}")
     print(f"layer: {(rows[-1][0] - base) / 1e3:.2f} us")
+    # the two ends of the last recorded step: embedding and first norm; last finish + final norm, head, sampling
+    step = ev[-(2 + per_layer * a.layers + 3):]
+    print("start and end of the step:")
+    for idx in (0, 1, len(step) - 4, len(step) - 3, len(step) - 2):
+        (t1, t0, g, b), nxt = step[idx], step[idx + 1]
+        print(f"{(t1 - step[0][0]) / 1e3:12.2f} {(t1 - t0) / 1e3:16.2f} {(nxt[0] - t1) / 1e3:7.2f}  {g} / {b}")
+    print(f"step up to the sampling kernel: {(step[-1][0] - step[0][0]) / 1e3:.2f} us")
 
 
 def main(argv=None) -> int:
