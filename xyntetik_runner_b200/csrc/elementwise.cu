@@ -231,7 +231,8 @@ struct __align__(16) Bf16x8 { __nv_bfloat162 p[4]; };
 __global__ void __launch_bounds__(256)
 k_rope_store_vec(RopeStoreArgs a) {
     xr_pdl_launch();
-    xr_pdl_wait();
+    // positions, block tables and frequencies do not change while the step runs: the token's page and the table of
+    // its angles are worked out before the kernel ahead (the product that writes the rows) is complete
     extern __shared__ float rope_cs[];                 // [half] cosines, [half] sines
     const int t = blockIdx.x;
     const int qkv_dim = (a.H + 2 * a.K) * a.hd;
@@ -250,6 +251,7 @@ k_rope_store_vec(RopeStoreArgs a) {
         rope_cs[half + j] = sinf(ang);
     }
     __syncthreads();
+    xr_pdl_wait();
     const int groups = half >> 3;                      // groups of eight pairs per head
     const int rot_heads = kdst ? a.H + a.K : a.H;      // without a cache to write, K is not needed
     for (int u = threadIdx.x; u < rot_heads * groups; u += blockDim.x) {
