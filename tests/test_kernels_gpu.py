@@ -260,6 +260,13 @@ ATT_CASES = [
     (8, 2, 128, 8, 0, [(0, 1), (7, 1), (8, 2), (300, 1), (1029, 1)]),
     (4, 1, 64, 16, 70, [(100, 1), (69, 1), (70, 1), (71, 1), (2100, 3)]),
     (16, 4, 128, 128, 0, [(2500, 1), (127, 1), (128, 1), (3000, 4)]),
+    # enough (request, kv head) pairs that a request is cut into 2 to 8 spans, which the bulk-copy kernel combines
+    # inside a cluster: requests of the same step with fewer spans than the longest (blocks without keys), with
+    # one span, with several rows, and a window
+    (8, 4, 128, 32, 0, [(2099, 1), (69, 1), (600, 1), (1300, 2), (63, 1), (64, 1), (2047, 1), (0, 1)]),
+    (4, 4, 64, 8, 0, [(1099, 1), (500, 4), (1000, 16), (3, 2), (767, 1), (768, 1), (100, 1), (1090, 3), (0, 1), (511, 1), (512, 2), (7, 1)]),
+    (16, 8, 64, 16, 1000, [(4999, 1), (900, 1), (999, 1), (1000, 2), (1001, 1), (3000, 1), (2500, 2), (40, 1)]),
+    (16, 16, 64, 64, 0, [(699, 1), (5, 1), (350, 1), (351, 1), (64, 1), (698, 2), (200, 1), (0, 1)]),
 ]
 
 
@@ -269,6 +276,9 @@ def test_attention_kernels(case_id, kind):
     H, K, hd, page, window, segs = ATT_CASES[case_id]
     dtype = torch.float32 if kind == "simt_f32" else torch.bfloat16
     case = _paged_case(case_id, H, K, hd, page, segs, dtype, window)
+    if case_id >= 11:
+        from xyntetik_runner_b200 import kernels
+        assert 2 <= kernels.attention_mma_splits(case["max_len"], window, len(segs) * K) <= 8        # what the case is for
     got = _run_attention(case, "simt" if kind.startswith("simt") else "mma", H, K, hd, page, window, dtype, tma=kind == "mma_tma")
     ref = case["ref"]
     # inputs are exact in the kernel's own dtype, so the error is that of the arithmetic: float32 sums,
@@ -444,6 +454,8 @@ def test_sampling_kernel_matches_the_plain_chain(V):
     logits[3, :] = logits[3, 0]                         # all equal: every cut is decided by ids
     logits[4, V // 2:] = logits[4, V // 2]              # a long tie in the tail
     logits[5, 1] = logits[5].max() + 5; logits[5, 2] = logits[5, 1]      # a tie at the top
+    logits[8, V - 1] = logits[8].max() + 5; logits[8, V // 3] = logits[8, V - 1]     # a greedy row: equal maxima far apart
+    logits[12, :] = -np.inf; logits[12, V - 2] = -1e30                   # a greedy row: one finite value near the end
     temp = [0.0, 0.7, 1.0, 1.5] * 6
     top_k = [0, 0, 5, 40, 0, 3, 0, 1] * 3
     top_p = [1.0, 0.9, 1.0, 0.5, 0.3, 1.0, 0.95, 1.0] * 3
@@ -466,7 +478,8 @@ def test_sampling_kernel_matches_the_plain_chain(V):
             dist = sample_chain(logits[r], draws[r], temp[r], distance_of=got[r], **kw)
             assert dist <= 2e-6, f"row {r}: kernel {got[r]}, plain {want}, draw {dist:.3e} outside the token's interval"
     # greedy rows are exact: first index among equal maxima
-    assert got[0] == int(np.argmax(logits[0])) and got[4 * 1] == int(np.argmax(logits[4]))
+    for r in range(0, rows, 4):
+        assert got[r] == int(np.argmax(logits[r])), f"greedy row {r}"
 
 
 def test_sampling_kernel_follows_the_distribution():

@@ -476,11 +476,26 @@ __device__ __forceinline__ bool att_mbar_wait(uint64_t* bar, uint32_t parity) {
     return false;
 }
 
-template <int HD, int STAGES>
+// CLUSTER: the spans of one (request, kv head) are the blocks of one thread-block cluster (grid.x = cluster size <=
+// 8) and combine their results among themselves: every block sends each block the slice of its accumulator that
+// block is to finish, and its rows' (maximum, sum) pairs, into that block's shared memory; after one cluster barrier
+// each block weighs and adds what it received, in ascending span order, and writes its slice of the output rows.
+// The partial results then never leave the SMs and no merge kernel follows.
+#define ATT_CLUSTER_MAX 8
+__device__ __forceinline__ uint32_t att_map_to_rank(const void* mine, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(att_smem_u32(mine)), "r"(rank));
+    return remote;
+}
+__device__ __forceinline__ void att_cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void att_cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+
+template <int HD, int STAGES, bool CLUSTER>
 __global__ void __launch_bounds__(ATT_THREADS)
 k_attention_keys_tma(const __grid_constant__ CUtensorMap cache_map, AttnMmaArgs a) {
     xr_pdl_launch();
     constexpr int LD = HD + 8;
+    constexpr int QUADS = HD / 4;
     constexpr int TILE_ELEMS = ATT_TILE * HD;                      // one K (or V) tile, swizzled sub-tiles of 64 columns
     extern __shared__ __align__(16) uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);     // TMA with the 128-byte swizzle wants 1 KB
@@ -489,16 +504,26 @@ k_attention_keys_tma(const __grid_constant__ CUtensorMap cache_map, AttnMmaArgs 
     __nv_bfloat16* qs = vbuf + STAGES * TILE_ELEMS;                // [16][LD]
     uint64_t* full = (uint64_t*)(qs + 16 * LD);
     volatile int* gave_up = (volatile int*)(full + STAGES);
+    // CLUSTER: what the other spans send.  Nothing else lives here: a span that is done early writes into the
+    // shared memory of one that is still at work.
+    float4* recv_acc = (float4*)(((uintptr_t)(gave_up + 1) + 15) & ~(uintptr_t)15);      // [spans][per] quadruples
+    float2* recv_ml = (float2*)(recv_acc + 16 * QUADS + ATT_CLUSTER_MAX);                // [spans][16] (maximum, sum)
     const int seg = blockIdx.z, kvh = blockIdx.y, span = blockIdx.x;
     const int L = a.seg_len[seg], rows_total = L * a.G;
-    if (rows_total > 16) return;
+    if (rows_total > 16) return;                                   // (the whole cluster: it shares the request)
     const int pos0 = a.seg_pos0[seg], tok_base = a.seg_start[seg];
     const int hi_all = pos0 + L - 1;
     const int lo_all = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
     const int SPAN = a.span;
     const int first_span = lo_all / SPAN;
     const int k_begin = (first_span + span) * SPAN;
-    if (k_begin > hi_all) return;
+    const int n_spans = hi_all / SPAN - first_span + 1;            // spans of this request that hold keys
+    if (CLUSTER) att_cluster_arrive();                             // "this block runs": waited for before anyone writes to it
+    if (k_begin > hi_all) {
+        // no keys for this span: nobody sends to it and it owns no output, but the cluster's barriers count it
+        if (CLUSTER) { att_cluster_wait(); att_cluster_arrive(); att_cluster_wait(); }
+        return;
+    }
     const int lo = max(lo_all, k_begin), hi = min(hi_all, k_begin + SPAN - 1);
     const int* bt = a.block_tables + (size_t)seg * a.max_pages;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -604,24 +629,110 @@ k_attention_keys_tma(const __grid_constant__ CUtensorMap cache_map, AttnMmaArgs 
         ml_s[(warp * 16 + rb) * 2] = m[1]; ml_s[(warp * 16 + rb) * 2 + 1] = l[1];
     }
     __syncthreads();
-    size_t item = ((size_t)seg * a.K + kvh) * a.max_splits + span;
-    float* pacc = a.part_acc + item * 16 * HD;
-    float* pml = a.part_ml + item * 16 * 2;
-    for (int i = threadIdx.x; i < rows_total * HD; i += ATT_THREADS) {
-        int r = i / HD, d = i % HD;
+    if (!CLUSTER) {
+        size_t item = ((size_t)seg * a.K + kvh) * a.max_splits + span;
+        float* pacc = a.part_acc + item * 16 * HD;
+        float* pml = a.part_ml + item * 16 * 2;
+        for (int i = threadIdx.x; i < rows_total * HD; i += ATT_THREADS) {
+            int r = i / HD, d = i % HD;
+            float mm = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < 4; w++) mm = fmaxf(mm, ml_s[(w * 16 + r) * 2]);
+            float off = mm == -INFINITY ? 0.f : mm;
+            float acc = 0.f, ll = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; w++) {
+                float f = expf(ml_s[(w * 16 + r) * 2] - off);
+                acc += acc_s[(w * 16 + r) * HD + d] * f;
+                ll += ml_s[(w * 16 + r) * 2 + 1] * f;
+            }
+            pacc[r * HD + d] = acc;
+            if (d == 0) { pml[r * 2] = mm; pml[r * 2 + 1] = ll; }
+        }
+        return;
+    }
+    // Quadruple q of the output rows (row q / QUADS, columns 4 (q % QUADS) ..) is finished by span q % n_spans, which
+    // keeps it at [sender][q / n_spans].
+    const int owned = rows_total * QUADS, per = (owned + n_spans - 1) / n_spans;
+    att_cluster_wait();                                           // every block of the cluster has begun
+    if (n_spans == 1) {
+        // nothing to exchange: the four warps' sums are the result
+        for (int q = threadIdx.x; q < owned; q += ATT_THREADS) {
+            const int r = q / QUADS, d = (q % QUADS) * 4;
+            float mm = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < 4; w++) mm = fmaxf(mm, ml_s[(w * 16 + r) * 2]);
+            const float off = mm == -INFINITY ? 0.f : mm;
+            float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+            float ll = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; w++) {
+                const float f = expf(ml_s[(w * 16 + r) * 2] - off);
+                const float4 v = *reinterpret_cast<const float4*>(acc_s + (w * 16 + r) * HD + d);
+                t.x += v.x * f; t.y += v.y * f; t.z += v.z * f; t.w += v.w * f;
+                ll += ml_s[(w * 16 + r) * 2 + 1] * f;
+            }
+            const float inv = 1.0f / ll;
+            __nv_bfloat16* dst = a.out + ((long long)(tok_base + r / a.G) * a.H + (kvh * a.G + r % a.G)) * HD + d;
+            __nv_bfloat162 lo2 = __floats2bfloat162_rn(t.x * inv, t.y * inv), hi2 = __floats2bfloat162_rn(t.z * inv, t.w * inv);
+            uint2 packed;
+            packed.x = *reinterpret_cast<uint32_t*>(&lo2);
+            packed.y = *reinterpret_cast<uint32_t*>(&hi2);
+            *reinterpret_cast<uint2*>(dst) = packed;
+        }
+        att_cluster_arrive();
+        att_cluster_wait();
+        return;
+    }
+    for (int q = threadIdx.x; q < owned; q += ATT_THREADS) {
+        const int r = q / QUADS, d = (q % QUADS) * 4;
         float mm = -INFINITY;
 #pragma unroll
         for (int w = 0; w < 4; w++) mm = fmaxf(mm, ml_s[(w * 16 + r) * 2]);
-        float off = mm == -INFINITY ? 0.f : mm;
-        float acc = 0.f, ll = 0.f;
+        const float off = mm == -INFINITY ? 0.f : mm;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        float ll = 0.f;
 #pragma unroll
         for (int w = 0; w < 4; w++) {
-            float f = expf(ml_s[(w * 16 + r) * 2] - off);
-            acc += acc_s[(w * 16 + r) * HD + d] * f;
+            const float f = expf(ml_s[(w * 16 + r) * 2] - off);
+            const float4 v = *reinterpret_cast<const float4*>(acc_s + (w * 16 + r) * HD + d);
+            acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
             ll += ml_s[(w * 16 + r) * 2 + 1] * f;
         }
-        pacc[r * HD + d] = acc;
-        if (d == 0) { pml[r * 2] = mm; pml[r * 2 + 1] = ll; }
+        uint32_t dst = att_map_to_rank(recv_acc + span * per + q / n_spans, (uint32_t)(q % n_spans));
+        asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "f"(acc.x), "f"(acc.y), "f"(acc.z), "f"(acc.w) : "memory");
+        if (d == 0) {
+            for (int o = 0; o < n_spans; o++) {
+                uint32_t dm = att_map_to_rank(recv_ml + span * 16 + r, (uint32_t)o);
+                asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(dm), "f"(mm), "f"(ll) : "memory");
+            }
+        }
+    }
+    att_cluster_arrive();
+    att_cluster_wait();
+    for (int j = threadIdx.x; j < per; j += ATT_THREADS) {
+        const int q = j * n_spans + span;
+        if (q >= owned) break;
+        const int r = q / QUADS, d = (q % QUADS) * 4;
+        float mm = -INFINITY;
+        for (int sp = 0; sp < n_spans; sp++) mm = fmaxf(mm, recv_ml[sp * 16 + r].x);
+        const float off = mm == -INFINITY ? 0.f : mm;
+        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+        float ll = 0.f;
+        for (int sp = 0; sp < n_spans; sp++) {
+            const float2 ml = recv_ml[sp * 16 + r];
+            const float wk = __expf(ml.x - off);
+            const float4 v = recv_acc[sp * per + j];
+            t.x += v.x * wk; t.y += v.y * wk; t.z += v.z * wk; t.w += v.w * wk;
+            ll += ml.y * wk;
+        }
+        const float inv = 1.0f / ll;
+        __nv_bfloat16* dst = a.out + ((long long)(tok_base + r / a.G) * a.H + (kvh * a.G + r % a.G)) * HD + d;
+        __nv_bfloat162 lo2 = __floats2bfloat162_rn(t.x * inv, t.y * inv), hi2 = __floats2bfloat162_rn(t.z * inv, t.w * inv);
+        uint2 packed;
+        packed.x = *reinterpret_cast<uint32_t*>(&lo2);
+        packed.y = *reinterpret_cast<uint32_t*>(&hi2);
+        *reinterpret_cast<uint2*>(dst) = packed;
     }
 }
 
@@ -828,7 +939,14 @@ static AttEncodeFn att_encode() {
     return fn;
 }
 
-// The bulk-copy keys kernel, when the shapes allow it.  Returns 1 if launched, 0 if not applicable, < 0 on error.
+static bool att_cluster_merge_enabled() {
+    static int on = -1;
+    if (on < 0) { const char* e = getenv("XRB200_NO_CLUSTER_MERGE"); on = (e && e[0] == '1') ? 0 : 1; }
+    return on == 1;
+}
+
+// The bulk-copy keys kernel, when the shapes allow it.  Returns 1 if launched (2: and the spans are combined
+// already), 0 if not applicable, < 0 on error.
 template <int HD>
 static int launch_keys_tma(const AttnMmaArgs& a, const void* cache_base, long long n_pages, int n_seg, cudaStream_t stream) {
   if constexpr (HD != 64 && HD != 128) {
@@ -850,24 +968,49 @@ static int launch_keys_tma(const AttnMmaArgs& a, const void* cache_base, long lo
         return -3;
     constexpr int LD = HD + 8;
     constexpr int STAGE = 2 * ATT_TILE * HD * 2, REST = 16 * LD * 2 + 64 + 1024;
+    constexpr int RECV = (16 * (HD / 4) + ATT_CLUSTER_MAX) * 16 + ATT_CLUSTER_MAX * 16 * 8 + 16;
     constexpr int S2 = 2 * STAGE + REST, S3 = 3 * STAGE + REST, S4 = 4 * STAGE + REST;
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(k_attention_keys_tma<HD, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, S2) != cudaSuccess ||
-            cudaFuncSetAttribute(k_attention_keys_tma<HD, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, S3) != cudaSuccess ||
-            cudaFuncSetAttribute(k_attention_keys_tma<HD, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, S4) != cudaSuccess)
+        if (cudaFuncSetAttribute(k_attention_keys_tma<HD, 2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, S2) != cudaSuccess ||
+            cudaFuncSetAttribute(k_attention_keys_tma<HD, 3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, S3) != cudaSuccess ||
+            cudaFuncSetAttribute(k_attention_keys_tma<HD, 4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, S4) != cudaSuccess ||
+            cudaFuncSetAttribute(k_attention_keys_tma<HD, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, S2 + RECV) != cudaSuccess ||
+            cudaFuncSetAttribute(k_attention_keys_tma<HD, 3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, S3 + RECV) != cudaSuccess ||
+            cudaFuncSetAttribute(k_attention_keys_tma<HD, 4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, S4 + RECV) != cudaSuccess)
             return XR_ERR_LAUNCH;
         configured = true;
     }
     // the fewer CTAs there are, the deeper each one's ring of tiles, so that as many bytes stay in flight per SM
     dim3 grid(a.max_splits, a.K, n_seg);
     long long ctas = (long long)a.max_splits * a.K * n_seg;
-    if (ctas <= 148)
-        xr_launch((k_attention_keys_tma<HD, 4>), dim3(grid), dim3(ATT_THREADS), S4, stream, map, a);
-    else if (ctas <= 2 * 148)
-        xr_launch((k_attention_keys_tma<HD, 3>), dim3(grid), dim3(ATT_THREADS), S3, stream, map, a);
+    const int depth = ctas <= 148 ? 4 : (ctas <= 2 * 148 ? 3 : 2);
+    // (a single span sends nothing and needs no room to receive; otherwise the room must not cost a resident CTA)
+    const int ring = depth == 4 ? S4 : (depth == 3 ? S3 : S2), recv = a.max_splits == 1 ? 0 : RECV;
+    const int fit = (227 * 1024) / (ring + 1024), fit_recv = (227 * 1024) / (ring + recv + 1024);
+    if (a.max_splits <= ATT_CLUSTER_MAX && att_cluster_merge_enabled() && (fit_recv == fit || ctas <= (long long)fit_recv * 148)) {
+        // the spans of a request as one cluster, which also combines them (returns 2: no merge kernel is to follow)
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid; cfg.blockDim = dim3(ATT_THREADS); cfg.stream = stream;
+        cfg.dynamicSmemBytes = ring + recv;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = a.max_splits; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = xr_pdl_enabled() ? 2 : 1;
+        if (depth == 4) cudaLaunchKernelEx(&cfg, k_attention_keys_tma<HD, 4, true>, map, a);
+        else if (depth == 3) cudaLaunchKernelEx(&cfg, k_attention_keys_tma<HD, 3, true>, map, a);
+        else cudaLaunchKernelEx(&cfg, k_attention_keys_tma<HD, 2, true>, map, a);
+        return xr_launch_status() == XR_OK ? 2 : XR_ERR_LAUNCH;
+    }
+    if (depth == 4)
+        xr_launch((k_attention_keys_tma<HD, 4, false>), dim3(grid), dim3(ATT_THREADS), S4, stream, map, a);
+    else if (depth == 3)
+        xr_launch((k_attention_keys_tma<HD, 3, false>), dim3(grid), dim3(ATT_THREADS), S3, stream, map, a);
     else
-        xr_launch((k_attention_keys_tma<HD, 2>), dim3(grid), dim3(ATT_THREADS), S2, stream, map, a);
+        xr_launch((k_attention_keys_tma<HD, 2, false>), dim3(grid), dim3(ATT_THREADS), S2, stream, map, a);
     return xr_launch_status() == XR_OK ? 1 : XR_ERR_LAUNCH;
   }
 }
@@ -901,6 +1044,7 @@ static int launch_attention(const AttnMmaArgs& a, int n_seg, int max_seg_len, in
         int tma = launch_keys_tma<HD>(a, cache_base, n_pages, n_seg, stream);
         if (tma < 0) return tma;
         // few CTAs (small batch): deeper stages; many: more CTAs per SM.  The arithmetic is the same.
+        if (tma == 2) return XR_OK;                    // the spans were combined inside the clusters
         if (tma == 1) {
         } else if ((long long)a.max_splits * a.K * n_seg <= 2 * 148)
             xr_launch((k_attention_keys<HD, 4>), dim3(a.max_splits, a.K, n_seg), dim3(ATT_THREADS), SMEM_KEYS4, stream, a);

@@ -95,6 +95,8 @@ __global__ void __launch_bounds__(256)
 k_finish_add_rmsnorm_cluster(const float* __restrict__ partial, int splits, int n, const float* __restrict__ bias,
                              float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out, int d, int slice, float eps) {
     xr_pdl_launch();
+    // "this block runs": its neighbours wait for that before they write into its shared memory
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     __shared__ float scratch[33];
     __shared__ float slice_ss[FIN_CLUSTER];      // every block's sum of squares, written here by that block
     const int t = blockIdx.x / FIN_CLUSTER;
@@ -154,6 +156,7 @@ k_finish_add_rmsnorm_cluster(const float* __restrict__ partial, int splits, int 
     ss = xr_block_sum(ss, scratch);
     // each block hands its sum to all eight (itself included); after the one barrier nobody touches a neighbour's
     // shared memory again, so blocks may leave as they finish
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");      // (long since complete: all eight began together)
     if (threadIdx.x < FIN_CLUSTER) fin_cluster_write(&slice_ss[rank], (uint32_t)threadIdx.x, ss);
     fin_cluster_sync();
     float total = 0.f;

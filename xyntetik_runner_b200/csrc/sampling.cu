@@ -110,19 +110,49 @@ __device__ int nth_equal_id(int V, const float* vals, unsigned thr, long long n,
 __global__ void __launch_bounds__(SMP_THREADS)
 k_sample(SampleArgs a, float* scratch /* [rows, V] scaled values, or null when nothing needs them */) {
     xr_pdl_launch();
-    xr_pdl_wait();
     __shared__ double sh[40 + SMP_THREADS];
     __shared__ float sh_f[33];
     __shared__ int sh_i[33];
     int row = blockIdx.x, tid = threadIdx.x;
     const float* lg = a.logits + (size_t)row * a.ld;
+    // (the rows' parameters are written before the step's kernels are queued: they may be read before the wait)
     float temp = a.temp[row];
     int V = a.V;
+    xr_pdl_wait();
 
     if (temp <= 0.f) {
-        // argmax, first index on ties (src/sample.c:169-172)
+        // argmax, first index on ties (src/sample.c:169-172).  A row is half a megabyte that one block reads alone:
+        // eight 16-byte loads a thread are issued as one run, so the row takes a few trips to L2, not dozens.
         float best = -INFINITY; int bi = 0x7fffffff;
-        for (int i = tid; i < V; i += SMP_THREADS) {
+        int done = 0;
+        if ((((uintptr_t)lg) & 15) == 0) {
+            const float4* lg4 = reinterpret_cast<const float4*>(lg);
+            const int quads = V >> 2;
+            for (int q0 = 0; q0 < quads; q0 += 8 * SMP_THREADS) {
+                float4 v[8];
+#pragma unroll
+                for (int k = 0; k < 8; k++) {
+                    int q = q0 + k * SMP_THREADS + tid;
+                    v[k] = xr_ld_now4(lg4 + (q < quads ? q : quads - 1));
+                }
+#pragma unroll
+                for (int k = 0; k < 8; k++) xr_ld_fence(v[k]);
+#pragma unroll
+                for (int k = 0; k < 8; k++) {
+                    int q = q0 + k * SMP_THREADS + tid;
+                    if (q < quads) {
+                        // ascending indices within the thread, so `>` alone keeps the first of equal values
+                        int i = q << 2;
+                        if (v[k].x > best) { best = v[k].x; bi = i; }
+                        if (v[k].y > best) { best = v[k].y; bi = i + 1; }
+                        if (v[k].z > best) { best = v[k].z; bi = i + 2; }
+                        if (v[k].w > best) { best = v[k].w; bi = i + 3; }
+                    }
+                }
+            }
+            done = quads << 2;
+        }
+        for (int i = done + tid; i < V; i += SMP_THREADS) {
             float x = lg[i];
             if (x > best || (x == best && i < bi)) { best = x; bi = i; }
         }
