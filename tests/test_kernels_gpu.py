@@ -434,7 +434,7 @@ def test_attention_tc(case_id):
 # ---------------------------------------------------------------------------------------------
 # the sampling kernel against the plain chain
 # ---------------------------------------------------------------------------------------------
-def _sample_rows(logits, temp, top_k, top_p, min_p, pen, draws, recent=None):
+def _sample_rows(logits, temp, top_k, top_p, min_p, pen, draws, recent=None, one_block=False):
     from xyntetik_runner_b200 import kernels
     rows, V = logits.shape
     f = lambda a: torch.tensor(a, dtype=torch.float32, device=DEV)
@@ -442,12 +442,15 @@ def _sample_rows(logits, temp, top_k, top_p, min_p, pen, draws, recent=None):
     scratch = torch.empty(rows * V, dtype=torch.float32, device=DEV)
     rec = None if recent is None else torch.tensor(recent, dtype=torch.int32, device=DEV)
     kernels.sample(torch.from_numpy(logits).to(DEV), f(temp), torch.tensor(top_k, dtype=torch.int32, device=DEV), f(top_p), f(min_p),
-                   f(pen), f(draws), rec, scratch, out)
+                   f(pen), f(draws), rec, scratch, out, one_block=one_block)
     return out.cpu().tolist()
 
 
-@pytest.mark.parametrize("V", [17, 387, 5000, 128256])
-def test_sampling_kernel_matches_the_plain_chain(V):
+@pytest.mark.parametrize("V,one_block", [(17, False), (387, False), (1027, False), (5000, False), (5000, True), (16384 + 3, False),
+                                         (128256, False), (128256, True), (131072, False), (131073, False)])
+def test_sampling_kernel_matches_the_plain_chain(V, one_block):
+    """Rows of more than 1,024 values go to the cluster kernel (up to 131,072 values), others and `one_block` to the
+    one-block kernel; both against the plain chain."""
     from plain_llama import sample_chain
     rng = np.random.RandomState(V)
     rows = 24
@@ -470,7 +473,7 @@ def test_sampling_kernel_matches_the_plain_chain(V):
         recent[r, :k] = rng.randint(0, V, size=k)
         if k > 3:
             recent[r, 1] = recent[r, 0]                 # a token that occurs twice is penalised twice
-    got = _sample_rows(logits, temp, top_k, top_p, min_p, pen, draws, recent)
+    got = _sample_rows(logits, temp, top_k, top_p, min_p, pen, draws, recent, one_block=one_block)
     for r in range(rows):
         kw = dict(top_k=top_k[r], top_p=top_p[r], min_p=min_p[r], repeat_penalty=pen[r], recent=[t for t in recent[r] if t >= 0])
         want = sample_chain(logits[r], draws[r], temp[r], **kw)

@@ -12,8 +12,9 @@
 //      in [0, 1) that the host makes from the request's own xorshift64 state, src/sample.c:13-20).
 // The reference sorts; this kernel never does.  Every cut above is a prefix of the same order, so it
 // is described by a threshold in an order-preserving integer image of v (plus, among exact ties, a
-// count of ids).  Thresholds are found by descending over the 32 key bits, each step one block-wide
-// sum in a fixed order, which makes the result deterministic.
+// count of ids).  Thresholds are found by descending over the 32 key bits, two bits a pass (three
+// candidate thresholds, each with its own block-wide sum in a fixed order, which makes the result
+// deterministic); a pass reads the row in runs of eight 16-byte loads per thread.
 #include "common.cuh"
 #include <math.h>
 
@@ -74,6 +75,75 @@ __device__ __forceinline__ long long blk_sum_ll(long long v, double* sh) {
     return s[32];
 }
 
+// The same sums for three values at once (one pass of a descent weighs three candidate thresholds).
+__device__ __forceinline__ void blk_sum3_d(double (&v)[3], double* sh) {
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int j = 0; j < 3; j++)
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v[j] += __shfl_xor_sync(0xffffffffu, v[j], o);
+    __syncthreads();
+    if (lane == 0) { sh[warp * 3] = v[0]; sh[warp * 3 + 1] = v[1]; sh[warp * 3 + 2] = v[2]; }
+    __syncthreads();
+    if (warp < 3) {
+        double t = lane < (SMP_THREADS / 32) ? sh[lane * 3 + warp] : 0.0;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        if (lane == 0) sh[100 + warp] = t;
+    }
+    __syncthreads();
+    v[0] = sh[100]; v[1] = sh[101]; v[2] = sh[102];
+}
+__device__ __forceinline__ void blk_sum3_ll(long long (&v)[3], double* sh) {
+    long long* s = (long long*)sh;
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int j = 0; j < 3; j++)
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v[j] += __shfl_xor_sync(0xffffffffu, v[j], o);
+    __syncthreads();
+    if (lane == 0) { s[warp * 3] = v[0]; s[warp * 3 + 1] = v[1]; s[warp * 3 + 2] = v[2]; }
+    __syncthreads();
+    if (warp < 3) {
+        long long t = lane < (SMP_THREADS / 32) ? s[lane * 3 + warp] : 0;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        if (lane == 0) s[100 + warp] = t;
+    }
+    __syncthreads();
+    v[0] = s[100]; v[1] = s[101]; v[2] = s[102];
+}
+
+// f(i, vals[i]) for every i of the row.  A row is half a megabyte that one block reads alone, many times: eight
+// 16-byte loads a thread are issued as one run, so a pass takes a few trips to L2 instead of dozens.  (A row that
+// does not start on a 16-byte boundary -- an odd vocabulary -- is read element by element.)
+template <typename F>
+__device__ __forceinline__ void smp_for_each(const float* vals, int V, F f) {
+    const int tid = threadIdx.x;
+    int done = 0;
+    if ((((uintptr_t)vals) & 15) == 0) {
+        const float4* v4 = reinterpret_cast<const float4*>(vals);
+        const int quads = V >> 2;
+        for (int q0 = 0; q0 < quads; q0 += 8 * SMP_THREADS) {
+            float4 v[8];
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                int q = q0 + k * SMP_THREADS + tid;
+                v[k] = xr_ld_now4(v4 + (q < quads ? q : quads - 1));
+            }
+#pragma unroll
+            for (int k = 0; k < 8; k++) xr_ld_fence(v[k]);
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                int q = q0 + k * SMP_THREADS + tid;
+                if (q < quads) { f(4 * q, v[k].x); f(4 * q + 1, v[k].y); f(4 * q + 2, v[k].z); f(4 * q + 3, v[k].w); }
+            }
+        }
+        done = quads << 2;
+    }
+    for (int i = done + tid; i < V; i += SMP_THREADS) f(i, vals[i]);
+}
+
 // The set of surviving candidates: key > thr, or key == thr and fewer than `n_eq` equal keys have
 // a smaller id.  n_eq < 0 keeps every equal key.
 struct Cut { unsigned thr; long long n_eq; };
@@ -107,6 +177,61 @@ __device__ int nth_equal_id(int V, const float* vals, unsigned thr, long long n,
     return found;
 }
 
+// argmax of a row, first index on ties (src/sample.c:169-172), by one block.  A row is half a megabyte that the block
+// reads alone: eight 16-byte loads a thread are issued as one run, so the row takes a few trips to L2, not dozens.
+__device__ __forceinline__ void smp_argmax(const float* lg, int V, int* out, float* sh_f, int* sh_i) {
+    const int tid = threadIdx.x;
+    float best = -INFINITY; int bi = 0x7fffffff;
+    int done = 0;
+    if ((((uintptr_t)lg) & 15) == 0) {
+        const float4* lg4 = reinterpret_cast<const float4*>(lg);
+        const int quads = V >> 2;
+        for (int q0 = 0; q0 < quads; q0 += 8 * SMP_THREADS) {
+            float4 v[8];
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                int q = q0 + k * SMP_THREADS + tid;
+                v[k] = xr_ld_now4(lg4 + (q < quads ? q : quads - 1));
+            }
+#pragma unroll
+            for (int k = 0; k < 8; k++) xr_ld_fence(v[k]);
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                int q = q0 + k * SMP_THREADS + tid;
+                if (q < quads) {
+                    // ascending indices within the thread, so `>` alone keeps the first of equal values
+                    int i = q << 2;
+                    if (v[k].x > best) { best = v[k].x; bi = i; }
+                    if (v[k].y > best) { best = v[k].y; bi = i + 1; }
+                    if (v[k].z > best) { best = v[k].z; bi = i + 2; }
+                    if (v[k].w > best) { best = v[k].w; bi = i + 3; }
+                }
+            }
+        }
+        done = quads << 2;
+    }
+    for (int i = done + tid; i < V; i += SMP_THREADS) {
+        float x = lg[i];
+        if (x > best || (x == best && i < bi)) { best = x; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ob = __shfl_xor_sync(0xffffffffu, best, o); int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    if ((tid & 31) == 0) { sh_f[tid >> 5] = best; sh_i[tid >> 5] = bi; }
+    __syncthreads();
+    if (tid < 32) {
+        best = sh_f[tid]; bi = sh_i[tid];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            float ob = __shfl_xor_sync(0xffffffffu, best, o); int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+        }
+        if (tid == 0) *out = bi == 0x7fffffff ? 0 : bi;
+    }
+}
+
 __global__ void __launch_bounds__(SMP_THREADS)
 k_sample(SampleArgs a, float* scratch /* [rows, V] scaled values, or null when nothing needs them */) {
     xr_pdl_launch();
@@ -120,66 +245,13 @@ k_sample(SampleArgs a, float* scratch /* [rows, V] scaled values, or null when n
     int V = a.V;
     xr_pdl_wait();
 
-    if (temp <= 0.f) {
-        // argmax, first index on ties (src/sample.c:169-172).  A row is half a megabyte that one block reads alone:
-        // eight 16-byte loads a thread are issued as one run, so the row takes a few trips to L2, not dozens.
-        float best = -INFINITY; int bi = 0x7fffffff;
-        int done = 0;
-        if ((((uintptr_t)lg) & 15) == 0) {
-            const float4* lg4 = reinterpret_cast<const float4*>(lg);
-            const int quads = V >> 2;
-            for (int q0 = 0; q0 < quads; q0 += 8 * SMP_THREADS) {
-                float4 v[8];
-#pragma unroll
-                for (int k = 0; k < 8; k++) {
-                    int q = q0 + k * SMP_THREADS + tid;
-                    v[k] = xr_ld_now4(lg4 + (q < quads ? q : quads - 1));
-                }
-#pragma unroll
-                for (int k = 0; k < 8; k++) xr_ld_fence(v[k]);
-#pragma unroll
-                for (int k = 0; k < 8; k++) {
-                    int q = q0 + k * SMP_THREADS + tid;
-                    if (q < quads) {
-                        // ascending indices within the thread, so `>` alone keeps the first of equal values
-                        int i = q << 2;
-                        if (v[k].x > best) { best = v[k].x; bi = i; }
-                        if (v[k].y > best) { best = v[k].y; bi = i + 1; }
-                        if (v[k].z > best) { best = v[k].z; bi = i + 2; }
-                        if (v[k].w > best) { best = v[k].w; bi = i + 3; }
-                    }
-                }
-            }
-            done = quads << 2;
-        }
-        for (int i = done + tid; i < V; i += SMP_THREADS) {
-            float x = lg[i];
-            if (x > best || (x == best && i < bi)) { best = x; bi = i; }
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            float ob = __shfl_xor_sync(0xffffffffu, best, o); int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
-        }
-        if ((tid & 31) == 0) { sh_f[tid >> 5] = best; sh_i[tid >> 5] = bi; }
-        __syncthreads();
-        if (tid < 32) {
-            best = sh_f[tid]; bi = sh_i[tid];
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                float ob = __shfl_xor_sync(0xffffffffu, best, o); int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-                if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
-            }
-            if (tid == 0) a.out[row] = bi == 0x7fffffff ? 0 : bi;
-        }
-        return;
-    }
+    if (temp <= 0.f) { smp_argmax(lg, V, a.out + row, sh_f, sh_i); return; }
 
     // Stage the row: copy, penalise the recent tokens (once per occurrence in the window, as the
     // reference's loop does, src/sample.c:148-166), then scale by 1/temp.  Later passes read the
     // staged values back, so every pass sees the same numbers.
     float* vals = scratch + (size_t)row * V;
-    for (int i = tid; i < V; i += SMP_THREADS) vals[i] = lg[i];
+    smp_for_each(lg, V, [&](int i, float v) { vals[i] = v; });
     __syncthreads();
     float pen = a.penalty[row];
     if (a.recent != nullptr && pen != 1.0f && tid < SMP_RECENT) {
@@ -197,11 +269,11 @@ k_sample(SampleArgs a, float* scratch /* [rows, V] scaled values, or null when n
     }
     __syncthreads();
     float mx = -INFINITY;
-    for (int i = tid; i < V; i += SMP_THREADS) {
-        float v = vals[i] / temp;
+    smp_for_each(vals, V, [&](int i, float x) {
+        float v = x / temp;
         vals[i] = v;
         mx = fmaxf(mx, v);
-    }
+    });
     mx = xr_warp_max(mx);
     if ((tid & 31) == 0) sh_f[tid >> 5] = mx;
     __syncthreads();
@@ -215,15 +287,16 @@ k_sample(SampleArgs a, float* scratch /* [rows, V] scaled values, or null when n
     // ---- top-k: the k-th largest key by descending over the key bits with counts ----
     if (top_k > 0 && top_k < V) {
         unsigned thr = 0;
-        for (int bit = 31; bit >= 0; bit--) {
-            unsigned cand = thr | (1u << bit);
-            long long c = 0;
-            for (int i = tid; i < V; i += SMP_THREADS) c += (xr_key(vals[i]) >= cand);
-            c = blk_sum_ll(c, sh);
-            if (c >= top_k) thr = cand;       // at least k keys are >= cand: the k-th largest is >= cand
+        for (int shift = 30; shift >= 0; shift -= 2) {
+            const unsigned c1 = thr | (1u << shift), c2 = thr | (2u << shift), c3 = thr | (3u << shift);
+            long long c[3] = {0, 0, 0};
+            smp_for_each(vals, V, [&](int, float v) { unsigned k = xr_key(v); c[0] += (k >= c1); c[1] += (k >= c2); c[2] += (k >= c3); });
+            blk_sum3_ll(c, sh);
+            // at least k keys are >= a candidate: the k-th largest is >= it
+            thr = c[2] >= top_k ? c3 : (c[1] >= top_k ? c2 : (c[0] >= top_k ? c1 : thr));
         }
         long long gt = 0;
-        for (int i = tid; i < V; i += SMP_THREADS) gt += (xr_key(vals[i]) > thr);
+        smp_for_each(vals, V, [&](int, float v) { gt += (xr_key(v) > thr); });
         gt = blk_sum_ll(gt, sh);
         cut.thr = thr; cut.n_eq = (long long)top_k - gt;      // that many of the equal keys, by id
     }
@@ -231,7 +304,7 @@ k_sample(SampleArgs a, float* scratch /* [rows, V] scaled values, or null when n
     int eq_id_end = V;
     if (cut.n_eq >= 0) {
         long long eq = 0;
-        for (int i = tid; i < V; i += SMP_THREADS) eq += (xr_key(vals[i]) == cut.thr);
+        smp_for_each(vals, V, [&](int, float v) { eq += (xr_key(v) == cut.thr); });
         eq = blk_sum_ll(eq, sh);
         if (cut.n_eq < eq) eq_id_end = nth_equal_id(V, vals, cut.thr, cut.n_eq, sh);
     }
@@ -239,7 +312,7 @@ k_sample(SampleArgs a, float* scratch /* [rows, V] scaled values, or null when n
 
     // ---- mass of the survivors ----
     double Z = 0.0;
-    for (int i = tid; i < V; i += SMP_THREADS) { unsigned k = xr_key(vals[i]); if (SURVIVES(i, k)) Z += (double)expf(vals[i] - mx); }
+    smp_for_each(vals, V, [&](int i, float v) { unsigned k = xr_key(v); if (SURVIVES(i, k)) Z += (double)expf(v - mx); });
     Z = blk_sum_d(Z, sh);
 
     // ---- top-p: shortest prefix with cumulative probability >= top_p ----
@@ -248,18 +321,24 @@ k_sample(SampleArgs a, float* scratch /* [rows, V] scaled values, or null when n
         double target = (double)top_p * Z;
         // largest key x with mass{key >= x} >= target
         unsigned thr = 0;
-        for (int bit = 31; bit >= 0; bit--) {
-            unsigned cand = thr | (1u << bit);
-            double ms = 0.0;
-            for (int i = tid; i < V; i += SMP_THREADS) { unsigned k = xr_key(vals[i]); if (k >= cand && SURVIVES(i, k)) ms += (double)expf(vals[i] - mx); }
-            ms = blk_sum_d(ms, sh);
-            if (ms >= target) thr = cand;
+        for (int shift = 30; shift >= 0; shift -= 2) {
+            const unsigned c1 = thr | (1u << shift), c2 = thr | (2u << shift), c3 = thr | (3u << shift);
+            double ms[3] = {0.0, 0.0, 0.0};
+            smp_for_each(vals, V, [&](int i, float v) {
+                unsigned k = xr_key(v);
+                if (k >= c1 && SURVIVES(i, k)) {
+                    double e = (double)expf(v - mx);
+                    ms[0] += e; ms[1] += k >= c2 ? e : 0.0; ms[2] += k >= c3 ? e : 0.0;
+                }
+            });
+            blk_sum3_d(ms, sh);
+            thr = ms[2] >= target ? c3 : (ms[1] >= target ? c2 : (ms[0] >= target ? c1 : thr));
         }
         {
             // among equal keys at thr, keep only as many (by id) as the prefix needs; if thr is also where top-k cut,
             // no more than top-k left there
             double gtm = 0.0; long long eqn = 0;
-            for (int i = tid; i < V; i += SMP_THREADS) { unsigned k = xr_key(vals[i]); if (k > thr) gtm += (double)expf(vals[i] - mx); eqn += (k == thr); }
+            smp_for_each(vals, V, [&](int, float v) { unsigned k = xr_key(v); if (k > thr) gtm += (double)expf(v - mx); eqn += (k == thr); });
             gtm = blk_sum_d(gtm, sh);
             eqn = blk_sum_ll(eqn, sh);
             long long avail = (thr == cut.thr && cut.n_eq >= 0 && cut.n_eq < eqn) ? cut.n_eq : eqn;
@@ -276,7 +355,7 @@ k_sample(SampleArgs a, float* scratch /* [rows, V] scaled values, or null when n
             eq_id_end = need < eqn ? nth_equal_id(V, vals, thr, need, sh) : V;
         }
         Z = 0.0;
-        for (int i = tid; i < V; i += SMP_THREADS) { unsigned k = xr_key(vals[i]); if (SURVIVES(i, k)) Z += (double)expf(vals[i] - mx); }
+        smp_for_each(vals, V, [&](int i, float v) { unsigned k = xr_key(v); if (SURVIVES(i, k)) Z += (double)expf(v - mx); });
         Z = blk_sum_d(Z, sh);
     }
 
@@ -285,10 +364,10 @@ k_sample(SampleArgs a, float* scratch /* [rows, V] scaled values, or null when n
     float e_floor = min_p > 0.f ? min_p : 0.f;
     if (e_floor > 0.f) {
         Z = 0.0;
-        for (int i = tid; i < V; i += SMP_THREADS) {
-            unsigned k = xr_key(vals[i]); float e = expf(vals[i] - mx);
+        smp_for_each(vals, V, [&](int i, float v) {
+            unsigned k = xr_key(v); float e = expf(v - mx);
             if (SURVIVES(i, k) && e >= e_floor) Z += (double)e;
-        }
+        });
         Z = blk_sum_d(Z, sh);
     }
 #define FINAL(i, k, e) (SURVIVES(i, k) && (e) >= e_floor)
@@ -296,22 +375,27 @@ k_sample(SampleArgs a, float* scratch /* [rows, V] scaled values, or null when n
     // ---- the pick: first candidate whose cumulative mass exceeds r * Z ----
     double want = (double)a.draw[row] * Z;
     unsigned thr = 0; bool any = false;
-    for (int bit = 31; bit >= 0; bit--) {
-        unsigned cand = thr | (1u << bit);
-        double ms = 0.0;
-        for (int i = tid; i < V; i += SMP_THREADS) {
-            unsigned k = xr_key(vals[i]); float e = expf(vals[i] - mx);
-            if (k >= cand && FINAL(i, k, e)) ms += (double)e;
-        }
-        ms = blk_sum_d(ms, sh);
-        if (ms > want) { thr = cand; any = true; }
+    for (int shift = 30; shift >= 0; shift -= 2) {
+        const unsigned c1 = thr | (1u << shift), c2 = thr | (2u << shift), c3 = thr | (3u << shift);
+        double ms[3] = {0.0, 0.0, 0.0};
+        smp_for_each(vals, V, [&](int i, float v) {
+            unsigned k = xr_key(v);
+            if (k >= c1) {
+                float e = expf(v - mx);
+                if (FINAL(i, k, e)) { ms[0] += (double)e; ms[1] += k >= c2 ? (double)e : 0.0; ms[2] += k >= c3 ? (double)e : 0.0; }
+            }
+        });
+        blk_sum3_d(ms, sh);
+        if (ms[2] > want) { thr = c3; any = true; }
+        else if (ms[1] > want) { thr = c2; any = true; }
+        else if (ms[0] > want) { thr = c1; any = true; }
     }
     // candidates with key == thr that are in the final set, and the mass above them
     double gtm = 0.0; long long eqn = 0;
-    for (int i = tid; i < V; i += SMP_THREADS) {
-        unsigned k = xr_key(vals[i]); float e = expf(vals[i] - mx);
+    smp_for_each(vals, V, [&](int i, float v) {
+        unsigned k = xr_key(v); float e = expf(v - mx);
         if (FINAL(i, k, e)) { if (k > thr) gtm += (double)e; else if (k == thr) eqn++; }
-    }
+    });
     gtm = blk_sum_d(gtm, sh);
     eqn = blk_sum_ll(eqn, sh);
     int pick;
@@ -345,10 +429,399 @@ k_sample(SampleArgs a, float* scratch /* [rows, V] scaled values, or null when n
     if (tid == 0) a.out[row] = pick;
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same chain with a row spread over a cluster of SMP_CL blocks.  One block re-reads its row from L2 for
+// every pass of a descent (some sixty passes of half a megabyte at what one SM can load); here every thread keeps
+// SMP_PER consecutive values of the row in registers, a pass is arithmetic on those, a block-wide sum, and one
+// exchange of the blocks' sums through distributed shared memory.  All blocks of a cluster add the same numbers
+// in the same order (blocks in rank order), so they take the same decisions, and whatever guards an exchange is
+// a function of such sums and of the row's parameters only: the blocks of a cluster always meet at the same
+// barriers.  Vocabularies above SMP_CL * SMP_THREADS * SMP_PER keep the one-block kernel.
+// ---------------------------------------------------------------------------------------------
+#define SMP_CL 8
+#define SMP_PER 16
+
+struct SmpCluster {
+    unsigned long long (*slots)[SMP_CL][3];     // shared memory [2][SMP_CL][3]: what each block sent, by exchange parity
+    double* sh;                                  // the block sums' scratch
+    int phase, rank;
+};
+
+// Every thread of the block holds the same three words; afterwards smp_cl_get(c, r, j) is word j of block r.
+// Two sets of slots alternate: a block can be one exchange ahead of another, never two (the barrier), so what it
+// writes is never what the other still reads.
+__device__ __forceinline__ void smp_cl_exchange(SmpCluster& c, unsigned long long w0, unsigned long long w1, unsigned long long w2) {
+    if (threadIdx.x < SMP_CL) {
+        uint32_t local = (uint32_t)__cvta_generic_to_shared(&c.slots[c.phase][c.rank][0]), remote;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"((uint32_t)threadIdx.x));
+        asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(remote), "l"(w0) : "memory");
+        asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(remote + 8), "l"(w1) : "memory");
+        asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(remote + 16), "l"(w2) : "memory");
+    }
+    __syncwarp();
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    c.phase ^= 1;
+}
+__device__ __forceinline__ unsigned long long smp_cl_get(const SmpCluster& c, int r, int j) { return c.slots[c.phase ^ 1][r][j]; }
+
+__device__ __forceinline__ void smp_cl_sum3_ll(SmpCluster& c, long long (&v)[3]) {
+    blk_sum3_ll(v, c.sh);
+    smp_cl_exchange(c, (unsigned long long)v[0], (unsigned long long)v[1], (unsigned long long)v[2]);
+#pragma unroll
+    for (int j = 0; j < 3; j++) {
+        long long t = 0;
+        for (int r = 0; r < SMP_CL; r++) t += (long long)smp_cl_get(c, r, j);
+        v[j] = t;
+    }
+}
+__device__ __forceinline__ void smp_cl_sum3_d(SmpCluster& c, double (&v)[3]) {
+    blk_sum3_d(v, c.sh);
+    smp_cl_exchange(c, (unsigned long long)__double_as_longlong(v[0]), (unsigned long long)__double_as_longlong(v[1]),
+                    (unsigned long long)__double_as_longlong(v[2]));
+#pragma unroll
+    for (int j = 0; j < 3; j++) {
+        double t = 0.0;
+        for (int r = 0; r < SMP_CL; r++) t += __longlong_as_double((long long)smp_cl_get(c, r, j));
+        v[j] = t;
+    }
+}
+__device__ __forceinline__ double smp_cl_sum_d(SmpCluster& c, double x) { double v[3] = {x, 0.0, 0.0}; smp_cl_sum3_d(c, v); return v[0]; }
+__device__ __forceinline__ long long smp_cl_sum_ll(SmpCluster& c, long long x) { long long v[3] = {x, 0, 0}; smp_cl_sum3_ll(c, v); return v[0]; }
+
+// One exchange for a sum of doubles and a count.
+__device__ __forceinline__ void smp_cl_sum_d_ll(SmpCluster& c, double& d, long long& n) {
+    d = blk_sum_d(d, c.sh);
+    n = blk_sum_ll(n, c.sh);
+    smp_cl_exchange(c, (unsigned long long)__double_as_longlong(d), (unsigned long long)n, 0ull);
+    double td = 0.0; long long tn = 0;
+    for (int r = 0; r < SMP_CL; r++) { td += __longlong_as_double((long long)smp_cl_get(c, r, 0)); tn += (long long)smp_cl_get(c, r, 1); }
+    d = td; n = tn;
+}
+
+// id such that exactly `n` candidates with key == thr have an id below it.  A thread's ids are consecutive and
+// threads, then blocks, follow one another in id order, so a prefix over (block, thread) is a prefix over ids.
+template <int PER>
+__device__ int smp_cl_nth_equal_id(SmpCluster& c, int V, const float (&v)[PER], int base, int nvalid, unsigned thr, long long n) {
+    long long mine = 0;
+#pragma unroll
+    for (int j = 0; j < PER; j++) mine += (j < nvalid && xr_key(v[j]) == thr);
+    long long* s = (long long*)c.sh + 40;
+    __shared__ int found, owner;
+    __shared__ long long owner_skip;
+    __syncthreads();
+    s[threadIdx.x] = mine;
+    if (threadIdx.x == 0) { found = V; owner = -1; }
+    const long long total = blk_sum_ll(mine, c.sh);              // (its barriers also publish s[] and found)
+    smp_cl_exchange(c, (unsigned long long)total, 0ull, 0ull);
+    long long before = 0;
+    for (int r = 0; r < c.rank; r++) before += (long long)smp_cl_get(c, r, 0);
+    const long long local = n - before;                           // the wanted one is this block's local-th, if it is here
+    if (threadIdx.x == 0 && local >= 0 && local < total) {
+        long long run = 0;
+        for (int t = 0; t < SMP_THREADS; t++) {
+            if (run + s[t] > local) { owner = t; owner_skip = local - run; break; }
+            run += s[t];
+        }
+    }
+    __syncthreads();
+    if ((int)threadIdx.x == owner) {
+        long long cnt = 0;
+#pragma unroll
+        for (int j = 0; j < PER; j++)
+            if (j < nvalid && xr_key(v[j]) == thr) { if (cnt == owner_skip) found = base + j; cnt++; }
+    }
+    __syncthreads();
+    smp_cl_exchange(c, (unsigned long long)found, 0ull, 0ull);
+    int f = V;
+    for (int r = 0; r < SMP_CL; r++) f = min(f, (int)smp_cl_get(c, r, 0));
+    __syncthreads();                                              // found and owner may be written again by the next call
+    return f;
+}
+
+template <int PER>
+__global__ void __launch_bounds__(SMP_THREADS)
+k_sample_cluster(SampleArgs a) {
+    xr_pdl_launch();
+    __shared__ double sh[40 + SMP_THREADS];
+    __shared__ float sh_f[33];
+    __shared__ int sh_i[33];
+    __shared__ unsigned long long slots[2][SMP_CL][3];
+    __shared__ int rec_tok[SMP_RECENT], rec_cnt[SMP_RECENT];
+    const int row = blockIdx.x / SMP_CL, tid = threadIdx.x;
+    SmpCluster c{slots, sh, 0, (int)(blockIdx.x % SMP_CL)};
+    const float* lg = a.logits + (size_t)row * a.ld;
+    // (the rows' parameters are written before the step's kernels are queued: they may be read before the wait)
+    const float temp = a.temp[row];
+    const int V = a.V;
+    xr_pdl_wait();
+    if (temp <= 0.f) {                              // a greedy row: one block does it (the whole cluster leaves here)
+        if (c.rank == 0) smp_argmax(lg, V, a.out + row, sh_f, sh_i);
+        return;
+    }
+    // "this block runs": nobody writes into a block's shared memory before all of the cluster have begun
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+
+    // ---- the thread's values: ids base .. base + nvalid - 1 ----
+    const int base = (c.rank * SMP_THREADS + tid) * PER;
+    const int nvalid = V - base < 0 ? 0 : (V - base < PER ? V - base : PER);
+    float v[PER];
+    if (nvalid == PER && ((((uintptr_t)(lg + base)) & 15) == 0)) {
+        const float4* src = reinterpret_cast<const float4*>(lg + base);
+        float4 q[PER / 4];
+#pragma unroll
+        for (int k = 0; k < PER / 4; k++) q[k] = xr_ld_now4(src + k);
+#pragma unroll
+        for (int k = 0; k < PER / 4; k++) { xr_ld_fence(q[k]); v[4 * k] = q[k].x; v[4 * k + 1] = q[k].y; v[4 * k + 2] = q[k].z; v[4 * k + 3] = q[k].w; }
+    } else {
+#pragma unroll
+        for (int j = 0; j < PER; j++) v[j] = j < nvalid ? lg[base + j] : -INFINITY;
+    }
+    // ---- repeat penalty, once per occurrence in the window (src/sample.c:148-166) ----
+    const float pen = a.penalty[row];
+    if (a.recent != nullptr && pen != 1.0f) {
+        if (tid < SMP_RECENT) {
+            const int* rec = a.recent + (size_t)row * SMP_RECENT;
+            int tok = rec[tid];
+            bool first = tok >= 0 && tok < V; int cnt = 0;
+            if (first)
+                for (int j = 0; j < SMP_RECENT; j++) { if (rec[j] == tok) { cnt++; if (j < tid) first = false; } }
+            rec_tok[tid] = first ? tok : -1;
+            rec_cnt[tid] = cnt;
+        }
+        __syncthreads();
+        for (int e = 0; e < SMP_RECENT; e++) {
+            const int off = rec_tok[e] - base;
+            if (off >= 0 && off < nvalid) {
+#pragma unroll
+                for (int j = 0; j < PER; j++)
+                    if (j == off) { float x = v[j]; for (int k = 0; k < rec_cnt[e]; k++) x = x > 0.f ? x / pen : x * pen; v[j] = x; }
+            }
+        }
+    }
+    // ---- scale, and the row's maximum ----
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < PER; j++) { v[j] = v[j] / temp; if (j < nvalid) mx = fmaxf(mx, v[j]); }
+    mx = xr_warp_max(mx);
+    __syncthreads();
+    if ((tid & 31) == 0) sh_f[tid >> 5] = mx;
+    __syncthreads();
+    if (tid < 32) { float t = sh_f[tid]; t = xr_warp_max(t); if (tid == 0) sh_f[32] = t; }
+    __syncthreads();
+    smp_cl_exchange(c, (unsigned long long)__float_as_uint(sh_f[32]), 0ull, 0ull);
+    mx = -INFINITY;
+    for (int r = 0; r < SMP_CL; r++) mx = fmaxf(mx, __uint_as_float((unsigned)smp_cl_get(c, r, 0)));
+
+    Cut cut{0u, -1};               // everything survives
+    const int top_k = a.top_k[row];
+    // ---- top-k: the k-th largest key by descending over the key bits with counts ----
+    if (top_k > 0 && top_k < V) {
+        unsigned thr = 0;
+        for (int shift = 30; shift >= 0; shift -= 2) {
+            const unsigned c1 = thr | (1u << shift), c2 = thr | (2u << shift), c3 = thr | (3u << shift);
+            long long n[3] = {0, 0, 0};
+#pragma unroll
+            for (int j = 0; j < PER; j++)
+                if (j < nvalid) { unsigned k = xr_key(v[j]); n[0] += (k >= c1); n[1] += (k >= c2); n[2] += (k >= c3); }
+            smp_cl_sum3_ll(c, n);
+            thr = n[2] >= top_k ? c3 : (n[1] >= top_k ? c2 : (n[0] >= top_k ? c1 : thr));
+        }
+        long long gt = 0;
+#pragma unroll
+        for (int j = 0; j < PER; j++) gt += (j < nvalid && xr_key(v[j]) > thr);
+        gt = smp_cl_sum_ll(c, gt);
+        cut.thr = thr; cut.n_eq = (long long)top_k - gt;      // that many of the equal keys, by id
+    }
+    // id bound for equal keys (V when all of them survive)
+    int eq_id_end = V;
+    if (cut.n_eq >= 0) {
+        long long eq = 0;
+#pragma unroll
+        for (int j = 0; j < PER; j++) eq += (j < nvalid && xr_key(v[j]) == cut.thr);
+        eq = smp_cl_sum_ll(c, eq);
+        if (cut.n_eq < eq) eq_id_end = smp_cl_nth_equal_id<PER>(c, V, v, base, nvalid, cut.thr, cut.n_eq);
+    }
+#define CL_SURVIVES(i, k) ((k) > cut.thr || ((k) == cut.thr && (i) < eq_id_end))
+
+    // ---- mass of the survivors ----
+    double Z = 0.0;
+#pragma unroll
+    for (int j = 0; j < PER; j++)
+        if (j < nvalid) { unsigned k = xr_key(v[j]); if (CL_SURVIVES(base + j, k)) Z += (double)expf(v[j] - mx); }
+    Z = smp_cl_sum_d(c, Z);
+
+    // ---- top-p: shortest prefix with cumulative probability >= top_p ----
+    const float top_p = a.top_p[row];
+    if (top_p < 1.0f) {
+        const double target = (double)top_p * Z;
+        unsigned thr = 0;                       // largest key x with mass{key >= x} >= target
+        for (int shift = 30; shift >= 0; shift -= 2) {
+            const unsigned c1 = thr | (1u << shift), c2 = thr | (2u << shift), c3 = thr | (3u << shift);
+            double ms[3] = {0.0, 0.0, 0.0};
+#pragma unroll
+            for (int j = 0; j < PER; j++) {
+                unsigned k = xr_key(v[j]);
+                if (j < nvalid && k >= c1 && CL_SURVIVES(base + j, k)) {
+                    double e = (double)expf(v[j] - mx);
+                    ms[0] += e; ms[1] += k >= c2 ? e : 0.0; ms[2] += k >= c3 ? e : 0.0;
+                }
+            }
+            smp_cl_sum3_d(c, ms);
+            thr = ms[2] >= target ? c3 : (ms[1] >= target ? c2 : (ms[0] >= target ? c1 : thr));
+        }
+        // among equal keys at thr, keep only as many (by id) as the prefix needs; if thr is also where top-k cut,
+        // no more than top-k left there
+        double gtm = 0.0; long long eqn = 0;
+#pragma unroll
+        for (int j = 0; j < PER; j++)
+            if (j < nvalid) { unsigned k = xr_key(v[j]); if (k > thr) gtm += (double)expf(v[j] - mx); eqn += (k == thr); }
+        smp_cl_sum_d_ll(c, gtm, eqn);
+        const long long avail = (thr == cut.thr && cut.n_eq >= 0 && cut.n_eq < eqn) ? cut.n_eq : eqn;
+        long long need = avail;
+        if (avail > 1) {
+            // each equal candidate adds e; the prefix ends at the first whose cumulative sum reaches target
+            float vt = __uint_as_float((thr & 0x80000000u) ? (thr & 0x7fffffffu) : ~thr);
+            double e = (double)expf(vt - mx);
+            long long n = (long long)ceil((target - gtm) / e - 1e-9);
+            if (n < 1) n = 1;
+            if (n < need) need = n;
+        }
+        cut.thr = thr; cut.n_eq = need;
+        eq_id_end = need < eqn ? smp_cl_nth_equal_id<PER>(c, V, v, base, nvalid, thr, need) : V;
+        Z = 0.0;
+#pragma unroll
+        for (int j = 0; j < PER; j++)
+            if (j < nvalid) { unsigned k = xr_key(v[j]); if (CL_SURVIVES(base + j, k)) Z += (double)expf(v[j] - mx); }
+        Z = smp_cl_sum_d(c, Z);
+    }
+
+    // ---- min-p: drop candidates with p < min_p * p_max; the best candidate has exp(v - mx) = 1 ----
+    const float min_p = a.min_p[row];
+    const float e_floor = min_p > 0.f ? min_p : 0.f;
+    if (e_floor > 0.f) {
+        Z = 0.0;
+#pragma unroll
+        for (int j = 0; j < PER; j++)
+            if (j < nvalid) { unsigned k = xr_key(v[j]); float e = expf(v[j] - mx); if (CL_SURVIVES(base + j, k) && e >= e_floor) Z += (double)e; }
+        Z = smp_cl_sum_d(c, Z);
+    }
+#define CL_FINAL(i, k, e) (CL_SURVIVES(i, k) && (e) >= e_floor)
+
+    // ---- the pick: first candidate whose cumulative mass exceeds r * Z ----
+    const double want = (double)a.draw[row] * Z;
+    unsigned thr = 0; bool any = false;
+    for (int shift = 30; shift >= 0; shift -= 2) {
+        const unsigned c1 = thr | (1u << shift), c2 = thr | (2u << shift), c3 = thr | (3u << shift);
+        double ms[3] = {0.0, 0.0, 0.0};
+#pragma unroll
+        for (int j = 0; j < PER; j++) {
+            unsigned k = xr_key(v[j]);
+            if (j < nvalid && k >= c1) {
+                float e = expf(v[j] - mx);
+                if (CL_FINAL(base + j, k, e)) { ms[0] += (double)e; ms[1] += k >= c2 ? (double)e : 0.0; ms[2] += k >= c3 ? (double)e : 0.0; }
+            }
+        }
+        smp_cl_sum3_d(c, ms);
+        if (ms[2] > want) { thr = c3; any = true; }
+        else if (ms[1] > want) { thr = c2; any = true; }
+        else if (ms[0] > want) { thr = c1; any = true; }
+    }
+    // candidates with key == thr that are in the final set, and the mass above them
+    double gtm = 0.0; long long eqn = 0;
+#pragma unroll
+    for (int j = 0; j < PER; j++)
+        if (j < nvalid) {
+            unsigned k = xr_key(v[j]); float e = expf(v[j] - mx);
+            if (CL_FINAL(base + j, k, e)) { if (k > thr) gtm += (double)e; else if (k == thr) eqn++; }
+        }
+    smp_cl_sum_d_ll(c, gtm, eqn);
+    if (!any || eqn == 0) {
+        // the walk ran off the end (r * Z rounded up to the whole mass): the reference returns the last
+        // candidate (src/sample.c:119); that is the smallest final key, largest id.  Both in one word whose
+        // minimum is wanted: key above, inverted id below.
+        unsigned long long low = ~0ull;
+#pragma unroll
+        for (int j = 0; j < PER; j++)
+            if (j < nvalid) {
+                unsigned k = xr_key(v[j]); float e = expf(v[j] - mx);
+                if (CL_FINAL(base + j, k, e)) {
+                    unsigned long long w = ((unsigned long long)k << 32) | (unsigned long long)(0xffffffffu - (unsigned)(base + j));
+                    low = w < low ? w : low;
+                }
+            }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) { unsigned long long t = __shfl_xor_sync(0xffffffffu, low, o); low = t < low ? t : low; }
+        unsigned long long* ws = (unsigned long long*)sh;
+        __syncthreads();
+        if ((tid & 31) == 0) ws[tid >> 5] = low;
+        __syncthreads();
+        low = ws[0];
+        for (int w = 1; w < SMP_THREADS / 32; w++) low = ws[w] < low ? ws[w] : low;
+        smp_cl_exchange(c, low, 0ull, 0ull);
+        for (int r = 0; r < SMP_CL; r++) { unsigned long long t = smp_cl_get(c, r, 0); low = t < low ? t : low; }
+        if (c.rank == 0 && tid == 0) a.out[row] = low == ~0ull ? 0 : (int)(0xffffffffu - (unsigned)(low & 0xffffffffull));
+        return;
+    }
+    long long nth = 0;
+    if (eqn > 1) {
+        float vt = __uint_as_float((thr & 0x80000000u) ? (thr & 0x7fffffffu) : ~thr);
+        double e = (double)expf(vt - mx);
+        nth = (long long)floor((want - gtm) / e);
+        if (nth < 0) nth = 0;
+        if (nth >= eqn) nth = eqn - 1;
+    }
+    const int pick = smp_cl_nth_equal_id<PER>(c, V, v, base, nvalid, thr, nth);
+    if (c.rank == 0 && tid == 0) a.out[row] = pick;
+#undef CL_SURVIVES
+#undef CL_FINAL
+}
+
+static int launch_sample_cluster(const SampleArgs& a, int rows, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(rows * SMP_CL); cfg.blockDim = dim3(SMP_THREADS); cfg.dynamicSmemBytes = 0; cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = SMP_CL; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = xr_pdl_enabled() ? 2 : 1;
+    cudaLaunchKernelEx(&cfg, k_sample_cluster<SMP_PER>, a);
+    return xr_launch_status();
+}
+
+// Whether these rows go to the cluster kernel (XRB200_NO_CLUSTER_SAMPLE=1 keeps the one-block kernel).  A cluster
+// block fills an SM (1,024 threads of 64 registers), so clusters run in waves of (SMs / 8) rows; a wave took 190 us
+// where the one-block kernel took 720 us for any number of rows up to the SM count (vocabulary 128,256, top-k and
+// top-p): beyond three waves the one-block kernel is the faster one.
+static bool smp_use_cluster(int rows, int V) {
+    static int off = -1, sms = 0;
+    if (off < 0) {
+        const char* e = getenv("XRB200_NO_CLUSTER_SAMPLE"); off = (e && e[0] && e[0] != '0') ? 1 : 0;
+        int dev = 0; cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < SMP_CL) sms = SMP_CL;
+    }
+    if (off || V <= SMP_THREADS || (long long)V > (long long)SMP_CL * SMP_THREADS * SMP_PER) return false;
+    return rows <= 3 * (sms / SMP_CL);
+}
+
 // scratch: [rows, V] floats when any row has temp > 0 (may be null when all rows are greedy).
 XR_EXPORT int xr_sample(const float* logits, long long ld, int rows, int V, const float* temp, const int* top_k,
                         const float* top_p, const float* min_p, const float* penalty, const float* draw,
                         const int* recent, float* scratch, int* out, cudaStream_t stream) {
+    if (rows < 1 || V < 1 || ld < V) return XR_ERR_ARG;
+    SampleArgs a{logits, ld, V, temp, top_k, top_p, min_p, penalty, draw, recent, out};
+    if (smp_use_cluster(rows, V)) return launch_sample_cluster(a, rows, stream);
+    xr_launch(k_sample, dim3(rows), dim3(SMP_THREADS), 0, stream, a, scratch);
+    return xr_launch_status();
+}
+
+// The one-block kernel whatever the width (what xr_sample falls back to; tests compare the two).
+XR_EXPORT int xr_sample_one_block(const float* logits, long long ld, int rows, int V, const float* temp, const int* top_k,
+                                  const float* top_p, const float* min_p, const float* penalty, const float* draw,
+                                  const int* recent, float* scratch, int* out, cudaStream_t stream) {
     if (rows < 1 || V < 1 || ld < V) return XR_ERR_ARG;
     SampleArgs a{logits, ld, V, temp, top_k, top_p, min_p, penalty, draw, recent, out};
     xr_launch(k_sample, dim3(rows), dim3(SMP_THREADS), 0, stream, a, scratch);

@@ -2,6 +2,7 @@
 
     python -m xyntetik_runner_b200.probe gemm --tokens 8 --rows 14336 --k 4096 --epilogue swiglu
     python -m xyntetik_runner_b200.probe attention --batch 8 --context 8192 [--portion 1]
+    python -m xyntetik_runner_b200.probe sample --rows 8 --vocab 128256 [--one-block]
     XRB200_TRACE=1 python -m xyntetik_runner_b200.probe timeline --batch 8 --context 8192 --layers 8
 
 Times are CUDA-event times of `--iters` launches replayed from one CUDA graph (so that launch gaps do not
@@ -107,6 +108,24 @@ def attention(a) -> None:
           f"{kv_bytes / us / 1e3:.0f} GB/s of keys+values, {flops / us / 1e6:.1f} TFLOP/s")
 
 
+def sample(a) -> None:
+    """The sampling kernel on `--rows` rows of random logits, for a few settings of the chain."""
+    dev = torch.device("cuda:0")
+    rows, V = a.rows, a.vocab
+    logits = torch.randn(rows, V, device=dev) * 3
+    full = lambda v, dt=torch.float32: torch.full((rows,), v, dtype=dt, device=dev)
+    out = torch.zeros(rows, dtype=torch.int32, device=dev)
+    scratch = torch.empty(rows * V, dtype=torch.float32, device=dev)
+    recent = torch.full((rows, 256), -1, dtype=torch.int32, device=dev)
+    recent[:, :40] = torch.randint(0, V, (rows, 40), dtype=torch.int32, device=dev)
+    settings = {"greedy": (0.0, 0, 1.0, 0.0, 1.0), "temperature": (0.8, 0, 1.0, 0.0, 1.0), "top-k 40": (0.8, 40, 1.0, 0.0, 1.0),
+                "top-k 40, top-p 0.95": (0.8, 40, 0.95, 0.0, 1.0), "top-k 40, top-p 0.95, min-p 0.05, penalty 1.1": (0.8, 40, 0.95, 0.05, 1.1)}
+    for name, (temp, k, p, m, pen) in settings.items():
+        args = (logits, full(temp), full(k, torch.int32), full(p), full(m), full(pen), full(0.37), recent, scratch, out)
+        us = _time(lambda i: kernels.sample(*args, any_sampled=temp > 0, one_block=a.one_block), a.iters, a.plain)
+        print(f"sample rows={rows} vocab={V} {name}: {us:.1f} us")
+
+
 def timeline(a) -> None:
     import ctypes
     import numpy as np
@@ -191,15 +210,19 @@ def main(argv=None) -> int:
     t.add_argument("--page-size", type=int, default=64)
     t.add_argument("--no-tc", action="store_true", help="prompt portions on the mma.sync kernel instead of tcgen05")
     t.add_argument("--no-tma", action="store_true", help="decode kernel with per-thread cp.async gathers instead of bulk copies")
+    sm = sub.add_parser("sample")
+    sm.add_argument("--rows", type=int, default=8)
+    sm.add_argument("--vocab", type=int, default=128256)
+    sm.add_argument("--one-block", action="store_true", help="one block a row whatever the width (no cluster)")
     tl = sub.add_parser("timeline")
     tl.add_argument("--batch", type=int, default=8)
     tl.add_argument("--context", type=int, default=8192)
     tl.add_argument("--layers", type=int, default=8)
-    for p in (g, t):
+    for p in (g, t, sm):
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--plain", action="store_true", help="no CUDA graph")
     a = ap.parse_args(argv)
-    {"gemm": gemm, "attention": attention, "timeline": timeline}[a.what](a)
+    {"gemm": gemm, "attention": attention, "sample": sample, "timeline": timeline}[a.what](a)
     return 0
 
 
