@@ -1,7 +1,8 @@
 """Generality of the parts: a toy architecture defined HERE -- a mixer with per-request state of its own, a
-feed-forward with routing, attention without a position encoding, a schedule that runs a layer twice and
-lets a layer read another layer's cache -- is registered, built from a folder, and stepped through the
-engine without any change to the framework's files.  It is compared with a plain computation written here.
+feed-forward with routing, attention without a position encoding and attention with a position encoding of the
+test's own (half of each head rotated, frequencies in arithmetic steps), a norm of the test's own (mean removed
+first, no weights), a schedule that runs a layer twice and lets a layer read another layer's cache -- is
+registered, built from a folder, and stepped through the engine without any change to the framework's files.  It is compared with a plain computation written here.
 It is a test fixture, not a model of anything.
 """
 import json
@@ -12,12 +13,21 @@ import pytest
 import torch
 
 import traces
-from plain_llama import attention, matvec_rows, read_folder, rmsnorm, rope_apply, rope_inv_freq, swiglu
+from plain_llama import attention, matvec_rows, read_folder, rmsnorm, rope_apply, swiglu
 
 pytestmark = pytest.mark.gpu
 
 TOY = {"architectures": ["ToyForCausalLM"], "vocab": 97, "width": 48, "heads": 4, "kv_heads": 2, "head_dim": 16,
-       "inner": 72, "eps": 1e-5, "experts": 3, "state": 24, "theta": 10000.0, "max_positions": 512}
+       "inner": 72, "eps": 1e-5, "experts": 3, "state": 24, "rotary_dim": 8, "rotary_step": 3.0, "max_positions": 512}
+
+
+def toy_inv_freq(rotary_dim, step):
+    return (1.0 / (1.0 + np.float32(step) * np.arange(rotary_dim // 2, dtype=np.float32))).astype(np.float32)
+
+
+def centred(x, eps):
+    c = x.astype(np.float64) - x.astype(np.float64).mean(axis=-1, keepdims=True)
+    return (c / np.sqrt((c * c).mean(axis=-1, keepdims=True) + np.float64(np.float32(eps)))).astype(np.float32)
 
 
 def _define():
@@ -26,8 +36,9 @@ def _define():
     from xyntetik_runner_b200 import kernels
     from xyntetik_runner_b200.config.registry import register_architecture
     from xyntetik_runner_b200.engine.model import ModelPlan, ScheduleEntry
-    from xyntetik_runner_b200.parts import (Embedding, FeedForward, GQAAttention, Head, Mixer, NoPosition, PreNormBlock,
-                                            RMSNorm, Rope, StateNeed, SwiGLU, register_feed_forward, register_mixer)
+    from xyntetik_runner_b200.parts import (Embedding, FeedForward, GQAAttention, Head, Mixer, NoPosition, Norm,
+                                            PositionEncoding, PreNormBlock, RMSNorm, StateNeed, SwiGLU, make,
+                                            register_feed_forward, register_mixer, register_norm, register_position)
     from xyntetik_runner_b200.weights.loader import TensorSpec
 
     class RunningSumMixer(Mixer):
@@ -87,8 +98,40 @@ def _define():
                 g, u = gu[:, :self.inner], gu[:, self.inner:]
                 x[idx] += (g / (1 + torch.exp(-g)) * u) @ self.dn[e].T
 
+    class StepRotary(PositionEncoding):
+        """A rotary encoding with laws of its own: only the first `rotary_dim` values of a head are rotated, and
+        pair j turns at 1 / (1 + step * j) radians a position."""
+
+        def __init__(self, rotary_dim, step):
+            self.rotary_dim = rotary_dim
+            self.inv_freq_host = toy_inv_freq(rotary_dim, step)
+            self.inv_freq = None
+
+        def prepare(self, rt):
+            self.inv_freq = torch.from_numpy(self.inv_freq_host.copy()).to(rt.device)
+
+    class CentredNorm(Norm):
+        """out = (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps): no weights, float32."""
+
+        def __init__(self, width, eps):
+            self.width, self.eps = width, float(eps)
+
+        def tensors(self):
+            return {}
+
+        def bind(self, tensors, rt):
+            pass
+
+        def forward(self, ctx, x, out, rows=None):
+            ctx.materialize(x)
+            src = x if rows is None else x[rows.long()]
+            c = src - src.mean(dim=1, keepdim=True)
+            out[:src.shape[0]] = (c * torch.rsqrt((c * c).mean(dim=1, keepdim=True) + self.eps)).to(out.dtype)
+
     register_mixer("toy_running_sum", RunningSumMixer, replace=True)
     register_feed_forward("toy_routed", RoutedFF, replace=True)
+    register_position("toy_step_rotary", StepRotary, replace=True)
+    register_norm("toy_centred", CentredNorm, replace=True)
 
     class ToyConfig:
         def __init__(self, d):
@@ -100,10 +143,11 @@ def _define():
         emb = Embedding(c.vocab, c.width, "emb.weight")
         norm = lambda name: RMSNorm(c.width, c.eps, name)
         att0 = GQAAttention(c.width, c.heads, c.kv_heads, c.head_dim, NoPosition(), "l0.att.")
-        att2 = GQAAttention(c.width, c.heads, c.kv_heads, c.head_dim, Rope(c.head_dim, c.theta), "l2.att.", window=40)
+        att2 = GQAAttention(c.width, c.heads, c.kv_heads, c.head_dim,
+                            make("position", "toy_step_rotary", rotary_dim=c.rotary_dim, step=c.rotary_step), "l2.att.", window=40)
         blocks = [
             PreNormBlock(norm("l0.n1"), att0, norm("l0.n2"), RoutedFF(c.width, c.inner, c.experts, "l0.ff.")),
-            PreNormBlock(norm("l1.n1"), RunningSumMixer(c.width, c.state, "l1.mix."), norm("l1.n2"),
+            PreNormBlock(norm("l1.n1"), RunningSumMixer(c.width, c.state, "l1.mix."), make("norm", "toy_centred", width=c.width, eps=c.eps),
                          SwiGLU(c.width, c.inner, "l1.ff.")),
             PreNormBlock(norm("l2.n1"), att2, norm("l2.n2"), SwiGLU(c.width, c.inner, "l2.ff.")),
         ]
@@ -121,7 +165,7 @@ def plain_toy(folder, ids):
     T = len(ids)
     H, K, hd, d, F = cfg["heads"], cfg["kv_heads"], cfg["head_dim"], cfg["width"], cfg["inner"]
     pos = np.arange(T)
-    inv = rope_inv_freq(cfg["theta"], hd)
+    inv = toy_inv_freq(cfg["rotary_dim"], cfg["rotary_step"])        # rope_apply rotates the first 2 * len(inv) values of a head
     x = w["emb.weight"][np.asarray(ids)].astype(np.float32)
 
     def att(prefix, h, rope, window, kv_from=None):
@@ -155,7 +199,7 @@ def plain_toy(folder, ids):
     h = rmsnorm(x, w["l1.n1"], cfg["eps"])
     run = np.cumsum(h.astype(np.float64) @ w["l1.mix.in.weight"].astype(np.float64).T, axis=0)
     x = x + (run @ w["l1.mix.out.weight"].astype(np.float64).T).astype(np.float32)
-    x = x + ffn("l1.ff.", rmsnorm(x, w["l1.n2"], cfg["eps"]))
+    x = x + ffn("l1.ff.", centred(x, cfg["eps"]))
     h2 = rmsnorm(x, w["l2.n1"], cfg["eps"])                     # the keys of schedule entry 2 come from here
     x = x + att("l2.att.", h2, True, 40)
     x = x + ffn("l2.ff.", rmsnorm(x, w["l2.n2"], cfg["eps"]))
@@ -211,6 +255,7 @@ def test_unknown_part_kinds_are_refused():
     from xyntetik_runner_b200.parts import kinds, make
     _define()
     assert "toy_running_sum" in kinds("mixer") and "gqa_attention" in kinds("mixer") and "swiglu" in kinds("feed_forward")
+    assert "toy_step_rotary" in kinds("position") and "rope" in kinds("position") and "toy_centred" in kinds("norm")
     with pytest.raises(ValueError, match="unknown mixer kind"):
         make("mixer", "nope")
     m = make("norm", "rmsnorm", width=8, eps=1e-5, name="n")

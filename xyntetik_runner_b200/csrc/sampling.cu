@@ -793,9 +793,9 @@ static int launch_sample_cluster(const SampleArgs& a, int rows, cudaStream_t str
 }
 
 // Whether these rows go to the cluster kernel (XRB200_NO_CLUSTER_SAMPLE=1 keeps the one-block kernel).  A cluster
-// block fills an SM (1,024 threads of 64 registers), so clusters run in waves of (SMs / 8) rows; a wave took 190 us
-// where the one-block kernel took 720 us for any number of rows up to the SM count (vocabulary 128,256, top-k and
-// top-p): beyond three waves the one-block kernel is the faster one.
+// block fills an SM (1,024 threads of 64 registers), so clusters run in waves of (SMs / 8) rows.  Measured at a
+// vocabulary of 128,256 with top-k and top-p: 180 us a wave (8 rows 180, 24 rows 355, 48 rows 700), where the
+// one-block kernel takes 715 us for any number of rows up to the SM count; up to two waves the cluster kernel wins.
 static bool smp_use_cluster(int rows, int V) {
     static int off = -1, sms = 0;
     if (off < 0) {
@@ -804,7 +804,7 @@ static bool smp_use_cluster(int rows, int V) {
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < SMP_CL) sms = SMP_CL;
     }
     if (off || V <= SMP_THREADS || (long long)V > (long long)SMP_CL * SMP_THREADS * SMP_PER) return false;
-    return rows <= 3 * (sms / SMP_CL);
+    return rows <= 2 * (sms / SMP_CL);
 }
 
 // scratch: [rows, V] floats when any row has temp > 0 (may be null when all rows are greedy).
