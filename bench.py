@@ -2,6 +2,8 @@
 """Decode and prefill throughput of the engine at Llama-3-8B shape, random weights, one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference]
+    python bench.py --shape llama-2-13b --context 3840      # the same measurement at another shape of the architecture
+    python bench.py --workload mixed                        # 64 requests of 16..4,096 tokens through Runner.generate
 
 A "step" is one decode step of the whole batch through the engine's step function and the device
 sampler.  One JSON line is printed: `value` = decoded tokens per second at batch 8 with every request
@@ -28,6 +30,14 @@ LLAMA3_8B = {
     "rms_norm_eps": 1e-5, "rope_theta": 500000.0, "rope_scaling": None, "max_position_embeddings": 8192,
     "tie_word_embeddings": False, "hidden_act": "silu", "torch_dtype": "bfloat16",
 }
+LLAMA32_1B = dict(LLAMA3_8B, hidden_size=2048, num_hidden_layers=16, head_dim=64, intermediate_size=8192, tie_word_embeddings=True,
+                  rope_scaling={"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                                "original_max_position_embeddings": 8192})
+LLAMA2_13B = dict(LLAMA3_8B, hidden_size=5120, num_hidden_layers=40, num_attention_heads=40, num_key_value_heads=40,
+                  intermediate_size=13824, vocab_size=32000, rope_theta=10000.0, max_position_embeddings=4096)
+# shape name -> (config.json keys, weight seed, default context of the decode measurement, name in the metric)
+SHAPES = {"llama-3-8b": (LLAMA3_8B, 2, 8192, "Llama-3-8B"), "llama-3.2-1b": (LLAMA32_1B, 3, 8192, "Llama-3.2-1B"),
+          "llama-2-13b": (LLAMA2_13B, 4, 3840, "Llama-2-13B")}
 FULL_LAYERS = 32
 CONTEXT = 8192
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
@@ -91,6 +101,44 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def mixed_workload(args) -> int:
+    """64 requests at once with prompts of 16 to 4,096 random tokens (uniform), 128 tokens generated for each, through
+    the Python entry point: prompt portions share steps with decoded tokens under the scheduler's token budget.
+    Wall-clock time of the second of two runs (the first warms up graphs and buffers); host token ids in and out."""
+    import numpy as np
+    import torch
+    from xyntetik_runner_b200 import kernels
+    from xyntetik_runner_b200.config.llama import LlamaConfig
+    from xyntetik_runner_b200.engine.runner import Runner
+    shape = args.shape or "llama-3.2-1b"
+    cfgd, seed, _, _ = SHAPES[shape]
+    cfg = LlamaConfig.from_dict(cfgd)
+    n_req, new = 64, 128
+    rng = np.random.RandomState(seed)
+    lens = rng.randint(16, 4097, size=n_req)
+    prompts = [[int(t) for t in rng.randint(0, cfg.vocab_size, size=int(n))] for n in lens]
+    runner = Runner(config=cfg, random_seed=seed, ctx=4096 + new + 32, batch=2048, parallel=n_req)
+    clocks = ClockSampler()
+    clocks.start()
+    out = None
+    for rep in range(2):
+        torch.cuda.synchronize()
+        launches0, t0 = kernels.launch_count, time.perf_counter()
+        res = runner.generate(prompts, n=new, ignore_eos=True)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        gen = sum(len(r.tokens) for r in res)
+        out = {"workload": f"{n_req} requests at once, prompts uniform in [16, 4096], {new} generated each, prompt portions mixed with decoding",
+               "model": shape + "-shape", "dtype": "bf16", "data": f"synthetic (random weights seed {seed}, random token ids)",
+               "seconds": dt, "prompt_tokens": int(lens.sum()), "generated_tokens": gen,
+               "value": (int(lens.sum()) + gen) / dt, "unit": "tok/s (prompt + generated)", "generated_tok_s": gen / dt,
+               "steps": runner.scheduler.stats.get("steps"), "gpu_launches": kernels.launch_count - launches0,
+               "step_token_budget": 2048}
+    out["clocks"] = clocks.stop()
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -104,6 +152,9 @@ def main() -> int:
     ap.add_argument("--decode-only", action="store_true", help="time the decode step only (for profiling a small run)")
     ap.add_argument("--prefill-only", action="store_true", help="time the 2,048-token prefill only (for profiling a small run)")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel of a decode step one by one")
+    ap.add_argument("--shape", choices=sorted(SHAPES), default=None, help="layer sizes (default llama-3-8b)")
+    ap.add_argument("--workload", choices=["decode", "mixed"], default="decode",
+                    help="mixed: many requests with prompts of mixed length through Runner.generate (default shape llama-3.2-1b)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -113,6 +164,8 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py measures one GPU (N=1); N={args.gpus} is not supported by this engine")
         return 2
+    if args.workload == "mixed":
+        return mixed_workload(args)
     W = max(3, args.warmup)
     K = max(1, args.steps)
 
@@ -126,14 +179,23 @@ def main() -> int:
     from xyntetik_runner_b200.sampling.sampler import RequestSampler, SamplingParams
 
     pk = peaks()
-    cfgd = dict(LLAMA3_8B, num_hidden_layers=args.layers)
+    shape = args.shape or "llama-3-8b"
+    shape_cfg, seed, shape_ctx, shape_name = SHAPES[shape]
+    full_layers = shape_cfg["num_hidden_layers"]
+    if args.shape is not None and args.layers == FULL_LAYERS:
+        args.layers = full_layers
+    if args.shape is not None and args.context == CONTEXT:
+        args.context = shape_ctx
+    cfgd = dict(shape_cfg, num_hidden_layers=args.layers, max_position_embeddings=max(shape_cfg["max_position_embeddings"], args.context))
     cfg = LlamaConfig.from_dict(cfgd)
     if args.decode_only or args.prefill_only:
         args.skip_points = True
-    max_b = args.batch if args.skip_points else max(args.batch, 64)
     ctx_len = args.context
+    kv_token_bytes = 4 * cfg.num_hidden_layers * cfg.num_key_value_heads * cfg.head_dim
+    big_fits = 64 * ctx_len * kv_token_bytes <= 100e9          # batch 64 at this context within the memory left beside the weights
+    max_b = args.batch if (args.skip_points or not big_fits) else max(args.batch, 64)
     t_load = time.perf_counter()
-    eng = random_engine(cfg, 2, EngineParams(dtype="bfloat16", max_tokens=max_b * ctx_len, page_size=64, max_requests=max_b,
+    eng = random_engine(cfg, seed, EngineParams(dtype="bfloat16", max_tokens=max_b * ctx_len, page_size=64, max_requests=max_b,
                                              max_request_tokens=ctx_len, max_step_tokens=2048,
                                              cuda_graphs=not args.no_graphs))
     for kv in eng.kv:                      # keys and values of an imagined earlier context
@@ -254,10 +316,12 @@ def main() -> int:
 
     points = {}
     if not args.skip_points:
-        for b in (1, 64):
+        for b in (1, 64) if big_fits else (1,):
             r = decode_run(b, start_len, max(4, K // 2), W)
             points[f"decode_b{b}"] = b * 1e3 / r["ms"]
         for b in (1, 8, 64):          # the reference workload: 512-token prompts, 256 generated (mid-point 640)
+            if b > max_b:
+                continue
             r = decode_run(b, 640 - W - max(4, K // 2), max(4, K // 2), W)
             points[f"decode_b{b}_ctx640"] = b * 1e3 / r["ms"]
     clk = clocks.stop()
@@ -268,10 +332,11 @@ def main() -> int:
     step_bytes = eng.weight_bytes_per_step() + kv_bytes
     achieved = step_bytes / (ms * 1e-3) / 1e9
     line = {
-        "metric": "decode tok/s at batch 8 (Llama-3-8B shape, bf16, context 8192)", "value": value, "unit": "tok/s",
+        "metric": f"decode tok/s at batch {args.batch} ({shape_name} shape, bf16, context {ctx_len})",
+        "value": value, "unit": "tok/s",
         "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights seed 2, random token ids, random cached keys/values)",
-        "config": {"model": "llama-3-8b-shape", "layers": cfg.num_hidden_layers, "layers_of_model": FULL_LAYERS,
+        "vs_baseline": None, "dtype": "bf16", "data": f"synthetic (random weights seed {seed}, random token ids, random cached keys/values)",
+        "config": {"model": shape + "-shape", "layers": cfg.num_hidden_layers, "layers_of_model": full_layers,
                    "hidden": d, "heads": H, "kv_heads": Kh, "head_dim": hd, "intermediate": F, "vocab": V,
                    "global_batch": args.batch, "seq_len": ctx_len, "page_size": 64, "parallelism": "single-gpu",
                    "l2": "step inputs (weights) exceed L2", "peaks": pk["source"]},

@@ -405,14 +405,14 @@ TC_ATT_CASES = [
 ]
 
 
+@pytest.mark.parametrize("hd", [128, 64])
 @pytest.mark.parametrize("case_id", range(len(TC_ATT_CASES)))
-def test_attention_tc(case_id):
-    """Prompt attention on tcgen05 against the float64 computation (head size 128)."""
+def test_attention_tc(case_id, hd):
+    """Prompt attention on tcgen05 against the float64 computation (head sizes 128 and 64)."""
     from xyntetik_runner_b200 import kernels
     H, K, page, window, segs = TC_ATT_CASES[case_id]
-    hd = 128
     assert kernels.attention_tc_supported(torch.bfloat16, H, K, hd, page)
-    c = _paged_case(100 + case_id, H, K, hd, page, segs, torch.bfloat16, window)
+    c = _paged_case(100 + case_id + hd, H, K, hd, page, segs, torch.bfloat16, window)
     out = torch.full((c["n"], H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
     cache = c["cache"]
     kernels.attention_tc(c["qkv"], out, c["starts"], c["lens"], c["pos0"], c["bt"], (cache.data_ptr(), cache.shape[0], cache.shape[1], 0),

@@ -2,8 +2,8 @@
 // paged cache: S = Q K^T and O += P V as tcgen05.mma with S and O in tensor memory, Q, K, V brought to shared
 // memory by TMA (128-byte swizzle; K and V straight from the pages), softmax in float32 by the thread that
 // owns the row.  Same arithmetic as the row-tiled mma.sync kernel (attention_mma.cu), which stays as the
-// path for the shapes this one does not take.  Needs bfloat16, head size 128, heads per kv head dividing
-// 128, a power-of-two page size >= 8.
+// path for the shapes this one does not take.  Needs bfloat16, head size 64 or 128 (one or two 64-column
+// halves of Q, K, V and O), heads per kv head dividing 128, a power-of-two page size >= 8.
 //
 // A CTA owns 128 packed rows (token i / G, head i % G) of one (request, kv head) and walks its keys in tiles
 // of 128, in ascending order.  Roles (192 threads):
@@ -38,7 +38,6 @@
 
 #define TA_ROWS 128
 #define TA_KEYS 128
-#define TA_HD 128
 #define TA_THREADS 352
 #define TA_SPIN (1u << 24)
 
@@ -149,14 +148,16 @@ __device__ __forceinline__ uint64_t ta_desc_k(uint32_t saddr) {
 __device__ __forceinline__ uint64_t ta_desc_mn(uint32_t saddr, uint32_t lbo) {
     return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
-// instruction descriptor: float32 accumulate, bfloat16 A and B, M = 128, N = 128; b_mn: B is MN-major
-__host__ __device__ constexpr uint32_t ta_idesc(bool b_mn) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+// instruction descriptor: float32 accumulate, bfloat16 A and B, M = 128, N = n; b_mn: B is MN-major
+__host__ __device__ constexpr uint32_t ta_idesc(bool b_mn, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
 
 // P_TMEM: P is written over the first 64 columns of its tile's S in tensor memory and read from there by the
 // product (half the shared-memory traffic of P V, no P stores to shared memory); else through shared memory.
-template <bool P_TMEM>
+// HD: head size, 64 or 128.  Shared memory keeps the layout of head size 128 (a stage of K or V is two halves
+// apart); at head size 64 only the first half of each is filled and read.
+template <bool P_TMEM, int HD>
 __global__ void __launch_bounds__(TA_THREADS, 1)
 k_attention_tc(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map, AttnTcArgs a) {
     // 14 half tiles of 16 KB leave no room for alignment slack: the array is declared 1 KB aligned (what the
@@ -168,6 +169,8 @@ k_attention_tc(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         return;
     }
     constexpr int HALF = TA_ROWS * 128;                   // bytes of one [128 rows][64 columns] half tile
+    constexpr int NH = HD / 64;                           // 64-column halves of a head
+    static_assert(HD == 64 || HD == 128, "head size 64 or 128");
     uint8_t* q_s = smem;                                  // [2 halves][128 rows][128 B]
     uint8_t* p_s = q_s + 2 * HALF;                        // [2 buffers][2 halves (keys 0-63, 64-127)][128 rows][128 B]
     uint8_t* k_s = p_s + 4 * HALF;                        // [2 stages][2 halves (hd)][128 keys][128 B]
@@ -222,9 +225,9 @@ k_attention_tc(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         if (lane == 0) {
             const bool keys = warp == 8;
             if (keys) {
-                ta_expect(q_full, 2 * HALF);
+                ta_expect(q_full, NH * HALF);
                 int tok0 = tok_base + row0 / a.G;
-                for (int c = 0; c < 2; c++) ta_tma_3d(q_s + c * HALF, &q_map, c * 64, kvh * a.G, tok0, q_full);
+                for (int c = 0; c < NH; c++) ta_tma_3d(q_s + c * HALF, &q_map, c * 64, kvh * a.G, tok0, q_full);
             }
             const int box_rows = a.page_size < 64 ? a.page_size : 64;
             uint64_t* full = keys ? k_full : v_full;
@@ -233,7 +236,7 @@ k_attention_tc(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
             for (int j = 0; j < n_tiles; j++) {
                 int s = j & 1;
                 if (j >= 2) ta_wait(&empty[s], ((j >> 1) - 1) & 1, gave_up);
-                ta_expect(&full[s], 2 * HALF);
+                ta_expect(&full[s], NH * HALF);
                 int key0 = (t_lo + j) * TA_KEYS;
                 for (int r0 = 0; r0 < TA_KEYS; r0 += box_rows) {
                     int kp = key0 + r0;
@@ -241,21 +244,21 @@ k_attention_tc(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
                     int page = pi < a.max_pages ? a.block_tables[(size_t)seg * a.max_pages + pi] : -1;
                     long long row = ((((long long)page * a.n_layers + a.layer) * 2 + (keys ? 0 : 1)) * a.K + kvh) * a.page_size + (kp & (a.page_size - 1));
                     if (page < 0) row = -1024;                          // outside the tensor: the copy fills zeros
-                    for (int c = 0; c < 2; c++) ta_tma_2d(base + (s * 2 + c) * HALF + r0 * 128, &kv_map, c * 64, (int)row, &full[s]);
+                    for (int c = 0; c < NH; c++) ta_tma_2d(base + (s * 2 + c) * HALF + r0 * 128, &kv_map, c * 64, (int)row, &full[s]);
                 }
             }
         }
     } else if (warp == 9) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            constexpr uint32_t id_qk = ta_idesc(false), id_pv = ta_idesc(true);
+            constexpr uint32_t id_qk = ta_idesc(false, TA_KEYS), id_pv = ta_idesc(true, HD);
             auto issue_qk = [&](int j) {
                 int s = j & 1;
                 ta_wait(&k_full[s], (j >> 1) & 1, gave_up);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 uint32_t qa = ta_smem(q_s), kb = ta_smem(k_s + s * 2 * HALF);
 #pragma unroll
-                for (int kk = 0; kk < TA_HD / 16; kk++) {
+                for (int kk = 0; kk < HD / 16; kk++) {
                     uint32_t off = (kk >> 2) * HALF + (kk & 3) * 32;
                     ta_mma((j & 1) ? tm_s1 : tm_s0, ta_desc_k(qa + off), ta_desc_k(kb + off), id_qk, kk > 0 ? 1u : 0u);
                 }
@@ -332,16 +335,16 @@ k_attention_tc(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
             if (m == -INFINITY) { if (mx != -INFINITY) m = mx; }          // O and l of this row are still zero
             else if (mx > m + 8.0f) { corr = ta_exp2(m - mx); m = mx; }
             if (j > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
-                // O is in use by the product of the previous tile until it completes; each thread rescales its 64 columns
+                // O is in use by the product of the previous tile until it completes; each thread rescales its half of the columns
                 ta_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, gave_up);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 l *= corr;
 #pragma unroll 1
-                for (int c = 0; c < 2; c++) {
-                    ta_ld32(tm_o + lane_off + half * 64 + c * 32, v);
+                for (int c = 0; c < NH; c++) {
+                    ta_ld32(tm_o + lane_off + half * (HD / 2) + c * 32, v);
 #pragma unroll
                     for (int i = 0; i < 32; i++) v[i] *= corr;
-                    ta_st32(tm_o + lane_off + half * 64 + c * 32, v);
+                    ta_st32(tm_o + lane_off + half * (HD / 2) + c * 32, v);
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
@@ -399,8 +402,9 @@ k_attention_tc(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
                 int s = j & 1;
                 ta_wait(&v_full[s], (j >> 1) & 1, gave_up);
                 int first_bad = hi + 1 - (t_lo + j) * TA_KEYS;
-                for (int e = half * 128 + r; e < (TA_KEYS - first_bad) * 16; e += 256) {
-                    int row = first_bad + (e >> 4), ch = e & 15;
+                constexpr int CH = HD / 8;                               // 16-byte chunks of a value row
+                for (int e = half * 128 + r; e < (TA_KEYS - first_bad) * CH; e += 256) {
+                    int row = first_bad + e / CH, ch = e % CH;
                     *reinterpret_cast<uint4*>(v_s + (s * 2 + (ch >> 3)) * HALF + row * 128 + (((ch & 7) ^ (row & 7)) << 4)) = make_uint4(0, 0, 0, 0);
                 }
             }
@@ -420,11 +424,11 @@ k_attention_tc(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
             l = x[r] + x[128 + r];
             const bool live = pr < rows_total;
             float inv = live ? 1.0f / l : 0.f;
-            __nv_bfloat16* dst = a.out + ((long long)(tok_base + (live ? pr : 0) / a.G) * a.H + (kvh * a.G + (live ? pr : 0) % a.G)) * TA_HD + half * 64;
+            __nv_bfloat16* dst = a.out + ((long long)(tok_base + (live ? pr : 0) / a.G) * a.H + (kvh * a.G + (live ? pr : 0) % a.G)) * HD + half * (HD / 2);
             float v[32];
 #pragma unroll 1
-            for (int c = 0; c < 2; c++) {
-                ta_ld32(tm_o + lane_off + half * 64 + c * 32, v);            // warp-wide: rows past the portion load too
+            for (int c = 0; c < NH; c++) {
+                ta_ld32(tm_o + lane_off + half * (HD / 2) + c * 32, v);      // warp-wide: rows past the portion load too
                 if (!live) continue;
 #pragma unroll
                 for (int i = 0; i < 32; i += 8) {
@@ -465,7 +469,7 @@ static TaEncodeFn ta_encode() {
 
 // 1 if this kernel takes the shape, 0 if not (the caller then uses the mma.sync kernel).
 XR_EXPORT int xr_attention_tc_supported(int H, int K, int hd, int page_size) {
-    if (hd != TA_HD || K < 1 || H % K != 0) return 0;
+    if ((hd != 64 && hd != 128) || K < 1 || H % K != 0) return 0;
     int G = H / K;
     if (G > 128 || (128 % G) != 0) return 0;
     if (page_size < 8 || (page_size & (page_size - 1)) != 0) return 0;
@@ -513,8 +517,10 @@ XR_EXPORT int xr_attention_tc(const void* q, void* out, const void* cache_base, 
     static bool configured = false;
     static bool p_tmem = true;                 // XRB200_ATTENTION_P_SMEM=1: P through shared memory (for comparisons)
     if (!configured) {
-        if (cudaFuncSetAttribute(k_attention_tc<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
-            cudaFuncSetAttribute(k_attention_tc<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+        if (cudaFuncSetAttribute(k_attention_tc<true, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
+            cudaFuncSetAttribute(k_attention_tc<false, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
+            cudaFuncSetAttribute(k_attention_tc<true, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
+            cudaFuncSetAttribute(k_attention_tc<false, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
             return XR_ERR_LAUNCH;
         const char* e = getenv("XRB200_ATTENTION_P_SMEM");
         p_tmem = !(e && e[0] && e[0] != '0');
@@ -522,7 +528,13 @@ XR_EXPORT int xr_attention_tc(const void* q, void* out, const void* cache_base, 
     }
     long long tiles = ((long long)max_seg_len * G + TA_ROWS - 1) / TA_ROWS;
     if (tiles > 0x7fffffffLL) return XR_ERR_ARG;
-    if (p_tmem) xr_launch(k_attention_tc<true>, dim3((unsigned)tiles, K, n_seg), dim3(TA_THREADS), SMEM, stream, qm, kvm, a);
-    else xr_launch(k_attention_tc<false>, dim3((unsigned)tiles, K, n_seg), dim3(TA_THREADS), SMEM, stream, qm, kvm, a);
+    const dim3 grid((unsigned)tiles, K, n_seg);
+    if (hd == 128) {
+        if (p_tmem) xr_launch(k_attention_tc<true, 128>, grid, dim3(TA_THREADS), SMEM, stream, qm, kvm, a);
+        else xr_launch(k_attention_tc<false, 128>, grid, dim3(TA_THREADS), SMEM, stream, qm, kvm, a);
+    } else {
+        if (p_tmem) xr_launch(k_attention_tc<true, 64>, grid, dim3(TA_THREADS), SMEM, stream, qm, kvm, a);
+        else xr_launch(k_attention_tc<false, 64>, grid, dim3(TA_THREADS), SMEM, stream, qm, kvm, a);
+    }
     return xr_launch_status();
 }
