@@ -109,3 +109,39 @@ def test_batch_does_not_change_a_request_in_32_bit(folders):
         outs.append(traces.collect(steps, res, vocab))
     for rid in reqs:
         assert np.array_equal(outs[0][rid], outs[1][rid]) and np.array_equal(outs[0][rid], outs[2][rid]), rid
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_batches_of_shrinking_size(folders, dtype):
+    """Thirteen requests decode together and end one after another.  Decode-only steps of more than eight requests
+    are filled up to a multiple of eight with rows of no request, so that the sizes of the steps repeat and their
+    CUDA graphs are few; the logits of the real rows are those of the plain implementation, and a request that
+    shares a step with filler rows is not changed by them."""
+    name = "B"
+    vocab = tiny.CONFIGS[name]["vocab_size"]
+    plain = PlainLlama(folders[name, dtype])
+    reqs = {f"q{i}": traces.random_tokens(900 + i, 18 + 3 * i, vocab) for i in range(13)}
+    tail = {rid: 4 + 2 * i for i, rid in enumerate(reqs)}                    # tokens decoded one by one, all different
+    steps, k = [], 0
+    for rid, toks in reqs.items():
+        head = len(toks) - tail[rid]
+        steps.append({"step": k, "entries": [{"id": rid, "tokens": toks[:head], "want": list(range(head))}], "end": []})
+        k += 1
+    at = {rid: len(t) - tail[rid] for rid, t in reqs.items()}
+    sizes = []
+    while any(at[rid] < len(reqs[rid]) for rid in reqs):
+        live = [rid for rid in reqs if at[rid] < len(reqs[rid])]
+        entries = [{"id": rid, "tokens": [reqs[rid][at[rid]]], "want": [0]} for rid in live]
+        for rid in live:
+            at[rid] += 1
+        steps.append({"step": k, "entries": entries, "end": [rid for rid in live if at[rid] == len(reqs[rid])]})
+        sizes.append(len(live))
+        k += 1
+    assert max(sizes) == 13 and len(set(sizes)) >= 10                        # the batch really shrinks step by step
+    res, eng = run(folders[name, dtype], dtype, steps, PAGE[name], max_requests=16)
+    got = traces.collect(steps, res, vocab)
+    for rid, toks in reqs.items():
+        traces.assert_close(got[rid], plain.logits(toks), dtype, f"shrinking batch/{dtype}/{rid}")
+    # sizes 9..13 all ran as steps of 16 rows: one graph for them, replayed
+    assert sum(1 for key in eng._graphs if key[0] == 16) <= 1 and not any(8 < key[0] < 16 for key in eng._graph_seen)
+    assert eng.graph_replays >= sum(1 for s in sizes if s > 8) - 2

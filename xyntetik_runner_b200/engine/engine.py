@@ -133,10 +133,12 @@ class Engine:
         max_req = p.max_request_tokens or min(plan.max_positions, n_pages * p.page_size)
         self.cache = CacheManager([g.spec for g in self.model.groups] or [], n_pages, p.page_size,
                                   p.max_requests, max_req)
-        # device arrays of keys and values: [page][layer in group][K|V][kv head][token in page][head_dim]
+        # device arrays of keys and values: [page][layer in group][K|V][kv head][token in page][head_dim].  One page
+        # more than the pool hands out: the rows that fill a decode step up to a repeating size write there.
         self.kv: List[torch.Tensor] = []
+        self._filler_page = n_pages
         for g in self.model.groups:
-            self.kv.append(torch.zeros((n_pages, g.n_layers, 2, g.kv_heads, p.page_size, g.head_dim),
+            self.kv.append(torch.zeros((n_pages + 1, g.n_layers, 2, g.kv_heads, p.page_size, g.head_dim),
                                        dtype=self.act_dtype, device=self.device))
         self._cache_layer: Dict[int, tuple] = {}
         for lay in self.model.layers:
@@ -161,6 +163,10 @@ class Engine:
         # addresses of the step's buffers, so any buffer that is made anew invalidates all graphs.
         self._graphs: Dict[tuple, object] = {}
         self._graph_ok = p.cuda_graphs and all(part.graph_safe for part in plan.parts())
+        # Decode-only steps of more than 8 requests are filled up to a multiple of 8 with rows of a request that does
+        # not exist (one token at position 0, keys and values in the spare page, logits dropped), so that a few graphs
+        # serve every batch size.  Not with per-request state: a filler row has no slot of its own.
+        self._fill_ok = self._graph_ok and not self.model.state_needs
         self._graph_seen: Dict[tuple, int] = {}
         self._buf_generation = 0
         self.graph_replays = 0
@@ -256,6 +262,8 @@ class Engine:
             logits = self._forward_graphed(ctx)
         else:
             logits = self._forward(ctx)
+        if ctx.real_rows != ctx.n_rows:
+            logits = logits[:ctx.real_rows]          # the filler rows' logits are nobody's
         for e in entries:
             self.cache.commit(e.request)
         self.steps_run += 1
@@ -264,9 +272,13 @@ class Engine:
     def _describe(self, entries: Sequence[StepEntry]) -> StepContext:
         """Flatten the batch and bring its description to the device in one copy."""
         cache = self.cache
-        S = len(entries)
+        S_real = len(entries)
         n = sum(len(e.tokens) for e in entries)
-        R = sum(len(e.want) for e in entries)
+        R_real = sum(len(e.want) for e in entries)
+        fill = 0
+        if self._fill_ok and S_real > 8 and n == S_real:
+            fill = min(-(-S_real // 8) * 8, max(self.params.max_requests, S_real)) - S_real
+        S, n, R = S_real + fill, n + fill, R_real + fill
         G = len(cache.groups)
         mp = cache.max_pages_per_request
         sizes = [n, n, n, max(R, 1), S, S, S, S] + [S * mp] * G
@@ -301,10 +313,18 @@ class Engine:
             max_kv = max(max_kv, p0 + m)
             decode_only &= (m == 1)
             at += m
+        for si in range(S_real, S):                  # filler rows: token 0 at position 0, wanted so that every row is
+            tok[at], pos[at], seg[at], rows[ri] = 0, 0, si, at
+            s_start[si], s_len[si], s_pos0[si], s_slot[si] = at, 1, 0, s_slot[0]
+            at += 1
+            ri += 1
         for g in range(G):
             bt = host[offs[8 + g]:offs[8 + g] + S * mp].reshape(S, mp)
             for si, e in enumerate(entries):
                 bt[si] = cache.block_table(g, e.request)
+            if fill:
+                bt[S_real:] = -1
+                bt[S_real:, 0] = self._filler_page
         dev = self._buf("step_description", (total,), torch.int32)
         dev.copy_(pinned[:total], non_blocking=True)
         self.h2d_bytes += total * 4
@@ -312,7 +332,7 @@ class Engine:
             self._pinned_done[slot_i] = torch.cuda.Event()
         self._pinned_done[slot_i].record()
         ctx = StepContext(self)
-        ctx.n, ctx.n_seg, ctx.n_rows = n, S, R
+        ctx.n, ctx.n_seg, ctx.n_rows, ctx.real_rows = n, S, R, R_real
         view = lambda i: dev[int(offs[i]):int(offs[i]) + sizes[i]]
         ctx.token_ids, ctx.positions, ctx.tok_seg, ctx.logit_rows = view(0), view(1), view(2), view(3)
         ctx.seg_start, ctx.seg_len, ctx.seg_pos0, ctx.seg_slot = view(4), view(5), view(6), view(7)
