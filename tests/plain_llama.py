@@ -260,6 +260,18 @@ class PlainLlama:
 # --------------------------------------------------------------------------
 # sampling (src/sample.c), on given logits
 # --------------------------------------------------------------------------
+def score_logprobs(logits: np.ndarray, tokens) -> np.ndarray:
+    """Teacher-forced scoring (src/main.c:1395-1405): for position i, lp = lg[tokens[i + 1]] - (max + log(sum exp(lg - max))),
+    maximum and result in float32, the sum in double.  logits: [T, vocab] of the whole sequence; returns T - 1 values."""
+    out = np.zeros(len(tokens) - 1, dtype=F32)
+    for i in range(len(tokens) - 1):
+        lg = logits[i].astype(F32)
+        mx = lg.max()
+        total = np.exp((lg - mx).astype(F32)).astype(np.float64).sum()
+        out[i] = F32(lg[tokens[i + 1]] - F32(mx + F32(np.log(F32(total)))))
+    return out
+
+
 def xorshift64(state: int):
     """src/sample.c:13-17."""
     m = (1 << 64) - 1

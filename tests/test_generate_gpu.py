@@ -222,6 +222,63 @@ def test_command_line(folders, tmp_path):
     assert out.returncode == 2 and "refused" in out.stderr
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_scoring(folders, dtype):
+    """Runner.score (the reference's --score): per-token log-probabilities of a prompt, whatever the portion."""
+    from plain_llama import score_logprobs
+    from xyntetik_runner_b200 import Runner
+    folder = folders["B", dtype]
+    toks = traces.random_tokens(31, 90, tiny.CONFIGS["B"]["vocab_size"])
+    plain_logits = PlainLlama(folder).logits(toks)
+    want = score_logprobs(plain_logits, toks)
+    r = Runner(folder, dtype=dtype, ctx=128, parallel=1, page_size=8)
+    # a log-probability is a logit minus a soft maximum of logits: twice the logits' own tolerance
+    tol = 2 * traces.TOL[dtype]["max_rel"] * float(np.abs(plain_logits).max())
+    for portion in (256, 7, 1):
+        got = np.array(r.score(toks, portion=portion), dtype=np.float32)
+        assert got.shape == want.shape and np.isfinite(got).all()
+        assert np.abs(got - want).max() <= tol, (portion, float(np.abs(got - want).max()))
+    assert not r.engine.cache.live_requests()
+    with pytest.raises(ValueError, match="at least 2 tokens"):
+        r.score([5])
+
+
+def test_rope_base_override(folders, tmp_path):
+    """Runner(rope_base=...) (the command line's --rope-base) is the model whose config.json names that base."""
+    import shutil
+    from xyntetik_runner_b200 import Runner
+    src = folders["A", "float32"]
+    dst = str(tmp_path / "other_base")
+    shutil.copytree(src, dst)
+    with open(os.path.join(dst, "config.json")) as f:
+        cfg = json.load(f)
+    cfg["rope_theta"] = 777.0
+    with open(os.path.join(dst, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    toks = traces.random_tokens(5, 40, tiny.CONFIGS["A"]["vocab_size"])
+    a = Runner(src, dtype="float32", ctx=64, rope_base=777.0).score(toks)
+    b = Runner(dst, dtype="float32", ctx=64).score(toks)
+    c = Runner(src, dtype="float32", ctx=64).score(toks)
+    assert a == b and a != c
+
+
+def test_command_line_scoring(folders):
+    from plain_llama import score_logprobs
+    folder = folders["A", "float32"]
+    ids = [1, 65, 66, 67, 68, 69, 70]
+    plain_logits = PlainLlama(folder).logits(ids)
+    want = score_logprobs(plain_logits, ids)
+    tol = 2 * traces.TOL["float32"]["max_rel"] * float(np.abs(plain_logits).max())
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "runner"), "-m", folder, "-p", "ABCDEF", "--score",
+                          "--dtype", "float32", "-c", "64"], capture_output=True, text=True, env=env, timeout=300)
+    assert out.returncode == 0, out.stderr
+    d = json.loads(out.stdout)
+    assert d["schema_version"] == "xyntetik.runner.score.v1" and d["tokens"] == ids and d["n_scored"] == 6
+    assert np.abs(np.array(d["logprobs"]) - want).max() <= tol
+    assert abs(d["nll_total"] + float(want.astype(np.float64).sum())) <= 6 * tol and abs(d["ppl"] - np.exp(d["nll_mean"])) <= 1e-4
+
+
 def test_trace_run_program(folders, tmp_path):
     """bin/trace_run as a user runs it: steps on standard input, <step>.f32 files and `done` lines out."""
     folder = folders["B", "bfloat16"]

@@ -486,6 +486,26 @@ def test_sampling_kernel_matches_the_plain_chain(V, one_block):
         assert got[r] == int(np.argmax(logits[r])), f"greedy row {r}"
 
 
+@pytest.mark.parametrize("V", [5, 387, 1027, 128256])
+def test_logprob_kernel(V):
+    """log softmax(row)[target] against float64, rows that start off a 16-byte boundary included (odd V)."""
+    from xyntetik_runner_b200 import kernels
+    rng = np.random.RandomState(V)
+    rows = 9
+    lg = (rng.randn(rows, V) * 4).astype(np.float32)
+    lg[2, :] = -3.5                                      # a flat row: log(1 / V)
+    lg[3, V // 2] = 60.0                                 # one value far above the rest
+    target = rng.randint(0, V, size=rows).astype(np.int32)
+    target[3] = V // 2
+    out = torch.full((rows,), 7.0, dtype=torch.float32, device=DEV)
+    kernels.logprob(torch.from_numpy(lg).to(DEV), torch.from_numpy(target).to(DEV), out)
+    x = lg.astype(np.float64)
+    m = x.max(axis=1, keepdims=True)
+    ref = x[np.arange(rows), target] - (m[:, 0] + np.log(np.exp(x - m).sum(axis=1)))
+    assert np.abs(out.cpu().numpy() - ref).max() <= 2e-6 * max(1.0, float(np.abs(ref).max()))
+    assert abs(float(out[2]) + np.log(V)) <= 1e-5 and abs(float(out[3])) <= 1e-6
+
+
 def test_sampling_kernel_follows_the_distribution():
     """Many draws at one row: empirical frequencies of the kept tokens match softmax(logits / temp)."""
     V, n = 50, 4000

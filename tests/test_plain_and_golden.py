@@ -77,3 +77,10 @@ def test_sampling_chain():
     x = 88172645463325252
     x = xorshift64(x)
     assert x == 8748534153485358512 and 0.0 <= uniform_from_state(x) < 1.0
+
+
+def test_score_logprobs():
+    from plain_llama import score_logprobs
+    lg = np.log(np.array([[0.5, 0.25, 0.25], [0.1, 0.2, 0.7], [1 / 3, 1 / 3, 1 / 3]], dtype=np.float64)).astype(np.float32) + 7.0
+    lp = score_logprobs(lg, [0, 1, 2])
+    assert lp.shape == (2,) and np.allclose(lp, np.log([0.25, 0.7]), atol=1e-6)

@@ -3,6 +3,7 @@
 Options keep the reference's names and meanings where it has them: -m (here a model FOLDER with
 config.json and model.safetensors), -p, -f, -n (default 256, -1 = until a stop id), -c, -b, -s (0 is
 refused), --temp (0 = greedy), --top-k, --top-p, --min-p, --repeat-penalty, --ignore-eos, --no-bos,
+--score (teacher-forced log-probabilities of the prompt, the reference's JSON), --parallel, --rope-base,
 --bench-json, -v/--version.  Tokenisation is outside the engine: a prompt is either ``ids:1,2,3`` or
 text taken byte by byte (token id = byte value), and the output is printed as ids (and as bytes where
 every id is one).
@@ -59,6 +60,10 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--min-p", type=float, default=0.0, help="min-p vs the top candidate (0 = off)")
     ap.add_argument("--repeat-penalty", type=float, default=1.0, help="penalty on recently emitted tokens (1 = off)")
     ap.add_argument("--ignore-eos", action="store_true", help="keep generating past stop ids")
+    ap.add_argument("--score", action="store_true",
+                    help="teacher-forced scoring: per-token log P(token|prefix) of the prompt as JSON; nothing is generated")
+    ap.add_argument("--parallel", type=int, default=1, help="request slots of the engine (default 1)")
+    ap.add_argument("--rope-base", type=float, default=None, help="override rope frequency base")
     ap.add_argument("--no-bos", action="store_true", help="do not prepend the BOS token")
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16",
                     help="bfloat16: serving kernels; float32: everything in true 32 bit")
@@ -94,7 +99,11 @@ def main(argv=None) -> int:
             return 0
     from .engine.runner import Runner
     t0 = time.perf_counter()
-    runner = Runner(args.model, dtype=args.dtype, ctx=args.ctx, batch=args.batch, parallel=1, page_size=args.page_size)
+    if args.parallel < 1 or (args.rope_base is not None and not args.rope_base > 0):
+        print("error: --parallel needs N >= 1 and --rope-base a positive base", file=sys.stderr)
+        return 2
+    runner = Runner(args.model, dtype=args.dtype, ctx=args.ctx, batch=args.batch, parallel=args.parallel,
+                    page_size=args.page_size, rope_base=args.rope_base)
     plan = runner.engine.plan
     print(f"loaded {args.model} in {time.perf_counter() - t0:.2f} s ({args.dtype})", file=sys.stderr)
     if args.bench_json:
@@ -122,6 +131,20 @@ def main(argv=None) -> int:
     if not ids:
         print("error: empty prompt", file=sys.stderr)
         return 2
+    if args.score:
+        # the reference's --score output (src/main.c:1377-1428)
+        import math
+        try:
+            lps = runner.score(ids, portion=min(args.batch, 256))
+        except ValueError as e:
+            print(f"error: --score: {e}", file=sys.stderr)
+            return 2
+        nll = -sum(lps)
+        mean = nll / len(lps)
+        print(json.dumps({"schema_version": "xyntetik.runner.score.v1", "n_tokens": len(ids), "n_scored": len(lps), "tokens": ids,
+                          "logprobs": [float(f"{x:.9g}") for x in lps], "nll_total": float(f"{nll:.9g}"),
+                          "nll_mean": float(f"{mean:.9g}"), "ppl": float(f"{math.exp(mean):.9g}")}))
+        return 0
     t0 = time.perf_counter()
     first = {}
     def on_token(rid, tok, done):

@@ -807,6 +807,42 @@ static bool smp_use_cluster(int rows, int V) {
     return rows <= 2 * (sms / SMP_CL);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Teacher-forced scoring: out[row] = log P(target[row]) under softmax(logits[row]), the arithmetic of the
+// reference's --score mode (src/main.c:1395-1405): float maximum, sum of expf(v - max) in double, float result
+// v[target] - (max + logf((float)sum)).  One block a row.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(SMP_THREADS)
+k_logprob(const float* logits, long long ld, int V, const int* target, float* out) {
+    xr_pdl_launch();
+    __shared__ double sh[40 + 64];
+    __shared__ float sh_f[33];
+    const int row = blockIdx.x, tid = threadIdx.x;
+    const float* lg = logits + (size_t)row * ld;
+    xr_pdl_wait();
+    float mx = -INFINITY;
+    smp_for_each(lg, V, [&](int, float v) { mx = fmaxf(mx, v); });
+    mx = xr_warp_max(mx);
+    if ((tid & 31) == 0) sh_f[tid >> 5] = mx;
+    __syncthreads();
+    if (tid < 32) { float t = sh_f[tid]; t = xr_warp_max(t); if (tid == 0) sh_f[32] = t; }
+    __syncthreads();
+    mx = sh_f[32];
+    double sum = 0.0;
+    smp_for_each(lg, V, [&](int, float v) { sum += (double)expf(v - mx); });
+    sum = blk_sum_d(sum, sh);
+    if (tid == 0) {
+        int t = target[row];
+        out[row] = (t >= 0 && t < V) ? lg[t] - (mx + logf((float)sum)) : -INFINITY;
+    }
+}
+
+XR_EXPORT int xr_logprob(const float* logits, long long ld, int rows, int V, const int* target, float* out, cudaStream_t stream) {
+    if (rows < 1 || V < 1 || ld < V) return XR_ERR_ARG;
+    xr_launch(k_logprob, dim3(rows), dim3(SMP_THREADS), 0, stream, logits, ld, V, target, out);
+    return xr_launch_status();
+}
+
 // scratch: [rows, V] floats when any row has temp > 0 (may be null when all rows are greedy).
 XR_EXPORT int xr_sample(const float* logits, long long ld, int rows, int V, const float* temp, const int* top_k,
                         const float* top_p, const float* min_p, const float* penalty, const float* draw,

@@ -14,6 +14,7 @@ from typing import Dict, List, Optional, Sequence, Union
 
 import torch
 
+from .. import kernels
 from ..sampling.sampler import DeviceSampler, SamplingParams
 from .engine import Engine, EngineParams, StepEntry, random_engine
 from .scheduler import Request, Scheduler, SchedulerParams, StepPlan
@@ -84,22 +85,34 @@ class Runner:
     def __init__(self, model: Optional[str] = None, *, config=None, random_seed: Optional[int] = None,
                  dtype: str = "bfloat16", ctx: Optional[int] = None, batch: int = 2048, parallel: int = 8,
                  max_tokens: Optional[int] = None, page_size: int = 64, prefill_chunk: Optional[int] = None,
-                 device: str = "cuda:0", engine: Optional[Engine] = None):
+                 device: str = "cuda:0", engine: Optional[Engine] = None, rope_base: Optional[float] = None):
         """model: folder with config.json + model.safetensors.  Or `config` (a typed configuration) with
         `random_seed` for seeded random weights.  ctx: longest request (default min(model limit, 4096), the
         reference's -c default, src/model.c:3075).  batch: token budget of a step (-b).  parallel: live
-        requests.  max_tokens: tokens the page pool holds (default parallel * ctx)."""
+        requests.  max_tokens: tokens the page pool holds (default parallel * ctx).  rope_base: use this
+        frequency base instead of the configuration's (--rope-base, src/model.c:282)."""
         if engine is None:
             if model is not None:
                 from ..config import registry
                 _, cfg = registry.load_config(model)
             else:
                 cfg = config
+            if rope_base is not None:
+                import dataclasses
+                if not hasattr(cfg, "rope_theta"):
+                    raise ValueError("rope_base: this architecture's configuration has no rope_theta")
+                cfg = dataclasses.replace(cfg, rope_theta=float(rope_base))
             model_limit = getattr(cfg, "max_position_embeddings", 4096)
             ctx = ctx or min(model_limit, 4096)
             ep = EngineParams(dtype=dtype, max_tokens=max_tokens or parallel * ctx, page_size=page_size,
                               max_requests=parallel, max_request_tokens=ctx, max_step_tokens=batch, device=device)
-            engine = Engine(model, ep) if model is not None else random_engine(cfg, random_seed or 0, ep)
+            if model is not None and rope_base is not None:
+                from ..weights.loader import FolderSource
+                engine = Engine(params=ep, config=cfg, source=FolderSource(model))
+            elif model is not None:
+                engine = Engine(model, ep)
+            else:
+                engine = random_engine(cfg, random_seed or 0, ep)
         self.engine = engine
         self.executor = EngineExecutor(engine)
         self.scheduler = Scheduler(engine.cache, self.executor,
@@ -149,3 +162,34 @@ class Runner:
             r = sch.finished.pop(rid)
             out.append(GenerationResult(list(r.generated), r.finish_reason, len(r.prompt), r.preemptions))
         return out[0] if single else out
+
+    def score(self, tokens: Sequence[int], portion: int = 256) -> List[float]:
+        """Teacher-forced scoring, the reference's --score mode (src/main.c:1344-1433): log P(tokens[i + 1] | tokens[:i + 1])
+        for every i, in float32 from the logits (float maximum, double sum of exponentials).  The tokens run through
+        the step function in portions of at most `portion` (each portion's logits are [portion, vocabulary] float32);
+        by the engine's exactness rule the result does not depend on the portion beyond rounding.  Nothing is sampled."""
+        toks = [int(t) for t in tokens]
+        if len(toks) < 2:
+            raise ValueError(f"scoring needs at least 2 tokens to score a transition (got {len(toks)})")
+        if len(toks) > self.engine.cache.max_pages_per_request * self.engine.cache.page_size:
+            raise ValueError(f"the prompt is {len(toks)} tokens, the context is "
+                             f"{self.engine.cache.max_pages_per_request * self.engine.cache.page_size}")
+        eng = self.engine
+        portion = max(1, min(portion, eng.params.max_step_tokens))
+        rid = ("score", self._next_id)
+        self._next_id += 1
+        out: List[float] = []
+        n_score = len(toks) - 1
+        target = torch.tensor(toks[1:], dtype=torch.int32, device=eng.device)
+        lp = torch.empty(n_score, dtype=torch.float32, device=eng.device)
+        try:
+            for at in range(0, n_score, portion):
+                m = min(portion, n_score - at)
+                logits = eng.step([StepEntry(rid, toks[at:at + m], list(range(m)))])
+                kernels.logprob(logits, target[at:at + m], lp[at:at + m])
+            out = lp.cpu().tolist()
+        finally:
+            if eng.is_live(rid):
+                eng.end(rid)
+        eng.check_status()
+        return out

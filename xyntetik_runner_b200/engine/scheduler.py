@@ -312,21 +312,29 @@ class Scheduler:
 
     def _plan_ahead(self, plan: StepPlan) -> Optional[StepPlan]:
         """The step after `plan`, if it can be told without `plan`'s tokens: `plan` decodes one token for every
-        live request, nobody can be admitted, and every request can take one more token afterwards.  Reserves its pages."""
+        live request, nobody can be admitted, and every request that goes on can take one more token afterwards.
+        A request that reaches its length with this step's token is known to end, whatever the token: it is left
+        out of the next step (unless somebody waits for its slot).  Reserves the next step's pages."""
         if plan.preempted or len(plan.entries) != len(self.live):
             return None
         if self.waiting and self.cache.has_free_slot():
             return None                      # the next plan may admit somebody: that is for plan() to decide
         limit = self.cache.max_pages_per_request * self.cache.page_size
+        going_on = []
         for e in plan.entries:
             r = e.request
             if e.count != 1 or not e.wants_token or r.status != LIVE or r.pending != 1 or r.sampler.needs_window():
                 return None
             if 0 < r.max_new_tokens <= len(r.generated) + 1 or len(r.tokens) + 1 >= limit:
-                return None                  # it ends with this step's token
+                if self.waiting:
+                    return None              # it ends with this step's token and its slot has a taker
+                continue
+            going_on.append(e)
+        if not going_on:
+            return None
         # pages: this step's reservations are committed (the executor's launch did that), one more token each
         taken = []
-        for e in plan.entries:
+        for e in going_on:
             if not self.cache.can_reserve(e.request.id, 1):
                 for rid in taken:
                     self.cache.cancel(rid)
@@ -334,7 +342,7 @@ class Scheduler:
             self.cache.reserve(e.request.id, 1)
             taken.append(e.request.id)
         nxt = StepPlan()
-        for e in plan.entries:
+        for e in going_on:
             nxt.entries.append(PlannedEntry(e.request, e.request.computed + e.count, 1, True))
         return nxt
 

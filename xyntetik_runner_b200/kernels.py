@@ -65,6 +65,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "xr_attention_tc": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _ll, _i, _i, _vp],
         "xr_sample": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
         "xr_sample_one_block": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
+        "xr_logprob": [_vp, _ll, _i, _i, _vp, _vp, _vp],
     }
     for name, args in sig.items():
         fn = getattr(L, name)
@@ -207,6 +208,16 @@ def sample(logits: torch.Tensor, temp, top_k, top_p, min_p, penalty, draw, recen
     _check(fn(logits.data_ptr(), logits.stride(0), rows, V, temp.data_ptr(), top_k.data_ptr(),
               top_p.data_ptr(), min_p.data_ptr(), penalty.data_ptr(), draw.data_ptr(), _ptr(recent),
               scratch.data_ptr(), out.data_ptr(), _stream()), "sample")
+    _count()
+
+
+def logprob(logits: torch.Tensor, target: torch.Tensor, out: torch.Tensor) -> None:
+    """out[i] = log softmax(logits[i])[target[i]] (float maximum, double sum of exponentials, float result)."""
+    _dev(target, out)
+    rows, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and logits.is_cuda
+    assert target.dtype == torch.int32 and target.numel() >= rows and out.dtype == torch.float32 and out.numel() >= rows
+    _check(lib().xr_logprob(logits.data_ptr(), logits.stride(0), rows, V, target.data_ptr(), out.data_ptr(), _stream()), "logprob")
     _count()
 
 
