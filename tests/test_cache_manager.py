@@ -122,3 +122,43 @@ def test_random_orders_keep_the_invariants(seed):
         m.close(rid)
     m.audit()
     assert m.free_pages() == [p.n_pages for p in m.pools]
+
+
+def test_describe_step_flattens_a_batch():
+    """The step description: ids, positions (from the requests' lengths), segments, wanted rows, block-table rows,
+    and filler segments at position 0 that point at the spare page."""
+    m = CacheManager([GroupSpec("full"), GroupSpec("w", window=6)], n_pages=16, page_size=4, max_requests=4, max_request_tokens=32)
+    for rid, held in (("a", 9), ("b", 0), ("c", 3)):
+        m.open(rid)
+        if held:
+            m.reserve(rid, held); m.commit(rid)
+    batch = [("c", [7], [0]), ("a", [11, 12, 13], [0, 2]), ("b", [5, 6], [])]
+    for rid, toks, _ in batch:
+        m.reserve(rid, len(toks))
+    i32 = np.int32
+    slots = np.array([m.slot_of(r) for r, _, _ in batch], dtype=i32)
+    counts = np.array([len(t) for _, t, _ in batch], dtype=i32)
+    tokens = np.array([x for _, t, _ in batch for x in t], dtype=i32)
+    want_counts = np.array([len(w) for _, _, w in batch], dtype=i32)
+    wants = np.array([x for _, _, w in batch for x in w], dtype=i32)
+    fill, n, S, R, mp = 2, 6 + 2, 3 + 2, 3 + 2, m.max_pages_per_request
+    arrs = [np.full(k, -9, dtype=i32) for k in (n, n, n, R, S, S, S, S)]
+    bts = [np.full((S, mp), -9, dtype=i32) for _ in m.groups]
+    max_kv = m.describe_step(slots, counts, tokens, want_counts, wants, fill, 16, [a.ctypes.data for a in arrs],
+                             [b.ctypes.data for b in bts])
+    tok, pos, seg, rows, s_start, s_len, s_pos0, s_slot = arrs
+    assert max_kv == 12
+    assert tok.tolist() == [7, 11, 12, 13, 5, 6, 0, 0] and pos.tolist() == [3, 9, 10, 11, 0, 1, 0, 0]
+    assert seg.tolist() == [0, 1, 1, 1, 2, 2, 3, 4] and rows.tolist() == [0, 1, 3, 6, 7]
+    assert s_start.tolist() == [0, 1, 4, 6, 7] and s_len.tolist() == [1, 3, 2, 1, 1] and s_pos0.tolist() == [3, 9, 0, 0, 0]
+    assert s_slot.tolist()[:3] == slots.tolist()
+    for g in range(2):
+        for si, (rid, _, _) in enumerate(batch):
+            assert (bts[g][si] == m.block_table(g, rid)).all()
+        assert (bts[g][3:, 0] == 16).all() and (bts[g][3:, 1:] == -1).all()
+    for rid, _, _ in batch:
+        m.commit(rid)
+    m.audit()
+    m.close("b")
+    with pytest.raises(CacheError):
+        m.describe_step(slots, counts, tokens, want_counts, wants, 0, 16, [a.ctypes.data for a in arrs], [b.ctypes.data for b in bts])

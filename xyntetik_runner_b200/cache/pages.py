@@ -10,16 +10,51 @@ own and every request a block table per group.  Pages go back to the pool
 when a request ends, and -- in a window group -- as soon as every position in
 the page lies behind the window of every query still to come.
 
-This module is host bookkeeping only (no tensors of keys or values): the
-device arrays are owned by ``cache.storage``.  Nothing here is zeroed on
-reuse; validity is the request's length.
+The bookkeeping itself is native code (``csrc/host/page_cache.cpp``, built into
+``libxrhost.so`` and called through ctypes); this module gives it its Python
+face: requests by id instead of by slot, exceptions instead of return codes.
+The block tables are numpy arrays made here and written by the library.  It is
+host bookkeeping only (no tensors of keys or values): the device arrays are
+owned by the engine.  Nothing is zeroed on reuse; validity is the request's
+length.
 """
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence
 
 import numpy as np
+
+from ..csrc import build as _build
+
+_OK, _OUT_OF_PAGES, _TOO_LONG = 0, 1, 2
+_host = None
+
+
+def host_lib() -> ctypes.CDLL:
+    """The native host library (compiled at first use; there is no other implementation)."""
+    global _host
+    if _host is None:
+        L = ctypes.CDLL(_build.host_library_path())
+        vp, i, ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+        sig = {
+            "xrh_pool_create": (vp, [i]), "xrh_pool_destroy": (None, [vp]), "xrh_pool_n_free": (i, [vp]),
+            "xrh_pool_take": (i, [vp]), "xrh_pool_give": (i, [vp, i]),
+            "xrh_cache_create": (vp, [i, vp, i, i, i, i, vp]), "xrh_cache_destroy": (None, [vp]),
+            "xrh_has_free_slot": (i, [vp]), "xrh_n_free": (i, [vp, i]), "xrh_high_water": (i, [vp, i]),
+            "xrh_pool_take_of": (i, [vp, i]), "xrh_pool_give_of": (i, [vp, i, i]),
+            "xrh_open": (i, [vp]), "xrh_close": (i, [vp, i]), "xrh_length": (ll, [vp, i]), "xrh_reserved": (ll, [vp, i]),
+            "xrh_pages_needed": (i, [vp, i, ll, vp]), "xrh_can_reserve": (i, [vp, i, ll]), "xrh_reserve": (i, [vp, i, ll]),
+            "xrh_commit": (i, [vp, i]), "xrh_cancel": (i, [vp, i]), "xrh_release_behind_window": (i, [vp, i]),
+            "xrh_audit": (i, [vp, ctypes.c_char_p, i]),
+            "xrh_describe": (ll, [vp, i] + [vp] * 5 + [i, i] + [vp] * 9),
+        }
+        for name, (res, args) in sig.items():
+            fn = getattr(L, name)
+            fn.restype, fn.argtypes = res, args
+        _host = L
+    return _host
 
 
 class OutOfPages(RuntimeError):
@@ -38,41 +73,56 @@ class GroupSpec:
 
 
 class PagePool:
-    """A stack of free page numbers with a record of who holds what."""
+    """A stack of free page numbers with a record of who holds what (a pool on its own)."""
 
     def __init__(self, n_pages: int):
         if n_pages < 1:
             raise CacheError("a pool needs at least one page")
         self.n_pages = n_pages
-        self._free: List[int] = list(range(n_pages - 1, -1, -1))   # pop() hands out 0 first
-        self._held = np.zeros(n_pages, dtype=bool)
+        self._L = host_lib()
+        self._h = self._L.xrh_pool_create(n_pages)
+        if not self._h:
+            raise MemoryError("the page pool could not be made")
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._L.xrh_pool_destroy(self._h)
+            self._h = None
 
     @property
     def n_free(self) -> int:
-        return len(self._free)
+        return self._L.xrh_pool_n_free(self._h)
 
     def take(self) -> int:
-        if not self._free:
+        p = self._L.xrh_pool_take(self._h)
+        if p < 0:
             raise OutOfPages("pool is empty")
-        p = self._free.pop()
-        self._held[p] = True
         return p
 
     def give(self, page: int) -> None:
-        if page < 0 or page >= self.n_pages or not self._held[page]:
+        if self._L.xrh_pool_give(self._h, int(page)) != _OK:
             raise CacheError(f"page {page} is given back but not held")
-        self._held[page] = False
-        self._free.append(page)
 
 
-class _Request:
-    __slots__ = ("slot", "length", "reserved", "first_live_page")
+class _GroupPool:
+    """One group's pool inside a cache manager."""
 
-    def __init__(self, slot: int, n_groups: int):
-        self.slot = slot
-        self.length = 0            # tokens whose keys are in the cache
-        self.reserved = 0          # tokens reserved beyond `length` for the step in flight
-        self.first_live_page = [0] * n_groups   # per group: table entries below this were released
+    def __init__(self, manager: "CacheManager", g: int, n_pages: int):
+        self._m, self._g, self.n_pages = manager, g, n_pages
+
+    @property
+    def n_free(self) -> int:
+        return self._m._L.xrh_n_free(self._m._h, self._g)
+
+    def take(self) -> int:
+        p = self._m._L.xrh_pool_take_of(self._m._h, self._g)
+        if p < 0:
+            raise OutOfPages("pool is empty")
+        return p
+
+    def give(self, page: int) -> None:
+        if self._m._L.xrh_pool_give_of(self._m._h, self._g, int(page)) != _OK:
+            raise CacheError(f"page {page} is given back but not held")
 
 
 class CacheManager:
@@ -88,202 +138,138 @@ class CacheManager:
                  max_requests: int, max_request_tokens: int):
         if page_size < 1:
             raise CacheError("page_size must be >= 1")
+        if n_pages < 1:
+            raise CacheError("a pool needs at least one page")
         self.groups = list(groups)
         self.page_size = page_size
         self.max_requests = max_requests
         self.max_pages_per_request = -(-max_request_tokens // page_size)
-        self.pools = [PagePool(n_pages) for _ in self.groups]
-        # block tables: [group][slot, page index] -> page number, -1 where none is held
-        self.tables = [np.full((max_requests, self.max_pages_per_request), -1, dtype=np.int32)
-                       for _ in self.groups]
-        self._free_slots: List[int] = list(range(max_requests - 1, -1, -1))
-        self._requests: Dict[object, _Request] = {}
+        # block tables: [group][slot, page index] -> page number, -1 where none is held (written by the library)
+        self.tables = [np.full((max_requests, self.max_pages_per_request), -1, dtype=np.int32) for _ in self.groups]
+        G = len(self.groups)
+        self._L = host_lib()
+        windows = (ctypes.c_int * max(G, 1))(*[-1 if g.window is None else int(g.window) for g in self.groups])
+        self._table_ptrs = (ctypes.c_void_p * max(G, 1))(*[t.ctypes.data for t in self.tables])
+        self._h = self._L.xrh_cache_create(G, windows, n_pages, page_size, max_requests, self.max_pages_per_request,
+                                           self._table_ptrs)
+        if not self._h:
+            raise CacheError("the cache manager could not be made (sizes must be positive)")
+        self.pools = [_GroupPool(self, g, n_pages) for g in range(G)]
+        self._slots: Dict[object, int] = {}                         # request id -> slot
         self.generation = np.zeros(max_requests, dtype=np.int64)   # bumped when a slot is assigned
-        self.high_water = [0] * len(self.groups)
+        self._need = (ctypes.c_int * max(G, 1))()
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._L.xrh_cache_destroy(self._h)
+            self._h = None
+
+    @property
+    def high_water(self) -> List[int]:
+        return [self._L.xrh_high_water(self._h, g) for g in range(len(self.groups))]
 
     # ---- requests and slots ------------------------------------------------
     def has_free_slot(self) -> bool:
-        return bool(self._free_slots)
+        return bool(self._L.xrh_has_free_slot(self._h))
 
     def open(self, request_id) -> int:
-        if request_id in self._requests:
+        if request_id in self._slots:
             raise CacheError(f"request {request_id!r} is already open")
-        if not self._free_slots:
+        slot = self._L.xrh_open(self._h)
+        if slot < 0:
             raise OutOfPages("no free request slot")
-        slot = self._free_slots.pop()
-        self._requests[request_id] = _Request(slot, len(self.groups))
+        self._slots[request_id] = slot
         self.generation[slot] += 1
         return slot
 
     def slot_of(self, request_id) -> int:
-        return self._req(request_id).slot
+        return self._slot(request_id)
 
     def length(self, request_id) -> int:
-        return self._req(request_id).length
+        return self._L.xrh_length(self._h, self._slot(request_id))
 
     def is_open(self, request_id) -> bool:
-        return request_id in self._requests
+        return request_id in self._slots
 
     def live_requests(self):
-        return list(self._requests)
+        return list(self._slots)
 
-    def _req(self, request_id) -> _Request:
+    def _slot(self, request_id) -> int:
         try:
-            return self._requests[request_id]
+            return self._slots[request_id]
         except KeyError:
             raise CacheError(f"request {request_id!r} is not open") from None
 
     # ---- pages ---------------------------------------------------------------
-    def _first_needed_page(self, g: int, query_pos: int) -> int:
-        """Lowest page index that a query at `query_pos` (or any later one) can read in group g."""
-        w = self.groups[g].window
-        if w is None:
-            return 0
-        first_key = max(0, query_pos - w + 1)
-        return first_key // self.page_size
-
     def pages_needed(self, request_id, n_new: int) -> List[int]:
         """Pages per group that reserving `n_new` more tokens would take (after releasing
         what the window has passed)."""
-        r = self._req(request_id)
-        start = r.length + r.reserved
-        end = start + n_new
-        out = []
-        for g in range(len(self.groups)):
-            have_upto = -(-start // self.page_size)           # table entries [first_live, have_upto) exist
-            want_upto = -(-end // self.page_size)
-            first = max(self._first_needed_page(g, start), r.first_live_page[g])
-            lo = max(have_upto, first)
-            out.append(max(0, want_upto - lo))
-        return out
+        self._L.xrh_pages_needed(self._h, self._slot(request_id), n_new, self._need)
+        return [self._need[g] for g in range(len(self.groups))]
 
     def free_pages(self) -> List[int]:
-        return [p.n_free for p in self.pools]
+        return [self._L.xrh_n_free(self._h, g) for g in range(len(self.groups))]
 
     def can_reserve(self, request_id, n_new: int) -> bool:
-        r = self._req(request_id)
-        if r.length + r.reserved + n_new > self.max_pages_per_request * self.page_size:
-            return False
-        need = self.pages_needed(request_id, n_new)
-        # pages that the window lets go before this step count as free
-        rel = self._releasable(r, r.length + r.reserved)
-        return all(need[g] <= self.pools[g].n_free + rel[g] for g in range(len(self.groups)))
-
-    def _releasable(self, r: _Request, query_pos: int) -> List[int]:
-        out = []
-        for g in range(len(self.groups)):
-            first = self._first_needed_page(g, query_pos)
-            held_upto = -(-(r.length + r.reserved) // self.page_size)
-            out.append(max(0, min(first, held_upto) - r.first_live_page[g]))
-        return out
+        """Whether `reserve` would succeed; pages that the window lets go before this step count as free."""
+        return bool(self._L.xrh_can_reserve(self._h, self._slot(request_id), n_new))
 
     def release_behind_window(self, request_id) -> int:
         """Give back the pages no query from position `length` on can read.  Returns how many."""
-        r = self._req(request_id)
-        n = 0
-        for g in range(len(self.groups)):
-            first = min(self._first_needed_page(g, r.length + r.reserved),
-                        -(-(r.length + r.reserved) // self.page_size))
-            tab = self.tables[g][r.slot]
-            for i in range(r.first_live_page[g], first):
-                if tab[i] >= 0:
-                    self.pools[g].give(int(tab[i]))
-                    tab[i] = -1
-                    n += 1
-            r.first_live_page[g] = max(r.first_live_page[g], first)
-        return n
+        return self._L.xrh_release_behind_window(self._h, self._slot(request_id))
 
     def reserve(self, request_id, n_new: int) -> None:
         """Take the pages that the request's next `n_new` tokens need, in every group, or none."""
         if n_new < 1:
             raise CacheError("reserve needs n_new >= 1")
-        r = self._req(request_id)
-        start = r.length + r.reserved
-        if start + n_new > self.max_pages_per_request * self.page_size:
+        code = self._L.xrh_reserve(self._h, self._slot(request_id), n_new)
+        if code == _TOO_LONG:
             raise OutOfPages(f"request {request_id!r} would exceed {self.max_pages_per_request} pages")
-        if not self.can_reserve(request_id, n_new):
+        if code == _OUT_OF_PAGES:
             raise OutOfPages(f"request {request_id!r}: {self.pages_needed(request_id, n_new)} pages needed, "
                              f"{self.free_pages()} free")
-        self.release_behind_window(request_id)
-        end = start + n_new
-        for g in range(len(self.groups)):
-            have_upto = -(-start // self.page_size)
-            want_upto = -(-end // self.page_size)
-            lo = max(have_upto, r.first_live_page[g])
-            tab = self.tables[g][r.slot]
-            for i in range(lo, want_upto):
-                tab[i] = self.pools[g].take()
-            used = self.pools[g].n_pages - self.pools[g].n_free
-            self.high_water[g] = max(self.high_water[g], used)
-        r.reserved += n_new
+        if code != _OK:
+            raise CacheError(f"reserve({request_id!r}, {n_new}) failed with code {code}")
 
     def commit(self, request_id) -> None:
         """The step ran: reserved tokens now count as held."""
-        r = self._req(request_id)
-        r.length += r.reserved
-        r.reserved = 0
+        self._L.xrh_commit(self._h, self._slot(request_id))
 
     def cancel(self, request_id) -> None:
         """The planned step did not run: give back pages that only the reservation needed."""
-        r = self._req(request_id)
-        if r.reserved == 0:
-            return
-        keep_upto = -(-r.length // self.page_size)
-        had_upto = -(-(r.length + r.reserved) // self.page_size)
-        for g in range(len(self.groups)):
-            tab = self.tables[g][r.slot]
-            for i in range(max(keep_upto, r.first_live_page[g]), had_upto):
-                if tab[i] >= 0:
-                    self.pools[g].give(int(tab[i]))
-                    tab[i] = -1
-        r.reserved = 0
+        self._L.xrh_cancel(self._h, self._slot(request_id))
 
     def close(self, request_id) -> int:
         """The request ended: all its pages and its slot go back.  Returns the slot."""
-        r = self._req(request_id)
-        upto = -(-(r.length + r.reserved) // self.page_size)
-        for g in range(len(self.groups)):
-            tab = self.tables[g][r.slot]
-            for i in range(r.first_live_page[g], upto):
-                if tab[i] >= 0:
-                    self.pools[g].give(int(tab[i]))
-            tab[:] = -1
-        del self._requests[request_id]
-        self._free_slots.append(r.slot)
-        return r.slot
+        slot = self._slot(request_id)
+        self._L.xrh_close(self._h, slot)
+        del self._slots[request_id]
+        return slot
 
     def block_table(self, g: int, request_id) -> np.ndarray:
-        return self.tables[g][self._req(request_id).slot]
+        return self.tables[g][self._slot(request_id)]
+
+    # ---- the step description ---------------------------------------------------
+    def describe_step(self, slots: np.ndarray, counts: np.ndarray, tokens: np.ndarray, want_counts: np.ndarray,
+                      wants: np.ndarray, fill: int, filler_page: int, out: Sequence[int], block_tables: Sequence[int]) -> int:
+        """Flatten a batch into the arrays the kernels read (see ``xrh_describe`` in csrc/host/page_cache.cpp).
+        slots, counts, want_counts: int32 per segment; tokens, wants: int32, all segments' one after another;
+        out: addresses of the eight int32 arrays (token ids, positions, token -> segment, wanted rows, and per
+        segment first row, length, first position, slot); block_tables: one address per group.  Positions are the
+        requests' lengths as they are now.  Returns the longest context among the segments."""
+        bt = (ctypes.c_void_p * max(len(block_tables), 1))(*block_tables)
+        r = self._L.xrh_describe(self._h, len(slots), slots.ctypes.data, counts.ctypes.data, tokens.ctypes.data,
+                                 want_counts.ctypes.data, wants.ctypes.data, fill, filler_page, *out, bt)
+        if r < 0:
+            raise CacheError(f"describe_step: a request of the step is not open (code {r})")
+        return int(r)
 
     # ---- checking (tests and debugging) ---------------------------------------
     def audit(self) -> None:
         """Raise if a page is lost, held twice, or a table disagrees with a request's length."""
-        for g, pool in enumerate(self.pools):
-            seen = np.zeros(pool.n_pages, dtype=np.int32)
-            for rid, r in self._requests.items():
-                tab = self.tables[g][r.slot]
-                upto = -(-(r.length + r.reserved) // self.page_size)
-                for i, p in enumerate(tab):
-                    if p >= 0:
-                        if not (r.first_live_page[g] <= i < upto):
-                            raise CacheError(f"group {g} request {rid!r}: page at index {i} outside its live range")
-                        seen[p] += 1
-                    elif r.first_live_page[g] <= i < upto:
-                        raise CacheError(f"group {g} request {rid!r}: hole at index {i}")
-            if (seen > 1).any():
-                raise CacheError(f"group {g}: page {int(np.argmax(seen > 1))} is in two tables")
-            free = np.zeros(pool.n_pages, dtype=np.int32)
-            for p in pool._free:
-                free[p] += 1
-            if (free > 1).any():
-                raise CacheError(f"group {g}: page {int(np.argmax(free > 1))} is free twice")
-            if ((seen + free) != 1).any():
-                bad = int(np.argmax((seen + free) != 1))
-                raise CacheError(f"group {g}: page {bad} is {'lost' if seen[bad] + free[bad] == 0 else 'both free and held'}")
-            if not (pool._held == (seen == 1)).all():
-                raise CacheError(f"group {g}: held flags disagree with the tables")
-        slots = [r.slot for r in self._requests.values()]
-        if len(set(slots)) != len(slots) or set(slots) & set(self._free_slots):
+        msg = ctypes.create_string_buffer(256)
+        if self._L.xrh_audit(self._h, msg, len(msg)) != 0:
+            raise CacheError(msg.value.decode())
+        slots = list(self._slots.values())
+        if len(set(slots)) != len(slots):
             raise CacheError("a request slot is used twice")
-        if len(slots) + len(self._free_slots) != self.max_requests:
-            raise CacheError("a request slot is lost")

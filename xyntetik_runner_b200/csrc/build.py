@@ -1,4 +1,5 @@
-"""Compiling the CUDA sources of this folder into one shared library for sm_100a.
+"""Compiling the CUDA sources of this folder into one shared library for sm_100a, and the C++ sources under
+host/ into a second one (see the end of this file).
 
 The library is plain CUDA with `extern "C"` launchers (no Python or torch
 headers), so a file compiles in seconds.  It is built in-tree
@@ -159,5 +160,63 @@ def _compile(out_dir: str, digest: str, verbose: bool) -> str:
     return lib
 
 
+# ---------------------------------------------------------------------------------------------
+# The host library: the C++ sources under host/ (page pools, block tables, step descriptions; no CUDA) built with
+# the C++ compiler into libxrhost.so, by the same rules: in-tree, rebuilt when a source changes, no fallback.
+# ---------------------------------------------------------------------------------------------
+HOST_DIR = os.path.join(HERE, "host")
+HOST_LIB = "libxrhost.so"
+HOST_FLAGS = ["-O2", "-std=c++17", "-Wall", "-Wextra", "-shared", "-fPIC", "-fvisibility=hidden"]
+
+
+def host_sources() -> List[str]:
+    return sorted(f for f in os.listdir(HOST_DIR) if f.endswith(".cpp"))
+
+
+def find_cxx() -> str:
+    for cand in (os.environ.get("XRB200_CXX"), os.environ.get("CXX"), "g++", "c++", "clang++"):
+        path = shutil.which(cand) if cand else None
+        if path:
+            return path
+    raise BuildError("no C++ compiler found (looked at $XRB200_CXX, $CXX, g++, c++, clang++); "
+                     "the host library cannot be built and there is no other path")
+
+
+def host_library_path(build: bool = True) -> str:
+    """Path of an up-to-date host library; compiles it if needed (and allowed)."""
+    h = hashlib.sha256()
+    h.update(" ".join(HOST_FLAGS).encode())
+    for f in host_sources():
+        h.update(f.encode())
+        with open(os.path.join(HOST_DIR, f), "rb") as fh:
+            h.update(fh.read())
+    digest = h.hexdigest()
+    for d in _build_dirs():
+        lib, stamp = os.path.join(d, HOST_LIB), os.path.join(d, "digest_host.txt")
+        if os.path.isfile(lib) and os.path.isfile(stamp):
+            with open(stamp) as f:
+                if f.read().strip() == digest:
+                    return lib
+    if not build:
+        raise BuildError("the host library is not built")
+    for d in _build_dirs():
+        if not _writable(d):
+            continue
+        tmp_lib = os.path.join(d, f".{HOST_LIB}.{os.getpid()}")
+        cmd = [find_cxx()] + HOST_FLAGS + ["-o", tmp_lib] + [os.path.join(HOST_DIR, f) for f in host_sources()]
+        env = dict(os.environ)
+        env.setdefault("TMPDIR", d)
+        r = subprocess.run(cmd, capture_output=True, text=True, env=env)
+        if r.returncode != 0:
+            raise BuildError(f"the C++ compiler failed on the host library:\n{r.stdout}\n{r.stderr}")
+        lib = os.path.join(d, HOST_LIB)
+        os.replace(tmp_lib, lib)
+        with open(os.path.join(d, "digest_host.txt"), "w") as f:
+            f.write(digest + "\n")
+        return lib
+    raise BuildError("no writable folder for the build: " + ", ".join(_build_dirs()))
+
+
 if __name__ == "__main__":
     print(library_path())
+    print(host_library_path())

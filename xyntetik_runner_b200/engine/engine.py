@@ -273,12 +273,20 @@ class Engine:
         """Flatten the batch and bring its description to the device in one copy."""
         cache = self.cache
         S_real = len(entries)
-        n = sum(len(e.tokens) for e in entries)
-        R_real = sum(len(e.want) for e in entries)
+        i32 = np.int32
+        counts = np.fromiter((len(e.tokens) for e in entries), i32, S_real)
+        want_counts = np.fromiter((len(e.want) for e in entries), i32, S_real)
+        slots = np.fromiter((cache.slot_of(e.request) for e in entries), i32, S_real)
+        n_real, R_real = int(counts.sum()), int(want_counts.sum())
+        if n_real == S_real:
+            tokens = np.fromiter((e.tokens[0] for e in entries), np.int64, S_real).astype(i32)
+        else:
+            tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries]).astype(i32)
+        wants = np.fromiter((w for e in entries for w in e.want), i32, R_real)
         fill = 0
-        if self._fill_ok and S_real > 8 and n == S_real:
+        if self._fill_ok and S_real > 8 and n_real == S_real:
             fill = min(-(-S_real // 8) * 8, max(self.params.max_requests, S_real)) - S_real
-        S, n, R = S_real + fill, n + fill, R_real + fill
+        S, n, R = S_real + fill, n_real + fill, R_real + fill
         G = len(cache.groups)
         mp = cache.max_pages_per_request
         sizes = [n, n, n, max(R, 1), S, S, S, S] + [S * mp] * G
@@ -293,38 +301,11 @@ class Engine:
         pinned = self._pinned[slot_i]
         host = pinned.numpy()
         tok, pos, seg, rows, s_start, s_len, s_pos0, s_slot = (host[offs[i]:offs[i] + sizes[i]] for i in range(8))
-        at, ri, max_kv = 0, 0, 0
-        decode_only = True
-        for si, e in enumerate(entries):
-            m = len(e.tokens)
-            p0 = cache.length(e.request)
-            if m == 1:
-                tok[at] = e.tokens[0]
-                pos[at] = p0
-                seg[at] = si
-            else:
-                tok[at:at + m] = np.asarray(e.tokens, dtype=np.int64).astype(np.int32)
-                pos[at:at + m] = np.arange(p0, p0 + m, dtype=np.int32)
-                seg[at:at + m] = si
-            for w in e.want:
-                rows[ri] = at + w
-                ri += 1
-            s_start[si], s_len[si], s_pos0[si], s_slot[si] = at, m, p0, cache.slot_of(e.request)
-            max_kv = max(max_kv, p0 + m)
-            decode_only &= (m == 1)
-            at += m
-        for si in range(S_real, S):                  # filler rows: token 0 at position 0, wanted so that every row is
-            tok[at], pos[at], seg[at], rows[ri] = 0, 0, si, at
-            s_start[si], s_len[si], s_pos0[si], s_slot[si] = at, 1, 0, s_slot[0]
-            at += 1
-            ri += 1
-        for g in range(G):
-            bt = host[offs[8 + g]:offs[8 + g] + S * mp].reshape(S, mp)
-            for si, e in enumerate(entries):
-                bt[si] = cache.block_table(g, e.request)
-            if fill:
-                bt[S_real:] = -1
-                bt[S_real:, 0] = self._filler_page
+        # the flattening itself is native (csrc/host/page_cache.cpp: xrh_describe); it writes into the pinned buffer
+        base = host.ctypes.data
+        max_kv = cache.describe_step(slots, counts, tokens, want_counts, wants, fill, self._filler_page,
+                                     [base + 4 * int(offs[i]) for i in range(8)], [base + 4 * int(offs[8 + g]) for g in range(G)])
+        decode_only = n_real == S_real
         dev = self._buf("step_description", (total,), torch.int32)
         dev.copy_(pinned[:total], non_blocking=True)
         self.h2d_bytes += total * 4
