@@ -113,6 +113,8 @@ def rope_inv_freq(theta: float, rope_dim: int, scaling=None) -> np.ndarray:
     if scaling is None:
         return inv
     kind = scaling.get("rope_type", scaling.get("type"))
+    if kind == "linear":                       # every frequency divided by the factor, in float32 (src/model.c:361-362)
+        return (inv / F32(scaling["factor"])).astype(F32)
     if kind != "llama3":
         raise ValueError(f"rope_scaling {kind}")
     factor = float(scaling["factor"])

@@ -186,3 +186,11 @@ def test_rope_table_matches_the_plain_formula():
     ratio = plain / scaled
     assert ratio[0] == 1.0 and abs(ratio[-1] - 8.0) < 1e-5 and (np.diff(ratio) >= -1e-6).all()
     assert ((ratio > 1.001) & (ratio < 7.999)).any()          # the interpolated band is exercised
+    # linear scaling: every frequency divided by the factor
+    lin = LlamaConfig.from_dict(dict(tiny.TINY_A, rope_scaling={"type": "linear", "factor": 2.5}))
+    assert lin.rope_scaling.rope_type == "linear" and LlamaConfig.from_dict(lin.to_dict()) == lin
+    mine = Rope(lin.head_dim, lin.rope_theta, scaling=lin.rope_scaling).inv_freq_host
+    assert np.array_equal(mine, rope_inv_freq(lin.rope_theta, lin.head_dim, {"type": "linear", "factor": 2.5}))
+    assert np.allclose(Rope(lin.head_dim, lin.rope_theta).inv_freq_host / mine, 2.5, rtol=1e-6)
+    with pytest.raises(ConfigError, match="factor"):
+        LlamaConfig.from_dict(dict(tiny.TINY_A, rope_scaling={"type": "linear", "factor": 0.0}))

@@ -260,6 +260,17 @@ def test_rope_base_override(folders, tmp_path):
     b = Runner(dst, dtype="float32", ctx=64).score(toks)
     c = Runner(src, dtype="float32", ctx=64).score(toks)
     assert a == b and a != c
+    # --rope-scale: forced linear scaling is the model whose config.json asks for it, and the plain implementation's
+    from plain_llama import score_logprobs
+    cfg["rope_theta"] = tiny.CONFIGS["A"]["rope_theta"]
+    cfg["rope_scaling"] = {"rope_type": "linear", "factor": 3.0}
+    with open(os.path.join(dst, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    d = Runner(src, dtype="float32", ctx=64, rope_scale=3.0).score(toks)
+    e = Runner(dst, dtype="float32", ctx=64).score(toks)
+    plain_logits = PlainLlama(dst).logits(toks)
+    tol = 2 * traces.TOL["float32"]["max_rel"] * float(np.abs(plain_logits).max())
+    assert d == e and d != c and np.abs(np.array(e) - score_logprobs(plain_logits, toks)).max() <= tol
 
 
 def test_command_line_scoring(folders):

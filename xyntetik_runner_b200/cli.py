@@ -3,7 +3,7 @@
 Options keep the reference's names and meanings where it has them: -m (here a model FOLDER with
 config.json and model.safetensors), -p, -f, -n (default 256, -1 = until a stop id), -c, -b, -s (0 is
 refused), --temp (0 = greedy), --top-k, --top-p, --min-p, --repeat-penalty, --ignore-eos, --no-bos,
---score (teacher-forced log-probabilities of the prompt, the reference's JSON), --parallel, --rope-base,
+--score (teacher-forced log-probabilities of the prompt, the reference's JSON), --parallel, --rope-base, --rope-scale,
 --bench-json, -v/--version.  Tokenisation is outside the engine: a prompt is either ``ids:1,2,3`` or
 text taken byte by byte (token id = byte value), and the output is printed as ids (and as bytes where
 every id is one).
@@ -64,6 +64,7 @@ def build_parser() -> argparse.ArgumentParser:
                     help="teacher-forced scoring: per-token log P(token|prefix) of the prompt as JSON; nothing is generated")
     ap.add_argument("--parallel", type=int, default=1, help="request slots of the engine (default 1)")
     ap.add_argument("--rope-base", type=float, default=None, help="override rope frequency base")
+    ap.add_argument("--rope-scale", type=float, default=None, help="force linear rope position scaling by F")
     ap.add_argument("--no-bos", action="store_true", help="do not prepend the BOS token")
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16",
                     help="bfloat16: serving kernels; float32: everything in true 32 bit")
@@ -99,11 +100,12 @@ def main(argv=None) -> int:
             return 0
     from .engine.runner import Runner
     t0 = time.perf_counter()
-    if args.parallel < 1 or (args.rope_base is not None and not args.rope_base > 0):
-        print("error: --parallel needs N >= 1 and --rope-base a positive base", file=sys.stderr)
+    if args.parallel < 1 or (args.rope_base is not None and not args.rope_base > 0) or \
+            (args.rope_scale is not None and not args.rope_scale > 0):
+        print("error: --parallel needs N >= 1, --rope-base a positive base, --rope-scale a positive factor", file=sys.stderr)
         return 2
     runner = Runner(args.model, dtype=args.dtype, ctx=args.ctx, batch=args.batch, parallel=args.parallel,
-                    page_size=args.page_size, rope_base=args.rope_base)
+                    page_size=args.page_size, rope_base=args.rope_base, rope_scale=args.rope_scale)
     plan = runner.engine.plan
     print(f"loaded {args.model} in {time.perf_counter() - t0:.2f} s ({args.dtype})", file=sys.stderr)
     if args.bench_json:

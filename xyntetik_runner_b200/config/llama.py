@@ -24,17 +24,16 @@ class ConfigError(ValueError):
 
 @dataclass(frozen=True)
 class RopeScaling:
-    """``rope_scaling`` of type ``llama3``: per-frequency divisors.
-
-    The reference consumes these as a ``rope_freqs.weight`` tensor written by
-    the converter (src/model.c:291-297); here they are computed from the four
-    numbers below when the position table is built.
+    """``rope_scaling``.  Type ``llama3``: per-frequency divisors.  The reference consumes these as a
+    ``rope_freqs.weight`` tensor written by the converter (src/model.c:291-297); here they are computed
+    from the four numbers below when the position table is built.  Type ``linear``: every frequency is
+    divided by ``factor`` (src/model.c:361-362); the other three numbers are unused.
     """
     rope_type: str
     factor: float
-    low_freq_factor: float
-    high_freq_factor: float
-    original_max_position_embeddings: int
+    low_freq_factor: float = 1.0
+    high_freq_factor: float = 4.0
+    original_max_position_embeddings: int = 0
 
 
 @dataclass(frozen=True)
@@ -130,8 +129,16 @@ class LlamaConfig:
             kind = rs.get("rope_type", rs.get("type"))
             if kind == "default":
                 rs = None                     # "default" names the unscaled table
+            elif kind == "linear":
+                try:
+                    scaling = RopeScaling(rope_type="linear", factor=float(rs["factor"]))
+                except KeyError as e:
+                    raise ConfigError(f"config.json: rope_scaling lacks {e}") from None
+                if not scaling.factor > 0:
+                    raise ConfigError("config.json: rope_scaling factor must be positive")
+                rs = None
             elif kind != "llama3":
-                raise ConfigError(f"config.json: rope_scaling type '{kind}' is not supported (only 'llama3')")
+                raise ConfigError(f"config.json: rope_scaling type '{kind}' is not supported (only 'llama3' and 'linear')")
         if rs is not None:
             try:
                 scaling = RopeScaling(
@@ -248,7 +255,7 @@ class LlamaConfig:
         }
         if self.rope_scaling is not None:
             rs = self.rope_scaling
-            d["rope_scaling"] = {
+            d["rope_scaling"] = {"rope_type": "linear", "factor": rs.factor} if rs.rope_type == "linear" else {
                 "rope_type": rs.rope_type, "factor": rs.factor,
                 "low_freq_factor": rs.low_freq_factor, "high_freq_factor": rs.high_freq_factor,
                 "original_max_position_embeddings": rs.original_max_position_embeddings,

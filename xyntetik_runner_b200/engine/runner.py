@@ -85,12 +85,14 @@ class Runner:
     def __init__(self, model: Optional[str] = None, *, config=None, random_seed: Optional[int] = None,
                  dtype: str = "bfloat16", ctx: Optional[int] = None, batch: int = 2048, parallel: int = 8,
                  max_tokens: Optional[int] = None, page_size: int = 64, prefill_chunk: Optional[int] = None,
-                 device: str = "cuda:0", engine: Optional[Engine] = None, rope_base: Optional[float] = None):
+                 device: str = "cuda:0", engine: Optional[Engine] = None, rope_base: Optional[float] = None,
+                 rope_scale: Optional[float] = None):
         """model: folder with config.json + model.safetensors.  Or `config` (a typed configuration) with
         `random_seed` for seeded random weights.  ctx: longest request (default min(model limit, 4096), the
         reference's -c default, src/model.c:3075).  batch: token budget of a step (-b).  parallel: live
         requests.  max_tokens: tokens the page pool holds (default parallel * ctx).  rope_base: use this
-        frequency base instead of the configuration's (--rope-base, src/model.c:282)."""
+        frequency base instead of the configuration's (--rope-base, src/model.c:282).  rope_scale: force linear
+        position scaling by this factor instead of the configuration's scaling (--rope-scale, src/model.c:324-326)."""
         if engine is None:
             if model is not None:
                 from ..config import registry
@@ -102,11 +104,17 @@ class Runner:
                 if not hasattr(cfg, "rope_theta"):
                     raise ValueError("rope_base: this architecture's configuration has no rope_theta")
                 cfg = dataclasses.replace(cfg, rope_theta=float(rope_base))
+            if rope_scale is not None:
+                import dataclasses
+                from ..config.llama import RopeScaling
+                if not hasattr(cfg, "rope_scaling"):
+                    raise ValueError("rope_scale: this architecture's configuration has no rope_scaling")
+                cfg = dataclasses.replace(cfg, rope_scaling=RopeScaling(rope_type="linear", factor=float(rope_scale)))
             model_limit = getattr(cfg, "max_position_embeddings", 4096)
             ctx = ctx or min(model_limit, 4096)
             ep = EngineParams(dtype=dtype, max_tokens=max_tokens or parallel * ctx, page_size=page_size,
                               max_requests=parallel, max_request_tokens=ctx, max_step_tokens=batch, device=device)
-            if model is not None and rope_base is not None:
+            if model is not None and (rope_base is not None or rope_scale is not None):
                 from ..weights.loader import FolderSource
                 engine = Engine(params=ep, config=cfg, source=FolderSource(model))
             elif model is not None:

@@ -5,7 +5,8 @@ model's per-frequency factors where it has them (src/model.c:291-297).  The refe
 factors from a tensor its converter wrote; for ``rope_scaling`` of type llama3 they are computed
 here from the four numbers of the configuration: with wavelength lam = 2*pi/f,
 ``lam < orig/high`` keeps f, ``lam > orig/low`` divides f by ``factor``, and between the two
-f' = (1-s) f/factor + s f with s = (orig/lam - low) / (high - low).  The rotation itself (angle =
+f' = (1-s) f/factor + s f with s = (orig/lam - low) / (high - low).  ``rope_scaling`` of type linear divides
+every frequency by ``factor`` (src/model.c:361-362).  The rotation itself (angle =
 position * inv_freq in float32, pairs (j, j + rotary_dim/2), src/model.c:3514-3532) happens in the
 kernel that also stores K and V.
 """
@@ -45,7 +46,9 @@ class Rope(PositionEncoding):
         j = np.arange(half, dtype=np.float32)
         expo = (np.float32(-2.0) * j / np.float32(self.rotary_dim)).astype(np.float32) if half else j
         inv = np.power(np.float32(theta), expo).astype(np.float32)
-        if scaling is not None:
+        if scaling is not None and getattr(scaling, "rope_type", "llama3") == "linear":
+            inv = (inv / np.float32(scaling.factor)).astype(np.float32)          # src/model.c:361-362
+        elif scaling is not None:
             div = llama3_divisors(inv, scaling.factor, scaling.low_freq_factor, scaling.high_freq_factor,
                                   scaling.original_max_position_embeddings)
             inv = (inv / div).astype(np.float32)
