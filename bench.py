@@ -135,6 +135,26 @@ def mixed_workload(args) -> int:
                "steps": runner.scheduler.stats.get("steps"), "gpu_launches": kernels.launch_count - launches0,
                "step_token_budget": 2048}
     out["clocks"] = clocks.stop()
+    if args.step_log:
+        # once more, step by step: what each step held and how long the host waited for it
+        sch = runner.scheduler
+        for p in prompts:
+            runner.submit(p, new, ignore_eos=True)
+        torch.cuda.synchronize()
+        lines, seen = [], dict(sch.stats)
+        while sch.has_work():
+            t0 = time.perf_counter()
+            res = sch.step()
+            ms = (time.perf_counter() - t0) * 1e3
+            now = dict(sch.stats)
+            lines.append(f"{len(lines)} {'ahead' if now['steps_launched_ahead'] > seen['steps_launched_ahead'] else 'plain'} "
+                         f"tokens_out={len(res)} prompt_tokens={now['prefill_tokens'] - seen['prefill_tokens']} "
+                         f"decode_tokens={now['decode_tokens'] - seen['decode_tokens']} ms={ms:.2f}")
+            seen = now
+        sch.finished.clear()
+        with open(args.step_log, "w") as f:
+            f.write("# step, launched-ahead or plain, tokens returned, prompt tokens run, decoded tokens run, wall ms of Scheduler.step\n")
+            f.write("\n".join(lines) + "\n")
     print(json.dumps(out))
     return 0
 
@@ -155,6 +175,7 @@ def main() -> int:
     ap.add_argument("--shape", choices=sorted(SHAPES), default=None, help="layer sizes (default llama-3-8b)")
     ap.add_argument("--workload", choices=["decode", "mixed"], default="decode",
                     help="mixed: many requests with prompts of mixed length through Runner.generate (default shape llama-3.2-1b)")
+    ap.add_argument("--step-log", default=None, metavar="FILE", help="with --workload mixed: write one line per step to FILE")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
