@@ -136,8 +136,8 @@ def timeline(a) -> None:
     from .engine.engine import EngineParams, StepEntry, random_engine
     from .sampling.sampler import DeviceSampler, RequestSampler, SamplingParams
     cfg = LlamaConfig.from_dict({
-        "architectures": ["LlamaForCausalLM"], "hidden_size": 4096, "num_hidden_layers": a.layers, "num_attention_heads": 32,
-        "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 14336, "vocab_size": 128256, "rms_norm_eps": 1e-5,
+        "architectures": ["LlamaForCausalLM"], "hidden_size": a.hidden, "num_hidden_layers": a.layers, "num_attention_heads": a.heads,
+        "num_key_value_heads": a.kv_heads, "head_dim": a.head_dim, "intermediate_size": a.intermediate, "vocab_size": a.vocab, "rms_norm_eps": 1e-5,
         "rope_theta": 500000.0, "max_position_embeddings": a.context, "tie_word_embeddings": False, "hidden_act": "silu",
         "torch_dtype": "bfloat16"})
     B = a.batch
@@ -170,8 +170,12 @@ def timeline(a) -> None:
             t0, t1, g, b = (int(x) for x in rec[f, k])
             ev.append((t1, t0, (g >> 40, (g >> 20) & 0xfffff, g & 0xfffff), b))
     ev.sort()
-    # the step: embed, norm, then ten kernels a layer; print the second layer and the start of the third
-    per_layer = 10
+    # the step that was recorded: embedding, first norm, the same kernels layer after layer (the last finish of the
+    # last layer also does the final norm), then head product and sampling; print the second layer and the start
+    # of the third
+    per_layer = (len(ev) - 4) // a.layers
+    if per_layer < 1 or 2 + per_layer * a.layers + 2 != len(ev):
+        raise SystemExit(f"{len(ev)} launches were recorded: not embedding + norm + {a.layers} equal layers + 2")
     first = 2 + per_layer
     rows = ev[first:first + per_layer + 1]
     if len(rows) < per_layer + 1:
@@ -183,9 +187,9 @@ def timeline(a) -> None:
         print(f"{(t1 - base) / 1e3:12.2f} {(t1 - t0) / 1e3:16.2f} {(nxt[0] - t1) / 1e3:7.2f}  {g} / {b}")
     print(f"layer: {(rows[-1][0] - base) / 1e3:.2f} us")
     # the two ends of the last recorded step: embedding and first norm; last finish + final norm, head, sampling
-    step = ev[-(2 + per_layer * a.layers + 3):]
+    step = ev
     print("start and end of the step:")
-    for idx in (0, 1, len(step) - 4, len(step) - 3, len(step) - 2):
+    for idx in (0, 1, len(step) - 3, len(step) - 2):
         (t1, t0, g, b), nxt = step[idx], step[idx + 1]
         print(f"{(t1 - step[0][0]) / 1e3:12.2f} {(t1 - t0) / 1e3:16.2f} {(nxt[0] - t1) / 1e3:7.2f}  {g} / {b}")
     print(f"step up to the sampling kernel: {(step[-1][0] - step[0][0]) / 1e3:.2f} us")
@@ -218,6 +222,12 @@ def main(argv=None) -> int:
     tl.add_argument("--batch", type=int, default=8)
     tl.add_argument("--context", type=int, default=8192)
     tl.add_argument("--layers", type=int, default=8)
+    tl.add_argument("--hidden", type=int, default=4096)
+    tl.add_argument("--heads", type=int, default=32)
+    tl.add_argument("--kv-heads", type=int, default=8)
+    tl.add_argument("--head-dim", type=int, default=128)
+    tl.add_argument("--intermediate", type=int, default=14336)
+    tl.add_argument("--vocab", type=int, default=128256)
     for p in (g, t, sm):
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--plain", action="store_true", help="no CUDA graph")
