@@ -1,4 +1,6 @@
-// Picking the next token from float32 logits on the device, one block per row.
+// Picking the next token from float32 logits on the device: one block per row (k_sample), or, for rows of more
+// than 1,024 values and few rows, a cluster of eight blocks per row that keeps the row in registers
+// (k_sample_cluster, further down); and the log-probability of a given token per row (k_logprob, at the end).
 //
 // The chain is the reference's `sample_pick` (src/sample.c:141-329) with
 // `pick_scaled` (src/sample.c:86-127):
