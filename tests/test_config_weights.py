@@ -12,7 +12,7 @@ from xyntetik_runner_b200 import architectures  # noqa: F401
 from xyntetik_runner_b200.architectures.llama import build_llama
 from xyntetik_runner_b200.config import registry
 from xyntetik_runner_b200.config.llama import ConfigError, LlamaConfig
-from xyntetik_runner_b200.weights.loader import FolderSource, RandomSource, WeightsError, load_tensors
+from xyntetik_runner_b200.weights.loader import FolderSource, WeightsError, load_tensors
 from xyntetik_runner_b200.weights.safetensors_io import SafetensorsError, SafetensorsFile, write_safetensors
 
 

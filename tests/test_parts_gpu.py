@@ -1,13 +1,10 @@
 """Each part of a layer alone (norm, position encoding + cache store, attention, feed-forward, block,
 embedding and head), driven through its own interface, against the plain functions."""
-import math
-
 import numpy as np
 import pytest
 import torch
 
 import tiny
-import traces
 from plain_llama import PlainLlama, attention, embed, matvec_rows, rmsnorm, rope_apply, swiglu
 
 pytestmark = pytest.mark.gpu

@@ -5,9 +5,6 @@ first, no weights), a schedule that runs a layer twice and lets a layer read ano
 registered, built from a folder, and stepped through the engine without any change to the framework's files.  It is compared with a plain computation written here.
 It is a test fixture, not a model of anything.
 """
-import json
-import os
-
 import numpy as np
 import pytest
 import torch
@@ -33,7 +30,6 @@ def centred(x, eps):
 def _define():
     """Parts and architecture of the toy model (defined inside a function so that importing this file on a
     machine without a GPU does nothing)."""
-    from xyntetik_runner_b200 import kernels
     from xyntetik_runner_b200.config.registry import register_architecture
     from xyntetik_runner_b200.engine.model import ModelPlan, ScheduleEntry
     from xyntetik_runner_b200.parts import (Embedding, FeedForward, GQAAttention, Head, Mixer, NoPosition, Norm,

@@ -18,7 +18,7 @@ only (the reference's `want_logits`, src/model.c:6478-6481, generalised).
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence
 
 import numpy as np

@@ -9,7 +9,7 @@ line (src/main.c:188-340): ``n`` (-n, max new tokens, default 256), ``temp`` (--
 from __future__ import annotations
 
 import time
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Union
 
 import torch

@@ -25,9 +25,9 @@ from __future__ import annotations
 
 from collections import deque
 from dataclasses import dataclass, field
-from typing import Deque, Dict, List, Optional, Sequence, Tuple
+from typing import Deque, Dict, List, Optional, Tuple
 
-from ..cache.pages import CacheManager, OutOfPages
+from ..cache.pages import CacheManager
 from ..sampling.sampler import RequestSampler, SamplingParams
 
 WAITING, LIVE, FINISHED = "waiting", "live", "finished"
