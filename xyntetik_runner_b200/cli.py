@@ -4,7 +4,8 @@ Options keep the reference's names and meanings where it has them: -m (here a mo
 config.json and model.safetensors), -p, -f, -n (default 256, -1 = until a stop id), -c, -b, -s (0 is
 refused), --temp (0 = greedy), --top-k, --top-p, --min-p, --repeat-penalty, --ignore-eos, --no-bos,
 --score (teacher-forced log-probabilities of the prompt, the reference's JSON), --parallel, --rope-base, --rope-scale,
---bench-json, -v/--version.  Tokenisation is outside the engine: a prompt is either ``ids:1,2,3`` or
+--bench-json, -v/--version.  Tokenisation is outside the engine: a prompt is either ``ids:1,2,3`` (or a file of
+ids, --prompt-ids) or
 text taken byte by byte (token id = byte value), and the output is printed as ids (and as bytes where
 every id is one).
 """
@@ -50,6 +51,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("-m", dest="model", help="model folder (config.json + model.safetensors)")
     ap.add_argument("-p", dest="prompt", default=None, help="prompt: text (bytes) or ids:1,2,3; \\n etc. are unescaped")
     ap.add_argument("-f", dest="file", default=None, help="read prompt from file (appended after -p text)")
+    ap.add_argument("--prompt-ids", default=None, metavar="FILE",
+                    help="read the prompt as token ids from FILE (integers separated by commas or white space); instead of -p / -f")
     ap.add_argument("-n", dest="n", type=int, default=256, help="max tokens to generate (default 256, -1 = until a stop id)")
     ap.add_argument("-c", dest="ctx", type=int, default=None, help="context length (default: min(model max, 4096))")
     ap.add_argument("-b", dest="batch", type=int, default=2048, help="prompt portion / step token budget (default 2048)")
@@ -123,11 +126,18 @@ def main(argv=None) -> int:
         print(json.dumps({"prompt_tokens": 512, "gen_tokens": len(res.tokens), "prompt_s": prompt_s, "gen_s": gen_s,
                           "prompt_tok_s": 512 / prompt_s, "gen_tok_s": (len(res.tokens) - 1) / gen_s if gen_s > 0 else 0.0}))
         return 0
-    text = unescape(args.prompt) if args.prompt is not None else ""
-    if args.file:
-        with open(args.file, "r", encoding="utf-8") as f:
-            text += f.read()
-    ids = encode_prompt(text, plan.vocab_size)
+    if args.prompt_ids is not None:
+        if args.prompt is not None or args.file:
+            print("error: --prompt-ids stands instead of -p and -f", file=sys.stderr)
+            return 2
+        with open(args.prompt_ids, "r", encoding="utf-8") as f:
+            ids = encode_prompt("ids:" + ",".join(f.read().replace(",", " ").split()), plan.vocab_size)
+    else:
+        text = unescape(args.prompt) if args.prompt is not None else ""
+        if args.file:
+            with open(args.file, "r", encoding="utf-8") as f:
+                text += f.read()
+        ids = encode_prompt(text, plan.vocab_size)
     if not args.no_bos and plan.bos_id is not None:
         ids = [plan.bos_id] + ids
     if not ids:
