@@ -120,6 +120,28 @@ def test_stop_ids_end_a_request(folders):
     assert q.finish_reason == "stop" and q.generated == free[:first]
 
 
+def test_callback_ends_a_request(folders):
+    """on_token returning False ends that request at once (reason "abort"); the request beside it goes on unchanged,
+    also while steps are launched ahead."""
+    from xyntetik_runner_b200.engine.runner import Runner
+    folder = folders["A", "float32"]
+    plain = PlainLlama(folder)
+    pa, pb = traces.random_tokens(21, 9, 256), traces.random_tokens(22, 14, 256)
+    want_a, want_b = plain.generate_greedy(pa, 10), plain.generate_greedy(pb, 10)
+    r = Runner(folder, dtype="float32", ctx=128, parallel=2, page_size=16)
+    seen = {0: 0, 1: 0}
+
+    def on_token(rid, tok, done):
+        seen[rid] += 1
+        return not (rid == 0 and seen[0] == 4)           # the first request is ended when its 4th token arrives
+
+    a, b = r.generate([pa, pb], n=10, temp=0.0, ignore_eos=True, on_token=on_token)
+    assert a.finish_reason == "abort" and a.tokens == want_a[:4]
+    assert b.finish_reason == "length" and b.tokens == want_b
+    assert not r.engine.cache.live_requests()
+    r.engine.cache.audit()
+
+
 @pytest.mark.parametrize("temp", [0.0, 0.9])
 def test_steps_launched_ahead_give_the_same_tokens(folders, temp):
     """Decode steps launched before the tokens of the step ahead of them are read (the device feeds the sampled ids

@@ -217,6 +217,31 @@ def test_steps_launched_ahead_change_nothing(seed):
     assert any(reason == "stop" for _, reason in outcomes[0].values())
 
 
+@pytest.mark.parametrize("ahead", [False, True])
+def test_abort_frees_at_once_and_leaves_the_others_alone(ahead):
+    cache = CacheManager([GroupSpec("full")], 64, 4, 4, 128)
+    ex = PipelinedFakeExecutor(cache)
+    s = Scheduler(cache, ex, SchedulerParams(max_step_tokens=32, look_ahead=ahead))
+    for rid, n in (("a", 9), ("b", 5), ("c", 7), ("d", 3), ("e", 4)):
+        s.add(Request(rid, list(range(10, 10 + n)), max_new_tokens=12))
+    assert s.abort("e") and "e" not in [r.id for r in s.waiting]            # still waiting (four slots): leaves the queue
+    assert s.finished["e"].finish_reason == "abort" and s.finished["e"].generated == []
+    for _ in range(5):
+        s.step()
+    held = cache.free_pages()[0]
+    n_b = len([r for r in s.live if r.id == "b"][0].generated)
+    assert 0 < n_b < 12
+    assert s.abort("b") and not s.abort("b") and not s.abort("nobody")
+    assert cache.free_pages()[0] > held and "b" not in cache.live_requests()     # its pages and slot are back in this call
+    cache.audit()
+    s.run_to_completion()
+    assert s.finished["b"].finish_reason == "abort" and s.finished["b"].generated == expected_tokens("b", 5, n_b)
+    for rid, n in (("a", 9), ("c", 7), ("d", 3)):
+        assert s.finished[rid].generated == expected_tokens(rid, n, 12) and s.finished[rid].finish_reason == "length"
+    assert cache.free_pages() == [64] and not cache.live_requests()
+    cache.audit()
+
+
 def test_sampler_state_is_per_request_and_follows_the_reference_generator():
     from plain_llama import uniform_from_state, xorshift64
     s = RequestSampler(SamplingParams(temperature=0.8, seed=12345))

@@ -146,7 +146,9 @@ class Runner:
                  top_k: int = 0, top_p: float = 1.0, min_p: float = 0.0, repeat_penalty: float = 1.0,
                  seed: Optional[int] = None, ignore_eos: bool = False, on_token=None):
         """Generate for one prompt (a list of ids) or several (a list of lists), all scheduled together.
-        With several prompts and a seed, request i samples with seed + i.  Returns GenerationResult(s)."""
+        With several prompts and a seed, request i samples with seed + i.  `on_token(request, token, finished)` is
+        called for every token as it arrives; returning False ends that request there (finish reason "abort").
+        Returns GenerationResult(s)."""
         single = len(prompts) > 0 and isinstance(prompts[0], int)
         plist = [prompts] if single else list(prompts)
         ids = [self.submit(p, n, temp, top_k, top_p, min_p, repeat_penalty,
@@ -158,7 +160,8 @@ class Runner:
             res = sch.step()
             if on_token is not None:
                 for rid, tok, done in res:
-                    on_token(rid, tok, done)
+                    if on_token(rid, tok, done) is False and not done:
+                        sch.abort(rid)           # the callback asked for the end of this request (src/engine.c:1844-1848)
             if not res and not sch.live and sch.waiting and len(sch.finished) == before:
                 r = sch.waiting.popleft()
                 sch._finish(r, "rejected")

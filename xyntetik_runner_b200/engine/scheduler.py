@@ -131,6 +131,25 @@ class Scheduler:
     def has_work(self) -> bool:
         return bool(self.waiting or self.live)
 
+    def abort(self, request_id) -> bool:
+        """End a request now, whatever its state (the reference's callback abort and cancel, src/engine.c:1844-1848,
+        src/scheduler.c:383-385): a waiting one leaves the queue, a live one gives its pages and its slot back in this
+        call; what it has generated so far stays in `finished` with the reason "abort".  False if it is not known
+        (or already finished).  A step launched ahead that still holds a row for it computes that row for nothing;
+        the pages it writes are handed to nobody before that step has run (the next step follows it on the stream)."""
+        for r in self.waiting:
+            if r.id == request_id:
+                self.waiting.remove(r)
+                self._finish(r, "abort")
+                return True
+        for r in self.live:
+            if r.id == request_id:
+                if r.tokens and r.tokens[-1] == IN_FLIGHT:
+                    r.tokens.pop()               # the mark of a token that nobody will read
+                self._finish(r, "abort")
+                return True
+        return False
+
     # ---- planning -----------------------------------------------------------------------
     def _preempt(self, victim: Request, plan: StepPlan) -> None:
         for e in list(plan.entries):
