@@ -142,6 +142,10 @@ class Runner:
                                    ignore_eos=ignore_eos))
         return rid
 
+    def abort(self, request_id) -> bool:
+        """End a submitted request now; its pages and slot are free when this returns (see Scheduler.abort)."""
+        return self.scheduler.abort(request_id)
+
     def generate(self, prompts: Union[Sequence[int], Sequence[Sequence[int]]], n: int = 256, temp: float = 0.0,
                  top_k: int = 0, top_p: float = 1.0, min_p: float = 0.0, repeat_penalty: float = 1.0,
                  seed: Optional[int] = None, ignore_eos: bool = False, on_token=None):
