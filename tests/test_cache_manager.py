@@ -162,3 +162,40 @@ def test_describe_step_flattens_a_batch():
     m.close("b")
     with pytest.raises(CacheError):
         m.describe_step(slots, counts, tokens, want_counts, wants, 0, 16, [a.ctypes.data for a in arrs], [b.ctypes.data for b in bts])
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_pages_held_follow_the_formula(seed):
+    """After every commit a request holds, in a group that keeps all keys, ceil(length / page) pages, and in a window
+    group the pages from the one that holds the first key its next query can still read up to the last: counted here
+    from lengths alone and compared with the pools."""
+    rng = np.random.RandomState(50 + seed)
+    ps, window, n_pages = int(rng.choice([2, 4, 8])), int(rng.randint(2, 30)), 200
+    m = CacheManager([GroupSpec("full"), GroupSpec("w", window=window)], n_pages, ps, 5, ps * 30)
+    lengths = {}
+
+    released = {}                                   # request -> first page index still held in the window group
+    for it in range(500):
+        op = rng.rand()
+        if op < 0.15 and m.has_free_slot():
+            rid = f"r{it}"
+            m.open(rid); lengths[rid] = 0; released[rid] = 0
+        elif op < 0.85 and lengths:
+            rid = list(lengths)[rng.randint(len(lengths))]
+            n = int(rng.randint(1, 2 * ps + 2))
+            if lengths[rid] + n <= ps * 30:
+                # reserving releases what a query at the current length can no longer read
+                first_key = max(0, lengths[rid] - window + 1)
+                released[rid] = max(released[rid], min(first_key // ps, -(-lengths[rid] // ps)))
+                m.reserve(rid, n); m.commit(rid)
+                lengths[rid] += n
+        elif lengths:
+            rid = list(lengths)[rng.randint(len(lengths))]
+            m.close(rid); del lengths[rid]; del released[rid]
+        full = sum(-(-n // ps) for n in lengths.values())
+        win = sum(-(-n // ps) - released[rid] for rid, n in lengths.items())
+        assert m.free_pages() == [n_pages - full, n_pages - win], (it, lengths, released)
+        for rid, n in lengths.items():
+            tab = m.block_table(1, rid)
+            assert (tab[:released[rid]] == -1).all() and (tab[released[rid]:-(-n // ps)] >= 0).all()
+    m.audit()
