@@ -73,7 +73,7 @@ def read_folder(model_dir: str):
 def matvec_rows(x: np.ndarray, w: np.ndarray, bias=None) -> np.ndarray:
     """y[t][r] = sum_i W[r][i] * x[t][i] (+ b[r]): src/model.c:3426-3506 (`matvec_b`),
     float32 values, one rounding of a wide sum."""
-    y = x.astype(np.float64) @ w.astype(np.float64).T
+    y = x.astype(np.float64) @ np.asarray(w, dtype=np.float64).T           # (no copy when w is wide already)
     if bias is not None:
         y = y + bias.astype(np.float64)
     return y.astype(F32)
@@ -180,6 +180,32 @@ def attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, scale: float, window=
     return out
 
 
+def attention_in_blocks(q: np.ndarray, k: np.ndarray, v: np.ndarray, scale: float, window=None, block: int = 256) -> np.ndarray:
+    """The same function as ``attention`` for long sequences: per head, a block of queries at a time against all
+    keys up to the block's last position, the keys a query may not see masked out before the softmax
+    (the reference's loop bounds t0..p, src/model.c:3556-3573, as a mask)."""
+    T, H, hd = q.shape
+    K = k.shape[1]
+    mul = H // K
+    out = np.zeros((T, H, hd), dtype=F32)
+    sc = np.float64(F32(scale))
+    for h in range(H):
+        kk = k[:, h // mul, :].astype(np.float64)
+        vv = v[:, h // mul, :].astype(np.float64)
+        for p0 in range(0, T, block):
+            p1 = min(T, p0 + block)
+            t_lo = 0 if window is None else max(0, p0 - window + 1)
+            s = (q[p0:p1, h].astype(np.float64) @ kk[t_lo:p1].T) * sc
+            pos = np.arange(p0, p1)[:, None]
+            key = np.arange(t_lo, p1)[None, :]
+            hidden = key > pos
+            if window is not None:
+                hidden |= key < pos - window + 1
+            s = np.where(hidden, -np.inf, s)
+            out[p0:p1, h] = (softmax_rows(s) @ vv[t_lo:p1]).astype(F32)
+    return out
+
+
 def swiglu(g: np.ndarray, u: np.ndarray) -> np.ndarray:
     """h = g / (1 + exp(-g)) * u, and 0 where g < -80 (src/model.c:4451-4452)."""
     gg = g.astype(np.float64)
@@ -193,8 +219,13 @@ def swiglu(g: np.ndarray, u: np.ndarray) -> np.ndarray:
 # the model
 # --------------------------------------------------------------------------
 class PlainLlama:
-    def __init__(self, model_dir: str):
-        self.cfg, self.w = read_folder(model_dir)
+    def __init__(self, model_dir: str = None, *, config: dict = None, tensors: dict = None):
+        """From a folder, or from config.json's keys as a dict plus {tensor name: float32 array}."""
+        if model_dir is not None:
+            self.cfg, self.w = read_folder(model_dir)
+        else:
+            self.cfg, self.w = dict(config), dict(tensors)
+        self._wide = {}         # float64 copies of the matrices, made once (big models would convert them at every call)
         c = self.cfg
         self.d = c["hidden_size"]
         self.L = c["num_hidden_layers"]
@@ -214,22 +245,28 @@ class PlainLlama:
             return self.window
         return None
 
+    def mat(self, name: str) -> np.ndarray:
+        if name not in self._wide:
+            self._wide[name] = self.w[name].astype(np.float64)
+        return self._wide[name]
+
     def layer(self, x: np.ndarray, l: int, positions: np.ndarray) -> np.ndarray:
         """x -> norm -> attention -> +x -> norm -> feed-forward -> +x (src/model.c:6206-6423)."""
         w, p = self.w, f"model.layers.{l}."
         T = x.shape[0]
+        attend = attention if T <= 256 else attention_in_blocks
         bias = (lambda n: w.get(p + n)) if self.cfg.get("attention_bias") else (lambda n: None)
         xb = rmsnorm(x, w[p + "input_layernorm.weight"], self.eps)
-        q = matvec_rows(xb, w[p + "self_attn.q_proj.weight"], bias("self_attn.q_proj.bias")).reshape(T, self.H, self.hd)
-        k = matvec_rows(xb, w[p + "self_attn.k_proj.weight"], bias("self_attn.k_proj.bias")).reshape(T, self.K, self.hd)
-        v = matvec_rows(xb, w[p + "self_attn.v_proj.weight"], bias("self_attn.v_proj.bias")).reshape(T, self.K, self.hd)
+        q = matvec_rows(xb, self.mat(p + "self_attn.q_proj.weight"), bias("self_attn.q_proj.bias")).reshape(T, self.H, self.hd)
+        k = matvec_rows(xb, self.mat(p + "self_attn.k_proj.weight"), bias("self_attn.k_proj.bias")).reshape(T, self.K, self.hd)
+        v = matvec_rows(xb, self.mat(p + "self_attn.v_proj.weight"), bias("self_attn.v_proj.bias")).reshape(T, self.K, self.hd)
         q = rope_apply(q, positions, self.inv_freq)          # after projection, before the cache (src/model.c:6276-6299)
         k = rope_apply(k, positions, self.inv_freq)
-        o = attention(q, k, v, self.scale, self._window(l)).reshape(T, self.H * self.hd)
-        x = (x + matvec_rows(o, w[p + "self_attn.o_proj.weight"], bias("self_attn.o_proj.bias"))).astype(F32)
+        o = attend(q, k, v, self.scale, self._window(l)).reshape(T, self.H * self.hd)
+        x = (x + matvec_rows(o, self.mat(p + "self_attn.o_proj.weight"), bias("self_attn.o_proj.bias"))).astype(F32)
         xb = rmsnorm(x, w[p + "post_attention_layernorm.weight"], self.eps)
-        h = swiglu(matvec_rows(xb, w[p + "mlp.gate_proj.weight"]), matvec_rows(xb, w[p + "mlp.up_proj.weight"]))
-        x = (x + matvec_rows(h, w[p + "mlp.down_proj.weight"])).astype(F32)
+        h = swiglu(matvec_rows(xb, self.mat(p + "mlp.gate_proj.weight")), matvec_rows(xb, self.mat(p + "mlp.up_proj.weight")))
+        x = (x + matvec_rows(h, self.mat(p + "mlp.down_proj.weight"))).astype(F32)
         return x
 
     def hidden(self, ids) -> np.ndarray:
@@ -239,12 +276,14 @@ class PlainLlama:
             x = self.layer(x, l, pos)
         return x
 
-    def logits(self, ids) -> np.ndarray:
-        """Logits at every position of the whole sequence: final norm, then the head, which is the
-        embedding table when the model has no lm_head tensor (src/model.c:2353-2354, 6478-6481)."""
+    def logits(self, ids, rows=None) -> np.ndarray:
+        """Logits at every position of the whole sequence (or at the positions `rows`): final norm, then the
+        head, which is the embedding table when the model has no lm_head tensor (src/model.c:2353-2354, 6478-6481)."""
         x = self.hidden(ids)
+        if rows is not None:
+            x = x[np.asarray(rows, dtype=np.int64)]
         xb = rmsnorm(x, self.w["model.norm.weight"], self.eps)
-        head = self.w["lm_head.weight"] if "lm_head.weight" in self.w else self.w["model.embed_tokens.weight"]
+        head = self.mat("lm_head.weight" if "lm_head.weight" in self.w else "model.embed_tokens.weight")
         return matvec_rows(xb, head)
 
     def generate_greedy(self, ids, n_new: int):

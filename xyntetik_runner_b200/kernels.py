@@ -66,6 +66,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "xr_sample": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
         "xr_sample_one_block": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
         "xr_logprob": [_vp, _ll, _i, _i, _vp, _vp, _vp],
+        "xr_random_normal": [_vp, _i, _ll, ctypes.c_ulonglong, ctypes.c_ulonglong, _f, _f, _vp],
     }
     for name, args in sig.items():
         fn = getattr(L, name)
@@ -218,6 +219,15 @@ def logprob(logits: torch.Tensor, target: torch.Tensor, out: torch.Tensor) -> No
     assert logits.dtype == torch.float32 and logits.stride(1) == 1 and logits.is_cuda
     assert target.dtype == torch.int32 and target.numel() >= rows and out.dtype == torch.float32 and out.numel() >= rows
     _check(lib().xr_logprob(logits.data_ptr(), logits.stride(0), rows, V, target.data_ptr(), out.data_ptr(), _stream()), "logprob")
+    _count()
+
+
+def random_normal(out: torch.Tensor, key: int, mean: float, std: float, first: int = 0) -> None:
+    """out.flat[i] = mean + std * z(key, first + i): the counter-based generator of csrc/random_fill.cu, whose
+    values equal ``weights.random_fill.normal_values`` bit for bit."""
+    _dev(out)
+    _check(lib().xr_random_normal(out.data_ptr(), dtype_code(out.dtype), out.numel(), key & 0xFFFFFFFFFFFFFFFF, first,
+                                  float(mean), float(std), _stream()), "random_normal")
     _count()
 
 

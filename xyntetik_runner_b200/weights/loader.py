@@ -83,19 +83,18 @@ class FolderSource(TensorSource):
         return self._owner[name].get(name).to(device, non_blocking=False)
 
 
-def tensor_seed(seed: int, name: str) -> int:
-    """Seed of one tensor's stream: every tensor draws independently of the others' sizes."""
-    return int.from_bytes(hashlib.sha256(f"{seed}:{name}".encode()).digest()[:7], "little")
-
-
 class RandomSource(TensorSource):
     """Seeded random tensors for a list of specs.
 
     Matrices ~ N(0, std); vectors marked "ones_jitter" are 1 + N(0, jitter)
     (with jitter 0 they are exactly 1, the reference fixture's norm weights,
-    scripts/make-test-model.py:276,287).  Values are drawn in float32 and
-    rounded to `dtype` (nearest even).  Streams differ between generator
-    devices, so a folder is always written from the CPU generator.
+    scripts/make-test-model.py:276,287).  Values are drawn in float32 by the
+    counter-based generator of ``weights.random_fill`` -- element i of tensor
+    `name` is a function of (seed, name, i) alone -- and rounded to `dtype`
+    (nearest even).  `gen_device` "cpu" draws with numpy, a CUDA device with
+    the kernel of the same recipe; the bits are the same, so a model drawn on
+    the device for a measurement can be re-made anywhere, whole or tensor by
+    tensor, without a folder.
     """
 
     def __init__(self, specs: Mapping[str, TensorSpec], seed: int, dtype: torch.dtype,
@@ -110,35 +109,34 @@ class RandomSource(TensorSource):
     def listing(self):
         return {n: (self.dtype_of(s), tuple(s.shape)) for n, s in self.specs.items()}
 
-    def fetch(self, name, device):
-        spec = self.specs[name]
-        g = torch.Generator(device=self.gen_device)
-        g.manual_seed(tensor_seed(self.seed, name))
+    def law(self, spec: TensorSpec):
+        """(mean, std) of a spec's values, or a constant."""
         if spec.init == "zeros" or spec.kind == "table":
-            t = torch.zeros(spec.shape, dtype=torch.float32, device=self.gen_device)
-        elif spec.init == "ones":
-            t = torch.ones(spec.shape, dtype=torch.float32, device=self.gen_device)
-        else:
-            t = torch.empty(spec.shape, dtype=torch.float32, device=self.gen_device)
-            # drawn row by row for big matrices so that the float32 staging copy stays small
-            if t.dim() == 2 and t.numel() > (1 << 26):
-                out = torch.empty(spec.shape, dtype=self.dtype, device=device)
-                rows = max(1, (1 << 26) // t.shape[1])
-                del t
-                for r0 in range(0, spec.shape[0], rows):
-                    r1 = min(spec.shape[0], r0 + rows)
-                    blk = torch.empty((r1 - r0, spec.shape[1]), dtype=torch.float32, device=self.gen_device)
-                    blk.normal_(0.0, self.std, generator=g)
-                    out[r0:r1] = blk.to(device=device, dtype=self.dtype)
-                return out
-            if spec.init == "ones_jitter":
-                if self.jitter > 0:
-                    t.normal_(1.0, self.jitter, generator=g)
-                else:
-                    t.fill_(1.0)
-            else:
-                t.normal_(0.0, self.std, generator=g)
-        return t.to(device=device, dtype=self.dtype_of(spec))
+            return 0.0
+        if spec.init == "ones":
+            return 1.0
+        if spec.init == "ones_jitter":
+            return (1.0, self.jitter) if self.jitter > 0 else 1.0
+        return (0.0, self.std)
+
+    def fetch(self, name, device):
+        from . import random_fill
+        spec = self.specs[name]
+        law = self.law(spec)
+        dt = self.dtype_of(spec)
+        if not isinstance(law, tuple):
+            return torch.full(tuple(spec.shape), law, dtype=dt, device=device)
+        key = random_fill.tensor_key(self.seed, name)
+        count = 1
+        for s in spec.shape:
+            count *= int(s)
+        if self.gen_device.type == "cuda":
+            from .. import kernels
+            out = torch.empty(tuple(spec.shape), dtype=dt, device=self.gen_device)
+            kernels.random_normal(out, key, law[0], law[1])
+            return out.to(device)
+        vals = torch.from_numpy(random_fill.normal_values(key, 0, count, law[0], law[1])).view(tuple(spec.shape))
+        return vals.to(dt).to(device)
 
 
 def load_tensors(expected: Mapping[str, TensorSpec], source: TensorSource,
