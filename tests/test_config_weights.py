@@ -2,6 +2,7 @@
 import copy
 import json
 import os
+import shutil
 
 import numpy as np
 import pytest
@@ -194,3 +195,118 @@ def test_rope_table_matches_the_plain_formula():
     assert np.allclose(Rope(lin.head_dim, lin.rope_theta).inv_freq_host / mine, 2.5, rtol=1e-6)
     with pytest.raises(ConfigError, match="factor"):
         LlamaConfig.from_dict(dict(tiny.TINY_A, rope_scaling={"type": "linear", "factor": 0.0}))
+
+
+def test_llama3_divisors_against_constants():
+    """The per-frequency divisors of rope_scaling type llama3, pinned by numbers: how many frequencies stay as they
+    are, how many are divided by the whole factor, and the divisors of the band between (worked out in float64 from
+    the turns a frequency makes over the original context, turns = orig * f / 2 pi: more than `high` turns keeps f,
+    fewer than `low` divides by `factor`, between them f' = (1 - s) f / factor + s f with
+    s = (turns - low) / (high - low)), for the parameters of Llama-3.1, Llama-3.2 and tiny configuration B."""
+    from xyntetik_runner_b200.parts.position import llama3_divisors
+    cases = {
+        # (theta, head size, factor, low, high, original context): (kept, fully divided, {index: divisor})
+        (5e5, 128, 8.0, 1.0, 4.0, 8192): (29, 29, {29: 1.207483871283662, 30: 1.5534146285049257, 31: 2.0263132059050557,
+                                                     32: 2.694529687894733, 33: 3.6842525277457185, 34: 5.257326588708465}),
+        (5e5, 64, 32.0, 1.0, 4.0, 8192): (15, 14, {15: 1.6513292457638984, 16: 3.292262102940884, 17: 9.666728978753287}),
+        (5e5, 32, 8.0, 1.0, 4.0, 64): (2, 13, {2: 2.4422593898300864}),
+    }
+    for (theta, hd, factor, low, high, orig), (kept, full, band) in cases.items():
+        j = np.arange(hd // 2, dtype=np.float32)
+        inv = np.power(np.float32(theta), (np.float32(-2.0) * j / np.float32(hd)).astype(np.float32)).astype(np.float32)
+        div = llama3_divisors(inv, factor, low, high, orig)
+        assert div.dtype == np.float32 and int((div == 1.0).sum()) == kept and int((div == np.float32(factor)).sum()) == full
+        assert len(band) == hd // 2 - kept - full
+        for idx, want in band.items():
+            assert abs(float(div[idx]) - want) <= 3e-6 * want, (hd, idx, float(div[idx]), want)      # inv is float32: 1e-7 relative, amplified near s = 0
+        assert (np.diff(div) >= 0).all()
+
+
+def _write_shards(folder, tensors, split_at, weight_map=None, extra_in_second=None):
+    """Write `tensors` as two shards and an index; the first `split_at` names go to the first shard."""
+    from xyntetik_runner_b200.weights.safetensors_io import write_safetensors
+    names = list(tensors)
+    shards = {"model-00001-of-00002.safetensors": names[:split_at], "model-00002-of-00002.safetensors": names[split_at:]}
+    wm = {}
+    for fn, ns in shards.items():
+        items = [(n, tensors[n]) for n in ns]
+        if fn.startswith("model-00002") and extra_in_second:
+            items += list(extra_in_second.items())
+        write_safetensors(os.path.join(folder, fn), items)
+        wm.update({n: fn for n in ns})
+    with open(os.path.join(folder, "model.safetensors.index.json"), "w") as f:
+        json.dump({"metadata": {}, "weight_map": wm if weight_map is None else weight_map(wm)}, f)
+
+
+def test_sharded_folder_loads_and_its_errors_come_as_one(tmp_path):
+    """Two shards and model.safetensors.index.json (the layout of a real multi-gigabyte checkpoint): the same tensors
+    as the single file; a name stored twice, one that the index does not list, and one that the index lists but no
+    shard holds are all named in ONE error."""
+    src = tiny.make_folder(str(tmp_path / "one"), "B")
+    single = SafetensorsFile(os.path.join(src, "model.safetensors"))
+    tensors = {n: single.get(n).clone() for n in single.names()}
+    specs = _specs("B")
+    good = tmp_path / "two"
+    good.mkdir()
+    shutil.copy(os.path.join(src, "config.json"), good / "config.json")
+    _write_shards(str(good), tensors, split_at=11)
+    got = load_tensors(specs, FolderSource(str(good)), torch.device("cpu"))
+    want = load_tensors(specs, FolderSource(src), torch.device("cpu"))
+    assert set(got) == set(want) and all(torch.equal(got[n], want[n]) for n in want)
+    assert len(FolderSource(str(good)).files) == 2
+    # broken: a tensor of the first shard stored again in the second, one extra tensor that the index does not list,
+    # and the index lists one name more than the shards hold
+    names = list(tensors)
+    bad = tmp_path / "bad"
+    bad.mkdir()
+    _write_shards(str(bad), tensors, split_at=11, extra_in_second={names[0]: tensors[names[0]], "model.stray": torch.zeros(3)},
+                  weight_map=lambda wm: dict(wm, **{"model.ghost.weight": "model-00001-of-00002.safetensors"}))
+    with pytest.raises(WeightsError) as ei:
+        FolderSource(str(bad))
+    msg = str(ei.value)
+    assert "stored twice" in msg and names[0] in msg and "model.stray" in msg and "not in the index" in msg
+    assert "model.ghost.weight" in msg and "in no shard" in msg
+    # the index names a shard that is not there: a clear error as well
+    os.remove(bad / "model-00002-of-00002.safetensors")
+    with pytest.raises(Exception, match="model-00002-of-00002.safetensors"):
+        FolderSource(str(bad))
+    # a name in the index only, nothing else wrong: reported as missing with the other mismatches by load_tensors
+    part = tmp_path / "part"
+    part.mkdir()
+    fewer = {n: t for n, t in tensors.items() if n != "model.norm.weight"}
+    _write_shards(str(part), fewer, split_at=5, weight_map=lambda wm: dict(wm, **{"model.norm.weight": "model-00001-of-00002.safetensors"}))
+    with pytest.raises(WeightsError) as ei:
+        load_tensors(specs, FolderSource(str(part)), torch.device("cpu"))
+    assert ei.value.missing == ["model.norm.weight"]
+
+
+def test_random_values_do_not_depend_on_how_they_are_drawn():
+    """The counter-based generator: a tensor's values are a function of (seed, name, element) alone -- whole or in
+    pieces, whatever else was drawn before -- normal, and the same numbers forever (pinned below: a change of the
+    recipe would change every seeded model)."""
+    from xyntetik_runner_b200.weights import random_fill as rf
+    from xyntetik_runner_b200.weights.loader import RandomSource, TensorSpec
+    key = rf.tensor_key(7, "model.layers.3.mlp.up_proj.weight")
+    whole = rf.normal_values(key, 0, 5000, 0.0, 0.02)
+    assert np.array_equal(np.concatenate([rf.normal_values(key, 0, 1234, 0.0, 0.02), rf.normal_values(key, 1234, 3766, 0.0, 0.02)]), whole)
+    assert np.array_equal(rf.unit_normal_at(key, np.array([4999, 0, 17]))[[1, 2, 0]] * np.float32(0.02), whole[[0, 17, 4999]])
+    assert not np.array_equal(rf.normal_values(rf.tensor_key(7, "other"), 0, 100, 0.0, 0.02), whole[:100])
+    z = rf.normal_values(key, 0, 1 << 18, 0.0, 1.0)
+    assert abs(float(z.mean())) < 0.01 and abs(float(z.std()) - 1) < 0.01 and abs(float((z ** 4).mean()) - 3) < 0.1
+    assert abs(float(np.corrcoef(z[:-1], z[1:])[0, 1])) < 0.01
+    assert rf.unit_normal_at(rf.tensor_key(2, "model.embed_tokens.weight"), np.arange(3)).view(np.uint32).tolist() == PINNED_DRAWS
+    # bfloat16 rounding to nearest even, as torch rounds
+    x = rf.normal_values(key, 0, 4096, 0.0, 1.0)
+    assert np.array_equal(rf.to_bfloat16_bits(x), torch.from_numpy(x).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16))
+    # through the source: the order of fetches and the other tensors' sizes change nothing
+    specs = {"a": TensorSpec((5, 7)), "b": TensorSpec((3,), "vector", "ones_jitter"), "c": TensorSpec((2, 2), init="zeros")}
+    s1 = RandomSource(specs, 11, torch.float32, std=0.1, norm_jitter=0.1)
+    s2 = RandomSource(dict(specs, a2=TensorSpec((900, 9))), 11, torch.float32, std=0.1, norm_jitter=0.1)
+    dev = torch.device("cpu")
+    s2.fetch("a2", dev)
+    for n in ("b", "a", "c"):
+        assert torch.equal(s1.fetch(n, dev), s2.fetch(n, dev))
+    assert float(s1.fetch("c", dev).abs().sum()) == 0 and abs(float(s1.fetch("b", dev).mean()) - 1) < 0.2
+
+
+PINNED_DRAWS = [3197608319, 3192270923, 1071824072]      # float32 bit patterns of z(seed 2, "model.embed_tokens.weight", 0..2)

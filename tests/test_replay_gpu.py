@@ -8,14 +8,15 @@ from plain_llama import PlainLlama
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [5, 11, 17, 70, 130, 41], "B": [1, 9, 33, 70, 150, 64], "C": [3, 29, 66, 100, 129, 48]}
-PAGE = {"A": 16, "B": 8, "C": 64}
+LENGTHS = {"A": [5, 11, 17, 70, 130, 41], "B": [1, 9, 33, 70, 150, 64], "C": [3, 29, 66, 100, 129, 48],
+           "D": [2, 19, 90, 35, 60, 77, 50, 88], "E": [7, 140, 33, 64, 90, 21]}
+PAGE = {"A": 16, "B": 8, "C": 64, "D": 4, "E": 32}
 
 
 @pytest.fixture(scope="module")
 def folders(tmp_path_factory):
     out = {}
-    for name in "ABC":
+    for name in "ABCDE":
         for dt in ("float32", "bfloat16"):
             out[name, dt] = tiny.make_folder(str(tmp_path_factory.mktemp(f"tiny{name}_{dt}")), name, dt)
     return out
@@ -54,7 +55,7 @@ CUTS = {
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("cut", list(CUTS))
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_cutting_matches_plain(folders, reference, name, cut, dtype):
     reqs, ref = reference[name, dtype]
     steps = CUTS[cut](reqs)

@@ -125,6 +125,18 @@ def test_a_lone_request_that_outgrows_the_pool_finishes_with_length():
     assert r.finish_reason == "length" and len(r.tokens) == 13 and cache.free_pages() == [3]
 
 
+def test_a_request_that_planning_ends_is_reported_by_step():
+    """A lone request that can get no further page is ended by the plan itself; step() says so (finished=True),
+    so that a caller who follows step()'s returns sees every request end."""
+    s, _, cache = make(n_pages=3, page=4, budget=64, max_req_tokens=64)
+    s.add(Request("a", list(range(6)), max_new_tokens=100))
+    seen = []
+    while s.has_work():
+        seen += s.step()
+    assert seen[-1] == ("a", None, True) and sum(1 for _, _, done in seen if done) == 1
+    assert [t for _, t, _ in seen if t is not None] == s.finished["a"].generated
+
+
 def test_context_limit_finishes_a_request():
     s, _, _ = make(max_req_tokens=16, page=4)
     s.add(Request("a", list(range(10)), max_new_tokens=100))
@@ -186,6 +198,61 @@ class PipelinedFakeExecutor(FakeExecutor):
 
     def wait(self, handle):
         return handle
+
+
+class FailingExecutor(PipelinedFakeExecutor):
+    """Refuses the launches whose numbers are in `fail_at`, the way the engine's executor does when a kernel
+    refuses or the runtime fails before the step is whole: the plan's reservations are given back, then it raises."""
+
+    def __init__(self, cache, stop_at=None, fail_at=()):
+        super().__init__(cache, stop_at)
+        self.fail_at, self.n_launches, self.failed = set(fail_at), 0, 0
+
+    def launch(self, plan, feed_rows=None):
+        self.n_launches += 1
+        if self.n_launches in self.fail_at:
+            for e in plan.entries:
+                self.cache.cancel(e.request.id)
+            self.failed += 1
+            raise RuntimeError("injected: the step failed before it was whole")
+        return super().launch(plan, feed_rows)
+
+
+@pytest.mark.parametrize("ahead", [False, True])
+@pytest.mark.parametrize("seed", range(4))
+def test_a_step_that_fails_to_launch_changes_no_token(seed, ahead):
+    """Launches fail now and then (also launches ahead of their turn, also in steps that admitted or preempted):
+    the caller sees the exception, calls step() again, and every request ends with the tokens and the reason of a
+    run without failures; no page is lost."""
+    outcomes = []
+    for fail_at in ((), (2, 3, 7, 11, 12, 20, 33, 34, 35, 50)):
+        rng = np.random.RandomState(300 + seed)
+        n_pages, page = int(rng.randint(14, 40)), 4
+        cache = CacheManager([GroupSpec("full")], n_pages, page, 4, 60)
+        sizes = [(int(rng.randint(1, 20)), int(rng.randint(1, 25))) for _ in range(10)]
+        stops = {(i, sizes[i][0] + int(rng.randint(1, sizes[i][1] + 1))): 7 for i in range(0, 10, 3)}
+        ex = FailingExecutor(cache, stops, fail_at)
+        s = Scheduler(cache, ex, SchedulerParams(max_step_tokens=int(rng.randint(8, 30)), prefill_chunk=int(rng.randint(3, 12)),
+                                                 look_ahead=ahead))
+        for i, (n, k) in enumerate(sizes):
+            s.add(Request(i, [int(t) for t in rng.randint(10, 50, size=n)], max_new_tokens=k, stop_ids=(7,)))
+        steps = raised = 0
+        while s.has_work():
+            try:
+                s.step()
+            except RuntimeError:
+                raised += 1
+            steps += 1
+            cache.audit()
+            for r in s.live:                      # nothing reserved is left over between steps, failed or not
+                assert cache.reserved(r.id) == 0 or s._ahead is not None
+            assert steps < 5000
+        assert cache.free_pages() == [n_pages] and not cache.live_requests()
+        if fail_at:
+            assert ex.failed >= 5 and raised + s.stats.get("ahead_launches_failed", 0) == ex.failed
+            assert ahead == (s.stats.get("ahead_launches_failed", 0) > 0) or not ahead
+        outcomes.append({i: (r.generated, r.finish_reason) for i, r in s.finished.items()})
+    assert outcomes[0] == outcomes[1]
 
 
 @pytest.mark.parametrize("seed", range(6))

@@ -33,7 +33,7 @@ def _define():
     from xyntetik_runner_b200.config.registry import register_architecture
     from xyntetik_runner_b200.engine.model import ModelPlan, ScheduleEntry
     from xyntetik_runner_b200.parts import (Embedding, FeedForward, GQAAttention, Head, Mixer, NoPosition, Norm,
-                                            PositionEncoding, PreNormBlock, RMSNorm, StateNeed, SwiGLU, make,
+                                            PositionEncoding, PreNormBlock, RMSNorm, Rotary, StateNeed, SwiGLU, make,
                                             register_feed_forward, register_mixer, register_norm, register_position)
     from xyntetik_runner_b200.weights.loader import TensorSpec
 
@@ -105,6 +105,9 @@ def _define():
 
         def prepare(self, rt):
             self.inv_freq = torch.from_numpy(self.inv_freq_host.copy()).to(rt.device)
+
+        def rotary(self):
+            return Rotary(self.rotary_dim, self.inv_freq)
 
     class CentredNorm(Norm):
         """out = (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps): no weights, float32."""

@@ -37,8 +37,23 @@ TINY_C = {
     "attention_bias": True, "hidden_act": "silu", "torch_dtype": "float32", "sliding_window": 24,
     "layer_types": ["sliding_attention", "full_attention", "sliding_attention"],
 }
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
-SEEDS = {"A": 0, "B": 1, "C": 2}
+# head sizes that are no multiple of 16 (config.json allows any even size, src/model.c:2316-2322): 24 with as many
+# kv heads as heads, and 100 -- the head size of a 3,200-wide model with 32 heads -- with biases and linear
+# position scaling
+TINY_D = {
+    "architectures": ["LlamaForCausalLM"], "hidden_size": 72, "num_hidden_layers": 2, "num_attention_heads": 3,
+    "num_key_value_heads": 3, "head_dim": 24, "intermediate_size": 104, "vocab_size": 211, "rms_norm_eps": 2e-5,
+    "rope_theta": 10000.0, "rope_scaling": None, "max_position_embeddings": 1024, "tie_word_embeddings": True,
+    "hidden_act": "silu", "torch_dtype": "float32",
+}
+TINY_E = {
+    "architectures": ["LlamaForCausalLM"], "hidden_size": 200, "num_hidden_layers": 2, "num_attention_heads": 2,
+    "num_key_value_heads": 1, "head_dim": 100, "intermediate_size": 144, "vocab_size": 150, "rms_norm_eps": 1e-6,
+    "rope_theta": 30000.0, "rope_scaling": {"rope_type": "linear", "factor": 2.5}, "max_position_embeddings": 1024,
+    "tie_word_embeddings": False, "attention_bias": True, "hidden_act": "silu", "torch_dtype": "float32",
+}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
+SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3, "E": 4}
 
 
 def make_folder(path: str, name: str, dtype: str = "float32", std: float = 0.1) -> str:

@@ -188,6 +188,10 @@ class CacheManager:
     def length(self, request_id) -> int:
         return self._L.xrh_length(self._h, self._slot(request_id))
 
+    def reserved(self, request_id) -> int:
+        """Tokens reserved for a step that has not been committed or cancelled yet."""
+        return self._L.xrh_reserved(self._h, self._slot(request_id))
+
     def is_open(self, request_id) -> bool:
         return request_id in self._slots
 

@@ -175,6 +175,8 @@ struct RopeStoreArgs {
     long long page_stride;       // elements between pages
     long long v_offset;          // elements from a layer's K block to its V block
     int n, H, K, hd, rotary_dim, max_pages, page_size;
+    int adjacent;                // 0: pair j is elements (j, j + rotary_dim/2); 1: elements (2j, 2j + 1)
+    float mscale;                // factor on the cosines and sines (1 unless the position encoding scales magnitudes)
 };
 
 // One block per token.  A thread owns pair index j (and every `blockDim.x / half`-th head): the angle
@@ -200,13 +202,14 @@ __global__ void k_rope_store(RopeStoreArgs a) {
         const int j = threadIdx.x % half, h0 = threadIdx.x / half;
         if (threadIdx.x < lanes * half) {
             float ang = (float)pos * a.inv_freq[j];
-            float c = cosf(ang), s = sinf(ang);
+            float c = cosf(ang) * a.mscale, s = sinf(ang) * a.mscale;
+            const int i0 = a.adjacent ? 2 * j : j, i1 = a.adjacent ? 2 * j + 1 : j + half;
             for (int head = h0; head < a.H + a.K; head += lanes) {
                 T* src = row + (size_t)head * a.hd;
-                float x0 = xr_to_f32<T>(src[j]), x1 = xr_to_f32<T>(src[j + half]);
+                float x0 = xr_to_f32<T>(src[i0]), x1 = xr_to_f32<T>(src[i1]);
                 T y0 = xr_from_f32<T>(x0 * c - x1 * s), y1 = xr_from_f32<T>(x0 * s + x1 * c);
-                if (head < a.H) { src[j] = y0; src[j + half] = y1; }
-                else if (kdst) { T* d = kdst + (size_t)(head - a.H) * head_step; d[j] = y0; d[j + half] = y1; }
+                if (head < a.H) { src[i0] = y0; src[i1] = y1; }
+                else if (kdst) { T* d = kdst + (size_t)(head - a.H) * head_step; d[i0] = y0; d[i1] = y1; }
             }
         }
     }
@@ -247,8 +250,8 @@ k_rope_store_vec(RopeStoreArgs a) {
     const size_t head_step = (size_t)a.page_size * a.hd;
     for (int j = threadIdx.x; j < half; j += blockDim.x) {
         float ang = (float)pos * a.inv_freq[j];
-        rope_cs[j] = cosf(ang);
-        rope_cs[half + j] = sinf(ang);
+        rope_cs[j] = cosf(ang) * a.mscale;
+        rope_cs[half + j] = sinf(ang) * a.mscale;
     }
     __syncthreads();
     xr_pdl_wait();
@@ -256,6 +259,21 @@ k_rope_store_vec(RopeStoreArgs a) {
     const int rot_heads = kdst ? a.H + a.K : a.H;      // without a cache to write, K is not needed
     for (int u = threadIdx.x; u < rot_heads * groups; u += blockDim.x) {
         int head = u / groups, j0 = (u % groups) << 3;
+        if (a.adjacent) {
+            // eight pairs are sixteen consecutive elements: two vectors, each bfloat162 one pair
+            __nv_bfloat16* src = row + (size_t)head * a.hd + 2 * j0;
+            Bf16x8 v[2] = {*reinterpret_cast<const Bf16x8*>(src), *reinterpret_cast<const Bf16x8*>(src + 8)};
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                float2 x = __bfloat1622float2(v[k >> 2].p[k & 3]);
+                float c = rope_cs[j0 + k], sn = rope_cs[half + j0 + k];
+                v[k >> 2].p[k & 3] = __floats2bfloat162_rn(x.x * c - x.y * sn, x.x * sn + x.y * c);
+            }
+            __nv_bfloat16* dst = head < a.H ? src : kdst + (size_t)(head - a.H) * head_step + 2 * j0;
+            *reinterpret_cast<Bf16x8*>(dst) = v[0];
+            *reinterpret_cast<Bf16x8*>(dst + 8) = v[1];
+            continue;
+        }
         __nv_bfloat16* src = row + (size_t)head * a.hd + j0;
         Bf16x8 lo = *reinterpret_cast<const Bf16x8*>(src), hi = *reinterpret_cast<const Bf16x8*>(src + half);
 #pragma unroll
@@ -286,12 +304,12 @@ k_rope_store_vec(RopeStoreArgs a) {
 XR_EXPORT int xr_rope_store(void* qkv, int dtype, const int* positions, const int* tok_seg, const int* block_tables,
                             const float* inv_freq, void* cache_k, long long page_stride, long long v_offset,
                             int n, int H, int K, int hd, int rotary_dim, int max_pages, int page_size,
-                            cudaStream_t stream) {
+                            int adjacent_pairs, float mscale, cudaStream_t stream) {
     if (n < 1 || H < 1 || K < 1 || hd < 1 || rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1) ||
         page_size < 1 || H + 2 * K > 65535)
         return XR_ERR_ARG;
     RopeStoreArgs a{qkv, positions, tok_seg, block_tables, inv_freq, cache_k, page_stride, v_offset,
-                    n, H, K, hd, rotary_dim, max_pages, page_size};
+                    n, H, K, hd, rotary_dim, max_pages, page_size, adjacent_pairs ? 1 : 0, mscale};
     int threads = 256;
     if (dtype == XR_BF16 && (hd & 7) == 0 && (rotary_dim & 15) == 0 && ((uintptr_t)qkv & 15) == 0 &&
         (cache_k == nullptr || ((((uintptr_t)cache_k) & 15) == 0 && (page_stride & 7) == 0 && (v_offset & 7) == 0))) {

@@ -254,6 +254,8 @@ struct FinishRopeArgs {
     const int* positions; const int* tok_seg; const int* block_tables; const float* inv_freq;
     __nv_bfloat16* cache_k; long long page_stride, v_offset;
     int n, H, K, hd, rotary_dim, max_pages, page_size;
+    int adjacent;                    // pairs (2j, 2j + 1) instead of (j, j + rotary_dim/2)
+    float mscale;                    // factor on the cosines and sines
 };
 
 __global__ void k_finish_rope_store(FinishRopeArgs a) {
@@ -272,25 +274,24 @@ __global__ void k_finish_rope_store(FinishRopeArgs a) {
         int page = a.block_tables[(size_t)a.tok_seg[t] * a.max_pages + pos / a.page_size];
         dst = a.cache_k + (size_t)page * a.page_stride + (is_k ? 0 : a.v_offset) + ((size_t)kvh * a.page_size + (pos % a.page_size)) * a.hd;
     }
+    // A thread's unit is a pair (its index below half, in a head that is rotated) or a single element that is not
+    // rotated (the tail of a Q or K head beyond the rotated width, and all of V).
+    const bool rotated = is_q || is_k;
     const int j_mine = threadIdx.x;                            // the block is as wide as the head for the usual head sizes
-    float cos_mine = 1.f, sin_mine = 0.f, bias0 = 0.f, bias1 = 0.f;
-    if (j_mine < half && (is_q || is_k)) {
+    float cos_mine = 1.f, sin_mine = 0.f;
+    if (j_mine < half && rotated) {
         float ang = (float)pos * a.inv_freq[j_mine];
-        cos_mine = cosf(ang); sin_mine = sinf(ang);
-    }
-    if (a.bias != nullptr && j_mine < a.hd) {
-        bias0 = a.bias[col0 + j_mine];
-        if (j_mine < half && (is_q || is_k)) bias1 = a.bias[col0 + j_mine + half];
+        cos_mine = cosf(ang) * a.mscale; sin_mine = sinf(ang) * a.mscale;
     }
     xr_pdl_wait();
-    for (int j = threadIdx.x; j < a.hd; j += blockDim.x) {
-        bool rot_lo = (is_q || is_k) && j < half;
-        bool rot_hi = (is_q || is_k) && j >= half && j < 2 * half;
-        if (rot_hi) continue;                                 // written by the thread that owns j - half
+    const int units = rotated ? a.hd - half : a.hd;            // pairs first, then the elements beyond them
+    for (int u = threadIdx.x; u < units; u += blockDim.x) {
+        const bool pair = rotated && u < half;
+        const int i0 = pair ? (a.adjacent ? 2 * u : u) : (rotated ? u + half : u);
+        const int i1 = pair ? (a.adjacent ? 2 * u + 1 : u + half) : i0;
         // the loads of eight splits are in flight together (indices clamped, so that none is conditional); the sums
         // are taken in split order
         float v0 = 0.f, v1 = 0.f;
-        const int j1 = rot_lo ? j + half : j;
         const size_t split_stride = (size_t)a.n * qkv_dim;
         const float* p0 = a.partial + (size_t)t * qkv_dim + col0;
         for (int s0 = 0; s0 < a.splits; s0 += 8) {
@@ -298,8 +299,8 @@ __global__ void k_finish_rope_store(FinishRopeArgs a) {
 #pragma unroll
             for (int q = 0; q < 8; q++) {
                 const float* p = p0 + (size_t)min(s0 + q, a.splits - 1) * split_stride;
-                x0[q] = xr_ld_now(p + j);
-                x1[q] = xr_ld_now(p + j1);
+                x0[q] = xr_ld_now(p + i0);
+                x1[q] = xr_ld_now(p + i1);
             }
 #pragma unroll
             for (int q = 0; q < 8; q++) { xr_ld_fence(x0[q]); xr_ld_fence(x1[q]); }
@@ -307,23 +308,22 @@ __global__ void k_finish_rope_store(FinishRopeArgs a) {
             for (int q = 0; q < 8; q++) {
                 const bool live = s0 + q < a.splits;
                 v0 += live ? x0[q] : 0.f;
-                v1 += (live && rot_lo) ? x1[q] : 0.f;
+                v1 += (live && pair) ? x1[q] : 0.f;
             }
         }
-        if (j == j_mine) { v0 += bias0; v1 += bias1; }
-        else if (a.bias) { v0 += a.bias[col0 + j]; if (rot_lo) v1 += a.bias[col0 + j + half]; }
-        if (rot_lo) {
+        if (a.bias) { v0 += a.bias[col0 + i0]; if (pair) v1 += a.bias[col0 + i1]; }
+        if (pair) {
             // the product's output is rounded to the activation dtype before the rotation, as on the unfused path
             v0 = __bfloat162float(__float2bfloat16_rn(v0)); v1 = __bfloat162float(__float2bfloat16_rn(v1));
             float c = cos_mine, s = sin_mine;
-            if (j != j_mine) {                                // a head wider than the block: later rounds
-                float ang = (float)pos * a.inv_freq[j];
-                c = cosf(ang); s = sinf(ang);
+            if (u != j_mine) {                                // a head wider than the block: later rounds
+                float ang = (float)pos * a.inv_freq[u];
+                c = cosf(ang) * a.mscale; s = sinf(ang) * a.mscale;
             }
-            dst[j] = __float2bfloat16_rn(v0 * c - v1 * s);
-            dst[j + half] = __float2bfloat16_rn(v0 * s + v1 * c);
+            dst[i0] = __float2bfloat16_rn(v0 * c - v1 * s);
+            dst[i1] = __float2bfloat16_rn(v0 * s + v1 * c);
         } else {
-            dst[j] = __float2bfloat16_rn(v0);
+            dst[i0] = __float2bfloat16_rn(v0);
         }
     }
 }
@@ -331,12 +331,13 @@ __global__ void k_finish_rope_store(FinishRopeArgs a) {
 XR_EXPORT int xr_finish_rope_store(const float* partial, int splits, const float* bias, void* qkv, const int* positions,
                                    const int* tok_seg, const int* block_tables, const float* inv_freq, void* cache_k,
                                    long long page_stride, long long v_offset, int n, int H, int K, int hd, int rotary_dim,
-                                   int max_pages, int page_size, cudaStream_t stream) {
+                                   int max_pages, int page_size, int adjacent_pairs, float mscale, cudaStream_t stream) {
     if (n < 1 || H < 1 || K < 1 || hd < 1 || rotary_dim < 0 || rotary_dim > hd || (rotary_dim & 1) || page_size < 1 ||
         splits < 1 || H + 2 * K > 65535)
         return XR_ERR_ARG;
     FinishRopeArgs a{partial, splits, bias, (__nv_bfloat16*)qkv, positions, tok_seg, block_tables, inv_freq,
-                     (__nv_bfloat16*)cache_k, page_stride, v_offset, n, H, K, hd, rotary_dim, max_pages, page_size};
+                     (__nv_bfloat16*)cache_k, page_stride, v_offset, n, H, K, hd, rotary_dim, max_pages, page_size,
+                     adjacent_pairs ? 1 : 0, mscale};
     int threads = hd >= 128 ? 128 : (hd >= 64 ? 64 : 32);
     xr_launch(k_finish_rope_store, dim3(n, H + 2 * K), dim3(threads), 0, stream, a);
     return xr_launch_status();

@@ -221,7 +221,8 @@ class Engine:
         return slot
 
     # ---- the step ----------------------------------------------------------------
-    def step(self, entries: Sequence[StepEntry], reserved: bool = False, feed: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], reserved: bool = False, feed: Optional[torch.Tensor] = None,
+             commit: bool = True) -> torch.Tensor:
         """Run one batch.  Returns float32 logits [number of wanted places, vocab] on the device, in the
         order of the entries and of each entry's `want`; the tensor is reused by the next step.
 
@@ -229,7 +230,15 @@ class Engine:
         feed[j] as it is when this step runs, e.g. what the step before sampled, which the host has not read yet.
 
         Unless `reserved`, pages for every entry's tokens are taken here (all or nothing: on
-        ``OutOfPages`` the cache is as before the call).  A request not seen before is opened."""
+        ``OutOfPages`` the cache is as before the call).  A request not seen before is opened.
+
+        A step that fails owns no row of the cache (the reference's rule for a position handed out for a forward
+        that never ran, src/engine.c:1917-1925): whatever is raised between the reservation and the last launch --
+        a kernel refusing its sizes, the runtime refusing a launch, an allocation that fails -- the reservations
+        of every entry are given back, the caller's too when `reserved`, requests that this call opened are closed,
+        and the exception goes on to the caller; the same entries can then be run again.  With ``commit=False``
+        the caller finishes the step itself: ``commit_step`` once everything that belongs to it (sampling) has
+        been launched, ``cancel_step`` if that failed."""
         entries = [e for e in entries if len(e.tokens) > 0]
         if not entries:
             return torch.empty((0, self.plan.vocab_size), dtype=torch.float32, device=self.device)
@@ -241,33 +250,45 @@ class Engine:
             for w in e.want:
                 if not (0 <= w < len(e.tokens)):
                     raise ValueError(f"request {e.request!r}: wanted place {w} is outside its {len(e.tokens)} tokens")
-        opened, taken = [], []
-        if not reserved:
-            try:
+        opened: List[object] = []
+        try:
+            if not reserved:
                 for e in entries:
                     if not self.cache.is_open(e.request):
                         self._open(e.request)
                         opened.append(e.request)
                     self.cache.reserve(e.request, len(e.tokens))
-                    taken.append(e.request)
-            except OutOfPages:
-                for r in taken:
-                    self.cache.cancel(r)
-                for r in opened:
-                    self.cache.close(r)
-                raise
-        ctx = self._describe(entries)
-        ctx.token_feed = feed
-        if ctx.decode_only and self._graph_ok:
-            logits = self._forward_graphed(ctx)
-        else:
-            logits = self._forward(ctx)
+            ctx = self._describe(entries)
+            ctx.token_feed = feed
+            if ctx.decode_only and self._graph_ok:
+                logits = self._forward_graphed(ctx)
+            else:
+                logits = self._forward(ctx)
+        except BaseException:
+            self.cancel_step(entries, opened)
+            raise
         if ctx.real_rows != ctx.n_rows:
             logits = logits[:ctx.real_rows]          # the filler rows' logits are nobody's
-        for e in entries:
-            self.cache.commit(e.request)
-        self.steps_run += 1
+        if commit:
+            self.commit_step(entries)
         return logits
+
+    def commit_step(self, entries: Sequence[StepEntry]) -> None:
+        """The step's launches are all queued: its tokens now count as held by their requests."""
+        for e in entries:
+            if len(e.tokens) > 0:
+                self.cache.commit(e.request)
+        self.steps_run += 1
+
+    def cancel_step(self, entries: Sequence[StepEntry], opened: Sequence[object] = ()) -> None:
+        """The step did not run to its end: give back what was reserved for it and close the requests in `opened`.
+        Rows that its kernels may have written lie beyond every request's length and are nobody's."""
+        for e in entries:
+            if self.cache.is_open(e.request):
+                self.cache.cancel(e.request)
+        for r in opened:
+            if self.cache.is_open(r):
+                self.cache.close(r)
 
     def _describe(self, entries: Sequence[StepEntry]) -> StepContext:
         """Flatten the batch and bring its description to the device in one copy."""

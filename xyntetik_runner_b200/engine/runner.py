@@ -58,17 +58,29 @@ class EngineExecutor:
                 assert e.count == 1
                 toks = [-(1 + feed_rows[e.request.id])]
             entries.append(StepEntry(e.request.id, toks, [e.count - 1] if e.wants_token else []))
-        logits = self.engine.step(entries, reserved=True, feed=self.feed)
+        # the engine gives the plan's reservations back if anything in the step fails; so does this method when the
+        # sampling that belongs to the step fails, and only then is the step committed
+        logits = self.engine.step(entries, reserved=True, feed=self.feed, commit=False)
         wanting = [e.request for e in plan.entries if e.wants_token]
-        if not wanting:
-            return InFlight([], None, None)
-        ids = self.sampler.pick(logits, [r.sampler for r in wanting], out=self.feed)
-        host = self._host[self._next]
-        self._next = (self._next + 1) % len(self._host)
-        host[:len(wanting)].copy_(ids, non_blocking=True)                       # device -> host
-        done = torch.cuda.Event()
-        done.record()
-        return InFlight(wanting, host, done)
+        draws = [r.sampler.rng for r in wanting]
+        try:
+            if not wanting:
+                step = InFlight([], None, None)
+            else:
+                ids = self.sampler.pick(logits, [r.sampler for r in wanting], out=self.feed)
+                host = self._host[self._next]
+                self._next = (self._next + 1) % len(self._host)
+                host[:len(wanting)].copy_(ids, non_blocking=True)                       # device -> host
+                done = torch.cuda.Event()
+                done.record()
+                step = InFlight(wanting, host, done)
+        except BaseException:
+            self.engine.cancel_step(entries)
+            for r, state in zip(wanting, draws):
+                r.sampler.rng = state          # a draw made for a step that did not happen is made again
+            raise
+        self.engine.commit_step(entries)
+        return step
 
     def wait(self, step: InFlight) -> Dict[object, int]:
         if not step.wanting:
@@ -82,6 +94,8 @@ class EngineExecutor:
 
 
 class Runner:
+    STATUS_EVERY = 64        # generate() reads the kernels' status word every so many steps (one small device read)
+
     def __init__(self, model: Optional[str] = None, *, config=None, random_seed: Optional[int] = None,
                  dtype: str = "bfloat16", ctx: Optional[int] = None, batch: int = 2048, parallel: int = 8,
                  max_tokens: Optional[int] = None, page_size: int = 64, prefill_chunk: Optional[int] = None,
@@ -159,6 +173,7 @@ class Runner:
                            None if seed is None else seed + i, ignore_eos) for i, p in enumerate(plist)]
         t0 = time.perf_counter()
         sch = self.scheduler
+        steps = 0
         while sch.has_work():
             before = len(sch.finished)
             res = sch.step()
@@ -169,6 +184,9 @@ class Runner:
             if not res and not sch.live and sch.waiting and len(sch.finished) == before:
                 r = sch.waiting.popleft()
                 sch._finish(r, "rejected")
+            steps += 1
+            if steps % self.STATUS_EVERY == 0:
+                self.engine.check_status()       # a kernel that gave up a wait: stop now, not after a run of garbage
         torch.cuda.synchronize(self.engine.device)
         self.engine.check_status()
         self.timing["generate_s"] = time.perf_counter() - t0

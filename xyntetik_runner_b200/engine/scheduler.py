@@ -75,6 +75,7 @@ class PlannedEntry:
 class StepPlan:
     entries: List[PlannedEntry] = field(default_factory=list)
     preempted: List[object] = field(default_factory=list)
+    finished: List[object] = field(default_factory=list)     # requests that planning itself ended (pool too small)
 
     @property
     def n_tokens(self) -> int:
@@ -101,6 +102,7 @@ class Scheduler:
         self.finished: Dict[object, Request] = {}
         self._tick = 0
         self._ahead = None                      # (plan, executor's handle) of a step launched ahead of its turn
+        self._ended_unreported: List[object] = []   # ended by a plan whose step then failed to launch
         self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "preemptions": 0, "max_batch": 0,
                       "steps_launched_ahead": 0}
 
@@ -151,10 +153,13 @@ class Scheduler:
         return False
 
     # ---- planning -----------------------------------------------------------------------
-    def _preempt(self, victim: Request, plan: StepPlan) -> None:
+    def _preempt(self, victim: Request, plan: StepPlan) -> int:
+        """Push `victim` back to the queue.  Returns the tokens of the step's budget that its planned entry held."""
+        given_back = 0
         for e in list(plan.entries):
             if e.request is victim:
                 plan.entries.remove(e)
+                given_back += e.count
         self.cache.cancel(victim.id)
         self.cache.close(victim.id)
         self.live.remove(victim)
@@ -164,6 +169,7 @@ class Scheduler:
         self.waiting.appendleft(victim)
         plan.preempted.append(victim.id)
         self.stats["preemptions"] += 1
+        return given_back
 
     def _fit(self, req: Request, want: int) -> int:
         """Largest portion <= want whose pages can be reserved now (0: none)."""
@@ -199,10 +205,11 @@ class Scheduler:
                 continue
             if len(self.live) == 1:
                 self._finish(r, "length")          # alone and still no page: the pool is its limit
+                plan.finished.append(r.id)
                 continue
             victim = self.live[-1]
             vi = len(self.live) - 1
-            self._preempt(victim, plan)
+            budget += self._preempt(victim, plan)
             if vi < i:
                 i -= 1
             # try the same index again (it is r again unless r itself was the victim)
@@ -241,11 +248,13 @@ class Scheduler:
         # 4. nobody can move: free the newest request's pages for the older ones
         if not plan.entries and self.live:
             if len(self.live) == 1:
+                plan.finished.append(self.live[0].id)
                 self._finish(self.live[0], "length")
             else:
                 self._preempt(self.live[-1], plan)
                 inner = self.plan()
                 inner.preempted = plan.preempted + inner.preempted
+                inner.finished = plan.finished + inner.finished
                 return inner
         return plan
 
@@ -275,11 +284,23 @@ class Scheduler:
             self._ahead = None
             if all(e.request.status == FINISHED for e in plan.entries):
                 plan = handle = None         # every request of it ended in the step before: nothing to collect
+        ended_by_plan: List[object] = []
         if plan is None:
             plan = self.plan()
+            ended_by_plan = plan.finished
             if not plan.entries:
-                return []
-            handle = self.executor.launch(plan) if hasattr(self.executor, "launch") else None
+                return [(rid, None, True) for rid in ended_by_plan]
+            # A step that fails to launch leaves nothing behind: the executor gives the reservations back, and what
+            # planning did (admissions, preemptions) stands as a consistent state from which the next call plans anew.
+            # Requests that planning itself ended are reported by that call.
+            try:
+                handle = self.executor.launch(plan) if hasattr(self.executor, "launch") else None
+            except BaseException:
+                self._ended_unreported.extend(ended_by_plan)
+                raise
+        if self._ended_unreported:
+            ended_by_plan = self._ended_unreported + list(ended_by_plan)
+            self._ended_unreported = []
         advanced = False
         if handle is not None and self.params.look_ahead:
             nxt = self._plan_ahead(plan)
@@ -290,12 +311,33 @@ class Scheduler:
                     e.request.computed += e.count
                     e.request.tokens.append(IN_FLIGHT)
                 rows = {e.request.id: i for i, e in enumerate(plan.entries)}
-                self._ahead = (nxt, self.executor.launch(nxt, feed_rows=rows))
-                self.stats["steps_launched_ahead"] += 1
-        sampled: Dict[object, int] = self.executor.wait(handle) if handle is not None else self.executor.run(plan)
+                try:
+                    self._ahead = (nxt, self.executor.launch(nxt, feed_rows=rows))
+                    self.stats["steps_launched_ahead"] += 1
+                except Exception:
+                    # the step ahead could not be launched (its reservations are given back already): take the marks
+                    # out again and go on as if it had not been tried; the next call plans and launches it in its turn,
+                    # and a fault that lasts is raised from there
+                    advanced = False
+                    self._ahead = None
+                    for e in plan.entries:
+                        e.request.computed -= e.count
+                        e.request.tokens.pop()
+                    self.stats["ahead_launches_failed"] = self.stats.get("ahead_launches_failed", 0) + 1
+        if handle is not None:
+            sampled: Dict[object, int] = self.executor.wait(handle)
+        else:
+            try:
+                sampled = self.executor.run(plan)
+            except BaseException:
+                for e in plan.entries:             # an executor without `launch`: the plan's pages are still reserved
+                    if self.cache.is_open(e.request.id):
+                        self.cache.cancel(e.request.id)
+                self._ended_unreported.extend(ended_by_plan)
+                raise
         self.stats["steps"] += 1
         self.stats["max_batch"] = max(self.stats["max_batch"], len(plan.entries))
-        out = []
+        out = [(rid, None, True) for rid in ended_by_plan]
         limit = self.cache.max_pages_per_request * self.cache.page_size
         for e in plan.entries:
             r = e.request

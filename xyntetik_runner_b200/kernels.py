@@ -49,7 +49,7 @@ def _declare(L: ctypes.CDLL) -> None:
     sig = {
         "xr_embed": [_vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _vp],
         "xr_rmsnorm": [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
-        "xr_rope_store": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _vp],
+        "xr_rope_store": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
         "xr_silu_mul": [_vp, _vp, _i, _i, _i, _vp],
         "xr_residual_add": [_vp, _vp, _i, _i, _i, _vp],
         "xr_gemm_simt": [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _ll, _ll, _vp],
@@ -57,7 +57,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "xr_gemm_tc": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _ll, _ll, _vp, _ll, _vp, _i, _i, ctypes.POINTER(ctypes.c_int), _i, _vp],
         "xr_finish_add_rmsnorm": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
         "xr_finish_plain": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _ll, _vp],
-        "xr_finish_rope_store": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _vp],
+        "xr_finish_rope_store": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
         "xr_attention_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _f,
                              _i, _i, _i, _i, _i, _vp, _ll, _i, _i, _vp, _vp],
         "xr_attention_mma_splits": [_i, _i, _ll],
@@ -135,15 +135,18 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, eps: float, row
 
 def rope_store(qkv: torch.Tensor, positions, tok_seg, block_tables, inv_freq: Optional[torch.Tensor],
                cache_k_ptr: Optional[int], page_stride: int, v_offset: int, H: int, K: int, hd: int,
-               rotary_dim: int, max_pages: int, page_size: int) -> None:
-    """Rotate Q in place, rotate K and store K, V into their pages (cache_k_ptr None: store nothing)."""
+               rotary_dim: int, max_pages: int, page_size: int, adjacent: bool = False, mscale: float = 1.0) -> None:
+    """Rotate Q in place, rotate K and store K, V into their pages (cache_k_ptr None: store nothing).  Pair j of
+    a head is elements (j, j + rotary_dim/2), or (2j, 2j + 1) with `adjacent`; cosines and sines are multiplied
+    by `mscale` (src/model.c:3514-3532)."""
     _dev(qkv, positions, tok_seg, block_tables, inv_freq)
     n = qkv.shape[0]
     assert qkv.shape[1] == (H + 2 * K) * hd
     assert rotary_dim == 0 or (inv_freq is not None and inv_freq.dtype == torch.float32 and inv_freq.numel() >= rotary_dim // 2)
     _check(lib().xr_rope_store(qkv.data_ptr(), dtype_code(qkv.dtype), positions.data_ptr(), tok_seg.data_ptr(),
                                block_tables.data_ptr(), _ptr(inv_freq), cache_k_ptr, page_stride, v_offset,
-                               n, H, K, hd, rotary_dim, max_pages, page_size, _stream()), "rope_store")
+                               n, H, K, hd, rotary_dim, max_pages, page_size, int(adjacent), float(mscale), _stream()),
+           "rope_store")
     _count()
 
 
@@ -344,7 +347,7 @@ def finish_plain(partial: torch.Tensor, splits: int, bias: Optional[torch.Tensor
 def finish_rope_store(partial: torch.Tensor, splits: int, bias: Optional[torch.Tensor], qkv: torch.Tensor, positions,
                       tok_seg, block_tables, inv_freq: Optional[torch.Tensor], cache_k_ptr: Optional[int],
                       page_stride: int, v_offset: int, H: int, K: int, hd: int, rotary_dim: int, max_pages: int,
-                      page_size: int) -> None:
+                      page_size: int, adjacent: bool = False, mscale: float = 1.0) -> None:
     """Sum the partials of the fused QKV product (+ bias), rotate Q and K, write Q into `qkv` and K, V into
     their pages (into `qkv` when cache_k_ptr is None)."""
     _dev(qkv, positions, tok_seg, block_tables, inv_freq, bias)
@@ -352,7 +355,8 @@ def finish_rope_store(partial: torch.Tensor, splits: int, bias: Optional[torch.T
     assert qkv.dtype == torch.bfloat16 and qkv.shape[1] == (H + 2 * K) * hd and partial.numel() >= splits * n * qkv.shape[1]
     _check(lib().xr_finish_rope_store(partial.data_ptr(), splits, _ptr(bias), qkv.data_ptr(), positions.data_ptr(),
                                       tok_seg.data_ptr(), block_tables.data_ptr(), _ptr(inv_freq), cache_k_ptr, page_stride,
-                                      v_offset, n, H, K, hd, rotary_dim, max_pages, page_size, _stream()), "finish_rope_store")
+                                      v_offset, n, H, K, hd, rotary_dim, max_pages, page_size, int(adjacent), float(mscale),
+                                      _stream()), "finish_rope_store")
     _count()
 
 

@@ -1,5 +1,5 @@
 """Parts that layers are put together from; importing this package registers the built-in kinds."""
-from .base import (Block, FeedForward, KVNeed, Mixer, Norm, Part, PositionEncoding, Runtime, StateNeed, kinds, make,
+from .base import (Block, FeedForward, KVNeed, Mixer, Norm, Part, PositionEncoding, Rotary, Runtime, StateNeed, kinds, make,
                    register_block, register_feed_forward, register_mixer, register_norm, register_position)
 from .attention import GQAAttention
 from .block import PreNormBlock

@@ -37,13 +37,14 @@ class GQAAttention(Mixer):
                  q: str = "q_proj", k: str = "k_proj", v: str = "v_proj", o: str = "o_proj"):
         if heads % kv_heads:
             raise ValueError("heads must be a multiple of kv_heads")
-        if head_dim % 16 or head_dim > 256:
-            raise ValueError(f"head_dim {head_dim}: the attention kernels take multiples of 16 up to 256")
+        if not (1 <= head_dim <= 256):
+            raise ValueError(f"head_dim {head_dim}: the attention kernels take head sizes up to 256")
         self.width, self.H, self.K, self.hd = width, heads, kv_heads, head_dim
         self.position, self.prefix, self.bias, self.window = position, prefix, bias, window
         self.scale = 1.0 / math.sqrt(head_dim) if scale is None else float(scale)   # src/model.h:464-467
         self.proj = (q, k, v, o)
         self.qkv = self.out = None
+        self.rot = None
 
     def kv_need(self):
         return KVNeed(self.K, self.hd, self.window)
@@ -71,6 +72,16 @@ class GQAAttention(Mixer):
         del ws
         self.out = Linear(tensors[o + ".weight"], obias).prepare(rt)
         self.position.prepare(rt)
+        try:
+            rot = self.position.rotary()
+        except NotImplementedError as e:
+            raise ValueError(f"{self.prefix}: this mixer takes position encodings that rotate query and key pairs, or "
+                             f"none ({e}); another kind needs a mixer of its own") from None
+        if rot is not None and rot.rotary_dim > self.hd:
+            raise ValueError(f"{self.prefix}: rotary_dim {rot.rotary_dim} exceeds head_dim {self.hd}")
+        # (rotary_dim, inv_freq, adjacent pairs, mscale) as the rotation kernels take them
+        self.rot = (0, None, False, 1.0) if rot is None or rot.rotary_dim == 0 else \
+            (rot.rotary_dim, rot.inv_freq, rot.pairing == "adjacent", rot.mscale)
 
     def weight_bytes(self):
         return self.qkv.nbytes() + self.out.nbytes()
@@ -83,16 +94,17 @@ class GQAAttention(Mixer):
         k_ptr, page_stride, v_offset = ctx.cache_layer(lay)
         bt = ctx.block_tables[lay.group]
         store_ptr = k_ptr if lay.writes_cache else None
+        rot_dim, rot_freq, adjacent, mscale = self.rot
         if pend is not None and lay.writes_cache:
             # the product was split along K: its finish, the rotation and the page store are one kernel
             kernels.finish_rope_store(pend.partial, pend.splits, pend.bias, qkv, ctx.positions, ctx.tok_seg, bt,
-                                      self.position.inv_freq, store_ptr, page_stride, v_offset, self.H, self.K, self.hd,
-                                      self.position.rotary_dim, ctx.max_pages, ctx.page_size)
+                                      rot_freq, store_ptr, page_stride, v_offset, self.H, self.K, self.hd,
+                                      rot_dim, ctx.max_pages, ctx.page_size, adjacent, mscale)
         else:
             if pend is not None:
                 pend.finish()
-            kernels.rope_store(qkv, ctx.positions, ctx.tok_seg, bt, self.position.inv_freq, store_ptr, page_stride,
-                               v_offset, self.H, self.K, self.hd, self.position.rotary_dim, ctx.max_pages, ctx.page_size)
+            kernels.rope_store(qkv, ctx.positions, ctx.tok_seg, bt, rot_freq, store_ptr, page_stride,
+                               v_offset, self.H, self.K, self.hd, rot_dim, ctx.max_pages, ctx.page_size, adjacent, mscale)
         o = ctx.buf("attn_out", (n, self.H * self.hd), ctx.act_dtype)
         # Q is read in place from the fused rows (row stride = qkv_dim)
         G = self.H // self.K

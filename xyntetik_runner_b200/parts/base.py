@@ -72,11 +72,36 @@ class Norm(Part):
         raise NotImplementedError
 
 
+@dataclass(frozen=True)
+class Rotary:
+    """A position encoding that rotates pairs of query and key elements by angle = position * inv_freq[j]
+    (src/model.c:3514-3532): everything the rotation kernels and a mixer need to know of it."""
+    rotary_dim: int                        # leading elements of every head that are rotated (even; 0: none)
+    inv_freq: Optional[torch.Tensor]       # float32 [rotary_dim / 2] on the device (None when rotary_dim is 0)
+    pairing: str = "half"                  # "half": pair j = (j, j + rotary_dim/2); "adjacent": (2j, 2j + 1)
+    mscale: float = 1.0                    # factor on every cosine and sine (src/model.c:283, 375)
+
+    def __post_init__(self):
+        if self.pairing not in ("half", "adjacent"):
+            raise ValueError(f"pairing '{self.pairing}': choose half or adjacent")
+        if self.rotary_dim % 2 or self.rotary_dim < 0:
+            raise ValueError("rotary_dim must be even and not negative")
+
+
 class PositionEncoding:
-    """How positions enter a mixer.  Built once from the configuration; holds no model weights."""
+    """How positions enter a mixer.  Built once from the configuration; holds no model weights.
+
+    The built-in mixer knows one family: rotations of query and key pairs, described by ``rotary()`` after
+    ``prepare``.  A position encoding of another family (a bias on the scores, a scale on the query that depends
+    on the position, learned vectors added to the embedding) needs a mixer or an embedding part written for it;
+    it leaves ``rotary`` unimplemented and the built-in mixer refuses it by name."""
 
     def prepare(self, rt: Runtime) -> None:
         pass
+
+    def rotary(self) -> Optional[Rotary]:
+        """The rotation to apply to queries and keys, or None for no rotation at all."""
+        raise NotImplementedError(f"{type(self).__name__} does not describe itself as a rotation of query and key pairs")
 
 
 class Mixer(Part):

@@ -18,7 +18,7 @@ from typing import Optional
 import numpy as np
 import torch
 
-from .base import PositionEncoding, register_position
+from .base import PositionEncoding, Rotary, register_position
 
 
 def llama3_divisors(inv_freq: np.ndarray, factor: float, low: float, high: float, orig: int) -> np.ndarray:
@@ -37,8 +37,13 @@ def llama3_divisors(inv_freq: np.ndarray, factor: float, low: float, high: float
 
 
 class Rope(PositionEncoding):
-    def __init__(self, head_dim: int, theta: float, rotary_dim: Optional[int] = None, scaling=None):
+    def __init__(self, head_dim: int, theta: float, rotary_dim: Optional[int] = None, scaling=None,
+                 pairing: str = "half", mscale: float = 1.0):
+        """pairing "half" rotates elements (j, j + rotary_dim/2), the layout of a config.json + safetensors
+        checkpoint; "adjacent" rotates (2j, 2j + 1), the layout the reference's llama files carry
+        (src/model.c:1464-1466).  mscale multiplies every cosine and sine (src/model.c:283, 375)."""
         self.head_dim = head_dim
+        self.pairing, self.mscale = pairing, float(mscale)
         self.rotary_dim = head_dim if rotary_dim is None else rotary_dim
         if self.rotary_dim % 2 or self.rotary_dim > head_dim or self.rotary_dim < 0:
             raise ValueError("rotary_dim must be even and at most head_dim")
@@ -58,11 +63,15 @@ class Rope(PositionEncoding):
     def prepare(self, rt):
         self.inv_freq = torch.from_numpy(self.inv_freq_host.copy()).to(rt.device)
 
+    def rotary(self):
+        return Rotary(self.rotary_dim, self.inv_freq if self.rotary_dim else None, self.pairing, self.mscale)
+
 
 class NoPosition(PositionEncoding):
     """No position signal of its own (order comes from the causal mask alone)."""
-    rotary_dim = 0
-    inv_freq = None
+
+    def rotary(self):
+        return None
 
 
 register_position("rope", Rope)

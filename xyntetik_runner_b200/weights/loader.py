@@ -16,12 +16,13 @@ they bind.
 from __future__ import annotations
 
 import hashlib
+import os
 from dataclasses import dataclass
 from typing import Dict, List, Mapping, Tuple
 
 import torch
 
-from .safetensors_io import SafetensorsFile, open_model_files
+from .safetensors_io import SafetensorsFile, open_model_files, read_weight_map
 
 
 @dataclass(frozen=True)
@@ -67,14 +68,23 @@ class FolderSource(TensorSource):
         self.where = model_dir
         self.files: List[SafetensorsFile] = open_model_files(model_dir)
         self._owner: Dict[str, SafetensorsFile] = {}
-        dup = []
+        wm = read_weight_map(model_dir)
+        odd: List[str] = []
         for f in self.files:
+            shard = os.path.basename(f.path)
             for n in f.names():
                 if n in self._owner:
-                    dup.append(n)
+                    odd.append(f"{n} (stored twice: {os.path.basename(self._owner[n].path)} and {shard})")
+                elif wm is not None and n not in wm:
+                    odd.append(f"{n} (in {shard} but not in the index)")
+                elif wm is not None and wm[n] != shard:
+                    odd.append(f"{n} (in {shard}, the index says {wm[n]})")
                 self._owner[n] = f
-        if dup:
-            raise WeightsError(model_dir, [], [f"{n} (stored twice)" for n in dup], [], [])
+        # a name that the index lists but no shard holds is simply absent from the listing: load_tensors reports it
+        # as missing together with everything else
+        self.index_only = sorted(n for n in (wm or {}) if n not in self._owner)
+        if odd:
+            raise WeightsError(model_dir, [f"{n} (in the index, in no shard)" for n in self.index_only], odd, [], [])
 
     def listing(self):
         return {n: (f.tensors[n].dtype, f.tensors[n].shape) for n, f in self._owner.items()}

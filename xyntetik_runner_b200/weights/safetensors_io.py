@@ -15,7 +15,7 @@ import mmap
 import os
 import struct
 from dataclasses import dataclass
-from typing import Dict, Iterable, Iterator, List, Tuple
+from typing import Optional, Dict, Iterable, Iterator, List, Tuple
 
 import torch
 
@@ -107,20 +107,38 @@ class SafetensorsFile:
         self._f.close()
 
 
+def read_weight_map(model_dir: str) -> Optional[Dict[str, str]]:
+    """{tensor name: shard file} of model.safetensors.index.json, or None for a folder with a single file."""
+    if os.path.isfile(os.path.join(model_dir, "model.safetensors")):
+        return None
+    index = os.path.join(model_dir, "model.safetensors.index.json")
+    if not os.path.isfile(index):
+        raise SafetensorsError(f"{model_dir}: no model.safetensors (nor an index) found")
+    try:
+        with open(index, "r", encoding="utf-8") as f:
+            wm = json.load(f).get("weight_map")
+    except (OSError, ValueError) as e:
+        raise SafetensorsError(f"{index}: {e}") from None
+    if not isinstance(wm, dict) or not wm or not all(isinstance(k, str) and isinstance(v, str) for k, v in wm.items()):
+        raise SafetensorsError(f"{index}: weight_map must map tensor names to file names")
+    for fn in wm.values():
+        if os.path.basename(fn) != fn:
+            raise SafetensorsError(f"{index}: shard '{fn}' is not a plain file name")
+    return wm
+
+
 def open_model_files(model_dir: str) -> List[SafetensorsFile]:
     """The safetensors files of a model folder: the single file, or the shards an index names."""
-    single = os.path.join(model_dir, "model.safetensors")
-    index = os.path.join(model_dir, "model.safetensors.index.json")
-    if os.path.isfile(single):
-        return [SafetensorsFile(single)]
-    if os.path.isfile(index):
-        with open(index, "r", encoding="utf-8") as f:
-            wm = json.load(f).get("weight_map", {})
-        files = sorted(set(wm.values()))
-        if not files:
-            raise SafetensorsError(f"{index}: empty weight_map")
-        return [SafetensorsFile(os.path.join(model_dir, fn)) for fn in files]
-    raise SafetensorsError(f"{model_dir}: no model.safetensors (nor an index) found")
+    wm = read_weight_map(model_dir)
+    if wm is None:
+        return [SafetensorsFile(os.path.join(model_dir, "model.safetensors"))]
+    out = []
+    for fn in sorted(set(wm.values())):
+        path = os.path.join(model_dir, fn)
+        if not os.path.isfile(path):
+            raise SafetensorsError(f"{model_dir}: the index names shard '{fn}', which is not there")
+        out.append(SafetensorsFile(path))
+    return out
 
 
 def write_safetensors(path: str, tensors: Iterable[Tuple[str, torch.Tensor]], metadata: Dict[str, str] = None,
