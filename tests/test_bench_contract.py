@@ -1,5 +1,5 @@
 """What bench.py answers without a GPU: more than one GPU is refused with exit code 2 and one line; the reference
-arm prints its `unavailable` record and exits 0."""
+arm, which needs a GPU to draw the model it gives the reference program, prints its `unavailable` record and exits 0."""
 import json
 import os
 import subprocess
@@ -17,7 +17,7 @@ def test_more_than_one_gpu_is_refused():
     assert r.returncode == 2 and len(r.stdout.strip().splitlines()) == 1 and "N=2" in r.stdout
 
 
-def test_reference_arm_is_unavailable():
+def test_reference_arm_answers_in_one_line_without_a_gpu():
     r = run("--impl", "reference", "--gpus", "1", "--steps", "2", "--warmup", "1")
     assert r.returncode == 0
     d = json.loads(r.stdout)
