@@ -135,19 +135,21 @@ def rope_inv_freq(theta: float, rope_dim: int, scaling=None) -> np.ndarray:
     return out
 
 
-def rope_apply(v: np.ndarray, positions: np.ndarray, inv_freq: np.ndarray) -> np.ndarray:
-    """v: [T, heads, hd].  a = pos * f_j in float32; (x0, x1) -> (x0 c - x1 s, x0 s + x1 c) on the
-    pairs (j, j + half) (src/model.c:3514-3532 with rope_neox; mscale = 1)."""
+def rope_apply(v: np.ndarray, positions: np.ndarray, inv_freq: np.ndarray, adjacent: bool = False, mscale: float = 1.0) -> np.ndarray:
+    """v: [T, heads, hd].  a = pos * f_j in float32; (c, s) = (cos a, sin a) * mscale; (x0, x1) -> (x0 c - x1 s,
+    x0 s + x1 c) on the pairs (j, j + half), the reference's `rope_neox` branch, or on (2j, 2j + 1) with
+    `adjacent`, its branch for files with permuted rows (src/model.c:3514-3532; mscale src/model.c:283, 375)."""
     T, nh, hd = v.shape
     half = inv_freq.shape[0]
     a = (positions.astype(F32)[:, None] * inv_freq[None, :]).astype(F32)      # float32 product
-    c = np.cos(a.astype(np.float64)).astype(F32)[:, None, :]
-    s = np.sin(a.astype(np.float64)).astype(F32)[:, None, :]
+    c = (np.cos(a.astype(np.float64)).astype(F32) * F32(mscale)).astype(F32)[:, None, :]
+    s = (np.sin(a.astype(np.float64)).astype(F32) * F32(mscale)).astype(F32)[:, None, :]
     out = v.copy()
-    x0 = v[:, :, :half]
-    x1 = v[:, :, half:2 * half]
-    out[:, :, :half] = (x0 * c - x1 * s).astype(F32)
-    out[:, :, half:2 * half] = (x0 * s + x1 * c).astype(F32)
+    i0 = np.arange(0, 2 * half, 2) if adjacent else np.arange(half)
+    i1 = i0 + 1 if adjacent else i0 + half
+    x0, x1 = v[:, :, i0], v[:, :, i1]
+    out[:, :, i0] = (x0 * c - x1 * s).astype(F32)
+    out[:, :, i1] = (x0 * s + x1 * c).astype(F32)
     return out
 
 

@@ -29,3 +29,15 @@ def test_prompt_forms():
 def test_refusals_before_anything_is_loaded(capsys):
     assert main(["-p", "x"]) == 2 and "-m MODEL is required" in capsys.readouterr().err
     assert main(["-m", "folder", "-p", "x", "-s", "0"]) == 2 and "refused" in capsys.readouterr().err
+
+
+def test_ref_runs_the_plain_implementation_without_a_gpu(tmp_path, capsys):
+    """--ref: greedy tokens of the plain implementation, from the same folder and prompt syntax as the engine's."""
+    import tiny
+    from plain_llama import PlainLlama
+    folder = tiny.make_folder(str(tmp_path / "a"), "A")
+    assert main(["-m", folder, "-p", "ids:7,8,9,200", "-n", "5", "--ref", "--ignore-eos", "-t", "2"]) == 0
+    out = capsys.readouterr().out.strip()
+    bos = tiny.TINY_A["bos_token_id"]
+    assert out == "ids:" + ",".join(str(t) for t in PlainLlama(folder).generate_greedy([bos, 7, 8, 9, 200], 5))
+    assert main(["-m", folder, "-p", "x", "--ref", "--temp", "0.5"]) == 2

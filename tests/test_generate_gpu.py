@@ -244,6 +244,27 @@ def test_command_line(folders, tmp_path):
     assert out.returncode == 2 and "refused" in out.stderr
 
 
+def test_context_fitted_to_memory_and_batched_bench_json(folders):
+    """-c 0 (the reference's auto-fit): the context is the model's limit when memory allows; --bench-json with
+    --parallel runs that many 512-token prompts at once and reports the phases' rates with a per-kernel table."""
+    from xyntetik_runner_b200.cli import main
+    from xyntetik_runner_b200.engine.runner import Runner
+    folder = folders["A", "bfloat16"]
+    r = Runner(folder, ctx=0, parallel=2, page_size=16)
+    assert r.engine.cache.max_pages_per_request * 16 == 1024        # tiny A's max_position_embeddings
+    del r
+    import contextlib
+    import io
+    buf = io.StringIO()
+    with contextlib.redirect_stdout(buf):
+        assert main(["-m", folder, "--bench-json", "-n", "12", "--parallel", "3", "-c", "0", "--page-size", "16"]) == 0
+    d = json.loads(buf.getvalue().strip().splitlines()[-1])
+    assert d["batch"] == 3 and d["prompt_tokens"] == 3 * 512 and d["gen_tokens"] == 36 and d["gen_tok_s"] > 0 and d["prompt_tok_s"] > 0
+    names = [row["kernel"] for row in d["kernels"]]
+    assert any("attention" in n for n in names) and any("head product" in n for n in names)
+    assert all(row["us"] > 0 and 0 <= row["frac"] < 1.5 for row in d["kernels"])      # (a tiny model: fractions near zero)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_scoring(folders, dtype):
     """Runner.score (the reference's --score): per-token log-probabilities of a prompt, whatever the portion."""

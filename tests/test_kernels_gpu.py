@@ -49,22 +49,59 @@ def test_gemm_tc(n, n_out, k, epi):
         assert err <= tol * scale, f"splits={splits}: max err {err:.3e} vs {tol * scale:.3e}"
 
 
+def _activation(name, g):
+    if name == "silu":
+        return torch.where(g < -80, torch.zeros_like(g), g / (1 + torch.exp(-g)))
+    if name == "gelu_tanh":
+        return 0.5 * g * (1 + torch.tanh(0.7978845608 * (g + 0.044715 * g ** 3)))
+    return g
+
+
+@pytest.mark.parametrize("act", ["silu", "gelu_tanh", "none"])
 @pytest.mark.parametrize("n,F,k", [(1, 128, 64), (7, 176, 72), (3, 40, 72), (5, 64, 64), (8, 200, 1024), (16, 1000, 520), (33, 300, 256), (256, 256, 128), (70, 1024, 512), (300, 200, 264), (600, 384, 128), (2500, 2000, 192)])
-def test_gemm_tc_swiglu(n, F, k):
+def test_gemm_tc_gated(n, F, k, act):
+    """out = act(x . W_gate) * (x . W_up) in the product's epilogue, on the packed layout that interleaves gate and
+    up rows (64 features per 128-row tile), uncut and cut along K, for every activation."""
     from xyntetik_runner_b200 import kernels
+    if act != "silu" and (n, F, k) not in ((7, 176, 72), (33, 300, 256), (300, 200, 264), (16, 1000, 520)):
+        pytest.skip("the other activations run on a few of the sizes")
     g = torch.Generator(device="cpu").manual_seed(n + F + k)
     x = torch.randn(n, k, generator=g).to(torch.bfloat16)
     w = (torch.randn(2 * F, k, generator=g) * (3.0 / math.sqrt(k))).to(torch.bfloat16)
     gate = x.double() @ w[:F].double().T
     up = x.double() @ w[F:].double().T
-    ref = gate / (1 + torch.exp(-gate)) * up
+    ref = _activation(act, gate) * up
+    packed = kernels.pack_weight(w.to(DEV), halves=2)
+    assert packed.shape[0] == -(-F // 64) and packed.shape[2:] == (128, 64)
+    torch.cuda.synchronize()
     # (at most 16 tokens: the decode kernel, which is cut into more slices along K)
     for splits in (0, 1, 2) if n > 16 else (0, 1, 2, 3, 5, 8):
-        out = torch.empty(n, F, dtype=torch.bfloat16, device=DEV)
-        kernels.gemm_tc(x.to(DEV), w.to(DEV), out, None, kernels.EPI_SWIGLU, force_splits=splits)
-        kernels.tc_check_status(torch.device(DEV))
+        for dt, tol in ((torch.bfloat16, 2 ** -8), (torch.float32, 3e-5 if act == "none" else 2e-3)):     # (SiLU and GELU use the hardware's approximate exp and tanh)
+            out = torch.full((n, F), float("nan"), dtype=dt, device=DEV)
+            kernels.gemm_tc(x.to(DEV), packed, out, None, kernels.EPI_GATED, force_splits=splits, packed_rows=F, act=kernels.ACTIVATIONS[act])
+            kernels.tc_check_status(torch.device(DEV))
+            err = float((out.cpu().double() - ref).abs().max())
+            assert err <= tol * float(ref.abs().max()) + 1e-6, (splits, dt, err)
+    with pytest.raises(kernels.KernelError):            # the gated product takes packed weights only
+        kernels.gemm_tc(x.to(DEV), w.to(DEV), torch.empty(n, F, dtype=torch.bfloat16, device=DEV), None, kernels.EPI_GATED)
+
+
+@pytest.mark.parametrize("act", ["silu", "gelu_tanh"])
+@pytest.mark.parametrize("n,n_out,k", [(5, 200, 136), (40, 384, 1024), (300, 130, 264)])
+def test_gemm_tc_store_with_activation(n, n_out, k, act):
+    """out = act(x . W + bias): the epilogue of an ungated feed-forward's first product, uncut and cut along K."""
+    from xyntetik_runner_b200 import kernels
+    g = torch.Generator().manual_seed(n + n_out)
+    x = torch.randn(n, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(n_out, k, generator=g) * (2.0 / math.sqrt(k))).to(torch.bfloat16)
+    bias = torch.randn(n_out, generator=g)
+    ref = _activation(act, x.double() @ w.double().T + bias.double())
+    for splits in (0, 1, 3):
+        out = torch.empty(n, n_out, dtype=torch.bfloat16, device=DEV)
+        kernels.gemm_tc(x.to(DEV), w.to(DEV), out, bias.to(DEV), kernels.EPI_STORE, force_splits=splits, act=kernels.ACTIVATIONS[act])
         err = float((out.cpu().double() - ref).abs().max())
         assert err <= 2 ** -8 * float(ref.abs().max()) + 1e-6, (splits, err)
+    kernels.tc_check_status(torch.device(DEV))
 
 
 def test_gemm_tc_strided_rows_and_far_columns():
@@ -156,12 +193,21 @@ def test_silu_mul():
     kernels.silu_mul(gu.to(DEV), h)
     assert float((h.cpu().double() - ref).abs().max()) <= 1e-6 * float(ref.abs().max())
     assert float(h[0, 0]) == 0.0 and float(h[0, 1]) != 0.0
+    # the other activations, gated and not, float32 and bfloat16, in place too
+    for act in ("gelu_tanh", "none", "silu"):
+        want = _activation(act, g) * u
+        kernels.act_mul(gu.to(DEV), h, kernels.ACTIVATIONS[act], gated=True)
+        assert float((h.cpu().double() - want).abs().max()) <= 2e-6 * float(want.abs().max()), act
+        y = gu.to(DEV).to(torch.bfloat16)
+        want = _activation(act, y.cpu().double())
+        kernels.act_mul(y, y, kernels.ACTIVATIONS[act], gated=False)
+        assert float((y.cpu().double() - want).abs().max()) <= 2 ** -8 * float(want.abs().max()), act
 
 
 # ---------------------------------------------------------------------------------------------
 # attention over a paged cache, against a float64 computation
 # ---------------------------------------------------------------------------------------------
-def _paged_case(seed, H, K, hd, page, seg_specs, dtype, window=0, spike=None):
+def _paged_case(seed, H, K, hd, page, seg_specs, dtype, window=0, spike=None, spikes=()):
     """seg_specs: [(pos0, length)].  Builds a cache with shuffled pages holding keys/values for positions
     [0, pos0 + length) of every request, and queries for the last `length` positions.  Returns everything the
     kernels need plus the float64 reference output."""
@@ -185,6 +231,10 @@ def _paged_case(seed, H, K, hd, page, seg_specs, dtype, window=0, spike=None):
             # one far key stands out for the last query of this request: its value must dominate the output
             _, key_pos, strength = spike
             k[key_pos] = q[-1].reshape(K, H // K, hd)[:, 0] * strength / hd
+        for seg_i, query_i, key_pos, logit in spikes:
+            # key `key_pos` is made to score about `logit` against query `query_i` (first head of every kv group)
+            if seg_i == s:
+                k[key_pos] = q[query_i].reshape(K, H // K, hd)[:, 0] * (logit * math.sqrt(hd) / hd)
         if dtype == torch.bfloat16:
             k, v, q = bf16_round(k), bf16_round(v), bf16_round(q)
         for i in range(-(-T // page)):
@@ -301,6 +351,57 @@ def test_attention_finds_a_far_key(kind):
         assert float(err) <= 1.2e-2, (key_pos, float(err))
 
 
+@pytest.mark.parametrize("kind,hd,page", [("tc", 128, 16), ("tc", 128, 64), ("tc", 64, 32), ("rows", 128, 16), ("rows", 48, 8), ("simt", 64, 16)])
+@pytest.mark.parametrize("window", [0, 100])
+def test_prompt_attention_finds_keys_at_tile_page_and_window_edges(kind, hd, page, window):
+    """Prompt portions (more than 16 packed rows: the tcgen05 kernel and the row-tiled mma.sync kernel).  With plain
+    random keys a row's output is an average of hundreds of values and one lost key moves it by a thousandth;
+    here chosen queries have ONE key that carries most of their weight -- at the first and last key of a 64- and
+    128-key tile, of a page and of a copy box, on the diagonal, at position 0 -- so a kernel that drops or misplaces
+    it is off by half the row.  With a window, the key at p - window + 1 must dominate and an equally strong key at
+    p - window must count for nothing.  The queries sit at the first and last token of a 128-row tile of packed
+    rows (four heads a token: tokens 0, 31, 32, 63 of the portion) and at its end.  Errors are taken row by row
+    against that row's own size."""
+    from xyntetik_runner_b200 import kernels
+    H, K = 8, 2
+    p0, L = 201, 300                                   # positions 201..500 are in the step, 0..200 lie in the cache
+    queries = [0, 31, 32, 63, 64, 170, L - 1]
+    spikes = []
+    for n_q, i in enumerate(queries):
+        p = p0 + i
+        if window:
+            spikes += [(0, i, p - window + 1, 9.0), (0, i, p - window, 9.0)]
+        else:
+            key = [0, 63, 64, 127, 128, p, p - 1][n_q]
+            spikes.append((0, i, key, 9.0))
+    case = _paged_case(7 + hd + page + window, H, K, hd, page, [(p0, L), (0, 40)], torch.bfloat16, window, spikes=spikes)
+    out = torch.full((case["n"], H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    cache = case["cache"]
+    if kind == "tc":
+        assert kernels.attention_tc_supported(torch.bfloat16, H, K, hd, page)
+        kernels.attention_tc(case["qkv"], out, case["starts"], case["lens"], case["pos0"], case["bt"],
+                             (cache.data_ptr(), cache.shape[0], cache.shape[1], 0), H, K, hd, case["max_pages"], page, window,
+                             case["scale"], case["n_seg"], int(case["lens_host"].max()))
+        kernels.tc_check_status(torch.device(DEV))
+        got = out.cpu().double()
+    else:
+        got = _run_attention(case, "simt" if kind == "simt" else "mma", H, K, hd, page, window, torch.bfloat16)
+    ref = case["ref"]
+    assert not torch.isnan(got).any()
+    G = H // K
+    for i in queries:
+        for kvh in range(K):
+            h = kvh * G                                   # the head the key was aimed at
+            row_ref, row_got = ref[i, h * hd:(h + 1) * hd], got[i, h * hd:(h + 1) * hd]
+            err = float((row_got - row_ref).abs().max() / row_ref.abs().max())
+            assert err <= 2e-2, (kind, window, i, kvh, err)
+    # and the spiked key really dominates its row in the reference (else the case would prove nothing)
+    plain = _paged_case(7 + hd + page + window, H, K, hd, page, [(p0, L), (0, 40)], torch.bfloat16, window)["ref"]
+    assert float((plain[queries[0], :hd] - ref[queries[0], :hd]).abs().max()) > 0.3
+    # every row, against the size of the whole output
+    assert float((got - ref).abs().max() / ref.abs().max()) <= 1.5e-2
+
+
 @pytest.mark.parametrize("n,d", [(6, 200), (6, 1000), (3, 4096), (13, 5128), (70, 1000)])
 def test_fused_finishes_match_the_separate_kernels(n, d):
     """Deferred split-K products finished by the fused kernels give what product + separate kernels give
@@ -320,21 +421,31 @@ def test_fused_finishes_match_the_separate_kernels(n, d):
     kernels.rmsnorm(a, nw, h_a, 1e-5)
     # fused
     b = resid.clone()
-    used = kernels.gemm_tc(x_in, w, b, bias, kernels.EPI_ADD, force_splits=4, defer=True)
-    assert used == 4 and torch.equal(b, resid)                    # nothing written yet
+    sums = kernels.gemm_tc_deferred(x_in, w, b, bias, kernels.EPI_ADD, force_splits=4)
+    assert sums.splits == 4 and torch.equal(b, resid)            # nothing written yet
     h_b = torch.empty(n, d, dtype=torch.bfloat16, device=DEV)
-    kernels.finish_add_rmsnorm(kernels.tc_workspace(torch.device(DEV))[0], used, bias, b, nw, h_b, 1e-5)
+    kernels.finish_add_rmsnorm(sums.partial, sums.splits, bias, b, nw, h_b, 1e-5)
+    sums.release()
     assert torch.allclose(a, b, rtol=0, atol=1e-5 * float(a.abs().max()))
     assert float((h_a.float() - h_b.float()).abs().max()) <= 2 ** -7 * float(h_a.float().abs().max())
     # plain finish
     c = resid.clone()
-    used = kernels.gemm_tc(x_in, w, c, bias, kernels.EPI_ADD, force_splits=3, defer=True)
-    kernels.finish_plain(kernels.tc_workspace(torch.device(DEV))[0], used, bias, c, True)
+    sums = kernels.gemm_tc_deferred(x_in, w, c, bias, kernels.EPI_ADD, force_splits=3)
+    # a second deferred product while the first is outstanding gets a slab of its own
+    other = torch.zeros(n, d, device=DEV)
+    sums2 = kernels.gemm_tc_deferred(x_in, w, other, None, kernels.EPI_STORE, force_splits=2)
+    assert sums2.partial.data_ptr() >= sums.partial.data_ptr() + 4 * sums.partial.numel()
+    kernels.finish_plain(sums.partial, sums.splits, bias, c, True)
+    kernels.finish_plain(sums2.partial, sums2.splits, None, other, False)
+    sums.release(), sums2.release()
     assert torch.allclose(a, c, rtol=0, atol=1e-5 * float(a.abs().max()))
+    assert torch.allclose(other + bias + resid, a, rtol=0, atol=2e-5 * float(a.abs().max()))
+    assert kernels.workspace(torch.device(DEV)).live == 0 and kernels.workspace(torch.device(DEV)).top == 0
 
 
-@pytest.mark.parametrize("H,K,hd,rot", [(6, 2, 48, 48), (6, 2, 32, 32), (3, 1, 64, 32), (2, 2, 128, 128), (5, 1, 16, 16)])
-def test_finish_rope_store_matches_rope_store(H, K, hd, rot):
+@pytest.mark.parametrize("adjacent,mscale", [(False, 1.0), (True, 1.0), (True, 0.83)])
+@pytest.mark.parametrize("H,K,hd,rot", [(6, 2, 48, 48), (6, 2, 32, 32), (3, 1, 64, 32), (2, 2, 128, 128), (5, 1, 16, 16), (2, 1, 24, 20)])
+def test_finish_rope_store_matches_rope_store(H, K, hd, rot, adjacent, mscale):
     from xyntetik_runner_b200 import kernels
     g = torch.Generator().manual_seed(4)
     page, n, kdim = 8, 5, 512
@@ -351,13 +462,14 @@ def test_finish_rope_store_matches_rope_store(H, K, hd, rot):
         cache = torch.zeros(7, 1, 2, K, page, hd, dtype=torch.bfloat16, device=DEV)
         qkv = torch.zeros(n, qkv_dim, dtype=torch.bfloat16, device=DEV)
         if fused:
-            used = kernels.gemm_tc(x_in, w, qkv, bias, kernels.EPI_STORE, force_splits=2, defer=True)
-            kernels.finish_rope_store(kernels.tc_workspace(torch.device(DEV))[0], used, bias, qkv, positions, tok_seg, bt, inv_freq,
-                                      cache.data_ptr(), cache.stride(0), cache.stride(2), H, K, hd, rot, 3, page)
+            sums = kernels.gemm_tc_deferred(x_in, w, qkv, bias, kernels.EPI_STORE, force_splits=2)
+            kernels.finish_rope_store(sums.partial, sums.splits, bias, qkv, positions, tok_seg, bt, inv_freq,
+                                      cache.data_ptr(), cache.stride(0), cache.stride(2), H, K, hd, rot, 3, page, adjacent, mscale)
+            sums.release()
         else:
             kernels.gemm_tc(x_in, w, qkv, bias, kernels.EPI_STORE, force_splits=1)
             kernels.rope_store(qkv, positions, tok_seg, bt, inv_freq, cache.data_ptr(), cache.stride(0), cache.stride(2),
-                               H, K, hd, rot, 3, page)
+                               H, K, hd, rot, 3, page, adjacent, mscale)
         outs.append((qkv[:, :H * hd].float().cpu(), cache.float().cpu()))
     (q0, c0), (q1, c1) = outs
     assert float(c0.abs().sum()) > 0
@@ -382,16 +494,19 @@ def test_gemm_tc_packed_layout(n, n_out, k):
         kernels.gemm_tc(x, w, a, None, kernels.EPI_STORE, force_splits=splits)
         kernels.gemm_tc(x, packed, b, None, kernels.EPI_STORE, force_splits=splits, packed_rows=n_out)
         assert torch.equal(a, b)
-    # SwiGLU halves
+    # the gated layout against the product of the plain matrix followed by the activation kernel (both round the
+    # same float32 sums once, so they agree to a step of bfloat16)
     F = n_out
     w2 = (torch.randn(2 * F, k, generator=g) / math.sqrt(k)).to(torch.bfloat16).to(DEV)
-    a = torch.empty(n, F, dtype=torch.bfloat16, device=DEV)
-    b = torch.empty(n, F, dtype=torch.bfloat16, device=DEV)
-    kernels.gemm_tc(x, w2, a, None, kernels.EPI_SWIGLU)
+    gu = torch.empty(n, 2 * F, dtype=torch.float32, device=DEV)
+    a = torch.empty(n, F, dtype=torch.float32, device=DEV)
+    b = torch.empty(n, F, dtype=torch.float32, device=DEV)
+    kernels.gemm_tc(x, w2, gu, None, kernels.EPI_STORE, force_splits=1)
+    kernels.act_mul(gu, a, kernels.ACT_SILU, gated=True)
     p2 = kernels.pack_weight(w2, halves=2)
     torch.cuda.synchronize()
-    kernels.gemm_tc(x, p2, b, None, kernels.EPI_SWIGLU, packed_rows=F)
-    assert torch.equal(a, b)
+    kernels.gemm_tc(x, p2, b, None, kernels.EPI_GATED, packed_rows=F, force_splits=1)
+    assert float((a - b).abs().max()) <= 2e-3 * float(a.abs().max())
     kernels.tc_check_status(torch.device(DEV))
 
 

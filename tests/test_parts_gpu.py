@@ -137,11 +137,14 @@ def test_parts_alone(setup, name, dtype):
     eng.end("c")
 
 
+@pytest.mark.parametrize("adjacent,mscale", [(False, 1.0), (True, 1.0), (False, 1.3), (True, 0.7)])
 @pytest.mark.parametrize("dtype,hd,rot", [(torch.float32, 80, 48), (torch.bfloat16, 80, 48), (torch.bfloat16, 72, 40),
-                                          (torch.bfloat16, 128, 128), (torch.bfloat16, 64, 0)])
-def test_rotation_and_store_kernel_at_other_sizes(dtype, hd, rot):
+                                          (torch.bfloat16, 128, 128), (torch.bfloat16, 64, 0), (torch.float32, 25, 10),
+                                          (torch.bfloat16, 100, 100)])
+def test_rotation_and_store_kernel_at_other_sizes(dtype, hd, rot, adjacent, mscale):
     """rope_store with a partial rotary dimension and odd page size against the plain rotation: float32, and
-    bfloat16 on its 16-byte vector path (head size a multiple of 8, rotated width of 16) and off it."""
+    bfloat16 on its 16-byte vector path (head size a multiple of 8, rotated width of 16) and off it; pairs
+    (j, j + half) and adjacent pairs (2j, 2j + 1); cosines and sines scaled by mscale."""
     from plain_llama import rope_inv_freq
     from xyntetik_runner_b200 import kernels
     H, K, page, n = 5, 1, 5, 9
@@ -159,12 +162,12 @@ def test_rotation_and_store_kernel_at_other_sizes(dtype, hd, rot):
     t = torch.from_numpy(qkv).cuda().to(dtype)
     kernels.rope_store(t, torch.from_numpy(positions).cuda(), torch.from_numpy(tok_seg).cuda(), torch.from_numpy(bt).cuda(),
                        torch.from_numpy(inv).cuda() if rot else None, cache.data_ptr(), cache.stride(0), cache.stride(2),
-                       H, K, hd, rot, 62, page)
+                       H, K, hd, rot, 62, page, adjacent, mscale)
     q_ref = qkv[:, :H * hd].reshape(n, H, hd).copy()
     k_ref = qkv[:, H * hd:(H + K) * hd].reshape(n, K, hd).copy()
     if rot:
-        q_ref[:, :, :rot] = rope_apply(q_ref[:, :, :rot], positions, inv)
-        k_ref[:, :, :rot] = rope_apply(k_ref[:, :, :rot], positions, inv)
+        q_ref[:, :, :rot] = rope_apply(q_ref[:, :, :rot], positions, inv, adjacent, mscale)
+        k_ref[:, :, :rot] = rope_apply(k_ref[:, :, :rot], positions, inv, adjacent, mscale)
     got = t.float().cpu().numpy()
     assert np.abs(got[:, :H * hd].reshape(n, H, hd) - q_ref).max() < tol
     c = cache.float().cpu().numpy()

@@ -259,3 +259,146 @@ def test_unknown_part_kinds_are_refused():
         make("mixer", "nope")
     m = make("norm", "rmsnorm", width=8, eps=1e-5, name="n")
     assert m.width == 8
+
+
+# ---------------------------------------------------------------------------------------------
+# A second toy, for the parts that the first one does not reach: a block that runs mixer and feed-forward side by
+# side from ONE norm (so a product whose sum is still pending on the residual stream meets other products cut along
+# K), the built-in attention with an adjacent-pair rotation whose cosines and sines are scaled, an ungated GELU
+# feed-forward and a gated GELU one -- all through ``Linear`` in bfloat16 at widths where the tensor-core product
+# is cut along K and its sum deferred.  Block and architecture are defined here; nothing in the package changes.
+# ---------------------------------------------------------------------------------------------
+TOY2 = {"architectures": ["Toy2ForCausalLM"], "vocab": 131, "width": 1024, "heads": 16, "kv_heads": 4, "head_dim": 64,
+        "inner": 1536, "eps": 1e-5, "theta": 777.0, "mscale": 0.9, "max_positions": 512, "torch_dtype": "bfloat16"}
+
+
+def gelu_tanh(g):
+    g = g.astype(np.float64)
+    return (0.5 * g * (1.0 + np.tanh(0.7978845608 * (g + 0.044715 * g ** 3)))).astype(np.float32)
+
+
+def _define2():
+    from xyntetik_runner_b200.config.registry import register_architecture
+    from xyntetik_runner_b200.engine.model import ModelPlan, ScheduleEntry
+    from xyntetik_runner_b200.parts import (Block, Embedding, GQAAttention, Head, PreNormBlock, RMSNorm, make, register_block)
+
+    class ParallelBlock(Block):
+        """x += mixer(norm(x)) + feed_forward(norm(x)): one norm, both parts read it, both add into the stream."""
+
+        def __init__(self, norm, mixer, feed_forward):
+            self.norm, self.mixer, self.feed_forward = norm, mixer, feed_forward
+
+        graph_safe = True
+
+        def parts(self):
+            return (self.norm, self.mixer, self.feed_forward)
+
+        def tensors(self):
+            out = {}
+            for p in self.parts():
+                out.update(p.tensors())
+            return out
+
+        def bind(self, tensors, rt):
+            for p in self.parts():
+                p.bind(tensors, rt)
+
+        def weight_bytes(self):
+            return sum(p.weight_bytes() for p in self.parts())
+
+        def forward(self, ctx, x, lay):
+            h = ctx.buf("parallel_normed", (x.shape[0], x.shape[1]), ctx.act_dtype)
+            self.norm.forward(ctx, x, h)
+            self.mixer.forward(ctx, h, x, lay)          # leaves its last product's sum pending on x ...
+            self.feed_forward.forward(ctx, h, x)        # ... while these products run, cut along K themselves
+
+    register_block("toy_parallel", ParallelBlock, replace=True)
+
+    class Toy2Config:
+        def __init__(self, d):
+            self.__dict__.update(d)
+            self.architecture = d["architectures"][0]
+
+    def build(c):
+        emb = Embedding(c.vocab, c.width, "emb.weight")
+        norm = lambda name: RMSNorm(c.width, c.eps, name)
+        rope = lambda: make("position", "rope", head_dim=c.head_dim, theta=c.theta, pairing="adjacent", mscale=c.mscale)
+        att = lambda p: GQAAttention(c.width, c.heads, c.kv_heads, c.head_dim, rope(), p)
+        blocks = [
+            make("block", "toy_parallel", norm=norm("l0.n"), mixer=att("l0.att."),
+                 feed_forward=make("feed_forward", "mlp", width=c.width, inner=c.inner, prefix="l0.ff.", activation="gelu_tanh")),
+            PreNormBlock(norm("l1.n1"), att("l1.att."), norm("l1.n2"),
+                         make("feed_forward", "gated", width=c.width, inner=c.inner, prefix="l1.ff.", activation="gelu_tanh")),
+        ]
+        return ModelPlan(emb, blocks, [ScheduleEntry(0), ScheduleEntry(1)], norm("final.weight"),
+                         Head(c.vocab, c.width, name="head.weight"), c.width, c.vocab, c.max_positions)
+
+    register_architecture("Toy2ForCausalLM", Toy2Config, build, replace=True)
+    return Toy2Config, build
+
+
+def plain_toy2(folder, ids):
+    from plain_llama import rope_inv_freq
+    cfg, w = read_folder(folder)
+    T = len(ids)
+    H, K, hd = cfg["heads"], cfg["kv_heads"], cfg["head_dim"]
+    pos = np.arange(T)
+    inv = rope_inv_freq(cfg["theta"], hd)
+    x = w["emb.weight"][np.asarray(ids)].astype(np.float32)
+
+    def att(prefix, h):
+        q = matvec_rows(h, w[prefix + "q_proj.weight"]).reshape(T, H, hd)
+        k = matvec_rows(h, w[prefix + "k_proj.weight"]).reshape(T, K, hd)
+        v = matvec_rows(h, w[prefix + "v_proj.weight"]).reshape(T, K, hd)
+        q, k = rope_apply(q, pos, inv, True, cfg["mscale"]), rope_apply(k, pos, inv, True, cfg["mscale"])
+        return matvec_rows(attention(q, k, v, 1.0 / np.sqrt(hd)).reshape(T, H * hd), w[prefix + "o_proj.weight"])
+
+    h = rmsnorm(x, w["l0.n"], cfg["eps"])
+    x = x + att("l0.att.", h) + matvec_rows(gelu_tanh(matvec_rows(h, w["l0.ff.up_proj.weight"])), w["l0.ff.down_proj.weight"])
+    x = x + att("l1.att.", rmsnorm(x, w["l1.n1"], cfg["eps"]))
+    h = rmsnorm(x, w["l1.n2"], cfg["eps"])
+    gated = gelu_tanh(matvec_rows(h, w["l1.ff.gate_proj.weight"])) * matvec_rows(h, w["l1.ff.up_proj.weight"])
+    x = x + matvec_rows(gated.astype(np.float32), w["l1.ff.down_proj.weight"])
+    return matvec_rows(rmsnorm(x, w["final.weight"], cfg["eps"]), w["head.weight"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_parallel_block_adjacent_rotation_and_gelu_feed_forwards(tmp_path, dtype):
+    from xyntetik_runner_b200.engine.engine import Engine, EngineParams
+    from xyntetik_runner_b200.engine.replay import replay
+    from xyntetik_runner_b200.parts import linear
+    from xyntetik_runner_b200.weights.loader import write_model_folder
+    Toy2Config, build = _define2()
+    folder = str(tmp_path / "toy2")
+    write_model_folder(folder, TOY2, build(Toy2Config(TOY2)).tensor_specs(), seed=6, dtype=torch.bfloat16, std=0.03,
+                       norm_jitter=0.1, gen_device="cuda:0")
+    reqs = {f"r{i}": traces.random_tokens(10 + i, n, TOY2["vocab"]) for i, n in enumerate((5, 40, 70))}
+    ref = {rid: plain_toy2(folder, t) for rid, t in reqs.items()}
+    before = dict(linear.counters)
+    for cut in (traces.whole, lambda r: traces.tail_decoded(r, 12), lambda r: traces.mixed(r, seed=3, max_live=3)):
+        steps = cut(reqs)
+        eng = Engine(folder, EngineParams(dtype=dtype, max_tokens=traces.pool_tokens(steps, 16) + 64, page_size=16, max_requests=3))
+        got = traces.collect(steps, replay(eng, steps), TOY2["vocab"])
+        for rid in reqs:
+            traces.assert_close(got[rid], ref[rid], dtype, f"toy2/{dtype}/{rid}")
+        eng.cache.audit()
+        eng.check_status()
+    if dtype == "bfloat16":
+        # the serving path ran, and products were cut along K with their sums deferred (the parallel block then holds
+        # one pending on the stream while the feed-forward's products run)
+        assert linear.counters["tcgen05"] > before["tcgen05"] and linear.counters["deferred"] > before["deferred"] + 10
+        from xyntetik_runner_b200 import kernels
+        assert kernels.workspace(eng.device).live <= 1
+
+
+def test_a_position_encoding_that_is_no_rotation_is_refused_by_name():
+    from xyntetik_runner_b200.parts import GQAAttention, PositionEncoding, Runtime
+
+    class ScoreBias(PositionEncoding):
+        """(a bias on the scores by distance: not something the built-in mixer can apply)"""
+
+    m = GQAAttention(64, 4, 2, 16, ScoreBias(), "a.")
+    tensors = {f"a.{n}_proj.weight": torch.zeros(s, dtype=torch.float32, device="cuda") for n, s in
+               (("q", (64, 64)), ("k", (32, 64)), ("v", (32, 64)), ("o", (64, 64)))}
+    with pytest.raises(ValueError, match="ScoreBias"):
+        m.bind(tensors, Runtime(torch.device("cuda:0"), torch.float32, 16, 64, 2))

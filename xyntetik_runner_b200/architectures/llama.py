@@ -40,4 +40,16 @@ def build_llama(cfg: LlamaConfig) -> ModelPlan:
                      bos_id=cfg.bos_token_id)
 
 
-register_architecture("LlamaForCausalLM", LlamaConfig.from_dict, build_llama, replace=True)
+def override_llama(cfg: LlamaConfig, rope_base=None, rope_scale=None) -> LlamaConfig:
+    """The reference's run-time overrides: another frequency base (--rope-base, src/model.c:282) and linear position
+    scaling by a factor in place of the configuration's scaling (--rope-scale, src/model.c:324-326)."""
+    import dataclasses
+    from ..config.llama import RopeScaling
+    if rope_base is not None:
+        cfg = dataclasses.replace(cfg, rope_theta=float(rope_base))
+    if rope_scale is not None:
+        cfg = dataclasses.replace(cfg, rope_scaling=RopeScaling(rope_type="linear", factor=float(rope_scale)))
+    return cfg
+
+
+register_architecture("LlamaForCausalLM", LlamaConfig.from_dict, build_llama, override=override_llama, replace=True)

@@ -4,7 +4,9 @@ Options keep the reference's names and meanings where it has them: -m (here a mo
 config.json and model.safetensors), -p, -f, -n (default 256, -1 = until a stop id), -c, -b, -s (0 is
 refused), --temp (0 = greedy), --top-k, --top-p, --min-p, --repeat-penalty, --ignore-eos, --no-bos,
 --score (teacher-forced log-probabilities of the prompt, the reference's JSON), --parallel, --rope-base, --rope-scale,
---bench-json, -v/--version.  Tokenisation is outside the engine: a prompt is either ``ids:1,2,3`` (or a file of
+--bench-json (extended: --parallel sequences at once and a per-kernel table), -t, -v/--version; -c 0 fits the context
+to the free memory.  Where the reference has --gpu off to run its CPU code, --ref runs the plain implementation
+that the tests compare the engine with (greedy only; it is slow and is found only in a source checkout).  Tokenisation is outside the engine: a prompt is either ``ids:1,2,3`` (or a file of
 ids, --prompt-ids) or
 text taken byte by byte (token id = byte value), and the output is printed as ids (and as bytes where
 every id is one).
@@ -54,7 +56,11 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--prompt-ids", default=None, metavar="FILE",
                     help="read the prompt as token ids from FILE (integers separated by commas or white space); instead of -p / -f")
     ap.add_argument("-n", dest="n", type=int, default=256, help="max tokens to generate (default 256, -1 = until a stop id)")
-    ap.add_argument("-c", dest="ctx", type=int, default=None, help="context length (default: min(model max, 4096))")
+    ap.add_argument("-c", dest="ctx", type=int, default=None,
+                    help="context length (default: min(model max, 4096); 0 = as long as the model allows and memory holds)")
+    ap.add_argument("-t", dest="threads", type=int, default=None, help="CPU threads (used by --ref only: the engine computes on the GPU)")
+    ap.add_argument("--ref", action="store_true",
+                    help="generate greedily with the plain CPU implementation under tests/ instead of the engine (for comparison)")
     ap.add_argument("-b", dest="batch", type=int, default=2048, help="prompt portion / step token budget (default 2048)")
     ap.add_argument("-s", dest="seed", type=int, default=None, help="RNG seed (default: time; 0 is refused)")
     ap.add_argument("--temp", type=float, default=0.0, help="temperature (0 = greedy: the argmax, no repeat penalty)")
@@ -73,11 +79,53 @@ def build_parser() -> argparse.ArgumentParser:
                     help="bfloat16: serving kernels; float32: everything in true 32 bit")
     ap.add_argument("--page-size", type=int, default=64, help="tokens per cache page")
     ap.add_argument("--bench-json", action="store_true",
-                    help="prefill a 512-token prompt, decode -n tokens with stop ids ignored, print timings as JSON")
+                    help="prefill 512-token prompts (--parallel of them at once), decode -n tokens each with stop ids ignored, "
+                         "print timings and a per-kernel table as JSON")
     ap.add_argument("--random", type=int, default=None, metavar="SEED",
                     help="with -m: write config.json-described random weights into the folder first (needs config.json)")
     ap.add_argument("-v", "--version", action="version", version=f"runner-b200 {__version__}")
     return ap
+
+
+def run_plain(args) -> int:
+    """--ref: the plain implementation of the tests (whole sequences on the CPU, no cache), greedy decoding."""
+    import os
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    tests = os.path.join(here, "tests")
+    if not os.path.isfile(os.path.join(tests, "plain_llama.py")):
+        print("error: --ref needs tests/plain_llama.py of a source checkout", file=sys.stderr)
+        return 2
+    if args.temp > 0 or args.score or args.bench_json:
+        print("error: --ref decodes greedily only (no --temp, --score or --bench-json)", file=sys.stderr)
+        return 2
+    if args.threads:
+        import torch
+        torch.set_num_threads(args.threads)
+        os.environ["OMP_NUM_THREADS"] = str(args.threads)
+    sys.path.insert(0, tests)
+    from plain_llama import PlainLlama
+    m = PlainLlama(args.model)
+    text = unescape(args.prompt) if args.prompt is not None else ""
+    if args.file:
+        with open(args.file, "r", encoding="utf-8") as f:
+            text += f.read()
+    ids = encode_prompt(text, m.cfg["vocab_size"])
+    bos = m.cfg.get("bos_token_id")
+    if not args.no_bos and bos is not None:
+        ids = [int(bos)] + ids
+    if not ids:
+        print("error: empty prompt", file=sys.stderr)
+        return 2
+    stops = m.cfg.get("eos_token_id")
+    stops = set() if (stops is None or args.ignore_eos) else set(stops if isinstance(stops, list) else [stops])
+    out = []
+    for _ in range(args.n if args.n > 0 else 256):
+        tok = m.generate_greedy(ids + out, 1)[0]
+        if tok in stops:
+            break
+        out.append(tok)
+    print("ids:" + ",".join(str(t) for t in out))
+    return 0
 
 
 def main(argv=None) -> int:
@@ -101,6 +149,8 @@ def main(argv=None) -> int:
         print(f"wrote random weights (seed {args.random}) to {os.path.join(args.model, 'model.safetensors')}", file=sys.stderr)
         if args.prompt is None and args.file is None and not args.bench_json:
             return 0
+    if args.ref:
+        return run_plain(args)
     from .engine.runner import Runner
     t0 = time.perf_counter()
     if args.parallel < 1 or (args.rope_base is not None and not args.rope_base > 0) or \
@@ -112,19 +162,33 @@ def main(argv=None) -> int:
     plan = runner.engine.plan
     print(f"loaded {args.model} in {time.perf_counter() - t0:.2f} s ({args.dtype})", file=sys.stderr)
     if args.bench_json:
+        # the reference's --bench-json (src/main.c:1435-1515): prompt_tok_s, gen_tok_s, prompt_s, gen_s of a 512-token
+        # prompt and -n decoded tokens; here for --parallel sequences at once, with the kernels' own times beside them
         import numpy as np
-        ids = [int(t) for t in np.random.RandomState(0).randint(0, plan.vocab_size, size=512)]
+        from . import measure
+        B = args.parallel
+        rng = np.random.RandomState(0)
+        prompts = [[int(t) for t in rng.randint(0, plan.vocab_size, size=512)] for _ in range(B)]
         n_new = args.n if args.n > 0 else 128
-        stamps = {}
+        first, last = {}, {}
+
         def on_token(rid, tok, done):
-            stamps.setdefault("first", time.perf_counter())
+            first.setdefault(rid, time.perf_counter())
+            last[rid] = time.perf_counter()
         t0 = time.perf_counter()
-        res = runner.generate(ids, n=n_new, temp=args.temp, seed=args.seed, ignore_eos=True, on_token=on_token)
-        t1 = time.perf_counter()
-        prompt_s = stamps["first"] - t0
-        gen_s = t1 - stamps["first"]
-        print(json.dumps({"prompt_tokens": 512, "gen_tokens": len(res.tokens), "prompt_s": prompt_s, "gen_s": gen_s,
-                          "prompt_tok_s": 512 / prompt_s, "gen_tok_s": (len(res.tokens) - 1) / gen_s if gen_s > 0 else 0.0}))
+        res = runner.generate(prompts, n=n_new, temp=args.temp, seed=args.seed, ignore_eos=True, on_token=on_token)
+        t_first, t_last = max(first.values()), max(last.values())          # every prompt is in; every sequence is done
+        prompt_s, gen_s = t_first - t0, t_last - t_first
+        gen = sum(len(r.tokens) for r in res)
+        out = {"batch": B, "prompt_tokens": 512 * B, "gen_tokens": gen, "prompt_s": prompt_s, "gen_s": gen_s,
+               "prompt_tok_s": 512 * B / prompt_s, "gen_tok_s": (gen - B) / gen_s if gen_s > 0 else 0.0,
+               "dtype": args.dtype, "steps": runner.scheduler.stats.get("steps")}
+        cfg = runner.engine.config
+        if args.dtype == "bfloat16" and all(hasattr(cfg, k) for k in ("hidden_size", "num_attention_heads", "num_key_value_heads",
+                                                                      "head_dim", "intermediate_size", "vocab_size")):
+            del runner
+            out["kernels"] = measure.kernel_table(cfg, B, 512 + n_new // 2, True, measure.peaks(), iters=10)
+        print(json.dumps(out))
         return 0
     if args.prompt_ids is not None:
         if args.prompt is not None or args.file:

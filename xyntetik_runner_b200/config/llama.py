@@ -11,15 +11,12 @@ from __future__ import annotations
 
 import json
 import os
+from .base import ConfigError, read_config_json  # noqa: F401  (both are also importable from here)
 from dataclasses import dataclass, field
 from typing import Any, Mapping, Optional, Tuple
 
 DIM_MAX = 1 << 20          # per-axis ceiling, src/model.c:31
 LAYERS_MAX = 100000        # src/model.c:1429-1433
-
-
-class ConfigError(ValueError):
-    """config.json is missing a key, or holds a value the engine refuses."""
 
 
 @dataclass(frozen=True)
@@ -290,19 +287,3 @@ def _typed(key: str, v: Any, kind):
             raise ConfigError(f"config.json: '{key}' must be a string, got {v!r}")
         return v
     raise TypeError(kind)
-
-
-def read_config_json(path: str) -> dict:
-    """Read `path` (a model folder or the json file itself) into a dict."""
-    if os.path.isdir(path):
-        path = os.path.join(path, "config.json")
-    try:
-        with open(path, "r", encoding="utf-8") as f:
-            d = json.load(f)
-    except FileNotFoundError:
-        raise ConfigError(f"no config.json at {path}") from None
-    except json.JSONDecodeError as e:
-        raise ConfigError(f"{path}: not valid JSON ({e})") from None
-    if not isinstance(d, dict):
-        raise ConfigError(f"{path}: top level must be an object")
-    return d

@@ -11,9 +11,9 @@ description (see ``engine.model``).
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Callable, Dict
+from typing import Any, Callable, Dict, Optional
 
-from .llama import ConfigError, read_config_json
+from .base import ConfigError, read_config_json
 
 
 @dataclass(frozen=True)
@@ -21,6 +21,10 @@ class Architecture:
     name: str
     config_from_dict: Callable[[dict], Any]
     build_plan: Callable[[Any], Any]      # configuration -> engine.model.ModelPlan
+    # run-time overrides of the configuration that the entry points offer (the reference's --rope-base and
+    # --rope-scale, src/model.c:282, 324-326): (configuration, rope_base=..., rope_scale=...) -> configuration, or
+    # None when the architecture has nothing of the kind
+    override: Optional[Callable[..., Any]] = None
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
@@ -30,10 +34,10 @@ class UnknownArchitecture(ConfigError):
     pass
 
 
-def register_architecture(name: str, config_from_dict, build_plan, *, replace: bool = False) -> None:
+def register_architecture(name: str, config_from_dict, build_plan, *, override=None, replace: bool = False) -> None:
     if name in _ARCHITECTURES and not replace:
         raise ValueError(f"architecture '{name}' is already registered")
-    _ARCHITECTURES[name] = Architecture(name, config_from_dict, build_plan)
+    _ARCHITECTURES[name] = Architecture(name, config_from_dict, build_plan, override)
 
 
 def unregister_architecture(name: str) -> None:

@@ -28,7 +28,7 @@
 
 #define ATT_TILE 64            // keys per tile
 #define ATT_ROWS 64            // packed query rows per CTA in the rows kernel
-#define ATT_KEYS_SLOTS (3 * 148)   // CTAs of the keys kernel that are resident at once (two stages: three per SM)
+#define ATT_KEYS_SLOTS (3 * xr_sm_count())   // CTAs of the keys kernel that are resident at once (two stages: three per SM)
 #define ATT_MAX_SPLITS 256     // most spans per request
 #define ATT_THREADS 128
 
@@ -50,6 +50,7 @@ struct AttnMmaArgs {
     // bulk-copy (TMA) variant of the keys kernel: the whole cache group as rows of head_dim elements
     int n_layers, layer;         // layers in the cache group, this layer's index
     int* status;                 // set non-zero if a bounded wait gives up
+    int recv_rows;               // cluster variant: most packed rows any request of the step has (sizes what a block receives)
 };
 
 // Span length (keys) of the keys kernel for a step whose longest request covers `range` keys and that has
@@ -507,7 +508,7 @@ k_attention_keys_tma(const __grid_constant__ CUtensorMap cache_map, AttnMmaArgs 
     // CLUSTER: what the other spans send.  Nothing else lives here: a span that is done early writes into the
     // shared memory of one that is still at work.
     float4* recv_acc = (float4*)(((uintptr_t)(gave_up + 1) + 15) & ~(uintptr_t)15);      // [spans][per] quadruples
-    float2* recv_ml = (float2*)(recv_acc + 16 * QUADS + ATT_CLUSTER_MAX);                // [spans][16] (maximum, sum)
+    float2* recv_ml = (float2*)(recv_acc + a.recv_rows * QUADS + ATT_CLUSTER_MAX);       // [spans][16] (maximum, sum)
     const int seg = blockIdx.z, kvh = blockIdx.y, span = blockIdx.x;
     const int L = a.seg_len[seg], rows_total = L * a.G;
     if (rows_total > 16) return;                                   // (the whole cluster: it shares the request)
@@ -542,7 +543,8 @@ k_attention_keys_tma(const __grid_constant__ CUtensorMap cache_map, AttnMmaArgs 
         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(att_smem_u32(&full[s])), "r"(2 * TILE_ELEMS * 2) : "memory");
         for (int r0 = 0; r0 < ATT_TILE; r0 += box_rows) {
             int kp = t * ATT_TILE + r0;
-            int page = bt[kp >> a.page_shift];                     // -1 (no page): the copy reads outside the tensor and fills zeros
+            const int pi = kp >> a.page_shift;
+            int page = pi < a.max_pages ? bt[pi] : -1;             // -1 (no page): the copy reads outside the tensor and fills zeros
             int tok = kp & (a.page_size - 1);
             long long rowk = ((((long long)page * a.n_layers + a.layer) * 2 + 0) * a.K + kvh) * a.page_size + tok;
             long long rowv = rowk + (long long)a.K * a.page_size;
@@ -984,11 +986,14 @@ static int launch_keys_tma(const AttnMmaArgs& a, const void* cache_base, long lo
     // the fewer CTAs there are, the deeper each one's ring of tiles, so that as many bytes stay in flight per SM
     dim3 grid(a.max_splits, a.K, n_seg);
     long long ctas = (long long)a.max_splits * a.K * n_seg;
-    const int depth = ctas <= 148 ? 4 : (ctas <= 2 * 148 ? 3 : 2);
+    const int depth = ctas <= xr_sm_count() ? 4 : (ctas <= 2 * xr_sm_count() ? 3 : 2);
     // (a single span sends nothing and needs no room to receive; otherwise the room must not cost a resident CTA)
-    const int ring = depth == 4 ? S4 : (depth == 3 ? S3 : S2), recv = a.max_splits == 1 ? 0 : RECV;
+    // what a block receives from the other spans is sized by the step's largest number of packed rows (a decode step:
+    // the heads of one group), so that the room seldom costs a resident CTA
+    const int recv_sized = (a.recv_rows * (HD / 4) + ATT_CLUSTER_MAX) * 16 + ATT_CLUSTER_MAX * 16 * 8 + 16;
+    const int ring = depth == 4 ? S4 : (depth == 3 ? S3 : S2), recv = a.max_splits == 1 ? 0 : (recv_sized < RECV ? recv_sized : RECV);
     const int fit = (227 * 1024) / (ring + 1024), fit_recv = (227 * 1024) / (ring + recv + 1024);
-    if (a.max_splits <= ATT_CLUSTER_MAX && att_cluster_merge_enabled() && (fit_recv == fit || ctas <= (long long)fit_recv * 148)) {
+    if (a.max_splits <= ATT_CLUSTER_MAX && att_cluster_merge_enabled() && (fit_recv == fit || ctas <= (long long)fit_recv * xr_sm_count())) {
         // the spans of a request as one cluster, which also combines them (returns 2: no merge kernel is to follow)
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = grid; cfg.blockDim = dim3(ATT_THREADS); cfg.stream = stream;
@@ -1046,7 +1051,7 @@ static int launch_attention(const AttnMmaArgs& a, int n_seg, int max_seg_len, in
         // few CTAs (small batch): deeper stages; many: more CTAs per SM.  The arithmetic is the same.
         if (tma == 2) return XR_OK;                    // the spans were combined inside the clusters
         if (tma == 1) {
-        } else if ((long long)a.max_splits * a.K * n_seg <= 2 * 148)
+        } else if ((long long)a.max_splits * a.K * n_seg <= 2 * xr_sm_count())
             xr_launch((k_attention_keys<HD, 4>), dim3(a.max_splits, a.K, n_seg), dim3(ATT_THREADS), SMEM_KEYS4, stream, a);
         else
             xr_launch((k_attention_keys<HD, 2>), dim3(a.max_splits, a.K, n_seg), dim3(ATT_THREADS), SMEM_KEYS2, stream, a);
@@ -1081,7 +1086,8 @@ XR_EXPORT int xr_attention_mma(const void* q, void* out, const void* cache_k, co
     if (H / K > 16 && any_short) return XR_ERR_ARG;     // more heads per group than one instruction tile holds
     AttnMmaArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)cache_k, seg_start, seg_len, seg_pos0,
                   block_tables, part_acc, part_ml, q_stride, page_stride, v_offset, H, K, H / K, max_pages, page_size, window,
-                  splits, 0, scale, -1, n_layers, layer, status};
+                  splits, 0, scale, -1, n_layers, layer, status, 16};
+    { long long rows = (long long)(max_seg_len < 1 ? 1 : max_seg_len) * a.G; a.recv_rows = rows < 16 ? (int)rows : 16; }
     a.span = att_choose_span(att_range(max_kv_len, window), (long long)n_seg * K);
     if (any_short && splits != (att_range(max_kv_len, window) + a.span - 1) / a.span + (window > 0 ? 1 : 0)) return XR_ERR_ARG;
     if ((page_size & (page_size - 1)) == 0) { int sh = 0; while ((1 << sh) < page_size) sh++; a.page_shift = sh; }

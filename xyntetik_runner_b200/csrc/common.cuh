@@ -67,6 +67,20 @@ static inline bool xr_pdl_enabled() {
     return on == 1;
 }
 
+// Streaming multiprocessors of the current device (asked once per device): grids and wave models are sized by
+// it, so a part exposed with fewer of them than the full chip is not over-subscribed.
+static inline int xr_sm_count() {
+    static int known[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (known[dev] == 0) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v < 1) v = 148;
+        known[dev] = v;
+    }
+    return known[dev];
+}
+
 template <typename... KArgs, typename... Args>
 static inline void xr_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
     cudaLaunchConfig_t cfg = {};

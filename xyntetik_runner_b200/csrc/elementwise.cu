@@ -323,29 +323,39 @@ XR_EXPORT int xr_rope_store(void* qkv, int dtype, const int* positions, const in
 }
 
 // ---------------------------------------------------------------------------
-// SwiGLU: h = silu(g) * u with g, u the two halves of each row of gu [n, 2F];
-// silu(g) = g / (1 + exp(-g)), and 0 for g < -80 (src/model.c:4451-4452; the
-// reference's kernel is src/kernels.cu:2868-2874).
+// Activation of a feed-forward: gated, h = act(g) * u with g, u the two halves of each row of gu [n, 2F]
+// (src/model.c:4425-4452, `gated_act`); ungated, h = act(x) of x [n, F] (src/model.c:6380-6396).
+// act 1: SiLU, g / (1 + exp(-g)), 0 for g < -80 (src/model.c:4451-4452; the reference's kernel is
+// src/kernels.cu:2868-2874); act 2: tanh-GELU, 0.5 g (1 + tanh(0.7978845608 (g + 0.044715 g^3)))
+// (src/model.c:4438-4441); act 0: none.  Full-precision expf and tanhf: this is the kernel of the true 32-bit path.
 // ---------------------------------------------------------------------------
+__device__ __forceinline__ float xr_activation(int act, float g) {
+    if (act == 1) return g < -80.0f ? 0.0f : g / (1.0f + expf(-g));
+    if (act == 2) return 0.5f * g * (1.0f + tanhf(0.7978845608f * (g + 0.044715f * g * g * g)));
+    return g;
+}
+
 template <typename T>
-__global__ void k_silu_mul(const T* __restrict__ gu, T* __restrict__ h, int n, int F) {
+__global__ void k_act_mul(const T* gu, T* h, int n, int F, int act, int gated) {       // (h may be gu: no __restrict__)
     xr_pdl_launch();
     xr_pdl_wait();
     size_t total = (size_t)n * F;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         size_t t = i / F, f = i % F;
-        float g = xr_to_f32<T>(gu[t * 2 * F + f]), u = xr_to_f32<T>(gu[t * 2 * F + F + f]);
-        float v = g < -80.0f ? 0.0f : (g / (1.0f + expf(-g))) * u;
+        float v;
+        if (gated) v = xr_activation(act, xr_to_f32<T>(gu[t * 2 * F + f])) * xr_to_f32<T>(gu[t * 2 * F + F + f]);
+        else v = xr_activation(act, xr_to_f32<T>(gu[i]));
         h[i] = xr_from_f32<T>(v);
     }
 }
 
-XR_EXPORT int xr_silu_mul(const void* gu, void* h, int dtype, int n, int F, cudaStream_t stream) {
-    if (n < 1 || F < 1) return XR_ERR_ARG;
+// gated: gu [n, 2F] -> h [n, F]; ungated: gu [n, F] -> h [n, F] (h may be gu)
+XR_EXPORT int xr_act_mul(const void* gu, void* h, int dtype, int n, int F, int act, int gated, cudaStream_t stream) {
+    if (n < 1 || F < 1 || act < 0 || act > 2) return XR_ERR_ARG;
     size_t total = (size_t)n * F;
-    int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-    if (dtype == XR_F32) xr_launch((k_silu_mul<float>), dim3(blocks), dim3(256), 0, stream, (const float*)gu, (float*)h, n, F);
-    else if (dtype == XR_BF16) xr_launch((k_silu_mul<__nv_bfloat16>), dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)h, n, F);
+    int blocks = (int)((total + 255) / 256 < (size_t)xr_sm_count() * 16 ? (total + 255) / 256 : xr_sm_count() * 16);
+    if (dtype == XR_F32) xr_launch((k_act_mul<float>), dim3(blocks), dim3(256), 0, stream, (const float*)gu, (float*)h, n, F, act, gated);
+    else if (dtype == XR_BF16) xr_launch((k_act_mul<__nv_bfloat16>), dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)h, n, F, act, gated);
     else return XR_ERR_ARG;
     return xr_launch_status();
 }
@@ -365,7 +375,7 @@ __global__ void k_residual_add(float* __restrict__ x, const T* __restrict__ dlt,
 XR_EXPORT int xr_residual_add(float* x, const void* dlt, int dtype, int n, int d, cudaStream_t stream) {
     if (n < 1 || d < 1) return XR_ERR_ARG;
     size_t total = (size_t)n * d;
-    int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    int blocks = (int)((total + 255) / 256 < xr_sm_count() * 16 ? (total + 255) / 256 : xr_sm_count() * 16);
     if (dtype == XR_F32) xr_launch((k_residual_add<float>), dim3(blocks), dim3(256), 0, stream, x, (const float*)dlt, total);
     else if (dtype == XR_BF16) xr_launch((k_residual_add<__nv_bfloat16>), dim3(blocks), dim3(256), 0, stream, x, (const __nv_bfloat16*)dlt, total);
     else return XR_ERR_ARG;

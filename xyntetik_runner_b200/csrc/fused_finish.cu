@@ -233,7 +233,7 @@ XR_EXPORT int xr_finish_plain(const float* partial, int splits, const float* bia
                               int n, int width, long long ldo, cudaStream_t stream) {
     if (n < 1 || width < 1 || splits < 1 || ldo < width) return XR_ERR_ARG;
     size_t total = (size_t)n * width;
-    int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+    int blocks = (int)((total + 255) / 256 < xr_sm_count() * 8 ? (total + 255) / 256 : xr_sm_count() * 8);
     if (accumulate) {
         if (out_dtype != XR_F32) return XR_ERR_ARG;
         xr_launch((k_finish_plain<float, true>), dim3(blocks), dim3(256), 0, stream, partial, splits, n, width, bias, (float*)out, ldo);

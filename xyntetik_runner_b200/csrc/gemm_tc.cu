@@ -17,10 +17,12 @@
 // A K loop over 64-element blocks runs through a ring of shared-memory stages.  Steps of more than 128 tokens
 // run on pairs of CTAs (k_gemm_tc_pair below): persistent clusters of two, one instruction across both.
 //
-// Epilogues: store (bfloat16 or float32, optional bias), add into the float32 residual stream,
-// two-accumulator SwiGLU (gate rows and up rows of the same features multiply the same X tile;
-// h = silu(g) * u leaves the CTA, the [n, 2F] intermediate never exists), or a split-K partial to
-// scratch that `k_splitk_finish` sums in a fixed order and finishes with the same epilogues.
+// Epilogues: store (bfloat16 or float32, optional bias, optional activation), add into the float32 residual
+// stream, gated (h = act(g) * u: the packed matrix interleaves gate and up rows so that one 128-row tile holds
+// 64 features, sixteen gate rows beside their sixteen up rows in every quarter of the accumulator's lanes; a
+// thread gets its partner's half by warp shuffles and the [n, 2F] intermediate never exists), or a split-K
+// partial to scratch that `k_splitk_finish` sums in a fixed order and finishes with the same epilogues.
+// Activations: none, SiLU (0 below -80, src/model.c:4451-4452), tanh-GELU (src/model.c:4438-4441).
 //
 // Every wait on an mbarrier is bounded: after XR_SPIN_LIMIT polls the waiter raises the CTA's abort
 // flag, every role leaves its loop, in-flight copies are waited for (bounded again), tensor memory is
@@ -41,8 +43,12 @@ __host__ __device__ constexpr int tc_threads(int bn) { return bn <= 16 ? 192 : T
 
 #define TC_EPI_STORE 0     // out[t][r] = acc (+ bias), bfloat16 or float32
 #define TC_EPI_ADD 1       // out[t][r] += acc (+ bias), float32 residual stream
-#define TC_EPI_SWIGLU 2    // out[t][f] = silu(acc_gate) * acc_up
-#define TC_EPI_PARTIAL 3   // scratch[split][t][r] = acc (float32); dual: gate rows then up rows
+#define TC_EPI_GATED 2     // out[t][f] = act(acc of gate row f) * (acc of up row f); W packed with the rows interleaved
+#define TC_EPI_PARTIAL 3   // scratch[split][t][r] = acc (float32), r a row of the product as it is packed
+
+#define TC_ACT_NONE 0
+#define TC_ACT_SILU 1
+#define TC_ACT_GELU_TANH 2
 
 // ---------------------------------------------------------------------------------------------
 // PTX wrappers
@@ -107,6 +113,16 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, float* v) {
 __device__ __forceinline__ float tc_silu(float g) {
     return g < -80.0f ? 0.0f : __fdividef(g, 1.0f + __expf(-g));
 }
+// tanh-GELU: 0.5 g (1 + tanh(0.7978845608 (g + 0.044715 g^3))) (src/model.c:4438-4441), tanh by the hardware's
+// approximation for the same reason
+__device__ __forceinline__ float tc_gelu_tanh(float g) {
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978845608f * (g + 0.044715f * g * g * g)));
+    return 0.5f * g * (1.0f + t);
+}
+__device__ __forceinline__ float tc_act(int act, float g) {
+    return act == TC_ACT_SILU ? tc_silu(g) : (act == TC_ACT_GELU_TANH ? tc_gelu_tanh(g) : g);
+}
 
 // K-major operand tile in shared memory, rows of 128 bytes, 128-byte swizzle, groups of 8 rows 1024 bytes
 // apart: start address and offsets in 16-byte units, descriptor version 1 (bit 46), layout type 2 (bits 61-63).
@@ -130,10 +146,11 @@ struct TcParams {
     float* partial;             // split-K scratch
     int* status;                // device word: non-zero when a wait gave up
     long long ldo;              // row stride of out in elements
-    int n, n_out, K;            // tokens, output features (per half in SwiGLU mode), reduction length
+    int n, n_out, K;            // tokens, output features (gated: features, the product has 128 rows per 64 of them), reduction length
     int splits;                 // z-slices of the grid; slice z handles K blocks [z*total/splits, (z+1)*total/splits)
     int epilogue, out_dtype;
-    int up_row_offset;          // SwiGLU: rows of the up projection start here in W (packed: in units of rows too)
+    int act;                    // TC_ACT_*: applied to the stored value (store epilogue) or to the gate (gated epilogue)
+    int gated;                  // the product's rows are gate and up rows interleaved (also when the epilogue is PARTIAL)
     int bn;                     // tokens per tile: a multiple of 16, at most the kernel's BN (which sizes the buffers)
     int packed;                 // W is stored tile by tile: [row tile][K block][128][64], see xr_gemm_tc
     int w_kblocks;              // packed: K blocks per row tile in the packed array
@@ -141,26 +158,53 @@ struct TcParams {
 };
 
 // ---------------------------------------------------------------------------------------------
-// Epilogue of one tile, run by warps 2..9 once the accumulators are complete.  A warp may only read the 32
+// Epilogue of one tile, run by warps 2..9 once the accumulator is complete.  A warp may only read the 32
 // tensor-memory lanes of its index mod 4, so two warps share each quarter and take alternate 16-column
-// chunks (with sixteen epilogue warps, four share a quarter).  `up_cols`: column offset of the second (up)
-// accumulator of a SwiGLU product.
+// chunks (with sixteen epilogue warps, four share a quarter).
+//
+// Gated products: quarter q of the tile's 128 rows holds the gate rows of features 64 tile + 16 q + (0..15) in its
+// lanes 0..15 and their up rows in lanes 16..31.  Of a 16-column chunk the gate lanes finish columns 0..7 and the
+// up lanes columns 8..15; each gets the other half of what it needs from its partner lane (lane xor 16) by shuffle.
 // ---------------------------------------------------------------------------------------------
-template <bool DUAL>
-__device__ __forceinline__ void tc_epilogue(const TcParams& p, uint32_t tmem_base, int up_cols, int row0, int tok0, int warp, int lane,
+__device__ __forceinline__ void tc_epilogue(const TcParams& p, uint32_t tmem_base, int row0, int tok0, int warp, int lane,
                                             int warps_per_quarter = 2, int split = (int)blockIdx.z) {
     const int quad = warp & 3, chunk_first = (warp - 2) >> 2;
-    const int r = row0 + quad * 32 + lane;            // output feature of this thread
+    const int r = row0 + quad * 32 + lane;            // row of the product that this thread's lane holds
     const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
-    const bool row_ok = r < p.n_out;
+    const bool gated_out = p.epilogue == TC_EPI_GATED;
+    // feature of a gated product: 64 per 128-row tile, 16 per quarter
+    const int f = (row0 >> 1) + quad * 16 + (lane & 15), up_lane = lane >> 4;
+    const bool row_ok = gated_out ? f < p.n_out : r < (p.gated ? ((p.n_out + 63) / 64) * 128 : p.n_out);
     const float b = (p.bias != nullptr && row_ok && (p.epilogue == TC_EPI_STORE || p.epilogue == TC_EPI_ADD) && split == 0)
                         ? p.bias[r] : 0.f;
 #pragma unroll 1
     for (int c0 = chunk_first * 16; c0 < p.bn; c0 += 16 * warps_per_quarter) {
         if (tok0 + c0 >= p.n) break;               // warp-uniform
-        float g[16], u[16];
+        float g[16];
         tc_ld16(taddr + c0, g);
-        if (DUAL) tc_ld16(taddr + up_cols + c0, u);
+        if (gated_out) {
+            // gate lanes send their columns 8..15 and receive the up values of columns 0..7; up lanes the reverse
+            float other[8];
+#pragma unroll
+            for (int c = 0; c < 8; c++) other[c] = __shfl_xor_sync(0xffffffffu, up_lane ? g[c] : g[8 + c], 16);
+            if (!row_ok) continue;
+            const int col0 = tok0 + c0 + (up_lane ? 8 : 0);
+            float v[8];
+#pragma unroll
+            for (int c = 0; c < 8; c++) v[c] = up_lane ? tc_act(p.act, other[c]) * g[8 + c] : tc_act(p.act, g[c]) * other[c];
+            if (p.out_dtype == XR_BF16) {
+                __nv_bfloat16* dst = (__nv_bfloat16*)p.out + (size_t)col0 * p.ldo + f;
+#pragma unroll
+                for (int c = 0; c < 8; c++)
+                    if (col0 + c < p.n) dst[(size_t)c * p.ldo] = __float2bfloat16_rn(v[c]);
+            } else {
+                float* dst = (float*)p.out + (size_t)col0 * p.ldo + f;
+#pragma unroll
+                for (int c = 0; c < 8; c++)
+                    if (col0 + c < p.n) dst[(size_t)c * p.ldo] = v[c];
+            }
+            continue;
+        }
         if (!row_ok) continue;
         if (p.epilogue == TC_EPI_ADD) {
             // read-modify-write of the float32 residual: all loads first, so that they overlap
@@ -175,25 +219,19 @@ __device__ __forceinline__ void tc_epilogue(const TcParams& p, uint32_t tmem_bas
                 if (tok0 + c0 + c < p.n) dst[(size_t)c * p.ldo] = old[c] + (g[c] + b);
             continue;
         }
-        // The values of the chunk first, in one stretch without a branch (the chains of the sixteen elements then
-        // interleave: SiLU is an exp2, a reciprocal and two products each), then the stores; a chunk that runs past
-        // the last token stores only what exists.
+        // a chunk that runs past the last token stores only what exists
         const int live = p.n - (tok0 + c0) < 16 ? p.n - (tok0 + c0) : 16;
         if (p.epilogue == TC_EPI_PARTIAL) {
-            const size_t width = DUAL ? 2 * (size_t)p.n_out : (size_t)p.n_out;
+            const size_t width = p.gated ? (size_t)((p.n_out + 63) / 64) * 128 : (size_t)p.n_out;
             float* dst = p.partial + ((size_t)split * p.n + tok0 + c0) * width + r;
 #pragma unroll
-            for (int c = 0; c < 16; c++) {
-                if (c < live) {
-                    dst[(size_t)c * width] = g[c];
-                    if (DUAL) dst[(size_t)c * width + p.n_out] = u[c];
-                }
-            }
+            for (int c = 0; c < 16; c++)
+                if (c < live) dst[(size_t)c * width] = g[c];
             continue;
         }
         float v[16];
 #pragma unroll
-        for (int c = 0; c < 16; c++) v[c] = DUAL ? tc_silu(g[c]) * u[c] : g[c] + b;
+        for (int c = 0; c < 16; c++) v[c] = tc_act(p.act, g[c] + b);
         if (p.out_dtype == XR_BF16) {
             __nv_bfloat16* dst = (__nv_bfloat16*)p.out + (size_t)(tok0 + c0) * p.ldo + r;
 #pragma unroll
@@ -212,14 +250,14 @@ __device__ __forceinline__ void tc_epilogue(const TcParams& p, uint32_t tmem_bas
 // The kernel.  grid = (token tiles, row tiles, K splits): the CTAs that share a tile of W are neighbours in
 // launch order, so W comes from HBM once and from L2 for the others.
 // ---------------------------------------------------------------------------------------------
-template <int BN, int STAGES, bool DUAL, int MINB>
+template <int BN, int STAGES, int MINB>
 __global__ void __launch_bounds__(tc_threads(BN), MINB)
 k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     constexpr int W_BYTES = TC_BM * TC_BK * 2;
     constexpr int X_BYTES = BN * TC_BK * 2;
-    constexpr int STAGE_BYTES = W_BYTES * (DUAL ? 2 : 1) + X_BYTES;
-    constexpr int ACC_COLS = DUAL ? 2 * BN : BN;
+    constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
+    constexpr int ACC_COLS = BN;
     constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : (ACC_COLS <= 64 ? 64 : (ACC_COLS <= 128 ? 128 : (ACC_COLS <= 256 ? 256 : 512)));
     // carve shared memory: stages (1024-byte aligned), then barriers
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -256,16 +294,12 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     auto load_w = [&](int i) {
         int s = i % STAGES;
         uint8_t* st = smem + s * STAGE_BYTES;
-        mbar_expect_tx(&full[s], W_BYTES * (DUAL ? 2 : 1) + p.bn * TC_BK * 2);
+        mbar_expect_tx(&full[s], W_BYTES + p.bn * TC_BK * 2);
         if (p.packed) {
             // tile (row tile, K block) is 128 consecutive rows of 64 elements: one contiguous 16 KB read
-            int y = (blockIdx.y * p.w_kblocks + kb0 + i) * TC_BM;
-            tma_load_2d(st, &map_w, 0, y, &full[s]);
-            if (DUAL) tma_load_2d(st + W_BYTES, &map_w, 0, y + (p.up_row_offset / TC_BM) * p.w_kblocks * TC_BM, &full[s]);
+            tma_load_2d(st, &map_w, 0, (blockIdx.y * p.w_kblocks + kb0 + i) * TC_BM, &full[s]);
         } else {
-            int kx = (kb0 + i) * TC_BK;
-            tma_load_2d(st, &map_w, kx, row0, &full[s]);
-            if (DUAL) tma_load_2d(st + W_BYTES, &map_w, kx, p.up_row_offset + row0, &full[s]);
+            tma_load_2d(st, &map_w, (kb0 + i) * TC_BK, row0, &full[s]);
         }
     };
     const int early = nkb < STAGES ? nkb : STAGES;
@@ -283,7 +317,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                     if (!mbar_wait(&empty[s], ((i / STAGES) - 1) & 1, abort_flag)) break;
                     load_w(i);
                 }
-                tma_load_2d(smem + s * STAGE_BYTES + W_BYTES * (DUAL ? 2 : 1), &map_x, (kb0 + i) * TC_BK, tok0, &full[s]);
+                tma_load_2d(smem + s * STAGE_BYTES + W_BYTES, &map_x, (kb0 + i) * TC_BK, tok0, &full[s]);
                 issued = i + 1;
             }
             if (*abort_flag) {
@@ -303,14 +337,10 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                 if (!ok) break;
                 tc_fence_after();
                 uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
-                uint32_t b_addr = a_addr + W_BYTES * (DUAL ? 2 : 1);
+                uint32_t b_addr = a_addr + W_BYTES;
 #pragma unroll
-                for (int k = 0; k < TC_BK / 16; k++) {
-                    uint64_t bd = smem_desc_sw128(b_addr + k * 32);
-                    uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
-                    tc_mma(tmem_base, smem_desc_sw128(a_addr + k * 32), bd, idesc, acc);
-                    if (DUAL) tc_mma(tmem_base + BN, smem_desc_sw128(a_addr + W_BYTES + k * 32), bd, idesc, acc);
-                }
+                for (int k = 0; k < TC_BK / 16; k++)
+                    tc_mma(tmem_base, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc, (i > 0 || k > 0) ? 1u : 0u);
                 tc_commit(&empty[s]);          // the stage is free once these MMAs have read it
             }
             if (ok) tc_commit(acc_ready);      // accumulators complete
@@ -319,7 +349,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         // ---------------- epilogue: warps 2..9 ----------------
         bool ok = mbar_wait(acc_ready, 0, abort_flag);
         tc_fence_after();
-        if (ok) tc_epilogue<DUAL>(p, tmem_base, BN, row0, tok0, warp, lane);
+        if (ok) tc_epilogue(p, tmem_base, row0, tok0, warp, lane);
     }
     tc_fence_before();
     __syncthreads();
@@ -388,13 +418,13 @@ __device__ __forceinline__ void mbar_arrive_remote(uint32_t bar_cluster_addr) {
 // of stages runs on across tiles (the producer fetches the next tile's operands while the epilogue of this one
 // runs), and the single product keeps two accumulators in tensor memory, so that the MMAs of the next tile
 // overlap the epilogue too; the SwiGLU product fills tensor memory with one pair of accumulators and waits.
-template <int STAGES, bool DUAL>
+template <int STAGES>
 __global__ void __launch_bounds__(TC2_THREADS, 1)
 k_gemm_tc_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     constexpr int W_BYTES = TC_BM * TC_BK * 2;
     constexpr int X_BYTES = (TC2_BN / 2) * TC_BK * 2;
-    constexpr int STAGE_BYTES = W_BYTES * (DUAL ? 2 : 1) + X_BYTES;
+    constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
     constexpr int TMEM_COLS = 512;
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full = (uint64_t*)(smem + STAGES * STAGE_BYTES);
@@ -410,10 +440,8 @@ k_gemm_tc_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
     const int half = p.bn >> 1;                              // tokens this CTA stages
     const int nkb = (p.K + TC_BK - 1) / TC_BK;
-    const uint32_t stage_bytes = W_BYTES * (DUAL ? 2 : 1) + half * TC_BK * 2;
-    // two accumulators (sets of two for SwiGLU) of TC2_BN columns each when they fit the 512 columns, else one
-    const int ACC_BUFS = (DUAL && p.bn > TC2_BN / 2) ? 1 : 2;
-    const int up_cols = p.bn > TC2_BN / 2 ? TC2_BN : TC2_BN / 2;      // SwiGLU: the up accumulator sits this far after the gate's
+    const uint32_t stage_bytes = W_BYTES + half * TC_BK * 2;
+    constexpr int ACC_BUFS = 2;                              // two accumulators of TC2_BN columns each
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -448,15 +476,9 @@ k_gemm_tc_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     const uint32_t bar = tc_map_to_rank(smem_u32(&full[s]), 0);
                     if (rank == 0) mbar_expect_tx(&full[s], 2 * stage_bytes);
                     int kx = i * TC_BK;
-                    if (p.packed) {
-                        int y = (row_tile * p.w_kblocks + i) * TC_BM;
-                        tma_load_2d_pair(st, &map_w, 0, y, bar);
-                        if (DUAL) tma_load_2d_pair(st + W_BYTES, &map_w, 0, y + (p.up_row_offset / TC_BM) * p.w_kblocks * TC_BM, bar);
-                    } else {
-                        tma_load_2d_pair(st, &map_w, kx, row_tile * TC_BM, bar);
-                        if (DUAL) tma_load_2d_pair(st + W_BYTES, &map_w, kx, p.up_row_offset + row_tile * TC_BM, bar);
-                    }
-                    tma_load_2d_pair(st + W_BYTES * (DUAL ? 2 : 1), &map_x, kx, tok0 + (int)rank * half, bar);
+                    if (p.packed) tma_load_2d_pair(st, &map_w, 0, (row_tile * p.w_kblocks + i) * TC_BM, bar);
+                    else tma_load_2d_pair(st, &map_w, kx, row_tile * TC_BM, bar);
+                    tma_load_2d_pair(st + W_BYTES, &map_x, kx, tok0 + (int)rank * half, bar);
                 }
             }
             if (*abort_flag) {
@@ -488,14 +510,10 @@ k_gemm_tc_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     if (!ok) break;
                     tc_fence_after();
                     uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES);
-                    uint32_t b_addr = a_addr + W_BYTES * (DUAL ? 2 : 1);
+                    uint32_t b_addr = a_addr + W_BYTES;
 #pragma unroll
-                    for (int k = 0; k < TC_BK / 16; k++) {
-                        uint64_t bd = smem_desc_sw128(b_addr + k * 32);
-                        uint32_t acc = (i > kb0 || k > 0) ? 1u : 0u;
-                        tc_mma_pair(acc_addr, smem_desc_sw128(a_addr + k * 32), bd, idesc, acc);
-                        if (DUAL) tc_mma_pair(acc_addr + up_cols, smem_desc_sw128(a_addr + W_BYTES + k * 32), bd, idesc, acc);
-                    }
+                    for (int k = 0; k < TC_BK / 16; k++)
+                        tc_mma_pair(acc_addr, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc, (i > kb0 || k > 0) ? 1u : 0u);
                     tc_commit_pair(&empty[s]);
                 }
                 if (ok) tc_commit_pair(&acc_full[b]);
@@ -511,7 +529,7 @@ k_gemm_tc_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             if (!mbar_wait(&acc_full[b], (j / ACC_BUFS) & 1, abort_flag)) break;
             tc_fence_after();
             const int row0 = (2 * (tile / p.tok_tiles) + (int)rank) * TC_BM, tok0 = (tile % p.tok_tiles) * p.bn;
-            tc_epilogue<DUAL>(p, tmem_base + (uint32_t)b * TC2_BN, up_cols, row0, tok0, warp, lane, 4, split);
+            tc_epilogue(p, tmem_base + (uint32_t)b * TC2_BN, row0, tok0, warp, lane, 4, split);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_remote(acc_empty_bar0 + (uint32_t)b * 8);
@@ -533,25 +551,28 @@ k_gemm_tc_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 struct FinishParams {
     const float* partial; void* out; const float* bias;
     long long ldo;
-    int n, n_out, splits, epilogue, out_dtype, dual;
+    int n, n_out, splits, epilogue, out_dtype, gated, act;
 };
 
 __global__ void k_splitk_finish(FinishParams p) {
     xr_pdl_launch();
     xr_pdl_wait();
     size_t total = (size_t)p.n * p.n_out;
-    size_t width = p.dual ? 2 * (size_t)p.n_out : (size_t)p.n_out;
+    // a gated product's partials are rows as packed: feature f has its gate row at 128 (f / 64) + 32 ((f % 64) / 16)
+    // + f % 16 and its up row sixteen further
+    size_t width = p.gated ? (size_t)((p.n_out + 63) / 64) * 128 : (size_t)p.n_out;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         size_t t = i / p.n_out, r = i % p.n_out;
+        const size_t rg = p.gated ? (r >> 6) * 128 + ((r & 63) >> 4) * 32 + (r & 15) : r;
+        const size_t ru = p.gated ? rg + 16 : rg;
         // four splits' loads in flight together (indices clamped: no load is conditional), summed in split order
         float g = 0.f, u = 0.f;
-        const size_t ru = p.dual ? p.n_out + r : r;
         for (int s0 = 0; s0 < p.splits; s0 += 4) {
             float a[4], b[4];
 #pragma unroll
             for (int q = 0; q < 4; q++) {
                 const float* src = p.partial + ((size_t)min(s0 + q, p.splits - 1) * p.n + t) * width;
-                a[q] = xr_ld_now(src + r);
+                a[q] = xr_ld_now(src + rg);
                 b[q] = xr_ld_now(src + ru);
             }
 #pragma unroll
@@ -560,12 +581,13 @@ __global__ void k_splitk_finish(FinishParams p) {
             for (int q = 0; q < 4; q++) {
                 const bool live = s0 + q < p.splits;
                 g += live ? a[q] : 0.f;
-                u += (live && p.dual) ? b[q] : 0.f;
+                u += (live && p.gated) ? b[q] : 0.f;
             }
         }
         float v;
-        if (p.dual) v = tc_silu(g) * u;
-        else v = g + (p.bias ? p.bias[r] : 0.f);
+        if (p.gated) v = tc_act(p.act, g) * u;
+        else if (p.epilogue == TC_EPI_ADD) v = g + (p.bias ? p.bias[r] : 0.f);
+        else v = tc_act(p.act, g + (p.bias ? p.bias[r] : 0.f));
         size_t o = t * p.ldo + r;
         if (p.epilogue == TC_EPI_ADD) ((float*)p.out)[o] += v;
         else if (p.out_dtype == XR_BF16) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16_rn(v);
@@ -605,24 +627,24 @@ static bool make_map(CUtensorMap* m, const void* base, long long rows, long long
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN, int STAGES, bool DUAL, int MINB>
+template <int BN, int STAGES, int MINB>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, const TcParams& p, dim3 grid, cudaStream_t stream) {
-    constexpr int STAGE_BYTES = TC_BM * TC_BK * 2 * (DUAL ? 2 : 1) + BN * TC_BK * 2;
+    constexpr int STAGE_BYTES = TC_BM * TC_BK * 2 + BN * TC_BK * 2;
     constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + (2 * STAGES + 1) * 8 + 16;
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(k_gemm_tc<BN, STAGES, DUAL, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+        if (cudaFuncSetAttribute(k_gemm_tc<BN, STAGES, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
             return XR_ERR_LAUNCH;
         configured = true;
     }
-    xr_launch((k_gemm_tc<BN, STAGES, DUAL, MINB>), dim3(grid), dim3(tc_threads(BN)), SMEM, stream, mw, mx, p);
+    xr_launch((k_gemm_tc<BN, STAGES, MINB>), dim3(grid), dim3(tc_threads(BN)), SMEM, stream, mw, mx, p);
     return xr_launch_status();
 }
 
-template <int STAGES, bool DUAL>
+#define TC2_STAGES 6
 struct PairLaunch {
-    static constexpr int STAGE_BYTES = TC_BM * TC_BK * 2 * (DUAL ? 2 : 1) + (TC2_BN / 2) * TC_BK * 2;
-    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + (2 * STAGES + 4) * 8 + 16;
+    static constexpr int STAGE_BYTES = TC_BM * TC_BK * 2 + (TC2_BN / 2) * TC_BK * 2;
+    static constexpr int SMEM = TC2_STAGES * STAGE_BYTES + 1024 + (2 * TC2_STAGES + 4) * 8 + 16;
     static void config(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, int clusters, cudaStream_t stream) {
         cfg = {};
         cfg.gridDim = dim3(2 * clusters); cfg.blockDim = dim3(TC2_THREADS); cfg.dynamicSmemBytes = SMEM; cfg.stream = stream;
@@ -639,11 +661,11 @@ struct PairLaunch {
         if (n < 0) {
             n = 0;
             cudaLaunchConfig_t cfg; cudaLaunchAttribute attr[2];
-            config(cfg, attr, 74, nullptr);
+            config(cfg, attr, xr_sm_count() / 2, nullptr);
             cfg.numAttrs = 1;
             int nc = 0;
-            if (cudaFuncSetAttribute(k_gemm_tc_pair<STAGES, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) == cudaSuccess &&
-                cudaOccupancyMaxActiveClusters(&nc, k_gemm_tc_pair<STAGES, DUAL>, &cfg) == cudaSuccess && nc > 0)
+            if (cudaFuncSetAttribute(k_gemm_tc_pair<TC2_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) == cudaSuccess &&
+                cudaOccupancyMaxActiveClusters(&nc, k_gemm_tc_pair<TC2_STAGES>, &cfg) == cudaSuccess && nc > 0)
                 n = nc;
             else
                 cudaGetLastError();        // the single-CTA kernel takes over; leave no error behind
@@ -656,7 +678,7 @@ struct PairLaunch {
         cudaLaunchConfig_t cfg; cudaLaunchAttribute attr[2];
         const int items = p.pair_tiles * p.splits;
         config(cfg, attr, items < most ? items : most, stream);
-        cudaLaunchKernelEx(&cfg, k_gemm_tc_pair<STAGES, DUAL>, mw, mx, p);
+        cudaLaunchKernelEx(&cfg, k_gemm_tc_pair<TC2_STAGES>, mw, mx, p);
         return xr_launch_status();
     }
 };
@@ -666,29 +688,9 @@ static bool pair_enabled() {
     return on == 1;
 }
 
-// CTAs of one product that fit the machine at once: two per SM for the small token tiles (their shared
-// memory is sized for that), one otherwise.
-static int resident_ctas(int bn, bool dual, int sms) { return (bn <= 32 || (bn == 64 && !dual)) ? 2 * sms : sms; }
-
-// Number of K splits when there are few output tiles.  A product runs in waves of `slots` CTAs, and a CTA costs
-// a fixed part (launch, barrier and tensor-memory set-up, filling the pipeline, the epilogue: about as long
-// as streaming six K blocks) plus its K blocks.  The split that minimises waves x (fixed + blocks) is chosen:
-// it fills the machine without cutting the work into pieces that are mostly overhead.
-static int choose_splits(int tiles, int tok_tiles, int total_kb, int slots) {
-    if (tok_tiles > 1 || tiles >= 2 * slots) return 1;       // only products with one tile of tokens are split
-    int max_s = total_kb / 4;
-    if (max_s > 16) max_s = 16;
-    if (max_s < 1) max_s = 1;
-    int best = 1;
-    long long best_cost = -1;
-    for (int s = 1; s <= max_s; s++) {
-        long long ctas = (long long)tiles * s;
-        long long waves = (ctas + slots - 1) / slots;
-        long long cost = waves * (6 + (total_kb + s - 1) / s);
-        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = s; }
-    }
-    return best;
-}
+// CTAs of one product that fit the machine at once: the shared memory of the token tiles up to 64 is sized for
+// two per SM (three for the 16-token tile, of which the grids fill two), one otherwise.
+static int resident_ctas(int bn, int sms) { return bn <= 64 ? 2 * sms : sms; }
 
 // Tokens per tile for a kernel whose buffers hold `cap` of them: up to `cap` tokens, the tokens rounded up to the
 // instruction's step of 16 (no work on padding); more, `cap` -- narrower tiles that would fill the last wave
@@ -703,95 +705,121 @@ static int choose_token_tile(int n, int cap) {
     return cap;
 }
 
-// X: [n, K] bfloat16 (row stride ldx), W: [n_out (x2 when swiglu), K] bfloat16 dense.
-// epilogue: TC_EPI_STORE / TC_EPI_ADD / TC_EPI_SWIGLU.  In SwiGLU mode W holds n_out gate rows followed by
-// n_out up rows and out is [n, n_out].  scratch: float32 workspace of at least xr_gemm_tc_scratch_floats()
-// elements (used when the product is split along K); status: device int, set non-zero if a wait gave up.
-XR_EXPORT long long xr_gemm_tc_scratch_floats(int n, int n_out, int swiglu) {
-    return 16LL * (long long)n * (long long)n_out * (swiglu ? 2 : 1);
+// How a product is cut into work: which kernel, how wide its token tiles, how many slices along K.  One function
+// for every entry point, so that two entry points given the same sizes and the same room for partial sums do the
+// same arithmetic.
+//
+// Costs are in units of the time one CTA needs for one K block (about 0.27 us).  A product runs in waves of
+// `slots` CTAs (CTA pairs in the pair kernel); a CTA costs a fixed part (launch, barrier and tensor-memory set-up,
+// filling the pipeline, the epilogue: about six units) plus its K blocks.  A product that is cut along K also pays
+// for its partial sums' way to memory and back (8 bytes per element and slice at about 5 TB/s, 170,000 elements a
+// unit) and for the kernel that sums them (fifteen units; five when the caller's next kernel does it in passing).
+// The cheapest number of slices is taken; only products with a single tile of tokens are cut (single-CTA kernel).
+struct TcPlan {
+    int bn;            // token capacity of the kernel's tile: 16, 32, 64, 128 or 256
+    int bn_eff;        // tokens per tile as launched
+    int tok_tiles, row_tiles, total_kb, splits;
+    bool pair;
+    long long rows;    // rows of the product (gated: 128 per 64 features)
+};
+
+static TcPlan plan_product(int n, int n_out, int K, bool gated, int force_splits, bool deferred, long long scratch_floats) {
+    TcPlan pl{};
+    pl.bn = n <= 16 ? 16 : (n <= 32 ? 32 : (n <= 64 ? 64 : (n <= 128 ? 128 : 256)));
+    pl.row_tiles = gated ? (n_out + 63) / 64 : (n_out + TC_BM - 1) / TC_BM;
+    pl.rows = gated ? (long long)pl.row_tiles * TC_BM : n_out;
+    pl.total_kb = (K + TC_BK - 1) / TC_BK;
+    pl.bn_eff = choose_token_tile(n, pl.bn);
+    pl.tok_tiles = (n + pl.bn_eff - 1) / pl.bn_eff;
+    const long long per_slice = (long long)n * pl.rows;              // partial sums of one slice
+    const long long finish = deferred ? 5 : 15;
+    const int pair_clusters = (pl.bn == 256 && pair_enabled()) ? PairLaunch::clusters() : 0;
+    pl.pair = pair_clusters > 0;
+    int splits = 1, max_s;
+    long long tiles, slots;
+    if (pl.pair) {
+        pl.bn_eff = (pl.bn_eff + 31) / 32 * 32;
+        pl.tok_tiles = (n + pl.bn_eff - 1) / pl.bn_eff;
+        tiles = (long long)pl.tok_tiles * ((pl.row_tiles + 1) / 2);
+        slots = pair_clusters;
+        max_s = tiles < slots ? (pl.total_kb / 8 < 8 ? pl.total_kb / 8 : 8) : 1;
+    } else {
+        tiles = (long long)pl.row_tiles * pl.tok_tiles;
+        slots = resident_ctas(pl.bn, xr_sm_count());
+        max_s = (pl.tok_tiles > 1 || tiles >= 2 * slots) ? 1 : (pl.total_kb / 4 < 16 ? pl.total_kb / 4 : 16);
+    }
+    if (max_s < 1) max_s = 1;
+    if (force_splits > 0) splits = force_splits;
+    else {
+        long long best_cost = -1;
+        for (int sp = 1; sp <= max_s; sp++) {
+            long long rounds = (tiles * sp + slots - 1) / slots;
+            long long cost = rounds * (6 + (pl.total_kb + sp - 1) / sp);
+            if (sp > 1) cost += finish + sp * per_slice / 170000;
+            if (best_cost < 0 || cost < best_cost) { best_cost = cost; splits = sp; }
+        }
+    }
+    if (splits > pl.total_kb) splits = pl.total_kb;
+    // no room for the partial sums: the product runs uncut (slower, the same result up to the order of the sums)
+    if (splits > 1 && scratch_floats < (long long)splits * per_slice) splits = 1;
+    pl.splits = splits;
+    return pl;
 }
 
-XR_EXPORT int xr_gemm_tc(const void* X, const void* W, const float* bias, void* out, int out_dtype, int epilogue,
+// Room for partial sums that no product of these sizes exceeds.
+XR_EXPORT long long xr_gemm_tc_scratch_floats(int n, int n_out, int gated) {
+    return 16LL * (long long)n * (gated ? (long long)((n_out + 63) / 64) * 128 : (long long)n_out);
+}
+
+// X: [n, K] bfloat16 (row stride ldx).  W: [n_out, K] bfloat16 dense, or packed tile by tile
+// ([row tile][K block][128][64], rows and K padded with zeros to whole tiles; n_out is then the logical row count).
+// epilogue: TC_EPI_STORE / TC_EPI_ADD / TC_EPI_GATED; act: TC_ACT_* (store: on the stored value; gated: on the gate).
+// A gated product needs the packed layout with gate and up rows interleaved (every 128-row tile holds 64 features:
+// in each quarter sixteen gate rows, then their sixteen up rows); n_out counts features and out is [n, n_out].
+// scratch: float32 workspace for products cut along K (xr_gemm_tc_scratch_floats bounds what is used); status:
+// device int, set non-zero if a wait gave up.
+XR_EXPORT int xr_gemm_tc(const void* X, const void* W, const float* bias, void* out, int out_dtype, int epilogue, int act,
                          int n, int n_out, int K, long long ldx, long long ldo, float* scratch,
                          long long scratch_floats, int* status, int force_splits, int defer_finish, int* splits_used,
                          int w_packed, cudaStream_t stream) {
     if (n < 1 || n_out < 1 || K < 8 || (K % 8) != 0 || (ldx % 8) != 0 || ldx < K || ldo < n_out) return XR_ERR_ARG;
     if (((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return XR_ERR_ARG;
-    if (epilogue != TC_EPI_STORE && epilogue != TC_EPI_ADD && epilogue != TC_EPI_SWIGLU) return XR_ERR_ARG;
-    if (epilogue == TC_EPI_ADD && out_dtype != XR_F32) return XR_ERR_ARG;
+    if (epilogue != TC_EPI_STORE && epilogue != TC_EPI_ADD && epilogue != TC_EPI_GATED) return XR_ERR_ARG;
+    if (epilogue == TC_EPI_ADD && (out_dtype != XR_F32 || act != TC_ACT_NONE)) return XR_ERR_ARG;
     if (out_dtype != XR_F32 && out_dtype != XR_BF16) return XR_ERR_ARG;
-    const bool dual = epilogue == TC_EPI_SWIGLU;
-    int bn = n <= 16 ? 16 : (n <= 32 ? 32 : (n <= 64 ? 64 : (n <= 128 ? 128 : 256)));
+    if (act != TC_ACT_NONE && act != TC_ACT_SILU && act != TC_ACT_GELU_TANH) return XR_ERR_ARG;
+    const bool gated = epilogue == TC_EPI_GATED;
+    if (gated && (!w_packed || bias != nullptr)) return XR_ERR_ARG;
+    const TcPlan pl = plan_product(n, n_out, K, gated, force_splits, defer_finish != 0, scratch ? scratch_floats : 0);
     CUtensorMap mw, mx;
-    // Packed W: [row tiles (gate tiles then up tiles for SwiGLU)][K blocks][128][64], rows and K padded with
-    // zeros to whole tiles; n_out must then be the logical row count and, for SwiGLU, the up half starts at
-    // the next multiple of 128 rows.
-    const int w_kblocks = (K + TC_BK - 1) / TC_BK;
-    const int rows_padded = (n_out + TC_BM - 1) / TC_BM * TC_BM;
+    const int rows_padded = gated ? (int)pl.rows : (n_out + TC_BM - 1) / TC_BM * TC_BM;
     if (w_packed) {
-        if (!make_map(&mw, W, (long long)(dual ? 2 : 1) * rows_padded * w_kblocks, TC_BK, TC_BK, TC_BM)) return -3;
-    } else if (!make_map(&mw, W, dual ? 2LL * n_out : n_out, K, K, TC_BM)) return -3;
-    int row_tiles = (n_out + TC_BM - 1) / TC_BM;
-    int bn_eff = choose_token_tile(n, bn);
-    int tok_tiles = (n + bn_eff - 1) / bn_eff;
-    int total_kb = (K + TC_BK - 1) / TC_BK;
-    int splits = force_splits > 0 ? force_splits : choose_splits(row_tiles * tok_tiles, tok_tiles, total_kb, resident_ctas(bn, dual, 148));
-    if (splits > total_kb) splits = total_kb;
-    if (splits > 1 && (scratch == nullptr || scratch_floats < (long long)splits * n * n_out * (dual ? 2 : 1))) splits = 1;
-    // many tokens: pairs of CTAs, each staging half of the tile's tokens; few tiles are cut along K so that the
-    // items fill the CTA pairs.  In units of the time of one K block (about 0.27 us): rounds x (a fixed part of six +
-    // K blocks per item), and for a cut product the finish kernel (fifteen) and the partial sums' way to memory
-    // and back (8 bytes per element and slice at about 5 TB/s); the cheapest number of slices is taken.
-    const int pair_clusters = (bn == 256 && pair_enabled()) ? (dual ? PairLaunch<4, true>::clusters() : PairLaunch<6, false>::clusters()) : 0;
-    const bool pair = pair_clusters > 0;
-    if (pair) {
-        bn_eff = (bn_eff + 31) / 32 * 32;
-        tok_tiles = (n + bn_eff - 1) / bn_eff;
-        const int tiles = tok_tiles * ((row_tiles + 1) / 2);
-        splits = 1;
-        if (force_splits > 0) splits = force_splits;
-        else if (tiles < pair_clusters) {
-            long long best_cost = -1;
-            for (int sp = 1; sp <= 8 && sp * 8 <= total_kb; sp++) {
-                long long rounds = ((long long)tiles * sp + pair_clusters - 1) / pair_clusters;
-                long long cost = rounds * (6 + (total_kb + sp - 1) / sp);
-                if (sp > 1) cost += 15 + (long long)sp * n * n_out * (dual ? 2 : 1) / 170000;
-                if (best_cost < 0 || cost < best_cost) { best_cost = cost; splits = sp; }
-            }
-        }
-        if (splits > total_kb) splits = total_kb;
-        if (splits > 1 && (scratch == nullptr || scratch_floats < (long long)splits * n * n_out * (dual ? 2 : 1))) splits = 1;
-    }
-    if (!make_map(&mx, X, n, K, ldx, pair ? bn_eff / 2 : bn_eff)) return -3;
-    if (row_tiles > 65535 || splits > 65535) return XR_ERR_ARG;
+        if (!make_map(&mw, W, (long long)rows_padded * pl.total_kb, TC_BK, TC_BK, TC_BM)) return -3;
+    } else if (!make_map(&mw, W, n_out, K, K, TC_BM)) return -3;
+    if (!make_map(&mx, X, n, K, ldx, pl.pair ? pl.bn_eff / 2 : pl.bn_eff)) return -3;
+    const int splits = pl.splits;
+    if (pl.row_tiles > 65535 || splits > 65535) return XR_ERR_ARG;
     if (splits_used) *splits_used = splits;
     TcParams p{out, bias, scratch, status, ldo, n, n_out, K, splits, splits > 1 ? TC_EPI_PARTIAL : epilogue, out_dtype,
-               w_packed ? rows_padded : n_out, bn_eff, w_packed, w_kblocks, tok_tiles, tok_tiles * ((row_tiles + 1) / 2)};
-    dim3 grid(tok_tiles, row_tiles, splits);
+               act, gated ? 1 : 0, pl.bn_eff, w_packed, pl.total_kb, pl.tok_tiles, pl.tok_tiles * ((pl.row_tiles + 1) / 2)};
+    dim3 grid(pl.tok_tiles, pl.row_tiles, splits);
     int rc;
-    if (pair) {
-        rc = dual ? PairLaunch<4, true>::launch(mw, mx, p, stream) : PairLaunch<6, false>::launch(mw, mx, p, stream);
-    } else if (!dual) {
-        switch (bn) {
-            case 16: rc = launch_tc<16, 4, false, 3>(mw, mx, p, grid, stream); break;
-            case 32: rc = launch_tc<32, 5, false, 2>(mw, mx, p, grid, stream); break;
-            case 64: rc = launch_tc<64, 4, false, 2>(mw, mx, p, grid, stream); break;
-            case 128: rc = launch_tc<128, 5, false, 1>(mw, mx, p, grid, stream); break;
-            default: rc = launch_tc<256, 4, false, 1>(mw, mx, p, grid, stream); break;
-        }
+    if (pl.pair) {
+        rc = PairLaunch::launch(mw, mx, p, stream);
     } else {
-        switch (bn) {
-            case 16: rc = launch_tc<16, 3, true, 2>(mw, mx, p, grid, stream); break;
-            case 32: rc = launch_tc<32, 3, true, 2>(mw, mx, p, grid, stream); break;
-            case 64: rc = launch_tc<64, 5, true, 1>(mw, mx, p, grid, stream); break;
-            case 128: rc = launch_tc<128, 4, true, 1>(mw, mx, p, grid, stream); break;
-            default: rc = launch_tc<256, 3, true, 1>(mw, mx, p, grid, stream); break;
+        switch (pl.bn) {
+            case 16: rc = launch_tc<16, 4, 3>(mw, mx, p, grid, stream); break;
+            case 32: rc = launch_tc<32, 5, 2>(mw, mx, p, grid, stream); break;
+            case 64: rc = launch_tc<64, 4, 2>(mw, mx, p, grid, stream); break;
+            case 128: rc = launch_tc<128, 5, 1>(mw, mx, p, grid, stream); break;
+            default: rc = launch_tc<256, 4, 1>(mw, mx, p, grid, stream); break;
         }
     }
     if (rc != XR_OK || splits == 1 || defer_finish) return rc;      // deferred: the caller's next kernel sums the partials
-    FinishParams f{scratch, out, bias, ldo, n, n_out, splits, epilogue, out_dtype, dual ? 1 : 0};
+    FinishParams f{scratch, out, bias, ldo, n, n_out, splits, epilogue, out_dtype, gated ? 1 : 0, act};
     size_t total = (size_t)n * n_out;
-    int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+    const int most = xr_sm_count() * 8;
+    int blocks = (int)((total + 255) / 256 < (size_t)most ? (total + 255) / 256 : most);
     xr_launch(k_splitk_finish, dim3(blocks), dim3(256), 0, stream, f);
     return xr_launch_status();
 }
@@ -818,6 +846,11 @@ XR_EXPORT long long xr_gemm_tc_noalloc_max_floats() { return (long long)XR_NOALL
 XR_EXPORT int xr_gemm_tc_noalloc(const void* X, const void* W, const float* bias, void* out, int out_dtype, int epilogue,
                                  int n, int n_out, int K, long long ldx, long long ldo, int* status_out_host,
                                  cudaStream_t stream) {
+    // arguments first: nothing is queued for a call that is refused
+    if (n < 1 || n_out < 1 || K < 8 || (K % 8) != 0 || (ldx % 8) != 0 || ldx < K || ldo < n_out) return XR_ERR_ARG;
+    if (((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return XR_ERR_ARG;
+    if (epilogue != TC_EPI_STORE && epilogue != TC_EPI_ADD) return XR_ERR_ARG;        // (the gated product wants packed weights)
+    if ((out_dtype != XR_F32 && out_dtype != XR_BF16) || (epilogue == TC_EPI_ADD && out_dtype != XR_F32)) return XR_ERR_ARG;
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= XR_NOALLOC_MAX_DEVICES) return -5;
     if (g_noalloc_scratch_ptr[dev] == nullptr) {
@@ -828,20 +861,15 @@ XR_EXPORT int xr_gemm_tc_noalloc(const void* X, const void* W, const float* bias
         g_noalloc_status_ptr[dev] = st;
         g_noalloc_scratch_ptr[dev] = sp;
     }
-    if (n < 1 || n_out < 1 || K < 8) return XR_ERR_ARG;
-    // the split the product would choose, and what it needs of the fixed array
-    const bool dual = epilogue == TC_EPI_SWIGLU;
-    int bn = n <= 16 ? 16 : (n <= 32 ? 32 : (n <= 64 ? 64 : (n <= 128 ? 128 : 256)));
-    int row_tiles = (n_out + TC_BM - 1) / TC_BM, tok_tiles = (n + bn - 1) / bn, total_kb = (K + TC_BK - 1) / TC_BK;
-    int splits = choose_splits(row_tiles * tok_tiles, tok_tiles, total_kb, resident_ctas(bn, dual, 148));
-    if (splits > total_kb) splits = total_kb;
-    long long need = splits > 1 ? (long long)splits * n * n_out * (dual ? 2 : 1) : 0;
-    if (need > (long long)XR_NOALLOC_SCRATCH_FLOATS) return -4;
+    // The cut that the ordinary entry point makes when it has all the room it may want; if the fixed array is too
+    // small for it the call is refused rather than run with another cut (and other rounding) than the caller expects.
+    const TcPlan want = plan_product(n, n_out, K, false, 0, false, xr_gemm_tc_scratch_floats(n, n_out, 0));
+    if (want.splits > 1 && (long long)want.splits * n * n_out > (long long)XR_NOALLOC_SCRATCH_FLOATS) return -4;
     // the status word must start at zero; the scratch needs no clearing (every partial that is read was
     // written by this call first)
     if (cudaMemsetAsync(g_noalloc_status_ptr[dev], 0, sizeof(int), stream) != cudaSuccess) return XR_ERR_LAUNCH;
-    int rc = xr_gemm_tc(X, W, bias, out, out_dtype, epilogue, n, n_out, K, ldx, ldo, g_noalloc_scratch_ptr[dev],
-                        (long long)XR_NOALLOC_SCRATCH_FLOATS, g_noalloc_status_ptr[dev], splits, 0, nullptr, 0, stream);
+    int rc = xr_gemm_tc(X, W, bias, out, out_dtype, epilogue, TC_ACT_NONE, n, n_out, K, ldx, ldo, g_noalloc_scratch_ptr[dev],
+                        (long long)XR_NOALLOC_SCRATCH_FLOATS, g_noalloc_status_ptr[dev], want.splits, 0, nullptr, 0, stream);
     if (rc != XR_OK) return rc;
     if (status_out_host != nullptr) {
         // optional: wait for the product and report whether a wait inside it gave up

@@ -89,7 +89,7 @@ XR_EXPORT int xr_random_normal(void* out, int dtype, long long n, unsigned long 
     if (n < 0 || (dtype != XR_F32 && dtype != XR_BF16)) return XR_ERR_ARG;
     if (n == 0) return XR_OK;
     long long blocks = (n + 255) / 256;
-    if (blocks > 148LL * 32) blocks = 148LL * 32;
+    if (blocks > (long long)xr_sm_count() * 32) blocks = (long long)xr_sm_count() * 32;
     if (dtype == XR_F32) k_random_normal<float><<<(int)blocks, 256, 0, stream>>>((float*)out, n, key, first, mean, std);
     else k_random_normal<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>((__nv_bfloat16*)out, n, key, first, mean, std);
     return xr_launch_status();

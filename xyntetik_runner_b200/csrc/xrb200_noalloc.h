@@ -10,18 +10,23 @@
  *
  *   int xr_gemm_tc_noalloc(X, W, bias, out, out_dtype, epilogue, n, n_out, K, ldx, ldo, status_out_host, stream)
  *
- * computes  out[t][r] = sum_k X[t][k] * W[r][k]  exactly as xr_gemm_tc does (same kernels, same choice of
- * K splits, so the same bits):
+ * computes  out[t][r] = sum_k X[t][k] * W[r][k]  exactly as xr_gemm_tc does when it is given all the scratch it
+ * may want: the same kernels and the same cut along K (one planner decides for both entry points, for every
+ * number of tokens), so the same bits:
  *   X        [n, K] bfloat16, row stride ldx elements (a multiple of 8), 16-byte aligned
- *   W        [n_out, K] bfloat16, dense  ([2 * n_out, K] with epilogue 2: gate rows, then up rows)
+ *   W        [n_out, K] bfloat16, dense
  *   bias     [n_out] float32 or NULL
  *   out      [n, n_out], row stride ldo; out_dtype 0 = float32, 1 = bfloat16
- *   epilogue 0 = store, 1 = add into a float32 `out`, 2 = SwiGLU of the two halves of W
+ *   epilogue 0 = store, 1 = add into a float32 `out`  (the gated product needs weights in the library's packed
+ *            layout and is not offered here)
  *   status_out_host  NULL, or a host int: the call then waits for the product and stores 0, or 1 if a
  *            bounded wait inside a kernel gave up (the output is then not valid)
- *   returns 0, or: -1 sizes/alignment the kernel refuses; -2 CUDA refused a launch; -3 tensor-map encoding
- *            failed; -4 the product needs more split-K scratch than the fixed array holds
- *            (xr_gemm_tc_noalloc_max_floats() float32 values: splits * n * n_out, twice that for SwiGLU);
+ *   returns 0, or: -1 sizes/alignment/epilogue the entry point refuses (checked before anything is queued);
+ *            -2 CUDA refused a launch; -3 tensor-map encoding failed; -4 the cut that the product would choose
+ *            needs more split-K scratch than the fixed array holds (xr_gemm_tc_noalloc_max_floats() float32 values;
+ *            the need is splits * n * n_out) -- the call is refused rather than run with another cut, whose sums
+ *            would round differently from what xr_gemm_tc gives; products that are not cut (most products of more
+ *            than a few hundred tokens) need no scratch and are never refused for it;
  *            -5 set-up failed (no current device, or the array's address could not be resolved).
  *
  * Rules that come with a scratch that nobody allocates:

@@ -292,6 +292,7 @@ class Engine:
 
     def _describe(self, entries: Sequence[StepEntry]) -> StepContext:
         """Flatten the batch and bring its description to the device in one copy."""
+        kernels.tc_workspace_reset(self.device)      # no deferred sum outlives its step
         cache = self.cache
         S_real = len(entries)
         i32 = np.int32

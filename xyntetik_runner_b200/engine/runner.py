@@ -103,28 +103,24 @@ class Runner:
                  rope_scale: Optional[float] = None):
         """model: folder with config.json + model.safetensors.  Or `config` (a typed configuration) with
         `random_seed` for seeded random weights.  ctx: longest request (default min(model limit, 4096), the
-        reference's -c default, src/model.c:3075).  batch: token budget of a step (-b).  parallel: live
+        reference's -c default, src/model.c:3075; 0: as long as the model allows and the free memory holds, its -c 0).  batch: token budget of a step (-b).  parallel: live
         requests.  max_tokens: tokens the page pool holds (default parallel * ctx).  rope_base: use this
         frequency base instead of the configuration's (--rope-base, src/model.c:282).  rope_scale: force linear
         position scaling by this factor instead of the configuration's scaling (--rope-scale, src/model.c:324-326)."""
         if engine is None:
+            from ..config import registry
             if model is not None:
-                from ..config import registry
-                _, cfg = registry.load_config(model)
+                arch, cfg = registry.load_config(model)
             else:
                 cfg = config
-            if rope_base is not None:
-                import dataclasses
-                if not hasattr(cfg, "rope_theta"):
-                    raise ValueError("rope_base: this architecture's configuration has no rope_theta")
-                cfg = dataclasses.replace(cfg, rope_theta=float(rope_base))
-            if rope_scale is not None:
-                import dataclasses
-                from ..config.llama import RopeScaling
-                if not hasattr(cfg, "rope_scaling"):
-                    raise ValueError("rope_scale: this architecture's configuration has no rope_scaling")
-                cfg = dataclasses.replace(cfg, rope_scaling=RopeScaling(rope_type="linear", factor=float(rope_scale)))
-            model_limit = getattr(cfg, "max_position_embeddings", 4096)
+                arch = registry.resolve(cfg.architecture)
+            if rope_base is not None or rope_scale is not None:
+                if arch.override is None:
+                    raise ValueError(f"architecture '{arch.name}' takes no rope_base / rope_scale override")
+                cfg = arch.override(cfg, rope_base=rope_base, rope_scale=rope_scale)
+            model_limit = arch.build_plan(cfg).max_positions        # (parts only, no weights: cheap)
+            if ctx == 0:
+                ctx = self._fit_context(arch, cfg, model_limit, parallel, page_size, dtype, device)
             ctx = ctx or min(model_limit, 4096)
             ep = EngineParams(dtype=dtype, max_tokens=max_tokens or parallel * ctx, page_size=page_size,
                               max_requests=parallel, max_request_tokens=ctx, max_step_tokens=batch, device=device)
@@ -143,6 +139,34 @@ class Runner:
                                    open_request=engine._open)
         self._next_id = 0
         self.timing: Dict[str, float] = {}
+
+    @staticmethod
+    def _fit_context(arch, cfg, model_limit: int, parallel: int, page_size: int, dtype: str, device: str) -> int:
+        """ctx=0, the reference's auto-fit (-c 0, src/main.c:512): the longest context, up to the model's limit, whose
+        keys and values for `parallel` requests fit the device memory that is free now beside the weights (nine
+        tenths of it: the step's buffers need room too)."""
+        plan = arch.build_plan(cfg)
+        elem = 2 if dtype in ("bfloat16", "bf16") else 4
+        wbytes = 0
+        wdt = 2 if getattr(cfg, "torch_dtype", "bfloat16") == "bfloat16" else 4
+        for spec in plan.tensor_specs().values():
+            n = 1
+            for s_ in spec.shape:
+                n *= int(s_)
+            wbytes += n * wdt
+        per_token = 0
+        for e in plan.schedule:
+            need = plan.blocks[e.layer].mixer.kv_need()
+            if need is not None and e.cache_from is None:
+                per_token += 2 * need.kv_heads * need.head_dim * elem
+        free, _ = torch.cuda.mem_get_info(torch.device(device))
+        room = int(0.9 * free) - 2 * wbytes                      # (packing a matrix needs a second copy for a moment)
+        if per_token == 0:
+            return model_limit
+        fit = room // (per_token * parallel) // page_size * page_size
+        if fit < page_size:
+            raise ValueError(f"-c 0: no context fits beside the weights ({free >> 20} MiB free, weights {wbytes >> 20} MiB)")
+        return int(min(model_limit, fit))
 
     def submit(self, prompt: Sequence[int], n: int = 256, temp: float = 0.0, top_k: int = 0, top_p: float = 1.0,
                min_p: float = 0.0, repeat_penalty: float = 1.0, seed: Optional[int] = None,

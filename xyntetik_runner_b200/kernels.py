@@ -50,11 +50,11 @@ def _declare(L: ctypes.CDLL) -> None:
         "xr_embed": [_vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _vp],
         "xr_rmsnorm": [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
         "xr_rope_store": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
-        "xr_silu_mul": [_vp, _vp, _i, _i, _i, _vp],
+        "xr_act_mul": [_vp, _vp, _i, _i, _i, _i, _i, _vp],
         "xr_residual_add": [_vp, _vp, _i, _i, _i, _vp],
         "xr_gemm_simt": [_vp, _i, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _ll, _ll, _vp],
         "xr_attention_simt": [_vp, _vp, _i, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
-        "xr_gemm_tc": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _ll, _ll, _vp, _ll, _vp, _i, _i, ctypes.POINTER(ctypes.c_int), _i, _vp],
+        "xr_gemm_tc": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _ll, _ll, _vp, _ll, _vp, _i, _i, ctypes.POINTER(ctypes.c_int), _i, _vp],
         "xr_finish_add_rmsnorm": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
         "xr_finish_plain": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _ll, _vp],
         "xr_finish_rope_store": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
@@ -150,12 +150,21 @@ def rope_store(qkv: torch.Tensor, positions, tok_seg, block_tables, inv_freq: Op
     _count()
 
 
-def silu_mul(gu: torch.Tensor, h: torch.Tensor) -> None:
+ACT_NONE, ACT_SILU, ACT_GELU_TANH = 0, 1, 2
+ACTIVATIONS = {"none": ACT_NONE, "silu": ACT_SILU, "gelu_tanh": ACT_GELU_TANH}
+
+
+def act_mul(gu: torch.Tensor, h: torch.Tensor, act: int = ACT_SILU, gated: bool = True) -> None:
+    """Gated: h[t][f] = act(gu[t][f]) * gu[t][F + f] for gu [n, 2F]; ungated: h = act(gu) for gu [n, F] (h may be gu)."""
     _dev(gu, h)
     n, F = h.shape
-    assert gu.shape == (n, 2 * F) and gu.dtype == h.dtype
-    _check(lib().xr_silu_mul(gu.data_ptr(), h.data_ptr(), dtype_code(h.dtype), n, F, _stream()), "silu_mul")
+    assert gu.shape == (n, 2 * F if gated else F) and gu.dtype == h.dtype
+    _check(lib().xr_act_mul(gu.data_ptr(), h.data_ptr(), dtype_code(h.dtype), n, F, int(act), int(gated), _stream()), "act_mul")
     _count()
+
+
+def silu_mul(gu: torch.Tensor, h: torch.Tensor) -> None:
+    act_mul(gu, h, ACT_SILU, True)
 
 
 def residual_add(x: torch.Tensor, delta: torch.Tensor) -> None:
@@ -235,30 +244,79 @@ def random_normal(out: torch.Tensor, key: int, mean: float, std: float, first: i
 
 
 # ---------------------------------------------------------------------------
-EPI_STORE, EPI_ADD, EPI_SWIGLU = 0, 1, 2
+EPI_STORE, EPI_ADD, EPI_GATED = 0, 1, 2
+EPI_SWIGLU = EPI_GATED          # the gated epilogue with the SiLU activation
 _TC_SCRATCH_FLOATS = 32 << 20
 _tc_state = {}
 
 
+class Workspace:
+    """Split-K scratch and status word of the tensor-core product on one device.
+
+    A product that is cut along K leaves float32 partial sums here.  When its caller defers the sum to its next
+    kernel the slab stays taken until that kernel has been launched (``PartialSums.release``), and products
+    launched meanwhile get room behind it: two deferred sums can never share memory, whatever order a block
+    runs its parts in.  Slabs are handed out by a bump pointer that returns to the start whenever nothing is
+    outstanding, so the usual order (product, then the kernel that sums it) always uses the same addresses,
+    which CUDA graphs need.  ``reset`` (called at the start of every engine step) drops slabs that a failed
+    step left behind."""
+
+    def __init__(self, device: torch.device):
+        self.scratch = torch.empty(_TC_SCRATCH_FLOATS, dtype=torch.float32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.top = 0            # floats taken from the start of the scratch
+        self.live = 0           # slabs outstanding
+
+    def reset(self) -> None:
+        self.top = self.live = 0
+
+    def room(self):
+        """(address, floats) of the free part."""
+        if self.live == 0:
+            self.top = 0
+        return self.scratch.data_ptr() + 4 * self.top, self.scratch.numel() - self.top
+
+    def take(self, floats: int) -> torch.Tensor:
+        at = self.top
+        self.top += (floats + 63) // 64 * 64
+        self.live += 1
+        return self.scratch[at:at + floats]
+
+    def give_back(self) -> None:
+        self.live = max(0, self.live - 1)
+        if self.live == 0:
+            self.top = 0
+
+
+def workspace(device: torch.device) -> Workspace:
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    ws = _tc_state.get(key)
+    if ws is None:
+        ws = _tc_state[key] = Workspace(device)
+    return ws
+
+
 def tc_workspace(device: torch.device):
     """(split-K scratch, status word) of the tensor-core product on `device`, made on first use."""
+    ws = workspace(device)
+    return ws.scratch, ws.status
+
+
+def tc_workspace_reset(device: torch.device) -> None:
+    """Forget deferred sums that were never finished (a step that failed half way)."""
     key = device.index if device.index is not None else torch.cuda.current_device()
-    st = _tc_state.get(key)
-    if st is None:
-        st = (torch.empty(_TC_SCRATCH_FLOATS, dtype=torch.float32, device=device),
-              torch.zeros(1, dtype=torch.int32, device=device))
-        _tc_state[key] = st
-    return st
+    if key in _tc_state:
+        _tc_state[key].reset()
 
 
 def tc_check_status(device: torch.device) -> None:
     """Raise if a tensor-core kernel gave up a wait since the last check (reads one word from the device)."""
     key = device.index if device.index is not None else torch.cuda.current_device()
-    st = _tc_state.get(key)
-    if st is not None:
-        code = int(st[1].item())
+    ws = _tc_state.get(key)
+    if ws is not None:
+        code = int(ws.status.item())
         if code != 0:
-            st[1].zero_()
+            ws.status.zero_()
             what = {1: "a tcgen05 product", 2: "the bulk-copy decode attention", 3: "the tcgen05 attention", 4: "the tcgen05 attention (shared memory not 1 KB aligned)"}.get(code, "a kernel")
             raise KernelError(f"{what} gave up waiting on a barrier; its output is not valid")
 
@@ -271,56 +329,101 @@ def gemm_tc_supported(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bo
 
 
 TILE_ROWS, TILE_K = 128, 64
+GATED_FEATURES = 64        # features per 128-row tile of a gated product
 
 
 def pack_weight(w: torch.Tensor, halves: int = 1) -> torch.Tensor:
     """Re-lay a [rows, K] bfloat16 matrix tile by tile for the tensor-core product:
     [row tile][K block][128][64], rows and K padded with zeros to whole tiles, so that every tile the
-    kernel fetches is one contiguous 16 KB read.  `halves` = 2 packs the two halves of the rows (gate, up)
-    separately, each padded to whole tiles."""
-    assert w.dtype == torch.bfloat16 and w.dim() == 2 and w.shape[0] % halves == 0
+    kernel fetches is one contiguous 16 KB read.
+
+    `halves` = 2: the rows are F gate rows followed by F up rows of a gated product.  They are interleaved so that
+    a 128-row tile holds 64 features: its rows 32 q .. 32 q + 15 are the gate rows of features 64 tile + 16 q + (0..15)
+    and rows 32 q + 16 .. 32 q + 31 their up rows (q = 0..3: the four quarters of the accumulator's lanes), which
+    lets the product's epilogue combine a feature's two sums inside one warp."""
+    assert w.dtype == torch.bfloat16 and w.dim() == 2 and w.shape[0] % halves == 0 and halves in (1, 2)
     rows, k = w.shape[0] // halves, w.shape[1]
-    rp, kp = -(-rows // TILE_ROWS) * TILE_ROWS, -(-k // TILE_K) * TILE_K
-    out = torch.zeros((halves, rp // TILE_ROWS, kp // TILE_K, TILE_ROWS, TILE_K), dtype=w.dtype, device=w.device)
-    for h in range(halves):
-        src = w[h * rows:(h + 1) * rows]
+    kp = -(-k // TILE_K) * TILE_K
+    if halves == 2:
+        fp = -(-rows // GATED_FEATURES) * GATED_FEATURES
+        both = torch.zeros((2, fp, kp), dtype=w.dtype, device=w.device)
+        both[0, :rows, :k] = w[:rows]
+        both[1, :rows, :k] = w[rows:]
+        # [half][tile][quarter][16][K] -> [tile][quarter][half][16][K]
+        src = both.view(2, fp // GATED_FEATURES, 4, 16, kp).permute(1, 2, 0, 3, 4).reshape(fp * 2, kp)
+        del both
+    else:
+        rp = -(-rows // TILE_ROWS) * TILE_ROWS
         if rp != rows or kp != k:
-            pad = torch.zeros((rp, kp), dtype=w.dtype, device=w.device)
-            pad[:rows, :k] = src
-            src = pad
-        out[h] = src.view(rp // TILE_ROWS, TILE_ROWS, kp // TILE_K, TILE_K).permute(0, 2, 1, 3)
-    return out
+            src = torch.zeros((rp, kp), dtype=w.dtype, device=w.device)
+            src[:rows, :k] = w
+        else:
+            src = w
+    rp = src.shape[0]
+    return src.view(rp // TILE_ROWS, TILE_ROWS, kp // TILE_K, TILE_K).permute(0, 2, 1, 3).contiguous()
+
+
+class PartialSums:
+    """float32 partial sums [splits][n][rows] of a product that was cut along K and whose sum is left to the
+    caller's next kernel.  The slab of the workspace they lie in is this object's until ``release``."""
+
+    def __init__(self, ws: Workspace, partial: torch.Tensor, splits: int):
+        self._ws, self.partial, self.splits = ws, partial, splits
+
+    def release(self) -> None:
+        if self._ws is not None:
+            self._ws.give_back()
+            self._ws = None
+
+
+def _gemm_tc(x, w, out, bias, epilogue, act, force_splits, defer, packed_rows):
+    n, k = x.shape
+    gated = epilogue == EPI_GATED
+    if packed_rows is not None:
+        # w comes from pack_weight(); packed_rows is the logical number of output features
+        n_out = packed_rows
+        tiles = -(-n_out // GATED_FEATURES) if gated else -(-n_out // TILE_ROWS)
+        assert w.dim() == 4 and w.shape[0] == tiles and w.shape[1] == -(-k // TILE_K) and out.shape == (n, n_out)
+        assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and k % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
+    else:
+        if gated:
+            raise KernelError("the gated product takes weights from pack_weight(w, halves=2)")
+        n_out = w.shape[0]
+        assert w.shape[1] == k and out.shape == (n, n_out) and gemm_tc_supported(x, w, out)
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == n_out and not gated)
+    assert not defer or not gated
+    ws = workspace(x.device)
+    at, room = ws.room()
+    used = ctypes.c_int(1)
+    _check(lib().xr_gemm_tc(x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), dtype_code(out.dtype), epilogue, int(act),
+                            n, n_out, k, x.stride(0), out.stride(0), at, room,
+                            ws.status.data_ptr(), force_splits, int(defer), ctypes.byref(used),
+                            int(packed_rows is not None), _stream()), "gemm_tc")
+    splits = used.value
+    _count(1 if (splits == 1 or defer) else 2)
+    if defer and splits > 1:
+        rows = tiles * TILE_ROWS if (gated and packed_rows is not None) else n_out
+        return PartialSums(ws, ws.take(splits * n * rows), splits)
+    return splits
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
-            epilogue: int = EPI_STORE, force_splits: int = 0, defer: bool = False,
-            packed_rows: Optional[int] = None) -> int:
-    """bfloat16 product on tcgen05.  EPI_STORE: out[t][r] = x.w (+bias); EPI_ADD: float32 out += ...;
-    EPI_SWIGLU: w is [2F, K] (gate rows, then up rows), out[t][f] = silu(x.w_gate) * (x.w_up).
+            epilogue: int = EPI_STORE, force_splits: int = 0, packed_rows: Optional[int] = None, act: Optional[int] = None) -> int:
+    """bfloat16 product on tcgen05.  EPI_STORE: out[t][r] = act(x.w + bias); EPI_ADD: float32 out += x.w + bias;
+    EPI_GATED: w from ``pack_weight(w, halves=2)``, out[t][f] = act(x.w_gate[f]) * (x.w_up[f]) (act defaults to SiLU).
+    Returns the number of K splits used."""
+    if act is None:
+        act = ACT_SILU if epilogue == EPI_GATED else ACT_NONE
+    return _gemm_tc(x, w, out, bias, epilogue, act, force_splits, False, packed_rows)
 
-    Returns the number of K splits used.  With `defer` and more than one split, `out` is NOT written: the
-    partial sums [splits][n][n_out] float32 stay in the workspace (``tc_workspace``) for the caller's next
-    kernel (``finish_*``) to sum, together with the bias."""
-    n, k = x.shape
-    if packed_rows is not None:
-        # w comes from pack_weight(); packed_rows is the logical number of output features (per half)
-        n_out = packed_rows
-        assert w.dim() == 5 and w.shape[0] == (2 if epilogue == EPI_SWIGLU else 1) and w.shape[2] == -(-k // TILE_K)
-        assert w.shape[1] == -(-n_out // TILE_ROWS) and out.shape == (n, n_out)
-        assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and k % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
-    else:
-        n_out = w.shape[0] // 2 if epilogue == EPI_SWIGLU else w.shape[0]
-        assert w.shape[1] == k and out.shape == (n, n_out) and gemm_tc_supported(x, w, out)
-    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == n_out and epilogue != EPI_SWIGLU)
-    assert not defer or epilogue != EPI_SWIGLU
-    scratch, status = tc_workspace(x.device)
-    used = ctypes.c_int(1)
-    _check(lib().xr_gemm_tc(x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), dtype_code(out.dtype), epilogue,
-                            n, n_out, k, x.stride(0), out.stride(0), scratch.data_ptr(), scratch.numel(),
-                            status.data_ptr(), force_splits, int(defer), ctypes.byref(used),
-                            int(packed_rows is not None), _stream()), "gemm_tc")
-    _count(1 if (used.value == 1 or defer) else 2)
-    return used.value
+
+def gemm_tc_deferred(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                     epilogue: int = EPI_STORE, force_splits: int = 0, packed_rows: Optional[int] = None) -> Optional[PartialSums]:
+    """The same product, its sum left to the caller when it was cut along K: returns ``PartialSums`` ([splits][n][n_out]
+    float32 in a slab of the workspace; `out` is NOT written, and the bias not added) for the caller's next kernel
+    (``finish_*``) to sum, then ``release()``.  Returns None when the product was not cut: `out` is complete."""
+    r = _gemm_tc(x, w, out, bias, epilogue, ACT_NONE, force_splits, True, packed_rows)
+    return r if isinstance(r, PartialSums) else None
 
 
 def finish_add_rmsnorm(partial: torch.Tensor, splits: int, bias: Optional[torch.Tensor], x: torch.Tensor,

@@ -4,7 +4,7 @@ from .base import (Block, FeedForward, KVNeed, Mixer, Norm, Part, PositionEncodi
 from .attention import GQAAttention
 from .block import PreNormBlock
 from .embedding import Embedding, Head
-from .feed_forward import SwiGLU
+from .feed_forward import GatedFeedForward, MLP, SwiGLU
 from .linear import Linear
 from .norm import RMSNorm
 from .position import NoPosition, Rope

@@ -100,6 +100,7 @@ class GQAAttention(Mixer):
             kernels.finish_rope_store(pend.partial, pend.splits, pend.bias, qkv, ctx.positions, ctx.tok_seg, bt,
                                       rot_freq, store_ptr, page_stride, v_offset, self.H, self.K, self.hd,
                                       rot_dim, ctx.max_pages, ctx.page_size, adjacent, mscale)
+            pend.release()
         else:
             if pend is not None:
                 pend.finish()

@@ -14,7 +14,7 @@ import torch
 
 from .. import kernels
 
-counters = {"tcgen05": 0, "simt": 0}
+counters = {"tcgen05": 0, "simt": 0, "deferred": 0}
 
 
 class Linear:
@@ -42,25 +42,36 @@ class Linear:
     def nbytes(self) -> int:
         return self._nbytes
 
-    def forward(self, x: torch.Tensor, out: torch.Tensor, accumulate: bool = False, defer: bool = False):
-        """out (+)= x W^T (+ bias).  With `defer`, a product that was split along K leaves its partial sums in
-        the workspace and returns ``Pending``; the caller's next kernel sums them (and adds the bias).
-        Otherwise returns None and `out` is complete."""
+    def forward(self, x: torch.Tensor, out: torch.Tensor, accumulate: bool = False, defer: bool = False,
+                act: int = kernels.ACT_NONE):
+        """out (+)= act(x W^T + bias) (an activation only without `accumulate`).  With `defer`, a product that was
+        split along K leaves its partial sums in a slab of the workspace and returns ``Pending``; the caller's next
+        kernel sums them (and adds the bias) and releases the slab.  Otherwise returns None and `out` is complete."""
         from . import linear_tc
-        if self.packed is not None:
+        assert self.halves == 1, "a matrix of two halves is multiplied by forward_gated"
+        assert act == kernels.ACT_NONE or not (accumulate or defer)
+        if self.packed is not None or linear_tc.usable(self, x, out, accumulate):
             counters["tcgen05"] += 1
-            return linear_tc.run(self, x, out, accumulate, defer)
-        if linear_tc.usable(self, x, out, accumulate):
-            counters["tcgen05"] += 1
-            return linear_tc.run(self, x, out, accumulate, defer)
+            return linear_tc.run(self, x, out, accumulate, defer, act)
         kernels.gemm_simt(x, self.weight, out, self.bias, accumulate)
+        if act != kernels.ACT_NONE:
+            kernels.act_mul(out, out, act, gated=False)
         counters["simt"] += 1
         return None
 
-    def swiglu_fused(self) -> bool:
+    def gated_fused(self) -> bool:
         return self.halves == 2 and self.packed is not None
 
-    def forward_swiglu(self, x: torch.Tensor, out: torch.Tensor) -> None:
-        """out[t][f] = silu(x . W_gate[f]) * (x . W_up[f]) in the product's epilogue (packed layout only)."""
-        kernels.gemm_tc(x, self.packed, out, None, kernels.EPI_SWIGLU, packed_rows=self.n_out // 2)
-        counters["tcgen05"] += 1
+    def forward_gated(self, x: torch.Tensor, out: torch.Tensor, act: int = kernels.ACT_SILU,
+                      scratch: Optional[torch.Tensor] = None) -> None:
+        """out[t][f] = act(x . W_gate[f]) * (x . W_up[f]): in the tensor-core product's epilogue when the matrix is
+        packed for it, else as the product [n, 2F] into `scratch` followed by the activation kernel."""
+        assert self.halves == 2
+        if self.packed is not None:
+            kernels.gemm_tc(x, self.packed, out, None, kernels.EPI_GATED, packed_rows=self.n_out // 2, act=act)
+            counters["tcgen05"] += 1
+            return
+        assert scratch is not None and scratch.shape == (x.shape[0], self.n_out)
+        kernels.gemm_simt(x, self.weight, scratch, None, False)
+        counters["simt"] += 1
+        kernels.act_mul(scratch, out, act, gated=True)

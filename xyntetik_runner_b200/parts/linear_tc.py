@@ -2,7 +2,6 @@
 from __future__ import annotations
 
 import os
-from dataclasses import dataclass
 from typing import Optional
 
 import torch
@@ -13,29 +12,38 @@ from .. import kernels
 ENABLED = os.environ.get("XRB200_NO_TC", "0") in ("", "0")
 
 
-@dataclass
 class Pending:
-    """Partial sums [splits][n][width] float32 of a product that still have to be summed into `out`."""
-    partial: torch.Tensor
-    splits: int
-    bias: Optional[torch.Tensor]
-    out: torch.Tensor
-    accumulate: bool
+    """A product whose sum over its K slices is still to be taken: float32 partial sums [splits][n][width] in a
+    slab of the product's workspace, to be summed into `out` (plus the bias).  Whoever takes the sum -- ``finish``,
+    or a kernel that does it in passing -- calls ``release`` afterwards; until then the slab is this product's
+    alone, so a part may start another product before it finishes this one."""
+
+    def __init__(self, sums: "kernels.PartialSums", bias: Optional[torch.Tensor], out: torch.Tensor, accumulate: bool):
+        self.sums, self.partial, self.splits = sums, sums.partial, sums.splits
+        self.bias, self.out, self.accumulate = bias, out, accumulate
+
+    def release(self) -> None:
+        self.sums.release()
 
     def finish(self) -> None:
         kernels.finish_plain(self.partial, self.splits, self.bias, self.out, self.accumulate)
+        self.release()
 
 
 def usable(lin, x, out, accumulate) -> bool:
     return ENABLED and lin.weight is not None and kernels.gemm_tc_supported(x, lin.weight, out)
 
 
-def run(lin, x, out, accumulate, defer=False):
+def run(lin, x, out, accumulate, defer=False, act=kernels.ACT_NONE):
     epi = kernels.EPI_ADD if accumulate else kernels.EPI_STORE
-    if lin.packed is not None:
-        splits = kernels.gemm_tc(x, lin.packed, out, lin.bias, epi, defer=defer, packed_rows=lin.n_out)
-    else:
-        splits = kernels.gemm_tc(x, lin.weight, out, lin.bias, epi, defer=defer)
-    if defer and splits > 1:
-        return Pending(kernels.tc_workspace(x.device)[0], splits, lin.bias, out, accumulate)
+    w, packed_rows = (lin.packed, lin.n_out) if lin.packed is not None else (lin.weight, None)
+    if defer:
+        assert act == kernels.ACT_NONE
+        sums = kernels.gemm_tc_deferred(x, w, out, lin.bias, epi, packed_rows=packed_rows)
+        if sums is None:
+            return None
+        from . import linear
+        linear.counters["deferred"] += 1
+        return Pending(sums, lin.bias, out, accumulate)
+    kernels.gemm_tc(x, w, out, lin.bias, epi, packed_rows=packed_rows, act=act)
     return None

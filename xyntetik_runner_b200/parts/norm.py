@@ -29,6 +29,7 @@ class RMSNorm(Norm):
         if pend is not None and rows is None:
             # the product before this norm left partial sums: sum, add into x and normalise in one pass
             kernels.finish_add_rmsnorm(pend.partial, pend.splits, pend.bias, x, self.weight, out, self.eps)
+            pend.release()
             return
         if pend is not None:
             pend.finish()

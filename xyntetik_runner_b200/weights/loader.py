@@ -181,13 +181,14 @@ def load_tensors(expected: Mapping[str, TensorSpec], source: TensorSource,
 
 
 def write_model_folder(path: str, config_dict: dict, specs: Mapping[str, TensorSpec], seed: int,
-                       dtype: torch.dtype, std: float = 0.02, norm_jitter: float = 0.01) -> None:
-    """Random-weights mode: write config.json and model.safetensors for `specs`."""
+                       dtype: torch.dtype, std: float = 0.02, norm_jitter: float = 0.01, gen_device: str = "cpu") -> None:
+    """Random-weights mode: write config.json and model.safetensors for `specs` (the same file whichever device
+    draws the values)."""
     import json
     import os
     from .safetensors_io import write_safetensors
     os.makedirs(path, exist_ok=True)
-    src = RandomSource(specs, seed, dtype, std=std, norm_jitter=norm_jitter)
+    src = RandomSource(specs, seed, dtype, std=std, norm_jitter=norm_jitter, gen_device=gen_device)
     layout = [(n, src.dtype_of(s), tuple(s.shape)) for n, s in specs.items()]
     cpu = torch.device("cpu")
     write_safetensors(os.path.join(path, "model.safetensors"),
