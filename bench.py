@@ -254,9 +254,19 @@ def timeline(args) -> int:
     lib.xr_trace_dump.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
     host = (ctypes.c_ulonglong * (32 * 4096 * 4))()
     counts = (ctypes.c_uint * 32)()
+    if args.portion > 1:
+        # a prompt step instead: one request of --portion tokens in one step
+        for r in ids:
+            eng.end(r)
+        ids, samplers = ids[:1], samplers[:1]
     for s in range(12):
-        logits = eng.step([StepEntry(r, [int(rng.randint(0, 1000))], [0]) for r in ids])
+        if args.portion > 1:
+            logits = eng.step([StepEntry(ids[0], [int(t) for t in rng.randint(0, 1000, size=args.portion)], [args.portion - 1])])
+        else:
+            logits = eng.step([StepEntry(r, [int(rng.randint(0, 1000))], [0]) for r in ids])
         sampler.pick(logits, samplers)
+        if args.portion > 1:
+            eng.end(ids[0])
         if s == 10:
             torch.cuda.synchronize()
             lib.xr_trace_dump(host, counts)            # drop what came before the step that is read
@@ -274,7 +284,7 @@ def timeline(args) -> int:
         raise SystemExit(f"{len(ev)} launches were recorded: not embedding + norm + {n_layers} equal layers + 2")
     first = 2 + per_layer
     rows = ev[first:first + per_layer + 1]
-    print(f"one layer of a decode step, batch {B}, context {ctx} (times in us)")
+    print(f"one layer of a {'prompt step of ' + str(args.portion) + ' tokens' if args.portion > 1 else 'decode step'}, batch {B}, context {ctx} (times in us)")
     print(f"{'could begin':>12} {'resident before':>16} {'took':>7}  grid / block")
     base = rows[0][0]
     for (t1, t0, g, b), nxt in zip(rows[:-1], rows[1:]):

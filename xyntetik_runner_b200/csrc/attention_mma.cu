@@ -65,6 +65,10 @@ static int att_choose_span(int range, long long items) {
     if (tiles < 1) tiles = 1;
     if (forced > 0) { int s = (forced + ATT_TILE - 1) / ATT_TILE; while ((tiles + s - 1) / s + 1 > ATT_MAX_SPLITS) s++; return s * ATT_TILE; }
     if (items < 1) items = 1;
+    // Many requests with short contexts: one span each.  The requests alone fill the machine, a span's tail is short,
+    // and a single span writes its output itself, so no merge follows (batch 64 at a context of 704, head size 128:
+    // 41 us against 37 + 8 us with four spans and their merge).
+    if (items >= ATT_KEYS_SLOTS && tiles <= 16) return tiles * ATT_TILE;
     // Times in nanoseconds, fitted to measurements at head size 128: a wave costs about 4 us before its first
     // keys arrive plus its tiles; a tile streams in 0.7 us when a CTA has an SM to itself (latency bound) and in
     // 2.1 us when the machine is full (bandwidth bound); the merge costs about 0.1 us per span.
@@ -993,7 +997,11 @@ static int launch_keys_tma(const AttnMmaArgs& a, const void* cache_base, long lo
     const int recv_sized = (a.recv_rows * (HD / 4) + ATT_CLUSTER_MAX) * 16 + ATT_CLUSTER_MAX * 16 * 8 + 16;
     const int ring = depth == 4 ? S4 : (depth == 3 ? S3 : S2), recv = a.max_splits == 1 ? 0 : (recv_sized < RECV ? recv_sized : RECV);
     const int fit = (227 * 1024) / (ring + 1024), fit_recv = (227 * 1024) / (ring + recv + 1024);
-    if (a.max_splits <= ATT_CLUSTER_MAX && att_cluster_merge_enabled() && (fit_recv == fit || ctas <= (long long)fit_recv * xr_sm_count())) {
+    // (clusters of spans are worth it while all of them are resident at once: with several waves of CTAs the
+    // co-scheduling of a cluster's blocks costs more than the merge kernel it saves -- batch 64 at a context of 704:
+    // 53 us as clusters of four against 37 + 8 us with the merge kernel)
+    (void)fit;
+    if (a.max_splits <= ATT_CLUSTER_MAX && att_cluster_merge_enabled() && (a.max_splits == 1 || ctas <= (long long)fit_recv * xr_sm_count())) {
         // the spans of a request as one cluster, which also combines them (returns 2: no merge kernel is to follow)
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = grid; cfg.blockDim = dim3(ATT_THREADS); cfg.stream = stream;

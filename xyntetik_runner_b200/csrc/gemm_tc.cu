@@ -713,7 +713,9 @@ static int choose_token_tile(int n, int cap) {
 // `slots` CTAs (CTA pairs in the pair kernel); a CTA costs a fixed part (launch, barrier and tensor-memory set-up,
 // filling the pipeline, the epilogue: about six units) plus its K blocks.  A product that is cut along K also pays
 // for its partial sums' way to memory and back (8 bytes per element and slice at about 5 TB/s, 170,000 elements a
-// unit) and for the kernel that sums them (fifteen units; five when the caller's next kernel does it in passing).
+// unit in the pair kernel, whose partial sums are tens of megabytes; a quarter of that in the single-CTA kernel, whose
+// few megabytes stay in L2) and for the kernel that sums them (fifteen units; none when the caller's next kernel does
+// it in passing).
 // The cheapest number of slices is taken; only products with a single tile of tokens are cut (single-CTA kernel).
 struct TcPlan {
     int bn;            // token capacity of the kernel's tile: 16, 32, 64, 128 or 256
@@ -732,7 +734,10 @@ static TcPlan plan_product(int n, int n_out, int K, bool gated, int force_splits
     pl.bn_eff = choose_token_tile(n, pl.bn);
     pl.tok_tiles = (n + pl.bn_eff - 1) / pl.bn_eff;
     const long long per_slice = (long long)n * pl.rows;              // partial sums of one slice
-    const long long finish = deferred ? 5 : 15;
+    // (the single-CTA kernel's partial sums are a few megabytes that the kernel after it finds in L2, and a deferred
+    // sum rides in a kernel that runs anyway: measured at 64 tokens, charging them the pair kernel's rates picks five
+    // slices for the 4096 x 4096 product where eight are faster, 9.3 against 7.7 us)
+    const long long finish = deferred ? 0 : 15;
     const int pair_clusters = (pl.bn == 256 && pair_enabled()) ? PairLaunch::clusters() : 0;
     pl.pair = pair_clusters > 0;
     int splits = 1, max_s;
@@ -755,7 +760,7 @@ static TcPlan plan_product(int n, int n_out, int K, bool gated, int force_splits
         for (int sp = 1; sp <= max_s; sp++) {
             long long rounds = (tiles * sp + slots - 1) / slots;
             long long cost = rounds * (6 + (pl.total_kb + sp - 1) / sp);
-            if (sp > 1) cost += finish + sp * per_slice / 170000;
+            if (sp > 1) cost += pl.pair ? 15 + sp * per_slice / 170000 : finish + sp * per_slice / 700000;
             if (best_cost < 0 || cost < best_cost) { best_cost = cost; splits = sp; }
         }
     }
