@@ -186,14 +186,18 @@ class PipelinedFakeExecutor(FakeExecutor):
 
     def __init__(self, cache, stop_at=None):
         super().__init__(cache, stop_at)
-        self.launched_ahead = 0
+        self.launched_ahead = self.ahead_with_prompt = self.ahead_with_admission = 0
 
     def launch(self, plan, feed_rows=None):
         from xyntetik_runner_b200.engine.scheduler import IN_FLIGHT
         for e in plan.entries:
-            fed = feed_rows is not None and e.request.id in feed_rows
+            fed = feed_rows is not None and e.request.id in feed_rows and e.tokens[-1] == IN_FLIGHT
             assert (IN_FLIGHT in e.tokens) == fed, "a token that is still in flight must come through the feed"
+            assert not fed or e.count == 1
         self.launched_ahead += feed_rows is not None
+        if feed_rows is not None:
+            self.ahead_with_prompt += any(e.count > 1 or not e.wants_token for e in plan.entries)
+            self.ahead_with_admission += bool(plan.admitted)
         return self.run(plan)          # commits at launch, as Engine.step does
 
     def wait(self, handle):
@@ -279,6 +283,9 @@ def test_steps_launched_ahead_change_nothing(seed):
             assert steps < 5000
         assert cache.free_pages() == [n_pages] and not cache.live_requests()
         assert (ex.launched_ahead > 0) == ahead
+        if ahead:
+            # not only decode steps: steps with prompt portions, and steps that admit, are launched ahead too
+            assert ex.ahead_with_prompt > 0 and ex.ahead_with_admission > 0 and ex.launched_ahead >= 0.5 * steps
         outcomes.append({i: (r.generated, r.finish_reason) for i, r in s.finished.items()})
     assert outcomes[0] == outcomes[1]
     assert any(reason == "stop" for _, reason in outcomes[0].values())

@@ -59,6 +59,20 @@ class Request:
 IN_FLIGHT = -1       # stands in a request's tokens for one that a launched step has not delivered yet
 
 
+class _IdentitySet:
+    """Membership by identity (requests are dataclasses: their equality compares fields)."""
+
+    def __init__(self, items=()):
+        self._ids = {id(x) for x in items}
+
+    def __contains__(self, x) -> bool:
+        return id(x) in self._ids
+
+
+class _NoLookAhead(Exception):
+    """Planning ahead met a decision that needs the running step's outcome (a preemption, a request to end)."""
+
+
 @dataclass
 class PlannedEntry:
     request: Request
@@ -76,6 +90,7 @@ class StepPlan:
     entries: List[PlannedEntry] = field(default_factory=list)
     preempted: List[object] = field(default_factory=list)
     finished: List[object] = field(default_factory=list)     # requests that planning itself ended (pool too small)
+    admitted: List["Request"] = field(default_factory=list)  # requests that this plan took from the queue
 
     @property
     def n_tokens(self) -> int:
@@ -186,15 +201,39 @@ class Scheduler:
                 hi = mid - 1
         return lo
 
-    def plan(self) -> StepPlan:
+    def _undo(self, plan: StepPlan) -> None:
+        """Take back what a plan that will not run has done: its reservations and its admissions."""
+        for e in plan.entries:
+            self.cache.cancel(e.request.id)
+        for r in reversed(plan.admitted):
+            self.cache.close(r.id)
+            self.live.remove(r)
+            r.status, r.admitted_at = WAITING, -1
+            self._tick -= 1
+            self.waiting.appendleft(r)
+        plan.entries.clear()
+        plan.admitted.clear()
+
+    def plan(self, ahead: bool = False, skip=()) -> StepPlan:
+        """The next step: who runs how many tokens.  `ahead`: the plan is made while the step before it is still
+        running, for the state that step will leave (its tokens standing in the requests as IN_FLIGHT marks);
+        requests in `skip` (known to end with that step) take no part, and a decision that needs that step's outcome
+        -- preempting, ending a request -- is not made: everything is undone and ``_NoLookAhead`` raised."""
         plan = StepPlan()
+        try:
+            return self._plan(plan, ahead, skip)
+        except _NoLookAhead:
+            self._undo(plan)
+            raise
+
+    def _plan(self, plan: StepPlan, ahead: bool, skip) -> StepPlan:
         budget = self.params.max_step_tokens
         chunk_cap = self.params.prefill_chunk or budget
         # 1. decoding requests: one token each; pages for them come before anything else
         i = 0
         while i < len(self.live):
             r = self.live[i]
-            if r.pending != 1 or budget < 1:
+            if r.pending != 1 or budget < 1 or r in skip:
                 i += 1
                 continue
             if self.cache.can_reserve(r.id, 1):
@@ -203,6 +242,8 @@ class Scheduler:
                 budget -= 1
                 i += 1
                 continue
+            if ahead:
+                raise _NoLookAhead()
             if len(self.live) == 1:
                 self._finish(r, "length")          # alone and still no page: the pool is its limit
                 plan.finished.append(r.id)
@@ -215,7 +256,7 @@ class Scheduler:
             # try the same index again (it is r again unless r itself was the victim)
         # 2. requests still reading their prompt, in admission order
         for r in self.live:
-            if r.pending < 1 or budget < 1 or any(e.request is r for e in plan.entries):
+            if r.pending < 1 or budget < 1 or r in skip or any(e.request is r for e in plan.entries):
                 continue
             n = self._fit(r, min(r.pending, budget, chunk_cap))
             if n > 0:
@@ -243,9 +284,12 @@ class Scheduler:
             r.admitted_at = self._tick
             self._tick += 1
             self.live.append(r)
+            plan.admitted.append(r)
             plan.entries.append(PlannedEntry(r, r.computed, n, n == r.pending))
             budget -= n
         # 4. nobody can move: free the newest request's pages for the older ones
+        if not plan.entries and self.live and ahead:
+            return plan                       # (decided when the running step's outcome is known)
         if not plan.entries and self.live:
             if len(self.live) == 1:
                 plan.finished.append(self.live[0].id)
@@ -272,12 +316,12 @@ class Scheduler:
         """Plan and run one step.  Returns [(request id, new token or None, finished)] for requests that
         got a token or finished in this step.
 
-        Looking ahead.  When the step at hand only decodes (every live request one token, nobody waiting, no
-        penalty window to send, nobody about to reach its length), the step after it is known but for the token
-        values: the same requests, one position on.  It is then launched BEFORE this step's tokens are read; the
-        device feeds it the sampled ids itself (executor's `feed`), and the host does its planning while the
-        device works.  A request that turns out to have stopped in this step has one more row computed in the next;
-        that row is dropped when its turn comes.  A step launched ahead is the next call's step."""
+        Looking ahead.  What the step after this one holds does not depend on the tokens this one samples, only on
+        whether they end a request (see ``_plan_ahead``).  So the next step -- decodes, prompt portions, admissions --
+        is planned and launched BEFORE this step's tokens are read; the device feeds it the sampled ids itself
+        (executor's `feed`), and the host does its planning while the device works.  A request that turns out to have
+        met a stop token in this step has one more row computed in the next; that row is dropped when its turn comes.
+        A step launched ahead is the next call's step."""
         plan = handle = None
         if self._ahead is not None:
             plan, handle = self._ahead
@@ -305,12 +349,9 @@ class Scheduler:
         if handle is not None and self.params.look_ahead:
             nxt = self._plan_ahead(plan)
             if nxt is not None:
-                # the tokens this step will bring take their places now, as marks, so that the next step can be described
+                # (the tokens this step will bring stand in their requests as marks now, see _plan_ahead)
                 advanced = True
-                for e in plan.entries:
-                    e.request.computed += e.count
-                    e.request.tokens.append(IN_FLIGHT)
-                rows = {e.request.id: i for i, e in enumerate(plan.entries)}
+                rows = {e.request.id: j for j, e in enumerate(e2 for e2 in plan.entries if e2.wants_token)}
                 try:
                     self._ahead = (nxt, self.executor.launch(nxt, feed_rows=rows))
                     self.stats["steps_launched_ahead"] += 1
@@ -320,9 +361,7 @@ class Scheduler:
                     # and a fault that lasts is raised from there
                     advanced = False
                     self._ahead = None
-                    for e in plan.entries:
-                        e.request.computed -= e.count
-                        e.request.tokens.pop()
+                    self._unmark(plan)
                     self.stats["ahead_launches_failed"] = self.stats.get("ahead_launches_failed", 0) + 1
         if handle is not None:
             sampled: Dict[object, int] = self.executor.wait(handle)
@@ -371,40 +410,45 @@ class Scheduler:
             out.append((r.id, tok, done is not None))
         return out
 
+    def _unmark(self, plan: StepPlan) -> None:
+        for e in plan.entries:
+            e.request.computed -= e.count
+            if e.wants_token:
+                e.request.tokens.pop()
+
     def _plan_ahead(self, plan: StepPlan) -> Optional[StepPlan]:
-        """The step after `plan`, if it can be told without `plan`'s tokens: `plan` decodes one token for every
-        live request, nobody can be admitted, and every request that goes on can take one more token afterwards.
-        A request that reaches its length with this step's token is known to end, whatever the token: it is left
-        out of the next step (unless somebody waits for its slot).  Reserves the next step's pages."""
-        if plan.preempted or len(plan.entries) != len(self.live):
-            return None
-        if self.waiting and self.cache.has_free_slot():
-            return None                      # the next plan may admit somebody: that is for plan() to decide
+        """The step after `plan`, planned while `plan` runs.  What the next step holds does not depend on the tokens
+        that `plan` samples, only on whether they end a request: a prompt's next portion is known, a request that
+        gets a token decodes one more (the device feeds it the token itself), waiting requests are admitted by the
+        slots and pages that are free now.  A request that reaches its length with this step's token is known to
+        end and is left out; one that meets a stop token is not, and has one row computed for nothing.  Not planned
+        ahead: a step whose sampling needs the token on the host (a repeat-penalty window), and a step that would have
+        to preempt or end a request (``plan`` decides that with the outcome in hand).  On success the tokens to come
+        stand in their requests as IN_FLIGHT marks and the next step's pages are reserved; else nothing is changed."""
         limit = self.cache.max_pages_per_request * self.cache.page_size
-        going_on = []
+        ending = []
         for e in plan.entries:
             r = e.request
-            if e.count != 1 or not e.wants_token or r.status != LIVE or r.pending != 1 or r.sampler.needs_window():
-                return None
-            if 0 < r.max_new_tokens <= len(r.generated) + 1 or len(r.tokens) + 1 >= limit:
-                if self.waiting:
-                    return None              # it ends with this step's token and its slot has a taker
-                continue
-            going_on.append(e)
-        if not going_on:
+            if r.status != LIVE:
+                return None                  # it ended in the step before this one: let the queue settle first
+            if e.wants_token:
+                if r.sampler.needs_window():
+                    return None
+                if 0 < r.max_new_tokens <= len(r.generated) + 1 or len(r.tokens) + 1 >= limit:
+                    ending.append(r)
+        for e in plan.entries:
+            e.request.computed += e.count
+            if e.wants_token:
+                e.request.tokens.append(IN_FLIGHT)
+        try:
+            nxt = self.plan(ahead=True, skip=_IdentitySet(ending))
+        except _NoLookAhead:
+            nxt = None
+        if nxt is None or not nxt.entries:
+            if nxt is not None:
+                self._undo(nxt)
+            self._unmark(plan)
             return None
-        # pages: this step's reservations are committed (the executor's launch did that), one more token each
-        taken = []
-        for e in going_on:
-            if not self.cache.can_reserve(e.request.id, 1):
-                for rid in taken:
-                    self.cache.cancel(rid)
-                return None
-            self.cache.reserve(e.request.id, 1)
-            taken.append(e.request.id)
-        nxt = StepPlan()
-        for e in going_on:
-            nxt.entries.append(PlannedEntry(e.request, e.request.computed + e.count, 1, True))
         return nxt
 
     def run_to_completion(self, max_steps: int = 1 << 30) -> None:
