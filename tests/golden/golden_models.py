@@ -16,8 +16,13 @@ GB = {"architectures": ["LlamaForCausalLM"], "hidden_size": 96, "num_hidden_laye
       "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
                        "original_max_position_embeddings": 64},
       "max_position_embeddings": 256, "tie_word_embeddings": False, "hidden_act": "silu", "torch_dtype": "float32"}
-MODELS = {"GA": (GA, 11), "GB": (GB, 12)}
-TOKENS = {"GA": 40, "GB": 100}
+# biases on q, k, v and o, linear position scaling, a head size (12) that is no multiple of 16
+GC = {"architectures": ["LlamaForCausalLM"], "hidden_size": 72, "num_hidden_layers": 2, "num_attention_heads": 6,
+      "num_key_value_heads": 2, "head_dim": 12, "intermediate_size": 104, "vocab_size": 211, "rms_norm_eps": 2e-5,
+      "rope_theta": 10000.0, "rope_scaling": {"rope_type": "linear", "factor": 2.5}, "max_position_embeddings": 256,
+      "tie_word_embeddings": False, "attention_bias": True, "hidden_act": "silu", "torch_dtype": "float32"}
+MODELS = {"GA": (GA, 11), "GB": (GB, 12), "GC": (GC, 13)}
+TOKENS = {"GA": 40, "GB": 100, "GC": 60}
 
 
 def lcg_uniform(seed: int, n: int) -> np.ndarray:
@@ -40,13 +45,16 @@ def tensors_for(cfg: dict, seed: int):
                    (p + "self_attn.k_proj.weight", (K * hd, d)), (p + "self_attn.v_proj.weight", (K * hd, d)),
                    (p + "self_attn.o_proj.weight", (d, H * hd)), (p + "post_attention_layernorm.weight", (d,)),
                    (p + "mlp.gate_proj.weight", (F, d)), (p + "mlp.up_proj.weight", (F, d)), (p + "mlp.down_proj.weight", (d, F))]
+        if cfg.get("attention_bias"):
+            shapes += [(p + "self_attn.q_proj.bias", (H * hd,)), (p + "self_attn.k_proj.bias", (K * hd,)),
+                       (p + "self_attn.v_proj.bias", (K * hd,)), (p + "self_attn.o_proj.bias", (d,))]
     shapes.append(("model.norm.weight", (d,)))
     if not cfg["tie_word_embeddings"]:
         shapes.append(("lm_head.weight", (V, d)))
     out = {}
     for i, (name, shape) in enumerate(shapes):
         u = lcg_uniform(seed * 1000 + i, int(np.prod(shape)))
-        vals = 1.0 + 0.1 * u if len(shape) == 1 else 0.12 * u
+        vals = 0.3 * u if name.endswith(".bias") else (1.0 + 0.1 * u if len(shape) == 1 else 0.12 * u)
         out[name] = vals.astype(np.float32).reshape(shape)
     return out
 

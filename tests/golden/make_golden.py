@@ -1,5 +1,5 @@
 #!/usr/bin/env python3
-"""Makes tests/golden/*.npz: logits of the REFERENCE's own CPU model code on two tiny llama models.
+"""Makes tests/golden/*.npz: logits of the REFERENCE's own CPU model code on three tiny llama models.
 
 How it was run (offline, CPU only).  The reference's sources were copied to a scratch folder and a small
 driver was compiled against them, with the CPU-only backend stub in place of the CUDA backend (the source
@@ -97,10 +97,13 @@ def write_gguf(path: str, cfg: dict, tensors: dict) -> None:
            kv_u32(f"{a}.attention.head_count", H), kv_u32(f"{a}.attention.head_count_kv", K),
            kv_u32(f"{a}.attention.key_length", hd), kv_u32(f"{a}.attention.value_length", hd),
            kv_f32(f"{a}.attention.layer_norm_rms_epsilon", cfg["rms_norm_eps"]), kv_f32(f"{a}.rope.freq_base", cfg["rope_theta"])]
+    sc = cfg.get("rope_scaling") or {}
+    if sc.get("rope_type", sc.get("type")) == "linear":            # src/model.c:317-326, 361-362
+        kvs += [kv_str(f"{a}.rope.scaling.type", "linear"), kv_f32(f"{a}.rope.scaling.factor", sc["factor"])]
     out = [("token_embd.weight", tensors["model.embed_tokens.weight"]), ("output_norm.weight", tensors["model.norm.weight"])]
     if "lm_head.weight" in tensors:
         out.append(("output.weight", tensors["lm_head.weight"]))
-    if cfg.get("rope_scaling"):
+    if sc.get("rope_type", sc.get("type")) == "llama3":
         plain = rope_inv_freq(cfg["rope_theta"], hd)
         scaled = rope_inv_freq(cfg["rope_theta"], hd, cfg["rope_scaling"])
         out.append(("rope_freqs.weight", (plain.astype(np.float64) / scaled.astype(np.float64)).astype(np.float32)))
@@ -115,6 +118,12 @@ def write_gguf(path: str, cfg: dict, tensors: dict) -> None:
                 (f"blk.{l}.ffn_gate.weight", tensors[p + "mlp.gate_proj.weight"]),
                 (f"blk.{l}.ffn_up.weight", tensors[p + "mlp.up_proj.weight"]),
                 (f"blk.{l}.ffn_down.weight", tensors[p + "mlp.down_proj.weight"])]
+        if cfg.get("attention_bias"):
+            # optional tensors (src/model.c:2832-2837); the q and k biases follow their rows' permutation
+            out += [(f"blk.{l}.attn_q.bias", permute_rows(tensors[p + "self_attn.q_proj.bias"].reshape(-1, 1), H, hd).reshape(-1)),
+                    (f"blk.{l}.attn_k.bias", permute_rows(tensors[p + "self_attn.k_proj.bias"].reshape(-1, 1), K, hd).reshape(-1)),
+                    (f"blk.{l}.attn_v.bias", tensors[p + "self_attn.v_proj.bias"]),
+                    (f"blk.{l}.attn_output.bias", tensors[p + "self_attn.o_proj.bias"])]
     header = struct.pack("<IIQQ", 0x46554747, 3, len(out), len(kvs))
     info, off = b"", 0
     for name, arr in out:

@@ -10,7 +10,7 @@ from plain_llama import (PlainLlama, attention, rope_apply, rope_inv_freq, sampl
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
 
-@pytest.mark.parametrize("name", ["GA", "GB"])
+@pytest.mark.parametrize("name", ["GA", "GB", "GC"])
 def test_plain_matches_the_reference_cpu_code(name, tmp_path):
     import sys
     sys.path.insert(0, GOLDEN)
