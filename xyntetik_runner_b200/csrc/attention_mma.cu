@@ -59,11 +59,8 @@ struct AttnMmaArgs {
 // taken: few requests are cut finely enough to fill the machine, many are cut so that the last wave is full.
 // The partition into spans changes only the order of the float32 sums, never which keys a query sees.
 static int att_choose_span(int range, long long items) {
-    static int forced = -1;
-    if (forced < 0) { const char* e = getenv("XRB200_ATTENTION_SPAN"); forced = e ? atoi(e) : 0; if (forced < 0) forced = 0; }
     int tiles = (range + ATT_TILE - 1) / ATT_TILE;
     if (tiles < 1) tiles = 1;
-    if (forced > 0) { int s = (forced + ATT_TILE - 1) / ATT_TILE; while ((tiles + s - 1) / s + 1 > ATT_MAX_SPLITS) s++; return s * ATT_TILE; }
     if (items < 1) items = 1;
     // Many requests with short contexts: one span each.  The requests alone fill the machine, a span's tail is short,
     // and a single span writes its output itself, so no merge follows (batch 64 at a context of 704, head size 128:

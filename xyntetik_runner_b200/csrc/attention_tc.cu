@@ -515,15 +515,13 @@ XR_EXPORT int xr_attention_tc(const void* q, void* out, const void* cache_base, 
                  window, n_layers, layer, scale * 1.4426950408889634f};
     constexpr int SMEM = 14 * TA_ROWS * 128 + 128 + 2 * 2 * 128 * 4;
     static bool configured = false;
-    static bool p_tmem = true;                 // XRB200_ATTENTION_P_SMEM=1: P through shared memory (for comparisons)
+    const bool p_tmem = true;                  // P stays in tensor memory (the other instantiation passes P through shared memory)
     if (!configured) {
         if (cudaFuncSetAttribute(k_attention_tc<true, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
             cudaFuncSetAttribute(k_attention_tc<false, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
             cudaFuncSetAttribute(k_attention_tc<true, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
             cudaFuncSetAttribute(k_attention_tc<false, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
             return XR_ERR_LAUNCH;
-        const char* e = getenv("XRB200_ATTENTION_P_SMEM");
-        p_tmem = !(e && e[0] && e[0] != '0');
         configured = true;
     }
     long long tiles = ((long long)max_seg_len * G + TA_ROWS - 1) / TA_ROWS;

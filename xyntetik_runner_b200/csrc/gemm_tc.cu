@@ -682,11 +682,6 @@ struct PairLaunch {
         return xr_launch_status();
     }
 };
-static bool pair_enabled() {
-    static int on = -1;
-    if (on < 0) { const char* e = getenv("XRB200_NO_PAIR"); on = (e && e[0] && e[0] != '0') ? 0 : 1; }
-    return on == 1;
-}
 
 // CTAs of one product that fit the machine at once: the shared memory of the token tiles up to 64 is sized for
 // two per SM (three for the 16-token tile, of which the grids fill two), one otherwise.
@@ -696,12 +691,9 @@ static int resident_ctas(int bn, int sms) { return bn <= 64 ? 2 * sms : sms; }
 // instruction's step of 16 (no work on padding); more, `cap` -- narrower tiles that would fill the last wave
 // better were measured (144..240 at 2,048 tokens) and are no faster, the product being bound by the operand
 // traffic of its tiles rather than by the number of waves.  The width changes nothing in the sums: every
-// output element is one accumulator over all of K.  XRB200_TOKEN_TILE=<width> overrides it in tuning runs.
+// output element is one accumulator over all of K.
 static int choose_token_tile(int n, int cap) {
     if (n <= cap) return (n + 15) / 16 * 16;
-    static int forced = -1;
-    if (forced < 0) { const char* e = getenv("XRB200_TOKEN_TILE"); forced = e ? atoi(e) : 0; }
-    if (forced >= 16 && forced <= cap && forced % 16 == 0) return forced;
     return cap;
 }
 
@@ -738,7 +730,7 @@ static TcPlan plan_product(int n, int n_out, int K, bool gated, int force_splits
     // sum rides in a kernel that runs anyway: measured at 64 tokens, charging them the pair kernel's rates picks five
     // slices for the 4096 x 4096 product where eight are faster, 9.3 against 7.7 us)
     const long long finish = deferred ? 0 : 15;
-    const int pair_clusters = (pl.bn == 256 && pair_enabled()) ? PairLaunch::clusters() : 0;
+    const int pair_clusters = pl.bn == 256 ? PairLaunch::clusters() : 0;
     pl.pair = pair_clusters > 0;
     int splits = 1, max_s;
     long long tiles, slots;

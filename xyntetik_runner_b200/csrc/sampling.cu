@@ -794,18 +794,14 @@ static int launch_sample_cluster(const SampleArgs& a, int rows, cudaStream_t str
     return xr_launch_status();
 }
 
-// Whether these rows go to the cluster kernel (XRB200_NO_CLUSTER_SAMPLE=1 keeps the one-block kernel).  A cluster
+// Whether these rows go to the cluster kernel (xr_sample_one_block is the entry point of the other).  A cluster
 // block fills an SM (1,024 threads of 64 registers), so clusters run in waves of (SMs / 8) rows.  Measured at a
 // vocabulary of 128,256 with top-k and top-p: 180 us a wave (8 rows 180, 24 rows 355, 48 rows 700), where the
 // one-block kernel takes 715 us for any number of rows up to the SM count; up to two waves the cluster kernel wins.
 static bool smp_use_cluster(int rows, int V) {
-    static int off = -1, sms = 0;
-    if (off < 0) {
-        const char* e = getenv("XRB200_NO_CLUSTER_SAMPLE"); off = (e && e[0] && e[0] != '0') ? 1 : 0;
-        int dev = 0; cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < SMP_CL) sms = SMP_CL;
-    }
-    if (off || V <= SMP_THREADS || (long long)V > (long long)SMP_CL * SMP_THREADS * SMP_PER) return false;
+    int sms = xr_sm_count();
+    if (sms < SMP_CL) sms = SMP_CL;
+    if (V <= SMP_THREADS || (long long)V > (long long)SMP_CL * SMP_THREADS * SMP_PER) return false;
     return rows <= 2 * (sms / SMP_CL);
 }
 

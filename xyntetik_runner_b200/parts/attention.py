@@ -21,12 +21,13 @@ from ..weights.loader import TensorSpec
 from .base import KVNeed, Mixer, PositionEncoding, register_mixer
 from .linear import Linear
 
-# XRB200_NO_MMA_ATTENTION=1 sends bfloat16 attention to the float32-arithmetic kernel (for bisecting)
-USE_MMA = os.environ.get("XRB200_NO_MMA_ATTENTION", "0") in ("", "0")
-# XRB200_NO_TMA_ATTENTION=1 keeps the decode kernel on per-thread cp.async gathers
+# Which attention kernels the mixer may use (module attributes, so that a test can compare paths): the mma.sync kernels
+# for bfloat16 (else the float32-arithmetic kernel), the tcgen05 kernel for prompt portions, bulk copies in the decode
+# kernel.  XRB200_NO_TMA_ATTENTION=1 (read once) keeps the decode kernel on per-thread cp.async gathers: a test runs
+# generation both ways in child processes and compares the tokens.
+USE_MMA = True
+USE_TC = True
 USE_TMA = os.environ.get("XRB200_NO_TMA_ATTENTION", "0") in ("", "0")
-# XRB200_NO_TC_ATTENTION=1 keeps prompt portions on the mma.sync kernel
-USE_TC = os.environ.get("XRB200_NO_TC_ATTENTION", "0") in ("", "0")
 counters = {"mma": 0, "simt": 0, "tcgen05": 0}
 
 

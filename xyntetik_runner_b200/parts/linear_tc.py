@@ -1,15 +1,13 @@
 """The tensor-core route of ``Linear``: bfloat16 activations times a bfloat16 matrix on tcgen05."""
 from __future__ import annotations
 
-import os
 from typing import Optional
 
 import torch
 
 from .. import kernels
 
-# XRB200_NO_TC=1 sends every product to the float32 FMA kernel (for bisecting a difference)
-ENABLED = os.environ.get("XRB200_NO_TC", "0") in ("", "0")
+ENABLED = True         # (False sends every product to the float32 FMA kernel: a test may set it to bisect a difference)
 
 
 class Pending:
