@@ -318,6 +318,11 @@ ATT_CASES = [
     (4, 4, 64, 8, 0, [(1099, 1), (500, 4), (1000, 16), (3, 2), (767, 1), (768, 1), (100, 1), (1090, 3), (0, 1), (511, 1), (512, 2), (7, 1)]),
     (16, 8, 64, 16, 1000, [(4999, 1), (900, 1), (999, 1), (1000, 2), (1001, 1), (3000, 1), (2500, 2), (40, 1)]),
     (16, 16, 64, 64, 0, [(699, 1), (5, 1), (350, 1), (351, 1), (64, 1), (698, 2), (200, 1), (0, 1)]),
+    # pages of 16 and a block table of 63 entries (1,008 tokens, no multiple of the 64-key tile): the last tile of the
+    # longest request would look one entry past its row of the table -- the next request's row, or past the table's
+    # end for the last request -- if the copy did not stop at the row's length
+    (8, 2, 64, 16, 0, [(200, 1), (999, 1)]),
+    (8, 2, 128, 16, 0, [(1007, 1), (999, 1), (3, 1)]),
 ]
 
 
