@@ -471,7 +471,7 @@ def main() -> int:
         clocks.stop()
         print(json.dumps({"prefill_only": True, "tokens": 2048, "ms": pre["ms"], "tok_s": pre["value"]}))
         return 0
-    decode_region(args.batch, start_len, 8, 8)          # untimed: clocks and caches as in the middle of a run
+    decode_region(args.batch, start_len, min(8, K), min(8, W))          # untimed: clocks and caches as in the middle of a run
     head = decode_point(args.batch, start_len, K, W, R)
     if args.decode_only:
         clocks.stop()

@@ -407,7 +407,7 @@ def test_prompt_attention_finds_keys_at_tile_page_and_window_edges(kind, hd, pag
     assert float((got - ref).abs().max() / ref.abs().max()) <= 1.5e-2
 
 
-@pytest.mark.parametrize("n,d", [(6, 200), (6, 1000), (3, 4096), (13, 5128), (70, 1000)])
+@pytest.mark.parametrize("n,d", [(6, 200), (6, 1000), (3, 4096), (13, 5128), (70, 1000), (40, 4096), (64, 2048), (20, 5120), (70, 8192), (17, 1028)])
 def test_fused_finishes_match_the_separate_kernels(n, d):
     """Deferred split-K products finished by the fused kernels give what product + separate kernels give
     (one block per token for narrow rows or many tokens, a cluster of blocks per token otherwise)."""
