@@ -31,7 +31,7 @@ from typing import Dict, Iterable, List, Optional, Tuple
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 RUNNER = os.path.join(HERE, "_ref", "runner")
-REFERENCE_SOURCE = "/root/reference"
+REFERENCE_SOURCE = os.environ.get("XYNTETIK_REFERENCE_SRC", "")      # the reference's source tree, to build the binary from when it is missing
 GGUF_F32, GGUF_BF16 = 0, 30            # tensor type codes (src/quants.h:22)
 
 
@@ -39,8 +39,8 @@ def ensure_runner() -> Tuple[Optional[str], str]:
     """(path of the reference binary, how it was had) or (None, why not)."""
     if os.path.isfile(RUNNER) and os.access(RUNNER, os.X_OK):
         return RUNNER, "built beforehand (baseline/_ref/runner)"
-    if not os.path.isdir(os.path.join(REFERENCE_SOURCE, "src")):
-        return None, f"baseline/_ref/runner is not there and the reference's sources ({REFERENCE_SOURCE}) are not on this machine"
+    if not REFERENCE_SOURCE or not os.path.isdir(os.path.join(REFERENCE_SOURCE, "src")):
+        return None, "baseline/_ref/runner is not there and XYNTETIK_REFERENCE_SRC does not name the reference's source tree"
     if shutil.which("make") is None or shutil.which("gcc") is None:
         return None, "make or gcc is not installed"
     work = tempfile.mkdtemp(prefix="xr_ref_build_")
