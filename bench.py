@@ -215,10 +215,11 @@ def one_kernel(args) -> int:
               f"{nbytes / us / 1e3:.0f} GB/s of weights, {2.0 * args.tokens * args.rows * halves * args.k / us / 1e6:.1f} TFLOP/s")
     elif args.kernel == "attention":
         B, ctx, L, H, K, hd = args.batch, args.context, args.portion, args.heads, args.kv_heads, args.head_dim
-        us = measure.time_attention(B, ctx, L, H, K, hd, args.page_size, it, plain, not args.no_tc, not args.no_tma)
-        flops = 4.0 * B * H * hd * (L * (ctx - L) + L * (L + 1) / 2)
-        print(f"attention batch={B} context={ctx} portion={L} heads={H}/{K} head_dim={hd}: {us:.1f} us, "
-              f"{B * ctx * K * hd * 4 / us / 1e3:.0f} GB/s of keys+values, {flops / us / 1e6:.1f} TFLOP/s")
+        us = measure.time_attention(B, ctx, L, H, K, hd, args.page_size, it, plain, not args.no_tc, not args.no_tma, spread=args.spread)
+        lengths = measure.spread_lengths(B, ctx, L) if args.spread else [ctx] * B
+        flops = sum(4.0 * H * hd * (L * (c - L) + L * (L + 1) / 2) for c in lengths)
+        print(f"attention batch={B} context={ctx}{' (lengths spread from an eighth of it)' if args.spread else ''} portion={L} heads={H}/{K} head_dim={hd}: {us:.1f} us, "
+              f"{sum(lengths) * K * hd * 4 / us / 1e3:.0f} GB/s of keys+values, {flops / us / 1e6:.1f} TFLOP/s")
     else:
         for name in measure.SAMPLING_SETTINGS:
             us = measure.time_sampling(args.sample_rows, args.vocab, name, it, plain, args.one_block)
@@ -325,7 +326,7 @@ def main() -> int:
                                ("vocab", int, 128256), ("iters", int, 20), ("sample-rows", int, 8)):
         ap.add_argument(f"--{name}", type=typ, default=default, help=argparse.SUPPRESS)
     ap.add_argument("--epilogue", choices=["store", "add", "swiglu"], default="store", help=argparse.SUPPRESS)
-    for name in ("plain", "no-tc", "no-tma", "one-block"):
+    for name in ("plain", "no-tc", "no-tma", "one-block", "spread"):
         ap.add_argument(f"--{name}", action="store_true", help=argparse.SUPPRESS)
     args = ap.parse_args()
     if args.gpus != 1:

@@ -274,7 +274,7 @@ def _paged_case(seed, H, K, hd, page, seg_specs, dtype, window=0, spike=None, sp
                 ref=torch.cat(refs), n=n, n_seg=n_seg, max_pages=max_pages, max_len=max_len, lens_host=lens, scale=scale)
 
 
-def _run_attention(case, kind, H, K, hd, page, window, dtype, tma=False):
+def _run_attention(case, kind, H, K, hd, page, window, dtype, tma=False, uneven=False):
     from xyntetik_runner_b200 import kernels
     c = case
     out = torch.zeros(c["n"], H * hd, dtype=dtype, device=DEV)
@@ -293,7 +293,7 @@ def _run_attention(case, kind, H, K, hd, page, window, dtype, tma=False):
         kernels.attention_mma(c["qkv"], qkv_dim, out, k_ptr, c["starts"], c["lens"], c["pos0"], c["bt"], pa, pm, page_stride,
                               v_off, H, K, hd, c["max_pages"], page, window, c["scale"], c["n_seg"], int(lens.max()),
                               c["max_len"], splits, bool((lens * G <= 16).any()), bool((lens * G > 16).any()),
-                              group=(cache.data_ptr(), cache.shape[0], cache.shape[1], 0) if tma else None)
+                              group=(cache.data_ptr(), cache.shape[0], cache.shape[1], 0) if tma else None, uneven=uneven)
         kernels.tc_check_status(torch.device(DEV))
     return out.cpu().double()
 
@@ -342,6 +342,63 @@ def test_attention_kernels(case_id, kind):
     tol = 2e-5 if kind == "simt_f32" else 1.2e-2
     err = (got - ref).abs().max(dim=1).values / ref.abs().max()
     assert float(err.max()) <= tol, f"worst rows {torch.topk(err, min(5, len(err))).indices.tolist()} err {float(err.max()):.3e}"
+
+
+def _even_share_segments(seed, n, longest, extras):
+    rng = np.random.RandomState(seed)
+    segs = [(int(p), 1) for p in rng.randint(0, longest, size=n)]
+    return segs + extras
+
+
+EVEN_CASES = [
+    # H, K, hd, page, window, segments: more (request, kv head) pairs than two CTAs per SM, so the bulk-copy kernel cuts
+    # the tiles of all pairs into even shares: requests of 1 to 80 tiles (one CTA's share is about ten, so some lie
+    # inside one share, most are cut in two, the longest into many), entries of two and four tokens, and prompt
+    # portions in the same step (no tiles in this kernel)
+    (32, 8, 128, 64, 0, _even_share_segments(1, 34, 1400, [(5099, 1), (0, 1), (63, 1), (64, 1), (300, 2), (301, 4), (0, 40), (700, 9)])),
+    # one query head per kv head, small pages, a window: the first tile of a request is not tile 0
+    (8, 8, 64, 16, 500, _even_share_segments(2, 36, 3000, [(499, 1), (500, 1), (501, 1), (2999, 2)])),
+    # fewer tiles than CTAs (most requests are prompt portions): empty shares, shares of one tile
+    (16, 4, 128, 128, 0, [(int(p), 1) for p in range(0, 46)] + [(100, 1), (150, 1), (191, 1), (192, 1)] + [(10 * i, 5) for i in range(30)]),
+    # head size 64, pages of 8, sixteen packed rows in some entries
+    (16, 8, 64, 8, 0, _even_share_segments(4, 36, 900, [(0, 8), (100, 8), (2047, 1), (2048, 1)])),
+    # about one pair per SM, lengths from 1 to 6,000 keys: even shares are taken on the caller's word that the
+    # lengths are uneven; the longest request is cut into many pieces that its owner gathers
+    (32, 8, 128, 32, 0, [(5999, 1), (0, 1), (3000, 2)] + [(40 * i * i, 1) for i in range(1, 12)] + [(100 + i, 1) for i in range(6)]),
+]
+
+
+@pytest.mark.parametrize("case_id", range(len(EVEN_CASES)))
+def test_decode_attention_in_even_shares(case_id):
+    """Every request's last query (first head of each kv head) has ONE key, somewhere in its range, that carries most of
+    its weight: a share that dropped, doubled or misplaced a tile, or an owner that missed a piece, is off by most
+    of the row.  Errors are taken row by row against the row's own size."""
+    from xyntetik_runner_b200 import kernels
+    H, K, hd, page, window, segs = EVEN_CASES[case_id]
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    uneven = case_id == 4
+    assert len(segs) * K > 2 * sms or (uneven and 8 * len(segs) * K >= 5 * sms)      # what the case is for
+    rng = np.random.RandomState(100 + case_id)
+    spikes = []
+    for s, (p0, L) in enumerate(segs):
+        p = p0 + L - 1
+        first = max(0, p - window + 1) if window else 0
+        spikes.append((s, L - 1, int(rng.randint(first, p + 1)), 9.0))
+    case = _paged_case(200 + case_id, H, K, hd, page, segs, torch.bfloat16, window, spikes=spikes)
+    even0 = kernels.attention_even_launches()
+    got = _run_attention(case, "mma", H, K, hd, page, window, torch.bfloat16, tma=True, uneven=uneven)
+    assert kernels.attention_even_launches() == even0 + 1
+    ref = case["ref"]
+    err = (got - ref).abs().max(dim=1).values / ref.abs().max(dim=1).values
+    assert float(err.max()) <= 2e-2, f"worst rows {torch.topk(err, min(5, len(err))).indices.tolist()} err {float(err.max()):.3e}"
+    # the flags that pieces are handed over with are lowered again, and the same launch gives the same bits
+    assert int(kernels.workspace(torch.device(DEV)).flags.abs().sum()) == 0
+    again = _run_attention(case, "mma", H, K, hd, page, window, torch.bfloat16, tma=True, uneven=uneven)
+    assert torch.equal(got, again)
+    # without the bulk copies (spans and the merge kernel) the same rows, to rounding
+    other = _run_attention(case, "mma", H, K, hd, page, window, torch.bfloat16, tma=False)
+    err2 = (other - ref).abs().max(dim=1).values / ref.abs().max(dim=1).values
+    assert float(err2.max()) <= 2e-2
 
 
 @pytest.mark.parametrize("kind", ["simt", "mma", "mma_tma"])
@@ -450,31 +507,43 @@ def test_fused_finishes_match_the_separate_kernels(n, d):
 
 @pytest.mark.parametrize("adjacent,mscale", [(False, 1.0), (True, 1.0), (True, 0.83)])
 @pytest.mark.parametrize("H,K,hd,rot", [(6, 2, 48, 48), (6, 2, 32, 32), (3, 1, 64, 32), (2, 2, 128, 128), (5, 1, 16, 16), (2, 1, 24, 20)])
-def test_finish_rope_store_matches_rope_store(H, K, hd, rot, adjacent, mscale):
+@pytest.mark.parametrize("n", [5, 40])
+def test_finish_rope_store_matches_rope_store(H, K, hd, rot, adjacent, mscale, n):
+    """Five tokens: one block per (token, head).  Forty: the kernel with 16-byte loads where the sizes allow it (pairs
+    (j, j + half), widths that are multiples of four), the same block-per-head kernel elsewhere."""
     from xyntetik_runner_b200 import kernels
     g = torch.Generator().manual_seed(4)
-    page, n, kdim = 8, 5, 512
+    page, kdim = 8, 512
     qkv_dim = (H + 2 * K) * hd
     x_in = torch.randn(n, kdim, generator=g).to(torch.bfloat16).to(DEV)
     w = (torch.randn(qkv_dim, kdim, generator=g) / 20).to(torch.bfloat16).to(DEV)
     bias = torch.randn(qkv_dim, generator=g).to(DEV)
-    positions = torch.tensor([3, 4, 5, 17, 9], dtype=torch.int32, device=DEV)
-    tok_seg = torch.tensor([0, 0, 0, 1, 2], dtype=torch.int32, device=DEV)
-    bt = torch.tensor([[2, 5, -1], [0, 1, 4], [6, 3, -1]], dtype=torch.int32, device=DEV)
+    if n == 5:
+        positions = torch.tensor([3, 4, 5, 17, 9], dtype=torch.int32, device=DEV)
+        tok_seg = torch.tensor([0, 0, 0, 1, 2], dtype=torch.int32, device=DEV)
+        bt = torch.tensor([[2, 5, -1], [0, 1, 4], [6, 3, -1]], dtype=torch.int32, device=DEV)
+        max_pages, n_pages = 3, 7
+    else:
+        runs = [(3, 17), (17, 1), (0, 9), (30, 13)]                # (first position, tokens) of four requests
+        assert sum(l for _, l in runs) == n
+        positions = torch.tensor([p for p0, l in runs for p in range(p0, p0 + l)], dtype=torch.int32, device=DEV)
+        tok_seg = torch.tensor([s for s, (_, l) in enumerate(runs) for _ in range(l)], dtype=torch.int32, device=DEV)
+        max_pages, n_pages = 6, 4 * 6 + 2
+        bt = torch.randperm(n_pages, generator=g)[:4 * max_pages].reshape(4, max_pages).to(torch.int32).to(DEV)
     inv_freq = torch.rand(rot // 2, generator=g).to(DEV)
     outs = []
     for fused in (False, True):
-        cache = torch.zeros(7, 1, 2, K, page, hd, dtype=torch.bfloat16, device=DEV)
+        cache = torch.zeros(n_pages, 1, 2, K, page, hd, dtype=torch.bfloat16, device=DEV)
         qkv = torch.zeros(n, qkv_dim, dtype=torch.bfloat16, device=DEV)
         if fused:
             sums = kernels.gemm_tc_deferred(x_in, w, qkv, bias, kernels.EPI_STORE, force_splits=2)
             kernels.finish_rope_store(sums.partial, sums.splits, bias, qkv, positions, tok_seg, bt, inv_freq,
-                                      cache.data_ptr(), cache.stride(0), cache.stride(2), H, K, hd, rot, 3, page, adjacent, mscale)
+                                      cache.data_ptr(), cache.stride(0), cache.stride(2), H, K, hd, rot, max_pages, page, adjacent, mscale)
             sums.release()
         else:
             kernels.gemm_tc(x_in, w, qkv, bias, kernels.EPI_STORE, force_splits=1)
             kernels.rope_store(qkv, positions, tok_seg, bt, inv_freq, cache.data_ptr(), cache.stride(0), cache.stride(2),
-                               H, K, hd, rot, 3, page, adjacent, mscale)
+                               H, K, hd, rot, max_pages, page, adjacent, mscale)
         outs.append((qkv[:, :H * hd].float().cpu(), cache.float().cpu()))
     (q0, c0), (q1, c1) = outs
     assert float(c0.abs().sum()) > 0

@@ -206,3 +206,67 @@ def test_device_and_host_draw_the_same_weights():
     assert np.array_equal(out.cpu().numpy(), rf.normal_values(key, first, 5000, 0.0, 1.0))
     z = rf.normal_values(key, 0, 1 << 20, 0.0, 1.0)
     assert abs(float(z.mean())) < 5e-3 and abs(float(z.std()) - 1.0) < 5e-3 and abs(float((z ** 4).mean()) - 3.0) < 0.05
+
+
+MANY = {
+    "architectures": ["LlamaForCausalLM"], "hidden_size": 512, "num_hidden_layers": 2, "num_attention_heads": 16,
+    "num_key_value_heads": 8, "head_dim": 64, "intermediate_size": 1024, "vocab_size": 1000, "rms_norm_eps": 1e-5,
+    "rope_theta": 10000.0, "rope_scaling": None, "max_position_embeddings": 2048, "tie_word_embeddings": False,
+    "hidden_act": "silu", "torch_dtype": "bfloat16",
+}
+
+
+@pytest.mark.parametrize("n_requests", [48, 14])
+def test_many_requests_of_unequal_length_decode_together(n_requests):
+    """48 requests x 8 kv heads are more (request, kv head) pairs than CTAs of the decode attention fit on the machine,
+    and 14 requests of 5 to 1,300 tokens are few but uneven: both go through the kernel that cuts the tiles of all
+    requests into even shares.  Prompts of 5 to 1,300 tokens, then six tokens each decoded together (plainly, captured,
+    replayed), every decoded position against the plain implementation."""
+    from xyntetik_runner_b200 import kernels
+    from xyntetik_runner_b200.architectures.llama import build_llama
+    from xyntetik_runner_b200.config.llama import LlamaConfig
+    from xyntetik_runner_b200.engine.engine import EngineParams, random_engine
+    from xyntetik_runner_b200.engine.replay import replay
+    from xyntetik_runner_b200.weights.loader import RandomSource
+    cfg = LlamaConfig.from_dict(MANY)
+    seed, V, n_decoded = 11, cfg.vocab_size, 6
+    rng = np.random.RandomState(n_requests)
+    lengths = [5, 63, 64, 65, 1300] + [int(x) for x in rng.randint(20, 1100, size=n_requests - 5)]
+    reqs = {f"r{i}": traces.random_tokens(100 + i, n + n_decoded, V) for i, n in enumerate(lengths)}
+    steps, batch, room = [], [], 2048
+    for rid, toks in reqs.items():
+        n = len(toks) - n_decoded
+        if n > room:
+            steps.append({"step": len(steps), "entries": batch, "end": []})
+            batch, room = [], 2048
+        batch.append({"id": rid, "tokens": toks[:n], "want": []})
+        room -= n
+    steps.append({"step": len(steps), "entries": batch, "end": []})
+    for j in range(n_decoded):
+        steps.append({"step": len(steps), "entries": [{"id": rid, "tokens": [toks[len(toks) - n_decoded + j]], "want": [0]}
+                                                      for rid, toks in reqs.items()],
+                      "end": list(reqs) if j == n_decoded - 1 else []})
+    src = RandomSource(build_llama(cfg).tensor_specs(), seed, torch.bfloat16, std=0.05, norm_jitter=0.1, gen_device="cuda:0")
+    tensors = {n: src.fetch(n, torch.device("cuda:0")).float().cpu().numpy() for n in src.specs}
+    plain = PlainLlama(config=MANY, tensors=tensors)
+    eng = random_engine(cfg, seed, EngineParams(dtype="bfloat16", max_tokens=traces.pool_tokens(steps), page_size=64,
+                                                max_requests=n_requests, max_step_tokens=2048), std=0.05, norm_jitter=0.1)
+    even0 = kernels.attention_even_launches()
+    res = replay(eng, steps)
+    eng.cache.audit()
+    assert kernels.attention_even_launches() >= even0 + 2 * cfg.num_hidden_layers      # the plain decode step and the captured one
+    assert eng.graph_replays >= n_decoded - 2
+    assert int(kernels.workspace(torch.device("cuda:0")).flags.abs().sum()) == 0
+    tol = traces.TOL["bfloat16"]
+    first = len(steps) - n_decoded
+    for i, (rid, toks) in enumerate(reqs.items()):
+        rows = list(range(len(toks) - n_decoded, len(toks)))
+        want = plain.logits(toks, rows=rows)
+        for j, w in enumerate(want):
+            row = res[first + j][i]
+            scale = float(np.abs(w).max())
+            d = np.abs(row.astype(np.float64) - w)
+            assert np.isfinite(row).all() and d.max() <= tol["max_rel"] * scale and d.mean() <= tol["mean_rel"] * scale, \
+                f"request {rid} ({len(toks) - n_decoded} tokens), decoded token {j}: max {d.max() / scale:.2e} mean {d.mean() / scale:.2e}"
+    del eng
+    torch.cuda.empty_cache()

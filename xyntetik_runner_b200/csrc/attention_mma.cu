@@ -22,6 +22,9 @@
 //    whole tiles long; the launcher picks their length so that the CTAs fill the machine in whole
 //    waves (att_choose_span); `k_attention_merge` combines them in ascending order.
 // K and V rows are gathered page by page with 16-byte cp.async copies (any page size), double buffered.
+// With head sizes 64 and 128 and power-of-two pages the keys kernel fetches whole page blocks with bulk copies
+// (k_attention_keys_tma: spans, combined inside a cluster where all of them are resident at once;
+// k_attention_keys_even: the tiles of all requests cut into one equal run per resident CTA, for many or unequal requests).
 #include "common.cuh"
 #include <math.h>
 #include <cuda.h>
@@ -739,6 +742,330 @@ k_attention_keys_tma(const __grid_constant__ CUtensorMap cache_map, AttnMmaArgs 
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// keys kernel in even shares.  With more (request, kv head) pairs than CTAs fit on the machine, one CTA per pair (or
+// per span) runs in waves whose last is mostly idle, and requests of unequal length make it worse.  Here the grid is
+// the number of CTAs that are resident at once, and the tiles of all pairs, laid end to end (request, kv head, tile),
+// are cut into that many equal runs.  A CTA walks its run with one ring of bulk copies that runs on across the
+// pairs it touches.  A pair that lies inside one run is finished there.  A pair that is cut belongs to the CTA that
+// holds its first tiles, and that piece is the last of its CTA's run.  Every later piece is the first of its CTA's
+// run: that CTA leaves (accumulator, maximum, sum) in its own slot of the scratch and raises its flag; the owner,
+// at the very end of its run, takes the pieces in ascending order, lowers the flags again and writes the rows.
+// A CTA waits only for CTAs that were given the piece as their first work and wait for nobody before it, and all CTAs
+// are resident at once (the grid is sized by the occupancy the runtime reports), so the wait ends; it is bounded all
+// the same.  The result is a fixed function of the step's lengths: the same sums in the same order.
+// Flags are touched after griddepcontrol.wait only: the launch of the layer before has completed by then.
+// ---------------------------------------------------------------------------------------------
+#define ATT_EVEN_MAX_SEGS 512
+
+__device__ __forceinline__ int att_ld_acquire(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void att_st_release(int* p, int v) {
+    asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+template <int HD, int STAGES>
+__global__ void __launch_bounds__(ATT_THREADS, 3)
+k_attention_keys_even(const __grid_constant__ CUtensorMap cache_map, AttnMmaArgs a, int n_seg, int* flags) {
+    xr_pdl_launch();
+    constexpr int LD = HD + 8, QUADS = HD / 4, TILE_ELEMS = ATT_TILE * HD;
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if ((att_smem_u32(smem_raw) & 1023u) != 0) {                   // the copies' 128-byte swizzle counts from 1 KB boundaries
+        if (tid == 0) atomicExch(a.status, 2);
+        return;
+    }
+    const int R = a.recv_rows;                                     // most packed rows of any request of the step
+    __nv_bfloat16* kbuf = (__nv_bfloat16*)smem_raw;                // [STAGES][TILE_ELEMS]
+    __nv_bfloat16* vbuf = kbuf + STAGES * TILE_ELEMS;              // [STAGES][TILE_ELEMS]
+    uint8_t* rest = (uint8_t*)(vbuf + STAGES * TILE_ELEMS);
+    // the Q rows at the start of a piece and the four warps' sums at its end share one region
+    __nv_bfloat16* qs = (__nv_bfloat16*)rest;                      // [16][LD]
+    float* acc_s = (float*)rest;                                   // [4][R][HD]
+    const int shared_region = 16 * LD * 2 > 4 * R * HD * 4 ? 16 * LD * 2 : 4 * R * HD * 4;
+    float* ml_s = (float*)(rest + shared_region);                  // [4][16][2]
+    uint64_t* full = (uint64_t*)(ml_s + 4 * 16 * 2);
+    int* seg_pre = (int*)(full + STAGES);                          // [n_seg + 1]: tiles of the requests before this one
+    volatile int* gave_up = (volatile int*)(seg_pre + n_seg + 1);
+
+    // tiles of every request (the step's description does not change while the step runs)
+    for (int s = tid; s < n_seg; s += ATT_THREADS) {
+        const int L = a.seg_len[s], p0 = a.seg_pos0[s];
+        int cnt = 0;
+        if (L > 0 && L * a.G <= 16) {
+            const int lo = a.window > 0 ? max(0, p0 - a.window + 1) : 0;
+            cnt = (p0 + L - 1) / ATT_TILE - lo / ATT_TILE + 1;
+        }
+        seg_pre[s + 1] = cnt;
+    }
+    if (tid == 0) {
+        seg_pre[0] = 0;
+        for (int s = 0; s < STAGES; s++)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(att_smem_u32(&full[s])), "r"(1));
+        *gave_up = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 0) {
+        int run = 0;
+        for (int base = 0; base < n_seg; base += 32) {
+            const int s = base + lane;
+            int v = s < n_seg ? seg_pre[s + 1] : 0;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int u = __shfl_up_sync(0xffffffffu, v, o);
+                if (lane >= o) v += u;
+            }
+            if (s < n_seg) seg_pre[s + 1] = run + v;
+            run += __shfl_sync(0xffffffffu, v, 31);
+        }
+    }
+    __syncthreads();
+    const long long T = (long long)a.K * seg_pre[n_seg];
+    const long long C = gridDim.x, c = blockIdx.x;
+    const long long begin = T * c / C, end = T * (c + 1) / C;
+    if (begin >= end) return;
+    const int n_mine = (int)(end - begin);
+
+    // the pair and the tile at place f of the row of all tiles; t_first and cnt: the pair's first tile and its tiles
+    auto locate = [&](long long f, int& seg, int& kvh, int& t, int& t_first, int& cnt) {
+        int lo = 0, hi = n_seg;                                    // K * seg_pre[lo] <= f < K * seg_pre[hi]
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if ((long long)a.K * seg_pre[mid] <= f) lo = mid; else hi = mid;
+        }
+        seg = lo;
+        cnt = seg_pre[lo + 1] - seg_pre[lo];
+        const int rem = (int)(f - (long long)a.K * seg_pre[lo]);
+        kvh = rem / cnt;
+        const int p0 = a.seg_pos0[lo];
+        t_first = (a.window > 0 ? max(0, p0 - a.window + 1) : 0) / ATT_TILE;
+        t = t_first + rem % cnt;
+    };
+
+    // thread 0 keeps the place of the next tile to fetch; tile number i of the run goes to stage i % STAGES
+    const int box_rows = a.page_size < ATT_TILE ? a.page_size : ATT_TILE;
+    int fs = 0, fk = 0, ft = 0, ft_first = 0, fcnt = 1, fetched = 0;
+    if (tid == 0) locate(begin, fs, fk, ft, ft_first, fcnt);
+    auto fetch_next = [&]() {
+        const int s = fetched % STAGES;
+        const int* bt = a.block_tables + (size_t)fs * a.max_pages;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the stage was read, and perhaps partly cleared, by threads
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(att_smem_u32(&full[s])), "r"(2 * TILE_ELEMS * 2) : "memory");
+        for (int r0 = 0; r0 < ATT_TILE; r0 += box_rows) {
+            const int kp = ft * ATT_TILE + r0;
+            const int pi = kp >> a.page_shift;
+            const int page = pi < a.max_pages ? bt[pi] : -1;       // -1 (no page): the copy reads outside the tensor and fills zeros
+            const int tok = kp & (a.page_size - 1);
+            long long rowk = ((((long long)page * a.n_layers + a.layer) * 2 + 0) * a.K + fk) * a.page_size + tok;
+            long long rowv = rowk + (long long)a.K * a.page_size;
+            if (page < 0) { rowk = -(long long)ATT_TILE; rowv = -(long long)ATT_TILE; }
+#pragma unroll
+            for (int cc = 0; cc < HD / 64; cc++) {
+                __nv_bfloat16* kd = kbuf + s * TILE_ELEMS + cc * (ATT_TILE * 64) + r0 * 64;
+                __nv_bfloat16* vd = vbuf + s * TILE_ELEMS + cc * (ATT_TILE * 64) + r0 * 64;
+                asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                             ::"r"(att_smem_u32(kd)), "l"(&cache_map), "r"(cc * 64), "r"((int)rowk), "r"(att_smem_u32(&full[s])) : "memory");
+                asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                             ::"r"(att_smem_u32(vd)), "l"(&cache_map), "r"(cc * 64), "r"((int)rowv), "r"(att_smem_u32(&full[s])) : "memory");
+            }
+        }
+        fetched++;
+        if (++ft == ft_first + fcnt) {                             // on to the next pair
+            if (++fk == a.K) {
+                fk = 0;
+                do { fs++; } while (fs < n_seg && seg_pre[fs + 1] == seg_pre[fs]);
+                if (fs < n_seg) {
+                    const int p0 = a.seg_pos0[fs];
+                    fcnt = seg_pre[fs + 1] - seg_pre[fs];
+                    ft_first = (a.window > 0 ? max(0, p0 - a.window + 1) : 0) / ATT_TILE;
+                }
+            }
+            ft = ft_first;
+        }
+    };
+    // tiles that hold keys of earlier steps only may be asked for before the kernel ahead in the stream is complete
+    if (tid == 0)
+        while (fetched < STAGES && fetched < n_mine && (ft + 1) * ATT_TILE <= a.seg_pos0[fs]) fetch_next();
+    xr_pdl_wait();
+    if (tid == 0)
+        while (fetched < STAGES && fetched < n_mine) fetch_next();
+    const int ra = lane >> 2, rb = ra + 8, t2 = (lane & 3) * 2;
+    long long pos = begin;
+    int i0 = 0;                                                    // number in the run of the piece's first tile
+    while (pos < end) {
+        int seg, kvh, t_from, t_first, cnt;
+        locate(pos, seg, kvh, t_from, t_first, cnt);
+        const int L = a.seg_len[seg], rows_total = L * a.G, pos0 = a.seg_pos0[seg], tok_base = a.seg_start[seg];
+        const int hi = pos0 + L - 1, lo = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
+        const int t_last = t_first + cnt - 1;
+        const long long left = end - pos;
+        const int n_here = (long long)(t_last - t_from + 1) < left ? t_last - t_from + 1 : (int)left;
+        const int t_to = t_from + n_here - 1;
+        __syncthreads();                                           // the sums of the piece before have been read
+        load_q<HD>(qs, a, tok_base, kvh, 0, 16, rows_total);
+        __syncthreads();
+        uint32_t qf[HD / 16][4];
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; kk++)
+            ldsm_x4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], qs + (lane & 15) * LD + kk * 16 + ((lane >> 4) << 3));
+        __syncthreads();                                           // every warp has its Q rows in registers: the region is free for the sums
+        const int pos_a = ra < rows_total ? pos0 + ra / a.G : -1, pos_b = rb < rows_total ? pos0 + rb / a.G : -1;
+        float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+        float o[HD / 8][4];
+#pragma unroll
+        for (int d = 0; d < HD / 8; d++) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f; }
+
+        for (int t = t_from; t <= t_to; t++) {
+            const int i = i0 + (t - t_from), cur = i % STAGES;
+            if (!att_mbar_wait(&full[cur], (i / STAGES) & 1)) *gave_up = 1;
+            __nv_bfloat16* vt = vbuf + cur * TILE_ELEMS;
+            if ((t + 1) * ATT_TILE - 1 > hi) {
+                // the tile runs past the last key: clear those value rows (0 x garbage must stay 0)
+                const int first_bad = hi + 1 - t * ATT_TILE;
+                for (int e = tid; e < (ATT_TILE - first_bad) * (HD / 8); e += ATT_THREADS) {
+                    const int r = first_bad + e / (HD / 8), cc = (e % (HD / 8)) * 8;
+                    *reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(tile_ptr<HD, true>(vt, r, cc))) = make_uint4(0, 0, 0, 0);
+                }
+                __syncthreads();
+            }
+            if (t * ATT_TILE < lo) {
+                const int n_bad = lo - t * ATT_TILE;
+                for (int e = tid; e < n_bad * (HD / 8); e += ATT_THREADS) {
+                    const int r = e / (HD / 8), cc = (e % (HD / 8)) * 8;
+                    *reinterpret_cast<uint4*>(const_cast<__nv_bfloat16*>(tile_ptr<HD, true>(vt, r, cc))) = make_uint4(0, 0, 0, 0);
+                }
+                __syncthreads();
+            }
+            const int c0 = warp * 16, kfirst = t * ATT_TILE + c0;
+            if (kfirst <= hi && kfirst + 15 >= lo) {
+                if (rows_total <= 8)
+                    tile_step<HD, 2, true, true>(qf, kbuf + cur * TILE_ELEMS, vt, c0, t * ATT_TILE, pos_a, pos_b, a.window, a.scale, m, l, o);
+                else
+                    tile_step<HD, 2, false, true>(qf, kbuf + cur * TILE_ELEMS, vt, c0, t * ATT_TILE, pos_a, pos_b, a.window, a.scale, m, l, o);
+            }
+            __syncthreads();                                       // everyone is done with stage `cur`:
+            if (tid == 0 && fetched < n_mine) fetch_next();        // tile i + STAGES goes into it at once, so the ring stays full
+        }
+        // the four warps' sums side by side
+#pragma unroll
+        for (int d = 0; d < HD / 8; d++) {
+            if (ra < rows_total) { acc_s[(warp * R + ra) * HD + d * 8 + t2] = o[d][0]; acc_s[(warp * R + ra) * HD + d * 8 + t2 + 1] = o[d][1]; }
+            if (rb < rows_total) { acc_s[(warp * R + rb) * HD + d * 8 + t2] = o[d][2]; acc_s[(warp * R + rb) * HD + d * 8 + t2 + 1] = o[d][3]; }
+        }
+        if ((lane & 3) == 0) {
+            ml_s[(warp * 16 + ra) * 2] = m[0]; ml_s[(warp * 16 + ra) * 2 + 1] = l[0];
+            ml_s[(warp * 16 + rb) * 2] = m[1]; ml_s[(warp * 16 + rb) * 2 + 1] = l[1];
+        }
+        __syncthreads();
+        // this thread's quadruples of the piece's rows: q = tid + ATT_THREADS j is row q / QUADS, columns 4 (q % QUADS) ..
+        const int owned = rows_total * QUADS;
+        float4 acc[4];
+        float mm[4], ll[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int q = tid + j * ATT_THREADS;
+            acc[j] = make_float4(0.f, 0.f, 0.f, 0.f); mm[j] = -INFINITY; ll[j] = 0.f;
+            if (q < owned) {
+                const int r = q / QUADS, d = (q % QUADS) * 4;
+#pragma unroll
+                for (int w = 0; w < 4; w++) mm[j] = fmaxf(mm[j], ml_s[(w * 16 + r) * 2]);
+                const float off = mm[j] == -INFINITY ? 0.f : mm[j];
+#pragma unroll
+                for (int w = 0; w < 4; w++) {
+                    const float f = expf(ml_s[(w * 16 + r) * 2] - off);
+                    const float4 v = *reinterpret_cast<const float4*>(acc_s + (w * R + r) * HD + d);
+                    acc[j].x += v.x * f; acc[j].y += v.y * f; acc[j].z += v.z * f; acc[j].w += v.w * f;
+                    ll[j] += ml_s[(w * 16 + r) * 2 + 1] * f;
+                }
+            }
+        }
+        if (t_from != t_first) {
+            // a later piece of a pair that began in a CTA before this one: leave it in this CTA's slot
+            float* pacc = a.part_acc + (size_t)c * 16 * HD;
+            float* pml = a.part_ml + (size_t)c * 32;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int q = tid + j * ATT_THREADS;
+                if (q < owned) {
+                    const int r = q / QUADS, d = (q % QUADS) * 4;
+                    *reinterpret_cast<float4*>(pacc + r * HD + d) = acc[j];
+                    if (d == 0) *reinterpret_cast<float2*>(pml + r * 2) = make_float2(mm[j], ll[j]);
+                }
+            }
+            __syncthreads();
+            if (tid == 0) { __threadfence(); att_st_release(flags + c, 1); }
+        } else {
+            if (t_to != t_last) {
+                // the first piece of a pair that goes on in the CTAs after this one: theirs, in ascending order
+                const long long pair_end = pos + cnt;
+                // the CTAs after this one whose runs begin inside the pair (with fewer tiles than CTAs some of them are empty)
+                int nf = 0;
+                for (long long c2 = c + 1; c2 < C && T * c2 / C < pair_end; c2++) nf++;
+                // their flags, each by a thread of its own; a CTA without tiles has nothing to say
+                for (int k = tid; k < nf; k += ATT_THREADS) {
+                    const long long c2 = c + 1 + k;
+                    if (T * c2 / C == T * (c2 + 1) / C) continue;
+                    bool there = false;
+                    for (uint32_t spin = 0; spin < ATT_SPIN_LIMIT && !there; spin++) there = att_ld_acquire(flags + c2) != 0;
+                    if (there) *(volatile int*)(flags + c2) = 0; else *gave_up = 1;
+                }
+                __syncthreads();
+                if (!*gave_up) {
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        const int q = tid + j * ATT_THREADS;
+                        if (q >= owned) continue;
+                        const int r = q / QUADS, d = (q % QUADS) * 4;
+                        // the piece after the one being added is on its way meanwhile
+                        float2 ml_next = make_float2(-INFINITY, 0.f);
+                        float4 v_next = make_float4(0.f, 0.f, 0.f, 0.f);
+                        auto ask = [&](int k) {
+                            const long long c2 = c + 1 + k;
+                            if (T * c2 / C == T * (c2 + 1) / C) { ml_next = make_float2(-INFINITY, 0.f); v_next = make_float4(0.f, 0.f, 0.f, 0.f); return; }
+                            ml_next = __ldcg(reinterpret_cast<const float2*>(a.part_ml + (size_t)c2 * 32 + r * 2));
+                            v_next = __ldcg(reinterpret_cast<const float4*>(a.part_acc + (size_t)c2 * 16 * HD + r * HD + d));
+                        };
+                        ask(0);
+                        for (int k = 0; k < nf; k++) {
+                            const float2 ml2 = ml_next;
+                            const float4 v = v_next;
+                            if (k + 1 < nf) ask(k + 1);
+                            const float top = fmaxf(mm[j], ml2.x), off = top == -INFINITY ? 0.f : top;
+                            const float f1 = expf(mm[j] - off), f2 = expf(ml2.x - off);
+                            acc[j].x = acc[j].x * f1 + v.x * f2; acc[j].y = acc[j].y * f1 + v.y * f2;
+                            acc[j].z = acc[j].z * f1 + v.z * f2; acc[j].w = acc[j].w * f1 + v.w * f2;
+                            ll[j] = ll[j] * f1 + ml2.y * f2;
+                            mm[j] = top;
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int q = tid + j * ATT_THREADS;
+                if (q < owned) {
+                    const int r = q / QUADS, d = (q % QUADS) * 4;
+                    const float inv = 1.0f / ll[j];
+                    __nv_bfloat16* dst = a.out + ((long long)(tok_base + r / a.G) * a.H + (kvh * a.G + r % a.G)) * HD + d;
+                    __nv_bfloat162 lo2 = __floats2bfloat162_rn(acc[j].x * inv, acc[j].y * inv), hi2 = __floats2bfloat162_rn(acc[j].z * inv, acc[j].w * inv);
+                    uint2 packed;
+                    packed.x = *reinterpret_cast<uint32_t*>(&lo2);
+                    packed.y = *reinterpret_cast<uint32_t*>(&hi2);
+                    *reinterpret_cast<uint2*>(dst) = packed;
+                }
+            }
+        }
+        pos += n_here;
+        i0 += n_here;
+    }
+    __syncthreads();
+    if (tid == 0 && *gave_up) atomicExch(a.status, 2);
+}
+
 // Combine the spans of one (request, kv head) and write the output rows.  grid (K, segments), MERGE_THREADS
 // threads.  Each row's span weights exp(m_s - M) go to shared memory first.  A thread then owns four
 // neighbouring output elements and every `groups`-th span (groups = threads / owned quadruples, so that all
@@ -942,6 +1269,18 @@ static AttEncodeFn att_encode() {
     return fn;
 }
 
+// Even shares are taken when there are more (request, kv head) pairs than CTAs with deep rings fit on the machine.
+// Requests of much the same length are better served by spans while one CTA per span is resident at once (measured at
+// up to 36 requests of 8 kv heads: 2 to 5 us less than even shares, whose pieces meet through global memory); requests
+// of unequal length leave most spans short, and even shares win from about two pairs per three SMs on (32 requests of
+// 512 to 4,096 keys: 52.8 against 63.4 us; 12 of 1,024 to 8,192: 46.8 against 59.5 us; with 8 such requests a long one is
+// cut into so many pieces that gathering them costs more than the balance gains, 38.5 against 33.1 us).
+static bool att_even_wanted(long long items, bool uneven) {
+    return items > 2LL * xr_sm_count() || (uneven && 8 * items >= 5LL * xr_sm_count());
+}
+static long long g_even_launches = 0;
+// Launches of the even-shares kernel so far (captures count once): lets a test see which kernel a step took.
+XR_EXPORT int xr_attention_even_launches() { return (int)(g_even_launches & 0x7fffffff); }
 static bool att_cluster_merge_enabled() {
     static int on = -1;
     if (on < 0) { const char* e = getenv("XRB200_NO_CLUSTER_MERGE"); on = (e && e[0] == '1') ? 0 : 1; }
@@ -951,7 +1290,8 @@ static bool att_cluster_merge_enabled() {
 // The bulk-copy keys kernel, when the shapes allow it.  Returns 1 if launched (2: and the spans are combined
 // already), 0 if not applicable, < 0 on error.
 template <int HD>
-static int launch_keys_tma(const AttnMmaArgs& a, const void* cache_base, long long n_pages, int n_seg, cudaStream_t stream) {
+static int launch_keys_tma(const AttnMmaArgs& a, const void* cache_base, long long n_pages, int n_seg, cudaStream_t stream,
+                           int* flags, int n_flags, long long room, bool uneven) {
   if constexpr (HD != 64 && HD != 128) {
     return 0;
   } else {
@@ -983,6 +1323,49 @@ static int launch_keys_tma(const AttnMmaArgs& a, const void* cache_base, long lo
             cudaFuncSetAttribute(k_attention_keys_tma<HD, 4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, S4 + RECV) != cudaSuccess)
             return XR_ERR_LAUNCH;
         configured = true;
+    }
+    if (att_even_wanted((long long)n_seg * a.K, uneven) && flags != nullptr && n_seg <= ATT_EVEN_MAX_SEGS && att_cluster_merge_enabled()) {
+        // even shares: as many CTAs as are resident at once
+        static bool even_configured = false;
+        constexpr int EVEN_MAX = 2 * 4 * ATT_TILE * HD * 2 + 16 * LD * 2 + 4 * 16 * HD * 4 + 512 + 64 + 4 * (ATT_EVEN_MAX_SEGS + 4);
+        if (!even_configured) {
+            if (cudaFuncSetAttribute(k_attention_keys_even<HD, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, EVEN_MAX) != cudaSuccess ||
+                cudaFuncSetAttribute(k_attention_keys_even<HD, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, EVEN_MAX) != cudaSuccess ||
+                cudaFuncSetAttribute(k_attention_keys_even<HD, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, EVEN_MAX) != cudaSuccess)
+                return XR_ERR_LAUNCH;
+            even_configured = true;
+        }
+        const int region = 16 * LD * 2 > 4 * a.recv_rows * HD * 4 ? 16 * LD * 2 : 4 * a.recv_rows * HD * 4;
+        const int tail = (region + 512 + 8 * 4 + 4 * (n_seg + 2) + 15) & ~15;
+        // the deepest ring with which three CTAs share an SM (measured: three with two stages stream faster than two with
+        // three: 128 requests at 704 keys 62.5 against 66.6 us, 48 at 1,500 keys 50.3 against 53.9 us), else two, else one
+        auto resident_with = [&](int depth, int bytes) {
+            static int known_key[32], known_val[32], known_n = 0;  // asked once per (ring depth, shared memory): the answer does not change
+            const int key = bytes * 8 + depth;
+            for (int i = 0; i < known_n; i++)
+                if (known_key[i] == key) return known_val[i];
+            int r = 0;
+            cudaError_t e = depth == 4 ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&r, k_attention_keys_even<HD, 4>, ATT_THREADS, bytes)
+                          : depth == 3 ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&r, k_attention_keys_even<HD, 3>, ATT_THREADS, bytes)
+                                       : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&r, k_attention_keys_even<HD, 2>, ATT_THREADS, bytes);
+            if (e != cudaSuccess) { cudaGetLastError(); return 0; }
+            if (known_n < 32) { known_key[known_n] = key; known_val[known_n] = r; known_n++; }
+            return r;
+        };
+        int depth = 2, bytes = 2 * STAGE + tail, resident = 0;
+        for (int want = 3; want >= 1 && resident == 0; want--)
+            for (int d = 4; d >= 2; d--) {
+                const int r = resident_with(d, d * STAGE + tail);
+                if (r >= want) { depth = d; bytes = d * STAGE + tail; resident = want; break; }
+            }
+        const long long ctas = (long long)resident * xr_sm_count();
+        if (resident >= 1 && ctas <= n_flags && ctas <= room) {
+            if (depth == 4) xr_launch((k_attention_keys_even<HD, 4>), dim3((unsigned)ctas), dim3(ATT_THREADS), bytes, stream, map, a, n_seg, flags);
+            else if (depth == 3) xr_launch((k_attention_keys_even<HD, 3>), dim3((unsigned)ctas), dim3(ATT_THREADS), bytes, stream, map, a, n_seg, flags);
+            else xr_launch((k_attention_keys_even<HD, 2>), dim3((unsigned)ctas), dim3(ATT_THREADS), bytes, stream, map, a, n_seg, flags);
+            g_even_launches++;
+            return xr_launch_status() == XR_OK ? 2 : XR_ERR_LAUNCH;
+        }
     }
     // the fewer CTAs there are, the deeper each one's ring of tiles, so that as many bytes stay in flight per SM
     dim3 grid(a.max_splits, a.K, n_seg);
@@ -1027,7 +1410,7 @@ static int launch_keys_tma(const AttnMmaArgs& a, const void* cache_base, long lo
 
 template <int HD>
 static int launch_attention(const AttnMmaArgs& a, int n_seg, int max_seg_len, int max_kv_len, int any_short, int any_long,
-                            const void* cache_base, long long n_pages, cudaStream_t stream) {
+                            const void* cache_base, long long n_pages, cudaStream_t stream, int* flags, int n_flags, long long room, bool uneven) {
     constexpr int LD = HD + 8;
     constexpr int SMEM_ROWS = (ATT_ROWS + 4 * ATT_TILE) * LD * 2;
     constexpr int KEYS_MERGE = 16 * LD * 2 + (4 * 16 * HD + 4 * 16 * 2) * 4;
@@ -1051,7 +1434,7 @@ static int launch_attention(const AttnMmaArgs& a, int n_seg, int max_seg_len, in
     }
     if (any_short) {
         if (n_seg > 65535 || a.K > 65535) return XR_ERR_ARG;
-        int tma = launch_keys_tma<HD>(a, cache_base, n_pages, n_seg, stream);
+        int tma = launch_keys_tma<HD>(a, cache_base, n_pages, n_seg, stream, flags, n_flags, room, uneven);
         if (tma < 0) return tma;
         // few CTAs (small batch): deeper stages; many: more CTAs per SM.  The arithmetic is the same.
         if (tma == 2) return XR_OK;                    // the spans were combined inside the clusters
@@ -1069,42 +1452,56 @@ static int launch_attention(const AttnMmaArgs& a, int n_seg, int max_seg_len, in
     return XR_OK;
 }
 
-// Spans the keys kernel needs for a longest key range of `max_kv_len` (window > 0: at most that many keys).
+// Slots of scratch per (request, kv head) pair that a step needs: the spans the keys kernel cuts a longest key range of
+// `max_kv_len` into (window > 0: at most that many keys), or, where even shares are taken, one slot per CTA.
 // `items`: (request, kv head) pairs of the step, n_seg * K.
-XR_EXPORT int xr_attention_mma_splits(int max_kv_len, int window, long long items) {
+static int att_spans(int max_kv_len, int window, long long items) {
     int range = att_range(max_kv_len, window);
     int span = att_choose_span(range, items);
     return (range + span - 1) / span + (window > 0 ? 1 : 0);
 }
+XR_EXPORT int xr_attention_mma_splits(int max_kv_len, int window, long long items) {
+    int need = att_spans(max_kv_len, window, items);
+    if (items >= 1 && att_even_wanted(items, true)) {
+        long long per = (3LL * xr_sm_count() + items - 1) / items;
+        if (per > need) need = (int)per;
+    }
+    return need;
+}
 
 // part_acc: float32 [n_seg * K * splits * 16 * hd], part_ml: float32 [n_seg * K * splits * 32]
-// (only read and written when any_short).  splits must be xr_attention_mma_splits(max_kv_len, window, n_seg * K).
+// (only read and written when any_short).  splits: at least xr_attention_mma_splits(max_kv_len, window, n_seg * K).
+// flags: n_flags zeroed words that only this kernel touches (it leaves them zero), or null.
+// uneven: the requests' key ranges differ much in length (a hint for the choice between spans and even shares).
 XR_EXPORT int xr_attention_mma(const void* q, void* out, const void* cache_k, const int* seg_start, const int* seg_len,
                                const int* seg_pos0, const int* block_tables, float* part_acc, float* part_ml,
                                long long q_stride, long long page_stride, long long v_offset, int n_seg, int H, int K,
                                int hd, int max_pages, int page_size, int window, float scale, int max_seg_len,
                                int max_kv_len, int splits, int any_short, int any_long, const void* cache_base,
-                               long long n_pages, int n_layers, int layer, int* status, cudaStream_t stream) {
+                               long long n_pages, int n_layers, int layer, int* status, int* flags, int n_flags,
+                               int uneven, cudaStream_t stream) {
     if (n_seg < 1 || H < 1 || K < 1 || H % K != 0 || hd < 16 || hd > 128 || hd % 16 != 0 || page_size < 1 || window < 0 ||
         (q_stride % 8) != 0 || ((uintptr_t)q & 15) || ((uintptr_t)cache_k & 15) || (page_stride % 8) != 0 || (v_offset % 8) != 0)
         return XR_ERR_ARG;
     if (H / K > 16 && any_short) return XR_ERR_ARG;     // more heads per group than one instruction tile holds
+    const int spans = att_spans(max_kv_len, window, (long long)n_seg * K);
+    if (any_short && splits < spans) return XR_ERR_ARG;
     AttnMmaArgs a{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)cache_k, seg_start, seg_len, seg_pos0,
                   block_tables, part_acc, part_ml, q_stride, page_stride, v_offset, H, K, H / K, max_pages, page_size, window,
-                  splits, 0, scale, -1, n_layers, layer, status, 16};
+                  spans, 0, scale, -1, n_layers, layer, status, 16};
     { long long rows = (long long)(max_seg_len < 1 ? 1 : max_seg_len) * a.G; a.recv_rows = rows < 16 ? (int)rows : 16; }
     a.span = att_choose_span(att_range(max_kv_len, window), (long long)n_seg * K);
-    if (any_short && splits != (att_range(max_kv_len, window) + a.span - 1) / a.span + (window > 0 ? 1 : 0)) return XR_ERR_ARG;
+    const long long room = (long long)splits * n_seg * K;
     if ((page_size & (page_size - 1)) == 0) { int sh = 0; while ((1 << sh) < page_size) sh++; a.page_shift = sh; }
     switch (hd) {
-        case 16: return launch_attention<16>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream);
-        case 32: return launch_attention<32>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream);
-        case 48: return launch_attention<48>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream);
-        case 64: return launch_attention<64>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream);
-        case 80: return launch_attention<80>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream);
-        case 96: return launch_attention<96>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream);
-        case 112: return launch_attention<112>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream);
-        case 128: return launch_attention<128>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream);
+        case 16: return launch_attention<16>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream, flags, n_flags, room, uneven != 0);
+        case 32: return launch_attention<32>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream, flags, n_flags, room, uneven != 0);
+        case 48: return launch_attention<48>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream, flags, n_flags, room, uneven != 0);
+        case 64: return launch_attention<64>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream, flags, n_flags, room, uneven != 0);
+        case 80: return launch_attention<80>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream, flags, n_flags, room, uneven != 0);
+        case 96: return launch_attention<96>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream, flags, n_flags, room, uneven != 0);
+        case 112: return launch_attention<112>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream, flags, n_flags, room, uneven != 0);
+        case 128: return launch_attention<128>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream, flags, n_flags, room, uneven != 0);
     }
     return XR_ERR_ARG;
 }

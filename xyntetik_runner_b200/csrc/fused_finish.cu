@@ -485,6 +485,85 @@ __global__ void k_finish_rope_store(FinishRopeArgs a) {
     }
 }
 
+// The same for steps of more than 16 tokens, where one block per (token, head) means thousands of small blocks that keep
+// the kernel after this one off the machine.  A thread takes four neighbouring pairs (j .. j + 3 with j + half ..) or
+// four neighbouring elements that are not rotated, with the 16-byte loads of up to eight splits in flight together; a
+// block takes 256 such units of one token.  Pairs (j, j + half) only; sums, roundings and products as above, in the same order.
+__global__ void __launch_bounds__(256) k_finish_rope_store_vec4(FinishRopeArgs a) {
+    xr_pdl_launch();
+    const int t = blockIdx.x;
+    const int half = a.rotary_dim >> 1, pair_units = half >> 2;
+    const int uq = (a.hd - half) >> 2, uv = a.hd >> 2;             // units of a rotated head and of a value head
+    const int rot_heads = a.H + a.K;
+    const int g = blockIdx.y * 256 + threadIdx.x;
+    if (g >= rot_heads * uq + a.K * uv) return;
+    int head, u;
+    const bool rotated = g < rot_heads * uq;
+    if (rotated) { head = g / uq; u = g - head * uq; }
+    else { const int r = g - rot_heads * uq; head = rot_heads + r / uv; u = r % uv; }
+    const bool pair = rotated && u < pair_units;
+    const int i0 = pair ? 4 * u : (rotated ? 2 * half + 4 * (u - pair_units) : 4 * u);
+    const int i1 = i0 + half;
+    const int qkv_dim = (a.H + 2 * a.K) * a.hd, col0 = head * a.hd;
+    const int pos = a.positions[t];
+    __nv_bfloat16* dst = a.qkv + (size_t)t * qkv_dim + col0;
+    if (head >= a.H && a.cache_k != nullptr) {
+        const bool is_k = head < rot_heads;
+        const int kvh = is_k ? head - a.H : head - rot_heads;
+        const int page = a.block_tables[(size_t)a.tok_seg[t] * a.max_pages + pos / a.page_size];
+        dst = a.cache_k + (size_t)page * a.page_stride + (is_k ? 0 : a.v_offset) + ((size_t)kvh * a.page_size + (pos % a.page_size)) * a.hd;
+    }
+    float c[4] = {1.f, 1.f, 1.f, 1.f}, sn[4] = {0.f, 0.f, 0.f, 0.f};
+    if (pair) {
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const float ang = (float)pos * a.inv_freq[i0 + e];
+            c[e] = cosf(ang) * a.mscale; sn[e] = sinf(ang) * a.mscale;
+        }
+    }
+    xr_pdl_wait();
+    float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f), v1 = v0;
+    const size_t split_stride = (size_t)a.n * qkv_dim;
+    const float* p0 = a.partial + (size_t)t * qkv_dim + col0;
+    for (int s0 = 0; s0 < a.splits; s0 += 8) {
+        float4 x0[8], x1[8];
+#pragma unroll
+        for (int q = 0; q < 8; q++) {
+            const float* p = p0 + (size_t)min(s0 + q, a.splits - 1) * split_stride;
+            x0[q] = xr_ld_now4(reinterpret_cast<const float4*>(p + i0));
+            x1[q] = xr_ld_now4(reinterpret_cast<const float4*>(p + (pair ? i1 : i0)));
+        }
+#pragma unroll
+        for (int q = 0; q < 8; q++) { xr_ld_fence(x0[q]); xr_ld_fence(x1[q]); }
+#pragma unroll
+        for (int q = 0; q < 8; q++) {
+            if (s0 + q < a.splits) {
+                v0.x += x0[q].x; v0.y += x0[q].y; v0.z += x0[q].z; v0.w += x0[q].w;
+                if (pair) { v1.x += x1[q].x; v1.y += x1[q].y; v1.z += x1[q].z; v1.w += x1[q].w; }
+            }
+        }
+    }
+    float a0[4] = {v0.x, v0.y, v0.z, v0.w}, a1[4] = {v1.x, v1.y, v1.z, v1.w};
+    if (a.bias) {
+#pragma unroll
+        for (int e = 0; e < 4; e++) { a0[e] += a.bias[col0 + i0 + e]; if (pair) a1[e] += a.bias[col0 + i1 + e]; }
+    }
+    __nv_bfloat16 o0[4], o1[4];
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        if (pair) {
+            // the product's output is rounded to the activation dtype before the rotation, as on the unfused path
+            const float r0 = __bfloat162float(__float2bfloat16_rn(a0[e])), r1 = __bfloat162float(__float2bfloat16_rn(a1[e]));
+            o0[e] = __float2bfloat16_rn(r0 * c[e] - r1 * sn[e]);
+            o1[e] = __float2bfloat16_rn(r0 * sn[e] + r1 * c[e]);
+        } else {
+            o0[e] = __float2bfloat16_rn(a0[e]);
+        }
+    }
+    *reinterpret_cast<uint2*>(dst + i0) = *reinterpret_cast<const uint2*>(o0);
+    if (pair) *reinterpret_cast<uint2*>(dst + i1) = *reinterpret_cast<const uint2*>(o1);
+}
+
 XR_EXPORT int xr_finish_rope_store(const float* partial, int splits, const float* bias, void* qkv, const int* positions,
                                    const int* tok_seg, const int* block_tables, const float* inv_freq, void* cache_k,
                                    long long page_stride, long long v_offset, int n, int H, int K, int hd, int rotary_dim,
@@ -495,6 +574,13 @@ XR_EXPORT int xr_finish_rope_store(const float* partial, int splits, const float
     FinishRopeArgs a{partial, splits, bias, (__nv_bfloat16*)qkv, positions, tok_seg, block_tables, inv_freq,
                      (__nv_bfloat16*)cache_k, page_stride, v_offset, n, H, K, hd, rotary_dim, max_pages, page_size,
                      adjacent_pairs ? 1 : 0, mscale};
+    const int half = rotary_dim >> 1;
+    if (n > 16 && !adjacent_pairs && hd % 4 == 0 && half % 4 == 0 && ((uintptr_t)partial & 15) == 0 && ((uintptr_t)qkv & 7) == 0 &&
+        ((uintptr_t)cache_k & 7) == 0 && page_stride % 4 == 0 && v_offset % 4 == 0) {
+        const int units = (H + K) * ((hd - half) >> 2) + K * (hd >> 2);
+        xr_launch(k_finish_rope_store_vec4, dim3(n, (units + 255) / 256), dim3(256), 0, stream, a);
+        return xr_launch_status();
+    }
     int threads = hd >= 128 ? 128 : (hd >= 64 ? 64 : 32);
     xr_launch(k_finish_rope_store, dim3(n, H + 2 * K), dim3(threads), 0, stream, a);
     return xr_launch_status();

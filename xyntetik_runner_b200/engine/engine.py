@@ -72,6 +72,7 @@ class StepContext:
         self.max_kv_len = 0            # longest key range any token of the step reads
         self._pending = {}
         self.decode_only = False       # every segment is a single token
+        self.uneven = False            # the requests' lengths differ much (a hint for kernels that split work by request)
 
     def buf(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
         return self._eng._buf(name, shape, dtype)
@@ -162,6 +163,7 @@ class Engine:
         # CUDA graphs of decode-only steps, keyed by (tokens, wanted rows, context bucket).  A graph holds the
         # addresses of the step's buffers, so any buffer that is made anew invalidates all graphs.
         self._graphs: Dict[tuple, object] = {}
+        self._uneven_of_shape: Dict[tuple, bool] = {}      # decode-only steps: the unevenness hint a shape was first seen with
         self._graph_ok = p.cuda_graphs and all(part.graph_safe for part in plan.parts())
         # Decode-only steps of more than 8 requests are filled up to a multiple of 8 with rows of a request that does
         # not exist (one token at position 0, keys and values in the spare page, logits dropped), so that a few graphs
@@ -192,6 +194,7 @@ class Engine:
             self._bufs[key] = t
             self._buf_generation += 1
             self._graphs.clear()
+            self._uneven_of_shape.clear()
         return t[:n].view(*shape)
 
     # ---- requests ----------------------------------------------------------------
@@ -346,6 +349,13 @@ class Engine:
         if decode_only:
             max_kv = -(-max_kv // 1024) * 1024      # a bucket, so that launch shapes repeat from step to step
         ctx.max_kv_len, ctx.decode_only = max_kv, decode_only
+        # equal spans of the longest request would be more than a quarter empty
+        ends = s_pos0[:S_real].astype(np.int64) + s_len[:S_real]
+        ctx.uneven = S_real > 1 and int(ends.max()) * S_real > 1.25 * int(ends.sum())
+        if decode_only:
+            # a step graph holds the kernels that were chosen when it was captured: the answer at the first step of a
+            # shape stands for all later steps of that shape, so that a shape has one graph
+            ctx.uneven = self._uneven_of_shape.setdefault((n, R, max_kv), ctx.uneven)
         return ctx
 
     def _forward_graphed(self, ctx: StepContext) -> torch.Tensor:

@@ -59,8 +59,9 @@ def _declare(L: ctypes.CDLL) -> None:
         "xr_finish_plain": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _ll, _vp],
         "xr_finish_rope_store": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
         "xr_attention_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _f,
-                             _i, _i, _i, _i, _i, _vp, _ll, _i, _i, _vp, _vp],
+                             _i, _i, _i, _i, _i, _vp, _ll, _i, _i, _vp, _vp, _i, _i, _vp],
         "xr_attention_mma_splits": [_i, _i, _ll],
+        "xr_attention_even_launches": [],
         "xr_attention_tc_supported": [_i, _i, _i, _i],
         "xr_attention_tc": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _ll, _i, _i, _vp],
         "xr_sample": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
@@ -247,6 +248,7 @@ def random_normal(out: torch.Tensor, key: int, mean: float, std: float, first: i
 EPI_STORE, EPI_ADD, EPI_GATED = 0, 1, 2
 EPI_SWIGLU = EPI_GATED          # the gated epilogue with the SiLU activation
 _TC_SCRATCH_FLOATS = 32 << 20
+_HANDOVER_FLAGS = 2048          # one word per CTA of the decode attention in even shares
 _tc_state = {}
 
 
@@ -264,6 +266,7 @@ class Workspace:
     def __init__(self, device: torch.device):
         self.scratch = torch.empty(_TC_SCRATCH_FLOATS, dtype=torch.float32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.flags = torch.zeros(_HANDOVER_FLAGS, dtype=torch.int32, device=device)   # raised and lowered inside one launch
         self.top = 0            # floats taken from the start of the scratch
         self.live = 0           # slabs outstanding
 
@@ -317,6 +320,7 @@ def tc_check_status(device: torch.device) -> None:
         code = int(ws.status.item())
         if code != 0:
             ws.status.zero_()
+            ws.flags.zero_()                  # a launch that gave up may have left some raised
             what = {1: "a tcgen05 product", 2: "the bulk-copy decode attention", 3: "the tcgen05 attention", 4: "the tcgen05 attention (shared memory not 1 KB aligned)"}.get(code, "a kernel")
             raise KernelError(f"{what} gave up waiting on a barrier; its output is not valid")
 
@@ -469,31 +473,41 @@ def attention_mma_supported(dtype: torch.dtype, H: int, K: int, hd: int) -> bool
 
 
 def attention_mma_splits(max_kv_len: int, window: int, items: int) -> int:
-    """Spans per request of the key-split kernel for a step with `items` = segments x kv heads."""
+    """Slots of scratch per (segment, kv head) pair that the key-split kernel needs for a step with `items` such
+    pairs: its spans per request, or its CTAs over the pairs where it cuts the step's tiles into even shares."""
     return int(lib().xr_attention_mma_splits(max_kv_len, window, items))
+
+
+def attention_even_launches() -> int:
+    """How often the decode attention was launched in even shares (rather than in spans) so far."""
+    return int(lib().xr_attention_even_launches())
 
 
 def attention_mma(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, cache_k_ptr: int, seg_start, seg_len, seg_pos0,
                   block_tables, part_acc: Optional[torch.Tensor], part_ml: Optional[torch.Tensor], page_stride: int,
                   v_offset: int, H: int, K: int, hd: int, max_pages: int, page_size: int, window: int, scale: float,
                   n_seg: int, max_seg_len: int, max_kv_len: int, splits: int, any_short: bool, any_long: bool,
-                  group: Optional[tuple] = None) -> None:
+                  group: Optional[tuple] = None, uneven: bool = False) -> None:
     """Causal attention over the pages on tensor cores (bfloat16).  Portions with at most 16 packed rows
     (tokens x heads per kv head) go through the key-split kernel and need `part_acc` [n_seg*K*splits*16*hd]
     and `part_ml` [n_seg*K*splits*32] float32 scratch; longer portions through the row-tiled kernel.
     `group` = (pointer to the cache group's array, its pages, its layers, this layer's index) lets the
-    key-split kernel fetch whole page blocks with bulk copies (head sizes 64 and 128, power-of-two pages)."""
+    key-split kernel fetch whole page blocks with bulk copies (head sizes 64 and 128, power-of-two pages).
+    `uneven`: the requests' lengths differ much; the kernel then cuts the tiles of all requests into even shares from
+    fewer requests on than it does otherwise."""
     _dev(out, seg_start, seg_len, seg_pos0, block_tables, part_acc, part_ml)
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and out.shape[1] == H * hd
     if any_short:
         assert part_acc is not None and part_acc.numel() >= n_seg * K * splits * 16 * hd
         assert part_ml is not None and part_ml.numel() >= n_seg * K * splits * 32
+    ws = workspace(out.device)
     _check(lib().xr_attention_mma(q.data_ptr(), out.data_ptr(), cache_k_ptr, seg_start.data_ptr(), seg_len.data_ptr(),
                                   seg_pos0.data_ptr(), block_tables.data_ptr(), _ptr(part_acc), _ptr(part_ml),
                                   q_row_stride, page_stride, v_offset, n_seg, H, K, hd, max_pages, page_size, window,
                                   float(scale), max_seg_len, max_kv_len, splits, int(any_short), int(any_long),
                                   group[0] if group else None, group[1] if group else 0, group[2] if group else 1,
-                                  group[3] if group else 0, tc_workspace(out.device)[1].data_ptr() if group else None,
+                                  group[3] if group else 0, ws.status.data_ptr() if group else None,
+                                  ws.flags.data_ptr() if group else None, ws.flags.numel() if group else 0, int(uneven),
                                   _stream()), "attention_mma")
     _count((1 if any_long else 0) + (2 if any_short else 0))
 

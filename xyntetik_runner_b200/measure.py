@@ -92,8 +92,10 @@ def time_product(tokens: int, rows: int, k: int, epilogue: str, iters: int = 20,
 
 
 def time_attention(batch: int, context: int, portion: int, heads: int, kv_heads: int, head_dim: int, page_size: int = 64,
-                   iters: int = 20, plain: bool = False, use_tc: bool = True, use_tma: bool = True, device: str = "cuda:0") -> float:
-    """Attention of `batch` requests whose last `portion` tokens are in the step, each at `context` tokens."""
+                   iters: int = 20, plain: bool = False, use_tc: bool = True, use_tma: bool = True, device: str = "cuda:0",
+                   spread: bool = False) -> float:
+    """Attention of `batch` requests whose last `portion` tokens are in the step, each at `context` tokens
+    (`spread`: at lengths from an eighth of `context` up to `context`, evenly; ``spread_lengths`` gives them)."""
     dev = torch.device(device)
     H, K, hd, page, B, ctx, L = heads, kv_heads, head_dim, page_size, batch, context, portion
     mp = -(-ctx // page)
@@ -108,6 +110,8 @@ def time_attention(batch: int, context: int, portion: int, heads: int, kv_heads:
     starts = torch.arange(0, n, L, dtype=torch.int32, device=dev)
     lens = torch.full((B,), L, dtype=torch.int32, device=dev)
     pos0 = torch.full((B,), ctx - L, dtype=torch.int32, device=dev)
+    if spread:
+        pos0 = torch.tensor([c - L for c in spread_lengths(B, ctx, L)], dtype=torch.int32, device=dev)
     short = L * (H // K) <= 16
     splits = kernels.attention_mma_splits(ctx, 0, B * K)
     pa = torch.empty(B * K * splits * 16 * hd, device=dev)
@@ -122,10 +126,16 @@ def time_attention(batch: int, context: int, portion: int, heads: int, kv_heads:
         kp = cache.data_ptr() + (i % layers) * cache.stride(1) * 2
         kernels.attention_mma(qkv, qkv.shape[1], out, kp, starts, lens, pos0, bt, pa, pm, cache.stride(0), cache.stride(2),
                               H, K, hd, mp, page, 0, 1 / math.sqrt(hd), B, L, ctx, splits, short, not short,
-                              group=(cache.data_ptr(), n_pages, layers, i % layers) if use_tma else None)
+                              group=(cache.data_ptr(), n_pages, layers, i % layers) if use_tma else None, uneven=spread)
     us = time_replayed(run, iters, plain)
     kernels.tc_check_status(dev)
     return us
+
+
+def spread_lengths(batch: int, context: int, portion: int = 1):
+    """Lengths from an eighth of `context` up to `context`, evenly (never shorter than the portion)."""
+    lo = max(portion, context // 8)
+    return [lo + (context - lo) * i // max(1, batch - 1) for i in range(batch)]
 
 
 def time_sampling(rows: int, vocab: int, setting: str = "greedy", iters: int = 20, plain: bool = False, one_block: bool = False,

@@ -130,7 +130,7 @@ class GQAAttention(Mixer):
                 kernels.attention_mma(qkv, qkv_dim, o, k_ptr, ctx.seg_start, ctx.seg_len, ctx.seg_pos0, bt, pa, pm,
                                       page_stride, v_offset, self.H, self.K, self.hd, ctx.max_pages, ctx.page_size,
                                       self.window or 0, self.scale, ctx.n_seg, int(seg_len.max()), ctx.max_kv_len, splits,
-                                      any_short, any_long, group=ctx.cache_group(lay) if USE_TMA else None)
+                                      any_short, any_long, group=ctx.cache_group(lay) if USE_TMA else None, uneven=ctx.uneven)
                 counters["mma"] += 1
         else:
             kernels.attention_simt(qkv, qkv_dim, o, k_ptr, ctx.positions, ctx.tok_seg, bt, page_stride, v_offset,
