@@ -172,3 +172,43 @@ def test_generation_goes_on_after_failed_steps(folder, monkeypatch, temp):
         results.append([(sch.finished[i].generated, sch.finished[i].finish_reason) for i in ids])
     assert results[0] == results[1]
     assert all(len(g) == 14 for g, _ in results[0])
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_runner_goes_on(folder):
+    """The bounded wait of the decode attention (a piece of a request handed over by another block) on a flag that
+    nothing raises: the probe kernel runs that wait for a few thousand looks, it runs out, and the kernel writes the
+    status word as the attention kernel would.  Nothing faults or hangs.  The host must then: raise at its next look at
+    the word (every `Runner.STATUS_EVERY` steps inside `generate`), clear the word, give back what the call held,
+    and generate the same tokens as before when asked again."""
+    import torch
+    from xyntetik_runner_b200 import kernels
+    from xyntetik_runner_b200.engine.runner import Runner
+    dev = torch.device("cuda:0")
+    kernels.tc_check_status(dev)
+    kernels.attention_wait_probe(dev)
+    with pytest.raises(kernels.KernelError, match="decode attention gave up waiting"):
+        kernels.tc_check_status(dev)
+    kernels.tc_check_status(dev)                            # the word was cleared by the look that raised
+    ws = kernels.workspace(dev)
+    assert int(ws.status.item()) == 0 and int(ws.flags.abs().sum()) == 0
+
+    V = tiny.TINY_B["vocab_size"]
+    prompts = [traces.random_tokens(70 + i, n, V) for i, n in enumerate((9, 21, 14))]
+    r = Runner(folder, dtype="float32", ctx=128, parallel=3, page_size=8)
+    want = [g.tokens for g in r.generate(prompts, n=12, ignore_eos=True)]
+    r.STATUS_EVERY = 2
+    seen = {"tokens": 0}
+
+    def on_token(rid, tok, done):
+        seen["tokens"] += 1
+        if seen["tokens"] == 7:
+            kernels.attention_wait_probe(dev)               # from here on the status word says that a kernel gave up
+        return True
+    with pytest.raises(kernels.KernelError, match="gave up waiting"):
+        r.generate(prompts, n=12, ignore_eos=True, on_token=on_token)
+    assert seen["tokens"] < 3 * 12                          # the call ended at a look at the word, not after all its tokens
+    r.engine.cache.audit()
+    assert not r.engine.cache.live_requests() and not r.scheduler.has_work() and not r.scheduler.finished
+    again = [g.tokens for g in r.generate(prompts, n=12, ignore_eos=True)]
+    assert again == want
+    r.engine.cache.audit()

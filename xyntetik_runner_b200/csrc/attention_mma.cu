@@ -767,6 +767,25 @@ __device__ __forceinline__ void att_st_release(int* p, int v) {
     asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+// Wait until the word at `flag` is not zero, at most `limit` looks (each a load from L2).  False: it stayed zero.
+__device__ __forceinline__ bool att_wait_flag(const int* flag, uint32_t limit) {
+    for (uint32_t spin = 0; spin < limit; spin++)
+        if (att_ld_acquire(flag) != 0) return true;
+    return false;
+}
+
+// The wait of the kernel below on a flag that nothing raises: it runs out after `limit` looks, and the kernel reports it
+// in the status word exactly as the attention kernel does.  For tests of what the host does with that word; the
+// context stays usable.
+__global__ void k_attention_wait_probe(const int* flag, int* status, uint32_t limit) {
+    if (!att_wait_flag(flag, limit)) atomicExch(status, 2);
+}
+XR_EXPORT int xr_attention_wait_probe(const int* flag, int* status, unsigned int limit, cudaStream_t stream) {
+    if (flag == nullptr || status == nullptr || limit < 1 || limit > ATT_SPIN_LIMIT) return XR_ERR_ARG;
+    k_attention_wait_probe<<<1, 1, 0, stream>>>(flag, status, limit);
+    return xr_launch_status();
+}
+
 template <int HD, int STAGES>
 __global__ void __launch_bounds__(ATT_THREADS, 3)
 k_attention_keys_even(const __grid_constant__ CUtensorMap cache_map, AttnMmaArgs a, int n_seg, int* flags) {
@@ -1009,9 +1028,7 @@ k_attention_keys_even(const __grid_constant__ CUtensorMap cache_map, AttnMmaArgs
                 for (int k = tid; k < nf; k += ATT_THREADS) {
                     const long long c2 = c + 1 + k;
                     if (T * c2 / C == T * (c2 + 1) / C) continue;
-                    bool there = false;
-                    for (uint32_t spin = 0; spin < ATT_SPIN_LIMIT && !there; spin++) there = att_ld_acquire(flags + c2) != 0;
-                    if (there) *(volatile int*)(flags + c2) = 0; else *gave_up = 1;
+                    if (att_wait_flag(flags + c2, ATT_SPIN_LIMIT)) *(volatile int*)(flags + c2) = 0; else *gave_up = 1;
                 }
                 __syncthreads();
                 if (!*gave_up) {
@@ -1281,6 +1298,8 @@ static bool att_even_wanted(long long items, bool uneven) {
 static long long g_even_launches = 0;
 // Launches of the even-shares kernel so far (captures count once): lets a test see which kernel a step took.
 XR_EXPORT int xr_attention_even_launches() { return (int)(g_even_launches & 0x7fffffff); }
+// XRB200_NO_CLUSTER_MERGE=1: spans and the merge kernel only (no exchange inside clusters, no even shares), so that a
+// test can compare the bulk-copy kernel with the per-thread copies where both add in the same order.
 static bool att_cluster_merge_enabled() {
     static int on = -1;
     if (on < 0) { const char* e = getenv("XRB200_NO_CLUSTER_MERGE"); on = (e && e[0] == '1') ? 0 : 1; }

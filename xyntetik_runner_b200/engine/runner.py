@@ -198,21 +198,30 @@ class Runner:
         t0 = time.perf_counter()
         sch = self.scheduler
         steps = 0
-        while sch.has_work():
-            before = len(sch.finished)
-            res = sch.step()
-            if on_token is not None:
-                for rid, tok, done in res:
-                    if on_token(rid, tok, done) is False and not done:
-                        sch.abort(rid)           # the callback asked for the end of this request (src/engine.c:1844-1848)
-            if not res and not sch.live and sch.waiting and len(sch.finished) == before:
-                r = sch.waiting.popleft()
-                sch._finish(r, "rejected")
-            steps += 1
-            if steps % self.STATUS_EVERY == 0:
-                self.engine.check_status()       # a kernel that gave up a wait: stop now, not after a run of garbage
-        torch.cuda.synchronize(self.engine.device)
-        self.engine.check_status()
+        try:
+            while sch.has_work():
+                before = len(sch.finished)
+                res = sch.step()
+                if on_token is not None:
+                    for rid, tok, done in res:
+                        if on_token(rid, tok, done) is False and not done:
+                            sch.abort(rid)       # the callback asked for the end of this request (src/engine.c:1844-1848)
+                if not res and not sch.live and sch.waiting and len(sch.finished) == before:
+                    r = sch.waiting.popleft()
+                    sch._finish(r, "rejected")
+                steps += 1
+                if steps % self.STATUS_EVERY == 0:
+                    self.engine.check_status()   # a kernel that gave up a wait: stop now, not after a run of garbage
+            torch.cuda.synchronize(self.engine.device)
+            self.engine.check_status()
+        except BaseException:
+            # the call ends here: its requests give back their pages and slots, and the runner can be used again
+            for rid in ids:
+                if rid not in sch.finished:
+                    sch.abort(rid)
+            for rid in ids:
+                sch.finished.pop(rid, None)
+            raise
         self.timing["generate_s"] = time.perf_counter() - t0
         out = []
         for rid in ids:

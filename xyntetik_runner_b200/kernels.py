@@ -62,6 +62,7 @@ def _declare(L: ctypes.CDLL) -> None:
                              _i, _i, _i, _i, _i, _vp, _ll, _i, _i, _vp, _vp, _i, _i, _vp],
         "xr_attention_mma_splits": [_i, _i, _ll],
         "xr_attention_even_launches": [],
+        "xr_attention_wait_probe": [_vp, _vp, ctypes.c_uint, _vp],
         "xr_attention_tc_supported": [_i, _i, _i, _i],
         "xr_attention_tc": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _ll, _i, _i, _vp],
         "xr_sample": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
@@ -481,6 +482,15 @@ def attention_mma_splits(max_kv_len: int, window: int, items: int) -> int:
 def attention_even_launches() -> int:
     """How often the decode attention was launched in even shares (rather than in spans) so far."""
     return int(lib().xr_attention_even_launches())
+
+
+def attention_wait_probe(device: torch.device, limit: int = 1 << 12) -> None:
+    """Run the decode attention's bounded wait on a flag that nothing raises: it runs out after `limit` looks and the
+    status word of `device` says so, as it would for a hand-over that never came (``tc_check_status`` then raises).
+    Nothing faults and nothing hangs; this exists so that tests can drive the host's handling of that word."""
+    ws = workspace(device)
+    _check(lib().xr_attention_wait_probe(ws.flags.data_ptr() + 4 * (ws.flags.numel() - 1), ws.status.data_ptr(), int(limit),
+                                         _stream()), "attention_wait_probe")
 
 
 def attention_mma(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, cache_k_ptr: int, seg_start, seg_len, seg_pos0,
