@@ -241,8 +241,10 @@ def timeline(args) -> int:
     from xyntetik_runner_b200.sampling.sampler import DeviceSampler, RequestSampler, SamplingParams
     cfg, _, seed, ctx, _, _, _ = shape_config(args)
     B, n_layers = args.batch, cfg.num_hidden_layers
-    eng = random_engine(cfg, seed, EngineParams(dtype="bfloat16", max_tokens=B * ctx, page_size=64, max_requests=B,
-                                                max_request_tokens=ctx, max_step_tokens=2048))
+    mixed = args.mixed and args.portion > 1      # --mixed: a prompt portion of --portion tokens beside --batch decoded tokens
+    eng = random_engine(cfg, seed, EngineParams(dtype="bfloat16", max_tokens=(B + (1 if mixed else 0)) * ctx, page_size=64,
+                                                max_requests=B + (1 if mixed else 0), max_request_tokens=ctx,
+                                                max_step_tokens=max(2048, args.portion + B)))
     for kv in eng.kv:
         kv.normal_(0.0, 1.0)
     sampler = DeviceSampler(eng.device)
@@ -255,18 +257,25 @@ def timeline(args) -> int:
     lib.xr_trace_dump.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
     host = (ctypes.c_ulonglong * (32 * 4096 * 4))()
     counts = (ctypes.c_uint * 32)()
-    if args.portion > 1:
+    if args.portion > 1 and not mixed:
         # a prompt step instead: one request of --portion tokens in one step
         for r in ids:
             eng.end(r)
         ids, samplers = ids[:1], samplers[:1]
     for s in range(12):
-        if args.portion > 1:
+        if mixed:
+            # the portion continues a prompt that already holds half of the context
+            eng.adopt("prompt", max(64, ctx // 2 - args.portion))
+            logits = eng.step([StepEntry(r, [int(rng.randint(0, 1000))], [0]) for r in ids] +
+                              [StepEntry("prompt", [int(t) for t in rng.randint(0, 1000, size=args.portion)], [])])
+        elif args.portion > 1:
             logits = eng.step([StepEntry(ids[0], [int(t) for t in rng.randint(0, 1000, size=args.portion)], [args.portion - 1])])
         else:
             logits = eng.step([StepEntry(r, [int(rng.randint(0, 1000))], [0]) for r in ids])
         sampler.pick(logits, samplers)
-        if args.portion > 1:
+        if mixed:
+            eng.end("prompt")
+        elif args.portion > 1:
             eng.end(ids[0])
         if s == 10:
             torch.cuda.synchronize()
@@ -285,7 +294,12 @@ def timeline(args) -> int:
         raise SystemExit(f"{len(ev)} launches were recorded: not embedding + norm + {n_layers} equal layers + 2")
     first = 2 + per_layer
     rows = ev[first:first + per_layer + 1]
-    print(f"one layer of a {'prompt step of ' + str(args.portion) + ' tokens' if args.portion > 1 else 'decode step'}, batch {B}, context {ctx} (times in us)")
+    what = "decode step"
+    if mixed:
+        what = f"step of {B} decoded tokens beside a prompt portion of {args.portion} tokens"
+    elif args.portion > 1:
+        what = f"prompt step of {args.portion} tokens"
+    print(f"one layer of a {what}, batch {B}, context {ctx} (times in us)")
     print(f"{'could begin':>12} {'resident before':>16} {'took':>7}  grid / block")
     base = rows[0][0]
     for (t1, t0, g, b), nxt in zip(rows[:-1], rows[1:]):
@@ -326,7 +340,7 @@ def main() -> int:
                                ("vocab", int, 128256), ("iters", int, 20), ("sample-rows", int, 8)):
         ap.add_argument(f"--{name}", type=typ, default=default, help=argparse.SUPPRESS)
     ap.add_argument("--epilogue", choices=["store", "add", "swiglu"], default="store", help=argparse.SUPPRESS)
-    for name in ("plain", "no-tc", "no-tma", "one-block", "spread"):
+    for name in ("plain", "no-tc", "no-tma", "one-block", "spread", "mixed"):
         ap.add_argument(f"--{name}", action="store_true", help=argparse.SUPPRESS)
     args = ap.parse_args()
     if args.gpus != 1:

@@ -293,7 +293,8 @@ def _run_attention(case, kind, H, K, hd, page, window, dtype, tma=False, uneven=
         kernels.attention_mma(c["qkv"], qkv_dim, out, k_ptr, c["starts"], c["lens"], c["pos0"], c["bt"], pa, pm, page_stride,
                               v_off, H, K, hd, c["max_pages"], page, window, c["scale"], c["n_seg"], int(lens.max()),
                               c["max_len"], splits, bool((lens * G <= 16).any()), bool((lens * G > 16).any()),
-                              group=(cache.data_ptr(), cache.shape[0], cache.shape[1], 0) if tma else None, uneven=uneven)
+                              group=(cache.data_ptr(), cache.shape[0], cache.shape[1], 0) if tma else None, uneven=uneven,
+                              seg_len_host=lens if tma else None)      # (the row-tiled kernel's grid: exact, or an upper bound)
         kernels.tc_check_status(torch.device(DEV))
     return out.cpu().double()
 
@@ -604,8 +605,10 @@ def test_attention_tc(case_id, hd):
     c = _paged_case(100 + case_id + hd, H, K, hd, page, segs, torch.bfloat16, window)
     out = torch.full((c["n"], H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
     cache = c["cache"]
+    # (the grid is sized from the lengths, or, without them, by an upper bound whose surplus blocks return at once)
     kernels.attention_tc(c["qkv"], out, c["starts"], c["lens"], c["pos0"], c["bt"], (cache.data_ptr(), cache.shape[0], cache.shape[1], 0),
-                         H, K, hd, c["max_pages"], page, window, c["scale"], c["n_seg"], int(c["lens_host"].max()))
+                         H, K, hd, c["max_pages"], page, window, c["scale"], c["n_seg"], int(c["lens_host"].max()),
+                         seg_len_host=c["lens_host"] if case_id % 2 == 0 else None)
     kernels.tc_check_status(torch.device(DEV))
     got, ref = out.cpu().double(), c["ref"]
     G = H // K

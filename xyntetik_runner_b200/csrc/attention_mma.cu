@@ -288,17 +288,29 @@ __device__ __forceinline__ void load_q(__nv_bfloat16* qs, const AttnMmaArgs& a, 
 // ---------------------------------------------------------------------------------------------
 template <int HD>
 __global__ void __launch_bounds__(ATT_THREADS)
-k_attention_rows(AttnMmaArgs a) {
+k_attention_rows(AttnMmaArgs a, int n_seg) {
     xr_pdl_launch();
-    xr_pdl_wait();
     constexpr int LD = HD + 8;
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __nv_bfloat16* qs = (__nv_bfloat16*)smem_raw;                 // [64][LD]
     __nv_bfloat16* kbuf = qs + ATT_ROWS * LD;                      // [2][64][LD]
     __nv_bfloat16* vbuf = kbuf + 2 * ATT_TILE * LD;                // [2][64][LD]
-    const int seg = blockIdx.z, kvh = blockIdx.y;
-    const int L = a.seg_len[seg], rows_total = L * a.G, row0 = blockIdx.x * ATT_ROWS;
-    if (rows_total <= 16 || row0 >= rows_total) return;            // short portions belong to the keys kernel
+    // The row tiles of the portions with more than 16 packed rows, laid end to end, are the grid's x (short portions
+    // belong to the keys kernel and have no blocks here); a block finds its (portion, tile) by walking the lengths.
+    const int kvh = blockIdx.y;
+    int seg = -1, tile = 0;
+    {
+        int before = 0;
+        for (int s = 0; s < n_seg; s++) {
+            const int rows = a.seg_len[s] * a.G;
+            const int t = rows > 16 ? (rows + ATT_ROWS - 1) / ATT_ROWS : 0;
+            if ((int)blockIdx.x < before + t) { seg = s; tile = (int)blockIdx.x - before; break; }
+            before += t;
+        }
+    }
+    if (seg < 0) return;                                           // (the caller gave an upper bound of the tiles)
+    xr_pdl_wait();
+    const int L = a.seg_len[seg], rows_total = L * a.G, row0 = tile * ATT_ROWS;
     const int pos0 = a.seg_pos0[seg], tok_base = a.seg_start[seg];
     const int* bt = a.block_tables + (size_t)seg * a.max_pages;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1429,7 +1441,8 @@ static int launch_keys_tma(const AttnMmaArgs& a, const void* cache_base, long lo
 
 template <int HD>
 static int launch_attention(const AttnMmaArgs& a, int n_seg, int max_seg_len, int max_kv_len, int any_short, int any_long,
-                            const void* cache_base, long long n_pages, cudaStream_t stream, int* flags, int n_flags, long long room, bool uneven) {
+                            const void* cache_base, long long n_pages, cudaStream_t stream, int* flags, int n_flags, long long room, bool uneven,
+                            long long row_tiles) {
     constexpr int LD = HD + 8;
     constexpr int SMEM_ROWS = (ATT_ROWS + 4 * ATT_TILE) * LD * 2;
     constexpr int KEYS_MERGE = 16 * LD * 2 + (4 * 16 * HD + 4 * 16 * 2) * 4;
@@ -1445,9 +1458,11 @@ static int launch_attention(const AttnMmaArgs& a, int n_seg, int max_seg_len, in
         configured = true;
     }
     if (any_long) {
-        long long tiles = ((long long)max_seg_len * a.G + ATT_ROWS - 1) / ATT_ROWS;
+        // row_tiles: the 64-row tiles of the portions with more than 16 packed rows, summed; 0: not known, and an upper
+        // bound is taken (blocks beyond the true number return at once)
+        long long tiles = row_tiles > 0 ? row_tiles : (((long long)max_seg_len * a.G + ATT_ROWS - 1) / ATT_ROWS) * n_seg;
         if (tiles > 0x7fffffffLL || n_seg > 65535 || a.K > 65535) return XR_ERR_ARG;
-        xr_launch((k_attention_rows<HD>), dim3((unsigned)tiles, a.K, n_seg), dim3(ATT_THREADS), SMEM_ROWS, stream, a);
+        xr_launch((k_attention_rows<HD>), dim3((unsigned)tiles, a.K, 1), dim3(ATT_THREADS), SMEM_ROWS, stream, a, n_seg);
         int rc = xr_launch_status();
         if (rc != XR_OK) return rc;
     }
@@ -1492,13 +1507,14 @@ XR_EXPORT int xr_attention_mma_splits(int max_kv_len, int window, long long item
 // (only read and written when any_short).  splits: at least xr_attention_mma_splits(max_kv_len, window, n_seg * K).
 // flags: n_flags zeroed words that only this kernel touches (it leaves them zero), or null.
 // uneven: the requests' key ranges differ much in length (a hint for the choice between spans and even shares).
+// row_tiles: the 64-row tiles of the portions with more than 16 packed rows, summed, or 0 if the caller does not know.
 XR_EXPORT int xr_attention_mma(const void* q, void* out, const void* cache_k, const int* seg_start, const int* seg_len,
                                const int* seg_pos0, const int* block_tables, float* part_acc, float* part_ml,
                                long long q_stride, long long page_stride, long long v_offset, int n_seg, int H, int K,
                                int hd, int max_pages, int page_size, int window, float scale, int max_seg_len,
                                int max_kv_len, int splits, int any_short, int any_long, const void* cache_base,
                                long long n_pages, int n_layers, int layer, int* status, int* flags, int n_flags,
-                               int uneven, cudaStream_t stream) {
+                               int uneven, long long row_tiles, cudaStream_t stream) {
     if (n_seg < 1 || H < 1 || K < 1 || H % K != 0 || hd < 16 || hd > 128 || hd % 16 != 0 || page_size < 1 || window < 0 ||
         (q_stride % 8) != 0 || ((uintptr_t)q & 15) || ((uintptr_t)cache_k & 15) || (page_stride % 8) != 0 || (v_offset % 8) != 0)
         return XR_ERR_ARG;
@@ -1513,14 +1529,14 @@ XR_EXPORT int xr_attention_mma(const void* q, void* out, const void* cache_k, co
     const long long room = (long long)splits * n_seg * K;
     if ((page_size & (page_size - 1)) == 0) { int sh = 0; while ((1 << sh) < page_size) sh++; a.page_shift = sh; }
     switch (hd) {
-        case 16: return launch_attention<16>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream, flags, n_flags, room, uneven != 0);
-        case 32: return launch_attention<32>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream, flags, n_flags, room, uneven != 0);
-        case 48: return launch_attention<48>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream, flags, n_flags, room, uneven != 0);
-        case 64: return launch_attention<64>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream, flags, n_flags, room, uneven != 0);
-        case 80: return launch_attention<80>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream, flags, n_flags, room, uneven != 0);
-        case 96: return launch_attention<96>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream, flags, n_flags, room, uneven != 0);
-        case 112: return launch_attention<112>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream, flags, n_flags, room, uneven != 0);
-        case 128: return launch_attention<128>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream, flags, n_flags, room, uneven != 0);
+        case 16: return launch_attention<16>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream, flags, n_flags, room, uneven != 0, row_tiles);
+        case 32: return launch_attention<32>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream, flags, n_flags, room, uneven != 0, row_tiles);
+        case 48: return launch_attention<48>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream, flags, n_flags, room, uneven != 0, row_tiles);
+        case 64: return launch_attention<64>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream, flags, n_flags, room, uneven != 0, row_tiles);
+        case 80: return launch_attention<80>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream, flags, n_flags, room, uneven != 0, row_tiles);
+        case 96: return launch_attention<96>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream, flags, n_flags, room, uneven != 0, row_tiles);
+        case 112: return launch_attention<112>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream, flags, n_flags, room, uneven != 0, row_tiles);
+        case 128: return launch_attention<128>(a, n_seg, max_seg_len, max_kv_len, any_short, any_long, cache_base, n_pages, stream, flags, n_flags, room, uneven != 0, row_tiles);
     }
     return XR_ERR_ARG;
 }

@@ -47,6 +47,7 @@ struct AttnTcArgs {
     int* status;
     int H, K, G, max_pages, page_size, page_shift, window, n_layers, layer;
     float scale_log2;            // scale * log2(e)
+    int n_seg;
 };
 
 __device__ __forceinline__ uint32_t ta_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -187,11 +188,25 @@ k_attention_tc(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     volatile int* gave_up = (volatile int*)(tmem_slot + 1);
     float* xch = (float*)(tmem_slot + 4);                // [2 tile parities][2 key halves][128 rows]
 
-    const int seg = blockIdx.z, kvh = blockIdx.y;
+    // The row tiles of the portions with more than 16 packed rows, laid end to end, are the grid's x (short portions
+    // belong to the key-split kernel and have no blocks here: a step may hold dozens of them beside one prompt
+    // portion).  A block finds its (portion, tile) by walking the portions' lengths; later tiles, which have the most
+    // keys, start first.
+    const int kvh = blockIdx.y;
+    int seg = -1, tile = 0;
+    {
+        const int want = (int)gridDim.x - 1 - (int)blockIdx.x;
+        int before = 0;
+        for (int s = 0; s < a.n_seg; s++) {
+            const int rows = a.seg_len[s] * a.G;
+            const int t = rows > 16 ? (rows + TA_ROWS - 1) / TA_ROWS : 0;
+            if (want < before + t) { seg = s; tile = want - before; break; }
+            before += t;
+        }
+    }
+    if (seg < 0) return;                                            // (the caller gave an upper bound of the tiles)
     const int L = a.seg_len[seg], rows_total = L * a.G;
-    const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;          // tiles with the most keys start first
     const int row0 = tile * TA_ROWS;
-    if (rows_total <= 16 || row0 >= rows_total) return;             // short portions belong to the key-split kernel
     xr_pdl_launch();
     xr_pdl_wait();
     const int pos0 = a.seg_pos0[seg], tok_base = a.seg_start[seg];
@@ -481,7 +496,7 @@ XR_EXPORT int xr_attention_tc_supported(int H, int K, int hd, int page_size) {
 XR_EXPORT int xr_attention_tc(const void* q, void* out, const void* cache_base, const int* seg_start, const int* seg_len,
                               const int* seg_pos0, const int* block_tables, int* status, long long q_row_stride, int n,
                               int n_seg, int H, int K, int hd, int max_pages, int page_size, int window, float scale,
-                              int max_seg_len, long long n_pages, int n_layers, int layer, cudaStream_t stream) {
+                              int max_seg_len, long long row_tiles, long long n_pages, int n_layers, int layer, cudaStream_t stream) {
     if (!xr_attention_tc_supported(H, K, hd, page_size) || n < 1 || n_seg < 1 || window < 0 || status == nullptr) return XR_ERR_ARG;
     if (((uintptr_t)q & 15) || ((uintptr_t)cache_base & 15) || (q_row_stride % 8) != 0) return XR_ERR_ARG;
     const int G = H / K;
@@ -512,7 +527,7 @@ XR_EXPORT int xr_attention_tc(const void* q, void* out, const void* cache_base, 
     int shift = 0;
     while ((1 << shift) < page_size) shift++;
     AttnTcArgs a{(__nv_bfloat16*)out, seg_start, seg_len, seg_pos0, block_tables, status, H, K, G, max_pages, page_size, shift,
-                 window, n_layers, layer, scale * 1.4426950408889634f};
+                 window, n_layers, layer, scale * 1.4426950408889634f, n_seg};
     constexpr int SMEM = 14 * TA_ROWS * 128 + 128 + 2 * 2 * 128 * 4;
     static bool configured = false;
     const bool p_tmem = true;                  // P stays in tensor memory (the other instantiation passes P through shared memory)
@@ -524,9 +539,11 @@ XR_EXPORT int xr_attention_tc(const void* q, void* out, const void* cache_base, 
             return XR_ERR_LAUNCH;
         configured = true;
     }
-    long long tiles = ((long long)max_seg_len * G + TA_ROWS - 1) / TA_ROWS;
+    // row_tiles: the 128-row tiles of the portions with more than 16 packed rows, summed; 0: not known, and an upper
+    // bound is taken (blocks beyond the true number return at once)
+    long long tiles = row_tiles > 0 ? row_tiles : (((long long)max_seg_len * G + TA_ROWS - 1) / TA_ROWS) * n_seg;
     if (tiles > 0x7fffffffLL) return XR_ERR_ARG;
-    const dim3 grid((unsigned)tiles, K, n_seg);
+    const dim3 grid((unsigned)tiles, K, 1);
     if (hd == 128) {
         if (p_tmem) xr_launch(k_attention_tc<true, 128>, grid, dim3(TA_THREADS), SMEM, stream, qm, kvm, a);
         else xr_launch(k_attention_tc<false, 128>, grid, dim3(TA_THREADS), SMEM, stream, qm, kvm, a);

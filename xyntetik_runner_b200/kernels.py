@@ -59,12 +59,12 @@ def _declare(L: ctypes.CDLL) -> None:
         "xr_finish_plain": [_vp, _i, _vp, _vp, _i, _i, _i, _i, _ll, _vp],
         "xr_finish_rope_store": [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
         "xr_attention_mma": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _i, _i, _i, _i, _i, _i, _i, _f,
-                             _i, _i, _i, _i, _i, _vp, _ll, _i, _i, _vp, _vp, _i, _i, _vp],
+                             _i, _i, _i, _i, _i, _vp, _ll, _i, _i, _vp, _vp, _i, _i, _ll, _vp],
         "xr_attention_mma_splits": [_i, _i, _ll],
         "xr_attention_even_launches": [],
         "xr_attention_wait_probe": [_vp, _vp, ctypes.c_uint, _vp],
         "xr_attention_tc_supported": [_i, _i, _i, _i],
-        "xr_attention_tc": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _ll, _i, _i, _vp],
+        "xr_attention_tc": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _ll, _ll, _i, _i, _vp],
         "xr_sample": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
         "xr_sample_one_block": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
         "xr_logprob": [_vp, _ll, _i, _i, _vp, _vp, _vp],
@@ -497,20 +497,25 @@ def attention_mma(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, cache_k
                   block_tables, part_acc: Optional[torch.Tensor], part_ml: Optional[torch.Tensor], page_stride: int,
                   v_offset: int, H: int, K: int, hd: int, max_pages: int, page_size: int, window: int, scale: float,
                   n_seg: int, max_seg_len: int, max_kv_len: int, splits: int, any_short: bool, any_long: bool,
-                  group: Optional[tuple] = None, uneven: bool = False) -> None:
+                  group: Optional[tuple] = None, uneven: bool = False, seg_len_host=None) -> None:
     """Causal attention over the pages on tensor cores (bfloat16).  Portions with at most 16 packed rows
     (tokens x heads per kv head) go through the key-split kernel and need `part_acc` [n_seg*K*splits*16*hd]
     and `part_ml` [n_seg*K*splits*32] float32 scratch; longer portions through the row-tiled kernel.
     `group` = (pointer to the cache group's array, its pages, its layers, this layer's index) lets the
     key-split kernel fetch whole page blocks with bulk copies (head sizes 64 and 128, power-of-two pages).
     `uneven`: the requests' lengths differ much; the kernel then cuts the tiles of all requests into even shares from
-    fewer requests on than it does otherwise."""
+    fewer requests on than it does otherwise.  seg_len_host: the portions' lengths on the host (numpy), from which the
+    row-tiled kernel's grid is sized exactly; without them every portion gets the blocks of the longest."""
     _dev(out, seg_start, seg_len, seg_pos0, block_tables, part_acc, part_ml)
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and out.shape[1] == H * hd
     if any_short:
         assert part_acc is not None and part_acc.numel() >= n_seg * K * splits * 16 * hd
         assert part_ml is not None and part_ml.numel() >= n_seg * K * splits * 32
     ws = workspace(out.device)
+    row_tiles = 0
+    if any_long and seg_len_host is not None:
+        rows = seg_len_host.astype("int64") * (H // K)
+        row_tiles = int(((rows + 63) // 64)[rows > 16].sum())
     _check(lib().xr_attention_mma(q.data_ptr(), out.data_ptr(), cache_k_ptr, seg_start.data_ptr(), seg_len.data_ptr(),
                                   seg_pos0.data_ptr(), block_tables.data_ptr(), _ptr(part_acc), _ptr(part_ml),
                                   q_row_stride, page_stride, v_offset, n_seg, H, K, hd, max_pages, page_size, window,
@@ -518,7 +523,7 @@ def attention_mma(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, cache_k
                                   group[0] if group else None, group[1] if group else 0, group[2] if group else 1,
                                   group[3] if group else 0, ws.status.data_ptr() if group else None,
                                   ws.flags.data_ptr() if group else None, ws.flags.numel() if group else 0, int(uneven),
-                                  _stream()), "attention_mma")
+                                  row_tiles, _stream()), "attention_mma")
     _count((1 if any_long else 0) + (2 if any_short else 0))
 
 
@@ -528,15 +533,21 @@ def attention_tc_supported(dtype: torch.dtype, H: int, K: int, hd: int, page_siz
 
 def attention_tc(qkv: torch.Tensor, out: torch.Tensor, seg_start, seg_len, seg_pos0, block_tables, group: tuple,
                  H: int, K: int, hd: int, max_pages: int, page_size: int, window: int, scale: float, n_seg: int,
-                 max_seg_len: int) -> None:
+                 max_seg_len: int, seg_len_host=None) -> None:
     """Causal attention of the portions with more than 16 packed rows on tcgen05 (S and O in tensor memory).
-    qkv: the step's fused rows (Q heads first); group = (pointer to the cache group's array, pages, layers, layer)."""
+    qkv: the step's fused rows (Q heads first); group = (pointer to the cache group's array, pages, layers, layer).
+    seg_len_host: the portions' lengths on the host (numpy), from which the grid is sized exactly; without them every
+    portion gets the blocks of the longest."""
     _dev(qkv, out, seg_start, seg_len, seg_pos0, block_tables)
     n = qkv.shape[0]
     assert qkv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and out.shape == (n, H * hd)
     status = tc_workspace(out.device)[1]
+    row_tiles = 0
+    if seg_len_host is not None:
+        rows = seg_len_host.astype("int64") * (H // K)
+        row_tiles = int(((rows + 127) // 128)[rows > 16].sum())
     _check(lib().xr_attention_tc(qkv.data_ptr(), out.data_ptr(), group[0], seg_start.data_ptr(), seg_len.data_ptr(),
                                  seg_pos0.data_ptr(), block_tables.data_ptr(), status.data_ptr(), qkv.stride(0), n, n_seg,
-                                 H, K, hd, max_pages, page_size, window, float(scale), max_seg_len, group[1], group[2],
+                                 H, K, hd, max_pages, page_size, window, float(scale), max_seg_len, row_tiles, group[1], group[2],
                                  group[3], _stream()), "attention_tc")
     _count()

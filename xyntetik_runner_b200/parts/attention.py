@@ -123,14 +123,15 @@ class GQAAttention(Mixer):
                 # prompt portions: S = Q K^T and O += P V on tcgen05
                 kernels.attention_tc(qkv, o, ctx.seg_start, ctx.seg_len, ctx.seg_pos0, bt, ctx.cache_group(lay), self.H,
                                      self.K, self.hd, ctx.max_pages, ctx.page_size, self.window or 0, self.scale, ctx.n_seg,
-                                     int(seg_len.max()))
+                                     int(seg_len.max()), seg_len_host=seg_len)
                 counters["tcgen05"] += 1
                 any_long = False
             if any_short or any_long:
                 kernels.attention_mma(qkv, qkv_dim, o, k_ptr, ctx.seg_start, ctx.seg_len, ctx.seg_pos0, bt, pa, pm,
                                       page_stride, v_offset, self.H, self.K, self.hd, ctx.max_pages, ctx.page_size,
                                       self.window or 0, self.scale, ctx.n_seg, int(seg_len.max()), ctx.max_kv_len, splits,
-                                      any_short, any_long, group=ctx.cache_group(lay) if USE_TMA else None, uneven=ctx.uneven)
+                                      any_short, any_long, group=ctx.cache_group(lay) if USE_TMA else None, uneven=ctx.uneven,
+                                      seg_len_host=seg_len)
                 counters["mma"] += 1
         else:
             kernels.attention_simt(qkv, qkv_dim, o, k_ptr, ctx.positions, ctx.tok_seg, bt, page_stride, v_offset,
