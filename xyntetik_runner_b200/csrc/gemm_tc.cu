@@ -804,10 +804,15 @@ XR_EXPORT int xr_gemm_tc(const void* X, const void* W, const float* bias, void* 
     if (pl.pair) {
         rc = PairLaunch::launch(mw, mx, p, stream);
     } else {
+        // With no more CTAs than SMs a CTA has its SM to itself: a ring twice as deep keeps as many bytes in flight as two
+        // CTAs would (the gated product of Llama-3.2-1B layer sizes at 64 tokens, 128 uncut tiles: 17.6 -> 15.9 us inside a
+        // step; what is left to the 10 us of its bytes is the tokens' tile, which every CTA fetches again with each
+        // K block through the same copy engine as its weights).
+        const bool alone = (long long)pl.tok_tiles * pl.row_tiles * splits <= xr_sm_count();
         switch (pl.bn) {
             case 16: rc = launch_tc<16, 4, 3>(mw, mx, p, grid, stream); break;
-            case 32: rc = launch_tc<32, 5, 2>(mw, mx, p, grid, stream); break;
-            case 64: rc = launch_tc<64, 4, 2>(mw, mx, p, grid, stream); break;
+            case 32: rc = alone ? launch_tc<32, 10, 1>(mw, mx, p, grid, stream) : launch_tc<32, 5, 2>(mw, mx, p, grid, stream); break;
+            case 64: rc = alone ? launch_tc<64, 8, 1>(mw, mx, p, grid, stream) : launch_tc<64, 4, 2>(mw, mx, p, grid, stream); break;
             case 128: rc = launch_tc<128, 5, 1>(mw, mx, p, grid, stream); break;
             default: rc = launch_tc<256, 4, 1>(mw, mx, p, grid, stream); break;
         }
