@@ -270,3 +270,60 @@ def test_many_requests_of_unequal_length_decode_together(n_requests):
                 f"request {rid} ({len(toks) - n_decoded} tokens), decoded token {j}: max {d.max() / scale:.2e} mean {d.mean() / scale:.2e}"
     del eng
     torch.cuda.empty_cache()
+
+
+LONG = {
+    "architectures": ["LlamaForCausalLM"], "hidden_size": 128, "num_hidden_layers": 2, "num_attention_heads": 4,
+    "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 320, "vocab_size": 300, "rms_norm_eps": 1e-5,
+    "rope_theta": 500000.0, "max_position_embeddings": 16384, "tie_word_embeddings": False, "hidden_act": "silu",
+    "torch_dtype": "bfloat16",
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 2048},
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decoding_across_position_8192(dtype):
+    """The benchmark's context length, checked: a prompt of 8,150 tokens in portions of 2,048 (the last portions attend
+    to thousands of cached keys), then 80 tokens decoded one by one beside a request of a few hundred tokens, across
+    position 8,192 (a new context bucket of the step graphs, 129 pages of 64, rotation angles of thousands of radians in
+    float32).  Every decoded position and the last prompt position against the plain implementation."""
+    from xyntetik_runner_b200.architectures.llama import build_llama
+    from xyntetik_runner_b200.config.llama import LlamaConfig
+    from xyntetik_runner_b200.engine.engine import EngineParams, random_engine
+    from xyntetik_runner_b200.engine.replay import replay
+    from xyntetik_runner_b200.weights.loader import RandomSource
+    cfg = LlamaConfig.from_dict(LONG)
+    seed, V, head, n_decoded = 21, cfg.vocab_size, 8150, 80
+    reqs = {"long": traces.random_tokens(7, head + n_decoded, V), "short": traces.random_tokens(8, 300 + n_decoded, V)}
+    steps = []
+    for at in range(0, head, 2048):
+        m = min(2048, head - at)
+        steps.append({"step": len(steps), "entries": [{"id": "long", "tokens": reqs["long"][at:at + m], "want": [m - 1] if at + m == head else []}], "end": []})
+    steps.append({"step": len(steps), "entries": [{"id": "short", "tokens": reqs["short"][:300], "want": [299]}], "end": []})
+    for j in range(n_decoded):
+        steps.append({"step": len(steps), "entries": [{"id": "long", "tokens": [reqs["long"][head + j]], "want": [0]},
+                                                      {"id": "short", "tokens": [reqs["short"][300 + j]], "want": [0]}],
+                      "end": ["long", "short"] if j == n_decoded - 1 else []})
+    src = RandomSource(build_llama(cfg).tensor_specs(), seed, torch.bfloat16, std=0.08, norm_jitter=0.1, gen_device="cuda:0")
+    tensors = {n: src.fetch(n, torch.device("cuda:0")).float().cpu().numpy() for n in src.specs}
+    plain = PlainLlama(config=LONG, tensors=tensors)
+    eng = random_engine(cfg, seed, EngineParams(dtype=dtype, max_tokens=traces.pool_tokens(steps), page_size=64, max_requests=2,
+                                                max_step_tokens=2048), std=0.08, norm_jitter=0.1)
+    res = replay(eng, steps)
+    eng.cache.audit()
+    assert eng.graph_replays >= n_decoded - 6 and len({k[2] for k in eng._graph_seen}) == 2      # two context buckets
+    ref = {"long": plain.logits(reqs["long"], rows=list(range(head - 1, head + n_decoded))),
+           "short": plain.logits(reqs["short"], rows=list(range(299, 300 + n_decoded)))}
+    first = len(steps) - n_decoded
+    got = {"long": [res[first - 2][0]] + [res[first + j][0] for j in range(n_decoded)],
+           "short": [res[first - 1][0]] + [res[first + j][1] for j in range(n_decoded)]}
+    tol = traces.TOL[dtype]
+    for rid in reqs:
+        for j, (row, want) in enumerate(zip(got[rid], ref[rid])):
+            scale = float(np.abs(want).max())
+            d = np.abs(row.astype(np.float64) - want)
+            assert np.isfinite(row).all() and d.max() <= tol["max_rel"] * scale and d.mean() <= tol["mean_rel"] * scale, \
+                f"{dtype}: request {rid}, row {j} of {n_decoded + 1}: max {d.max() / scale:.2e} mean {d.mean() / scale:.2e}"
+    del eng
+    torch.cuda.empty_cache()
