@@ -1,6 +1,8 @@
-// Picking the next token from float32 logits on the device: one block per row (k_sample), or, for rows of more
-// than 1,024 values and few rows, a cluster of eight blocks per row that keeps the row in registers
-// (k_sample_cluster, further down); and the log-probability of a given token per row (k_logprob, at the end).
+// Picking the next token from float32 logits on the device: one block per row (k_sample: the reference's short cuts
+// first -- top-k by selection, else the head of the distribution -- and threshold descents where they do not apply);
+// the descents alone spread over a cluster of eight blocks per row that keeps the row in registers, for rows of more
+// than 1,024 values and few rows (k_sample_cluster, further down; serving does not take it, tests and measurements
+// do); and the log-probability of a given token per row (k_logprob, at the end).
 //
 // The chain is the reference's `sample_pick` (src/sample.c:141-329) with
 // `pick_scaled` (src/sample.c:86-127):
@@ -12,7 +14,7 @@
 //   6. min-p drops candidates below min_p * p_max; renormalise;
 //   7. the pick is the first candidate whose cumulative probability exceeds r (a uniform draw
 //      in [0, 1) that the host makes from the request's own xorshift64 state, src/sample.c:13-20).
-// The reference sorts; this kernel never does.  Every cut above is a prefix of the same order, so it
+// The long way never sorts.  Every cut above is a prefix of the same order, so it
 // is described by a threshold in an order-preserving integer image of v (plus, among exact ties, a
 // count of ids).  Thresholds are found by descending over the 32 key bits, two bits a pass (three
 // candidate thresholds, each with its own block-wide sum in a fixed order, which makes the result
@@ -234,9 +236,94 @@ __device__ __forceinline__ void smp_argmax(const float* lg, int V, int* out, flo
     }
 }
 
+// The reference does not sort the vocabulary either when it can help it (src/sample.c:177-307): with top-k it selects
+// the k largest and sorts those; without, it gathers the head of the distribution (candidates within a factor of 1,024
+// of the best, loosened up to five times) and uses it once the head provably holds every survivor: top_p of the whole
+// mass, or everything above the min-p floor, or more mass than the draw needs.  The sorted candidates then go through
+// `pick_scaled` (src/sample.c:86-127) in float32, one after the other.  The same short cuts here: candidates are
+// gathered into shared memory, put in order by counting (key descending, id ascending), and the chain runs on them
+// with the reference's own arithmetic.  A row whose head does not fit, or is never enough, or whose walk runs off the
+// head's end, goes the long way (the threshold descents below), which needs no room and no sort.
+#define SMP_CAP 4096               // candidates that fit (the reference's HEAD_CAP)
+#define SMP_KMAX 1024              // largest top-k selected this way: the k-th largest of the threads' maxima bounds the k-th largest of the row
+
+__device__ __forceinline__ float smp_key_value(unsigned k) { return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k); }
+
+// Put the n gathered (key, id) in order and keep the first `keep`: s_p[rank] = value, s_id[rank] = id.
+__device__ __forceinline__ void smp_order(const unsigned* c_key, const int* c_id, int n, int keep, float* s_p, int* s_id) {
+    for (int j = threadIdx.x; j < n; j += SMP_THREADS) {
+        const unsigned kj = c_key[j];
+        const int ij = c_id[j];
+        int rank = 0;
+        for (int i = 0; i < n; i++) rank += (c_key[i] > kj) || (c_key[i] == kj && c_id[i] < ij);
+        if (rank < keep) { s_p[rank] = smp_key_value(kj); s_id[rank] = ij; }
+    }
+    __syncthreads();
+}
+
+// `pick_scaled` on m candidates in order (values in s_p, overwritten by their probabilities).  norm_sum > 0: the
+// whole vocabulary's sum of exponentials, which then is the denominator.  Returns the pick, or -1 if the walk ran off
+// the end of a head (norm_sum > 0).  Divisions are spread over the threads; every sum runs in one thread, in order.
+__device__ int smp_pick_scaled(float* s_p, const int* s_id, int m, float norm_sum, float top_p, float min_p, float r, float* bc_f, int* bc_i) {
+    const int tid = threadIdx.x;
+    const float top = s_p[0];
+    __syncthreads();
+    for (int i = tid; i < m; i += SMP_THREADS) s_p[i] = expf(s_p[i] - top);
+    __syncthreads();
+    if (tid == 0) {
+        float sum = 0.f;
+        for (int i = 0; i < m; i++) sum += s_p[i];
+        *bc_f = norm_sum > 0.f ? norm_sum : sum;
+    }
+    __syncthreads();
+    for (int i = tid; i < m; i += SMP_THREADS) s_p[i] /= *bc_f;
+    __syncthreads();
+    int k = m;
+    if (top_p < 1.0f) {
+        if (tid == 0) {
+            float cum = 0.f;
+            int cut = k;
+            for (int i = 0; i < k; i++) { cum += s_p[i]; if (cum >= top_p) { cut = i + 1; break; } }
+            cum = 0.f;
+            for (int i = 0; i < cut; i++) cum += s_p[i];
+            *bc_i = cut; *bc_f = cum;
+        }
+        __syncthreads();
+        k = *bc_i;
+        for (int i = tid; i < k; i += SMP_THREADS) s_p[i] /= *bc_f;
+        __syncthreads();
+    }
+    if (min_p > 0.0f) {
+        if (tid == 0) {
+            const float floor_p = min_p * s_p[0];
+            int cut = k;
+            for (int i = 1; i < k; i++) if (s_p[i] < floor_p) { cut = i; break; }
+            float cum = 0.f;
+            for (int i = 0; i < cut; i++) cum += s_p[i];
+            *bc_i = cut; *bc_f = cum;
+        }
+        __syncthreads();
+        if (*bc_i < k) {
+            k = *bc_i;
+            for (int i = tid; i < k; i += SMP_THREADS) s_p[i] /= *bc_f;
+        }
+        __syncthreads();
+    }
+    if (tid == 0) {
+        float cum = 0.f;
+        int pick = s_id[k - 1];
+        bool hit = false;
+        for (int i = 0; i < k; i++) { cum += s_p[i]; if (r < cum) { pick = s_id[i]; hit = true; break; } }
+        *bc_i = (hit || norm_sum <= 0.f) ? pick : -1;
+    }
+    __syncthreads();
+    return *bc_i;
+}
+
 __global__ void __launch_bounds__(SMP_THREADS)
-k_sample(SampleArgs a, float* scratch /* [rows, V] scaled values, or null when nothing needs them */) {
+k_sample(SampleArgs a, float* scratch /* [rows, V] scaled values, or null when nothing needs them */, int shortcuts) {
     xr_pdl_launch();
+    extern __shared__ __align__(16) uint8_t smp_dyn[];          // short cuts: [SMP_CAP] keys, ids, values in order, ids in order; window bits
     __shared__ double sh[40 + SMP_THREADS];
     __shared__ float sh_f[33];
     __shared__ int sh_i[33];
@@ -248,6 +335,131 @@ k_sample(SampleArgs a, float* scratch /* [rows, V] scaled values, or null when n
     xr_pdl_wait();
 
     if (temp <= 0.f) { smp_argmax(lg, V, a.out + row, sh_f, sh_i); return; }
+
+    if (shortcuts) {
+        // Nothing is staged here: a pass reads the logits and works out each value again, logit -> penalised (once per
+        // occurrence in the window) -> / temp, the same operations in the same order as the staging below.
+        unsigned* c_key = (unsigned*)smp_dyn;
+        int* c_id = (int*)(c_key + SMP_CAP);
+        float* s_p = (float*)(c_id + SMP_CAP);
+        int* s_id = (int*)(s_p + SMP_CAP);
+        unsigned* in_window = (unsigned*)(s_id + SMP_CAP);          // one bit per token id: it is in the window of recent tokens
+        __shared__ int rec_s[SMP_RECENT];
+        __shared__ int n_cand, bc_i;
+        __shared__ unsigned bound;
+        __shared__ float bc_f;
+        const float pen = a.penalty[row];
+        const bool penalised = a.recent != nullptr && pen != 1.0f;
+        if (penalised) {
+            for (int w = tid; w < (V + 31) / 32; w += SMP_THREADS) in_window[w] = 0u;
+            if (tid < SMP_RECENT) rec_s[tid] = a.recent[(size_t)row * SMP_RECENT + tid];
+            __syncthreads();
+            if (tid < SMP_RECENT) { const int tok = rec_s[tid]; if (tok >= 0 && tok < V) atomicOr(&in_window[tok >> 5], 1u << (tok & 31)); }
+            __syncthreads();
+        }
+        auto value_of = [&](int i, float x) {
+            if (penalised && ((in_window[i >> 5] >> (i & 31)) & 1u)) {
+                int cnt = 0;
+                for (int j = 0; j < SMP_RECENT; j++) cnt += rec_s[j] == i;
+                for (int c = 0; c < cnt; c++) x = x > 0.f ? x / pen : x * pen;
+            }
+            return x / temp;
+        };
+        // The largest value.  Dividing by a positive temperature keeps the order, so outside the window the largest value
+        // is the largest logit's; the window's few tokens are worked out one by one.  A thread asks whether a token is
+        // in the window only when it would be the thread's new maximum.
+        auto in_win = [&](int i) { return penalised && ((in_window[i >> 5] >> (i & 31)) & 1u) != 0u; };
+        float traw = -INFINITY;                                     // this thread's largest logit outside the window
+        smp_for_each(lg, V, [&](int i, float x) { if (x > traw && !in_win(i)) traw = x; });
+        float wv = -INFINITY;                                       // this thread's window token, if it has one: its value
+        int wtok = -1;
+        if (penalised && tid < SMP_RECENT) {
+            const int tok = rec_s[tid];
+            if (tok >= 0 && tok < V) {
+                bool first = true;
+                for (int j = 0; j < tid; j++) first = first && rec_s[j] != tok;
+                if (first) { wtok = tok; wv = value_of(tok, lg[tok]); }
+            }
+        }
+        float mx = xr_warp_max(fmaxf(traw / temp, wv));
+        if ((tid & 31) == 0) sh_f[tid >> 5] = mx;
+        __syncthreads();
+        if (tid < 32) { float t = sh_f[tid]; t = xr_warp_max(t); if (tid == 0) sh_f[32] = t; }
+        __syncthreads();
+        mx = sh_f[32];
+        __syncthreads();
+        const int top_k = a.top_k[row];
+        const float top_p = a.top_p[row], min_p = a.min_p[row], r = a.draw[row];
+        int m = 0;                     // candidates in order, if a short cut applies
+        float norm_sum = 0.f;
+        if (top_k > 0 && top_k < V && top_k <= SMP_KMAX) {
+            // The k largest of the threads' maxima are k tokens outside the window: the k-th largest of them is a lower
+            // bound of the row's k-th largest value, and usually few values lie above it.  A logit a shade below the bound
+            // may still round to the bound's value when divided, and then its id decides: the comparison that costs
+            // nothing lets those through, the one on the values is exact.
+            unsigned* tm = (unsigned*)s_id;
+            tm[tid] = xr_key(traw);
+            if (tid == 0) n_cand = 0;
+            __syncthreads();
+            // (the maxima of the first 8 k threads will do: their k-th largest is a bound all the same, somewhat lower, and
+            // ranking a few hundred keys against each other is quick where ranking all 1,024 costs more than a pass)
+            const int ranked = min(SMP_THREADS, max(128, 8 * top_k));
+            if (tid < ranked) {
+                const unsigned my = tm[tid];
+                int rank = 0;
+                for (int j = 0; j < ranked; j++) rank += (tm[j] > my) || (tm[j] == my && j < tid);
+                if (rank == top_k - 1) bound = my;
+            }
+            __syncthreads();
+            const float bound_x = smp_key_value(bound);
+            const float lo = bound_x - fabsf(bound_x) * 1e-6f - 1e-30f;
+            const unsigned lowest = xr_key(bound_x / temp);
+            smp_for_each(lg, V, [&](int i, float x) {
+                if (x >= lo && !in_win(i)) {
+                    const unsigned k = xr_key(x / temp);
+                    if (k >= lowest) { const int at = atomicAdd(&n_cand, 1); if (at < SMP_CAP) { c_key[at] = k; c_id[at] = i; } }
+                }
+            });
+            if (wtok >= 0 && xr_key(wv) >= lowest) { const int at = atomicAdd(&n_cand, 1); if (at < SMP_CAP) { c_key[at] = xr_key(wv); c_id[at] = wtok; } }
+            __syncthreads();
+            const int nc = n_cand;
+            if (nc >= top_k && nc <= SMP_CAP) { smp_order(c_key, c_id, nc, top_k, s_p, s_id); m = top_k; }
+        } else if (!(top_k > 0 && top_k < V) && V >= 4096) {
+            // the whole mass and the first head in one pass; a head that is not enough costs a pass per loosening
+            float t_log = logf(1.0f / 1024.0f);
+            double total = 0.0;
+            for (int loosen = 0; loosen < 6; loosen++, t_log *= 4.f) {
+                if (tid == 0) n_cand = 0;
+                __syncthreads();
+                double head = 0.0, all = 0.0;
+                smp_for_each(lg, V, [&](int i, float x) {
+                    const float v = value_of(i, x);
+                    const float e = expf(v - mx);
+                    if (loosen == 0) all += (double)e;
+                    if (v - mx >= t_log) {
+                        const int at = atomicAdd(&n_cand, 1);
+                        if (at < SMP_CAP) { c_key[at] = xr_key(v); c_id[at] = i; }
+                        head += (double)e;
+                    }
+                });
+                if (loosen == 0) total = blk_sum_d(all, sh);
+                head = blk_sum_d(head, sh);
+                const int nc = n_cand;
+                if (nc > SMP_CAP) break;                           // the head is too broad
+                const bool enough = top_p < 1.0f ? head >= (double)top_p * total
+                                  : (min_p > 0.0f ? t_log <= logf(min_p) : head > (double)r * total);
+                if (!enough) { __syncthreads(); continue; }
+                smp_order(c_key, c_id, nc, nc, s_p, s_id);
+                m = nc; norm_sum = (float)total;
+                break;
+            }
+        }
+        if (m > 0) {
+            const int pick = smp_pick_scaled(s_p, s_id, m, norm_sum, top_p, min_p, r, &bc_f, &bc_i);
+            if (pick >= 0) { if (tid == 0) a.out[row] = pick; return; }
+        }
+        __syncthreads();
+    }
 
     // Stage the row: copy, penalise the recent tokens (once per occurrence in the window, as the
     // reference's loop does, src/sample.c:148-166), then scale by 1/temp.  Later passes read the
@@ -284,8 +496,8 @@ k_sample(SampleArgs a, float* scratch /* [rows, V] scaled values, or null when n
     mx = sh_f[32];
     __syncthreads();
 
-    Cut cut{0u, -1};               // everything survives
     int top_k = a.top_k[row];
+    Cut cut{0u, -1};               // everything survives
     // ---- top-k: the k-th largest key by descending over the key bits with counts ----
     if (top_k > 0 && top_k < V) {
         unsigned thr = 0;
@@ -842,14 +1054,29 @@ XR_EXPORT int xr_logprob(const float* logits, long long ld, int rows, int V, con
 }
 
 // scratch: [rows, V] floats when any row has temp > 0 (may be null when all rows are greedy).
+static int launch_sample_block(const SampleArgs& a, int rows, float* scratch, int shortcuts, cudaStream_t stream) {
+    // candidates (keys, ids, values in order, ids in order) and one bit per token id for the window of recent tokens
+    constexpr int DYN_MAX = 160 * 1024;
+    const long long dyn = (long long)SMP_CAP * 16 + ((long long)(a.V + 31) / 32) * 4;
+    if (dyn > DYN_MAX) shortcuts = 0;                               // (a vocabulary of more than 786,432: the long way)
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(k_sample, cudaFuncAttributeMaxDynamicSharedMemorySize, DYN_MAX) != cudaSuccess) return XR_ERR_LAUNCH;
+        configured = true;
+    }
+    xr_launch(k_sample, dim3(rows), dim3(SMP_THREADS), shortcuts ? (size_t)dyn : 0, stream, a, scratch, shortcuts ? 1 : 0);
+    return xr_launch_status();
+}
+
+// shortcuts: take the reference's short cuts (one block a row); 0: the threshold descents only, a cluster of eight
+// blocks a row when the rows are few.
 XR_EXPORT int xr_sample(const float* logits, long long ld, int rows, int V, const float* temp, const int* top_k,
                         const float* top_p, const float* min_p, const float* penalty, const float* draw,
-                        const int* recent, float* scratch, int* out, cudaStream_t stream) {
+                        const int* recent, float* scratch, int* out, int shortcuts, cudaStream_t stream) {
     if (rows < 1 || V < 1 || ld < V) return XR_ERR_ARG;
     SampleArgs a{logits, ld, V, temp, top_k, top_p, min_p, penalty, draw, recent, out};
-    if (smp_use_cluster(rows, V)) return launch_sample_cluster(a, rows, stream);
-    xr_launch(k_sample, dim3(rows), dim3(SMP_THREADS), 0, stream, a, scratch);
-    return xr_launch_status();
+    if (!shortcuts && smp_use_cluster(rows, V)) return launch_sample_cluster(a, rows, stream);
+    return launch_sample_block(a, rows, scratch, shortcuts, stream);
 }
 
 // The one-block kernel whatever the width (what xr_sample falls back to; tests compare the two).
@@ -858,6 +1085,5 @@ XR_EXPORT int xr_sample_one_block(const float* logits, long long ld, int rows, i
                                   const int* recent, float* scratch, int* out, cudaStream_t stream) {
     if (rows < 1 || V < 1 || ld < V) return XR_ERR_ARG;
     SampleArgs a{logits, ld, V, temp, top_k, top_p, min_p, penalty, draw, recent, out};
-    xr_launch(k_sample, dim3(rows), dim3(SMP_THREADS), 0, stream, a, scratch);
-    return xr_launch_status();
+    return launch_sample_block(a, rows, scratch, 0, stream);
 }

@@ -65,7 +65,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "xr_attention_wait_probe": [_vp, _vp, ctypes.c_uint, _vp],
         "xr_attention_tc_supported": [_i, _i, _i, _i],
         "xr_attention_tc": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _ll, _ll, _i, _i, _vp],
-        "xr_sample": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
+        "xr_sample": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp],
         "xr_sample_one_block": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
         "xr_logprob": [_vp, _ll, _i, _i, _vp, _vp, _vp],
         "xr_random_normal": [_vp, _i, _ll, ctypes.c_ulonglong, ctypes.c_ulonglong, _f, _f, _vp],
@@ -209,20 +209,26 @@ def attention_simt(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, cache_
 
 
 def sample(logits: torch.Tensor, temp, top_k, top_p, min_p, penalty, draw, recent: Optional[torch.Tensor],
-           scratch: torch.Tensor, out: torch.Tensor, any_sampled: bool = True, one_block: bool = False) -> None:
+           scratch: torch.Tensor, out: torch.Tensor, any_sampled: bool = True, one_block: bool = False,
+           shortcuts: bool = True) -> None:
     """One token per row of float32 logits by the reference's sampling chain (see csrc/sampling.cu).
-    `scratch` must hold rows * vocab floats unless every row is greedy (`any_sampled` False).  Rows of more than
-    1,024 values are spread over a cluster of eight blocks each; `one_block` asks for the one-block kernel."""
+    `scratch` must hold rows * vocab floats unless every row is greedy (`any_sampled` False).  `shortcuts` (the
+    default): one block a row that selects the top-k, or gathers the head of the distribution, sorts that and walks
+    it as the reference does, and goes the long way only where that does not apply.  Without: the long way for every
+    row, by threshold descents that never sort, spread over a cluster of eight blocks a row when the rows are few
+    and have more than 1,024 values (`one_block`: in one block whatever the width)."""
     _dev(temp, top_k, top_p, min_p, penalty, draw, recent, scratch, out)
     rows, V = logits.shape
     assert logits.dtype == torch.float32 and logits.stride(1) == 1
     assert not any_sampled or scratch.numel() >= rows * V
     assert out.dtype == torch.int32 and top_k.dtype == torch.int32
     # (rows that are all greedy are one argmax each: nothing for a cluster to share)
-    fn = lib().xr_sample_one_block if (one_block or not any_sampled) else lib().xr_sample
-    _check(fn(logits.data_ptr(), logits.stride(0), rows, V, temp.data_ptr(), top_k.data_ptr(),
-              top_p.data_ptr(), min_p.data_ptr(), penalty.data_ptr(), draw.data_ptr(), _ptr(recent),
-              scratch.data_ptr(), out.data_ptr(), _stream()), "sample")
+    args = (logits.data_ptr(), logits.stride(0), rows, V, temp.data_ptr(), top_k.data_ptr(), top_p.data_ptr(), min_p.data_ptr(),
+            penalty.data_ptr(), draw.data_ptr(), _ptr(recent), scratch.data_ptr(), out.data_ptr())
+    if one_block or not any_sampled:
+        _check(lib().xr_sample_one_block(*args, _stream()), "sample")
+    else:
+        _check(lib().xr_sample(*args, int(shortcuts), _stream()), "sample")
     _count()
 
 

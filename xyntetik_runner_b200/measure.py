@@ -139,7 +139,7 @@ def spread_lengths(batch: int, context: int, portion: int = 1):
 
 
 def time_sampling(rows: int, vocab: int, setting: str = "greedy", iters: int = 20, plain: bool = False, one_block: bool = False,
-                  device: str = "cuda:0") -> float:
+                  device: str = "cuda:0", shortcuts: bool = True) -> float:
     dev = torch.device(device)
     settings = {"greedy": (0.0, 0, 1.0, 0.0, 1.0), "temperature": (0.8, 0, 1.0, 0.0, 1.0), "top-k 40": (0.8, 40, 1.0, 0.0, 1.0),
                 "top-k 40, top-p 0.95": (0.8, 40, 0.95, 0.0, 1.0), "top-k 40, top-p 0.95, min-p 0.05, penalty 1.1": (0.8, 40, 0.95, 0.05, 1.1)}
@@ -151,7 +151,7 @@ def time_sampling(rows: int, vocab: int, setting: str = "greedy", iters: int = 2
     recent = torch.full((rows, 256), -1, dtype=torch.int32, device=dev)
     recent[:, :40] = torch.randint(0, vocab, (rows, 40), dtype=torch.int32, device=dev)
     args = (logits, full(temp), full(k, torch.int32), full(p), full(m), full(pen), full(0.37), recent, scratch, out)
-    return time_replayed(lambda i: kernels.sample(*args, any_sampled=temp > 0, one_block=one_block), iters, plain)
+    return time_replayed(lambda i: kernels.sample(*args, any_sampled=temp > 0, one_block=one_block, shortcuts=shortcuts), iters, plain)
 
 
 SAMPLING_SETTINGS = ("greedy", "temperature", "top-k 40", "top-k 40, top-p 0.95", "top-k 40, top-p 0.95, min-p 0.05, penalty 1.1")
