@@ -222,7 +222,7 @@ def one_kernel(args) -> int:
               f"{sum(lengths) * K * hd * 4 / us / 1e3:.0f} GB/s of keys+values, {flops / us / 1e6:.1f} TFLOP/s")
     else:
         for name in measure.SAMPLING_SETTINGS:
-            us = measure.time_sampling(args.sample_rows, args.vocab, name, it, plain, args.one_block, shortcuts=not args.long_way)
+            us = measure.time_sampling(args.sample_rows, args.vocab, name, it, plain, args.one_block, shortcuts=not args.long_way, flat=args.flat)
             print(f"sample rows={args.sample_rows} vocab={args.vocab} {name}: {us:.1f} us")
     return 0
 
@@ -340,7 +340,7 @@ def main() -> int:
                                ("vocab", int, 128256), ("iters", int, 20), ("sample-rows", int, 8)):
         ap.add_argument(f"--{name}", type=typ, default=default, help=argparse.SUPPRESS)
     ap.add_argument("--epilogue", choices=["store", "add", "swiglu"], default="store", help=argparse.SUPPRESS)
-    for name in ("plain", "no-tc", "no-tma", "one-block", "spread", "mixed", "long-way"):
+    for name in ("plain", "no-tc", "no-tma", "one-block", "spread", "mixed", "long-way", "flat"):
         ap.add_argument(f"--{name}", action="store_true", help=argparse.SUPPRESS)
     args = ap.parse_args()
     if args.gpus != 1:
