@@ -142,10 +142,13 @@ def test_callback_ends_a_request(folders):
     r.engine.cache.audit()
 
 
-@pytest.mark.parametrize("temp", [0.0, 0.9])
-def test_steps_launched_ahead_give_the_same_tokens(folders, temp):
+@pytest.mark.parametrize("temp,penalty", [(0.0, 1.0), (0.9, 1.0), (1.4, 1.5)])
+def test_steps_launched_ahead_give_the_same_tokens(folders, temp, penalty):
     """Decode steps launched before the tokens of the step ahead of them are read (the device feeds the sampled ids
-    on) against the same run one step at a time: requests of different lengths, one that meets a stop token."""
+    on) against the same run one step at a time: requests of different lengths, one that meets a stop token.  With
+    a repeat penalty the window of recent tokens lacks, on the host, the token that is still on the device: the kernel
+    puts it in (unless it is one of the request's stop ids, which a window never holds: the last request goes on
+    after its stop ids with `ignore_eos`)."""
     from xyntetik_runner_b200.engine.runner import Runner
     folder = folders["B", "float32"]
     prompts = [traces.random_tokens(60 + i, n, 387) for i, n in enumerate((7, 19, 3, 12))]
@@ -154,7 +157,8 @@ def test_steps_launched_ahead_give_the_same_tokens(folders, temp):
     def run(ahead, stop):
         r = Runner(folder, dtype="float32", ctx=128, parallel=4, page_size=8)
         r.scheduler.params.look_ahead = ahead
-        ids = [r.submit(p, n=n, temp=temp, seed=5 + i, stop_ids=stop if i == 2 else [], ignore_eos=False)
+        ids = [r.submit(p, n=n, temp=temp, seed=5 + i, stop_ids=stop if i == 2 else (frequent if i == 3 else []),
+                        ignore_eos=i == 3, repeat_penalty=penalty)
                for i, (p, n) in enumerate(zip(prompts, lengths))]
         while r.scheduler.has_work():
             r.scheduler.step()
@@ -163,8 +167,10 @@ def test_steps_launched_ahead_give_the_same_tokens(folders, temp):
         done = [r.scheduler.finished[i] for i in ids]
         return [q.generated for q in done], [q.finish_reason for q in done], r.scheduler.stats["steps_launched_ahead"]
 
+    frequent = []
     free, _, n_ahead = run(False, [])
     assert n_ahead == 0 and [len(g) for g in free] == lengths
+    frequent = sorted(set(free[3]))[:5]                 # ids that the last request emits: exempt from its penalty from now on
     stop = [free[2][10]]
     want, reasons, _ = run(False, stop)
     assert reasons[2] == "stop" and want[2] == free[2][:free[2].index(stop[0])]

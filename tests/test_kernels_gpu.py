@@ -717,3 +717,48 @@ def test_sampling_kernel_follows_the_distribution():
     assert set(got.tolist()) <= set(order.tolist())
     freq = np.array([(got == t).mean() for t in order])
     assert np.abs(freq - p).max() < 4 * np.sqrt(0.25 / n)
+
+
+@pytest.mark.parametrize("shortcuts", [True, False])
+def test_sampling_with_a_window_token_that_is_still_on_the_device(shortcuts):
+    """A step queued before the host has read the step before it: the window of recent tokens that the host sends lacks
+    one token, which lies in the array of sampled ids on the device.  The kernel puts it into the entry the host names,
+    unless it is one of the row's exempt ids; the picks are those of the complete window."""
+    from xyntetik_runner_b200 import kernels
+    rng = np.random.RandomState(5)
+    rows, V = 12, 5003
+    logits = (rng.randn(rows, V) * 2).astype(np.float32)
+    f = lambda a: torch.tensor(a, dtype=torch.float32, device=DEV)
+    temp, top_k, top_p, min_p, pen = [0.9] * rows, [0, 40, 7] * 4, [0.9, 1.0] * 6, [0.0] * rows, [1.6, 0.7, 1.0] * 4
+    draws = [float(np.float32(x)) for x in rng.rand(rows)]
+    complete = np.full((rows, 256), -1, dtype=np.int32)
+    partial, pending = complete.copy(), np.full((rows, 3), -1, dtype=np.int32)
+    exempt = np.full((rows, kernels.EXEMPT_IDS), -1, dtype=np.int32)
+    feed = rng.randint(0, V, size=64).astype(np.int32)
+    for r in range(rows):
+        n = int(rng.randint(3, 250))
+        best = np.argsort(-logits[r])[:6]
+        complete[r, :n] = rng.choice(np.concatenate([best, rng.randint(0, V, size=20)]), size=n)
+        partial[r] = complete[r]
+        if r % 4 != 3:                                     # (every fourth row: nothing is pending)
+            slot, j = int(rng.randint(0, 256)), int(rng.randint(0, 64))
+            feed[j] = best[r % 6]                          # the token on the device is one of the likeliest: it matters
+            partial[r, slot] = int(rng.randint(0, V))      # what the host has there is the entry's old content
+            complete[r, slot] = feed[j]
+            pending[r] = (j, slot, 0)
+            if r % 4 == 2:                                 # ... and here it is exempt: the complete window has no entry for it
+                exempt[r, :3] = (int(rng.randint(0, V)), feed[j], 11)
+                pending[r, 2] = 3
+                complete[r, slot] = -1
+    outs = []
+    for window, pend in ((complete, None), (partial, pending)):
+        out = torch.full((rows,), -7, dtype=torch.int32, device=DEV)
+        scratch = torch.empty(rows * V, dtype=torch.float32, device=DEV)
+        i32 = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+        kernels.sample(torch.from_numpy(logits).to(DEV), f(temp), torch.tensor(top_k, dtype=torch.int32, device=DEV), f(top_p), f(min_p),
+                       f(pen), f(draws), i32(window), scratch, out, shortcuts=shortcuts,
+                       pending=None if pend is None else i32(pend), feed=None if pend is None else i32(feed),
+                       exempt=None if pend is None else i32(exempt))
+        outs.append(out.cpu().tolist())
+    assert outs[0] == outs[1]
+    assert len(set(outs[0])) > 3 and min(outs[0]) >= 0

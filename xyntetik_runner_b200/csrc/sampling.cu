@@ -24,6 +24,7 @@
 
 #define SMP_THREADS 1024
 #define SMP_RECENT 256
+#define SMP_EXEMPT 8          // ids per row that the window never holds
 
 struct SampleArgs {
     const float* logits;      // [rows, ld]
@@ -37,7 +38,25 @@ struct SampleArgs {
     const float* draw;        // r per row
     const int* recent;        // [rows, SMP_RECENT], entries < 0 are empty
     int* out;                 // [rows]
+    // A step may be queued before the host has read the token that the step before it sampled.  That token belongs in
+    // the window all the same: pending[3 row] is where it lies in `feed` (or -1: the window is complete),
+    // pending[3 row + 1] the window entry it takes, pending[3 row + 2] how many of exempt[SMP_EXEMPT row ..] count:
+    // ids that the window never holds (src/sample.c:159-162), which the host cannot strike out of a token it has not seen.
+    const int* pending;       // [rows, 3] or null
+    const int* feed;
+    const int* exempt;        // [rows, SMP_EXEMPT]
 };
+
+// Entry j of a row's window of recent tokens.
+__device__ __forceinline__ int smp_window_entry(const SampleArgs& a, int row, int j) {
+    int tok = a.recent[(size_t)row * SMP_RECENT + j];
+    if (a.pending != nullptr && a.pending[3 * row] >= 0 && a.pending[3 * row + 1] == j) {
+        tok = a.feed[a.pending[3 * row]];
+        for (int e = 0; e < a.pending[3 * row + 2] && e < SMP_EXEMPT; e++)
+            if (a.exempt[row * SMP_EXEMPT + e] == tok) tok = -1;
+    }
+    return tok;
+}
 
 __device__ __forceinline__ unsigned xr_key(float v) {
     unsigned u = __float_as_uint(v);
@@ -352,7 +371,7 @@ k_sample(SampleArgs a, float* scratch /* [rows, V] scaled values, or null when n
         const bool penalised = a.recent != nullptr && pen != 1.0f;
         if (penalised) {
             for (int w = tid; w < (V + 31) / 32; w += SMP_THREADS) in_window[w] = 0u;
-            if (tid < SMP_RECENT) rec_s[tid] = a.recent[(size_t)row * SMP_RECENT + tid];
+            if (tid < SMP_RECENT) rec_s[tid] = smp_window_entry(a, row, tid);
             __syncthreads();
             if (tid < SMP_RECENT) { const int tok = rec_s[tid]; if (tok >= 0 && tok < V) atomicOr(&in_window[tok >> 5], 1u << (tok & 31)); }
             __syncthreads();
@@ -468,16 +487,20 @@ k_sample(SampleArgs a, float* scratch /* [rows, V] scaled values, or null when n
     smp_for_each(lg, V, [&](int i, float v) { vals[i] = v; });
     __syncthreads();
     float pen = a.penalty[row];
-    if (a.recent != nullptr && pen != 1.0f && tid < SMP_RECENT) {
-        const int* rec = a.recent + (size_t)row * SMP_RECENT;
-        int tok = rec[tid];
-        if (tok >= 0 && tok < V) {
-            bool first = true; int cnt = 0;
-            for (int j = 0; j < SMP_RECENT; j++) { if (rec[j] == tok) { cnt++; if (j < tid) first = false; } }
-            if (first) {
-                float x = vals[tok];
-                for (int c = 0; c < cnt; c++) x = x > 0.f ? x / pen : x * pen;
-                vals[tok] = x;
+    if (a.recent != nullptr && pen != 1.0f) {
+        __shared__ int rec[SMP_RECENT];
+        if (tid < SMP_RECENT) rec[tid] = smp_window_entry(a, row, tid);
+        __syncthreads();
+        if (tid < SMP_RECENT) {
+            int tok = rec[tid];
+            if (tok >= 0 && tok < V) {
+                bool first = true; int cnt = 0;
+                for (int j = 0; j < SMP_RECENT; j++) { if (rec[j] == tok) { cnt++; if (j < tid) first = false; } }
+                if (first) {
+                    float x = vals[tok];
+                    for (int c = 0; c < cnt; c++) x = x > 0.f ? x / pen : x * pen;
+                    vals[tok] = x;
+                }
             }
         }
     }
@@ -795,15 +818,18 @@ k_sample_cluster(SampleArgs a) {
     // ---- repeat penalty, once per occurrence in the window (src/sample.c:148-166) ----
     const float pen = a.penalty[row];
     if (a.recent != nullptr && pen != 1.0f) {
+        if (tid < SMP_RECENT) rec_tok[tid] = smp_window_entry(a, row, tid);
+        __syncthreads();
+        int mine = -1, cnt = 0;
         if (tid < SMP_RECENT) {
-            const int* rec = a.recent + (size_t)row * SMP_RECENT;
-            int tok = rec[tid];
-            bool first = tok >= 0 && tok < V; int cnt = 0;
+            const int tok = rec_tok[tid];
+            bool first = tok >= 0 && tok < V;
             if (first)
-                for (int j = 0; j < SMP_RECENT; j++) { if (rec[j] == tok) { cnt++; if (j < tid) first = false; } }
-            rec_tok[tid] = first ? tok : -1;
-            rec_cnt[tid] = cnt;
+                for (int j = 0; j < SMP_RECENT; j++) { if (rec_tok[j] == tok) { cnt++; if (j < tid) first = false; } }
+            mine = first ? tok : -1;
         }
+        __syncthreads();
+        if (tid < SMP_RECENT) { rec_tok[tid] = mine; rec_cnt[tid] = cnt; }
         __syncthreads();
         for (int e = 0; e < SMP_RECENT; e++) {
             const int off = rec_tok[e] - base;
@@ -1072,9 +1098,11 @@ static int launch_sample_block(const SampleArgs& a, int rows, float* scratch, in
 // blocks a row when the rows are few.
 XR_EXPORT int xr_sample(const float* logits, long long ld, int rows, int V, const float* temp, const int* top_k,
                         const float* top_p, const float* min_p, const float* penalty, const float* draw,
-                        const int* recent, float* scratch, int* out, int shortcuts, cudaStream_t stream) {
+                        const int* recent, float* scratch, int* out, int shortcuts, const int* pending, const int* feed,
+                        const int* exempt, cudaStream_t stream) {
     if (rows < 1 || V < 1 || ld < V) return XR_ERR_ARG;
-    SampleArgs a{logits, ld, V, temp, top_k, top_p, min_p, penalty, draw, recent, out};
+    if (pending != nullptr && (feed == nullptr || exempt == nullptr || recent == nullptr)) return XR_ERR_ARG;
+    SampleArgs a{logits, ld, V, temp, top_k, top_p, min_p, penalty, draw, recent, out, pending, feed, exempt};
     if (!shortcuts && smp_use_cluster(rows, V)) return launch_sample_cluster(a, rows, stream);
     return launch_sample_block(a, rows, scratch, shortcuts, stream);
 }
@@ -1084,6 +1112,6 @@ XR_EXPORT int xr_sample_one_block(const float* logits, long long ld, int rows, i
                                   const float* top_p, const float* min_p, const float* penalty, const float* draw,
                                   const int* recent, float* scratch, int* out, cudaStream_t stream) {
     if (rows < 1 || V < 1 || ld < V) return XR_ERR_ARG;
-    SampleArgs a{logits, ld, V, temp, top_k, top_p, min_p, penalty, draw, recent, out};
+    SampleArgs a{logits, ld, V, temp, top_k, top_p, min_p, penalty, draw, recent, out, nullptr, nullptr, nullptr};
     return launch_sample_block(a, rows, scratch, 0, stream);
 }

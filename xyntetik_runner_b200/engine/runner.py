@@ -43,10 +43,15 @@ class EngineExecutor:
     of every step stay in one device array (`feed`), so that the step after it can be launched before the host
     has read them: an entry whose token is the scheduler's IN_FLIGHT mark is fed row `feed_rows[request]` of it."""
 
+    # A request whose sampling penalises recent tokens can be stepped ahead all the same: the token that is still on the
+    # device is put into its window there (DeviceSampler.pick, in_flight=).
+    windows_on_device = True
+
     def __init__(self, engine: Engine):
         self.engine = engine
         self.sampler = DeviceSampler(engine.device)
         self.feed = torch.zeros(max(engine.params.max_requests, 1), dtype=torch.int32, device=engine.device)
+        self.picked = torch.zeros_like(self.feed)       # where a step's tokens go first when its sampling reads `feed`
         self._host = [torch.empty(self.feed.numel(), dtype=torch.int32).pin_memory() for _ in range(3)]
         self._next = 0
 
@@ -67,7 +72,12 @@ class EngineExecutor:
             if not wanting:
                 step = InFlight([], None, None)
             else:
-                ids = self.sampler.pick(logits, [r.sampler for r in wanting], out=self.feed)
+                in_flight = [feed_rows.get(r.id, -1) if feed_rows is not None else -1 for r in wanting]
+                if any(j >= 0 and r.sampler.needs_window() for j, r in zip(in_flight, wanting)):
+                    ids = self.sampler.pick(logits, [r.sampler for r in wanting], out=self.picked, in_flight=in_flight, feed=self.feed)
+                    self.feed[:len(wanting)].copy_(ids)
+                else:
+                    ids = self.sampler.pick(logits, [r.sampler for r in wanting], out=self.feed)
                 host = self._host[self._next]
                 self._next = (self._next + 1) % len(self._host)
                 host[:len(wanting)].copy_(ids, non_blocking=True)                       # device -> host

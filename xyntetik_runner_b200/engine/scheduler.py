@@ -422,8 +422,8 @@ class Scheduler:
         gets a token decodes one more (the device feeds it the token itself), waiting requests are admitted by the
         slots and pages that are free now.  A request that reaches its length with this step's token is known to
         end and is left out; one that meets a stop token is not, and has one row computed for nothing.  Not planned
-        ahead: a step whose sampling needs the token on the host (a repeat-penalty window), and a step that would have
-        to preempt or end a request (``plan`` decides that with the outcome in hand).  On success the tokens to come
+        ahead: a step whose sampling needs the token on the host (a repeat-penalty window with an executor that cannot
+        complete it on the device), and a step that would have to preempt or end a request (``plan`` decides that with the outcome in hand).  On success the tokens to come
         stand in their requests as IN_FLIGHT marks and the next step's pages are reserved; else nothing is changed."""
         limit = self.cache.max_pages_per_request * self.cache.page_size
         ending = []
@@ -432,7 +432,7 @@ class Scheduler:
             if r.status != LIVE:
                 return None                  # it ended in the step before this one: let the queue settle first
             if e.wants_token:
-                if r.sampler.needs_window():
+                if r.sampler.needs_window() and not (getattr(self.executor, "windows_on_device", False) and r.sampler.window_on_device_ok()):
                     return None
                 if 0 < r.max_new_tokens <= len(r.generated) + 1 or len(r.tokens) + 1 >= limit:
                     ending.append(r)

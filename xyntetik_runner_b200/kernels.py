@@ -65,7 +65,7 @@ def _declare(L: ctypes.CDLL) -> None:
         "xr_attention_wait_probe": [_vp, _vp, ctypes.c_uint, _vp],
         "xr_attention_tc_supported": [_i, _i, _i, _i],
         "xr_attention_tc": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _i, _i, _i, _i, _i, _i, _i, _i, _f, _i, _ll, _ll, _i, _i, _vp],
-        "xr_sample": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp],
+        "xr_sample": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp],
         "xr_sample_one_block": [_vp, _ll, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
         "xr_logprob": [_vp, _ll, _i, _i, _vp, _vp, _vp],
         "xr_random_normal": [_vp, _i, _ll, ctypes.c_ulonglong, ctypes.c_ulonglong, _f, _f, _vp],
@@ -208,15 +208,23 @@ def attention_simt(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, cache_
     _count()
 
 
+EXEMPT_IDS = 8          # ids per row that a penalty window never holds, as the sampling kernel takes them
+
+
 def sample(logits: torch.Tensor, temp, top_k, top_p, min_p, penalty, draw, recent: Optional[torch.Tensor],
            scratch: torch.Tensor, out: torch.Tensor, any_sampled: bool = True, one_block: bool = False,
-           shortcuts: bool = True) -> None:
+           shortcuts: bool = True, pending: Optional[torch.Tensor] = None, feed: Optional[torch.Tensor] = None,
+           exempt: Optional[torch.Tensor] = None) -> None:
     """One token per row of float32 logits by the reference's sampling chain (see csrc/sampling.cu).
     `scratch` must hold rows * vocab floats unless every row is greedy (`any_sampled` False).  `shortcuts` (the
     default): one block a row that selects the top-k, or gathers the head of the distribution, sorts that and walks
     it as the reference does, and goes the long way only where that does not apply.  Without: the long way for every
     row, by threshold descents that never sort, spread over a cluster of eight blocks a row when the rows are few
-    and have more than 1,024 values (`one_block`: in one block whatever the width)."""
+    and have more than 1,024 values (`one_block`: in one block whatever the width).
+    `pending` (int32 [rows, 3]) with `feed` and `exempt` (int32 [rows, EXEMPT_IDS]): row r's window lacks the token that
+    the step before sampled and the host has not read yet; it is feed[pending[r, 0]] (-1: the window is complete),
+    takes window entry pending[r, 1], and is left out if it is among the first pending[r, 2] ids of exempt[r].
+    `out` must not be `feed` then."""
     _dev(temp, top_k, top_p, min_p, penalty, draw, recent, scratch, out)
     rows, V = logits.shape
     assert logits.dtype == torch.float32 and logits.stride(1) == 1
@@ -225,10 +233,15 @@ def sample(logits: torch.Tensor, temp, top_k, top_p, min_p, penalty, draw, recen
     # (rows that are all greedy are one argmax each: nothing for a cluster to share)
     args = (logits.data_ptr(), logits.stride(0), rows, V, temp.data_ptr(), top_k.data_ptr(), top_p.data_ptr(), min_p.data_ptr(),
             penalty.data_ptr(), draw.data_ptr(), _ptr(recent), scratch.data_ptr(), out.data_ptr())
+    if pending is not None:
+        _dev(pending, feed, exempt)
+        assert pending.dtype == torch.int32 and pending.numel() >= 3 * rows and exempt.dtype == torch.int32
+        assert exempt.numel() >= EXEMPT_IDS * rows and feed.dtype == torch.int32 and recent is not None
+        assert out.data_ptr() != feed.data_ptr() and any_sampled and not one_block
     if one_block or not any_sampled:
         _check(lib().xr_sample_one_block(*args, _stream()), "sample")
     else:
-        _check(lib().xr_sample(*args, int(shortcuts), _stream()), "sample")
+        _check(lib().xr_sample(*args, int(shortcuts), _ptr(pending), _ptr(feed), _ptr(exempt), _stream()), "sample")
     _count()
 
 

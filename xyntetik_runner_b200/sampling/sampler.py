@@ -75,6 +75,10 @@ class RequestSampler:
     def needs_window(self) -> bool:
         return self.params.temperature > 0 and self.params.repeat_penalty != 1.0
 
+    def window_on_device_ok(self) -> bool:
+        """The token that is still on the device can be put into the window there (the kernel takes a few exempt ids)."""
+        return len(self.no_penalty) <= kernels.EXEMPT_IDS
+
     def window(self) -> np.ndarray:
         w = self.recent.copy()
         for t in self.no_penalty:
@@ -90,9 +94,12 @@ class DeviceSampler:
         self._scratch: Optional[torch.Tensor] = None
         self._greedy: dict = {}          # rows -> parameter tensors of an all-greedy batch (they never change)
 
-    def pick(self, logits: torch.Tensor, samplers: List[RequestSampler], out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def pick(self, logits: torch.Tensor, samplers: List[RequestSampler], out: Optional[torch.Tensor] = None,
+             in_flight: Optional[List[int]] = None, feed: Optional[torch.Tensor] = None) -> torch.Tensor:
         """logits: float32 [rows, vocab] on the device, one RequestSampler per row (each makes its
-        draw here).  Returns int32 [rows] on the device (`out`, if given: int32, at least `rows` long)."""
+        draw here).  Returns int32 [rows] on the device (`out`, if given: int32, at least `rows` long).
+        in_flight[i] >= 0: row i's request got a token in the step before that the host has not read; it is
+        feed[in_flight[i]] and belongs in the row's penalty window, where the kernel puts it (`out` is not `feed` then)."""
         rows, V = logits.shape
         assert rows == len(samplers)
         if out is not None:
@@ -124,13 +131,23 @@ class DeviceSampler:
                 any_window |= s.needs_window()
         fd = torch.from_numpy(f).to(self.device, non_blocking=True)
         kd = torch.from_numpy(k).to(self.device, non_blocking=True)
-        recent = None
+        recent = pending = exempt = None
         if any_window:
             recent = torch.from_numpy(np.stack([s.window() for s in samplers])).to(self.device, non_blocking=True)
+            if in_flight is not None and any(j >= 0 and s.needs_window() for j, s in zip(in_flight, samplers)):
+                pend = np.full((rows, 3), -1, dtype=np.int32)
+                exm = np.full((rows, kernels.EXEMPT_IDS), -1, dtype=np.int32)
+                for i, (j, s) in enumerate(zip(in_flight, samplers)):
+                    if j >= 0 and s.needs_window():
+                        pend[i] = (j, s.head, len(s.no_penalty))
+                        exm[i, :len(s.no_penalty)] = s.no_penalty
+                pending = torch.from_numpy(pend).to(self.device, non_blocking=True)
+                exempt = torch.from_numpy(exm).to(self.device, non_blocking=True)
         need = rows * V if any_sampled else 1
         if self._scratch is None or self._scratch.numel() < need:
             self._scratch = torch.empty(need, dtype=torch.float32, device=self.device)
         if out is None:
             out = torch.empty(rows, dtype=torch.int32, device=self.device)
-        kernels.sample(logits, fd[0], kd, fd[1], fd[2], fd[3], fd[4], recent, self._scratch, out, any_sampled)
+        kernels.sample(logits, fd[0], kd, fd[1], fd[2], fd[3], fd[4], recent, self._scratch, out, any_sampled,
+                       pending=pending, feed=feed if pending is not None else None, exempt=exempt)
         return out
