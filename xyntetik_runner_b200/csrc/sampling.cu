@@ -1,8 +1,9 @@
-// Picking the next token from float32 logits on the device: one block per row (k_sample: the reference's short cuts
-// first -- top-k by selection, else the head of the distribution -- and threshold descents where they do not apply);
-// the descents alone spread over a cluster of eight blocks per row that keeps the row in registers, for rows of more
-// than 1,024 values and few rows (k_sample_cluster, further down; serving does not take it, tests and measurements
-// do); and the log-probability of a given token per row (k_logprob, at the end).
+// Picking the next token from float32 logits on the device, in two launches: the reference's short cuts, one block per
+// row (k_sample with shortcuts: top-k by selection, else the head of the distribution), then, for the rows they left
+// open (usually none: the launch then reads a word a row and ends), the long way by threshold descents -- spread over a
+// cluster of eight blocks per row that keeps the row in registers when the rows are few and have more than 1,024
+// values (k_sample_cluster, further down), else one block per row.  And the log-probability of a given token per row
+// (k_logprob, at the end).
 //
 // The chain is the reference's `sample_pick` (src/sample.c:141-329) with
 // `pick_scaled` (src/sample.c:86-127):
@@ -45,6 +46,10 @@ struct SampleArgs {
     const int* pending;       // [rows, 3] or null
     const int* feed;
     const int* exempt;        // [rows, SMP_EXEMPT]
+    // Rows that the short cuts left open: row r is wanted iff todo[r * todo_stride] != 0 (null: every row).  The kernel of
+    // the short cuts writes these words, the kernels of the long way only read them.
+    const int* todo;
+    long long todo_stride;
 };
 
 // Entry j of a row's window of recent tokens.
@@ -262,8 +267,10 @@ __device__ __forceinline__ void smp_argmax(const float* lg, int V, int* out, flo
 // `pick_scaled` (src/sample.c:86-127) in float32, one after the other.  The same short cuts here: candidates are
 // gathered into shared memory, put in order by counting (key descending, id ascending), and the chain runs on them
 // with the reference's own arithmetic.  A row whose head does not fit, or is never enough, or whose walk runs off the
-// head's end, goes the long way (the threshold descents below), which needs no room and no sort.
+// head's end, is left open for the long way (the threshold descents, launched behind this kernel), which needs no room
+// and no sort.
 #define SMP_CAP 4096               // candidates that fit (the reference's HEAD_CAP)
+#define SMP_DYN_MAX (160 * 1024)   // shared memory the short cuts may ask for: the candidates and one bit per token id
 #define SMP_KMAX 1024              // largest top-k selected this way: the k-th largest of the threads' maxima bounds the k-th largest of the row
 
 __device__ __forceinline__ float smp_key_value(unsigned k) { return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k); }
@@ -340,7 +347,7 @@ __device__ int smp_pick_scaled(float* s_p, const int* s_id, int m, float norm_su
 }
 
 __global__ void __launch_bounds__(SMP_THREADS)
-k_sample(SampleArgs a, float* scratch /* [rows, V] scaled values, or null when nothing needs them */, int shortcuts) {
+k_sample(SampleArgs a, float* scratch /* [rows, V] scaled values, or null when nothing needs them */, int shortcuts /* 1: the short cuts and nothing else */) {
     xr_pdl_launch();
     extern __shared__ __align__(16) uint8_t smp_dyn[];          // short cuts: [SMP_CAP] keys, ids, values in order, ids in order; window bits
     __shared__ double sh[40 + SMP_THREADS];
@@ -352,8 +359,16 @@ k_sample(SampleArgs a, float* scratch /* [rows, V] scaled values, or null when n
     float temp = a.temp[row];
     int V = a.V;
     xr_pdl_wait();
+    if (a.todo != nullptr && !shortcuts) {
+        // the long way after the short cuts: only for the rows they left open (the word lies where this row is staged
+        // below: everyone has read it before anyone writes there)
+        const int wanted = a.todo[(size_t)row * a.todo_stride];
+        __syncthreads();
+        if (!wanted) return;
+    }
+    int* todo_word = shortcuts ? const_cast<int*>(a.todo) + (size_t)row * a.todo_stride : nullptr;
 
-    if (temp <= 0.f) { smp_argmax(lg, V, a.out + row, sh_f, sh_i); return; }
+    if (temp <= 0.f) { smp_argmax(lg, V, a.out + row, sh_f, sh_i); if (todo_word && tid == 0) *todo_word = 0; return; }
 
     if (shortcuts) {
         // Nothing is staged here: a pass reads the logits and works out each value again, logit -> penalised (once per
@@ -467,17 +482,22 @@ k_sample(SampleArgs a, float* scratch /* [rows, V] scaled values, or null when n
                 if (nc > SMP_CAP) break;                           // the head is too broad
                 const bool enough = top_p < 1.0f ? head >= (double)top_p * total
                                   : (min_p > 0.0f ? t_log <= logf(min_p) : head > (double)r * total);
+                // (a head of hundreds that is not enough belongs to a flat row: four times the distance in the logarithm
+                // takes in most of the vocabulary, so the pass that would find that out is spared)
+                if (!enough && nc > SMP_CAP / 8) break;
                 if (!enough) { __syncthreads(); continue; }
                 smp_order(c_key, c_id, nc, nc, s_p, s_id);
                 m = nc; norm_sum = (float)total;
                 break;
             }
         }
-        if (m > 0) {
-            const int pick = smp_pick_scaled(s_p, s_id, m, norm_sum, top_p, min_p, r, &bc_f, &bc_i);
-            if (pick >= 0) { if (tid == 0) a.out[row] = pick; return; }
+        int pick = -1;
+        if (m > 0) pick = smp_pick_scaled(s_p, s_id, m, norm_sum, top_p, min_p, r, &bc_f, &bc_i);
+        if (tid == 0) {
+            if (pick >= 0) a.out[row] = pick;
+            *todo_word = pick >= 0 ? 0 : 1;          // open: the kernel of the long way, queued behind this one, takes the row
         }
-        __syncthreads();
+        return;
     }
 
     // Stage the row: copy, penalise the recent tokens (once per occurrence in the window, as the
@@ -792,6 +812,7 @@ k_sample_cluster(SampleArgs a) {
     const float temp = a.temp[row];
     const int V = a.V;
     xr_pdl_wait();
+    if (a.todo != nullptr && a.todo[(size_t)row * a.todo_stride] == 0) return;      // (the whole cluster: nobody writes these words here)
     if (temp <= 0.f) {                              // a greedy row: one block does it (the whole cluster leaves here)
         if (c.rank == 0) smp_argmax(lg, V, a.out + row, sh_f, sh_i);
         return;
@@ -1082,9 +1103,9 @@ XR_EXPORT int xr_logprob(const float* logits, long long ld, int rows, int V, con
 // scratch: [rows, V] floats when any row has temp > 0 (may be null when all rows are greedy).
 static int launch_sample_block(const SampleArgs& a, int rows, float* scratch, int shortcuts, cudaStream_t stream) {
     // candidates (keys, ids, values in order, ids in order) and one bit per token id for the window of recent tokens
-    constexpr int DYN_MAX = 160 * 1024;
+    constexpr int DYN_MAX = SMP_DYN_MAX;
     const long long dyn = (long long)SMP_CAP * 16 + ((long long)(a.V + 31) / 32) * 4;
-    if (dyn > DYN_MAX) shortcuts = 0;                               // (a vocabulary of more than 786,432: the long way)
+    if (shortcuts && dyn > DYN_MAX) return XR_ERR_ARG;              // (a vocabulary of more than 786,432; xr_sample checks before)
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(k_sample, cudaFuncAttributeMaxDynamicSharedMemorySize, DYN_MAX) != cudaSuccess) return XR_ERR_LAUNCH;
@@ -1102,9 +1123,18 @@ XR_EXPORT int xr_sample(const float* logits, long long ld, int rows, int V, cons
                         const int* exempt, cudaStream_t stream) {
     if (rows < 1 || V < 1 || ld < V) return XR_ERR_ARG;
     if (pending != nullptr && (feed == nullptr || exempt == nullptr || recent == nullptr)) return XR_ERR_ARG;
-    SampleArgs a{logits, ld, V, temp, top_k, top_p, min_p, penalty, draw, recent, out, pending, feed, exempt};
-    if (!shortcuts && smp_use_cluster(rows, V)) return launch_sample_cluster(a, rows, stream);
-    return launch_sample_block(a, rows, scratch, shortcuts, stream);
+    SampleArgs a{logits, ld, V, temp, top_k, top_p, min_p, penalty, draw, recent, out, pending, feed, exempt, nullptr, 0};
+    if ((long long)SMP_CAP * 16 + ((long long)(V + 31) / 32) * 4 > SMP_DYN_MAX) shortcuts = 0;      // (more than 786,432 values a row)
+    if (shortcuts) {
+        // the short cuts for every row, then the long way for the rows they left open (usually none: the second launch
+        // then reads one word a row and ends).  The words lie at the start of each row's staging area.
+        if (scratch == nullptr) return XR_ERR_ARG;
+        a.todo = (const int*)scratch; a.todo_stride = V;
+        int rc = launch_sample_block(a, rows, scratch, 1, stream);
+        if (rc != XR_OK) return rc;
+    }
+    if (smp_use_cluster(rows, V)) return launch_sample_cluster(a, rows, stream);
+    return launch_sample_block(a, rows, scratch, 0, stream);
 }
 
 // The one-block kernel whatever the width (what xr_sample falls back to; tests compare the two).
@@ -1112,6 +1142,6 @@ XR_EXPORT int xr_sample_one_block(const float* logits, long long ld, int rows, i
                                   const float* top_p, const float* min_p, const float* penalty, const float* draw,
                                   const int* recent, float* scratch, int* out, cudaStream_t stream) {
     if (rows < 1 || V < 1 || ld < V) return XR_ERR_ARG;
-    SampleArgs a{logits, ld, V, temp, top_k, top_p, min_p, penalty, draw, recent, out, nullptr, nullptr, nullptr};
+    SampleArgs a{logits, ld, V, temp, top_k, top_p, min_p, penalty, draw, recent, out, nullptr, nullptr, nullptr, nullptr, 0};
     return launch_sample_block(a, rows, scratch, 0, stream);
 }

@@ -218,9 +218,9 @@ def sample(logits: torch.Tensor, temp, top_k, top_p, min_p, penalty, draw, recen
     """One token per row of float32 logits by the reference's sampling chain (see csrc/sampling.cu).
     `scratch` must hold rows * vocab floats unless every row is greedy (`any_sampled` False).  `shortcuts` (the
     default): one block a row that selects the top-k, or gathers the head of the distribution, sorts that and walks
-    it as the reference does, and goes the long way only where that does not apply.  Without: the long way for every
-    row, by threshold descents that never sort, spread over a cluster of eight blocks a row when the rows are few
-    and have more than 1,024 values (`one_block`: in one block whatever the width).
+    it as the reference does; rows where that does not apply are left to a second launch that goes the long way for
+    them alone.  Without: the long way for every row, by threshold descents that never sort, spread over a cluster of
+    eight blocks a row when the rows are few and have more than 1,024 values (`one_block`: in one block whatever the width).
     `pending` (int32 [rows, 3]) with `feed` and `exempt` (int32 [rows, EXEMPT_IDS]): row r's window lacks the token that
     the step before sampled and the host has not read yet; it is feed[pending[r, 0]] (-1: the window is complete),
     takes window entry pending[r, 1], and is left out if it is among the first pending[r, 2] ids of exempt[r].
