@@ -290,8 +290,9 @@ def timeline(args) -> int:
             ev.append((t1, t0, (g >> 40, (g >> 20) & 0xfffff, g & 0xfffff), b))
     ev.sort()
     per_layer = (len(ev) - 4) // n_layers
-    if per_layer < 1 or 2 + per_layer * n_layers + 2 != len(ev):
-        raise SystemExit(f"{len(ev)} launches were recorded: not embedding + norm + {n_layers} equal layers + 2")
+    tail = len(ev) - 2 - per_layer * n_layers             # final norm, head product (and its finish, if it is cut along K)
+    if per_layer < 1 or tail < 2 or tail > 3:
+        raise SystemExit(f"{len(ev)} launches were recorded: not embedding + norm + {n_layers} equal layers + 2 or 3")
     first = 2 + per_layer
     rows = ev[first:first + per_layer + 1]
     what = "decode step"
@@ -306,7 +307,7 @@ def timeline(args) -> int:
         print(f"{(t1 - base) / 1e3:12.2f} {(t1 - t0) / 1e3:16.2f} {(nxt[0] - t1) / 1e3:7.2f}  {g} / {b}")
     print(f"layer: {(rows[-1][0] - base) / 1e3:.2f} us")
     print("start and end of the step:")
-    for idx in (0, 1, len(ev) - 3, len(ev) - 2):
+    for idx in [0, 1] + list(range(len(ev) - 1 - tail, len(ev) - 1)):
         (t1, t0, g, b), nxt = ev[idx], ev[idx + 1]
         print(f"{(t1 - ev[0][0]) / 1e3:12.2f} {(t1 - t0) / 1e3:16.2f} {(nxt[0] - t1) / 1e3:7.2f}  {g} / {b}")
     print(f"step up to the sampling kernel: {(ev[-1][0] - ev[0][0]) / 1e3:.2f} us")

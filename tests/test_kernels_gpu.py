@@ -294,7 +294,7 @@ def _run_attention(case, kind, H, K, hd, page, window, dtype, tma=False, uneven=
                               v_off, H, K, hd, c["max_pages"], page, window, c["scale"], c["n_seg"], int(lens.max()),
                               c["max_len"], splits, bool((lens * G <= 16).any()), bool((lens * G > 16).any()),
                               group=(cache.data_ptr(), cache.shape[0], cache.shape[1], 0) if tma else None, uneven=uneven,
-                              seg_len_host=lens if tma else None)      # (the row-tiled kernel's grid: exact, or an upper bound)
+                              row_tiles=kernels.long_row_tiles(lens, G, 64) if tma else 0)      # (the row-tiled kernel's grid: exact, or an upper bound)
         kernels.tc_check_status(torch.device(DEV))
     return out.cpu().double()
 
@@ -608,7 +608,7 @@ def test_attention_tc(case_id, hd):
     # (the grid is sized from the lengths, or, without them, by an upper bound whose surplus blocks return at once)
     kernels.attention_tc(c["qkv"], out, c["starts"], c["lens"], c["pos0"], c["bt"], (cache.data_ptr(), cache.shape[0], cache.shape[1], 0),
                          H, K, hd, c["max_pages"], page, window, c["scale"], c["n_seg"], int(c["lens_host"].max()),
-                         seg_len_host=c["lens_host"] if case_id % 2 == 0 else None)
+                         row_tiles=kernels.long_row_tiles(c["lens_host"], H // K, 128) if case_id % 2 == 0 else 0)
     kernels.tc_check_status(torch.device(DEV))
     got, ref = out.cpu().double(), c["ref"]
     G = H // K

@@ -1332,13 +1332,17 @@ static int launch_keys_tma(const AttnMmaArgs& a, const void* cache_base, long lo
     AttEncodeFn enc = att_encode();
     if (!enc) return 0;
     CUtensorMap map;
-    cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)total_rows};
-    cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
-    cuuint32_t box[2] = {64, (cuuint32_t)(a.page_size < ATT_TILE ? a.page_size : ATT_TILE)};
-    cuuint32_t estr[2] = {1, 1};
-    if (enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache_base), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    const unsigned box_rows = (unsigned)(a.page_size < ATT_TILE ? a.page_size : ATT_TILE);
+    const XrMapKey key{cache_base, {(unsigned long long)HD, (unsigned long long)total_rows, 0}, {(unsigned long long)HD * 2, 0}, {64, box_rows, 0}, 2, 0};
+    if (!xr_cached_map(&map, key, [&](CUtensorMap* out) {
+            cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)total_rows};
+            cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+            cuuint32_t box[2] = {64, box_rows};
+            cuuint32_t estr[2] = {1, 1};
+            return enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache_base), dims, strides, box, estr,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+        }))
         return -3;
     constexpr int LD = HD + 8;
     constexpr int STAGE = 2 * ATT_TILE * HD * 2, REST = 16 * LD * 2 + 64 + 1024;

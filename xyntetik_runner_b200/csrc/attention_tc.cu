@@ -507,21 +507,29 @@ XR_EXPORT int xr_attention_tc(const void* q, void* out, const void* cache_base, 
     CUtensorMap qm, kvm;
     {
         // Q as [token][head][hd]; a box is 64 columns x G heads x (128 / G) tokens = 128 packed rows
-        cuuint64_t dims[3] = {(cuuint64_t)hd, (cuuint64_t)H, (cuuint64_t)n};
-        cuuint64_t strides[2] = {(cuuint64_t)hd * 2, (cuuint64_t)q_row_stride * 2};
-        cuuint32_t box[3] = {64, (cuuint32_t)G, (cuuint32_t)(TA_ROWS / G)};
-        cuuint32_t estr[3] = {1, 1, 1};
-        if (enc(&qm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        const XrMapKey key{q, {(unsigned long long)hd, (unsigned long long)H, (unsigned long long)n}, {(unsigned long long)hd * 2, (unsigned long long)q_row_stride * 2},
+                           {64, (unsigned)G, (unsigned)(TA_ROWS / G)}, 3, 0};
+        if (!xr_cached_map(&qm, key, [&](CUtensorMap* out) {
+                cuuint64_t dims[3] = {(cuuint64_t)hd, (cuuint64_t)H, (cuuint64_t)n};
+                cuuint64_t strides[2] = {(cuuint64_t)hd * 2, (cuuint64_t)q_row_stride * 2};
+                cuuint32_t box[3] = {64, (cuuint32_t)G, (cuuint32_t)(TA_ROWS / G)};
+                cuuint32_t estr[3] = {1, 1, 1};
+                return enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+            }))
             return -3;
     }
     {
-        cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)total_rows};
-        cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
-        cuuint32_t box[2] = {64, (cuuint32_t)(page_size < 64 ? page_size : 64)};
-        cuuint32_t estr[2] = {1, 1};
-        if (enc(&kvm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache_base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        const unsigned box_rows = (unsigned)(page_size < 64 ? page_size : 64);
+        const XrMapKey key{cache_base, {(unsigned long long)hd, (unsigned long long)total_rows, 0}, {(unsigned long long)hd * 2, 0}, {64, box_rows, 0}, 2, 1};
+        if (!xr_cached_map(&kvm, key, [&](CUtensorMap* out) {
+                cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)total_rows};
+                cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
+                cuuint32_t box[2] = {64, box_rows};
+                cuuint32_t estr[2] = {1, 1};
+                return enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache_base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+            }))
             return -3;
     }
     int shift = 0;

@@ -81,6 +81,42 @@ static inline int xr_sm_count() {
     return known[dev];
 }
 
+// Tensor maps (TMA descriptors) that were encoded before.  A step encodes the same few dozen maps again and again (the
+// weights of each layer, the buffers that keep their addresses, the cache groups), and an encode costs the host a
+// few microseconds each, which a step of a few hundred tokens does not hide.  The key is everything the encode is
+// given; a slot is taken by its key's hash and simply overwritten by another key that lands there.  `Map` is
+// CUtensorMap (this header does not include cuda.h); `encode(&map)` makes the map and says whether it could.
+struct XrMapKey {
+    const void* base;
+    unsigned long long dims[3], strides[2];
+    unsigned box[3], rank, flavour;
+    bool operator==(const XrMapKey& o) const {
+        return base == o.base && dims[0] == o.dims[0] && dims[1] == o.dims[1] && dims[2] == o.dims[2] && strides[0] == o.strides[0] &&
+               strides[1] == o.strides[1] && box[0] == o.box[0] && box[1] == o.box[1] && box[2] == o.box[2] && rank == o.rank && flavour == o.flavour;
+    }
+};
+template <typename Map, typename Encode>
+static inline bool xr_cached_map(Map* out, const XrMapKey& key, Encode encode) {
+    constexpr int SLOTS = 1024;
+    struct Slot { XrMapKey key; Map map; bool full; };
+    static Slot* slots = nullptr;                 // (one table per kind of map and source file; never freed)
+    static volatile int busy = 0;
+    unsigned long long h = (unsigned long long)(uintptr_t)key.base * 0x9E3779B97F4A7C15ull;
+    h ^= (key.dims[0] * 31 + key.dims[1]) * 0xC2B2AE3D27D4EB4Full + key.strides[0] * 0x165667B19E3779F9ull + key.box[1] * 131 + key.flavour;
+    const int at = (int)((h >> 32) % SLOTS);
+    while (__sync_lock_test_and_set(&busy, 1)) {}           // calls from two host threads are rare and short
+    if (!slots) slots = new Slot[SLOTS]();
+    bool ok = true;
+    if (slots[at].full && slots[at].key == key) {
+        *out = slots[at].map;
+    } else {
+        ok = encode(out);
+        if (ok) { slots[at].key = key; slots[at].map = *out; slots[at].full = true; }
+    }
+    __sync_lock_release(&busy);
+    return ok;
+}
+
 template <typename... KArgs, typename... Args>
 static inline void xr_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
     cudaLaunchConfig_t cfg = {};

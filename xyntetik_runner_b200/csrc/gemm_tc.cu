@@ -618,13 +618,16 @@ static EncodeTiledFn get_encode() {
 static bool make_map(CUtensorMap* m, const void* base, long long rows, long long K, long long ld, int box_rows) {
     EncodeTiledFn enc = get_encode();
     if (!enc) return false;
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
-    cuuint32_t estr[2] = {1, 1};
-    return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    const XrMapKey key{base, {(unsigned long long)K, (unsigned long long)rows, 0}, {(unsigned long long)ld * 2, 0}, {TC_BK, (unsigned)box_rows, 0}, 2, 0};
+    return xr_cached_map(m, key, [&](CUtensorMap* out) {
+        cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+        cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+        cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+        cuuint32_t estr[2] = {1, 1};
+        return enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    });
 }
 
 template <int BN, int STAGES, int MINB>

@@ -71,11 +71,26 @@ class StepContext:
         self.host: Dict[str, np.ndarray] = {}
         self.max_kv_len = 0            # longest key range any token of the step reads
         self._pending = {}
+        self._views: Dict[tuple, torch.Tensor] = {}
+        self._memo: Dict[object, object] = {}
         self.decode_only = False       # every segment is a single token
         self.uneven = False            # the requests' lengths differ much (a hint for kernels that split work by request)
 
     def buf(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
-        return self._eng._buf(name, shape, dtype)
+        # (every layer asks for the same few views: made once a step)
+        key = (name, tuple(shape), dtype)
+        t = self._views.get(key)
+        if t is None:
+            t = self._views[key] = self._eng._buf(name, shape, dtype)
+        return t
+
+    def once(self, key, make):
+        """make() the first time `key` is asked for in this step, the same value afterwards: for what a part works out
+        from the step's description on the host and every layer would work out again."""
+        v = self._memo.get(key)
+        if v is None:
+            v = self._memo[key] = make()
+        return v
 
     # A part whose last product was split along K may leave the sum unfinished ("pending") on the residual
     # stream; the next norm finishes it in its own pass.  Anything else that reads or writes that tensor

@@ -81,7 +81,17 @@ def _check(code: int, what: str) -> None:
         raise KernelError(f"{what}: {_ERR.get(code, f'error {code}')}")
 
 
+try:
+    _raw_stream, _raw_device = torch._C._cuda_getCurrentRawStream, torch._C._cuda_getDevice
+except AttributeError:                   # (another torch: the documented way, a few microseconds a call)
+    _raw_stream = _raw_device = None
+
+
 def _stream() -> int:
+    """The current CUDA stream's handle.  Asked for at every launch: a step of a few hundred tokens is a few hundred
+    launches whose host time nothing hides, so it is the two C calls, not the Stream object that torch builds."""
+    if _raw_stream is not None:
+        return _raw_stream(_raw_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -286,6 +296,7 @@ class Workspace:
     def __init__(self, device: torch.device):
         self.scratch = torch.empty(_TC_SCRATCH_FLOATS, dtype=torch.float32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.status_ptr = self.status.data_ptr()
         self.flags = torch.zeros(_HANDOVER_FLAGS, dtype=torch.int32, device=device)   # raised and lowered inside one launch
         self.top = 0            # floats taken from the start of the scratch
         self.live = 0           # slabs outstanding
@@ -400,6 +411,10 @@ class PartialSums:
             self._ws = None
 
 
+_SPLITS_USED = ctypes.c_int(1)           # where xr_gemm_tc says how it cut the product (read at once after the call)
+_SPLITS_USED_REF = ctypes.byref(_SPLITS_USED)
+
+
 def _gemm_tc(x, w, out, bias, epilogue, act, force_splits, defer, packed_rows):
     n, k = x.shape
     gated = epilogue == EPI_GATED
@@ -418,12 +433,11 @@ def _gemm_tc(x, w, out, bias, epilogue, act, force_splits, defer, packed_rows):
     assert not defer or not gated
     ws = workspace(x.device)
     at, room = ws.room()
-    used = ctypes.c_int(1)
     _check(lib().xr_gemm_tc(x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), dtype_code(out.dtype), epilogue, int(act),
                             n, n_out, k, x.stride(0), out.stride(0), at, room,
-                            ws.status.data_ptr(), force_splits, int(defer), ctypes.byref(used),
+                            ws.status_ptr, force_splits, int(defer), _SPLITS_USED_REF,
                             int(packed_rows is not None), _stream()), "gemm_tc")
-    splits = used.value
+    splits = _SPLITS_USED.value
     _count(1 if (splits == 1 or defer) else 2)
     if defer and splits > 1:
         rows = tiles * TILE_ROWS if (gated and packed_rows is not None) else n_out
@@ -498,6 +512,13 @@ def attention_mma_splits(max_kv_len: int, window: int, items: int) -> int:
     return int(lib().xr_attention_mma_splits(max_kv_len, window, items))
 
 
+def long_row_tiles(seg_len_host, heads_per_kv_head: int, rows_per_tile: int) -> int:
+    """Row tiles of the portions that the prompt attention kernels take (more than 16 packed rows = tokens x query heads
+    per kv head), summed: the x extent of their grids.  seg_len_host: the portions' lengths (numpy, on the host)."""
+    rows = seg_len_host.astype("int64") * heads_per_kv_head
+    return int(((rows + rows_per_tile - 1) // rows_per_tile)[rows > 16].sum())
+
+
 def attention_even_launches() -> int:
     """How often the decode attention was launched in even shares (rather than in spans) so far."""
     return int(lib().xr_attention_even_launches())
@@ -516,25 +537,21 @@ def attention_mma(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, cache_k
                   block_tables, part_acc: Optional[torch.Tensor], part_ml: Optional[torch.Tensor], page_stride: int,
                   v_offset: int, H: int, K: int, hd: int, max_pages: int, page_size: int, window: int, scale: float,
                   n_seg: int, max_seg_len: int, max_kv_len: int, splits: int, any_short: bool, any_long: bool,
-                  group: Optional[tuple] = None, uneven: bool = False, seg_len_host=None) -> None:
+                  group: Optional[tuple] = None, uneven: bool = False, row_tiles: int = 0) -> None:
     """Causal attention over the pages on tensor cores (bfloat16).  Portions with at most 16 packed rows
     (tokens x heads per kv head) go through the key-split kernel and need `part_acc` [n_seg*K*splits*16*hd]
     and `part_ml` [n_seg*K*splits*32] float32 scratch; longer portions through the row-tiled kernel.
     `group` = (pointer to the cache group's array, its pages, its layers, this layer's index) lets the
     key-split kernel fetch whole page blocks with bulk copies (head sizes 64 and 128, power-of-two pages).
     `uneven`: the requests' lengths differ much; the kernel then cuts the tiles of all requests into even shares from
-    fewer requests on than it does otherwise.  seg_len_host: the portions' lengths on the host (numpy), from which the
-    row-tiled kernel's grid is sized exactly; without them every portion gets the blocks of the longest."""
+    fewer requests on than it does otherwise.  row_tiles: ``long_row_tiles(lengths, H // K, 64)``, which sizes the
+    row-tiled kernel's grid exactly; 0: every portion gets the blocks of the longest."""
     _dev(out, seg_start, seg_len, seg_pos0, block_tables, part_acc, part_ml)
     assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and out.shape[1] == H * hd
     if any_short:
         assert part_acc is not None and part_acc.numel() >= n_seg * K * splits * 16 * hd
         assert part_ml is not None and part_ml.numel() >= n_seg * K * splits * 32
     ws = workspace(out.device)
-    row_tiles = 0
-    if any_long and seg_len_host is not None:
-        rows = seg_len_host.astype("int64") * (H // K)
-        row_tiles = int(((rows + 63) // 64)[rows > 16].sum())
     _check(lib().xr_attention_mma(q.data_ptr(), out.data_ptr(), cache_k_ptr, seg_start.data_ptr(), seg_len.data_ptr(),
                                   seg_pos0.data_ptr(), block_tables.data_ptr(), _ptr(part_acc), _ptr(part_ml),
                                   q_row_stride, page_stride, v_offset, n_seg, H, K, hd, max_pages, page_size, window,
@@ -552,19 +569,15 @@ def attention_tc_supported(dtype: torch.dtype, H: int, K: int, hd: int, page_siz
 
 def attention_tc(qkv: torch.Tensor, out: torch.Tensor, seg_start, seg_len, seg_pos0, block_tables, group: tuple,
                  H: int, K: int, hd: int, max_pages: int, page_size: int, window: int, scale: float, n_seg: int,
-                 max_seg_len: int, seg_len_host=None) -> None:
+                 max_seg_len: int, row_tiles: int = 0) -> None:
     """Causal attention of the portions with more than 16 packed rows on tcgen05 (S and O in tensor memory).
     qkv: the step's fused rows (Q heads first); group = (pointer to the cache group's array, pages, layers, layer).
-    seg_len_host: the portions' lengths on the host (numpy), from which the grid is sized exactly; without them every
-    portion gets the blocks of the longest."""
+    row_tiles: ``long_row_tiles(lengths, H // K, 128)``, which sizes the grid exactly; 0: every portion gets the blocks
+    of the longest."""
     _dev(qkv, out, seg_start, seg_len, seg_pos0, block_tables)
     n = qkv.shape[0]
     assert qkv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and out.shape == (n, H * hd)
     status = tc_workspace(out.device)[1]
-    row_tiles = 0
-    if seg_len_host is not None:
-        rows = seg_len_host.astype("int64") * (H // K)
-        row_tiles = int(((rows + 127) // 128)[rows > 16].sum())
     _check(lib().xr_attention_tc(qkv.data_ptr(), out.data_ptr(), group[0], seg_start.data_ptr(), seg_len.data_ptr(),
                                  seg_pos0.data_ptr(), block_tables.data_ptr(), status.data_ptr(), qkv.stride(0), n, n_seg,
                                  H, K, hd, max_pages, page_size, window, float(scale), max_seg_len, row_tiles, group[1], group[2],

@@ -87,6 +87,15 @@ class GQAAttention(Mixer):
     def weight_bytes(self):
         return self.qkv.nbytes() + self.out.nbytes()
 
+    @staticmethod
+    def _portions(ctx, G):
+        """(some portion has at most 16 packed rows, some has more, the longest portion, the row tiles of the longer
+        ones in tiles of 128 and of 64 rows)"""
+        seg_len = ctx.host["seg_len"]
+        rows = seg_len * G
+        return (bool((rows <= 16).any()), bool((rows > 16).any()), int(seg_len.max()),
+                kernels.long_row_tiles(seg_len, G, 128), kernels.long_row_tiles(seg_len, G, 64))
+
     def forward(self, ctx, h, x, lay):
         n = h.shape[0]
         qkv_dim = (self.H + 2 * self.K) * self.hd
@@ -111,10 +120,10 @@ class GQAAttention(Mixer):
         # Q is read in place from the fused rows (row stride = qkv_dim)
         G = self.H // self.K
         if USE_MMA and kernels.attention_mma_supported(ctx.act_dtype, self.H, self.K, self.hd):
-            seg_len = ctx.host["seg_len"]
-            any_short = bool((seg_len * G <= 16).any())
-            any_long = bool((seg_len * G > 16).any())
-            splits = kernels.attention_mma_splits(ctx.max_kv_len, self.window or 0, ctx.n_seg * self.K)
+            # (what the portions' lengths say is the same for every layer of the step)
+            any_short, any_long, longest, tiles_tc, tiles_rows = ctx.once(("gqa_portions", G), lambda: self._portions(ctx, G))
+            splits = ctx.once(("gqa_splits", self.window or 0, self.K),
+                              lambda: kernels.attention_mma_splits(ctx.max_kv_len, self.window or 0, ctx.n_seg * self.K))
             pa = pm = None
             if any_short:
                 pa = ctx.buf("attn_part_acc", (ctx.n_seg * self.K * splits * 16 * self.hd,), torch.float32)
@@ -123,15 +132,15 @@ class GQAAttention(Mixer):
                 # prompt portions: S = Q K^T and O += P V on tcgen05
                 kernels.attention_tc(qkv, o, ctx.seg_start, ctx.seg_len, ctx.seg_pos0, bt, ctx.cache_group(lay), self.H,
                                      self.K, self.hd, ctx.max_pages, ctx.page_size, self.window or 0, self.scale, ctx.n_seg,
-                                     int(seg_len.max()), seg_len_host=seg_len)
+                                     longest, row_tiles=tiles_tc)
                 counters["tcgen05"] += 1
                 any_long = False
             if any_short or any_long:
                 kernels.attention_mma(qkv, qkv_dim, o, k_ptr, ctx.seg_start, ctx.seg_len, ctx.seg_pos0, bt, pa, pm,
                                       page_stride, v_offset, self.H, self.K, self.hd, ctx.max_pages, ctx.page_size,
-                                      self.window or 0, self.scale, ctx.n_seg, int(seg_len.max()), ctx.max_kv_len, splits,
+                                      self.window or 0, self.scale, ctx.n_seg, longest, ctx.max_kv_len, splits,
                                       any_short, any_long, group=ctx.cache_group(lay) if USE_TMA else None, uneven=ctx.uneven,
-                                      seg_len_host=seg_len)
+                                      row_tiles=tiles_rows)
                 counters["mma"] += 1
         else:
             kernels.attention_simt(qkv, qkv_dim, o, k_ptr, ctx.positions, ctx.tok_seg, bt, page_stride, v_offset,
