@@ -13,6 +13,7 @@ from typing import Optional
 import torch
 
 from .. import kernels
+from . import linear_tc
 
 counters = {"tcgen05": 0, "simt": 0, "deferred": 0}
 
@@ -31,7 +32,6 @@ class Linear:
 
     def prepare(self, rt, keep_plain: bool = False) -> "Linear":
         """Choose the layout for the engine's precision.  Returns self."""
-        from . import linear_tc
         if (linear_tc.ENABLED and rt.act_dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16
                 and self.k % 8 == 0 and self.weight.is_cuda):
             self.packed = kernels.pack_weight(self.weight, self.halves)
@@ -47,12 +47,14 @@ class Linear:
         """out (+)= act(x W^T + bias) (an activation only without `accumulate`).  With `defer`, a product that was
         split along K leaves its partial sums in a slab of the workspace and returns ``Pending``; the caller's next
         kernel sums them (and adds the bias) and releases the slab.  Otherwise returns None and `out` is complete."""
-        from . import linear_tc
         assert self.halves == 1, "a matrix of two halves is multiplied by forward_gated"
         assert act == kernels.ACT_NONE or not (accumulate or defer)
         if self.packed is not None or linear_tc.usable(self, x, out, accumulate):
             counters["tcgen05"] += 1
-            return linear_tc.run(self, x, out, accumulate, defer, act)
+            pending = linear_tc.run(self, x, out, accumulate, defer, act)
+            if pending is not None:
+                counters["deferred"] += 1
+            return pending
         kernels.gemm_simt(x, self.weight, out, self.bias, accumulate)
         if act != kernels.ACT_NONE:
             kernels.act_mul(out, out, act, gated=False)

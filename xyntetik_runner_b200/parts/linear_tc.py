@@ -40,8 +40,6 @@ def run(lin, x, out, accumulate, defer=False, act=kernels.ACT_NONE):
         sums = kernels.gemm_tc_deferred(x, w, out, lin.bias, epi, packed_rows=packed_rows)
         if sums is None:
             return None
-        from . import linear
-        linear.counters["deferred"] += 1
         return Pending(sums, lin.bias, out, accumulate)
     kernels.gemm_tc(x, w, out, lin.bias, epi, packed_rows=packed_rows, act=act)
     return None
