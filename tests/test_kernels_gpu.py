@@ -352,11 +352,12 @@ def _even_share_segments(seed, n, longest, extras):
 
 
 EVEN_CASES = [
-    # H, K, hd, page, window, segments: more (request, kv head) pairs than two CTAs per SM, so the bulk-copy kernel cuts
-    # the tiles of all pairs into even shares: requests of 1 to 80 tiles (one CTA's share is about ten, so some lie
-    # inside one share, most are cut in two, the longest into many), entries of two and four tokens, and prompt
-    # portions in the same step (no tiles in this kernel)
-    (32, 8, 128, 64, 0, _even_share_segments(1, 34, 1400, [(5099, 1), (0, 1), (63, 1), (64, 1), (300, 2), (301, 4), (0, 40), (700, 9)])),
+    # H, K, hd, page, window, segments: more (request, kv head) pairs than three CTAs per SM, so the bulk-copy kernel cuts
+    # the tiles of all pairs into even shares whatever the caller says of their lengths: requests of 1 to 80 tiles (one
+    # CTA's share is about ten, so some lie inside one share, most are cut in two, the longest into many), entries of
+    # two and four tokens, and prompt portions in the same step (no tiles in this kernel)
+    (32, 8, 128, 64, 0, _even_share_segments(1, 49, 1400, [(5099, 1), (0, 1), (63, 1), (64, 1), (300, 2), (301, 4), (0, 40), (700, 9)])),
+    # the cases below have fewer pairs (more than two an SM) and take even shares on the caller's word that the lengths are uneven
     # one query head per kv head, small pages, a window: the first tile of a request is not tile 0
     (8, 8, 64, 16, 500, _even_share_segments(2, 36, 3000, [(499, 1), (500, 1), (501, 1), (2999, 2)])),
     # fewer tiles than CTAs (most requests are prompt portions): empty shares, shares of one tile
@@ -377,8 +378,8 @@ def test_decode_attention_in_even_shares(case_id):
     from xyntetik_runner_b200 import kernels
     H, K, hd, page, window, segs = EVEN_CASES[case_id]
     sms = torch.cuda.get_device_properties(0).multi_processor_count
-    uneven = case_id == 4
-    assert len(segs) * K > 2 * sms or (uneven and 8 * len(segs) * K >= 5 * sms)      # what the case is for
+    uneven = case_id > 0
+    assert len(segs) * K > 3 * sms or (uneven and 8 * len(segs) * K >= 5 * sms)      # what the case is for
     rng = np.random.RandomState(100 + case_id)
     spikes = []
     for s, (p0, L) in enumerate(segs):

@@ -1299,13 +1299,14 @@ static AttEncodeFn att_encode() {
 }
 
 // Even shares are taken when there are more (request, kv head) pairs than CTAs with deep rings fit on the machine.
-// Requests of much the same length are better served by spans while one CTA per span is resident at once (measured at
-// up to 36 requests of 8 kv heads: 2 to 5 us less than even shares, whose pieces meet through global memory); requests
-// of unequal length leave most spans short, and even shares win from about two pairs per three SMs on (32 requests of
-// 512 to 4,096 keys: 52.8 against 63.4 us; 12 of 1,024 to 8,192: 46.8 against 59.5 us; with 8 such requests a long one is
-// cut into so many pieces that gathering them costs more than the balance gains, 38.5 against 33.1 us).
+// Requests of much the same length are better served by spans while one CTA per span is resident at once, three to an
+// SM (measured up to 52 requests of 8 kv heads and 8 of 40: 1 to 5 us less than even shares, whose pieces meet through
+// global memory); requests of unequal length leave most spans short, and even shares win from about two pairs per
+// three SMs on (32 requests of 512 to 4,096 keys: 52.8 against 63.4 us; 12 of 1,024 to 8,192: 46.8 against 59.5 us;
+// with 8 such requests a long one is cut into so many pieces that gathering them costs more than the balance gains,
+// 38.5 against 33.1 us).
 static bool att_even_wanted(long long items, bool uneven) {
-    return items > 2LL * xr_sm_count() || (uneven && 8 * items >= 5LL * xr_sm_count());
+    return items > 3LL * xr_sm_count() || (uneven && 8 * items >= 5LL * xr_sm_count());
 }
 static long long g_even_launches = 0;
 // Launches of the even-shares kernel so far (captures count once): lets a test see which kernel a step took.
