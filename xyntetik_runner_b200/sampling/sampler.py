@@ -139,6 +139,9 @@ class DeviceSampler:
                 exm = np.full((rows, kernels.EXEMPT_IDS), -1, dtype=np.int32)
                 for i, (j, s) in enumerate(zip(in_flight, samplers)):
                     if j >= 0 and s.needs_window():
+                        if not s.window_on_device_ok():
+                            raise ValueError(f"a request with {len(s.no_penalty)} ids exempt from the repeat penalty cannot have its "
+                                             f"window completed on the device (at most {kernels.EXEMPT_IDS}): sample it with the token on the host")
                         pend[i] = (j, s.head, len(s.no_penalty))
                         exm[i, :len(s.no_penalty)] = s.no_penalty
                 pending = torch.from_numpy(pend).to(self.device, non_blocking=True)
