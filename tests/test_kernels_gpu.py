@@ -370,6 +370,25 @@ EVEN_CASES = [
 ]
 
 
+def _random_even_case(seed):
+    """Sizes drawn at random: kv heads, query heads per kv head, head size, page size, a window or none, and 24 to 60
+    requests of 1 to 3,000 keys whose entries have as many tokens as 16 packed rows allow."""
+    rng = np.random.RandomState(1000 + seed)
+    K, G = int(rng.choice([8, 16])), int(rng.choice([1, 2, 4, 8]))
+    hd, page = int(rng.choice([64, 128])), int(rng.choice([8, 16, 32, 64, 128]))
+    window = int(rng.choice([0, 0, 70, 700]))
+    n = int(rng.randint(24, 61)) if K == 8 else int(rng.randint(12, 31))
+    segs = []
+    for _ in range(n):
+        L = int(rng.randint(1, 16 // G + 1)) if rng.rand() < 0.3 else 1
+        top = int(rng.choice([40, 300, 3000]))
+        segs.append((int(rng.randint(0, top)), L))
+    return K * G, K, hd, page, window, segs
+
+
+EVEN_CASES += [_random_even_case(i) for i in range(8)]
+
+
 @pytest.mark.parametrize("case_id", range(len(EVEN_CASES)))
 def test_decode_attention_in_even_shares(case_id):
     """Every request's last query (first head of each kv head) has ONE key, somewhere in its range, that carries most of
