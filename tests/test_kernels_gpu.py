@@ -239,8 +239,13 @@ def _paged_case(seed, H, K, hd, page, seg_specs, dtype, window=0, spike=None, sp
             k, v, q = bf16_round(k), bf16_round(v), bf16_round(q)
         for i in range(-(-T // page)):
             bt[s, i] = perm[nxt]; nxt += 1
-        for t in range(T):
-            if window and t < p0 - window + 1 - page:
+        if not window:
+            for i in range(-(-T // page)):                  # page by page (the same bytes as token by token below)
+                t0, t1 = i * page, min(T, (i + 1) * page)
+                cache[bt[s, i], 0, 0, :, :t1 - t0] = k[t0:t1].transpose(0, 1)
+                cache[bt[s, i], 0, 1, :, :t1 - t0] = v[t0:t1].transpose(0, 1)
+        for t in range(T if window else 0):
+            if t < p0 - window + 1 - page:
                 continue                                    # pages wholly behind the window may be gone
             cache[bt[s, t // page], 0, 0, :, t % page] = k[t]
             cache[bt[s, t // page], 0, 1, :, t % page] = v[t]
@@ -432,6 +437,45 @@ def test_attention_finds_a_far_key(kind):
         got = _run_attention(case, kind.split("_")[0], H, K, hd, page, 0, torch.bfloat16, tma=kind.endswith("tma"))
         err = (got - case["ref"]).abs().max() / case["ref"].abs().max()
         assert float(err) <= 1.2e-2, (key_pos, float(err))
+
+
+@pytest.mark.parametrize("key_pos", [3, 65537, 131071])
+def test_decode_attention_over_a_hundred_thousand_keys(key_pos):
+    """Contexts far beyond those of the other cases (Llama-3.1 allows 131,072 positions): one request with 131,072 keys
+    beside requests of 40,000 and 70,002, in which ONE key -- near the start, in the middle, the very last -- carries
+    nearly all the weight of the longest request's query.  Many spans and their merge in groups, page numbers in the
+    thousands and rows of the cache beyond 2^19 are in play, in every decode kernel."""
+    H, K, hd, page = 8, 2, 128, 64
+    segs = [(131071, 1), (39999, 1), (70000, 2)]
+    case = _paged_case(900 + key_pos % 7, H, K, hd, page, segs, torch.bfloat16, 0, spike=(0, key_pos, 180.0))
+    ref = case["ref"]
+    assert float(ref[0, :hd].abs().max()) > 0.5          # the spike row is one key's value, not a mean of thousands
+    for kind in ("simt", "mma", "mma_tma", "mma_tma_even"):
+        got = _run_attention(case, kind.split("_")[0], H, K, hd, page, 0, torch.bfloat16, tma="tma" in kind, uneven=kind.endswith("even"))
+        err = (got - ref).abs().max(dim=1).values / ref.abs().max(dim=1).values
+        assert float(err.max()) <= 2e-2, (kind, key_pos, err.tolist())
+
+
+def test_prompt_attention_far_into_a_long_context():
+    """A portion of 48 tokens at positions 100,000 to 100,047 on the tcgen05 kernel and on the row-tiled mma.sync kernel:
+    782 tiles of 128 keys for its two row tiles, with chosen queries whose weight lies on one key near the start, in
+    the middle, just before the portion and on the diagonal."""
+    from xyntetik_runner_b200 import kernels
+    H, K, hd, page = 8, 2, 128, 64
+    p0, L = 100000, 48
+    spikes = [(0, 0, 5, 16.0), (0, 17, 50000, 16.0), (0, 31, 100031, 16.0), (0, 47, 99999, 16.0)]
+    c = _paged_case(77, H, K, hd, page, [(p0, L)], torch.bfloat16, 0, spikes=spikes)
+    cache, ref = c["cache"], c["ref"]
+    for q in (0, 17, 31, 47):
+        assert float(ref[q, :hd].abs().max()) > 0.5
+    out = torch.full((c["n"], H * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    kernels.attention_tc(c["qkv"], out, c["starts"], c["lens"], c["pos0"], c["bt"], (cache.data_ptr(), cache.shape[0], cache.shape[1], 0),
+                         H, K, hd, c["max_pages"], page, 0, c["scale"], c["n_seg"], L, row_tiles=kernels.long_row_tiles(c["lens_host"], H // K, 128))
+    kernels.tc_check_status(torch.device(DEV))
+    outs = {"tcgen05": out.cpu().double(), "rows": _run_attention(c, "mma", H, K, hd, page, 0, torch.bfloat16)}
+    for name, got in outs.items():
+        err = (got - ref).abs().max(dim=1).values / ref.abs().max(dim=1).values
+        assert float(err.max()) <= 2e-2, (name, torch.topk(err, 5).indices.tolist(), float(err.max()))
 
 
 @pytest.mark.parametrize("kind,hd,page", [("tc", 128, 16), ("tc", 128, 64), ("tc", 64, 32), ("rows", 128, 16), ("rows", 48, 8), ("simt", 64, 16)])
