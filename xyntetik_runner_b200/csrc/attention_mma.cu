@@ -33,6 +33,7 @@
 #define ATT_ROWS 64            // packed query rows per CTA in the rows kernel
 #define ATT_KEYS_SLOTS (3 * xr_sm_count())   // CTAs of the keys kernel that are resident at once (two stages: three per SM)
 #define ATT_MAX_SPLITS 256     // most spans per request
+#define ATT_CLUSTER_MAX 8      // most spans that one cluster combines (the portable cluster size)
 #define ATT_THREADS 128
 
 struct AttnMmaArgs {
@@ -70,8 +71,9 @@ static int att_choose_span(int range, long long items) {
     // 41 us against 37 + 8 us with four spans and their merge).
     if (items >= ATT_KEYS_SLOTS && tiles <= 16) return tiles * ATT_TILE;
     // Times in nanoseconds, fitted to measurements at head size 128: a wave costs about 4 us before its first
-    // keys arrive plus its tiles; a tile streams in 0.7 us when a CTA has an SM to itself (latency bound) and in
-    // 2.1 us when the machine is full (bandwidth bound); the merge costs about 0.1 us per span.
+    // keys arrive plus its tiles; a tile streams in 0.9 us when a CTA has an SM to itself (latency bound) and in
+    // 2.1 us when the machine is full (bandwidth bound); the merge costs about 0.1 us per span.  (One request of
+    // 131,072 keys: 19 spans, a CTA per SM, 100 us; 27 spans, three CTAs on two SMs, 86 us; 55 spans, three per SM, 89 us.)
     int best = tiles;
     long long best_cost = -1;
     for (int s = tiles; s >= 1; s--) {
@@ -80,8 +82,13 @@ static int att_choose_span(int range, long long items) {
         long long ctas = items * splits;
         long long waves = (ctas + ATT_KEYS_SLOTS - 1) / ATT_KEYS_SLOTS;
         long long tile_ns = 2100 * (ctas < ATT_KEYS_SLOTS ? ctas : ATT_KEYS_SLOTS) / ATT_KEYS_SLOTS;
-        if (tile_ns < 700) tile_ns = 700;
+        if (tile_ns < 900) tile_ns = 900;
         long long cost = waves * (4000 + s * tile_ns) + 100LL * splits;
+        // spans that are not combined inside clusters (too many, or their blocks would not all be resident: the launcher's
+        // rule) are combined by a kernel of its own, which costs that much more than the exchange inside a cluster (4
+        // requests at 8,192 keys: 7 spans in clusters 3.62 ms a step, 8 spans and the merge kernel 3.72 ms; but one request
+        // at 2,048 keys: 16 spans and the merge kernel 3.07 ms, 8 spans in a cluster 3.13 ms)
+        if (splits > ATT_CLUSTER_MAX || ctas + 8LL * (splits - 1) > 2LL * xr_sm_count()) cost += 700;
         if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = s; }
     }
     return best * ATT_TILE;
@@ -498,7 +505,6 @@ __device__ __forceinline__ bool att_mbar_wait(uint64_t* bar, uint32_t parity) {
 // block is to finish, and its rows' (maximum, sum) pairs, into that block's shared memory; after one cluster barrier
 // each block weighs and adds what it received, in ascending span order, and writes its slice of the output rows.
 // The partial results then never leave the SMs and no merge kernel follows.
-#define ATT_CLUSTER_MAX 8
 __device__ __forceinline__ uint32_t att_map_to_rank(const void* mine, uint32_t rank) {
     uint32_t remote;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(att_smem_u32(mine)), "r"(rank));
@@ -1417,7 +1423,12 @@ static int launch_keys_tma(const AttnMmaArgs& a, const void* cache_base, long lo
     // co-scheduling of a cluster's blocks costs more than the merge kernel it saves -- batch 64 at a context of 704:
     // 53 us as clusters of four against 37 + 8 us with the merge kernel)
     (void)fit;
-    if (a.max_splits <= ATT_CLUSTER_MAX && att_cluster_merge_enabled() && (a.max_splits == 1 || ctas <= (long long)fit_recv * xr_sm_count())) {
+    // (a cluster's blocks lie in one of the machine's eight or so groups of SMs, so each group may leave up to a
+    // cluster less one of its slots unused: 8 spans for each of 32 (request, kv head) pairs are 256 blocks for 296
+    // slots, and inside a step, where a few slots are still held by the kernels around it, some clusters waited for
+    // others to end -- 131,072 keys, 4 requests: 16.8 ms a step against 14.7 with 5 spans each)
+    const long long packing = 8LL * (a.max_splits - 1);
+    if (a.max_splits <= ATT_CLUSTER_MAX && att_cluster_merge_enabled() && (a.max_splits == 1 || ctas + packing <= (long long)fit_recv * xr_sm_count())) {
         // the spans of a request as one cluster, which also combines them (returns 2: no merge kernel is to follow)
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = grid; cfg.blockDim = dim3(ATT_THREADS); cfg.stream = stream;
