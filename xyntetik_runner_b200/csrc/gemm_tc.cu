@@ -755,7 +755,7 @@ static TcPlan plan_product(int n, int n_out, int K, bool gated, int force_splits
         for (int sp = 1; sp <= max_s; sp++) {
             long long rounds = (tiles * sp + slots - 1) / slots;
             long long cost = rounds * (6 + (pl.total_kb + sp - 1) / sp);
-            if (sp > 1) cost += pl.pair ? 15 + sp * per_slice / 170000 : finish + sp * per_slice / 700000;
+            if (sp > 1) cost += pl.pair ? finish + sp * per_slice / 170000 : finish + sp * per_slice / 700000;
             if (best_cost < 0 || cost < best_cost) { best_cost = cost; splits = sp; }
         }
     }
