@@ -17,7 +17,8 @@ def bf16_round(a: torch.Tensor) -> torch.Tensor:
 @pytest.mark.parametrize("n,n_out,k", [(1, 128, 64), (5, 200, 136), (16, 384, 4096), (17, 130, 72), (64, 512, 1024),
                                        (100, 256, 264), (300, 640, 512), (2, 96, 8), (200, 384, 512), (520, 100, 200), (1030, 300, 72),
                                        # more tiles than CTA pairs (80, 90, 80 and 192 on 74): the pairs walk them in rounds
-                                       (1100, 4000, 512), (2300, 2560, 136), (1100, 4000, 1024), (2048, 6144, 1024)])
+                                       (1100, 4000, 512), (2300, 2560, 136), (1100, 4000, 1024), (2048, 6144, 1024),
+                                       (512, 9688, 1024)])          # two tiles more than a round of 74 pairs, the last row tile ragged
 @pytest.mark.parametrize("epi", ["store_bf16", "store_f32", "add", "bias"])
 def test_gemm_tc(n, n_out, k, epi):
     from xyntetik_runner_b200 import kernels
@@ -59,7 +60,7 @@ def _activation(name, g):
 
 
 @pytest.mark.parametrize("act", ["silu", "gelu_tanh", "none"])
-@pytest.mark.parametrize("n,F,k", [(1, 128, 64), (7, 176, 72), (3, 40, 72), (5, 64, 64), (8, 200, 1024), (16, 1000, 520), (33, 300, 256), (256, 256, 128), (70, 1024, 512), (300, 200, 264), (600, 384, 128), (2500, 2000, 192), (2048, 4800, 1024)])
+@pytest.mark.parametrize("n,F,k", [(1, 128, 64), (7, 176, 72), (3, 40, 72), (5, 64, 64), (8, 200, 1024), (16, 1000, 520), (33, 300, 256), (256, 256, 128), (70, 1024, 512), (300, 200, 264), (600, 384, 128), (2500, 2000, 192), (2048, 4800, 1024), (512, 4840, 1024)])
 def test_gemm_tc_gated(n, F, k, act):
     """out = act(x . W_gate) * (x . W_up) in the product's epilogue, on the packed layout that interleaves gate and
     up rows (64 features per 128-row tile), uncut and cut along K, for every activation."""

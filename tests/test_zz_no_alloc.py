@@ -35,7 +35,8 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_twice():
     # rule -- and one that is not cut at all
     cases = [(8, 512, 4096, 0, torch.bfloat16), (5, 256, 2048, 1, torch.float32), (8, 512, 4096, 0, torch.bfloat16),
              (200, 1024, 8192, 0, torch.bfloat16), (256, 2048, 4096, 1, torch.float32), (300, 512, 8192, 0, torch.float32),
-             (700, 4096, 512, 0, torch.bfloat16), (200, 1024, 8192, 0, torch.bfloat16)]
+             (700, 4096, 512, 0, torch.bfloat16), (200, 1024, 8192, 0, torch.bfloat16),
+             (512, 9688, 1024, 1, torch.float32)]            # (two tiles more than a round of the CTA pairs)
     cut = 0
     for call, (n, n_out, k, epi, out_dt) in enumerate(cases):
         x = torch.randn(n, k, generator=g).to(torch.bfloat16).to(dev)
