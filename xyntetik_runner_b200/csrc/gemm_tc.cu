@@ -416,8 +416,8 @@ __device__ __forceinline__ void mbar_arrive_remote(uint32_t bar_cluster_addr) {
 // have fewer tiles than the machine has CTA pairs); items are ordered slice by slice and within a slice token tile
 // fastest, so that clusters working at the same time share rows of W, and K ranges, in L2.  The ring
 // of stages runs on across tiles (the producer fetches the next tile's operands while the epilogue of this one
-// runs), and the single product keeps two accumulators in tensor memory, so that the MMAs of the next tile
-// overlap the epilogue too; the SwiGLU product fills tensor memory with one pair of accumulators and waits.
+// runs), and two accumulators are kept in tensor memory, so that the MMAs of the next tile overlap the epilogue
+// too (a gated product as well: its gate and up rows are interleaved in one tile, so it has one accumulator a tile).
 template <int STAGES>
 __global__ void __launch_bounds__(TC2_THREADS, 1)
 k_gemm_tc_pair(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcParams p) {
