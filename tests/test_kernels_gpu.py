@@ -441,6 +441,30 @@ def test_attention_finds_a_far_key(kind):
         assert float(err) <= 1.2e-2, (key_pos, float(err))
 
 
+def test_decode_attention_in_spans_of_many_counts():
+    """Twenty steps drawn at random (1 to 9 requests, 1 to 8 kv heads, up to 9,000 keys): the launcher cuts them into 3
+    to 30 spans a request, combined inside clusters of every size up to eight or by the merge kernel.  Every request's
+    query has one key that carries its weight."""
+    from xyntetik_runner_b200 import kernels
+    seen = set()
+    for seed in range(20):
+        rng = np.random.RandomState(5000 + seed)
+        K, G = int(rng.choice([1, 2, 4, 8])), int(rng.choice([1, 2, 4]))
+        hd, page = int(rng.choice([64, 128])), int(rng.choice([16, 64]))
+        n = int(rng.randint(1, 9))
+        top = int(rng.choice([600, 2500, 9000]))
+        segs = [(int(rng.randint(top // 3, top)), 1) for _ in range(n)]
+        if rng.rand() < 0.3:
+            segs.append((int(rng.randint(0, 50)), 1))
+        spikes = [(s, 0, int(rng.randint(0, p0 + 1)), 9.0) for s, (p0, L) in enumerate(segs)]
+        case = _paged_case(300 + seed, K * G, K, hd, page, segs, torch.bfloat16, 0, spikes=spikes)
+        seen.add(kernels.attention_mma_splits(case["max_len"], 0, len(segs) * K))
+        got = _run_attention(case, "mma", K * G, K, hd, page, 0, torch.bfloat16, tma=True)
+        err = (got - case["ref"]).abs().max(dim=1).values / case["ref"].abs().max(dim=1).values
+        assert float(err.max()) <= 2e-2, (seed, K, G, hd, page, segs, float(err.max()))
+    assert len([n for n in seen if n <= 8]) >= 4 and len([n for n in seen if n > 8]) >= 4, sorted(seen)
+
+
 @pytest.mark.parametrize("key_pos", [3, 65537, 131071])
 def test_decode_attention_over_a_hundred_thousand_keys(key_pos):
     """Contexts far beyond those of the other cases (Llama-3.1 allows 131,072 positions): one request with 131,072 keys
