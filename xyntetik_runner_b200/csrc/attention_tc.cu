@@ -6,15 +6,14 @@
 // halves of Q, K, V and O), heads per kv head dividing 128, a power-of-two page size >= 8.
 //
 // A CTA owns 128 packed rows (token i / G, head i % G) of one (request, kv head) and walks its keys in tiles
-// of 128, in ascending order.  Roles (192 threads):
+// of 128, in ascending order.  Roles (352 threads):
 //   warps 0..7 : softmax.  Row r = tensor-memory lane r is shared by two threads (warps w and w + 4 may both
 //                read lanes 32 (w % 4) ..): one takes keys 0..63 of a tile, the other keys 64..127; they
 //                exchange their maxima through shared memory.  Per tile: read S, running maximum, rescale O in
 //                tensor memory when needed, write P = exp(S - m) as bfloat16 over the first 64 columns of the
 //                tile's own S in tensor memory (row = lane, two values per column), where the product reads it
-//                as its A operand.  One softmax warp per scheduler could not hide its own latencies; two can.
-//                (A variant that passes P through shared memory, K-major with the 128-byte swizzle, is kept for
-//                comparisons: XRB200_ATTENTION_P_SMEM=1.)
+//                as its A operand (half the shared-memory traffic of P V against P passed through shared memory, and
+//                no stores of P there).  One softmax warp per scheduler could not hide its own latencies; two can.
 //   warp 8     : one lane issues the TMA copies of Q (once) and of the K tiles (two-stage ring; a K stage is free
 //                as soon as its Q K^T has run, so the next-but-one tile's keys are fetched two tiles ahead).
 //   warp 9     : one lane issues the matrix instructions; the warp owns the tensor-memory allocation.
@@ -154,14 +153,12 @@ __host__ __device__ constexpr uint32_t ta_idesc(bool b_mn, int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
 
-// P_TMEM: P is written over the first 64 columns of its tile's S in tensor memory and read from there by the
-// product (half the shared-memory traffic of P V, no P stores to shared memory); else through shared memory.
 // HD: head size, 64 or 128.  Shared memory keeps the layout of head size 128 (a stage of K or V is two halves
 // apart); at head size 64 only the first half of each is filled and read.
-template <bool P_TMEM, int HD>
+template <int HD>
 __global__ void __launch_bounds__(TA_THREADS, 1)
 k_attention_tc(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map, AttnTcArgs a) {
-    // 14 half tiles of 16 KB leave no room for alignment slack: the array is declared 1 KB aligned (what the
+    // 10 half tiles of 16 KB; the array is declared 1 KB aligned (what the
     // swizzled TMA boxes and the matrix descriptors need) and the kernel refuses to run if it is not
     extern __shared__ __align__(1024) uint8_t ta_smem_raw[];
     uint8_t* smem = ta_smem_raw;
@@ -173,8 +170,7 @@ k_attention_tc(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     constexpr int NH = HD / 64;                           // 64-column halves of a head
     static_assert(HD == 64 || HD == 128, "head size 64 or 128");
     uint8_t* q_s = smem;                                  // [2 halves][128 rows][128 B]
-    uint8_t* p_s = q_s + 2 * HALF;                        // [2 buffers][2 halves (keys 0-63, 64-127)][128 rows][128 B]
-    uint8_t* k_s = p_s + 4 * HALF;                        // [2 stages][2 halves (hd)][128 keys][128 B]
+    uint8_t* k_s = q_s + 2 * HALF;                        // [2 stages][2 halves (hd)][128 keys][128 B]
     uint8_t* v_s = k_s + 4 * HALF;                        // [2 stages][2 halves (hd)][128 keys][128 B]
     uint64_t* bars = (uint64_t*)(v_s + 4 * HALF);
     uint64_t* q_full = bars;            // 1
@@ -287,16 +283,15 @@ k_attention_tc(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
                 // S of the next tile while the softmax of this one runs: its buffer was released by p_full(j-1),
                 // which this thread waited for in the previous round
                 if (j + 1 < n_tiles) issue_qk(j + 1);
-                ta_wait(p_full, j & 1, gave_up);                    // P(j) is in shared memory, S(j) has been read
+                ta_wait(p_full, j & 1, gave_up);                    // P(j) is in tensor memory, S(j) has been read
                 ta_wait(&v_full[s], (j >> 1) & 1, gave_up);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                uint32_t pa = ta_smem(p_s + (j & 1) * 2 * HALF), vb = ta_smem(v_s + s * 2 * HALF);
+                uint32_t vb = ta_smem(v_s + s * 2 * HALF);
                 const uint32_t tm_p = (j & 1) ? tm_s1 : tm_s0;
 #pragma unroll
                 for (int kk = 0; kk < TA_KEYS / 16; kk++) {
                     uint64_t bd = ta_desc_mn(vb + kk * 16 * 128, HALF);
-                    if (P_TMEM) ta_mma_ts(tm_o, tm_p + kk * 8, bd, id_pv, (j > 0 || kk > 0) ? 1u : 0u);
-                    else ta_mma(tm_o, ta_desc_k(pa + (kk >> 2) * HALF + (kk & 3) * 32), bd, id_pv, (j > 0 || kk > 0) ? 1u : 0u);
+                    ta_mma_ts(tm_o, tm_p + kk * 8, bd, id_pv, (j > 0 || kk > 0) ? 1u : 0u);
                 }
                 ta_commit(&pv_done[j & 1]);
             }
@@ -363,11 +358,8 @@ k_attention_tc(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             }
-            // the shared-memory P buffer of this tile was read by the product of tile j - 2 (in tensor memory P lies
-            // over this tile's own S, which the tensor core wrote after that product)
-            if (!P_TMEM && j >= 2) ta_wait(&pv_done[j & 1], ((j >> 1) - 1) & 1, gave_up);
+            // (P lies over this tile's own S, which the tensor core wrote after the product of tile j - 2 had read its P)
             const float off = m == -INFINITY ? 0.f : m;
-            uint8_t* rowp = p_s + (j & 1) * 2 * HALF + half * HALF + r * 128;       // this thread's half row of P
             // The probabilities of this thread's 64 keys.  The pass without a mask has no branch inside, so that the
             // compiler can interleave the elements' chains (scale, exp2, sum, round) instead of walking them one by one.
             float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
@@ -398,18 +390,9 @@ k_attention_tc(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
                 }
             }
             sum0 = (sum0 + sum1) + (sum2 + sum3);
-            if (!P_TMEM) {
-                // keys c*32 .. c*32+31 of this half: four 16-byte chunks of the row, swizzled by the row
-#pragma unroll
-                for (int chunk = 0; chunk < 8; chunk++)
-                    *reinterpret_cast<uint4*>(rowp + ((chunk ^ (r & 7)) << 4)) =
-                        make_uint4(pall[chunk * 4], pall[chunk * 4 + 1], pall[chunk * 4 + 2], pall[chunk * 4 + 3]);
-            }
-            if (P_TMEM) {
-                // this thread's 64 probabilities, two per column, over columns 32 half .. 32 half + 31 of the tile's S
-                ta_st32u(((j & 1) ? tm_s1 : tm_s0) + lane_off + half * 32, pall);
-                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-            }
+            // this thread's 64 probabilities, two per column, over columns 32 half .. 32 half + 31 of the tile's S
+            ta_st32u(((j & 1) ? tm_s1 : tm_s0) + lane_off + half * 32, pall);
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             l += sum0;
             if ((t_lo + j) * TA_KEYS + TA_KEYS - 1 > hi) {
                 // The tile runs past the last key.  Probabilities there are zero, but the value rows hold whatever the
@@ -423,7 +406,7 @@ k_attention_tc(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
                     *reinterpret_cast<uint4*>(v_s + (s * 2 + (ch >> 3)) * HALF + row * 128 + (((ch & 7) ^ (row & 7)) << 4)) = make_uint4(0, 0, 0, 0);
                 }
             }
-            // make P (and the cleared rows) visible to the tensor core (async proxy), order the tensor-memory reads, then signal
+            // make the cleared rows visible to the tensor core (async proxy), order the tensor-memory accesses, then signal
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -536,14 +519,11 @@ XR_EXPORT int xr_attention_tc(const void* q, void* out, const void* cache_base, 
     while ((1 << shift) < page_size) shift++;
     AttnTcArgs a{(__nv_bfloat16*)out, seg_start, seg_len, seg_pos0, block_tables, status, H, K, G, max_pages, page_size, shift,
                  window, n_layers, layer, scale * 1.4426950408889634f, n_seg};
-    constexpr int SMEM = 14 * TA_ROWS * 128 + 128 + 2 * 2 * 128 * 4;
+    constexpr int SMEM = 10 * TA_ROWS * 128 + 128 + 2 * 2 * 128 * 4;
     static bool configured = false;
-    const bool p_tmem = true;                  // P stays in tensor memory (the other instantiation passes P through shared memory)
     if (!configured) {
-        if (cudaFuncSetAttribute(k_attention_tc<true, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
-            cudaFuncSetAttribute(k_attention_tc<false, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
-            cudaFuncSetAttribute(k_attention_tc<true, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
-            cudaFuncSetAttribute(k_attention_tc<false, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+        if (cudaFuncSetAttribute(k_attention_tc<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess ||
+            cudaFuncSetAttribute(k_attention_tc<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
             return XR_ERR_LAUNCH;
         configured = true;
     }
@@ -552,12 +532,7 @@ XR_EXPORT int xr_attention_tc(const void* q, void* out, const void* cache_base, 
     long long tiles = row_tiles > 0 ? row_tiles : (((long long)max_seg_len * G + TA_ROWS - 1) / TA_ROWS) * n_seg;
     if (tiles > 0x7fffffffLL) return XR_ERR_ARG;
     const dim3 grid((unsigned)tiles, K, 1);
-    if (hd == 128) {
-        if (p_tmem) xr_launch(k_attention_tc<true, 128>, grid, dim3(TA_THREADS), SMEM, stream, qm, kvm, a);
-        else xr_launch(k_attention_tc<false, 128>, grid, dim3(TA_THREADS), SMEM, stream, qm, kvm, a);
-    } else {
-        if (p_tmem) xr_launch(k_attention_tc<true, 64>, grid, dim3(TA_THREADS), SMEM, stream, qm, kvm, a);
-        else xr_launch(k_attention_tc<false, 64>, grid, dim3(TA_THREADS), SMEM, stream, qm, kvm, a);
-    }
+    if (hd == 128) xr_launch(k_attention_tc<128>, grid, dim3(TA_THREADS), SMEM, stream, qm, kvm, a);
+    else xr_launch(k_attention_tc<64>, grid, dim3(TA_THREADS), SMEM, stream, qm, kvm, a);
     return xr_launch_status();
 }
